@@ -1,0 +1,176 @@
+// Shared device helpers: order-preserving (distance, id) keys, the warp-owned
+// sorted list used for every top-k, and the reference's exact distance chains.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/ferrovec.h"
+
+typedef unsigned long long u64;
+
+namespace fv {
+
+// ---------------------------------------------------------------------------------------------
+// host-side error plumbing
+void set_error(const std::string& msg);
+int fail(int status, const std::string& msg);
+
+#define FV_CUDA(expr)                                                                          \
+  do {                                                                                         \
+    cudaError_t _e = (expr);                                                                   \
+    if (_e != cudaSuccess)                                                                     \
+      return fv::fail(FV_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e));        \
+  } while (0)
+
+#define FV_TRY(expr)            \
+  do {                          \
+    int _s = (expr);            \
+    if (_s != FV_OK) return _s; \
+  } while (0)
+
+inline size_t padded(size_t dim) { return (dim + 7) / 8 * 8; }
+
+// ---------------------------------------------------------------------------------------------
+// keys.  Neighbours are ordered by f32::total_cmp on the distance, then by id
+// (src/vector/mod.rs:60-64).  Mapping the float's bits to an unsigned integer that
+// sorts the same way and putting the id below it turns that order into one u64 compare.
+#define FV_EMPTY_KEY 0xFFFFFFFFFFFFFFFFull
+
+__host__ __device__ __forceinline__ uint32_t order_bits(float f) {
+#ifdef __CUDA_ARCH__
+  uint32_t b = __float_as_uint(f);
+#else
+  uint32_t b;
+  memcpy(&b, &f, 4);
+#endif
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__host__ __device__ __forceinline__ float order_bits_to_float(uint32_t k) {
+  uint32_t b = (k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k;
+#ifdef __CUDA_ARCH__
+  return __uint_as_float(b);
+#else
+  float f;
+  memcpy(&f, &b, 4);
+  return f;
+#endif
+}
+__host__ __device__ __forceinline__ u64 make_key(float d, uint32_t id) {
+  return (u64(order_bits(d)) << 32) | u64(id);
+}
+__host__ __device__ __forceinline__ float key_distance(u64 k) { return order_bits_to_float(uint32_t(k >> 32)); }
+__host__ __device__ __forceinline__ uint32_t key_id(u64 k) { return uint32_t(k & 0xFFFFFFFFull); }
+
+#ifdef __CUDACC__
+#define FV_FULL 0xFFFFFFFFu
+
+__device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+
+// the one dynamic shared-memory array of every kernel
+__device__ __forceinline__ unsigned char* dyn_smem() {
+  extern __shared__ __align__(16) unsigned char fv_dyn_smem[];
+  return fv_dyn_smem;
+}
+
+// ---------------------------------------------------------------------------------------------
+// A sorted list of L keys (ascending) owned by ONE warp, in shared or global memory.
+// All 32 lanes call every function with the same arguments.
+__device__ __forceinline__ void warp_list_init(u64* list, int L) {
+  for (int e = lane_id(); e < L; e += 32) list[e] = FV_EMPTY_KEY;
+  __syncwarp();
+}
+
+// Inserts `key` (must be < list[L-1]) and drops the last entry.  Works from the top chunk of
+// 32 entries downwards so that every read sees the list as it was before the call.
+__device__ __forceinline__ void warp_list_insert(u64* list, int L, u64 key) {
+  const int lane = lane_id();
+  for (int c = (L - 1) >> 5; c >= 0; --c) {
+    const int e = (c << 5) + lane;
+    const u64 cur = (e < L) ? list[e] : FV_EMPTY_KEY;
+    const u64 prev = (e > 0 && e <= L) ? list[e - 1] : 0ull;
+    __syncwarp();
+    if (e < L) {
+      u64 nv = cur;
+      if (!(cur < key)) nv = (e == 0 || prev < key) ? key : prev;
+      list[e] = nv;
+    }
+    const u64 low = __shfl_sync(FV_FULL, cur, 0);
+    __syncwarp();
+    if (low < key) break;
+  }
+}
+
+// Offers the candidates held one per lane (key = FV_EMPTY_KEY for "none") to the list, in lane order.
+// Returns the list's last key afterwards (the admission bound).
+__device__ __forceinline__ u64 warp_list_offer(u64* list, int L, u64 key, u64 bound) {
+  unsigned pending = __ballot_sync(FV_FULL, key < bound);
+  while (pending) {
+    const int src = __ffs(pending) - 1;
+    pending &= pending - 1;
+    const u64 k = __shfl_sync(FV_FULL, key, src);
+    if (k < bound) {
+      warp_list_insert(list, L, k);
+      bound = list[L - 1];
+    }
+  }
+  return bound;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The reference's distance arithmetic (src/kernels.rs:192-231): eight lane accumulators, each a
+// chain of fused multiply-adds over every eighth element, then the fixed pairwise lane sum.
+__device__ __forceinline__ float hsum8(const float* l) {
+  return __fadd_rn(__fadd_rn(__fadd_rn(l[0], l[4]), __fadd_rn(l[2], l[6])),
+                   __fadd_rn(__fadd_rn(l[1], l[5]), __fadd_rn(l[3], l[7])));
+}
+
+template <bool IS_L2>
+__device__ __forceinline__ void dist_step8(float* acc, const float4& a0, const float4& a1, const float4& b0,
+                                           const float4& b1) {
+  if (IS_L2) {
+    float d;
+    d = __fsub_rn(a0.x, b0.x); acc[0] = __fmaf_rn(d, d, acc[0]);
+    d = __fsub_rn(a0.y, b0.y); acc[1] = __fmaf_rn(d, d, acc[1]);
+    d = __fsub_rn(a0.z, b0.z); acc[2] = __fmaf_rn(d, d, acc[2]);
+    d = __fsub_rn(a0.w, b0.w); acc[3] = __fmaf_rn(d, d, acc[3]);
+    d = __fsub_rn(a1.x, b1.x); acc[4] = __fmaf_rn(d, d, acc[4]);
+    d = __fsub_rn(a1.y, b1.y); acc[5] = __fmaf_rn(d, d, acc[5]);
+    d = __fsub_rn(a1.z, b1.z); acc[6] = __fmaf_rn(d, d, acc[6]);
+    d = __fsub_rn(a1.w, b1.w); acc[7] = __fmaf_rn(d, d, acc[7]);
+  } else {
+    acc[0] = __fmaf_rn(a0.x, b0.x, acc[0]);
+    acc[1] = __fmaf_rn(a0.y, b0.y, acc[1]);
+    acc[2] = __fmaf_rn(a0.z, b0.z, acc[2]);
+    acc[3] = __fmaf_rn(a0.w, b0.w, acc[3]);
+    acc[4] = __fmaf_rn(a1.x, b1.x, acc[4]);
+    acc[5] = __fmaf_rn(a1.y, b1.y, acc[5]);
+    acc[6] = __fmaf_rn(a1.z, b1.z, acc[6]);
+    acc[7] = __fmaf_rn(a1.w, b1.w, acc[7]);
+  }
+}
+
+// Distance between `a` (shared or global, 16-byte aligned, pd floats) and row `b` (global).
+template <bool IS_L2>
+__device__ __forceinline__ float exact_distance(const float* __restrict__ a, const float* __restrict__ b, int pd) {
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const float4* a4 = reinterpret_cast<const float4*>(a);
+  const float4* b4 = reinterpret_cast<const float4*>(b);
+#pragma unroll 4
+  for (int c = 0; c < pd / 8; ++c) {
+    const float4 b0 = __ldg(b4 + 2 * c), b1 = __ldg(b4 + 2 * c + 1);
+    const float4 a0 = a4[2 * c], a1 = a4[2 * c + 1];
+    dist_step8<IS_L2>(acc, a0, a1, b0, b1);
+  }
+  const float s = hsum8(acc);
+  return IS_L2 ? s : -s;
+}
+
+__device__ __forceinline__ float exact_distance(int metric, const float* a, const float* b, int pd) {
+  return metric == FV_L2 ? exact_distance<true>(a, b, pd) : exact_distance<false>(a, b, pd);
+}
+#endif  // __CUDACC__
+
+}  // namespace fv

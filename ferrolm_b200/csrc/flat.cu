@@ -1,0 +1,418 @@
+// FlatIndex (src/vector/flat.rs) and the full-precision scan that every index shares.
+//
+// exact_scan_kernel evaluates the reference's distance chain (src/kernels.rs:200-231) for
+// (query, row) pairs and keeps, per query, the L smallest (distance, id) keys.  A warp owns
+// QT queries (in shared memory) and walks rows 32 at a time, one row per lane, so the rows a
+// warp sees have ascending ids and the strict pre-filter of flat.rs:45 is the lexicographic
+// order.  All warps of a block sweep the same rows, so row data is fetched once per block
+// and re-read from L1.
+#include <algorithm>
+
+#include "internal.h"
+
+namespace fv {
+
+template <int QT, bool IS_L2>
+__global__ void __launch_bounds__(128)
+    exact_scan_kernel(const float* __restrict__ rows, size_t n, int pd, const float* __restrict__ queries,
+                      size_t q_stride, const uint32_t* __restrict__ qids, size_t nq, int L, int prefilter_inf,
+                      uint32_t id_base, size_t rows_per_split, u64* __restrict__ parts) {
+  unsigned char* smem_raw = dyn_smem();
+  const int W = blockDim.x >> 5;
+  const int w = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  float* sq = reinterpret_cast<float*>(smem_raw);                               // [W*QT][pd]
+  u64* lists = reinterpret_cast<u64*>(smem_raw + size_t(W) * QT * pd * sizeof(float));  // [W*QT][L]
+
+  const size_t q0 = (size_t(blockIdx.x) * W + w) * QT;  // first query of this warp
+  const int nqw = q0 < nq ? int(min(size_t(QT), nq - q0)) : 0;
+  float* myq = sq + size_t(w) * QT * pd;
+  u64* mylists = lists + size_t(w) * QT * L;
+  for (int qi = 0; qi < QT; ++qi) {
+    if (qi < nqw) {
+      const size_t src = qids ? size_t(qids[q0 + qi]) : (q0 + qi);
+      for (int c = lane; c < pd; c += 32) myq[qi * pd + c] = queries[src * q_stride + c];
+    } else {
+      for (int c = lane; c < pd; c += 32) myq[qi * pd + c] = 0.f;
+    }
+    warp_list_init(mylists + qi * L, L);
+  }
+  __syncwarp();
+  if (nqw == 0) return;
+
+  const size_t r_begin = size_t(blockIdx.y) * rows_per_split;
+  const size_t r_end = min(n, r_begin + rows_per_split);
+  u64 bound[QT];
+#pragma unroll
+  for (int qi = 0; qi < QT; ++qi) bound[qi] = FV_EMPTY_KEY;
+
+  for (size_t r0 = r_begin; r0 < r_end; r0 += 32) {
+    const size_t row = r0 + lane;
+    const bool valid = row < r_end;
+    const float4* b4 = reinterpret_cast<const float4*>(rows + (valid ? row : r_begin) * size_t(pd));
+    float acc[QT][8];
+#pragma unroll
+    for (int qi = 0; qi < QT; ++qi)
+#pragma unroll
+      for (int l = 0; l < 8; ++l) acc[qi][l] = 0.f;
+#pragma unroll 2
+    for (int c = 0; c < pd / 8; ++c) {
+      const float4 b0 = __ldg(b4 + 2 * c), b1 = __ldg(b4 + 2 * c + 1);
+#pragma unroll
+      for (int qi = 0; qi < QT; ++qi) {
+        const float4* a4 = reinterpret_cast<const float4*>(myq + qi * pd) + 2 * c;
+        dist_step8<IS_L2>(acc[qi], a4[0], a4[1], b0, b1);
+      }
+    }
+#pragma unroll
+    for (int qi = 0; qi < QT; ++qi) {
+      if (qi < nqw) {
+        float d = hsum8(acc[qi]);
+        if (!IS_L2) d = -d;
+        u64 key = make_key(d, id_base + uint32_t(row));
+        if (!valid || (prefilter_inf && !(d < INFINITY))) key = FV_EMPTY_KEY;
+        bound[qi] = warp_list_offer(mylists + qi * L, L, key, bound[qi]);
+      }
+    }
+  }
+  __syncwarp();
+  const int P = gridDim.y;
+  for (int qi = 0; qi < nqw; ++qi) {
+    u64* dst = parts + ((q0 + qi) * size_t(P) + blockIdx.y) * size_t(L);
+    for (int e = lane; e < L; e += 32) dst[e] = mylists[qi * L + e];
+  }
+}
+
+// One warp per query: the L smallest of P sorted partial lists.
+__global__ void merge_keys_kernel(const u64* __restrict__ parts, int P, int Lin, size_t nq, int Lout,
+                                  u64* __restrict__ out) {
+  unsigned char* smem_raw = dyn_smem();
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t q = size_t(blockIdx.x) * (blockDim.x >> 5) + w;
+  if (q >= nq) return;
+  u64* list = reinterpret_cast<u64*>(smem_raw) + size_t(w) * Lout;
+  warp_list_init(list, Lout);
+  u64 bound = FV_EMPTY_KEY;
+  const u64* src = parts + q * size_t(P) * Lin;
+  const int total = P * Lin;
+  for (int i0 = 0; i0 < total; i0 += 32) {
+    const int i = i0 + lane;
+    const u64 key = i < total ? src[i] : FV_EMPTY_KEY;
+    bound = warp_list_offer(list, Lout, key, bound);
+  }
+  __syncwarp();
+  for (int e = lane; e < Lout; e += 32) out[q * size_t(Lout) + e] = list[e];
+}
+
+__global__ void keys_to_neighbors_kernel(const u64* __restrict__ keys, size_t nq, int L, int k,
+                                         fv_neighbor* __restrict__ out, uint32_t* __restrict__ counts,
+                                         const uint32_t* __restrict__ qids) {
+  const size_t q = blockIdx.x * size_t(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (q >= nq) return;
+  const size_t dst = qids ? size_t(qids[q]) : q;
+  int cnt = 0;
+  for (int e0 = 0; e0 < k; e0 += 32) {
+    const int e = e0 + lane;
+    u64 key = (e < k && e < L) ? keys[q * size_t(L) + e] : FV_EMPTY_KEY;
+    if (e < k) {
+      fv_neighbor nb;
+      if (key == FV_EMPTY_KEY) {
+        nb.id = 0xFFFFFFFFu;
+        nb.distance = INFINITY;
+      } else {
+        nb.id = key_id(key);
+        nb.distance = key_distance(key);
+      }
+      out[dst * size_t(k) + e] = nb;
+    }
+    cnt += __popc(__ballot_sync(FV_FULL, key != FV_EMPTY_KEY));
+  }
+  if (lane == 0 && counts) counts[dst] = uint32_t(cnt);
+}
+
+int keys_to_neighbors(fv_ctx* ctx, const u64* d_keys, size_t nq, int L, int k, fv_neighbor* d_out, uint32_t* d_counts,
+                      const uint32_t* d_query_ids) {
+  if (nq == 0) return FV_OK;
+  const int wpb = 8;
+  keys_to_neighbors_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, 0, ctx->stream>>>(d_keys, nq, L, k, d_out,
+                                                                                         d_counts, d_query_ids);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  return FV_OK;
+}
+
+template <int QT>
+static int launch_scan(fv_ctx* ctx, bool is_l2, dim3 grid, int threads, size_t smem, const float* rows, size_t n, int pd,
+                       const float* q, size_t q_stride, const uint32_t* qids, size_t nq, int L, bool prefilter,
+                       uint32_t id_base, size_t rps, u64* parts) {
+  auto kl2 = exact_scan_kernel<QT, true>;
+  auto kip = exact_scan_kernel<QT, false>;
+  auto k = is_l2 ? kl2 : kip;
+  if (smem > 48 * 1024) FV_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  k<<<grid, threads, smem, ctx->stream>>>(rows, n, pd, q, q_stride, qids, nq, L, prefilter ? 1 : 0, id_base, rps, parts);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  return FV_OK;
+}
+
+int exact_scan(fv_ctx* ctx, int metric, const float* d_rows, size_t n, int pd, const float* d_queries, size_t q_stride,
+               const uint32_t* d_query_ids, size_t nq, int L, bool prefilter_inf, uint32_t id_base, u64* d_out_keys,
+               int scratch_slot) {
+  if (nq == 0) return FV_OK;
+  if (L < 1 || L > 4096) return fail(FV_ERR_UNSUPPORTED, "top-k list length must be in 1..4096");
+  const size_t budget = std::min<size_t>(ctx->smem_optin, 200 * 1024);
+  // choose queries per warp (QT) and warps per block (W) so that queries + lists fit in shared memory
+  int QT = 8, W = 4;
+  auto need = [&](int qt, int w) { return size_t(w) * qt * (size_t(pd) * 4 + size_t(L) * 8); };
+  if (nq <= 8) QT = 2;
+  while (need(QT, W) > budget && W > 1) W >>= 1;
+  if (need(QT, W) > budget) QT = 2;
+  if (need(QT, W) > budget)
+    return fail(FV_ERR_UNSUPPORTED, "dimension and k too large for the shared-memory budget of the scan");
+  const size_t qgroups = (nq + size_t(QT) * W - 1) / (size_t(QT) * W);
+  while (W > 1 && nq <= size_t(QT) * (W / 2)) W >>= 1;  // do not launch warps without queries
+  // split the rows when there are too few query groups to fill the GPU
+  size_t S = 1;
+  const size_t target = size_t(ctx->sm_count) * 4;
+  if (qgroups < target) S = (target + qgroups - 1) / qgroups;
+  const size_t max_split = std::max<size_t>(1, n / 1024);
+  S = std::min(S, max_split);
+  S = std::min<size_t>(S, 4096);
+  size_t rps = (n + S - 1) / S;
+  rps = (rps + 31) / 32 * 32;
+  if (rps == 0) rps = 32;
+  S = std::max<size_t>(1, (n + rps - 1) / rps);
+  u64* parts = d_out_keys;
+  if (S > 1) {
+    FV_TRY(ctx->scratch[scratch_slot].reserve(nq * S * size_t(L) * sizeof(u64)));
+    parts = ctx->scratch[scratch_slot].as<u64>();
+  }
+  dim3 grid(unsigned((nq + size_t(QT) * W - 1) / (size_t(QT) * W)), unsigned(S));
+  const size_t smem = need(QT, W);
+  if (QT == 8)
+    FV_TRY(launch_scan<8>(ctx, metric == FV_L2, grid, W * 32, smem, d_rows, n, pd, d_queries, q_stride, d_query_ids, nq,
+                          L, prefilter_inf, id_base, rps, parts));
+  else
+    FV_TRY(launch_scan<2>(ctx, metric == FV_L2, grid, W * 32, smem, d_rows, n, pd, d_queries, q_stride, d_query_ids, nq,
+                          L, prefilter_inf, id_base, rps, parts));
+  if (S > 1) {
+    int wpb = 4;
+    while (wpb > 1 && size_t(wpb) * L * 8 > 96 * 1024) wpb >>= 1;
+    const size_t msmem = size_t(wpb) * L * 8;
+    if (msmem > 48 * 1024)
+      FV_CUDA(cudaFuncSetAttribute(merge_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(msmem)));
+    merge_keys_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, msmem, ctx->stream>>>(parts, int(S), L, nq, L,
+                                                                                         d_out_keys);
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
+  }
+  return FV_OK;
+}
+
+}  // namespace fv
+
+// ------------------------------------------------------------------------------------------------
+// FlatIndex
+namespace fv {
+struct TcSide;
+}
+
+struct fv_flat {
+  fv_ctx* ctx;
+  int metric;
+  uint32_t dim, pd;
+  size_t n = 0;
+  DevBuf data;  // n * pd f32
+  uint32_t id_base = 0;
+  int mode = 0;
+  fv::TcSide* tc = nullptr;  // tensor-core front end state (gemm_topk.cu)
+};
+
+namespace fv {
+// tensor-core front end (gemm_topk.cu)
+void tc_free(TcSide* tc);
+int tc_append(fv_ctx* ctx, TcSide** tc, int metric, const float* d_rows_new, size_t n_old, size_t n_new, int pd);
+int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n, int pd, const float* d_queries,
+              size_t nq, int k, uint32_t id_base, u64* d_out_keys);
+bool tc_usable(const TcSide* tc, size_t n, size_t nq, int k);
+}  // namespace fv
+
+extern "C" {
+
+int fv_flat_new(fv_ctx* ctx, int metric, uint32_t dim, fv_flat** out) {
+  if (!ctx || !out || dim == 0 || (metric != FV_L2 && metric != FV_INNER_PRODUCT))
+    return fv::fail(FV_ERR_ARG, "fv_flat_new: bad argument");
+  auto* ix = new fv_flat();
+  ix->ctx = ctx;
+  ix->metric = metric;
+  ix->dim = dim;
+  ix->pd = uint32_t(fv::padded(dim));
+  *out = ix;
+  return FV_OK;
+}
+
+void fv_flat_free(fv_flat* ix) {
+  if (!ix) return;
+  fv::DeviceGuard g(ix->ctx->device);
+  cudaStreamSynchronize(ix->ctx->stream);
+  fv::tc_free(ix->tc);
+  delete ix;
+}
+
+static int flat_add_impl(fv_flat* ix, const float* v, size_t n, bool dev) {
+  if (!ix || (!v && n)) return fv::fail(FV_ERR_ARG, "fv_flat_add: null argument");
+  if (n == 0) return FV_OK;
+  if (ix->n + n > 0xFFFFFFF0ull) return fv::fail(FV_ERR_UNSUPPORTED, "more than 2^32 rows");
+  fv_ctx* ctx = ix->ctx;
+  fv::DeviceGuard g(ctx->device);
+  const size_t row = size_t(ix->pd) * sizeof(float);
+  FV_TRY(ix->data.grow((ix->n + n) * row, ix->n * row, ctx->stream));
+  float* dst = ix->data.as<float>() + ix->n * size_t(ix->pd);
+  FV_TRY(fv::upload_padded(ctx, v, dev, n, ix->dim, ix->pd, dst));
+  FV_TRY(fv::tc_append(ctx, &ix->tc, ix->metric, dst, ix->n, n, int(ix->pd)));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  ix->n += n;
+  return FV_OK;
+}
+
+int fv_flat_add(fv_flat* ix, const float* vectors, size_t n) { return flat_add_impl(ix, vectors, n, false); }
+int fv_flat_add_dev(fv_flat* ix, const float* d_vectors, size_t n) { return flat_add_impl(ix, d_vectors, n, true); }
+
+size_t fv_flat_len(const fv_flat* ix) { return ix ? ix->n : 0; }
+
+int fv_flat_vector(const fv_flat* ix, uint32_t id, float* out_padded) {
+  if (!ix || !out_padded || id >= ix->n) return fv::fail(FV_ERR_ARG, "fv_flat_vector: bad argument");
+  fv::DeviceGuard g(ix->ctx->device);
+  FV_CUDA(cudaMemcpy(out_padded, ix->data.as<float>() + size_t(id) * ix->pd, size_t(ix->pd) * sizeof(float),
+                     cudaMemcpyDeviceToHost));
+  return FV_OK;
+}
+
+int fv_flat_set_id_base(fv_flat* ix, uint32_t id_base) {
+  if (!ix) return fv::fail(FV_ERR_ARG, "null index");
+  ix->id_base = id_base;
+  return FV_OK;
+}
+
+int fv_flat_set_mode(fv_flat* ix, int mode) {
+  if (!ix || mode < 0 || mode > 2) return fv::fail(FV_ERR_ARG, "fv_flat_set_mode: mode must be 0, 1 or 2");
+  ix->mode = mode;
+  return FV_OK;
+}
+
+// scratch slots: 0 padded queries, 1 final keys, 2 scan partials, 3.. tensor-core path
+int fv_flat_search_batch_dev(fv_flat* ix, const float* d_queries, size_t nq, size_t k, fv_neighbor* d_out,
+                             uint32_t* d_counts) {
+  if (!ix || (nq && (!d_queries || !d_out))) return fv::fail(FV_ERR_ARG, "fv_flat_search_batch: null argument");
+  if (k == 0) return fv::fail(FV_ERR_ARG, "k must be at least 1");
+  if (k > 4096) return fv::fail(FV_ERR_UNSUPPORTED, "k above 4096 is not supported");
+  if (nq == 0) return FV_OK;
+  fv_ctx* ctx = ix->ctx;
+  fv::DeviceGuard g(ctx->device);
+  ctx->stats = fv_stats{};
+  fv::stage_begin(ctx);
+  const int pd = int(ix->pd);
+  const float* q = d_queries;
+  if (ix->pd != ix->dim) {
+    FV_TRY(ctx->scratch[0].reserve(nq * size_t(pd) * sizeof(float)));
+    FV_TRY(fv::upload_padded(ctx, d_queries, true, nq, ix->dim, ix->pd, ctx->scratch[0].as<float>()));
+    q = ctx->scratch[0].as<float>();
+  }
+  const int L = int(k);
+  FV_TRY(ctx->scratch[1].reserve(nq * size_t(L) * sizeof(u64)));
+  u64* keys = ctx->scratch[1].as<u64>();
+  const bool want_tc = ix->mode == 1 || (ix->mode == 0 && fv::tc_usable(ix->tc, ix->n, nq, L));
+  if (want_tc) {
+    if (!fv::tc_usable(ix->tc, ix->n, nq, L))
+      return fv::fail(FV_ERR_UNSUPPORTED, "tensor-core search needs k <= 32 and at least 4096 rows");
+    FV_TRY(fv::tc_search(ctx, ix->tc, ix->metric, ix->data.as<float>(), ix->n, pd, q, nq, L, ix->id_base, keys));
+  } else {
+    FV_TRY(fv::exact_scan(ctx, ix->metric, ix->data.as<float>(), ix->n, pd, q, size_t(pd), nullptr, nq, L, true,
+                          ix->id_base, keys, 2));
+    fv::stage_mark(ctx);
+  }
+  FV_TRY(fv::keys_to_neighbors(ctx, keys, nq, L, int(k), d_out, d_counts));
+  fv::stage_mark(ctx);
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  fv::stage_end(ctx);
+  return FV_OK;
+}
+
+int fv_flat_search_batch(fv_flat* ix, const float* queries, size_t nq, size_t k, fv_neighbor* out, uint32_t* counts) {
+  if (!ix || (nq && (!queries || !out))) return fv::fail(FV_ERR_ARG, "fv_flat_search_batch: null argument");
+  if (nq == 0) return FV_OK;
+  fv_ctx* ctx = ix->ctx;
+  fv::DeviceGuard g(ctx->device);
+  const size_t qbytes = nq * size_t(ix->dim) * sizeof(float);
+  const size_t obytes = nq * k * sizeof(fv_neighbor);
+  FV_TRY(ctx->scratch[10].reserve(qbytes));
+  FV_TRY(ctx->scratch[11].reserve(obytes + nq * sizeof(uint32_t)));
+  float* dq = ctx->scratch[10].as<float>();
+  fv_neighbor* dout = ctx->scratch[11].as<fv_neighbor>();
+  uint32_t* dc = reinterpret_cast<uint32_t*>(ctx->scratch[11].as<unsigned char>() + obytes);
+  FV_CUDA(cudaMemcpyAsync(dq, queries, qbytes, cudaMemcpyHostToDevice, ctx->stream));
+  FV_TRY(fv_flat_search_batch_dev(ix, dq, nq, k, dout, dc));
+  FV_CUDA(cudaMemcpyAsync(out, dout, obytes, cudaMemcpyDeviceToHost, ctx->stream));
+  if (counts) FV_CUDA(cudaMemcpyAsync(counts, dc, nq * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  return FV_OK;
+}
+
+int fv_flat_search(fv_flat* ix, const float* query, size_t k, fv_neighbor* out, uint32_t* count) {
+  return fv_flat_search_batch(ix, query, 1, k, out, count);
+}
+
+// Merging per-shard results: the k_out best of nparts * k_in candidates per query.
+namespace fv {
+__global__ void merge_parts_kernel(const fv_neighbor* __restrict__ parts, const uint32_t* __restrict__ part_counts,
+                                   int nparts, size_t nq, int k_in, int k_out, u64* __restrict__ out) {
+  unsigned char* smem_raw = dyn_smem();
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t q = size_t(blockIdx.x) * (blockDim.x >> 5) + w;
+  if (q >= nq) return;
+  u64* list = reinterpret_cast<u64*>(smem_raw) + size_t(w) * k_out;
+  warp_list_init(list, k_out);
+  u64 bound = FV_EMPTY_KEY;
+  for (int p = 0; p < nparts; ++p) {
+    const int cnt = part_counts ? int(min(part_counts[size_t(p) * nq + q], uint32_t(k_in))) : k_in;
+    const fv_neighbor* src = parts + (size_t(p) * nq + q) * size_t(k_in);
+    for (int i0 = 0; i0 < cnt; i0 += 32) {
+      const int i = i0 + lane;
+      u64 key = FV_EMPTY_KEY;
+      if (i < cnt) {
+        const fv_neighbor nb = src[i];
+        if (nb.id != 0xFFFFFFFFu) key = make_key(nb.distance, nb.id);
+      }
+      bound = warp_list_offer(list, k_out, key, bound);
+    }
+  }
+  __syncwarp();
+  for (int e = lane; e < k_out; e += 32) out[q * size_t(k_out) + e] = list[e];
+}
+}  // namespace fv
+
+int fv_merge_topk_dev(fv_ctx* ctx, const fv_neighbor* d_parts, const uint32_t* d_part_counts, size_t nparts, size_t nq,
+                      size_t k_in, size_t k_out, fv_neighbor* d_out, uint32_t* d_counts) {
+  if (!ctx || !d_parts || !d_out || nparts == 0 || k_in == 0 || k_out == 0)
+    return fv::fail(FV_ERR_ARG, "fv_merge_topk_dev: bad argument");
+  if (k_out > 4096) return fv::fail(FV_ERR_UNSUPPORTED, "k above 4096 is not supported");
+  if (nq == 0) return FV_OK;
+  fv::DeviceGuard g(ctx->device);
+  FV_TRY(ctx->scratch[1].reserve(nq * k_out * sizeof(u64)));
+  u64* keys = ctx->scratch[1].as<u64>();
+  int wpb = 4;
+  while (wpb > 1 && size_t(wpb) * k_out * 8 > 96 * 1024) wpb >>= 1;
+  const size_t smem = size_t(wpb) * k_out * 8;
+  if (smem > 48 * 1024)
+    FV_CUDA(cudaFuncSetAttribute(fv::merge_parts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  fv::merge_parts_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, smem, ctx->stream>>>(
+      d_parts, d_part_counts, int(nparts), nq, int(k_in), int(k_out), keys);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  FV_TRY(fv::keys_to_neighbors(ctx, keys, nq, int(k_out), int(k_out), d_out, d_counts));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  return FV_OK;
+}
+
+}  // extern "C"

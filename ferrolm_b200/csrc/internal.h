@@ -1,0 +1,124 @@
+// Host-side internals shared by the translation units of libferrovec.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+// A growable device allocation (raw bytes).
+struct DevBuf {
+  void* p = nullptr;
+  size_t cap = 0;
+  ~DevBuf() { release(); }
+  DevBuf() = default;
+  DevBuf(const DevBuf&) = delete;
+  DevBuf& operator=(const DevBuf&) = delete;
+  void release() {
+    if (p) cudaFree(p);
+    p = nullptr;
+    cap = 0;
+  }
+  // Makes room for `bytes`; contents are NOT kept.
+  int reserve(size_t bytes) {
+    if (bytes <= cap) return FV_OK;
+    release();
+    size_t want = bytes + bytes / 8 + 256;
+    cudaError_t e = cudaMalloc(&p, want);
+    if (e != cudaSuccess) {
+      p = nullptr;
+      (void)cudaGetLastError();
+      return fv::fail(FV_ERR_NOMEM, "cudaMalloc of " + std::to_string(want) + " bytes: " + cudaGetErrorString(e));
+    }
+    cap = want;
+    return FV_OK;
+  }
+  // Makes room for `bytes`, keeping the first `keep` bytes.
+  int grow(size_t bytes, size_t keep, cudaStream_t s) {
+    if (bytes <= cap) return FV_OK;
+    size_t want = bytes > 2 * cap ? bytes : 2 * cap;
+    void* np = nullptr;
+    cudaError_t e = cudaMalloc(&np, want);
+    if (e != cudaSuccess && want > bytes) {
+      (void)cudaGetLastError();
+      want = bytes;
+      e = cudaMalloc(&np, want);
+    }
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      return fv::fail(FV_ERR_NOMEM, "cudaMalloc of " + std::to_string(want) + " bytes: " + cudaGetErrorString(e));
+    }
+    if (keep && p) {
+      e = cudaMemcpyAsync(np, p, keep, cudaMemcpyDeviceToDevice, s);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+      if (e != cudaSuccess) {
+        cudaFree(np);
+        return fv::fail(FV_ERR_CUDA, std::string("device copy while growing: ") + cudaGetErrorString(e));
+      }
+    }
+    if (p) cudaFree(p);
+    p = np;
+    cap = want;
+    return FV_OK;
+  }
+  template <class T>
+  T* as() const {
+    return static_cast<T*>(p);
+  }
+};
+
+enum { FV_NSCRATCH = 12, FV_NSTAGE = 8 };
+
+struct fv_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  int sm_count = 0;
+  size_t smem_optin = 0;
+  DevBuf scratch[FV_NSCRATCH];  // reused between calls; indices are private to each search routine
+  fv_stats stats{};
+  bool timing = false;
+  cudaEvent_t ev[FV_NSTAGE + 1] = {};
+  int ev_used = 0;
+  int* d_flags = nullptr;  // small device word array for error / overflow flags
+};
+
+namespace fv {
+
+// RAII: makes the context's device current for the duration of a call.
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+// stage timing helpers (no-ops unless ctx->timing)
+void stage_begin(fv_ctx* ctx);
+void stage_mark(fv_ctx* ctx);  // closes the current stage
+void stage_end(fv_ctx* ctx);   // after the stream is synchronised: fills stats.stage_ms
+
+// ---- the full-precision scan (flat.cu): for every query the L best rows by (distance, id).
+// d_out_keys: nq * L keys, ascending, FV_EMPTY_KEY padded.  `prefilter_inf`: a distance must be
+// < +inf to enter (flat.rs:45); off for the coarse quantizer, where every cell is pushed (ivfpq.rs:213).
+// `d_query_ids` (optional) selects a subset of the query rows: query i is d_queries[d_query_ids[i]].
+int exact_scan(fv_ctx* ctx, int metric, const float* d_rows, size_t n, int pd, const float* d_queries,
+               size_t q_stride, const uint32_t* d_query_ids, size_t nq, int L, bool prefilter_inf,
+               uint32_t id_base, u64* d_out_keys, int scratch_slot);
+
+// keys -> fv_neighbor rows and counts.  in: nq * L keys (ascending), out: nq * k neighbours.
+int keys_to_neighbors(fv_ctx* ctx, const u64* d_keys, size_t nq, int L, int k, fv_neighbor* d_out,
+                      uint32_t* d_counts, const uint32_t* d_query_ids = nullptr);
+
+// pads rows of `dim` floats to `pd` on the device (host or device source)
+int upload_padded(fv_ctx* ctx, const float* src, bool src_is_device, size_t n, size_t dim, size_t pd, float* d_dst);
+
+}  // namespace fv

