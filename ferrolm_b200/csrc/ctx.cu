@@ -1,5 +1,6 @@
 // Context, error reporting and the small host-side helpers of src/vector/mod.rs.
 #include <cmath>
+#include <mutex>
 #include <thread>
 #include <unordered_set>
 
@@ -13,6 +14,19 @@ void set_error(const std::string& msg) { g_error = msg; }
 int fail(int status, const std::string& msg) {
   g_error = msg;
   return status;
+}
+
+static std::mutex g_ctx_mutex;
+}  // namespace fv
+static void ctx_destroy_now(fv_ctx* ctx);
+namespace fv {
+void ctx_retain(fv_ctx* ctx) {
+  std::lock_guard<std::mutex> g(g_ctx_mutex);
+  ctx->refs++;
+}
+void ctx_release(fv_ctx* ctx) {
+  std::lock_guard<std::mutex> g(g_ctx_mutex);
+  if (--ctx->refs == 0 && ctx->closing) ctx_destroy_now(ctx);
 }
 
 void stage_begin(fv_ctx* ctx) {
@@ -65,6 +79,17 @@ int upload_padded(fv_ctx* ctx, const float* src, bool src_is_device, size_t n, s
 
 }  // namespace fv
 
+static void ctx_destroy_now(fv_ctx* ctx) {
+  fv::DeviceGuard g(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  for (auto& b : ctx->scratch) b.release();
+  for (auto& ev : ctx->ev)
+    if (ev) cudaEventDestroy(ev);
+  if (ctx->d_flags) cudaFree(ctx->d_flags);
+  cudaStreamDestroy(ctx->stream);
+  delete ctx;
+}
+
 extern "C" {
 
 const char* fv_last_error(void) { return fv::g_error.c_str(); }
@@ -109,14 +134,12 @@ int fv_ctx_create(int device, fv_ctx** out) {
 
 void fv_ctx_destroy(fv_ctx* ctx) {
   if (!ctx) return;
-  fv::DeviceGuard g(ctx->device);
-  cudaStreamSynchronize(ctx->stream);
-  for (auto& b : ctx->scratch) b.release();
-  for (auto& ev : ctx->ev)
-    if (ev) cudaEventDestroy(ev);
-  if (ctx->d_flags) cudaFree(ctx->d_flags);
-  cudaStreamDestroy(ctx->stream);
-  delete ctx;
+  std::lock_guard<std::mutex> g(fv::g_ctx_mutex);
+  if (ctx->refs > 0) {
+    ctx->closing = true;  // freed with the last index
+    return;
+  }
+  ctx_destroy_now(ctx);
 }
 
 int fv_ctx_device(const fv_ctx* ctx) { return ctx ? ctx->device : -1; }

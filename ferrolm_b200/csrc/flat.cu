@@ -248,6 +248,7 @@ int fv_flat_new(fv_ctx* ctx, int metric, uint32_t dim, fv_flat** out) {
   ix->metric = metric;
   ix->dim = dim;
   ix->pd = uint32_t(fv::padded(dim));
+  fv::ctx_retain(ctx);
   *out = ix;
   return FV_OK;
 }
@@ -257,7 +258,9 @@ void fv_flat_free(fv_flat* ix) {
   fv::DeviceGuard g(ix->ctx->device);
   cudaStreamSynchronize(ix->ctx->stream);
   fv::tc_free(ix->tc);
+  fv_ctx* ctx = ix->ctx;
   delete ix;
+  fv::ctx_release(ctx);
 }
 
 static int flat_add_impl(fv_flat* ix, const float* v, size_t n, bool dev) {

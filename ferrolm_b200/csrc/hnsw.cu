@@ -241,6 +241,10 @@ static inline bool h_less(const HNb& a, const HNb& b) {
 
 struct fv_hnsw {
   fv_ctx* ctx = nullptr;
+  ~fv_hnsw() {
+    d_data.release(); d_links0.release(); d_upper_off.release(); d_upper_flat.release();
+    if (ctx) fv::ctx_release(ctx);
+  }
   int metric = 0;
   uint32_t dim = 0, pd = 0;
   size_t m = 0, m0 = 0;
@@ -562,6 +566,7 @@ int fv_hnsw_build(fv_ctx* ctx, int metric, uint32_t dim, const float* vectors, s
   if (p->m < 2 || p->m > 64) return fv::fail(FV_ERR_UNSUPPORTED, "m must be in 2..64");
   auto h = std::unique_ptr<fv_hnsw>(new fv_hnsw());
   h->ctx = ctx;
+  fv::ctx_retain(ctx);
   h->metric = metric;
   h->dim = dim;
   h->pd = uint32_t(fv::padded(dim));
@@ -752,6 +757,7 @@ int fv_hnsw_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_hnsw** out) {
   const char* trunc = "index file is truncated";
   auto h = std::unique_ptr<fv_hnsw>(new fv_hnsw());
   h->ctx = ctx;
+  fv::ctx_retain(ctx);
   const uint32_t mc = u32();
   h->dim = u32();
   h->m = u32();

@@ -84,6 +84,8 @@ struct fv_ctx {
   cudaEvent_t ev[FV_NSTAGE + 1] = {};
   int ev_used = 0;
   int* d_flags = nullptr;  // small device word array for error / overflow flags
+  int refs = 0;            // indexes alive on this context
+  bool closing = false;    // fv_ctx_destroy was called while indexes were alive
 };
 
 namespace fv {
@@ -100,6 +102,10 @@ struct DeviceGuard {
     if (prev >= 0) cudaSetDevice(prev);
   }
 };
+
+// Indexes keep their context alive: destruction is deferred until the last one is freed.
+void ctx_retain(fv_ctx* ctx);
+void ctx_release(fv_ctx* ctx);
 
 // stage timing helpers (no-ops unless ctx->timing)
 void stage_begin(fv_ctx* ctx);

@@ -381,6 +381,11 @@ __global__ void __launch_bounds__(128) ivfpq_scan_kernel(ScanArgs a) {
 // ------------------------------------------------------------------------------------------------
 struct fv_ivfpq {
   fv_ctx* ctx = nullptr;
+  ~fv_ivfpq() {
+    centroids.release(); codebooks.release(); pre.release(); list_off.release();
+    codes.release(); ids.release(); vectors.release();
+    if (ctx) fv::ctx_release(ctx);
+  }
   int metric = 0;
   uint32_t dim = 0, pd = 0;
   size_t nlist = 0, m = 0, dsub = 0;
@@ -492,6 +497,7 @@ int fv_ivfpq_train(fv_ctx* ctx, int metric, uint32_t dim, const float* sample, s
   ctx->stats = fv_stats{};
   auto ix = std::unique_ptr<fv_ivfpq>(new fv_ivfpq());
   ix->ctx = ctx;
+  fv::ctx_retain(ctx);
   ix->metric = metric;
   ix->dim = dim;
   ix->pd = uint32_t(pd);
@@ -845,6 +851,7 @@ int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out)
   const char* trunc = "index file is truncated";
   auto ix = std::unique_ptr<fv_ivfpq>(new fv_ivfpq());
   ix->ctx = ctx;
+  fv::ctx_retain(ctx);
   const uint32_t mc = u32();
   ix->dim = u32();
   ix->nlist = u32();
