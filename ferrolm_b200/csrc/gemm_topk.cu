@@ -1,11 +1,807 @@
-// placeholder for the tensor-core front end; replaced by the tcgen05 implementation
+// Tensor-core front end of exact search (flat.rs:40-53 at batch scale).
+//
+//   scores(q, b) = ||b||^2 - 2 <q, b>      (L2; the per-query constant ||q||^2 is left out)
+//                = -<q, b>                 (inner product)
+//
+// computed as a 16-bit-input, fp32-accumulate GEMM on the 5th-generation tensor cores:
+// tcgen05.mma issued by one thread, operands staged in shared memory by TMA with the 128-byte
+// swizzle, accumulators in tensor memory.  The epilogue reads the accumulators back with
+// tcgen05.ld (one query row per thread), adds the row norms and keeps, per query and per work
+// segment, the KP smallest (score, id) pairs in registers.  A second kernel recomputes the
+// reference's exact fp32 distance chain (src/kernels.rs:200-231) for those candidates, picks the
+// k best by (distance, id) and CERTIFIES the result: a query passes only if every row that was
+// not a candidate is provably farther than its k-th result.  Queries that do not pass are
+// re-run by the full-precision scan, so the tensor cores never decide a result on their own.
+//
+// Work split: a unit is (query tile, 256 base rows).  Units are laid out query-tile major and cut
+// into equal contiguous runs, one per CTA (persistent, one CTA per SM); a run inside one query
+// tile is a segment and owns one candidate list per query.
+//
+// Two tilings share the code:
+//   MH = 2: 256 queries per tile, kept in shared memory for the whole segment (K <= 128);
+//           the two 128-row halves use the two accumulator slots, so each B tile is read once
+//           from L2 for 256 queries.
+//   MH = 1: 128 queries per tile (K <= 384); the two accumulator slots alternate between tiles.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cmath>
+
 #include "internal.h"
+
 namespace fv {
-struct TcSide {};
-void tc_free(TcSide* tc) { delete tc; }
-int tc_append(fv_ctx*, TcSide**, int, const float*, size_t, size_t, int) { return FV_OK; }
-int tc_search(fv_ctx*, TcSide*, int, const float*, size_t, int, const float*, size_t, int, uint32_t, u64*) {
-  return fail(FV_ERR_UNSUPPORTED, "tensor-core search is not built");
+
+static constexpr int KP = 16;          // candidates kept per query and segment
+static constexpr int TILE_N = 256;     // base rows per unit
+static constexpr int KBLK = 64;        // k elements per shared-memory block (128 bytes)
+static constexpr int A_BLOCK_BYTES = 128 * 128;   // 128 rows x 128 B
+static constexpr int B_STAGE_BYTES = TILE_N * 128;
+static constexpr int NTHREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+static constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s; then the kernel gives up
+
+// ------------------------------------------------------------------------------------------------
+// PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
-bool tc_usable(const TcSide*, size_t, size_t, int) { return false; }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another thread already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 lanes x 32 columns of 32-bit accumulators: thread l of the warp gets lane (base + l), columns c..c+31
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float min3(float a, float b, float c) {
+  float r;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, groups of
+// 8 rows 1024 bytes apart; bits 46-47 carry the descriptor version of this architecture.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= uint64_t((saddr & 0x3FFFF) >> 4);  // start address
+  d |= uint64_t(1) << 16;                 // leading byte offset (unused with swizzle): 1
+  d |= uint64_t(1024 >> 4) << 32;         // stride byte offset
+  d |= uint64_t(1) << 46;                 // version
+  d |= uint64_t(2) << 61;                 // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulate, A and B both K-major, M x N tile.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (uint32_t(n >> 3) << 17) |
+         (uint32_t(m >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------------------------
+struct GemmParams {
+  int n, nq;
+  int KB;          // 64-wide k blocks
+  int NT;          // base tiles of 256 rows
+  int MT;          // query tiles of 128 * MH rows
+  long long U;     // MT * NT units
+  long long upc;   // units per CTA
+  int segmax;      // candidate segments per CTA
+  int nstage;
+  float scale;     // -2 (L2) or -1 (inner product)
+  uint32_t idesc;
+  const float* bnorm;  // padded to a multiple of 256 with +inf
+  u64* cand;           // [grid * segmax][256][KP]
+  int* err;            // set to 1 when a bounded wait ran out
+};
+
+struct __align__(8) Barriers {
+  uint64_t full[8], empty[8];
+  uint64_t a_full, a_empty;
+  uint64_t tfull[2], tempty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int MH>
+__global__ void __launch_bounds__(NTHREADS, 1)
+    gemm_topk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  unsigned char* raw = dyn_smem();
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sA = base;                                            // [MH][KB] blocks of 16 KB
+  unsigned char* sB = sA + size_t(MH) * p.KB * A_BLOCK_BYTES;          // [nstage] stages of 32 KB
+  Barriers* bars = reinterpret_cast<Barriers*>(sB + size_t(p.nstage) * B_STAGE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long u0 = blockIdx.x * p.upc;
+  const long long u1 = min(p.U, u0 + p.upc);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.nstage; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->a_full, 1);
+    mbar_init(&bars->a_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->tfull[s], 1);
+      mbar_init(&bars->tempty[s], MH == 2 ? 4 : 8);
+    }
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {  // the MMA warp owns the tensor memory: all 512 columns (one CTA per SM)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&bars->tmem_base))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      long long it = 0;
+      int seg = 0, cur_mt = -1;
+      bool ok = true;
+      for (long long u = u0; u < u1 && ok; ++u) {
+        const int mt = int(u / p.NT), nt = int(u % p.NT);
+        if (mt != cur_mt) {
+          ok = mbar_wait(&bars->a_empty, (seg & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(&bars->a_full, uint32_t(MH * p.KB * A_BLOCK_BYTES));
+          for (int mh = 0; mh < MH; ++mh)
+            for (int kb = 0; kb < p.KB; ++kb)
+              tma_load_2d(sA + size_t(mh * p.KB + kb) * A_BLOCK_BYTES, &tmA, &bars->a_full, kb * KBLK,
+                          (mt * MH + mh) * 128);
+          cur_mt = mt;
+          seg++;
+        }
+        for (int kb = 0; kb < p.KB; ++kb, ++it) {
+          const int s = int(it % p.nstage);
+          ok = mbar_wait(&bars->empty[s], (uint32_t(it / p.nstage) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(&bars->full[s], uint32_t(B_STAGE_BYTES));
+          tma_load_2d(sB + size_t(s) * B_STAGE_BYTES, &tmB, &bars->full[s], kb * KBLK, nt * TILE_N);
+        }
+      }
+      // Do not leave while copies may still land in this CTA's shared memory: wait (bounded) until the
+      // MMA side has consumed everything that was issued, or until the abort flag says nobody will.
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      long long it = 0, job = 0;
+      int seg = 0, cur_mt = -1;
+      bool ok = true;
+      const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB);
+      for (long long u = u0; u < u1 && ok; ++u) {
+        const int mt = int(u / p.NT);
+        if (mt != cur_mt) {
+          ok = mbar_wait(&bars->a_full, seg & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          cur_mt = mt;
+          seg++;
+        }
+        for (int mh = 0; mh < MH && ok; ++mh, ++job) {
+          const int slot = int(job & 1);
+          ok = mbar_wait(&bars->tempty[slot], (uint32_t(job >> 1) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + uint32_t(slot * TILE_N);
+          for (int kb = 0; kb < p.KB; ++kb) {
+            const long long itk = it + kb;
+            const int s = int(itk % p.nstage);
+            if (mh == 0) {
+              ok = mbar_wait(&bars->full[s], uint32_t(itk / p.nstage) & 1, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+            }
+            const uint32_t a_addr = a_base + uint32_t((mh * p.KB + kb) * A_BLOCK_BYTES);
+            const uint32_t b_addr = b_base + uint32_t(s * B_STAGE_BYTES);
+#pragma unroll
+            for (int k4 = 0; k4 < KBLK / 16; ++k4)
+              tc_mma_f16(d_tmem, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), p.idesc,
+                         (kb | k4) != 0 ? 1u : 0u);
+            if (mh == MH - 1) tc_commit(&bars->empty[s]);  // the stage is free once these MMAs have read it
+          }
+          if (!ok) break;
+          tc_commit(&bars->tfull[slot]);
+        }
+        it += p.KB;
+        const bool last_of_segment = (u + 1 == u1) || int((u + 1) / p.NT) != mt;
+        if (ok && last_of_segment) tc_commit(&bars->a_empty);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue: 8 warps, one query row per thread
+    const int ew = warp - 2;
+    const int quad = warp & 3;   // tensor-memory lanes this warp may read: 32 * quad .. +31
+    const int grp = ew >> 2;     // MH = 2: which 128-row half (= accumulator slot); MH = 1: which column half
+    const int e = grp * 128 + quad * 32 + lane;  // list index inside a segment
+    const uint32_t lane_addr = uint32_t(quad * 32) << 16;
+    u64 lst[KP];
+    float thr = INFINITY;
+#pragma unroll
+    for (int j = 0; j < KP; ++j) lst[j] = FV_EMPTY_KEY;
+    long long tile_idx = 0;
+    int cur_mt = -1, seg_local = -1;
+    bool ok = true;
+    const int ncol = MH == 2 ? TILE_N : TILE_N / 2;
+    const int col0 = MH == 2 ? 0 : grp * (TILE_N / 2);
+    for (long long u = u0; u < u1 && ok; ++u, ++tile_idx) {
+      const int mt = int(u / p.NT), nt = int(u % p.NT);
+      if (mt != cur_mt) {
+        cur_mt = mt;
+        seg_local++;
+        thr = INFINITY;
+#pragma unroll
+        for (int j = 0; j < KP; ++j) lst[j] = FV_EMPTY_KEY;
+      }
+      const long long job = MH == 2 ? tile_idx * 2 + grp : tile_idx;
+      const int slot = int(job & 1);
+      ok = mbar_wait(&bars->tfull[slot], uint32_t(job >> 1) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t row_base = uint32_t(nt) * TILE_N + col0;
+      for (int c = 0; c < ncol; c += 32) {
+        float v[32];
+        tc_ld32(tmem_base + lane_addr + uint32_t(slot * TILE_N + col0 + c), v);
+        const float4* nrm = reinterpret_cast<const float4*>(p.bnorm + row_base + c);
+        float m = INFINITY;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 nn = __ldg(nrm + i);
+          v[4 * i + 0] = __fmaf_rn(v[4 * i + 0], p.scale, nn.x);
+          v[4 * i + 1] = __fmaf_rn(v[4 * i + 1], p.scale, nn.y);
+          v[4 * i + 2] = __fmaf_rn(v[4 * i + 2], p.scale, nn.z);
+          v[4 * i + 3] = __fmaf_rn(v[4 * i + 3], p.scale, nn.w);
+          m = fminf(min3(m, v[4 * i + 0], v[4 * i + 1]), fminf(v[4 * i + 2], v[4 * i + 3]));
+        }
+        if (m < thr) {
+          // rare path: insert the passing columns, in ascending id order, into the sorted register list
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (v[i] < thr) {
+              u64 key = make_key(v[i], row_base + uint32_t(c + i));
+#pragma unroll
+              for (int j = 0; j < KP; ++j) {
+                const u64 cur = lst[j];
+                const bool lt = key < cur;
+                lst[j] = lt ? key : cur;
+                key = lt ? cur : key;
+              }
+              thr = lst[KP - 1] == FV_EMPTY_KEY ? INFINITY : key_distance(lst[KP - 1]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tempty[slot]);
+      const bool last_of_segment = (u + 1 == u1) || int((u + 1) / p.NT) != mt;
+      if (last_of_segment) {
+        u64* dst = p.cand + ((size_t(blockIdx.x) * p.segmax + seg_local) * 256 + e) * KP;
+#pragma unroll
+        for (int j = 0; j < KP; j += 2) *reinterpret_cast<ulonglong2*>(dst + j) = make_ulonglong2(lst[j], lst[j + 1]);
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 1);
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// fp32 rows -> 16-bit operand rows (zero padded to Kp), squared norms and range statistics
+struct RangeStats {
+  float min_v, max_v;      // over all values seen
+  float max_norm2;         // largest squared row norm
+  int not_integer;         // some value is not integer-valued
+  int not_finite;
+};
+
+__device__ __forceinline__ void atomic_min_f(float* a, float v) {
+  if (v >= 0) atomicMin(reinterpret_cast<int*>(a), __float_as_int(v));
+  else atomicMax(reinterpret_cast<unsigned*>(a), __float_as_uint(v));
+}
+__device__ __forceinline__ void atomic_max_f(float* a, float v) {
+  if (v >= 0) atomicMax(reinterpret_cast<int*>(a), __float_as_int(v));
+  else atomicMin(reinterpret_cast<unsigned*>(a), __float_as_uint(v));
+}
+
+// one warp per row
+template <bool BF16>
+__global__ void convert_rows_kernel(const float* __restrict__ src, size_t n, int pd, int Kp, uint16_t* __restrict__ dst,
+                                    float* __restrict__ norm2, int is_l2, RangeStats* __restrict__ st) {
+  const int lane = threadIdx.x & 31;
+  const size_t row = blockIdx.x * size_t(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n) return;
+  float s = 0.f, mn = INFINITY, mx = -INFINITY;
+  int bad_int = 0, bad_fin = 0;
+  for (int c = lane; c < Kp; c += 32) {
+    float x = c < pd ? src[row * size_t(pd) + c] : 0.f;
+    if (c < pd) {
+      s = __fmaf_rn(x, x, s);
+      mn = fminf(mn, x);
+      mx = fmaxf(mx, x);
+      if (x != rintf(x)) bad_int = 1;
+      if (!(fabsf(x) <= 3.0e38f)) bad_fin = 1;
+    }
+    uint16_t h;
+    if (BF16) h = __bfloat16_as_ushort(__float2bfloat16_rn(x));
+    else h = __half_as_ushort(__float2half_rn(x));
+    dst[row * size_t(Kp) + c] = h;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_xor_sync(FV_FULL, s, o);
+    mn = fminf(mn, __shfl_xor_sync(FV_FULL, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(FV_FULL, mx, o));
+    bad_int |= __shfl_xor_sync(FV_FULL, bad_int, o);
+    bad_fin |= __shfl_xor_sync(FV_FULL, bad_fin, o);
+  }
+  if (lane == 0) {
+    if (norm2) norm2[row] = is_l2 ? s : 0.f;
+    atomic_min_f(&st->min_v, mn);
+    atomic_max_f(&st->max_v, mx);
+    atomic_max_f(&st->max_norm2, s);
+    if (bad_int) st->not_integer = 1;
+    if (bad_fin) st->not_finite = 1;
+  }
+}
+
+__global__ void fill_f32_kernel(float* p, size_t n, float v) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) p[i] = v;
+}
+
+__global__ void init_stats_kernel(RangeStats* st) {
+  st->min_v = INFINITY;
+  st->max_v = -INFINITY;
+  st->max_norm2 = 0.f;
+  st->not_integer = 0;
+  st->not_finite = 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Exact re-rank and certification: one warp per query.
+struct RerankParams {
+  const u64* cand;
+  const float* rows;      // n x pd fp32
+  const float* queries;   // nq x pd fp32
+  const float* qnorm2;    // nq (0 for inner product)
+  const RangeStats* bst;  // base statistics
+  const RangeStats* qst;  // query statistics
+  int n, nq, pd, Kp, k, MH, NT, segmax, is_l2, bf16;
+  long long upc;
+  uint32_t id_base;
+  u64* out_keys;          // nq x k
+  uint32_t* retry_ids;    // queries that did not certify
+  unsigned int* retry_count;
+};
+
+__global__ void rerank_kernel(RerankParams p) {
+  unsigned char* smem_raw = dyn_smem();
+  const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t q = size_t(blockIdx.x) * W + w;
+  if (q >= size_t(p.nq)) return;
+  float* sq = reinterpret_cast<float*>(smem_raw) + size_t(w) * p.pd;
+  u64* list = reinterpret_cast<u64*>(smem_raw + size_t(W) * p.pd * sizeof(float)) + size_t(w) * p.k;
+  for (int c = lane; c < p.pd; c += 32) sq[c] = p.queries[q * size_t(p.pd) + c];
+  warp_list_init(list, p.k);
+
+  // exact-arithmetic regime: integer-valued inputs small enough that every product, partial sum and
+  // distance is an integer below 2^24 in both the tensor-core score and the reference's fp32 chain
+  const float lo = fminf(p.bst->min_v, p.qst->min_v), hi = fmaxf(p.bst->max_v, p.qst->max_v);
+  const float mabs = fmaxf(fabsf(lo), fabsf(hi)), range = hi - lo;
+  const bool exact_regime = !p.bst->not_integer && !p.qst->not_integer && !p.bst->not_finite && !p.qst->not_finite &&
+                            mabs <= (p.bf16 ? 256.f : 2048.f) && float(p.Kp) * mabs * mabs <= 8388608.f &&
+                            float(p.Kp) * range * range < 16777216.f;
+  const float qn2 = p.qnorm2[q];
+  // error bound of a score against the reference distance (minus ||q||^2 for L2) outside that regime
+  const float u16 = p.bf16 ? 0.00390625f : 0.00048828125f;
+  const float qn = sqrtf(p.is_l2 ? qn2 : 0.f), bn = sqrtf(p.bst->max_norm2);
+  float eps;
+  {
+    // inner-product case needs the query norm too; it is recomputed here from the staged query
+    float s = 0.f;
+    for (int c = lane; c < p.pd; c += 32) s = __fmaf_rn(sq[c], sq[c], s);
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FV_FULL, s, o);
+    const float qnorm = p.is_l2 ? qn : sqrtf(s);
+    const float kf = float(p.Kp);
+    const float e_dot = (2.f * u16 * (1.f + u16) + kf * 4.7683716e-7f + kf * 1.1920929e-7f) * qnorm * bn +
+                        5.9604645e-8f * sqrtf(kf) * (qnorm + bn);
+    eps = p.is_l2 ? 2.f * e_dot + kf * 2.3841858e-7f * (qnorm * qnorm + bn * bn) * 2.f : e_dot;
+    eps = eps * 1.01f + 1e-30f;
+  }
+
+  const int rows_per_tile = 128 * p.MH;
+  const int mt = int(q / rows_per_tile), r = int(q % rows_per_tile);
+  const long long ub = (long long)mt * p.NT, ue = ub + p.NT - 1;
+  const int c_lo = int(ub / p.upc), c_hi = int(ue / p.upc);
+  const int lists_per_seg = p.MH == 2 ? 1 : 2;
+  float tau = INFINITY;   // smallest "last kept score" over the lists: every row outside the lists scores >= tau
+  bool mismatch = false;  // exact regime only: a score that is not the exact distance
+  u64 bound = FV_EMPTY_KEY;
+  for (int c = c_lo; c <= c_hi; ++c) {
+    const int seg_local = mt - int((c * p.upc) / p.NT);
+    for (int li = 0; li < lists_per_seg; ++li) {
+      const int e = li * 128 + r;
+      const u64* src = p.cand + ((size_t(c) * p.segmax + seg_local) * 256 + e) * KP;
+      u64 ck = lane < KP ? src[lane] : FV_EMPTY_KEY;
+      const u64 last = __shfl_sync(FV_FULL, ck, KP - 1);
+      if (last != FV_EMPTY_KEY) tau = fminf(tau, key_distance(last));
+      u64 key = FV_EMPTY_KEY;
+      if (ck != FV_EMPTY_KEY) {
+        const uint32_t id = key_id(ck);
+        float d;
+        if (id < uint32_t(p.n)) {
+          d = p.is_l2 ? exact_distance<true>(sq, p.rows + size_t(id) * p.pd, p.pd)
+                      : exact_distance<false>(sq, p.rows + size_t(id) * p.pd, p.pd);
+          if (exact_regime && d != key_distance(ck) + qn2) mismatch = true;
+          if (d < INFINITY) key = make_key(d, id + p.id_base);
+        } else {
+          mismatch = true;  // a padded row can only get here through a non-finite score
+        }
+      }
+      bound = warp_list_offer(list, p.k, key, bound);
+    }
+  }
+  __syncwarp();
+  mismatch = __any_sync(FV_FULL, mismatch);
+  const u64 kth = list[p.k - 1];
+  bool certified;
+  if (tau == INFINITY) {
+    certified = true;  // no list was full: every row of the index was a candidate
+  } else if (exact_regime) {
+    certified = !mismatch;  // scores are the distances (shifted by ||q||^2) and lists are (score, id) exact
+  } else {
+    certified = kth != FV_EMPTY_KEY && (key_distance(kth) - qn2) + eps < tau;
+  }
+  if (mismatch && exact_regime) certified = false;
+  for (int e = lane; e < p.k; e += 32) p.out_keys[q * size_t(p.k) + e] = list[e];
+  if (!certified && lane == 0) {
+    const unsigned int slot = atomicAdd(p.retry_count, 1u);
+    p.retry_ids[slot] = uint32_t(q);
+  }
+}
+
+__global__ void scatter_keys_kernel(const u64* __restrict__ src, const uint32_t* __restrict__ qids, size_t nsub, int L,
+                                    u64* __restrict__ dst) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < nsub * L; i += size_t(gridDim.x) * blockDim.x) {
+    const size_t s = i / L;
+    dst[size_t(qids[s]) * L + (i - s * L)] = src[i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// rows x Kp 16-bit matrix, boxes of `box_rows` rows x 64 elements, 128-byte swizzle
+static int make_tmap(CUtensorMap* map, bool bf16, void* ptr, size_t rows, int Kp, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(FV_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[2] = {cuuint64_t(Kp), cuuint64_t(rows)};
+  cuuint64_t gstride[1] = {cuuint64_t(Kp) * 2};
+  cuuint32_t box[2] = {cuuint32_t(KBLK), cuuint32_t(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ptr, gdim, gstride,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FV_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+  return FV_OK;
+}
+
+struct TcSide {
+  int pd = 0, Kp = 0;
+  bool bf16 = false;
+  size_t n = 0;            // rows converted
+  DevBuf half;             // n_cap x Kp 16-bit
+  DevBuf norm2;            // padded to 256, +inf beyond n
+  DevBuf stats;            // RangeStats (base), RangeStats (queries), retry counter, error word
+  RangeStats h_stats{};
+};
+
+void tc_free(TcSide* tc) { delete tc; }
+
+static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+static int convert(fv_ctx* ctx, bool bf16, const float* d_src, size_t n, int pd, int Kp, uint16_t* dst, float* norm2,
+                   bool is_l2, RangeStats* st) {
+  if (n == 0) return FV_OK;
+  const int wpb = 8;
+  const unsigned blocks = unsigned((n + wpb - 1) / wpb);
+  if (bf16)
+    convert_rows_kernel<true><<<blocks, wpb * 32, 0, ctx->stream>>>(d_src, n, pd, Kp, dst, norm2, is_l2 ? 1 : 0, st);
+  else
+    convert_rows_kernel<false><<<blocks, wpb * 32, 0, ctx->stream>>>(d_src, n, pd, Kp, dst, norm2, is_l2 ? 1 : 0, st);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  return FV_OK;
+}
+
+// Called by FlatIndex::add after the fp32 rows are in place.  d_rows_new points at the new rows.
+int tc_append(fv_ctx* ctx, TcSide** ptc, int metric, const float* d_rows_new, size_t n_old, size_t n_new, int pd) {
+  const int Kp = round_up(pd, KBLK);
+  if (Kp > 384) return FV_OK;  // beyond the tilings of this kernel: such an index uses the scan only
+  if (!*ptc) {
+    *ptc = new TcSide();
+    (*ptc)->pd = pd;
+    (*ptc)->Kp = Kp;
+  }
+  TcSide* tc = *ptc;
+  const size_t total = n_old + n_new;
+  if (!tc->stats.p) {
+    FV_TRY(tc->stats.reserve(256));
+    init_stats_kernel<<<1, 1, 0, ctx->stream>>>(tc->stats.as<RangeStats>());
+    FV_CUDA(cudaGetLastError());
+  }
+  FV_TRY(tc->half.grow(total * size_t(Kp) * 2 + 1024, n_old * size_t(Kp) * 2, ctx->stream));
+  const size_t npad = (total + TILE_N - 1) / TILE_N * TILE_N + TILE_N;
+  FV_TRY(tc->norm2.grow(npad * sizeof(float), n_old * sizeof(float), ctx->stream));
+  // pick the operand type from the range of the NEW rows first (fp16 unless the values do not fit)
+  DevBuf tmp_stats;
+  FV_TRY(tmp_stats.reserve(sizeof(RangeStats)));
+  init_stats_kernel<<<1, 1, 0, ctx->stream>>>(tmp_stats.as<RangeStats>());
+  FV_CUDA(cudaGetLastError());
+  uint16_t* dst = tc->half.as<uint16_t>() + n_old * size_t(Kp);
+  float* nrm = tc->norm2.as<float>() + n_old;
+  FV_TRY(convert(ctx, tc->bf16, d_rows_new, n_new, pd, Kp, dst, nrm, metric == FV_L2, tmp_stats.as<RangeStats>()));
+  RangeStats hs;
+  FV_CUDA(cudaMemcpyAsync(&hs, tmp_stats.p, sizeof(hs), cudaMemcpyDeviceToHost, ctx->stream));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  const float mabs = std::max(std::fabs(hs.min_v), std::fabs(hs.max_v));
+  const bool need_bf16 = !(mabs <= 32768.f);
+  if (need_bf16 && !tc->bf16) {
+    // values beyond the fp16 range: the whole operand copy becomes bf16.  The caller passes the new rows
+    // only, so the old ones are re-read from the fp32 matrix that precedes them in the same allocation.
+    tc->bf16 = true;
+    const float* all_rows = d_rows_new - n_old * size_t(pd);
+    init_stats_kernel<<<1, 1, 0, ctx->stream>>>(tc->stats.as<RangeStats>());
+    FV_TRY(convert(ctx, true, all_rows, total, pd, Kp, tc->half.as<uint16_t>(), tc->norm2.as<float>(), metric == FV_L2,
+                   tc->stats.as<RangeStats>()));
+  } else {
+    // fold the new rows' statistics into the running ones
+    FV_CUDA(cudaMemcpyAsync(&tc->h_stats, tc->stats.p, sizeof(RangeStats), cudaMemcpyDeviceToHost, ctx->stream));
+    FV_CUDA(cudaStreamSynchronize(ctx->stream));
+    RangeStats m = tc->h_stats;
+    m.min_v = std::min(m.min_v, hs.min_v);
+    m.max_v = std::max(m.max_v, hs.max_v);
+    m.max_norm2 = std::max(m.max_norm2, hs.max_norm2);
+    m.not_integer |= hs.not_integer;
+    m.not_finite |= hs.not_finite;
+    FV_CUDA(cudaMemcpyAsync(tc->stats.p, &m, sizeof(m), cudaMemcpyHostToDevice, ctx->stream));
+    FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  }
+  fill_f32_kernel<<<8, 256, 0, ctx->stream>>>(tc->norm2.as<float>() + total, npad - total, INFINITY);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  tc->n = total;
+  return FV_OK;
+}
+
+bool tc_usable(const TcSide* tc, size_t n, size_t nq, int k) {
+  (void)nq;
+  return tc && tc->n == n && k <= KP && n >= 4096 && n <= 0x7FFFFF00ull;
+}
+
+// scratch slots: 2 scan partials (fallback), 3 A operand, 5 query norms, 6 candidates, 7 retry ids, 8 fallback keys
+int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n, int pd, const float* d_queries,
+              size_t nq, int k, uint32_t id_base, u64* d_out_keys) {
+  const int Kp = tc->Kp;
+  const int KB = Kp / KBLK;
+  const int MH = KB <= 2 ? 2 : 1;
+  const int rows_per_tile = 128 * MH;
+  const int MT = int((nq + rows_per_tile - 1) / rows_per_tile);
+  const int NT = int((n + TILE_N - 1) / TILE_N);
+  const long long U = (long long)MT * NT;
+  const int grid = int(std::min<long long>(ctx->sm_count, U));
+  const long long upc = (U + grid - 1) / grid;
+  const int segmax = int((upc + NT - 1) / NT) + 1;
+  const size_t a_bytes = size_t(MH) * KB * A_BLOCK_BYTES;
+  const size_t budget = ctx->smem_optin;
+  int nstage = int((budget - 2048 - a_bytes) / B_STAGE_BYTES);
+  nstage = std::min(nstage, 8);
+  if (nstage < 2) return fail(FV_ERR_UNSUPPORTED, "not enough shared memory for the tensor-core tiling");
+  const size_t smem = 1024 + a_bytes + size_t(nstage) * B_STAGE_BYTES + sizeof(Barriers) + 64;
+
+  // queries -> 16-bit operand rows (padded to whole tiles with zeros), norms, statistics
+  const size_t nq_pad = size_t(MT) * rows_per_tile;
+  FV_TRY(ctx->scratch[3].reserve(nq_pad * size_t(Kp) * 2));
+  FV_TRY(ctx->scratch[5].reserve(nq_pad * sizeof(float)));
+  uint16_t* dA = ctx->scratch[3].as<uint16_t>();
+  float* qn2 = ctx->scratch[5].as<float>();
+  RangeStats* bst = tc->stats.as<RangeStats>();
+  RangeStats* qst = bst + 1;
+  unsigned int* retry_count = reinterpret_cast<unsigned int*>(qst + 1);
+  int* err = reinterpret_cast<int*>(retry_count + 1);
+  init_stats_kernel<<<1, 1, 0, ctx->stream>>>(qst);
+  FV_CUDA(cudaMemsetAsync(retry_count, 0, 8, ctx->stream));
+  if (nq_pad > nq) FV_CUDA(cudaMemsetAsync(dA + nq * size_t(Kp), 0, (nq_pad - nq) * size_t(Kp) * 2, ctx->stream));
+  FV_TRY(convert(ctx, tc->bf16, d_queries, nq, pd, Kp, dA, qn2, metric == FV_L2, qst));
+  stage_mark(ctx);
+
+  FV_TRY(ctx->scratch[6].reserve(size_t(grid) * segmax * 256 * KP * sizeof(u64)));
+  CUtensorMap tmA, tmB;
+  FV_TRY(make_tmap(&tmA, tc->bf16, dA, nq_pad, Kp, 128));
+  FV_TRY(make_tmap(&tmB, tc->bf16, tc->half.p, n, Kp, TILE_N));
+  GemmParams gp{};
+  gp.n = int(n);
+  gp.nq = int(nq);
+  gp.KB = KB;
+  gp.NT = NT;
+  gp.MT = MT;
+  gp.U = U;
+  gp.upc = upc;
+  gp.segmax = segmax;
+  gp.nstage = nstage;
+  gp.scale = metric == FV_L2 ? -2.f : -1.f;
+  gp.idesc = make_idesc(128, TILE_N, tc->bf16);
+  gp.bnorm = tc->norm2.as<float>();
+  gp.cand = ctx->scratch[6].as<u64>();
+  gp.err = err;
+  if (MH == 2) {
+    FV_CUDA(cudaFuncSetAttribute(gemm_topk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    gemm_topk_kernel<2><<<grid, NTHREADS, smem, ctx->stream>>>(tmA, tmB, gp);
+  } else {
+    FV_CUDA(cudaFuncSetAttribute(gemm_topk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    gemm_topk_kernel<1><<<grid, NTHREADS, smem, ctx->stream>>>(tmA, tmB, gp);
+  }
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  stage_mark(ctx);
+
+  FV_TRY(ctx->scratch[7].reserve(nq * sizeof(uint32_t)));
+  RerankParams rp{};
+  rp.cand = gp.cand;
+  rp.rows = d_rows;
+  rp.queries = d_queries;
+  rp.qnorm2 = qn2;
+  rp.bst = bst;
+  rp.qst = qst;
+  rp.n = int(n);
+  rp.nq = int(nq);
+  rp.pd = pd;
+  rp.Kp = Kp;
+  rp.k = k;
+  rp.MH = MH;
+  rp.NT = NT;
+  rp.segmax = segmax;
+  rp.is_l2 = metric == FV_L2 ? 1 : 0;
+  rp.bf16 = tc->bf16 ? 1 : 0;
+  rp.upc = upc;
+  rp.id_base = id_base;
+  rp.out_keys = d_out_keys;
+  rp.retry_ids = ctx->scratch[7].as<uint32_t>();
+  rp.retry_count = retry_count;
+  int wpb = 8;
+  while (wpb > 1 && size_t(wpb) * (size_t(pd) * 4 + size_t(k) * 8) > 48 * 1024) wpb >>= 1;
+  const size_t rsmem = size_t(wpb) * (size_t(pd) * 4 + size_t(k) * 8);
+  rerank_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, rsmem, ctx->stream>>>(rp);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  stage_mark(ctx);
+
+  unsigned int h_words[2] = {0, 0};  // retry count, error word
+  FV_CUDA(cudaMemcpyAsync(h_words, retry_count, sizeof(h_words), cudaMemcpyDeviceToHost, ctx->stream));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  if (h_words[1]) return fail(FV_ERR_TIMEOUT, "a bounded wait inside the tensor-core kernel ran out");
+  ctx->stats.uncertified = h_words[0];
+  if (h_words[0]) {
+    const size_t nsub = h_words[0];
+    FV_TRY(ctx->scratch[8].reserve(nsub * size_t(k) * sizeof(u64)));
+    u64* sub = ctx->scratch[8].as<u64>();
+    FV_TRY(exact_scan(ctx, metric, d_rows, n, pd, d_queries, size_t(pd), rp.retry_ids, nsub, k, true, id_base, sub, 2));
+    scatter_keys_kernel<<<ctx->sm_count, 256, 0, ctx->stream>>>(sub, rp.retry_ids, nsub, k, d_out_keys);
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
+  }
+  stage_mark(ctx);
+  return FV_OK;
+}
+
 }  // namespace fv
