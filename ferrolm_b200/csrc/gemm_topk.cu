@@ -28,16 +28,20 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 
 #include "internal.h"
 
 namespace fv {
 
-static constexpr int KP = 16;          // candidates kept per query and segment
+static constexpr int KP = 16;          // candidate slots per query and segment in the candidate buffer
+static constexpr int NORM_RING = 4;    // row-norm tiles (1 KB each) kept in shared memory
 static constexpr int TILE_N = 256;     // base rows per unit
 static constexpr int KBLK = 64;        // k elements per shared-memory block (128 bytes)
 static constexpr int A_BLOCK_BYTES = 128 * 128;   // 128 rows x 128 B
 static constexpr int B_STAGE_BYTES = TILE_N * 128;
+static constexpr int SCRATCH_BYTES = 8 * 16 * 32 * 4;  // per epilogue warp: 16 columns x 32 rows of scores
 static constexpr int NTHREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 static constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s; then the kernel gives up
 
@@ -90,6 +94,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       : "memory");
 }
 
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -110,9 +121,10 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
       : "memory");
 }
 
-// 32 lanes x 32 columns of 32-bit accumulators: thread l of the warp gets lane (base + l), columns c..c+31
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
-  uint32_t r[32];
+// 32 lanes x 32 columns of 32-bit accumulators: thread l of the warp gets lane (base + l), columns c..c+31.
+// The load is asynchronous: the registers are valid only after tc_ld_wait on the same array, which takes
+// them as in/out operands so that no use can be scheduled ahead of the wait.
+__device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -123,9 +135,16 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tc_ld_wait(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]),
+                 "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
+                 "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
 }
 
 __device__ __forceinline__ float min3(float a, float b, float c) {
@@ -177,14 +196,16 @@ struct __align__(8) Barriers {
   int abort_flag;
 };
 
-template <int MH>
+template <int MH, int KPT>
 __global__ void __launch_bounds__(NTHREADS, 1)
     gemm_topk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   unsigned char* raw = dyn_smem();
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sA = base;                                            // [MH][KB] blocks of 16 KB
   unsigned char* sB = sA + size_t(MH) * p.KB * A_BLOCK_BYTES;          // [nstage] stages of 32 KB
-  Barriers* bars = reinterpret_cast<Barriers*>(sB + size_t(p.nstage) * B_STAGE_BYTES);
+  unsigned char* scratch = sB + size_t(p.nstage) * B_STAGE_BYTES;   // 8 epilogue warps x 4 KB
+  float* snorm = reinterpret_cast<float*>(scratch + SCRATCH_BYTES);  // [NORM_RING][256]
+  Barriers* bars = reinterpret_cast<Barriers*>(scratch + SCRATCH_BYTES + NORM_RING * TILE_N * 4);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -219,10 +240,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      long long it = 0;
+      long long it = 0, tile_idx = 0;
       int seg = 0, cur_mt = -1;
       bool ok = true;
-      for (long long u = u0; u < u1 && ok; ++u) {
+      for (long long u = u0; u < u1 && ok; ++u, ++tile_idx) {
         const int mt = int(u / p.NT), nt = int(u % p.NT);
         if (mt != cur_mt) {
           ok = mbar_wait(&bars->a_empty, (seg & 1) ^ 1, abort_flag);
@@ -239,7 +260,13 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           const int s = int(it % p.nstage);
           ok = mbar_wait(&bars->empty[s], (uint32_t(it / p.nstage) & 1) ^ 1, abort_flag);
           if (!ok) break;
-          mbar_expect_tx(&bars->full[s], uint32_t(B_STAGE_BYTES));
+          // The unit's row norms ride on the barrier of its first k block.  A ring slot is reused NORM_RING
+          // units later; by then the epilogue of that unit is long done, because this stage could only be
+          // refilled after the MMAs of the unit nstage / KB back, which waited for the epilogues before it.
+          mbar_expect_tx(&bars->full[s], uint32_t(B_STAGE_BYTES + (kb == 0 ? TILE_N * 4 : 0)));
+          if (kb == 0)
+            bulk_load_1d(snorm + (tile_idx % NORM_RING) * TILE_N, p.bnorm + size_t(nt) * TILE_N, TILE_N * 4,
+                         &bars->full[s]);
           tma_load_2d(sB + size_t(s) * B_STAGE_BYTES, &tmB, &bars->full[s], kb * KBLK, nt * TILE_N);
         }
       }
@@ -304,10 +331,17 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     const int grp = ew >> 2;     // MH = 2: which 128-row half (= accumulator slot); MH = 1: which column half
     const int e = grp * 128 + quad * 32 + lane;  // list index inside a segment
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
-    u64 lst[KP];
+    // the KPT best (score, id) of this thread's query row in the current segment, ascending by score;
+    // rows arrive in ascending id order, so a strict score compare keeps the (score, id) order
+    float sc[KPT];
+    uint32_t idv[KPT];
     float thr = INFINITY;
+    float* sv = reinterpret_cast<float*>(scratch) + size_t(ew) * 512;  // 16 columns x 32 rows of scores
 #pragma unroll
-    for (int j = 0; j < KP; ++j) lst[j] = FV_EMPTY_KEY;
+    for (int j = 0; j < KPT; ++j) {
+      sc[j] = INFINITY;
+      idv[j] = 0xFFFFFFFFu;
+    }
     long long tile_idx = 0;
     int cur_mt = -1, seg_local = -1;
     bool ok = true;
@@ -320,7 +354,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         seg_local++;
         thr = INFINITY;
 #pragma unroll
-        for (int j = 0; j < KP; ++j) lst[j] = FV_EMPTY_KEY;
+        for (int j = 0; j < KPT; ++j) {
+          sc[j] = INFINITY;
+          idv[j] = 0xFFFFFFFFu;
+        }
       }
       const long long job = MH == 2 ? tile_idx * 2 + grp : tile_idx;
       const int slot = int(job & 1);
@@ -328,37 +365,68 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       if (!ok) break;
       tc_fence_after();
       const uint32_t row_base = uint32_t(nt) * TILE_N + col0;
-      for (int c = 0; c < ncol; c += 32) {
+      const uint32_t t_addr = tmem_base + lane_addr + uint32_t(slot * TILE_N + col0);
+      uint32_t rbuf0[32], rbuf1[32];
+      // One chunk = 32 columns.  Common path: add the row norms, take the minimum, compare with the bound.
+      // Rare path (entered by the whole warp when any of its 32 rows has a column below its bound): the
+      // scores are parked in this warp's shared-memory scratch so that they can be indexed, and each row
+      // inserts its passing columns, in ascending id order, into its sorted register list.
+      auto chunk = [&](uint32_t* r, int c) {
+        const float4* nrm = reinterpret_cast<const float4*>(snorm + (tile_idx % NORM_RING) * TILE_N + col0 + c);
         float v[32];
-        tc_ld32(tmem_base + lane_addr + uint32_t(slot * TILE_N + col0 + c), v);
-        const float4* nrm = reinterpret_cast<const float4*>(p.bnorm + row_base + c);
         float m = INFINITY;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float4 nn = __ldg(nrm + i);
-          v[4 * i + 0] = __fmaf_rn(v[4 * i + 0], p.scale, nn.x);
-          v[4 * i + 1] = __fmaf_rn(v[4 * i + 1], p.scale, nn.y);
-          v[4 * i + 2] = __fmaf_rn(v[4 * i + 2], p.scale, nn.z);
-          v[4 * i + 3] = __fmaf_rn(v[4 * i + 3], p.scale, nn.w);
-          m = fminf(min3(m, v[4 * i + 0], v[4 * i + 1]), fminf(v[4 * i + 2], v[4 * i + 3]));
+          const float4 nn = nrm[i];
+          v[4 * i + 0] = __fmaf_rn(__uint_as_float(r[4 * i + 0]), p.scale, nn.x);
+          v[4 * i + 1] = __fmaf_rn(__uint_as_float(r[4 * i + 1]), p.scale, nn.y);
+          v[4 * i + 2] = __fmaf_rn(__uint_as_float(r[4 * i + 2]), p.scale, nn.z);
+          v[4 * i + 3] = __fmaf_rn(__uint_as_float(r[4 * i + 3]), p.scale, nn.w);
+          m = min3(min3(m, v[4 * i + 0], v[4 * i + 1]), v[4 * i + 2], v[4 * i + 3]);
         }
-        if (m < thr) {
-          // rare path: insert the passing columns, in ascending id order, into the sorted register list
+        if (__any_sync(FV_FULL, m < thr)) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (v[i] < thr) {
-              u64 key = make_key(v[i], row_base + uint32_t(c + i));
+          for (int h = 0; h < 2; ++h) {  // two halves of 16 columns, in id order; the scratch holds one half
+            unsigned mask = 0;
 #pragma unroll
-              for (int j = 0; j < KP; ++j) {
-                const u64 cur = lst[j];
-                const bool lt = key < cur;
-                lst[j] = lt ? key : cur;
-                key = lt ? cur : key;
+            for (int i = 0; i < 16; ++i) {
+              sv[i * 32 + lane] = v[h * 16 + i];
+              mask |= (v[h * 16 + i] < thr) ? (1u << i) : 0u;
+            }
+            while (__any_sync(FV_FULL, mask != 0)) {
+              if (mask) {
+                const int i = __ffs(mask) - 1;
+                mask &= mask - 1;
+                const float val = sv[i * 32 + lane];
+                if (val < thr) {
+                  float cs = val;
+                  uint32_t ci = row_base + uint32_t(c + h * 16 + i);
+#pragma unroll
+                  for (int j = 0; j < KPT; ++j) {
+                    const bool lt = cs < sc[j];
+                    const float ts = sc[j];
+                    const uint32_t ti = idv[j];
+                    sc[j] = lt ? cs : ts;
+                    idv[j] = lt ? ci : ti;
+                    cs = lt ? ts : cs;
+                    ci = lt ? ti : ci;
+                  }
+                  thr = sc[KPT - 1];
+                }
               }
-              thr = lst[KP - 1] == FV_EMPTY_KEY ? INFINITY : key_distance(lst[KP - 1]);
             }
           }
         }
+      };
+      tc_ld32_issue(t_addr, rbuf0);
+#pragma unroll 1
+      for (int c = 0; c < ncol; c += 64) {
+        tc_ld_wait(rbuf0);
+        tc_ld32_issue(t_addr + uint32_t(c + 32), rbuf1);
+        chunk(rbuf0, c);
+        tc_ld_wait(rbuf1);
+        if (c + 64 < ncol) tc_ld32_issue(t_addr + uint32_t(c + 64), rbuf0);
+        chunk(rbuf1, c + 32);
       }
       tc_fence_before();
       __syncwarp();
@@ -367,7 +435,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       if (last_of_segment) {
         u64* dst = p.cand + ((size_t(blockIdx.x) * p.segmax + seg_local) * 256 + e) * KP;
 #pragma unroll
-        for (int j = 0; j < KP; j += 2) *reinterpret_cast<ulonglong2*>(dst + j) = make_ulonglong2(lst[j], lst[j + 1]);
+        for (int j = 0; j < KPT; j += 2) {
+          const u64 k0 = idv[j] == 0xFFFFFFFFu ? FV_EMPTY_KEY : make_key(sc[j], idv[j]);
+          const u64 k1 = idv[j + 1] == 0xFFFFFFFFu ? FV_EMPTY_KEY : make_key(sc[j + 1], idv[j + 1]);
+          *reinterpret_cast<ulonglong2*>(dst + j) = make_ulonglong2(k0, k1);
+        }
       }
     }
   }
@@ -461,7 +533,7 @@ struct RerankParams {
   const float* qnorm2;    // nq (0 for inner product)
   const RangeStats* bst;  // base statistics
   const RangeStats* qst;  // query statistics
-  int n, nq, pd, Kp, k, MH, NT, segmax, is_l2, bf16;
+  int n, nq, pd, Kp, k, MH, NT, segmax, is_l2, bf16, kp;
   long long upc;
   uint32_t id_base;
   u64* out_keys;          // nq x k
@@ -517,8 +589,8 @@ __global__ void rerank_kernel(RerankParams p) {
     for (int li = 0; li < lists_per_seg; ++li) {
       const int e = li * 128 + r;
       const u64* src = p.cand + ((size_t(c) * p.segmax + seg_local) * 256 + e) * KP;
-      u64 ck = lane < KP ? src[lane] : FV_EMPTY_KEY;
-      const u64 last = __shfl_sync(FV_FULL, ck, KP - 1);
+      u64 ck = lane < p.kp ? src[lane] : FV_EMPTY_KEY;
+      const u64 last = __shfl_sync(FV_FULL, ck, p.kp - 1);
       if (last != FV_EMPTY_KEY) tau = fminf(tau, key_distance(last));
       u64 key = FV_EMPTY_KEY;
       if (ck != FV_EMPTY_KEY) {
@@ -664,6 +736,8 @@ int tc_append(fv_ctx* ctx, TcSide** ptc, int metric, const float* d_rows_new, si
     init_stats_kernel<<<1, 1, 0, ctx->stream>>>(tc->stats.as<RangeStats>());
     FV_TRY(convert(ctx, true, all_rows, total, pd, Kp, tc->half.as<uint16_t>(), tc->norm2.as<float>(), metric == FV_L2,
                    tc->stats.as<RangeStats>()));
+    FV_CUDA(cudaMemcpyAsync(&tc->h_stats, tc->stats.p, sizeof(RangeStats), cudaMemcpyDeviceToHost, ctx->stream));
+    FV_CUDA(cudaStreamSynchronize(ctx->stream));
   } else {
     // fold the new rows' statistics into the running ones
     FV_CUDA(cudaMemcpyAsync(&tc->h_stats, tc->stats.p, sizeof(RangeStats), cudaMemcpyDeviceToHost, ctx->stream));
@@ -676,6 +750,7 @@ int tc_append(fv_ctx* ctx, TcSide** ptc, int metric, const float* d_rows_new, si
     m.not_finite |= hs.not_finite;
     FV_CUDA(cudaMemcpyAsync(tc->stats.p, &m, sizeof(m), cudaMemcpyHostToDevice, ctx->stream));
     FV_CUDA(cudaStreamSynchronize(ctx->stream));
+    tc->h_stats = m;
   }
   fill_f32_kernel<<<8, 256, 0, ctx->stream>>>(tc->norm2.as<float>() + total, npad - total, INFINITY);
   ctx->stats.launches++;
@@ -704,10 +779,11 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   const int segmax = int((upc + NT - 1) / NT) + 1;
   const size_t a_bytes = size_t(MH) * KB * A_BLOCK_BYTES;
   const size_t budget = ctx->smem_optin;
-  int nstage = int((budget - 2048 - a_bytes) / B_STAGE_BYTES);
-  nstage = std::min(nstage, 8);
+  int nstage = int((budget - 2048 - a_bytes - SCRATCH_BYTES - NORM_RING * TILE_N * 4) / B_STAGE_BYTES);
+  nstage = std::min(nstage, 6);
   if (nstage < 2) return fail(FV_ERR_UNSUPPORTED, "not enough shared memory for the tensor-core tiling");
-  const size_t smem = 1024 + a_bytes + size_t(nstage) * B_STAGE_BYTES + sizeof(Barriers) + 64;
+  const size_t smem = 1024 + a_bytes + size_t(nstage) * B_STAGE_BYTES + SCRATCH_BYTES + NORM_RING * TILE_N * 4 +
+                      sizeof(Barriers) + 64;
 
   // queries -> 16-bit operand rows (padded to whole tiles with zeros), norms, statistics
   const size_t nq_pad = size_t(MT) * rows_per_tile;
@@ -744,13 +820,18 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   gp.bnorm = tc->norm2.as<float>();
   gp.cand = ctx->scratch[6].as<u64>();
   gp.err = err;
-  if (MH == 2) {
-    FV_CUDA(cudaFuncSetAttribute(gemm_topk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    gemm_topk_kernel<2><<<grid, NTHREADS, smem, ctx->stream>>>(tmA, tmB, gp);
-  } else {
-    FV_CUDA(cudaFuncSetAttribute(gemm_topk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    gemm_topk_kernel<1><<<grid, NTHREADS, smem, ctx->stream>>>(tmA, tmB, gp);
-  }
+  // Candidate slots per list: the exact-arithmetic regime needs no margin beyond k (scores ARE the
+  // distances); otherwise the certificate needs candidates past the k-th, so the full 16 are kept.
+  const RangeStats& hb = tc->h_stats;
+  const float bm = std::max(std::fabs(hb.min_v), std::fabs(hb.max_v));
+  const bool base_exact = !hb.not_integer && !hb.not_finite && bm <= (tc->bf16 ? 256.f : 2048.f) &&
+                          float(Kp) * bm * bm <= 8388608.f;
+  const int kp = (base_exact && k <= 10) ? 10 : KP;
+  void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams) =
+      MH == 2 ? (kp == 10 ? gemm_topk_kernel<2, 10> : gemm_topk_kernel<2, 16>)
+              : (kp == 10 ? gemm_topk_kernel<1, 10> : gemm_topk_kernel<1, 16>);
+  FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  kern<<<grid, NTHREADS, smem, ctx->stream>>>(tmA, tmB, gp);
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
   stage_mark(ctx);
@@ -774,6 +855,7 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   rp.is_l2 = metric == FV_L2 ? 1 : 0;
   rp.bf16 = tc->bf16 ? 1 : 0;
   rp.upc = upc;
+  rp.kp = kp;
   rp.id_base = id_base;
   rp.out_keys = d_out_keys;
   rp.retry_ids = ctx->scratch[7].as<uint32_t>();
