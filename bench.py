@@ -1,0 +1,414 @@
+#!/usr/bin/env python
+"""Benchmark of the vector-search hot path: queries/s at recall@10 on N=1M, d=128, k=10.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload ivfpq|flat|hnsw] [--impl reference]
+
+One "step" is one search_batch over a 10,000-query batch (seeded synthetic data with the shape and
+value range of SIFT1M, which cannot be shipped: clipped-integer Gaussian mixture).  The default
+workload is the IVF-PQ configuration (nlist=1024, M=16x8 bit, trained on a 100,000-row sample,
+nprobe=64, refine=10); --workload flat is exact L2 search on the same data, --workload hnsw the
+graph index.  With N>1 GPUs (one process per GPU under torchrun) the base rows are sharded
+contiguously over the ranks (strong scaling: the 1M rows are fixed), every rank searches its shard
+and the per-shard candidates are all-gathered over NCCL and merged by a kernel of this library.
+
+The line printed by rank 0 carries: `value` (device-resident queries), `e2e` (host queries in pinned
+memory, copies inside the timed region), `roofline` of the dominant kernel (algorithmic bytes or
+flops per launch over its CUDA-event duration), `cpu_baseline` (the CPU oracle timed on the host
+cores on a bounded sample) and the sampled GPU clocks.
+
+--impl reference times the CPU restatement of the reference's algorithm (the reference is Rust and
+cannot be built here) on the host cores with all threads, same data and configuration.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_BASE, DIM, NQ, K = 1_000_000, 128, 10_000, 10
+CLUSTERS = 256
+IVF = dict(nlist=1024, m=16, iters=20, learn=100_000, nprobe=64, refine=10)
+HNSW = dict(m=16, ef_construction=200, ef=64)
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "tflops": float(p["bf16_tflops"]),
+                "tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.lines, self.proc, self.thread = index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for name, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_data(rank_rows: tuple[int, int]):
+    import ferrolm_b200 as fv
+
+    lo, hi = rank_rows
+    base = fv.datagen(0, 1, hi - lo, DIM, CLUSTERS, first_row=lo)
+    queries = fv.datagen(0, 2, NQ, DIM, CLUSTERS)
+    return base, queries
+
+
+# ----------------------------------------------------------------------------------------------- reference arm
+def run_reference(args):
+    """The CPU restatement of the reference (oracle/), all host threads, same data and configuration."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+
+    oracle.build()
+    import ferrolm_b200 as fv  # host-side data generator only; no GPU call is made on this arm
+
+    threads = oracle.cores()
+    base, queries = make_data((0, N_BASE))
+    sample = None
+    t0 = time.perf_counter()
+    if args.workload == "ivfpq":
+        learn = fv.datagen(0, 3, IVF["learn"], DIM, CLUSTERS)
+        ix = oracle.IvfPq.train(oracle.L2, DIM, learn, IVF["nlist"], IVF["m"], IVF["iters"], True, 1, threads)
+        ix.add(base, threads)
+        nqs = NQ
+        step = lambda: ix.search_batch(queries[:nqs], K, IVF["nprobe"], IVF["refine"], threads)
+        sample = f"all {nqs} queries per step, index built by the CPU oracle"
+    elif args.workload == "flat":
+        ix = oracle.FlatIndex(oracle.L2, DIM)
+        ix.add(base)
+        nqs = min(NQ, 64 * max(1, threads // 8))
+        step = lambda: ix.search_batch(queries[:nqs], K, threads)
+        sample = f"first {nqs} of {NQ} queries per step (a full batch is minutes of CPU time)"
+    else:
+        ix = oracle.Hnsw.build(oracle.L2, DIM, base, HNSW["m"], HNSW["ef_construction"], 1, threads)
+        nqs = NQ
+        step = lambda: ix.search_batch(queries[:nqs], K, HNSW["ef"], threads)
+        sample = f"all {nqs} queries per step, graph built by the CPU oracle with {threads} threads"
+    build_s = time.perf_counter() - t0
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    qps = nqs / dt
+    line = {
+        "impl": "reference", "metric": "queries/s at recall@10 (N=1M, d=128, k=10)", "value": qps, "unit": "queries/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.workload, 1),
+        "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": threads, "kind": "port", "sample": sample,
+                         "build_s": build_s},
+        "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(workload: str, n_gpus: int) -> dict:
+    cfg = {"n": N_BASE, "d": DIM, "nq": NQ, "k": K, "distribution": f"clipped-integer Gaussian mixture, {CLUSTERS} clusters",
+           "sharding": f"rows over {n_gpus} GPU(s), per-shard top-k all-gathered and merged" if n_gpus > 1 else "single GPU",
+           "l2_note": "inputs exceed L2: 1M x 128 f32 rows (512 MB) plus 16 MB of codes are re-read each step"}
+    if workload == "ivfpq":
+        cfg.update({"workload": "IVF-PQ L2 search, nlist=1024, M=16x8bit, nprobe=64, refine=10 (BASELINE configs[2])",
+                    **{k: IVF[k] for k in ("nlist", "m", "nprobe", "refine")}})
+    elif workload == "flat":
+        cfg.update({"workload": "exact L2 k-NN, tensor-core front end + exact re-rank (BASELINE configs[0] shape at N=1M)"})
+    else:
+        cfg.update({"workload": "HNSW L2 search, M=16, efC=200, efSearch=64 (BASELINE configs[3])", **HNSW})
+    return cfg
+
+
+# ----------------------------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import ferrolm_b200 as fv
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = fv.Context(local)
+    ctx.set_timing(True)
+    stream = torch.cuda.ExternalStream(ctx.stream_handle(), device=local)  # everything runs on the library's stream
+
+    per = (N_BASE + world - 1) // world
+    lo, hi = rank * per, min(N_BASE, (rank + 1) * per)
+    base, queries = make_data((lo, hi))
+    t_build = time.perf_counter()
+    refine = 0
+    if args.workload == "ivfpq":
+        learn = fv.datagen(0, 3, IVF["learn"], DIM, CLUSTERS)
+        ix = fv.IvfPq.train(ctx, fv.Metric.L2, DIM, learn, fv.IvfPqParams(IVF["nlist"], IVF["m"], IVF["iters"], True, 1))
+        ix.set_id_base(lo)
+        ix.add(base)
+        refine = IVF["refine"]
+    elif args.workload == "flat":
+        ix = fv.FlatIndex(ctx, fv.Metric.L2, DIM)
+        ix.set_id_base(lo)
+        ix.add(base)
+    else:
+        if world > 1:
+            raise SystemExit("hnsw: replicas only (one graph); run with --gpus 1")
+        ix = fv.Hnsw.build(ctx, fv.Metric.L2, DIM, base, fv.HnswParams(HNSW["m"], HNSW["ef_construction"], 1),
+                           threads=os.cpu_count() or 1)
+    build_s = time.perf_counter() - t_build
+
+    dq = torch.from_numpy(queries).cuda()
+    hq = torch.from_numpy(queries).pin_memory()
+    h_out = torch.empty((NQ, K, 2), dtype=torch.int32).pin_memory()
+    launches = [0]
+    stage_sum = np.zeros(8)
+    rows_scanned = [0]
+    work = [0, 0]
+
+    def local_search(q):
+        """One shard's search on device-resident queries; returns what the merge needs."""
+        if args.workload == "ivfpq":
+            if world > 1 and refine > 0:
+                r = ix.search_candidates(q, K * refine, IVF["nprobe"])
+            else:
+                r = ix.search_batch(q, K, IVF["nprobe"], refine)
+        elif args.workload == "flat":
+            r = ix.search_batch(q, K)
+        else:
+            r = ix.search_batch(q, K, HNSW["ef"])
+        st = ctx.stats()
+        launches[0] += st["launches"]
+        stage_sum[:] += np.array(st["stage_ms"])
+        rows_scanned[0] = st["rows_scanned"]
+        work[0], work[1] = st["dist_evals"], st["expansions"]
+        return r
+
+    def gather(t):
+        out = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.contiguous())
+        return out
+
+    def step(q):
+        with torch.cuda.stream(stream):
+            r = local_search(q)
+            if world == 1:
+                return r[0], r[1]
+            if args.workload == "ivfpq" and refine > 0:
+                adc, exact, counts = (gather(x) for x in r)
+                stream.synchronize()
+                launches[0] += 2
+                return ctx.merge_refine(adc, exact, counts, K)
+            parts, counts = gather(r[0]), gather(r[1])
+            stream.synchronize()
+            launches[0] += 2
+            return ctx.merge_topk(parts, counts, K)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing (value)
+    sampler = ClockSampler(local)
+    sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step(dq)
+    barrier()
+    launches[0] = 0
+    stage_sum[:] = 0
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        out, counts = step(dq)
+    ev1.record(stream)
+    barrier()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    steady_launches = launches[0]
+    stages = stage_sum / args.steps
+    # ---- end to end: host queries (pinned) in, host results out, every step
+    for _ in range(2):
+        with torch.cuda.stream(stream):
+            q = hq.to(f"cuda:{local}", non_blocking=True)
+        stream.synchronize()
+        o, c = step(q)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        with torch.cuda.stream(stream):
+            q = hq.to(f"cuda:{local}", non_blocking=True)
+        stream.synchronize()
+        o, c = step(q)
+        with torch.cuda.stream(stream):
+            h_out.copy_(o, non_blocking=True)
+        stream.synchronize()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    found = fv.neighbors_from_tensor(out)
+    cnt = counts.cpu().numpy().astype(np.uint32)
+    pk = peaks()
+    line = {
+        "metric": "queries/s at recall@10 (N=1M, d=128, k=10)", "value": NQ / (ms * 1e-3), "unit": "queries/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "data": "synthetic",
+        "dtype": "f32" if args.workload != "flat" else "f16 operands, f32 accumulate, f32 exact re-rank",
+        "config": workload_config(args.workload, world),
+        "e2e": {"value": NQ / (e2e_ms * 1e-3), "unit": "queries/s", "h2d_bytes_per_step": int(hq.numel() * 4),
+                "d2h_bytes_per_step": int(h_out.numel() * 4), "ms_per_step": e2e_ms},
+        "gpu_launches": int(steady_launches), "clocks": clocks, "build_s": build_s,
+        "stage_ms": [round(float(x), 4) for x in stages[:5]],
+    }
+    # ---- roofline of the dominant kernel (per launch = per step; durations from CUDA events on the library's stream)
+    if args.workload == "ivfpq":
+        kms = float(stages[1])
+        alg = rows_scanned[0] * IVF["m"]  # bytes of codes the scan has to read, this rank's shard
+        ach = alg / (kms * 1e-3) / 1e9
+        line["roofline"] = {"kernel": "ivfpq_scan_kernel", "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"],
+                            "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                            "algorithmic_bytes_per_launch": int(alg), "kernel_ms": kms}
+    elif args.workload == "flat":
+        kms = float(stages[1])
+        alg = 2.0 * NQ * (hi - lo) * DIM
+        ach = alg / (kms * 1e-3) / 1e12
+        line["roofline"] = {"kernel": "gemm_topk_kernel", "bound": "tensor", "achieved": ach, "peak": pk["tflops"],
+                            "unit": "TFLOP/s", "frac": ach / pk["tflops"], "traffic": None, "peak_source": pk["source"],
+                            "algorithmic_flops_per_launch": alg, "kernel_ms": kms,
+                            "frac_of_sustained_peak": ach / pk["tflops_sustained"]}
+    else:
+        kms = float(stages[0])
+        alg = work[0] * DIM * 4 + work[1] * (2 * HNSW["m"] + 1) * 4
+        ach = alg / (kms * 1e-3) / 1e9
+        line["roofline"] = {"kernel": "hnsw_search_kernel", "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"],
+                            "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                            "algorithmic_bytes_per_launch": int(alg), "kernel_ms": kms}
+    # ---- CPU baseline (the oracle on the host cores) and recall against exact search, on a bounded sample
+    if world == 1 and not args.no_cpu:
+        from oracle import oracle
+
+        oracle.build()
+        threads = oracle.cores()
+        nsub = min(NQ, 2000)
+        t0 = time.perf_counter()
+        if args.workload == "ivfpq":
+            oix = oracle.IvfPq.load(ix.save())  # the same trained index, byte for byte
+            load_s = time.perf_counter() - t0
+            t0 = time.perf_counter()
+            want, wc = oix.search_batch(queries[:nsub], K, IVF["nprobe"], refine, threads)
+            sample = f"first {nsub} of {NQ} queries, same index (loaded from the GPU-built FLIVFPQ1 bytes)"
+        elif args.workload == "flat":
+            nsub = 64
+            oix = oracle.FlatIndex(oracle.L2, DIM)
+            oix.add(base)
+            load_s = time.perf_counter() - t0
+            t0 = time.perf_counter()
+            want, wc = oix.search_batch(queries[:nsub], K, threads)
+            sample = f"first {nsub} of {NQ} queries"
+        else:
+            oix = oracle.Hnsw.load(ix.save())
+            load_s = time.perf_counter() - t0
+            t0 = time.perf_counter()
+            want, wc = oix.search_batch(queries[:nsub], K, HNSW["ef"], threads)
+            sample = f"first {nsub} of {NQ} queries, same graph (loaded from the FLHNSW01 bytes)"
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": nsub / dt, "unit": "queries/s", "cores": threads, "kind": "port",
+                                "sample": sample, "seconds": dt}
+        same_ids = int((found[:nsub]["id"] == want["id"]).all(axis=1).sum())
+        line["parity_sample"] = {"queries": nsub, "identical_id_rows": same_ids,
+                                 "bit_equal_distances": bool((found[:nsub]["distance"].view(np.uint32) ==
+                                                              want["distance"].view(np.uint32)).all())}
+        # recall@10 against exact search (GPU exact search, itself checked against the oracle in tests/)
+        flat = fv.FlatIndex(ctx, fv.Metric.L2, DIM)
+        flat.add(base)
+        truth, _ = flat.search_batch(queries[:nsub], K)
+        line["config"]["recall_at_10"] = fv.recall(found[:nsub], cnt[:nsub], truth["id"], K)
+    else:
+        line["cpu_baseline"] = None
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="ivfpq", choices=["ivfpq", "flat", "hnsw"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
