@@ -109,6 +109,7 @@ SIGNATURES = {
     "fv_recall": (C.c_double, [_vp, _vp, _vp, _sz, _sz, _sz]),
     "fv_merge_topk_dev": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp]),
     "fv_merge_refine_dev": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp]),
+    "fv_merge_topk_static_dev": (_i, [_i, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp]),
     "fv_datagen": (_i, [_i, _u64, _sz, _sz, _sz, _sz, _i, _vp]),
 }
 

@@ -129,6 +129,21 @@ class Context:
         return out, counts
 
 
+def merge_topk_static(parts, part_counts, k_out: int, out, counts):
+    """Shard merge that allocates nothing, for callers that cannot: the outputs are passed in (`out` is an
+    (nq, k_out, 2) int32 device tensor, `counts` (nq,) int32) and the scratch is a fixed array inside the
+    library.  Limits: nq * k_out <= 262144, k_out <= 1024; calls that overlap on one GPU race on that array."""
+    import torch
+
+    nparts, nq, k_in = parts.shape[0], parts.shape[1], parts.shape[2]
+    dev = parts.device.index if parts.device.index is not None else torch.cuda.current_device()
+    stream = torch.cuda.current_stream(parts.device)
+    check(lib().fv_merge_topk_static_dev(dev, stream.cuda_stream, parts.data_ptr(),
+                                         part_counts.data_ptr() if part_counts is not None else None, nparts, nq,
+                                         k_in, k_out, out.data_ptr(), counts.data_ptr()))
+    return out, counts
+
+
 def neighbors_from_tensor(t) -> np.ndarray:
     """(nq, k, 2) int32 device tensor -> (nq, k) NEIGHBOR array on the host."""
     a = t.cpu().numpy()
@@ -391,4 +406,4 @@ def kmeans_assign(ctx: Context, data, centroids) -> np.ndarray:
 
 __all__ = ["Metric", "Context", "FlatIndex", "IvfPq", "IvfPqParams", "Hnsw", "HnswParams", "NEIGHBOR", "padded",
            "normalize", "recall", "datagen", "kmeans_train", "kmeans_assign", "neighbors_from_tensor",
-           "FerrovecError"]
+           "merge_topk_static", "FerrovecError"]
