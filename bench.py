@@ -334,7 +334,7 @@ def run_ours(args):
                             "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
                             "algorithmic_bytes_per_launch": int(alg), "kernel_ms": kms}
     elif args.workload == "flat":
-        kms = float(stages[1])
+        kms = float(stages[2])  # stage 2 = main pass of the tensor-core kernel (0 convert, 1 sample pass, 3 re-rank)
         alg = 2.0 * NQ * (hi - lo) * DIM
         ach = alg / (kms * 1e-3) / 1e12
         line["roofline"] = {"kernel": "gemm_topk_kernel", "bound": "tensor", "achieved": ach, "peak": pk["tflops"],
@@ -396,6 +396,7 @@ def run_ours(args):
 
 
 def main():
+    global NQ, N_BASE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -403,7 +404,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="ivfpq", choices=["ivfpq", "flat", "hnsw"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--nq", type=int, default=NQ, help="queries per step (smaller = a profiling-sized case)")
+    ap.add_argument("--n", type=int, default=N_BASE, help="base rows (smaller = a profiling-sized case)")
     args = ap.parse_args()
+    NQ, N_BASE = args.nq, args.n
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -328,7 +328,7 @@ int fv_flat_search_batch_dev(fv_flat* ix, const float* d_queries, size_t nq, siz
   const bool want_tc = ix->mode == 1 || (ix->mode == 0 && fv::tc_usable(ix->tc, ix->n, nq, L));
   if (want_tc) {
     if (!fv::tc_usable(ix->tc, ix->n, nq, L))
-      return fv::fail(FV_ERR_UNSUPPORTED, "tensor-core search needs k <= 16, at least 4096 rows and a padded dimension of at most 384");
+      return fv::fail(FV_ERR_UNSUPPORTED, "tensor-core search needs k <= 32, at least 4096 rows and a padded dimension of at most 384");
     FV_TRY(fv::tc_search(ctx, ix->tc, ix->metric, ix->data.as<float>(), ix->n, pd, q, nq, L, ix->id_base, keys));
   } else {
     FV_TRY(fv::exact_scan(ctx, ix->metric, ix->data.as<float>(), ix->n, pd, q, size_t(pd), nullptr, nq, L, true,

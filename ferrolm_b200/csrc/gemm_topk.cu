@@ -41,8 +41,10 @@ static constexpr int TILE_N = 256;     // base rows per unit
 static constexpr int KBLK = 64;        // k elements per shared-memory block (128 bytes)
 static constexpr int A_BLOCK_BYTES = 128 * 128;   // 128 rows x 128 B
 static constexpr int B_STAGE_BYTES = TILE_N * 128;
-static constexpr int SCRATCH_BYTES = 8 * 16 * 32 * 4;  // per epilogue warp: 16 columns x 32 rows of scores
-static constexpr int NTHREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+static constexpr int NEPI = 16;        // epilogue warps: four per tensor-memory lane quadrant
+static constexpr int LISTS = NEPI * 32; // per-thread lists of one segment
+static constexpr int SCRATCH_BYTES = NEPI * 16 * 32 * 4;  // list mode only; per epilogue warp: 16 columns x 32 rows of scores
+static constexpr int NTHREADS = 64 + NEPI * 32;   // warp 0 TMA, warp 1 MMA, warps 2..17 epilogue
 static constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s; then the kernel gives up
 
 // ------------------------------------------------------------------------------------------------
@@ -181,11 +183,19 @@ struct GemmParams {
   long long upc;   // units per CTA
   int segmax;      // candidate segments per CTA
   int nstage;
+  int scratch_bytes;  // SCRATCH_BYTES in list mode, 0 in threshold mode
   float scale;     // -2 (L2) or -1 (inner product)
   uint32_t idesc;
   const float* bnorm;  // padded to a multiple of 256 with +inf
-  u64* cand;           // [grid * segmax][256][KP]
+  u64* cand;           // [grid * segmax][256][KP]  (list mode: output)
   int* err;            // set to 1 when a bounded wait ran out
+  // threshold mode: per-query bounds from the sample pass, and the candidate buffers they fill
+  const u64* tau_lists;  // the sample pass's `cand`
+  int tNT, tsegmax;      // its tiling
+  long long tupc;
+  u64* cbuf;             // [grid * segmax][256][ccap] (score, row) keys: one private list per epilogue thread and segment
+  unsigned int* ccnt;    // [grid * segmax][256] entries appended (may exceed ccap: overflow)
+  int ccap;
 };
 
 struct __align__(8) Barriers {
@@ -196,7 +206,50 @@ struct __align__(8) Barriers {
   int abort_flag;
 };
 
-template <int MH, int KPT>
+// The SAMPLE_R-th smallest score of query row `r` of query tile `mt` over the lists the sample pass left
+// (+inf when the sample holds fewer rows).  With a sample of 1 row in 32 about 32 * SAMPLE_R = 160 rows of the
+// full set score below it (negative binomial), fewer than 10 with probability < 1e-4.
+// Epilogue thread -> list index: warp group `sub` (0..3) * 128 + lane quadrant * 32 + lane.  MH = 2: sub & 1 is the
+// 128-row half of the query tile, sub >> 1 the half of the 256 columns; MH = 1: sub is the column quarter.
+// The li-th list that holds candidates of query row r of its tile:
+__device__ __forceinline__ int list_of_row(int MH, int r, int li) {
+  return MH == 2 ? ((r >> 7) + 2 * li) * 128 + (r & 127) : li * 128 + r;
+}
+
+static constexpr int SAMPLE_R = 5;
+static constexpr int SAMPLE_EVERY = 32;
+__device__ __forceinline__ float sample_tau(const u64* __restrict__ lists, int NT, long long upc, int segmax, int MH,
+                                            int mt, int r) {
+  float best[SAMPLE_R];
+#pragma unroll
+  for (int j = 0; j < SAMPLE_R; ++j) best[j] = INFINITY;
+  const long long ub = (long long)mt * NT, ue = ub + NT - 1;
+  const int c_lo = int(ub / upc), c_hi = int(ue / upc);
+  const int nl = MH == 2 ? 2 : 4;
+  for (int c = c_lo; c <= c_hi; ++c) {
+    const int seg_local = mt - int((c * upc) / NT);
+    for (int li = 0; li < nl; ++li) {
+      const u64* src = lists + ((size_t(c) * segmax + seg_local) * LISTS + list_of_row(MH, r, li)) * KP;
+#pragma unroll
+      for (int j = 0; j < SAMPLE_R; ++j) {
+        const u64 key = src[j];
+        if (key != FV_EMPTY_KEY) {
+          float sc = key_distance(key);
+#pragma unroll
+          for (int t = 0; t < SAMPLE_R; ++t) {
+            const bool lt = sc < best[t];
+            const float tmp = best[t];
+            best[t] = lt ? sc : tmp;
+            sc = lt ? tmp : sc;
+          }
+        }
+      }
+    }
+  }
+  return best[SAMPLE_R - 1];
+}
+
+template <int MH, int KPT, bool THRESH>
 __global__ void __launch_bounds__(NTHREADS, 1)
     gemm_topk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   unsigned char* raw = dyn_smem();
@@ -204,8 +257,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   unsigned char* sA = base;                                            // [MH][KB] blocks of 16 KB
   unsigned char* sB = sA + size_t(MH) * p.KB * A_BLOCK_BYTES;          // [nstage] stages of 32 KB
   unsigned char* scratch = sB + size_t(p.nstage) * B_STAGE_BYTES;   // 8 epilogue warps x 4 KB
-  float* snorm = reinterpret_cast<float*>(scratch + SCRATCH_BYTES);  // [NORM_RING][256]
-  Barriers* bars = reinterpret_cast<Barriers*>(scratch + SCRATCH_BYTES + NORM_RING * TILE_N * 4);
+  float* snorm = reinterpret_cast<float*>(scratch + p.scratch_bytes);  // [NORM_RING][256]
+  Barriers* bars = reinterpret_cast<Barriers*>(scratch + p.scratch_bytes + NORM_RING * TILE_N * 4);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -221,7 +274,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     mbar_init(&bars->a_empty, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars->tfull[s], 1);
-      mbar_init(&bars->tempty[s], MH == 2 ? 4 : 8);
+      mbar_init(&bars->tempty[s], MH == 2 ? NEPI / 2 : NEPI);
     }
     bars->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -328,14 +381,17 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     // ---------------------------------------------------------------- epilogue: 8 warps, one query row per thread
     const int ew = warp - 2;
     const int quad = warp & 3;   // tensor-memory lanes this warp may read: 32 * quad .. +31
-    const int grp = ew >> 2;     // MH = 2: which 128-row half (= accumulator slot); MH = 1: which column half
-    const int e = grp * 128 + quad * 32 + lane;  // list index inside a segment
+    const int sub = ew >> 2;     // warp group 0..3
+    const int grp = MH == 2 ? (sub & 1) : 0;  // MH = 2: which 128-row half (= accumulator slot)
+    const int e = sub * 128 + quad * 32 + lane;  // list index inside a segment
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
     // the KPT best (score, id) of this thread's query row in the current segment, ascending by score;
     // rows arrive in ascending id order, so a strict score compare keeps the (score, id) order
     float sc[KPT];
     uint32_t idv[KPT];
     float thr = INFINITY;
+    size_t cslot = 0;        // threshold mode: this thread's candidate list of the current segment
+    unsigned int ncand = 0;
     float* sv = reinterpret_cast<float*>(scratch) + size_t(ew) * 512;  // 16 columns x 32 rows of scores
 #pragma unroll
     for (int j = 0; j < KPT; ++j) {
@@ -345,8 +401,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     long long tile_idx = 0;
     int cur_mt = -1, seg_local = -1;
     bool ok = true;
-    const int ncol = MH == 2 ? TILE_N : TILE_N / 2;
-    const int col0 = MH == 2 ? 0 : grp * (TILE_N / 2);
+    const int ncol = MH == 2 ? TILE_N / 2 : TILE_N / 4;
+    const int col0 = MH == 2 ? (sub >> 1) * (TILE_N / 2) : sub * (TILE_N / 4);
     for (long long u = u0; u < u1 && ok; ++u, ++tile_idx) {
       const int mt = int(u / p.NT), nt = int(u % p.NT);
       if (mt != cur_mt) {
@@ -358,6 +414,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           sc[j] = INFINITY;
           idv[j] = 0xFFFFFFFFu;
         }
+        if (THRESH) {  // the bound is fixed for the whole segment: the sample pass's estimate
+          const int r = MH == 2 ? grp * 128 + quad * 32 + lane : (quad * 32 + lane);
+          thr = sample_tau(p.tau_lists, p.tNT, p.tupc, p.tsegmax, MH, mt, r);
+          cslot = (size_t(blockIdx.x) * p.segmax + seg_local) * LISTS + e;
+          ncand = 0;
+        }
       }
       const long long job = MH == 2 ? tile_idx * 2 + grp : tile_idx;
       const int slot = int(job & 1);
@@ -366,7 +428,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       tc_fence_after();
       const uint32_t row_base = uint32_t(nt) * TILE_N + col0;
       const uint32_t t_addr = tmem_base + lane_addr + uint32_t(slot * TILE_N + col0);
-      uint32_t rbuf0[32], rbuf1[32];
+      uint32_t rbuf0[32];
       // One chunk = 32 columns.  Common path: add the row norms, take the minimum, compare with the bound.
       // Rare path (entered by the whole warp when any of its 32 rows has a column below its bound): the
       // scores are parked in this warp's shared-memory scratch so that they can be indexed, and each row
@@ -374,7 +436,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       auto chunk = [&](uint32_t* r, int c) {
         const float4* nrm = reinterpret_cast<const float4*>(snorm + (tile_idx % NORM_RING) * TILE_N + col0 + c);
         float v[32];
-        float m = INFINITY;
+        float g[4] = {INFINITY, INFINITY, INFINITY, INFINITY};  // minima of the four groups of 8 columns
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float4 nn = nrm[i];
@@ -382,9 +444,28 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           v[4 * i + 1] = __fmaf_rn(__uint_as_float(r[4 * i + 1]), p.scale, nn.y);
           v[4 * i + 2] = __fmaf_rn(__uint_as_float(r[4 * i + 2]), p.scale, nn.z);
           v[4 * i + 3] = __fmaf_rn(__uint_as_float(r[4 * i + 3]), p.scale, nn.w);
-          m = min3(min3(m, v[4 * i + 0], v[4 * i + 1]), v[4 * i + 2], v[4 * i + 3]);
+          g[i >> 1] = min3(min3(g[i >> 1], v[4 * i + 0], v[4 * i + 1]), v[4 * i + 2], v[4 * i + 3]);
         }
-        if (__any_sync(FV_FULL, m < thr)) {
+        const float m = min3(fminf(g[0], g[1]), g[2], g[3]);
+        if (THRESH) {
+          // threshold mode: every column below the (fixed) bound is appended to this thread's private list
+          // (a plain store and a register counter: nothing to wait for)
+          if (__any_sync(FV_FULL, m < thr)) {
+            u64* cl = p.cbuf + cslot * size_t(p.ccap);
+#pragma unroll
+            for (int gi = 0; gi < 4; ++gi) {
+              if (__any_sync(FV_FULL, g[gi] < thr)) {
+#pragma unroll
+                for (int i = gi * 8; i < gi * 8 + 8; ++i) {
+                  if (v[i] < thr) {
+                    if (ncand < unsigned(p.ccap)) cl[ncand] = make_key(v[i], row_base + uint32_t(c + i));
+                    ncand++;
+                  }
+                }
+              }
+            }
+          }
+        } else if (__any_sync(FV_FULL, m < thr)) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {  // two halves of 16 columns, in id order; the scratch holds one half
             unsigned mask = 0;
@@ -418,22 +499,20 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           }
         }
       };
-      tc_ld32_issue(t_addr, rbuf0);
+      // four epilogue warps share each scheduler, so the tensor-memory load latency is hidden across warps
 #pragma unroll 1
-      for (int c = 0; c < ncol; c += 64) {
+      for (int c = 0; c < ncol; c += 32) {
+        tc_ld32_issue(t_addr + uint32_t(c), rbuf0);
         tc_ld_wait(rbuf0);
-        tc_ld32_issue(t_addr + uint32_t(c + 32), rbuf1);
         chunk(rbuf0, c);
-        tc_ld_wait(rbuf1);
-        if (c + 64 < ncol) tc_ld32_issue(t_addr + uint32_t(c + 64), rbuf0);
-        chunk(rbuf1, c + 32);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tempty[slot]);
       const bool last_of_segment = (u + 1 == u1) || int((u + 1) / p.NT) != mt;
-      if (last_of_segment) {
-        u64* dst = p.cand + ((size_t(blockIdx.x) * p.segmax + seg_local) * 256 + e) * KP;
+      if (THRESH && last_of_segment) p.ccnt[cslot] = ncand;
+      if (!THRESH && last_of_segment) {
+        u64* dst = p.cand + ((size_t(blockIdx.x) * p.segmax + seg_local) * LISTS + e) * KP;
 #pragma unroll
         for (int j = 0; j < KPT; j += 2) {
           const u64 k0 = idv[j] == 0xFFFFFFFFu ? FV_EMPTY_KEY : make_key(sc[j], idv[j]);
@@ -527,14 +606,19 @@ __global__ void init_stats_kernel(RangeStats* st) {
 // ------------------------------------------------------------------------------------------------
 // Exact re-rank and certification: one warp per query.
 struct RerankParams {
-  const u64* cand;
+  const u64* tau_lists;   // sample pass lists (for the bound every candidate was tested against)
+  int tNT, tsegmax;
+  long long tupc;
+  const u64* cbuf;        // candidates of the main pass: [grid * segmax][256][ccap]
+  const unsigned int* ccnt;
+  int ccap, NT, segmax;   // main-pass tiling
+  long long upc;
   const float* rows;      // n x pd fp32
   const float* queries;   // nq x pd fp32
   const float* qnorm2;    // nq (0 for inner product)
   const RangeStats* bst;  // base statistics
   const RangeStats* qst;  // query statistics
-  int n, nq, pd, Kp, k, MH, NT, segmax, is_l2, bf16, kp;
-  long long upc;
+  int n, nq, pd, Kp, k, MH, is_l2, bf16;
   uint32_t id_base;
   u64* out_keys;          // nq x k
   uint32_t* retry_ids;    // queries that did not certify
@@ -573,58 +657,76 @@ __global__ void rerank_kernel(RerankParams p) {
     const float e_dot = (2.f * u16 * (1.f + u16) + kf * 4.7683716e-7f + kf * 1.1920929e-7f) * qnorm * bn +
                         5.9604645e-8f * sqrtf(kf) * (qnorm + bn);
     eps = p.is_l2 ? 2.f * e_dot + kf * 2.3841858e-7f * (qnorm * qnorm + bn * bn) * 2.f : e_dot;
-    eps = eps * 1.01f + 1e-30f;
+    eps = exact_regime ? 0.f : eps * 1.01f + 1e-30f;
   }
 
   const int rows_per_tile = 128 * p.MH;
   const int mt = int(q / rows_per_tile), r = int(q % rows_per_tile);
-  const long long ub = (long long)mt * p.NT, ue = ub + p.NT - 1;
-  const int c_lo = int(ub / p.upc), c_hi = int(ue / p.upc);
-  const int lists_per_seg = p.MH == 2 ? 1 : 2;
-  float tau = INFINITY;   // smallest "last kept score" over the lists: every row outside the lists scores >= tau
+  // every row whose score is below tau is in the buffer; every other row scores >= tau
+  const float tau = sample_tau(p.tau_lists, p.tNT, p.tupc, p.tsegmax, p.MH, mt, r);
+  bool overflow = false;
   bool mismatch = false;  // exact regime only: a score that is not the exact distance
   u64 bound = FV_EMPTY_KEY;
+  const long long ub = (long long)mt * p.NT, ue = ub + p.NT - 1;
+  const int c_lo = int(ub / p.upc), c_hi = int(ue / p.upc);
+  const int lists_per_seg = p.MH == 2 ? 2 : 4;
   for (int c = c_lo; c <= c_hi; ++c) {
     const int seg_local = mt - int((c * p.upc) / p.NT);
     for (int li = 0; li < lists_per_seg; ++li) {
-      const int e = li * 128 + r;
-      const u64* src = p.cand + ((size_t(c) * p.segmax + seg_local) * 256 + e) * KP;
-      u64 ck = lane < p.kp ? src[lane] : FV_EMPTY_KEY;
-      const u64 last = __shfl_sync(FV_FULL, ck, p.kp - 1);
-      if (last != FV_EMPTY_KEY) tau = fminf(tau, key_distance(last));
-      u64 key = FV_EMPTY_KEY;
-      if (ck != FV_EMPTY_KEY) {
-        const uint32_t id = key_id(ck);
-        float d;
-        if (id < uint32_t(p.n)) {
-          d = p.is_l2 ? exact_distance<true>(sq, p.rows + size_t(id) * p.pd, p.pd)
-                      : exact_distance<false>(sq, p.rows + size_t(id) * p.pd, p.pd);
-          if (exact_regime && d != key_distance(ck) + qn2) mismatch = true;
-          if (d < INFINITY) key = make_key(d, id + p.id_base);
-        } else {
-          mismatch = true;  // a padded row can only get here through a non-finite score
+      const size_t slot = (size_t(c) * p.segmax + seg_local) * LISTS + list_of_row(p.MH, r, li);
+      const unsigned int cnt = p.ccnt[slot];
+      if (cnt > unsigned(p.ccap)) overflow = true;
+      const int nc = int(min(cnt, unsigned(p.ccap)));
+      const u64* src = p.cbuf + slot * size_t(p.ccap);
+      for (int i0 = 0; i0 < nc; i0 += 32) {
+        const int i = i0 + lane;
+        u64 key = FV_EMPTY_KEY;
+        if (i < nc) {
+          const u64 ck = src[i];
+          const uint32_t id = key_id(ck);
+          if (id < uint32_t(p.n)) {
+            const float d = p.is_l2 ? exact_distance<true>(sq, p.rows + size_t(id) * p.pd, p.pd)
+                                    : exact_distance<false>(sq, p.rows + size_t(id) * p.pd, p.pd);
+            if (exact_regime && d != key_distance(ck) + qn2) mismatch = true;
+            if (d < INFINITY) key = make_key(d, id + p.id_base);
+          } else {
+            mismatch = true;  // a padded row can only get here through a non-finite score
+          }
         }
+        bound = warp_list_offer(list, p.k, key, bound);
       }
-      bound = warp_list_offer(list, p.k, key, bound);
     }
   }
   __syncwarp();
   mismatch = __any_sync(FV_FULL, mismatch);
   const u64 kth = list[p.k - 1];
   bool certified;
-  if (tau == INFINITY) {
-    certified = true;  // no list was full: every row of the index was a candidate
-  } else if (exact_regime) {
-    certified = !mismatch;  // scores are the distances (shifted by ||q||^2) and lists are (score, id) exact
+  if (overflow || mismatch) {
+    certified = false;
+  } else if (tau == INFINITY) {
+    certified = true;  // every row with a finite score was a candidate
   } else {
+    // the k-th result must be provably nearer than anything that was not a candidate
     certified = kth != FV_EMPTY_KEY && (key_distance(kth) - qn2) + eps < tau;
   }
-  if (mismatch && exact_regime) certified = false;
   for (int e = lane; e < p.k; e += 32) p.out_keys[q * size_t(p.k) + e] = list[e];
   if (!certified && lane == 0) {
     const unsigned int slot = atomicAdd(p.retry_count, 1u);
     p.retry_ids[slot] = uint32_t(q);
   }
+}
+
+// rows of the strided sample: sample row i is base row floor(i * n / ns)
+__global__ void gather_sample_kernel(const uint16_t* __restrict__ half, const float* __restrict__ norm2, size_t n, int Kp,
+                                     size_t ns, uint16_t* __restrict__ samp, float* __restrict__ snorm) {
+  const int lane = threadIdx.x & 31;
+  const size_t i = blockIdx.x * size_t(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= ns) return;
+  const size_t src = size_t((unsigned long long)i * n / ns);
+  const uint4* a = reinterpret_cast<const uint4*>(half + src * size_t(Kp));
+  uint4* b = reinterpret_cast<uint4*>(samp + i * size_t(Kp));
+  for (int c = lane; c < Kp / 8; c += 32) b[c] = a[c];
+  if (lane == 0) snorm[i] = norm2[src];
 }
 
 __global__ void scatter_keys_kernel(const u64* __restrict__ src, const uint32_t* __restrict__ qids, size_t nsub, int L,
@@ -675,6 +777,8 @@ struct TcSide {
   DevBuf half;             // n_cap x Kp 16-bit
   DevBuf norm2;            // padded to 256, +inf beyond n
   DevBuf stats;            // RangeStats (base), RangeStats (queries), retry counter, error word
+  size_t ns = 0;           // rows of the strided sample (1 in SAMPLE_EVERY)
+  DevBuf samp, samp_norm2; // the sample's operand rows and norms (+inf padded)
   RangeStats h_stats{};
 };
 
@@ -756,89 +860,156 @@ int tc_append(fv_ctx* ctx, TcSide** ptc, int metric, const float* d_rows_new, si
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
   tc->n = total;
+  // the strided sample the threshold of the main pass is estimated from
+  tc->ns = std::max<size_t>(SAMPLE_R, total / SAMPLE_EVERY);
+  const size_t nspad = (tc->ns + TILE_N - 1) / TILE_N * TILE_N + TILE_N;
+  FV_TRY(tc->samp.reserve(tc->ns * size_t(Kp) * 2 + 1024));
+  FV_TRY(tc->samp_norm2.reserve(nspad * sizeof(float)));
+  gather_sample_kernel<<<unsigned((tc->ns + 7) / 8), 256, 0, ctx->stream>>>(
+      tc->half.as<uint16_t>(), tc->norm2.as<float>(), total, Kp, tc->ns, tc->samp.as<uint16_t>(),
+      tc->samp_norm2.as<float>());
+  fill_f32_kernel<<<8, 256, 0, ctx->stream>>>(tc->samp_norm2.as<float>() + tc->ns, nspad - tc->ns, INFINITY);
+  ctx->stats.launches += 2;
+  FV_CUDA(cudaGetLastError());
   return FV_OK;
 }
 
 bool tc_usable(const TcSide* tc, size_t n, size_t nq, int k) {
   (void)nq;
-  return tc && tc->n == n && k <= KP && n >= 4096 && n <= 0x7FFFFF00ull;
+  return tc && tc->n == n && k <= 32 && n >= 4096 && n <= 0x7FFFFF00ull;
 }
 
-// scratch slots: 2 scan partials (fallback), 3 A operand, 5 query norms, 6 candidates, 7 retry ids, 8 fallback keys
+// One launch of the GEMM kernel over `rows` operand rows.
+struct Tiling {
+  int KB, MH, MT, NT, grid, segmax, nstage;
+  long long U, upc;
+  size_t smem;
+};
+
+static int make_tiling(fv_ctx* ctx, int Kp, size_t nq, size_t rows, int scratch_bytes, Tiling* t) {
+  t->KB = Kp / KBLK;
+  t->MH = t->KB <= 2 ? 2 : 1;
+  const int rows_per_tile = 128 * t->MH;
+  t->MT = int((nq + rows_per_tile - 1) / rows_per_tile);
+  t->NT = int((rows + TILE_N - 1) / TILE_N);
+  t->U = (long long)t->MT * t->NT;
+  t->grid = int(std::min<long long>(ctx->sm_count, t->U));
+  t->upc = (t->U + t->grid - 1) / t->grid;
+  t->segmax = int((t->upc + t->NT - 1) / t->NT) + 1;
+  const size_t a_bytes = size_t(t->MH) * t->KB * A_BLOCK_BYTES;
+  const size_t fixed = 2048 + a_bytes + scratch_bytes + NORM_RING * TILE_N * 4;
+  if (ctx->smem_optin < fixed + 2 * B_STAGE_BYTES)
+    return fail(FV_ERR_UNSUPPORTED, "not enough shared memory for the tensor-core tiling");
+  t->nstage = std::min(int((ctx->smem_optin - fixed) / B_STAGE_BYTES), 6);
+  t->smem = 1024 + a_bytes + size_t(t->nstage) * B_STAGE_BYTES + scratch_bytes + NORM_RING * TILE_N * 4 +
+            sizeof(Barriers) + 64;
+  return FV_OK;
+}
+
+template <int KPT, bool THRESH>
+static int launch_gemm(fv_ctx* ctx, const Tiling& t, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                       const GemmParams& gp) {
+  void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams) =
+      t.MH == 2 ? gemm_topk_kernel<2, KPT, THRESH> : gemm_topk_kernel<1, KPT, THRESH>;
+  FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(t.smem)));
+  kern<<<t.grid, NTHREADS, t.smem, ctx->stream>>>(tmA, tmB, gp);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  return FV_OK;
+}
+
+static constexpr int CAND_CAP = 256;  // candidate slots per epilogue thread and segment in the main pass
+
+// Stages (fv_stats.stage_ms): 0 query conversion, 1 sample pass, 2 main pass, 3 re-rank + certificate, 4 fallback.
+// scratch slots: 2 scan partials (fallback), 3 A operand, 5 query norms + candidate counters, 6 sample lists,
+// 7 retry ids, 8 fallback keys, 9 candidate buffers
 int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n, int pd, const float* d_queries,
               size_t nq, int k, uint32_t id_base, u64* d_out_keys) {
   const int Kp = tc->Kp;
-  const int KB = Kp / KBLK;
-  const int MH = KB <= 2 ? 2 : 1;
-  const int rows_per_tile = 128 * MH;
-  const int MT = int((nq + rows_per_tile - 1) / rows_per_tile);
-  const int NT = int((n + TILE_N - 1) / TILE_N);
-  const long long U = (long long)MT * NT;
-  const int grid = int(std::min<long long>(ctx->sm_count, U));
-  const long long upc = (U + grid - 1) / grid;
-  const int segmax = int((upc + NT - 1) / NT) + 1;
-  const size_t a_bytes = size_t(MH) * KB * A_BLOCK_BYTES;
-  const size_t budget = ctx->smem_optin;
-  int nstage = int((budget - 2048 - a_bytes - SCRATCH_BYTES - NORM_RING * TILE_N * 4) / B_STAGE_BYTES);
-  nstage = std::min(nstage, 6);
-  if (nstage < 2) return fail(FV_ERR_UNSUPPORTED, "not enough shared memory for the tensor-core tiling");
-  const size_t smem = 1024 + a_bytes + size_t(nstage) * B_STAGE_BYTES + SCRATCH_BYTES + NORM_RING * TILE_N * 4 +
-                      sizeof(Barriers) + 64;
+  Tiling ts{}, tm{};
+  FV_TRY(make_tiling(ctx, Kp, nq, tc->ns, SCRATCH_BYTES, &ts));
+  FV_TRY(make_tiling(ctx, Kp, nq, n, 0, &tm));
+  const int rows_per_tile = 128 * tm.MH;
 
   // queries -> 16-bit operand rows (padded to whole tiles with zeros), norms, statistics
-  const size_t nq_pad = size_t(MT) * rows_per_tile;
+  const size_t nq_pad = size_t(tm.MT) * rows_per_tile;
   FV_TRY(ctx->scratch[3].reserve(nq_pad * size_t(Kp) * 2));
-  FV_TRY(ctx->scratch[5].reserve(nq_pad * sizeof(float)));
+  const size_t nlists = size_t(tm.grid) * tm.segmax * LISTS;
+  FV_TRY(ctx->scratch[5].reserve(nq_pad * sizeof(float) + nlists * sizeof(unsigned int)));
+  FV_TRY(ctx->scratch[6].reserve(size_t(ts.grid) * ts.segmax * LISTS * KP * sizeof(u64)));
+  FV_TRY(ctx->scratch[7].reserve(nq * sizeof(uint32_t)));
+  FV_TRY(ctx->scratch[9].reserve(nlists * size_t(CAND_CAP) * sizeof(u64)));
   uint16_t* dA = ctx->scratch[3].as<uint16_t>();
   float* qn2 = ctx->scratch[5].as<float>();
+  unsigned int* ccnt = reinterpret_cast<unsigned int*>(qn2 + nq_pad);
   RangeStats* bst = tc->stats.as<RangeStats>();
   RangeStats* qst = bst + 1;
   unsigned int* retry_count = reinterpret_cast<unsigned int*>(qst + 1);
   int* err = reinterpret_cast<int*>(retry_count + 1);
+  CUtensorMap tmA, tmS, tmB;
+  FV_TRY(make_tmap(&tmA, tc->bf16, dA, nq_pad, Kp, 128));
+  FV_TRY(make_tmap(&tmS, tc->bf16, tc->samp.p, tc->ns, Kp, TILE_N));
+  FV_TRY(make_tmap(&tmB, tc->bf16, tc->half.p, n, Kp, TILE_N));
+
   init_stats_kernel<<<1, 1, 0, ctx->stream>>>(qst);
   FV_CUDA(cudaMemsetAsync(retry_count, 0, 8, ctx->stream));
   if (nq_pad > nq) FV_CUDA(cudaMemsetAsync(dA + nq * size_t(Kp), 0, (nq_pad - nq) * size_t(Kp) * 2, ctx->stream));
   FV_TRY(convert(ctx, tc->bf16, d_queries, nq, pd, Kp, dA, qn2, metric == FV_L2, qst));
   stage_mark(ctx);
 
-  FV_TRY(ctx->scratch[6].reserve(size_t(grid) * segmax * 256 * KP * sizeof(u64)));
-  CUtensorMap tmA, tmB;
-  FV_TRY(make_tmap(&tmA, tc->bf16, dA, nq_pad, Kp, 128));
-  FV_TRY(make_tmap(&tmB, tc->bf16, tc->half.p, n, Kp, TILE_N));
-  GemmParams gp{};
-  gp.n = int(n);
-  gp.nq = int(nq);
-  gp.KB = KB;
-  gp.NT = NT;
-  gp.MT = MT;
-  gp.U = U;
-  gp.upc = upc;
-  gp.segmax = segmax;
-  gp.nstage = nstage;
-  gp.scale = metric == FV_L2 ? -2.f : -1.f;
-  gp.idesc = make_idesc(128, TILE_N, tc->bf16);
-  gp.bnorm = tc->norm2.as<float>();
-  gp.cand = ctx->scratch[6].as<u64>();
-  gp.err = err;
-  // Candidate slots per list: the exact-arithmetic regime needs no margin beyond k (scores ARE the
-  // distances); otherwise the certificate needs candidates past the k-th, so the full 16 are kept.
-  const RangeStats& hb = tc->h_stats;
-  const float bm = std::max(std::fabs(hb.min_v), std::fabs(hb.max_v));
-  const bool base_exact = !hb.not_integer && !hb.not_finite && bm <= (tc->bf16 ? 256.f : 2048.f) &&
-                          float(Kp) * bm * bm <= 8388608.f;
-  const int kp = (base_exact && k <= 10) ? 10 : KP;
-  void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams) =
-      MH == 2 ? (kp == 10 ? gemm_topk_kernel<2, 10> : gemm_topk_kernel<2, 16>)
-              : (kp == 10 ? gemm_topk_kernel<1, 10> : gemm_topk_kernel<1, 16>);
-  FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-  kern<<<grid, NTHREADS, smem, ctx->stream>>>(tmA, tmB, gp);
-  ctx->stats.launches++;
-  FV_CUDA(cudaGetLastError());
+  // sample pass: per query the SAMPLE_R best scores over 1 row in SAMPLE_EVERY
+  GemmParams gs{};
+  gs.n = int(tc->ns);
+  gs.nq = int(nq);
+  gs.KB = ts.KB;
+  gs.NT = ts.NT;
+  gs.MT = ts.MT;
+  gs.U = ts.U;
+  gs.upc = ts.upc;
+  gs.segmax = ts.segmax;
+  gs.nstage = ts.nstage;
+  gs.scratch_bytes = SCRATCH_BYTES;
+  gs.scale = metric == FV_L2 ? -2.f : -1.f;
+  gs.idesc = make_idesc(128, TILE_N, tc->bf16);
+  gs.bnorm = tc->samp_norm2.as<float>();
+  gs.cand = ctx->scratch[6].as<u64>();
+  gs.err = err;
+  FV_TRY((launch_gemm<SAMPLE_R + 1, false>(ctx, ts, tmA, tmS, gs)));
   stage_mark(ctx);
 
-  FV_TRY(ctx->scratch[7].reserve(nq * sizeof(uint32_t)));
+  // main pass: every row scoring below the query's sampled bound becomes a candidate
+  GemmParams gp = gs;
+  gp.n = int(n);
+  gp.NT = tm.NT;
+  gp.MT = tm.MT;
+  gp.U = tm.U;
+  gp.upc = tm.upc;
+  gp.segmax = tm.segmax;
+  gp.nstage = tm.nstage;
+  gp.scratch_bytes = 0;
+  gp.bnorm = tc->norm2.as<float>();
+  gp.cand = nullptr;
+  gp.tau_lists = gs.cand;
+  gp.tNT = ts.NT;
+  gp.tsegmax = ts.segmax;
+  gp.tupc = ts.upc;
+  gp.cbuf = ctx->scratch[9].as<u64>();
+  gp.ccnt = ccnt;
+  gp.ccap = CAND_CAP;
+  FV_TRY((launch_gemm<2, true>(ctx, tm, tmA, tmB, gp)));
+  stage_mark(ctx);
+
   RerankParams rp{};
-  rp.cand = gp.cand;
+  rp.tau_lists = gp.tau_lists;
+  rp.tNT = gp.tNT;
+  rp.tsegmax = gp.tsegmax;
+  rp.tupc = gp.tupc;
+  rp.cbuf = gp.cbuf;
+  rp.ccnt = gp.ccnt;
+  rp.ccap = gp.ccap;
+  rp.NT = tm.NT;
+  rp.segmax = tm.segmax;
+  rp.upc = tm.upc;
   rp.rows = d_rows;
   rp.queries = d_queries;
   rp.qnorm2 = qn2;
@@ -849,13 +1020,9 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   rp.pd = pd;
   rp.Kp = Kp;
   rp.k = k;
-  rp.MH = MH;
-  rp.NT = NT;
-  rp.segmax = segmax;
+  rp.MH = tm.MH;
   rp.is_l2 = metric == FV_L2 ? 1 : 0;
   rp.bf16 = tc->bf16 ? 1 : 0;
-  rp.upc = upc;
-  rp.kp = kp;
   rp.id_base = id_base;
   rp.out_keys = d_out_keys;
   rp.retry_ids = ctx->scratch[7].as<uint32_t>();

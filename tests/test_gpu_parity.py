@@ -50,8 +50,8 @@ def test_flat_matches_the_oracle(fv, oracle, ctx, metric, dim, n, nq, k, mode):
     if metric == IP:
         base, queries = oracle.normalize(base), oracle.normalize(queries)
     g, o = flat_pair(fv, oracle, ctx, metric, dim, base)
-    if mode == 1 and (k > 16 or n < 4096):
-        pytest.skip("tensor-core front end covers k <= 16 and n >= 4096")
+    if mode == 1 and (k > 32 or n < 4096):
+        pytest.skip("tensor-core front end covers k <= 32 and n >= 4096")
     g.set_mode(mode)
     got, gc = g.search_batch(queries, k)
     want, wc = o.search_batch(queries, k)
