@@ -18,6 +18,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cmath>
+#include <cstdlib>
 #include <memory>
 #include <mutex>
 #include <thread>
@@ -496,8 +497,12 @@ static int hnsw_search_dev(fv_hnsw* h, const float* d_queries, size_t nq, size_t
   g.ep = h->ep;
   g.n = n;
   // visited-table size: room for the nodes a beam of width ef usually touches, doubled
-  int log2slots = 10;
-  while ((size_t(1) << log2slots) < ef * h->m0 * 3 && log2slots < 26) log2slots++;
+  int log2slots = 11;
+  // visited-table size: a beam of width ef evaluates a few dozen nodes per entry kept; start at 48 * ef slots
+  // (the table may fill to one half) and let the overflow path quadruple it for the queries that need more
+  const char* menv = getenv("FV_HNSW_SLOTS_PER_EF");  // tuning knob
+  const size_t per_ef = menv ? size_t(atoi(menv)) : 48;
+  while ((size_t(1) << log2slots) < ef * per_ef && log2slots < 26) log2slots++;
   const uint32_t* d_qids = nullptr;
   size_t active = nq;
   std::vector<uint32_t> h_over(nq), retry;
@@ -507,7 +512,11 @@ static int hnsw_search_dev(fv_hnsw* h, const float* d_queries, size_t nq, size_t
     const size_t budget = std::min<size_t>(ctx->smem_optin, 200 * 1024);
     int W = 8;
     bool use_global = false;
-    if (base_bytes + slots * 4 > budget / 2) use_global = true;  // at least two warps per block in shared memory
+    // Tables in shared memory cap the resident warps (latency-bound kernel); in global memory they are
+    // L2-resident and 32 warps fit per SM.
+    const char* genv = getenv("FV_HNSW_TABLES");  // tuning knob: "smem" or "global"
+    use_global = genv ? genv[0] == 'g' : true;
+    if (base_bytes + slots * 4 > budget / 2) use_global = true;
     const size_t per_warp = base_bytes + (use_global ? 0 : slots * 4);
     while (W > 1 && per_warp * W > budget) W >>= 1;
     if (per_warp * W > budget) return fail(FV_ERR_UNSUPPORTED, "dimension and ef too large for shared memory");

@@ -10,6 +10,7 @@
 // host in data order (kmeans.rs:55-71), as does the stable filing of rows into lists.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <numeric>
 
 #include "internal.h"
@@ -226,7 +227,7 @@ struct ScanArgs {
 };
 
 template <bool M16>
-__global__ void __launch_bounds__(128) ivfpq_scan_kernel(ScanArgs a) {
+__global__ void __launch_bounds__(256) ivfpq_scan_kernel(ScanArgs a) {
   unsigned char* smem_raw = dyn_smem();
   const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int tab = a.m * int(KSUB);
@@ -262,6 +263,11 @@ __global__ void __launch_bounds__(128) ivfpq_scan_kernel(ScanArgs a) {
   }
   __syncthreads();
 
+  // The tightest last-kept key of any warp bounds the global keep-th best from above, so every warp may
+  // filter with it: a row that cannot enter that warp's list cannot be among the best `keep` overall.
+  __shared__ unsigned long long shared_bound;
+  if (tid == 0) shared_bound = FV_EMPTY_KEY;
+  __syncthreads();
   u64 bound = FV_EMPTY_KEY;
   unsigned long long scanned = 0;
   for (int p = 0; p < a.nprobe; ++p) {
@@ -311,7 +317,15 @@ __global__ void __launch_bounds__(128) ivfpq_scan_kernel(ScanArgs a) {
         }
         if (d < INFINITY) key = make_key(d, a.ids[off + r]);
       }
-      bound = warp_list_offer(mylist, a.keep, key, bound);
+      const u64 sb = *reinterpret_cast<volatile unsigned long long*>(&shared_bound);
+      const u64 eff = sb < bound ? sb : bound;
+      if (__any_sync(FV_FULL, key < eff)) {
+        const u64 nb = warp_list_offer(mylist, a.keep, key < eff ? key : FV_EMPTY_KEY, bound);
+        if (nb < bound) {
+          bound = nb;
+          if (lane == 0) atomicMin(&shared_bound, bound);
+        }
+      }
     }
     __syncthreads();
   }
@@ -694,7 +708,8 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   a.out_exact = d_exact;
   a.out_counts = d_counts;
   a.rows_scanned = d_rows;
-  const int W = 4;
+  const char* wenv = getenv("FV_IVF_WARPS");  // tuning knob
+  const int W = wenv ? atoi(wenv) : (keep <= 16 ? 8 : 4);
   const bool use_pre = ix->metric == FV_L2 && ix->has_pre;
   const size_t tab = ix->m * fv::KSUB;
   const size_t smem = (2 * size_t(pd) + tab * (use_pre ? 2 : 1)) * sizeof(float) + (size_t(W) * keep + keep + k) * sizeof(u64);
