@@ -8,8 +8,9 @@ value range of SIFT1M, which cannot be shipped: clipped-integer Gaussian mixture
 workload is the IVF-PQ configuration (nlist=1024, M=16x8 bit, trained on a 100,000-row sample,
 nprobe=64, refine=10); --workload flat is exact L2 search on the same data, --workload hnsw the
 graph index.  With N>1 GPUs (one process per GPU under torchrun) the base rows are sharded
-contiguously over the ranks (strong scaling: the 1M rows are fixed), every rank searches its shard
-and the per-shard candidates are all-gathered over NCCL and merged by a kernel of this library.
+over the ranks (strong scaling: the 1M rows are fixed) -- contiguous row ranges for exact search, inverted
+lists for IVF-PQ -- every rank searches its part and the per-rank candidates are all-gathered over NCCL and
+merged by a kernel of this library.
 
 The line printed by rank 0 carries: `value` (device-resident queries), `e2e` (host queries in pinned
 memory, copies inside the timed region), `roofline` of the dominant kernel (algorithmic bytes or
@@ -162,7 +163,8 @@ def run_reference(args):
 
 def workload_config(workload: str, n_gpus: int) -> dict:
     cfg = {"n": N_BASE, "d": DIM, "nq": NQ, "k": K, "distribution": f"clipped-integer Gaussian mixture, {CLUSTERS} clusters",
-           "sharding": f"rows over {n_gpus} GPU(s), per-shard top-k all-gathered and merged" if n_gpus > 1 else "single GPU",
+           "sharding": (f"{'inverted lists' if workload == 'ivfpq' else 'row ranges'} over {n_gpus} GPUs, per-shard candidates "
+                        "all-gathered (NCCL) and merged") if n_gpus > 1 else "single GPU",
            "l2_note": "inputs exceed L2: 1M x 128 f32 rows (512 MB) plus 16 MB of codes are re-read each step"}
     if workload == "ivfpq":
         cfg.update({"workload": "IVF-PQ L2 search, nlist=1024, M=16x8bit, nprobe=64, refine=10 (BASELINE configs[2])",
@@ -193,26 +195,36 @@ def run_ours(args):
     ctx.set_timing(True)
     stream = torch.cuda.ExternalStream(ctx.stream_handle(), device=local)  # everything runs on the library's stream
 
-    per = (N_BASE + world - 1) // world
-    lo, hi = rank * per, min(N_BASE, (rank + 1) * per)
-    base, queries = make_data((lo, hi))
+    from ferrolm_b200.sharding import ShardedSearch, row_range
+
     t_build = time.perf_counter()
-    refine = 0
+    refine, nprobe = 0, 0
     if args.workload == "ivfpq":
+        # sharded by inverted list: every rank trains the same quantizers (deterministic) and is given all rows;
+        # it keeps and scans the lists l with l % world == rank
+        lo, hi = 0, N_BASE
+        base, queries = make_data((lo, hi))
         learn = fv.datagen(0, 3, IVF["learn"], DIM, CLUSTERS)
         ix = fv.IvfPq.train(ctx, fv.Metric.L2, DIM, learn, fv.IvfPqParams(IVF["nlist"], IVF["m"], IVF["iters"], True, 1))
-        ix.set_id_base(lo)
+        ix.set_shard(rank, world)
         ix.add(base)
-        refine = IVF["refine"]
+        refine, nprobe = IVF["refine"], IVF["nprobe"]
+        searcher = ShardedSearch(ctx, ix, "ivfpq", world)
     elif args.workload == "flat":
+        lo, hi = row_range(rank, world, N_BASE)  # contiguous row shards
+        base, queries = make_data((lo, hi))
         ix = fv.FlatIndex(ctx, fv.Metric.L2, DIM)
         ix.set_id_base(lo)
         ix.add(base)
+        searcher = ShardedSearch(ctx, ix, "flat", world)
     else:
         if world > 1:
             raise SystemExit("hnsw: replicas only (one graph); run with --gpus 1")
+        lo, hi = 0, N_BASE
+        base, queries = make_data((lo, hi))
         ix = fv.Hnsw.build(ctx, fv.Metric.L2, DIM, base, fv.HnswParams(HNSW["m"], HNSW["ef_construction"], 1),
                            threads=os.cpu_count() or 1)
+        searcher = None
     build_s = time.perf_counter() - t_build
 
     dq = torch.from_numpy(queries).cuda()
@@ -223,43 +235,19 @@ def run_ours(args):
     rows_scanned = [0]
     work = [0, 0]
 
-    def local_search(q):
-        """One shard's search on device-resident queries; returns what the merge needs."""
-        if args.workload == "ivfpq":
-            if world > 1 and refine > 0:
-                r = ix.search_candidates(q, K * refine, IVF["nprobe"])
+    def step(q):
+        """One search_batch of the whole (possibly sharded) index on device-resident queries."""
+        with torch.cuda.stream(stream):
+            if searcher is None:
+                r = ix.search_batch(q, K, HNSW["ef"])
             else:
-                r = ix.search_batch(q, K, IVF["nprobe"], refine)
-        elif args.workload == "flat":
-            r = ix.search_batch(q, K)
-        else:
-            r = ix.search_batch(q, K, HNSW["ef"])
-        st = ctx.stats()
+                r = searcher.search_batch(q, K, nprobe, refine)
+        st = ctx.stats()  # the merge kernels add to the launch count and leave the search's stage times in place
         launches[0] += st["launches"]
         stage_sum[:] += np.array(st["stage_ms"])
         rows_scanned[0] = st["rows_scanned"]
         work[0], work[1] = st["dist_evals"], st["expansions"]
-        return r
-
-    def gather(t):
-        out = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
-        dist.all_gather_into_tensor(out, t.contiguous())
-        return out
-
-    def step(q):
-        with torch.cuda.stream(stream):
-            r = local_search(q)
-            if world == 1:
-                return r[0], r[1]
-            if args.workload == "ivfpq" and refine > 0:
-                adc, exact, counts = (gather(x) for x in r)
-                stream.synchronize()
-                launches[0] += 2
-                return ctx.merge_refine(adc, exact, counts, K)
-            parts, counts = gather(r[0]), gather(r[1])
-            stream.synchronize()
-            launches[0] += 2
-            return ctx.merge_topk(parts, counts, K)
+        return r[0], r[1]
 
     def barrier():
         if world > 1:
@@ -350,6 +338,17 @@ def run_ours(args):
         line["roofline"] = {"kernel": "hnsw_search_kernel", "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"],
                             "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
                             "algorithmic_bytes_per_launch": int(alg), "kernel_ms": kms}
+    # DRAM traffic of the dominant kernel: from the committed ncu capture of a smaller case, scaled to this launch
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            tr = json.load(f)[args.workload]
+        if args.workload == "flat":
+            line["roofline"]["traffic"] = tr["bytes_per_query_tile"] * ((NQ + 255) // 256) * (hi - lo) / 1_000_000
+        else:
+            line["roofline"]["traffic"] = tr["bytes_per_query"] * NQ
+        line["roofline"]["traffic_note"] = "ncu dram bytes of a smaller capture, scaled: " + tr["scaling"]
+    except Exception:
+        pass
     # ---- CPU baseline (the oracle on the host cores) and recall against exact search, on a bounded sample
     if world == 1 and not args.no_cpu:
         from oracle import oracle

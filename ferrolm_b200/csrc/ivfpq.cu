@@ -194,12 +194,29 @@ __global__ void move_lists_kernel(const uint32_t* __restrict__ old_off, const ui
 }
 
 __global__ void scatter_rows_kernel(const uint32_t* __restrict__ dest, const uint8_t* __restrict__ codes, size_t n,
-                                    int m, uint32_t first_id, uint8_t* __restrict__ new_codes,
-                                    uint32_t* __restrict__ new_ids) {
+                                    int m, uint32_t first_id, const uint32_t* __restrict__ row_ids,
+                                    uint8_t* __restrict__ new_codes, uint32_t* __restrict__ new_ids) {
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
     const size_t d = dest[i];
-    new_ids[d] = first_id + uint32_t(i);
+    new_ids[d] = row_ids ? row_ids[i] : first_id + uint32_t(i);
     for (int j = 0; j < m; ++j) new_codes[d * size_t(m) + j] = codes[i * size_t(m) + j];
+  }
+}
+
+// list-sharded add: keeps the rows a shard owns (row sel[s] of the chunk), with their global ids
+__global__ void gather_owned_kernel(const float* __restrict__ x, const uint32_t* __restrict__ assign,
+                                    const uint32_t* __restrict__ sel, size_t ns, int pd, uint32_t first_id,
+                                    float* __restrict__ xs, uint32_t* __restrict__ assign_s, uint32_t* __restrict__ ids_s) {
+  const int lane = threadIdx.x & 31;
+  const size_t s = blockIdx.x * size_t(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (s >= ns) return;
+  const size_t i = sel[s];
+  const float4* a = reinterpret_cast<const float4*>(x + i * size_t(pd));
+  float4* b = reinterpret_cast<float4*>(xs + s * size_t(pd));
+  for (int c = lane; c < pd / 4; c += 32) b[c] = a[c];
+  if (lane == 0) {
+    assign_s[s] = assign[i];
+    ids_s[s] = first_id + uint32_t(i);
   }
 }
 
@@ -215,8 +232,13 @@ struct ScanArgs {
   const uint8_t* codes;
   const uint32_t* ids;
   const float* vectors;  // may be null
+  const uint32_t* owned_ids;  // list-sharded index: ascending ids of the kept vectors (row s of `vectors`); else null
+  uint32_t owned_n;
+  int shard_rank, shard_world;  // this shard scans the probed lists l with l % world == rank
   int metric, pd, m, dsub, nprobe, keep, k;
   int refine;        // 1: re-rank the kept candidates exactly
+  int buffered;      // 1: per-warp unsorted buffers of 256 keys, compacted by sorting (16 < keep <= 128)
+  int lstride;       // keys of shared memory per warp: keep, or 256 when buffered
   int candidates;    // 1: write the kept candidates with both distances instead of the final k
   uint32_t id_base;
   u64* out_keys;             // nq x k        (candidates == 0)
@@ -225,6 +247,49 @@ struct ScanArgs {
   uint32_t* out_counts;      // nq
   unsigned long long* rows_scanned;
 };
+
+// Sorts the 256 keys at `buf` (shared memory, owned by the calling warp) ascending: a bitonic network with 8
+// keys per lane (element r * 32 + lane in register r), strides of 32 and more inside the lane, smaller ones by
+// shuffle.  Kept out of line so that the network exists once in the kernel.
+__device__ __noinline__ void warp_sort256(u64* buf, int cap) {  // cap <= 256 keys live at buf; the rest count as empty
+  const int lane = lane_id();
+  u64 v[8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r) v[r] = (r * 32 + lane) < cap ? buf[r * 32 + lane] : FV_EMPTY_KEY;
+#pragma unroll
+  for (int k = 2; k <= 256; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      if (j >= 32) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const int pr = r ^ (j >> 5);
+          if (pr > r) {
+            const bool asc = ((r * 32 + lane) & k) == 0;
+            const u64 x = v[r], y = v[pr];
+            const bool sw = asc ? (x > y) : (x < y);
+            v[r] = sw ? y : x;
+            v[pr] = sw ? x : y;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const bool asc = ((r * 32 + lane) & k) == 0;
+          const u64 o = __shfl_xor_sync(FV_FULL, v[r], j);
+          const bool keep_min = ((lane & j) == 0) == asc;
+          const u64 lo = v[r] < o ? v[r] : o, hi = v[r] < o ? o : v[r];
+          v[r] = keep_min ? lo : hi;
+        }
+      }
+    }
+  }
+  __syncwarp();
+#pragma unroll
+  for (int r = 0; r < 8; ++r)
+    if ((r * 32 + lane) < cap) buf[r * 32 + lane] = v[r];
+  __syncwarp();
+}
 
 template <bool M16>
 __global__ void __launch_bounds__(256) ivfpq_scan_kernel(ScanArgs a) {
@@ -237,12 +302,13 @@ __global__ void __launch_bounds__(256) ivfpq_scan_kernel(ScanArgs a) {
   float* qlut = lut + tab;                         // tab (L2 with tables only)
   const bool use_pre = a.metric == FV_L2 && a.pre != nullptr;
   u64* lists = reinterpret_cast<u64*>(qlut + (use_pre ? tab : 0));  // W x keep, then keep keys for the re-rank
-  u64* mylist = lists + size_t(w) * a.keep;
-  u64* rerank = lists + size_t(W) * a.keep;
+  u64* mylist = lists + size_t(w) * a.lstride;
+  u64* rerank = lists + size_t(W) * a.lstride;
   const size_t q = blockIdx.x;
 
   for (int c = tid; c < a.pd; c += blockDim.x) sq[c] = a.queries[q * size_t(a.pd) + c];
-  warp_list_init(mylist, a.keep);
+  warp_list_init(mylist, a.lstride);
+  int bcnt = 0;  // buffered mode: keys in this warp's buffer
   __syncthreads();
   if (a.metric == FV_INNER_PRODUCT) {  // ivfpq.rs:236-238, :307
     for (int i = tid; i < tab; i += blockDim.x) {
@@ -274,6 +340,7 @@ __global__ void __launch_bounds__(256) ivfpq_scan_kernel(ScanArgs a) {
     const u64 cell = a.cells[q * size_t(a.nprobe) + p];
     if (cell == FV_EMPTY_KEY) break;
     const uint32_t l = key_id(cell);
+    if (a.shard_world > 1 && int(l % uint32_t(a.shard_world)) != a.shard_rank) continue;  // another shard's list
     float base;
     if (a.metric == FV_L2 && use_pre) {  // ivfpq.rs:256-262
       const float* pre = a.pre + size_t(l) * tab;
@@ -319,7 +386,25 @@ __global__ void __launch_bounds__(256) ivfpq_scan_kernel(ScanArgs a) {
       }
       const u64 sb = *reinterpret_cast<volatile unsigned long long*>(&shared_bound);
       const u64 eff = sb < bound ? sb : bound;
-      if (__any_sync(FV_FULL, key < eff)) {
+      const unsigned hit = __ballot_sync(FV_FULL, key < eff);
+      if (a.buffered) {
+        // append the passing keys; when the buffer is nearly full, sort it and keep the best `keep`
+        if (hit) {
+          if (key < eff) mylist[bcnt + __popc(hit & ((1u << lane) - 1u))] = key;
+          bcnt += __popc(hit);
+          __syncwarp();
+          if (bcnt > a.lstride - 32) {
+            for (int e = bcnt + lane; e < a.lstride; e += 32) mylist[e] = FV_EMPTY_KEY;
+            __syncwarp();
+            warp_sort256(mylist, a.lstride);
+            bcnt = min(bcnt, a.keep);
+            if (bcnt == a.keep) {
+              bound = mylist[a.keep - 1];
+              if (lane == 0) atomicMin(&shared_bound, bound);
+            }
+          }
+        }
+      } else if (hit) {
         const u64 nb = warp_list_offer(mylist, a.keep, key < eff ? key : FV_EMPTY_KEY, bound);
         if (nb < bound) {
           bound = nb;
@@ -332,10 +417,27 @@ __global__ void __launch_bounds__(256) ivfpq_scan_kernel(ScanArgs a) {
   if (tid == 0 && a.rows_scanned) atomicAdd(a.rows_scanned, scanned);
 
   // fold the other warps' lists into warp 0's
+  if (a.buffered) {
+    for (int e = bcnt + lane; e < a.lstride; e += 32) mylist[e] = FV_EMPTY_KEY;
+    __syncwarp();
+    warp_sort256(mylist, a.lstride);  // every warp ends with its best `keep` sorted at the front
+  }
   __syncthreads();
-  if (w == 0) {
+  if (w == 0 && a.buffered) {
+    // merge by sorting two lists together; the buffer holds keep + 96 >= keep + 32 keys, so a list of `keep`
+    // goes in in pieces of at most lstride - keep keys
     for (int ow = 1; ow < W; ++ow) {
-      const u64* other = lists + size_t(ow) * a.keep;
+      const u64* other = lists + size_t(ow) * a.lstride;
+      const int room = a.lstride - a.keep;
+      for (int o0 = 0; o0 < a.keep; o0 += room) {
+        for (int e = lane; e < room; e += 32) mylist[a.keep + e] = (o0 + e) < a.keep ? other[o0 + e] : FV_EMPTY_KEY;
+        __syncwarp();
+        warp_sort256(mylist, a.lstride);
+      }
+    }
+  } else if (w == 0) {
+    for (int ow = 1; ow < W; ++ow) {
+      const u64* other = lists + size_t(ow) * a.lstride;
       for (int e0 = 0; e0 < a.keep; e0 += 32) {
         const int e = e0 + lane;
         bound = warp_list_offer(mylist, a.keep, e < a.keep ? other[e] : FV_EMPTY_KEY, bound);
@@ -355,7 +457,17 @@ __global__ void __launch_bounds__(256) ivfpq_scan_kernel(ScanArgs a) {
     float ex = INFINITY;
     if (c != FV_EMPTY_KEY) {
       const uint32_t id = key_id(c);
-      ex = exact_distance(a.metric, sq, a.vectors + size_t(id - a.id_base) * a.pd, a.pd);
+      size_t slot = size_t(id - a.id_base);
+      if (a.owned_ids) {  // position of the id among the ids this shard keeps (ascending)
+        uint32_t lo = 0, hi = a.owned_n;
+        while (lo < hi) {
+          const uint32_t mid = (lo + hi) >> 1;
+          if (a.owned_ids[mid] < id) lo = mid + 1;
+          else hi = mid;
+        }
+        slot = lo;
+      }
+      ex = exact_distance(a.metric, sq, a.vectors + slot * a.pd, a.pd);
       rk = make_key(ex, id);
     }
     rerank[e] = rk;
@@ -396,7 +508,7 @@ __global__ void __launch_bounds__(256) ivfpq_scan_kernel(ScanArgs a) {
 struct fv_ivfpq {
   fv_ctx* ctx = nullptr;
   ~fv_ivfpq() {
-    centroids.release(); codebooks.release(); pre.release(); list_off.release();
+    centroids.release(); codebooks.release(); pre.release(); list_off.release(); owned_ids.release();
     codes.release(); ids.release(); vectors.release();
     if (ctx) fv::ctx_release(ctx);
   }
@@ -405,7 +517,10 @@ struct fv_ivfpq {
   size_t nlist = 0, m = 0, dsub = 0;
   bool keep = false;
   uint32_t id_base = 0;
-  size_t count = 0;
+  size_t count = 0;   // rows stored here
+  size_t seen = 0;    // rows passed to add (equals count unless the index is list-sharded)
+  int shard_rank = 0, shard_world = 1;
+  DevBuf owned_ids;   // list-sharded: ids of the kept vectors, ascending
   std::vector<float> h_centroids, h_codebooks;
   std::vector<uint32_t> h_off;  // nlist + 1
   DevBuf centroids, codebooks, pre, list_off, codes, ids, vectors;
@@ -581,6 +696,14 @@ int fv_ivfpq_set_id_base(fv_ivfpq* ix, uint32_t id_base) {
   return FV_OK;
 }
 
+int fv_ivfpq_set_shard(fv_ivfpq* ix, int rank, int world) {
+  if (!ix || world < 1 || rank < 0 || rank >= world) return fv::fail(FV_ERR_ARG, "fv_ivfpq_set_shard: bad rank or world");
+  if (ix->seen) return fv::fail(FV_ERR_ARG, "the shard must be set before the first add");
+  ix->shard_rank = rank;
+  ix->shard_world = world;
+  return FV_OK;
+}
+
 // ivfpq.rs:161-192
 int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n_total) {
   if (!ix || (!vectors && n_total)) return fv::fail(FV_ERR_ARG, "fv_ivfpq_add: null argument");
@@ -589,29 +712,66 @@ int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n_total) {
   const size_t pd = ix->pd, m = ix->m;
   const size_t CH = size_t(1) << 22;
   for (size_t b0 = 0; b0 < n_total; b0 += CH) {
-    const size_t n = std::min(CH, n_total - b0);
-    if (ix->count + n > 0xFFFFFFF0ull) return fv::fail(FV_ERR_UNSUPPORTED, "more than 2^32 rows");
+    size_t n = std::min(CH, n_total - b0);
+    if (ix->seen + n > 0xFFFFFFF0ull) return fv::fail(FV_ERR_UNSUPPORTED, "more than 2^32 rows");
     const float* src = vectors + b0 * size_t(ix->dim);
-    DevBuf d_x_tmp, d_assign, d_codes, d_dest;
-    float* d_x;
-    if (ix->keep) {  // rows go straight to their place in the kept vectors
-      FV_TRY(ix->vectors.grow((ix->count + n) * pd * sizeof(float), ix->count * pd * sizeof(float), ctx->stream));
-      d_x = ix->vectors.as<float>() + ix->count * pd;
-    } else {
-      FV_TRY(d_x_tmp.reserve(n * pd * sizeof(float)));
-      d_x = d_x_tmp.as<float>();
-    }
+    DevBuf d_x_tmp, d_assign, d_codes, d_dest, d_sel, d_xs, d_assign_s, d_ids_s;
+    FV_TRY(d_x_tmp.reserve(n * pd * sizeof(float)));
+    float* d_x = d_x_tmp.as<float>();
     FV_TRY(fv::upload_padded(ctx, src, false, n, ix->dim, pd, d_x));
     FV_TRY(d_assign.reserve(n * sizeof(uint32_t)));
-    FV_TRY(d_codes.reserve(n * m));
-    FV_TRY(d_dest.reserve(n * sizeof(uint32_t)));
     // ivfpq.rs:194-204: L2 -> nearest centroid; inner product -> the best cell, every cell pushed
     FV_TRY(fv::assign_dev(ctx, ix->metric, ix->metric == FV_L2, d_x, n, ix->centroids.as<float>(), ix->nlist, pd,
                           d_assign.as<uint32_t>()));
-    FV_TRY(fv::launch_encode(ctx, ix, d_x, d_assign.as<uint32_t>(), n, d_codes.as<uint8_t>()));
-    std::vector<uint32_t> assign(n);
-    FV_CUDA(cudaMemcpyAsync(assign.data(), d_assign.p, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    std::vector<uint32_t> assign_all(n);
+    FV_CUDA(cudaMemcpyAsync(assign_all.data(), d_assign.p, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
     FV_CUDA(cudaStreamSynchronize(ctx->stream));
+    // list-sharded: keep only the rows whose list this shard owns; ids still count every row given to add
+    const size_t n_chunk = n;
+    const uint32_t first_id = ix->id_base + uint32_t(ix->seen);
+    const uint32_t* d_row_ids = nullptr;
+    uint32_t* d_assign_use = d_assign.as<uint32_t>();
+    std::vector<uint32_t> assign;
+    if (ix->shard_world > 1) {
+      std::vector<uint32_t> sel;
+      for (size_t i = 0; i < n; i++)
+        if (int(assign_all[i] % uint32_t(ix->shard_world)) == ix->shard_rank) {
+          sel.push_back(uint32_t(i));
+          assign.push_back(assign_all[i]);
+        }
+      n = sel.size();
+      FV_TRY(d_sel.reserve(n * sizeof(uint32_t) + 16));
+      FV_TRY(d_xs.reserve(n * pd * sizeof(float) + 16));
+      FV_TRY(d_assign_s.reserve(n * sizeof(uint32_t) + 16));
+      FV_TRY(d_ids_s.reserve(n * sizeof(uint32_t) + 16));
+      if (n) {
+        FV_CUDA(cudaMemcpyAsync(d_sel.p, sel.data(), n * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+        fv::gather_owned_kernel<<<unsigned((n + 7) / 8), 256, 0, ctx->stream>>>(
+            d_x, d_assign.as<uint32_t>(), d_sel.as<uint32_t>(), n, int(pd), first_id, d_xs.as<float>(),
+            d_assign_s.as<uint32_t>(), d_ids_s.as<uint32_t>());
+        ctx->stats.launches++;
+        FV_CUDA(cudaGetLastError());
+        FV_CUDA(cudaStreamSynchronize(ctx->stream));
+      }
+      d_x = d_xs.as<float>();
+      d_assign_use = d_assign_s.as<uint32_t>();
+      d_row_ids = d_ids_s.as<uint32_t>();
+      FV_TRY(ix->owned_ids.grow((ix->count + n) * sizeof(uint32_t) + 16, ix->count * sizeof(uint32_t), ctx->stream));
+      if (n)
+        FV_CUDA(cudaMemcpyAsync(ix->owned_ids.as<uint32_t>() + ix->count, d_row_ids, n * sizeof(uint32_t),
+                                cudaMemcpyDeviceToDevice, ctx->stream));
+    } else {
+      assign.swap(assign_all);
+    }
+    if (ix->keep) {
+      FV_TRY(ix->vectors.grow((ix->count + n) * pd * sizeof(float) + 16, ix->count * pd * sizeof(float), ctx->stream));
+      if (n)
+        FV_CUDA(cudaMemcpyAsync(ix->vectors.as<float>() + ix->count * pd, d_x, n * pd * sizeof(float),
+                                cudaMemcpyDeviceToDevice, ctx->stream));
+    }
+    FV_TRY(d_codes.reserve(n * m + 16));
+    FV_TRY(d_dest.reserve(n * sizeof(uint32_t) + 16));
+    if (n) FV_TRY(fv::launch_encode(ctx, ix, d_x, d_assign_use, n, d_codes.as<uint8_t>()));
     // file the rows into their lists in input order (a stable counting sort on the host)
     std::vector<uint32_t> add_cnt(ix->nlist, 0), new_off(ix->nlist + 1, 0), dest(n);
     for (size_t i = 0; i < n; i++) add_cnt[assign[i]]++;
@@ -625,7 +785,7 @@ int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n_total) {
     FV_TRY(d_new_off.reserve((ix->nlist + 1) * sizeof(uint32_t)));
     FV_CUDA(cudaMemcpyAsync(d_new_off.p, new_off.data(), (ix->nlist + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice,
                             ctx->stream));
-    FV_CUDA(cudaMemcpyAsync(d_dest.p, dest.data(), n * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+    if (n) FV_CUDA(cudaMemcpyAsync(d_dest.p, dest.data(), n * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
     if (ix->count) {
       fv::move_lists_kernel<<<unsigned(ix->nlist), 128, 0, ctx->stream>>>(
           ix->list_off.as<uint32_t>(), d_new_off.as<uint32_t>(), int(m), ix->codes.as<uint8_t>(), ix->ids.as<uint32_t>(),
@@ -634,8 +794,8 @@ int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n_total) {
       FV_CUDA(cudaGetLastError());
     }
     fv::scatter_rows_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(
-        d_dest.as<uint32_t>(), d_codes.as<uint8_t>(), n, int(m), ix->id_base + uint32_t(ix->count),
-        new_codes.as<uint8_t>(), new_ids.as<uint32_t>());
+        d_dest.as<uint32_t>(), d_codes.as<uint8_t>(), n, int(m), first_id, d_row_ids, new_codes.as<uint8_t>(),
+        new_ids.as<uint32_t>());
     ctx->stats.launches++;
     FV_CUDA(cudaGetLastError());
     FV_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -647,6 +807,7 @@ int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n_total) {
     FV_TRY(fv::upload_offsets(ix));
     FV_CUDA(cudaStreamSynchronize(ctx->stream));
     ix->count += n;
+    ix->seen += n_chunk;
   }
   return FV_OK;
 }
@@ -693,6 +854,10 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   a.codes = ix->codes.as<uint8_t>();
   a.ids = ix->ids.as<uint32_t>();
   a.vectors = ix->keep ? ix->vectors.as<float>() : nullptr;
+  a.owned_ids = ix->shard_world > 1 ? ix->owned_ids.as<uint32_t>() : nullptr;
+  a.owned_n = uint32_t(ix->count);
+  a.shard_rank = ix->shard_rank;
+  a.shard_world = ix->shard_world;
   a.metric = ix->metric;
   a.pd = pd;
   a.m = int(ix->m);
@@ -700,6 +865,8 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   a.nprobe = np;
   a.keep = int(keep);
   a.k = int(k);
+  a.buffered = keep > 16 && keep <= 128 ? 1 : 0;
+  a.lstride = a.buffered ? int(std::min<size_t>(256, (keep + 96 + 31) / 32 * 32)) : int(keep);
   a.refine = rerank && !candidates ? 1 : 0;
   a.candidates = candidates ? 1 : 0;
   a.id_base = ix->id_base;
@@ -709,10 +876,10 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   a.out_counts = d_counts;
   a.rows_scanned = d_rows;
   const char* wenv = getenv("FV_IVF_WARPS");  // tuning knob
-  const int W = wenv ? atoi(wenv) : (keep <= 16 ? 8 : 4);
+  const int W = wenv ? atoi(wenv) : (keep <= 128 ? 8 : 4);
   const bool use_pre = ix->metric == FV_L2 && ix->has_pre;
   const size_t tab = ix->m * fv::KSUB;
-  const size_t smem = (2 * size_t(pd) + tab * (use_pre ? 2 : 1)) * sizeof(float) + (size_t(W) * keep + keep + k) * sizeof(u64);
+  const size_t smem = (2 * size_t(pd) + tab * (use_pre ? 2 : 1)) * sizeof(float) + (size_t(W) * size_t(a.lstride) + keep + k) * sizeof(u64);
   if (smem > ctx->smem_optin) return fv::fail(FV_ERR_UNSUPPORTED, "m, k * refine too large for shared memory");
   auto kern = ix->m == 16 ? fv::ivfpq_scan_kernel<true> : fv::ivfpq_scan_kernel<false>;
   if (smem > 48 * 1024) FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
@@ -784,6 +951,7 @@ size_t fv_ivfpq_save_size(const fv_ivfpq* ix) {
 
 int fv_ivfpq_save(const fv_ivfpq* ix, uint8_t* buf, size_t cap, size_t* written) {
   if (!ix || !buf) return fv::fail(FV_ERR_ARG, "fv_ivfpq_save: null argument");
+  if (ix->shard_world > 1) return fv::fail(FV_ERR_UNSUPPORTED, "a list-sharded index holds part of the rows and cannot be saved as one file");
   const size_t need = fv_ivfpq_save_size(ix);
   if (cap < need) return fv::fail(FV_ERR_ARG, "fv_ivfpq_save: buffer too small");
   fv::DeviceGuard g(ix->ctx->device);
@@ -872,6 +1040,7 @@ int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out)
   ix->nlist = u32();
   ix->m = u32();
   ix->count = u32();
+  ix->seen = ix->count;
   if (!ok) return fv::fail(FV_ERR_FILE, trunc);
   if ((mc & 0xFF) > 1) return fv::fail(FV_ERR_FILE, "bad metric");
   ix->metric = int(mc & 0xFF);

@@ -1,0 +1,55 @@
+"""Host-side plumbing of the multi-GPU layout: one process per GPU, `torch.distributed` for the one
+exchange step.  The base is split over the ranks (contiguous row ranges for exact search, inverted lists
+for IVF-PQ), every rank searches its part for the whole query batch, the per-rank candidate lists are
+all-gathered and merged by a kernel of the library.  Nothing here computes distances.
+"""
+from __future__ import annotations
+
+
+def row_range(rank: int, world: int, n: int) -> tuple[int, int]:
+    """Contiguous rows [lo, hi) of rank `rank`: local row + lo is the global id (SURVEY 8e layout)."""
+    per = (n + world - 1) // world
+    lo = min(n, rank * per)
+    return lo, min(n, lo + per)
+
+
+def all_gather_stacked(t, world: int):
+    """(world, *t.shape) tensor holding every rank's `t`, rank-major; works for NCCL (CUDA) and gloo (CPU)."""
+    import torch
+    import torch.distributed as dist
+
+    t = t.contiguous()
+    out = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+    if t.is_cuda:
+        dist.all_gather_into_tensor(out, t)
+    else:
+        dist.all_gather(list(out.unbind(0)), t)
+    return out
+
+
+class ShardedSearch:
+    """search_batch over an index that is split across the ranks of the default process group.
+
+    kind "flat":  `index` is a FlatIndex over this rank's row range (set_id_base(lo) before add).
+    kind "ivfpq": `index` is an IvfPq with set_shard(rank, world) that was given all rows.
+    """
+
+    def __init__(self, ctx, index, kind: str, world: int):
+        self.ctx, self.index, self.kind, self.world = ctx, index, kind, world
+
+    def search_batch(self, queries, k: int, nprobe: int = 0, refine: int = 0):
+        ix = self.index
+        if self.kind == "flat":
+            out, counts = ix.search_batch(queries, k)
+            if self.world == 1:
+                return out, counts
+            return self.ctx.merge_topk(all_gather_stacked(out, self.world), all_gather_stacked(counts, self.world), k)
+        if self.world == 1:
+            return ix.search_batch(queries, k, nprobe, refine)
+        if refine > 0:
+            # a shard may not cut to k on its own: the global cut by compressed distance comes first
+            adc, exact, counts = ix.search_candidates(queries, k * refine, nprobe)
+            return self.ctx.merge_refine(all_gather_stacked(adc, self.world), all_gather_stacked(exact, self.world),
+                                         all_gather_stacked(counts, self.world), k)
+        out, counts = ix.search_batch(queries, k, nprobe, 0)
+        return self.ctx.merge_topk(all_gather_stacked(out, self.world), all_gather_stacked(counts, self.world), k)

@@ -273,6 +273,10 @@ class IvfPq:
     def set_id_base(self, base: int):
         check(lib().fv_ivfpq_set_id_base(self._h, base))
 
+    def set_shard(self, rank: int, world: int):
+        """Keep and scan only the inverted lists l with l % world == rank (give every shard the same rows)."""
+        check(lib().fv_ivfpq_set_shard(self._h, rank, world))
+
     def __len__(self) -> int:
         return lib().fv_ivfpq_len(self._h)
 

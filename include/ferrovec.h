@@ -129,6 +129,11 @@ int fv_ivfpq_search_batch_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, s
  * shard must not cut to k by itself: this call returns its best `keep` = k*refine candidates by compressed
  * distance (d_adc, ascending) together with their exact distances (d_exact), for fv_merge_refine_dev. */
 int fv_ivfpq_set_id_base(fv_ivfpq* ix, uint32_t id_base);
+/* Sharding by inverted list, for throughput: shard `rank` of `world` keeps (and scans) only the lists l with
+ * l % world == rank.  Every shard is given the same trained quantizers and the SAME rows in the same order
+ * (ids count every row passed to add); each keeps its own.  A search then does 1/world of the table builds and
+ * code scans; the per-shard results merge exactly as for row shards.  Call before the first add. */
+int fv_ivfpq_set_shard(fv_ivfpq* ix, int rank, int world);
 int fv_ivfpq_search_candidates_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t keep, size_t nprobe,
                                    fv_neighbor* d_adc, float* d_exact, uint32_t* d_counts);
 size_t fv_ivfpq_save_size(const fv_ivfpq* ix);

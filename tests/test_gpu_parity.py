@@ -308,6 +308,41 @@ def test_ivfpq_sharded_rerank_merge(fv, oracle, ctx):
     assert_same_neighbours(got, mc.cpu().numpy(), want, wc, "sharded re-rank")
 
 
+@pytest.mark.parametrize("refine", [0, 4])
+def test_ivfpq_sharded_by_list(fv, oracle, ctx, refine):
+    # every shard gets all rows and keeps the lists l % world == rank; merged result = unsharded result
+    import torch
+
+    from ferrolm_b200.sharding import ShardedSearch  # noqa: F401  (the multi-process form of this loop)
+
+    dim, n, nq, k, nprobe, world = 32, 12_000, 64, 10, 8, 3
+    base = oracle.testdata(n, dim, 3)
+    queries = oracle.testdata(nq, dim, 4)
+    o = oracle.IvfPq.train(L2, dim, base[:6000], 32, 8, 5, True, 1)
+    blob_empty = o.save()
+    o.add(base)
+    want, wc, rows = o.search_batch(queries, k, nprobe, refine, want_rows=True)
+    dq = torch.from_numpy(queries).cuda()
+    parts, scanned, total = [], 0, 0
+    for r in range(world):
+        g = fv.IvfPq.load(ctx, blob_empty)
+        g.set_shard(r, world)
+        g.add(base[:5000])
+        g.add(base[5000:])
+        total += len(g)
+        parts.append(g.search_candidates(dq, k * refine, nprobe) if refine else g.search_batch(dq, k, nprobe, 0))
+        scanned += ctx.stats()["rows_scanned"]
+        with pytest.raises(fv.FerrovecError, match="list-sharded"):
+            g.save()
+    assert total == n and scanned == rows
+    if refine:
+        merged, mc = ctx.merge_refine(*(torch.stack([p[i] for p in parts]) for i in range(3)), k)
+    else:
+        merged, mc = ctx.merge_topk(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]), k)
+    eq, tot = assert_same_neighbours(fv.neighbors_from_tensor(merged), mc.cpu().numpy(), want, wc, "list shards")
+    assert eq == tot
+
+
 # ------------------------------------------------------------------------------------------- HNSW
 @pytest.fixture(scope="module", params=[(L2, 40), (IP, 64)])
 def hnsw_pair(request, fv, oracle, ctx):
