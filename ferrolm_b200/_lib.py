@@ -112,6 +112,9 @@ SIGNATURES = {
     "fv_merge_refine_dev": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp]),
     "fv_merge_topk_static_dev": (_i, [_i, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp]),
     "fv_datagen": (_i, [_i, _u64, _sz, _sz, _sz, _sz, _i, _vp]),
+    "fv_read_fvecs": (_i, [C.c_char_p, _sz, _pp, C.POINTER(_sz), C.POINTER(_sz)]),
+    "fv_read_ivecs": (_i, [C.c_char_p, _sz, _pp, C.POINTER(_sz), C.POINTER(_sz)]),
+    "fv_free": (None, [_vp]),
 }
 
 _lib = None

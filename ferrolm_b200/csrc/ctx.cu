@@ -259,3 +259,65 @@ int fv_datagen(int kind, uint64_t seed, size_t first_row, size_t n, size_t dim, 
 }
 
 }  // extern "C"
+
+// ---- .fvecs / .ivecs files (src/vector/io.rs:7-42): per record a little-endian i32 dimension, then that many
+// 4-byte values.  The buffer handed back is malloc'ed; release it with fv_free.
+#include <cstdio>
+#include <cstdlib>
+
+static int read_vecs(const char* path, size_t limit, void** out, size_t* n, size_t* dim) {
+  if (!path || !out || !n || !dim) return fv::fail(FV_ERR_ARG, "read_vecs: null argument");
+  *out = nullptr;
+  *n = *dim = 0;
+  FILE* f = std::fopen(path, "rb");
+  if (!f) return fv::fail(FV_ERR_FILE, std::string(path) + ": cannot open");
+  std::fseek(f, 0, SEEK_END);
+  const long long size = std::ftell(f);
+  std::fseek(f, 0, SEEK_SET);
+  if (size < 4) {
+    std::fclose(f);
+    return fv::fail(FV_ERR_FILE, std::string(path) + ": empty");
+  }
+  int32_t d = 0;
+  if (std::fread(&d, 4, 1, f) != 1) d = 0;
+  const size_t rec = 4 + 4 * size_t(d > 0 ? d : 0);
+  if (d <= 0 || size_t(size) % rec != 0) {
+    std::fclose(f);
+    return fv::fail(FV_ERR_FILE, std::string(path) + ": not a vecs file of dimension " + std::to_string(d));
+  }
+  size_t rows = size_t(size) / rec;
+  if (limit && limit < rows) rows = limit;
+  unsigned char* buf = static_cast<unsigned char*>(std::malloc(rows * size_t(d) * 4 + 4));
+  std::vector<unsigned char> line(rec);
+  std::fseek(f, 0, SEEK_SET);
+  for (size_t r = 0; r < rows; r++) {
+    if (std::fread(line.data(), 1, rec, f) != rec) {
+      std::free(buf);
+      std::fclose(f);
+      return fv::fail(FV_ERR_FILE, std::string(path) + ": short read");
+    }
+    int32_t dr;
+    std::memcpy(&dr, line.data(), 4);
+    if (dr != d) {
+      std::free(buf);
+      std::fclose(f);
+      return fv::fail(FV_ERR_FILE, std::string(path) + ": record " + std::to_string(r) + " has a different dimension");
+    }
+    std::memcpy(buf + r * size_t(d) * 4, line.data() + 4, size_t(d) * 4);
+  }
+  std::fclose(f);
+  *out = buf;
+  *n = rows;
+  *dim = size_t(d);
+  return FV_OK;
+}
+
+extern "C" {
+int fv_read_fvecs(const char* path, size_t limit, float** out, size_t* n, size_t* dim) {
+  return read_vecs(path, limit, reinterpret_cast<void**>(out), n, dim);
+}
+int fv_read_ivecs(const char* path, size_t limit, uint32_t** out, size_t* n, size_t* dim) {
+  return read_vecs(path, limit, reinterpret_cast<void**>(out), n, dim);
+}
+void fv_free(void* p) { std::free(p); }
+}

@@ -169,6 +169,13 @@ int fv_normalize(float* data, size_t n, size_t dim);                            
 double fv_recall(const fv_neighbor* found, const uint32_t* counts, const uint32_t* truth, size_t truth_stride,
                  size_t nq, size_t k);                                                /* recall    :145 */
 
+/* ---- .fvecs / .ivecs benchmark files (src/vector/io.rs:7-42).  `limit` 0 = all rows.  *out is allocated by the
+ * library (rows * dim values, flattened) and released with fv_free.  Errors are FV_ERR_FILE with the reference's
+ * messages ("empty", "not a vecs file of dimension D", "record R has a different dimension"). */
+int fv_read_fvecs(const char* path, size_t limit, float** out, size_t* n, size_t* dim);      /* read_fvecs :30 */
+int fv_read_ivecs(const char* path, size_t limit, uint32_t** out, size_t* n, size_t* dim);   /* read_ivecs :36 */
+void fv_free(void* p);
+
 /* ---- merging per-shard results (no counterpart in the single-process reference; the row-sharded layout
  * needs it).  `d_parts` holds nparts blocks of nq*k_in neighbours, `d_part_counts` nparts*nq counts (may be
  * NULL = all k_in); the k_out best by (distance, id) of each query go to d_out. */
