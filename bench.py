@@ -39,6 +39,7 @@ if ROOT not in sys.path:
 N_BASE, DIM, NQ, K = 1_000_000, 128, 10_000, 10
 CLUSTERS = 256
 IVF = dict(nlist=1024, m=16, iters=20, learn=100_000, nprobe=64, refine=10)
+BIG_IVF = dict(nlist=16384, m=16, iters=20, learn=640_000, nprobe=32)  # configs[4]; 39 training rows per list
 HNSW = dict(m=16, ef_construction=200, ef=64)
 
 
@@ -199,7 +200,37 @@ def run_ours(args):
 
     t_build = time.perf_counter()
     refine, nprobe = 0, 0
-    if args.workload == "ivfpq":
+    if args.big:
+        # BASELINE configs[4]: 50M x 128, 4096 clusters; rows are generated on the GPU in chunks and never
+        # exist on the host.  exact search: row ranges; IVF-PQ: nlist=16384, nprobe=32, sharded by list.
+        queries = fv.datagen(0, 2, NQ, DIM, CLUSTERS)
+        base = None
+
+        def add_rows(index, r0, r1):
+            step_rows = 4_000_000
+            for a0 in range(r0, r1, step_rows):
+                t = fv.datagen_dev(ctx, 1, min(step_rows, r1 - a0), DIM, CLUSTERS, first_row=a0)
+                index.add(t)
+                del t
+
+        if args.workload == "ivfpq":
+            lo, hi = 0, N_BASE
+            learn = fv.datagen_dev(ctx, 3, BIG_IVF["learn"], DIM, CLUSTERS).cpu().numpy()
+            ix = fv.IvfPq.train(ctx, fv.Metric.L2, DIM, learn,
+                                fv.IvfPqParams(BIG_IVF["nlist"], BIG_IVF["m"], BIG_IVF["iters"], False, 1))
+            ix.set_shard(rank, world)
+            add_rows(ix, 0, N_BASE)
+            refine, nprobe = 0, BIG_IVF["nprobe"]
+            searcher = ShardedSearch(ctx, ix, "ivfpq", world)
+        elif args.workload == "flat":
+            lo, hi = row_range(rank, world, N_BASE)
+            ix = fv.FlatIndex(ctx, fv.Metric.L2, DIM)
+            ix.set_id_base(lo)
+            add_rows(ix, lo, hi)
+            searcher = ShardedSearch(ctx, ix, "flat", world)
+        else:
+            raise SystemExit("--big covers the flat and ivfpq workloads")
+    elif args.workload == "ivfpq":
         # sharded by inverted list: every rank trains the same quantizers (deterministic) and is given all rows;
         # it keeps and scans the lists l with l % world == rank
         lo, hi = 0, N_BASE
@@ -303,6 +334,8 @@ def run_ours(args):
 
     found = fv.neighbors_from_tensor(out)
     cnt = counts.cpu().numpy().astype(np.uint32)
+    if args.big:
+        args.no_cpu = True  # the rows never exist on the host; runs at different N are compared by the checksum below
     pk = peaks()
     line = {
         "metric": "queries/s at recall@10 (N=1M, d=128, k=10)", "value": NQ / (ms * 1e-3), "unit": "queries/s",
@@ -338,8 +371,17 @@ def run_ours(args):
         line["roofline"] = {"kernel": "hnsw_search_kernel", "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"],
                             "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
                             "algorithmic_bytes_per_launch": int(alg), "kernel_ms": kms}
+    line["result_checksum"] = int(found["id"].astype(np.uint64).sum() % (1 << 61))  # equal across GPU counts
+    if args.big:
+        line["config"]["workload"] = ("BASELINE configs[4], 50M x 128: " + ("exact L2 k-NN, row ranges" if args.workload == "flat" else
+                                     "IVF-PQ nlist=16384 M=16x8bit nprobe=32 refine=0, sharded by list"))
+        line["config"]["l2_note"] = "inputs exceed L2 by orders of magnitude"
+        if args.workload == "ivfpq":
+            line["config"].update({k: BIG_IVF[k] for k in ("nlist", "m", "nprobe")}, refine=0)
     # DRAM traffic of the dominant kernel: from the committed ncu capture of a smaller case, scaled to this launch
     try:
+        if args.big:
+            raise KeyError("no capture at this size")
         with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
             tr = json.load(f)[args.workload]
         if args.workload == "flat":
@@ -424,9 +466,15 @@ def main():
     ap.add_argument("--workload", default="ivfpq", choices=["ivfpq", "flat", "hnsw"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--nq", type=int, default=NQ, help="queries per step (smaller = a profiling-sized case)")
-    ap.add_argument("--n", type=int, default=N_BASE, help="base rows (smaller = a profiling-sized case)")
+    ap.add_argument("--n", type=int, default=None, help="base rows (smaller = a profiling-sized case)")
+    ap.add_argument("--big", action="store_true", help="BASELINE configs[4]: 50M rows, 4096 clusters, sharded")
     args = ap.parse_args()
-    NQ, N_BASE = args.nq, args.n
+    global CLUSTERS
+    NQ = args.nq
+    if args.big:
+        N_BASE, CLUSTERS = 50_000_000, 4096
+    if args.n:
+        N_BASE = args.n
     if args.impl == "reference":
         run_reference(args)
     else:

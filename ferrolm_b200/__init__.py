@@ -4,8 +4,8 @@ The package is a thin host-side mirror of the reference's Rust interface over th
 `include/ferrovec.h`; all search code is hand-written CUDA in `csrc/`.
 """
 from .vector import (NEIGHBOR, Context, FerrovecError, FlatIndex, Hnsw, HnswParams, IvfPq, IvfPqParams, Metric,
-                     datagen, kmeans_assign, kmeans_train, merge_topk_static, neighbors_from_tensor, normalize, padded,
+                     datagen, datagen_dev, kmeans_assign, kmeans_train, merge_topk_static, neighbors_from_tensor, normalize, padded,
                      recall)
 
 __all__ = ["NEIGHBOR", "Context", "FerrovecError", "FlatIndex", "Hnsw", "HnswParams", "IvfPq", "IvfPqParams", "Metric",
-           "datagen", "kmeans_assign", "kmeans_train", "merge_topk_static", "neighbors_from_tensor", "normalize", "padded", "recall"]
+           "datagen", "datagen_dev", "kmeans_assign", "kmeans_train", "merge_topk_static", "neighbors_from_tensor", "normalize", "padded", "recall"]

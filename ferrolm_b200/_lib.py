@@ -83,6 +83,7 @@ SIGNATURES = {
     "fv_ivfpq_train": (_i, [_vp, _i, _u32, _vp, _sz, C.POINTER(fv_ivfpq_params), _pp]),
     "fv_ivfpq_free": (None, [_vp]),
     "fv_ivfpq_add": (_i, [_vp, _vp, _sz]),
+    "fv_ivfpq_add_dev": (_i, [_vp, _vp, _sz]),
     "fv_ivfpq_len": (_sz, [_vp]),
     "fv_ivfpq_bytes_per_vector": (_sz, [_vp]),
     "fv_ivfpq_search": (_i, [_vp, _vp, _sz, _sz, _sz, _vp, _vp]),
@@ -115,6 +116,7 @@ SIGNATURES = {
     "fv_read_fvecs": (_i, [C.c_char_p, _sz, _pp, C.POINTER(_sz), C.POINTER(_sz)]),
     "fv_read_ivecs": (_i, [C.c_char_p, _sz, _pp, C.POINTER(_sz), C.POINTER(_sz)]),
     "fv_free": (None, [_vp]),
+    "fv_datagen_dev": (_i, [_vp, _u64, _sz, _sz, _sz, _sz, _vp]),
 }
 
 _lib = None

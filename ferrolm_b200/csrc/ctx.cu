@@ -321,3 +321,53 @@ int fv_read_ivecs(const char* path, size_t limit, uint32_t** out, size_t* n, siz
 }
 void fv_free(void* p) { std::free(p); }
 }
+
+// ---- the same generator on the device (kind 0 only), for bases too large to generate on the host cores.
+// Same streams and formulas as fv_datagen; the device's double-precision log/cos may differ from the host
+// library's in the last bit, so a value that lands within rounding of x.5 can round the other way: use one
+// generator or the other for a given experiment, not both.
+namespace fv {
+__global__ void datagen_kernel(uint64_t seed, size_t first_row, size_t n, int dim, size_t clusters,
+                               const float* __restrict__ centres, float* __restrict__ out) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+    const size_t row = first_row + i;
+    uint64_t s = ((seed ^ ((row + 1) * 0xD1B54A32D192ED03ull)) * 0x9E3779B97F4A7C15ull) | 1ull;
+    auto next = [&]() {
+      s ^= s >> 12;
+      s ^= s << 25;
+      s ^= s >> 27;
+      return s * 0x2545F4914F6CDD1Dull;
+    };
+    next();
+    const size_t c = size_t(next() % clusters);
+    for (int d = 0; d < dim; d++) {
+      const double u = 1.0 - double(next() >> 11) / 9007199254740992.0;
+      const double v = double(next() >> 11) / 9007199254740992.0;
+      const double nrm = sqrt(-2.0 * log(u)) * cos(6.283185307179586476925286766559 * v);
+      float x = centres[c * dim + d] + float(nrm) * 30.0f;
+      x = nearbyintf(x);
+      out[i * size_t(dim) + d] = x < 0.f ? 0.f : (x > 255.f ? 255.f : x);
+    }
+  }
+}
+}  // namespace fv
+
+extern "C" int fv_datagen_dev(fv_ctx* ctx, uint64_t seed, size_t first_row, size_t n, size_t dim, size_t clusters,
+                              float* d_out) {
+  if (!ctx || !d_out || dim == 0 || clusters == 0) return fv::fail(FV_ERR_ARG, "fv_datagen_dev: bad argument");
+  if (n == 0) return FV_OK;
+  std::vector<float> centres(clusters * dim);
+  {
+    XorShift c(seed * 1000003ull + 17);
+    for (auto& v : centres) v = float(c.uniform() * 255.0);
+  }
+  fv::DeviceGuard g(ctx->device);
+  DevBuf d_cen;
+  FV_TRY(d_cen.reserve(centres.size() * sizeof(float)));
+  FV_CUDA(cudaMemcpyAsync(d_cen.p, centres.data(), centres.size() * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  fv::datagen_kernel<<<ctx->sm_count * 8, 128, 0, ctx->stream>>>(seed, first_row, n, int(dim), clusters, d_cen.as<float>(),
+                                                                d_out);
+  FV_CUDA(cudaGetLastError());
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  return FV_OK;
+}

@@ -214,10 +214,6 @@ int exact_scan(fv_ctx* ctx, int metric, const float* d_rows, size_t n, int pd, c
 
 // ------------------------------------------------------------------------------------------------
 // FlatIndex
-namespace fv {
-struct TcSide;
-}
-
 struct fv_flat {
   fv_ctx* ctx;
   int metric;
@@ -229,14 +225,6 @@ struct fv_flat {
   fv::TcSide* tc = nullptr;  // tensor-core front end state (gemm_topk.cu)
 };
 
-namespace fv {
-// tensor-core front end (gemm_topk.cu)
-void tc_free(TcSide* tc);
-int tc_append(fv_ctx* ctx, TcSide** tc, int metric, const float* d_rows_new, size_t n_old, size_t n_new, int pd);
-int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n, int pd, const float* d_queries,
-              size_t nq, int k, uint32_t id_base, u64* d_out_keys);
-bool tc_usable(const TcSide* tc, size_t n, size_t nq, int k);
-}  // namespace fv
 
 extern "C" {
 
@@ -329,7 +317,7 @@ int fv_flat_search_batch_dev(fv_flat* ix, const float* d_queries, size_t nq, siz
   if (want_tc) {
     if (!fv::tc_usable(ix->tc, ix->n, nq, L))
       return fv::fail(FV_ERR_UNSUPPORTED, "tensor-core search needs k <= 32, at least 4096 rows and a padded dimension of at most 384");
-    FV_TRY(fv::tc_search(ctx, ix->tc, ix->metric, ix->data.as<float>(), ix->n, pd, q, nq, L, ix->id_base, keys));
+    FV_TRY(fv::tc_search(ctx, ix->tc, ix->metric, ix->data.as<float>(), ix->n, pd, q, nq, L, ix->id_base, keys, true));
   } else {
     FV_TRY(fv::exact_scan(ctx, ix->metric, ix->data.as<float>(), ix->n, pd, q, size_t(pd), nullptr, nq, L, true,
                           ix->id_base, keys, 2));

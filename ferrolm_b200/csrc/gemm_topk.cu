@@ -924,7 +924,7 @@ static constexpr int CAND_CAP = 256;  // candidate slots per epilogue thread and
 // scratch slots: 2 scan partials (fallback), 3 A operand, 5 query norms + candidate counters, 6 sample lists,
 // 7 retry ids, 8 fallback keys, 9 candidate buffers
 int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n, int pd, const float* d_queries,
-              size_t nq, int k, uint32_t id_base, u64* d_out_keys) {
+              size_t nq, int k, uint32_t id_base, u64* d_out_keys, bool mark_stages) {
   const int Kp = tc->Kp;
   Tiling ts{}, tm{};
   FV_TRY(make_tiling(ctx, Kp, nq, tc->ns, SCRATCH_BYTES, &ts));
@@ -955,7 +955,7 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   FV_CUDA(cudaMemsetAsync(retry_count, 0, 8, ctx->stream));
   if (nq_pad > nq) FV_CUDA(cudaMemsetAsync(dA + nq * size_t(Kp), 0, (nq_pad - nq) * size_t(Kp) * 2, ctx->stream));
   FV_TRY(convert(ctx, tc->bf16, d_queries, nq, pd, Kp, dA, qn2, metric == FV_L2, qst));
-  stage_mark(ctx);
+  if (mark_stages) stage_mark(ctx);
 
   // sample pass: per query the SAMPLE_R best scores over 1 row in SAMPLE_EVERY
   GemmParams gs{};
@@ -975,7 +975,7 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   gs.cand = ctx->scratch[6].as<u64>();
   gs.err = err;
   FV_TRY((launch_gemm<SAMPLE_R + 1, false>(ctx, ts, tmA, tmS, gs)));
-  stage_mark(ctx);
+  if (mark_stages) stage_mark(ctx);
 
   // main pass: every row scoring below the query's sampled bound becomes a candidate
   GemmParams gp = gs;
@@ -997,7 +997,7 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   gp.ccnt = ccnt;
   gp.ccap = CAND_CAP;
   FV_TRY((launch_gemm<2, true>(ctx, tm, tmA, tmB, gp)));
-  stage_mark(ctx);
+  if (mark_stages) stage_mark(ctx);
 
   RerankParams rp{};
   rp.tau_lists = gp.tau_lists;
@@ -1033,7 +1033,7 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   rerank_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, rsmem, ctx->stream>>>(rp);
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
-  stage_mark(ctx);
+  if (mark_stages) stage_mark(ctx);
 
   unsigned int h_words[2] = {0, 0};  // retry count, error word
   FV_CUDA(cudaMemcpyAsync(h_words, retry_count, sizeof(h_words), cudaMemcpyDeviceToHost, ctx->stream));
@@ -1049,7 +1049,7 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
     ctx->stats.launches++;
     FV_CUDA(cudaGetLastError());
   }
-  stage_mark(ctx);
+  if (mark_stages) stage_mark(ctx);
   return FV_OK;
 }
 

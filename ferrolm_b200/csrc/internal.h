@@ -124,6 +124,15 @@ int exact_scan(fv_ctx* ctx, int metric, const float* d_rows, size_t n, int pd, c
 int keys_to_neighbors(fv_ctx* ctx, const u64* d_keys, size_t nq, int L, int k, fv_neighbor* d_out,
                       uint32_t* d_counts, const uint32_t* d_query_ids = nullptr);
 
+// ---- tensor-core front end of exact search (gemm_topk.cu): 16-bit operand copy of a row set, searched with the
+// sampled-bound GEMM, exact re-rank and certificate; result keys are those of the full-precision chain.
+struct TcSide;
+void tc_free(TcSide* tc);
+int tc_append(fv_ctx* ctx, TcSide** tc, int metric, const float* d_rows_new, size_t n_old, size_t n_new, int pd);
+int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n, int pd, const float* d_queries,
+              size_t nq, int k, uint32_t id_base, u64* d_out_keys, bool mark_stages);
+bool tc_usable(const TcSide* tc, size_t n, size_t nq, int k);
+
 // pads rows of `dim` floats to `pd` on the device (host or device source)
 int upload_padded(fv_ctx* ctx, const float* src, bool src_is_device, size_t n, size_t dim, size_t pd, float* d_dst);
 

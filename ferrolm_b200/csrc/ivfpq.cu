@@ -508,6 +508,7 @@ __global__ void __launch_bounds__(256) ivfpq_scan_kernel(ScanArgs a) {
 struct fv_ivfpq {
   fv_ctx* ctx = nullptr;
   ~fv_ivfpq() {
+    fv::tc_free(ctc);
     centroids.release(); codebooks.release(); pre.release(); list_off.release(); owned_ids.release();
     codes.release(); ids.release(); vectors.release();
     if (ctx) fv::ctx_release(ctx);
@@ -521,6 +522,7 @@ struct fv_ivfpq {
   size_t seen = 0;    // rows passed to add (equals count unless the index is list-sharded)
   int shard_rank = 0, shard_world = 1;
   DevBuf owned_ids;   // list-sharded: ids of the kept vectors, ascending
+  fv::TcSide* ctc = nullptr;  // 16-bit copy of the centroids for the tensor-core coarse search
   std::vector<float> h_centroids, h_codebooks;
   std::vector<uint32_t> h_off;  // nlist + 1
   DevBuf centroids, codebooks, pre, list_off, codes, ids, vectors;
@@ -549,6 +551,10 @@ static int upload_quantizers(fv_ivfpq* ix) {
     FV_CUDA(cudaGetLastError());
     ix->has_pre = true;
   }
+  // coarse search as a small GEMM when there are enough cells (ivfpq.rs:211-220 at batch scale)
+  tc_free(ix->ctc);
+  ix->ctc = nullptr;
+  if (ix->nlist >= 4096) FV_TRY(tc_append(ctx, &ix->ctc, ix->metric, ix->centroids.as<float>(), 0, ix->nlist, int(ix->pd)));
   FV_CUDA(cudaStreamSynchronize(ctx->stream));
   return FV_OK;
 }
@@ -705,7 +711,7 @@ int fv_ivfpq_set_shard(fv_ivfpq* ix, int rank, int world) {
 }
 
 // ivfpq.rs:161-192
-int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n_total) {
+static int ivfpq_add_impl(fv_ivfpq* ix, const float* vectors, size_t n_total, bool src_is_device) {
   if (!ix || (!vectors && n_total)) return fv::fail(FV_ERR_ARG, "fv_ivfpq_add: null argument");
   fv_ctx* ctx = ix->ctx;
   fv::DeviceGuard g(ctx->device);
@@ -718,7 +724,7 @@ int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n_total) {
     DevBuf d_x_tmp, d_assign, d_codes, d_dest, d_sel, d_xs, d_assign_s, d_ids_s;
     FV_TRY(d_x_tmp.reserve(n * pd * sizeof(float)));
     float* d_x = d_x_tmp.as<float>();
-    FV_TRY(fv::upload_padded(ctx, src, false, n, ix->dim, pd, d_x));
+    FV_TRY(fv::upload_padded(ctx, src, src_is_device, n, ix->dim, pd, d_x));
     FV_TRY(d_assign.reserve(n * sizeof(uint32_t)));
     // ivfpq.rs:194-204: L2 -> nearest centroid; inner product -> the best cell, every cell pushed
     FV_TRY(fv::assign_dev(ctx, ix->metric, ix->metric == FV_L2, d_x, n, ix->centroids.as<float>(), ix->nlist, pd,
@@ -812,6 +818,9 @@ int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n_total) {
   return FV_OK;
 }
 
+int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n) { return ivfpq_add_impl(ix, vectors, n, false); }
+int fv_ivfpq_add_dev(fv_ivfpq* ix, const float* d_vectors, size_t n) { return ivfpq_add_impl(ix, d_vectors, n, true); }
+
 // scratch slots: 0 padded queries, 1 final keys, 2 scan partials, 4 cells
 static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,
                              bool candidates, fv_neighbor* d_out, uint32_t* d_counts, fv_neighbor* d_adc, float* d_exact) {
@@ -838,8 +847,11 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   FV_TRY(ctx->scratch[4].reserve(nq * size_t(np) * sizeof(u64)));
   u64* cells = ctx->scratch[4].as<u64>();
   // ivfpq.rs:211-220: every cell is pushed, no pre-filter
-  FV_TRY(fv::exact_scan(ctx, ix->metric, ix->centroids.as<float>(), ix->nlist, pd, q, size_t(pd), nullptr, nq, np, false,
-                        0, cells, 2));
+  if (nq >= 256 && fv::tc_usable(ix->ctc, ix->nlist, nq, np))
+    FV_TRY(fv::tc_search(ctx, ix->ctc, ix->metric, ix->centroids.as<float>(), ix->nlist, pd, q, nq, np, 0, cells, false));
+  else
+    FV_TRY(fv::exact_scan(ctx, ix->metric, ix->centroids.as<float>(), ix->nlist, pd, q, size_t(pd), nullptr, nq, np,
+                          false, 0, cells, 2));
   fv::stage_mark(ctx);
   FV_TRY(ctx->scratch[1].reserve(nq * kout * sizeof(u64)));
   unsigned long long* d_rows = reinterpret_cast<unsigned long long*>(ctx->d_flags + 16);

@@ -58,6 +58,16 @@ def datagen(kind: int, seed: int, n: int, dim: int, clusters: int, first_row: in
     return out
 
 
+def datagen_dev(ctx, seed: int, n: int, dim: int, clusters: int, first_row: int = 0):
+    """datagen kind 0 computed on the GPU into a new device tensor (for bases too large for the host cores)."""
+    import torch
+
+    out = torch.empty((n, dim), dtype=torch.float32, device=f"cuda:{ctx.device}")
+    torch.cuda.current_stream(out.device).synchronize()
+    check(lib().fv_datagen_dev(ctx._h, seed, first_row, n, dim, clusters, out.data_ptr()))
+    return out
+
+
 def _is_cuda_tensor(x) -> bool:
     return hasattr(x, "is_cuda") and bool(x.is_cuda)
 
@@ -267,6 +277,13 @@ class IvfPq:
         return IvfPq(ctx, h, dim)
 
     def add(self, vectors):
+        if _is_cuda_tensor(vectors):
+            import torch
+
+            v = vectors.contiguous().view(-1, self.dim)
+            torch.cuda.current_stream(v.device).synchronize()
+            check(lib().fv_ivfpq_add_dev(self._h, v.data_ptr(), v.shape[0]))
+            return
         v = _host_f32(vectors).reshape(-1, self.dim)
         check(lib().fv_ivfpq_add(self._h, v.ctypes.data_as(C.c_void_p), v.shape[0]))
 
@@ -409,5 +426,5 @@ def kmeans_assign(ctx: Context, data, centroids) -> np.ndarray:
 
 
 __all__ = ["Metric", "Context", "FlatIndex", "IvfPq", "IvfPqParams", "Hnsw", "HnswParams", "NEIGHBOR", "padded",
-           "normalize", "recall", "datagen", "kmeans_train", "kmeans_assign", "neighbors_from_tensor",
+           "normalize", "recall", "datagen", "datagen_dev", "kmeans_train", "kmeans_assign", "neighbors_from_tensor",
            "merge_topk_static", "FerrovecError"]

@@ -117,6 +117,7 @@ int fv_ivfpq_train(fv_ctx* ctx, int metric, uint32_t dim, const float* sample, s
                    const fv_ivfpq_params* p, fv_ivfpq** out);                          /* train :56 */
 void fv_ivfpq_free(fv_ivfpq* ix);
 int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n);                       /* add   :161 */
+int fv_ivfpq_add_dev(fv_ivfpq* ix, const float* d_vectors, size_t n);
 size_t fv_ivfpq_len(const fv_ivfpq* ix);                                              /* len   :128 */
 size_t fv_ivfpq_bytes_per_vector(const fv_ivfpq* ix);                                 /* bytes_per_vector :137 */
 int fv_ivfpq_search(fv_ivfpq* ix, const float* query, size_t k, size_t nprobe, size_t refine,
@@ -206,6 +207,10 @@ int fv_merge_topk_static_dev(int device, void* stream, const fv_neighbor* d_part
  * Row i depends only on (seed, i), so any row range can be generated independently. */
 int fv_datagen(int kind, uint64_t seed, size_t first_row, size_t n, size_t dim, size_t clusters, int threads,
                float* out);
+
+/* kind 0 of fv_datagen computed on the GPU into device memory (same streams and formulas; device libm, so a
+ * value within rounding of x.5 may round differently: do not mix the two generators within one experiment). */
+int fv_datagen_dev(fv_ctx* ctx, uint64_t seed, size_t first_row, size_t n, size_t dim, size_t clusters, float* d_out);
 
 #ifdef __cplusplus
 }

@@ -250,7 +250,7 @@ def test_ivfpq_without_precomputed_tables(fv, oracle, ctx):
     assert nlist * m * 256 > 64 << 20
     assert 16384 * 16 * 256 == 64 << 20  # the 50M-vector configuration still has tables
     base = oracle.testdata(6000, dim, 15)
-    queries = oracle.testdata(32, dim, 16)
+    queries = oracle.testdata(320, dim, 16)  # >= 256 queries and >= 4096 cells: the coarse search takes the GEMM path
     g = fv.IvfPq.train(ctx, L2, dim, base[:4200], fv.IvfPqParams(nlist, m, 2, True, 1))
     g.add(base)
     o = oracle.IvfPq.train(L2, dim, base[:4200], nlist, m, 2, True, 1)
