@@ -98,6 +98,8 @@ __global__ void __launch_bounds__(256)
           float d = INFINITY;
           if (i < cnt) {
             x = g.upper_flat[p + 1 + i];
+            const char* rowp = reinterpret_cast<const char*>(g.data + size_t(x) * g.pd);
+            for (int b = 0; b < g.pd * 4; b += 128) asm volatile("prefetch.global.L1 [%0];" ::"l"(rowp + b));
             d = exact_distance<IS_L2>(sq, g.data + size_t(x) * g.pd, g.pd);
           }
           n_dist += __popc(__ballot_sync(FV_FULL, i < cnt));
@@ -158,7 +160,13 @@ __global__ void __launch_bounds__(256)
         const int nfresh = __popc(__ballot_sync(FV_FULL, fresh));
         visited += nfresh;
         n_dist += nfresh;
-        if (fresh) key = beam_key(exact_distance<IS_L2>(sq, g.data + size_t(x) * g.pd, g.pd), x);
+        if (fresh) {
+          // all lines of the row are requested before the dependent FMA chains start, so the gather costs one
+          // memory round trip instead of one per unrolled group of loads
+          const char* rowp = reinterpret_cast<const char*>(g.data + size_t(x) * g.pd);
+          for (int b = 0; b < g.pd * 4; b += 128) asm volatile("prefetch.global.L1 [%0];" ::"l"(rowp + b));
+          key = beam_key(exact_distance<IS_L2>(sq, g.data + size_t(x) * g.pd, g.pd), x);
+        }
         // offer in stored order: admitted while the list is not full, or on a strictly smaller distance
         u64 bound = best[ef - 1];
         unsigned pending = __ballot_sync(FV_FULL, fresh);
