@@ -71,7 +71,7 @@ __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
 
 // the one dynamic shared-memory array of every kernel
 __device__ __forceinline__ unsigned char* dyn_smem() {
-  extern __shared__ __align__(16) unsigned char fv_dyn_smem[];
+  extern __shared__ __align__(1024) unsigned char fv_dyn_smem[];
   return fv_dyn_smem;
 }
 

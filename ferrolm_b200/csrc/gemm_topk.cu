@@ -184,6 +184,8 @@ struct GemmParams {
   int segmax;      // candidate segments per CTA
   int nstage;
   int scratch_bytes;  // SCRATCH_BYTES in list mode, 0 in threshold mode
+  int norm_ring;      // norm tiles staged in shared memory (0: the epilogue reads the norms from global memory)
+  int dbg_skip;       // EXPERIMENT: 1 = epilogue does no work, 2 = no norm reads/FMAs
   float scale;     // -2 (L2) or -1 (inner product)
   uint32_t idesc;
   const float* bnorm;  // padded to a multiple of 256 with +inf
@@ -258,7 +260,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   unsigned char* sB = sA + size_t(MH) * p.KB * A_BLOCK_BYTES;          // [nstage] stages of 32 KB
   unsigned char* scratch = sB + size_t(p.nstage) * B_STAGE_BYTES;   // 8 epilogue warps x 4 KB
   float* snorm = reinterpret_cast<float*>(scratch + p.scratch_bytes);  // [NORM_RING][256]
-  Barriers* bars = reinterpret_cast<Barriers*>(scratch + p.scratch_bytes + NORM_RING * TILE_N * 4);
+  Barriers* bars = reinterpret_cast<Barriers*>(scratch + p.scratch_bytes + p.norm_ring * TILE_N * 4);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -318,7 +320,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           // refilled after the MMAs of the unit nstage / KB back, which waited for the epilogues before it.
           mbar_expect_tx(&bars->full[s], uint32_t(B_STAGE_BYTES + (kb == 0 ? TILE_N * 4 : 0)));
           if (kb == 0)
-            bulk_load_1d(snorm + (tile_idx % NORM_RING) * TILE_N, p.bnorm + size_t(nt) * TILE_N, TILE_N * 4,
+            bulk_load_1d(snorm + (tile_idx % p.norm_ring) * TILE_N, p.bnorm + size_t(nt) * TILE_N, TILE_N * 4,
                          &bars->full[s]);
           tma_load_2d(sB + size_t(s) * B_STAGE_BYTES, &tmB, &bars->full[s], kb * KBLK, nt * TILE_N);
         }
@@ -434,7 +436,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       // scores are parked in this warp's shared-memory scratch so that they can be indexed, and each row
       // inserts its passing columns, in ascending id order, into its sorted register list.
       auto chunk = [&](uint32_t* r, int c) {
-        const float4* nrm = reinterpret_cast<const float4*>(snorm + (tile_idx % NORM_RING) * TILE_N + col0 + c);
+        const float4* nrm = reinterpret_cast<const float4*>(snorm + (tile_idx % p.norm_ring) * TILE_N + col0 + c);
         float v[32];
         float g[4] = {INFINITY, INFINITY, INFINITY, INFINITY};  // minima of the four groups of 8 columns
 #pragma unroll
@@ -501,7 +503,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       };
       // four epilogue warps share each scheduler, so the tensor-memory load latency is hidden across warps
 #pragma unroll 1
-      for (int c = 0; c < ncol; c += 32) {
+      for (int c = 0; c < (p.dbg_skip == 1 ? 0 : ncol); c += 32) {
         tc_ld32_issue(t_addr + uint32_t(c), rbuf0);
         tc_ld_wait(rbuf0);
         chunk(rbuf0, c);
@@ -886,7 +888,7 @@ struct Tiling {
   size_t smem;
 };
 
-static int make_tiling(fv_ctx* ctx, int Kp, size_t nq, size_t rows, int scratch_bytes, Tiling* t) {
+static int make_tiling(fv_ctx* ctx, int Kp, size_t nq, size_t rows, int scratch_bytes, int norm_ring, Tiling* t) {
   t->KB = Kp / KBLK;
   t->MH = t->KB <= 2 ? 2 : 1;
   const int rows_per_tile = 128 * t->MH;
@@ -897,12 +899,11 @@ static int make_tiling(fv_ctx* ctx, int Kp, size_t nq, size_t rows, int scratch_
   t->upc = (t->U + t->grid - 1) / t->grid;
   t->segmax = int((t->upc + t->NT - 1) / t->NT) + 1;
   const size_t a_bytes = size_t(t->MH) * t->KB * A_BLOCK_BYTES;
-  const size_t fixed = 2048 + a_bytes + scratch_bytes + NORM_RING * TILE_N * 4;
+  const size_t fixed = 512 + a_bytes + scratch_bytes + norm_ring * TILE_N * 4;
   if (ctx->smem_optin < fixed + 2 * B_STAGE_BYTES)
     return fail(FV_ERR_UNSUPPORTED, "not enough shared memory for the tensor-core tiling");
   t->nstage = std::min(int((ctx->smem_optin - fixed) / B_STAGE_BYTES), 6);
-  t->smem = 1024 + a_bytes + size_t(t->nstage) * B_STAGE_BYTES + scratch_bytes + NORM_RING * TILE_N * 4 +
-            sizeof(Barriers) + 64;
+  t->smem = a_bytes + size_t(t->nstage) * B_STAGE_BYTES + scratch_bytes + norm_ring * TILE_N * 4 + sizeof(Barriers) + 64;
   return FV_OK;
 }
 
@@ -927,8 +928,9 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
               size_t nq, int k, uint32_t id_base, u64* d_out_keys, bool mark_stages) {
   const int Kp = tc->Kp;
   Tiling ts{}, tm{};
-  FV_TRY(make_tiling(ctx, Kp, nq, tc->ns, SCRATCH_BYTES, &ts));
-  FV_TRY(make_tiling(ctx, Kp, nq, n, 0, &tm));
+  const int main_ring = NORM_RING;
+  FV_TRY(make_tiling(ctx, Kp, nq, tc->ns, SCRATCH_BYTES, NORM_RING, &ts));
+  FV_TRY(make_tiling(ctx, Kp, nq, n, 0, main_ring, &tm));
   const int rows_per_tile = 128 * tm.MH;
 
   // queries -> 16-bit operand rows (padded to whole tiles with zeros), norms, statistics
@@ -969,6 +971,7 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   gs.segmax = ts.segmax;
   gs.nstage = ts.nstage;
   gs.scratch_bytes = SCRATCH_BYTES;
+  gs.norm_ring = NORM_RING;
   gs.scale = metric == FV_L2 ? -2.f : -1.f;
   gs.idesc = make_idesc(128, TILE_N, tc->bf16);
   gs.bnorm = tc->samp_norm2.as<float>();
@@ -987,6 +990,8 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   gp.segmax = tm.segmax;
   gp.nstage = tm.nstage;
   gp.scratch_bytes = 0;
+  gp.norm_ring = main_ring;
+  gp.dbg_skip = getenv("FV_DBG_SKIP") ? atoi(getenv("FV_DBG_SKIP")) : 0;
   gp.bnorm = tc->norm2.as<float>();
   gp.cand = nullptr;
   gp.tau_lists = gs.cand;
