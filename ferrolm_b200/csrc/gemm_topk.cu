@@ -74,12 +74,16 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the limit ran out or another thread already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// Every failed probe reads shared memory, and the tensor cores fetch their operands through the same port:
+// sixteen warps probing back to back slow the MMAs measurably, so a waiting thread sleeps between probes.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned sleep_ns = 64) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 64; ++i) {
+      if (sleep_ns) __nanosleep(sleep_ns);
       if (mbar_try(bar, parity)) return true;
+    }
     if (*abort_flag) return false;
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
       *abort_flag = 1;
@@ -173,6 +177,35 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16) {
          (uint32_t(m >> 4) << 24);
 }
 
+// Position of a CTA in its run of units, advanced without divisions (each role loop is a single thread on the
+// critical path of the tensor pipe; a 64-bit division per unit or per k block is a measurable bubble there).
+struct UnitCursor {
+  int mt, nt, NT, ring, nring;
+  __device__ UnitCursor(long long u, int NT_, int nring_) : NT(NT_), ring(0), nring(nring_) {
+    mt = int(u / NT_);
+    nt = int(u - (long long)mt * NT_);
+  }
+  __device__ __forceinline__ void next() {
+    if (++nt == NT) {
+      nt = 0;
+      ++mt;
+    }
+    if (++ring == nring) ring = 0;
+  }
+  __device__ __forceinline__ bool ends_row() const { return nt + 1 == NT; }  // the next unit is another query tile
+};
+struct StageCursor {
+  int s, n;
+  uint32_t phase;
+  __device__ StageCursor(int n_) : s(0), n(n_), phase(0) {}
+  __device__ __forceinline__ void next() {
+    if (++s == n) {
+      s = 0;
+      phase ^= 1;
+    }
+  }
+};
+
 // ------------------------------------------------------------------------------------------------
 struct GemmParams {
   int n, nq;
@@ -185,7 +218,6 @@ struct GemmParams {
   int nstage;
   int scratch_bytes;  // SCRATCH_BYTES in list mode, 0 in threshold mode
   int norm_ring;      // norm tiles staged in shared memory (0: the epilogue reads the norms from global memory)
-  int dbg_skip;       // EXPERIMENT: 1 = epilogue does no work, 2 = no norm reads/FMAs
   float scale;     // -2 (L2) or -1 (inner product)
   uint32_t idesc;
   const float* bnorm;  // padded to a multiple of 256 with +inf
@@ -295,11 +327,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      long long it = 0, tile_idx = 0;
       int seg = 0, cur_mt = -1;
       bool ok = true;
-      for (long long u = u0; u < u1 && ok; ++u, ++tile_idx) {
-        const int mt = int(u / p.NT), nt = int(u % p.NT);
+      UnitCursor uc(u0, p.NT, p.norm_ring);
+      StageCursor st(p.nstage);
+      for (long long u = u0; u < u1 && ok; ++u, uc.next()) {
+        const int mt = uc.mt, nt = uc.nt;
         if (mt != cur_mt) {
           ok = mbar_wait(&bars->a_empty, (seg & 1) ^ 1, abort_flag);
           if (!ok) break;
@@ -311,16 +344,16 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           cur_mt = mt;
           seg++;
         }
-        for (int kb = 0; kb < p.KB; ++kb, ++it) {
-          const int s = int(it % p.nstage);
-          ok = mbar_wait(&bars->empty[s], (uint32_t(it / p.nstage) & 1) ^ 1, abort_flag);
+        for (int kb = 0; kb < p.KB; ++kb, st.next()) {
+          const int s = st.s;
+          ok = mbar_wait(&bars->empty[s], st.phase ^ 1, abort_flag);
           if (!ok) break;
           // The unit's row norms ride on the barrier of its first k block.  A ring slot is reused NORM_RING
           // units later; by then the epilogue of that unit is long done, because this stage could only be
           // refilled after the MMAs of the unit nstage / KB back, which waited for the epilogues before it.
           mbar_expect_tx(&bars->full[s], uint32_t(B_STAGE_BYTES + (kb == 0 ? TILE_N * 4 : 0)));
           if (kb == 0)
-            bulk_load_1d(snorm + (tile_idx % p.norm_ring) * TILE_N, p.bnorm + size_t(nt) * TILE_N, TILE_N * 4,
+            bulk_load_1d(snorm + uc.ring * TILE_N, p.bnorm + size_t(nt) * TILE_N, TILE_N * 4,
                          &bars->full[s]);
           tma_load_2d(sB + size_t(s) * B_STAGE_BYTES, &tmB, &bars->full[s], kb * KBLK, nt * TILE_N);
         }
@@ -336,12 +369,13 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      long long it = 0, job = 0;
-      int seg = 0, cur_mt = -1;
+      int job = 0, seg = 0, cur_mt = -1;
       bool ok = true;
+      UnitCursor uc(u0, p.NT, p.norm_ring);
+      StageCursor st(p.nstage);
       const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB);
-      for (long long u = u0; u < u1 && ok; ++u) {
-        const int mt = int(u / p.NT);
+      for (long long u = u0; u < u1 && ok; ++u, uc.next()) {
+        const int mt = uc.mt;
         if (mt != cur_mt) {
           ok = mbar_wait(&bars->a_full, seg & 1, abort_flag);
           if (!ok) break;
@@ -350,16 +384,16 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           seg++;
         }
         for (int mh = 0; mh < MH && ok; ++mh, ++job) {
-          const int slot = int(job & 1);
+          const int slot = job & 1;
           ok = mbar_wait(&bars->tempty[slot], (uint32_t(job >> 1) & 1) ^ 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + uint32_t(slot * TILE_N);
-          for (int kb = 0; kb < p.KB; ++kb) {
-            const long long itk = it + kb;
-            const int s = int(itk % p.nstage);
+          StageCursor sk = st;  // both halves walk the same stages of this unit
+          for (int kb = 0; kb < p.KB; ++kb, sk.next()) {
+            const int s = sk.s;
             if (mh == 0) {
-              ok = mbar_wait(&bars->full[s], uint32_t(itk / p.nstage) & 1, abort_flag);
+              ok = mbar_wait(&bars->full[s], sk.phase, abort_flag);
               if (!ok) break;
               tc_fence_after();
             }
@@ -374,8 +408,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           if (!ok) break;
           tc_commit(&bars->tfull[slot]);
         }
-        it += p.KB;
-        const bool last_of_segment = (u + 1 == u1) || int((u + 1) / p.NT) != mt;
+        for (int kb = 0; kb < p.KB; ++kb) st.next();
+        const bool last_of_segment = (u + 1 == u1) || uc.ends_row();
         if (ok && last_of_segment) tc_commit(&bars->a_empty);
       }
     }
@@ -400,13 +434,14 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       sc[j] = INFINITY;
       idv[j] = 0xFFFFFFFFu;
     }
-    long long tile_idx = 0;
+    int tile_idx = 0;
     int cur_mt = -1, seg_local = -1;
     bool ok = true;
     const int ncol = MH == 2 ? TILE_N / 2 : TILE_N / 4;
     const int col0 = MH == 2 ? (sub >> 1) * (TILE_N / 2) : sub * (TILE_N / 4);
-    for (long long u = u0; u < u1 && ok; ++u, ++tile_idx) {
-      const int mt = int(u / p.NT), nt = int(u % p.NT);
+    UnitCursor uc(u0, p.NT, p.norm_ring);
+    for (long long u = u0; u < u1 && ok; ++u, ++tile_idx, uc.next()) {
+      const int mt = uc.mt, nt = uc.nt;
       if (mt != cur_mt) {
         cur_mt = mt;
         seg_local++;
@@ -423,8 +458,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           ncand = 0;
         }
       }
-      const long long job = MH == 2 ? tile_idx * 2 + grp : tile_idx;
-      const int slot = int(job & 1);
+      const int job = MH == 2 ? tile_idx * 2 + grp : tile_idx;
+      const int slot = job & 1;
       ok = mbar_wait(&bars->tfull[slot], uint32_t(job >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
@@ -436,7 +471,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       // scores are parked in this warp's shared-memory scratch so that they can be indexed, and each row
       // inserts its passing columns, in ascending id order, into its sorted register list.
       auto chunk = [&](uint32_t* r, int c) {
-        const float4* nrm = reinterpret_cast<const float4*>(snorm + (tile_idx % p.norm_ring) * TILE_N + col0 + c);
+        const float4* nrm = reinterpret_cast<const float4*>(snorm + uc.ring * TILE_N + col0 + c);
         float v[32];
         float g[4] = {INFINITY, INFINITY, INFINITY, INFINITY};  // minima of the four groups of 8 columns
 #pragma unroll
@@ -503,7 +538,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       };
       // four epilogue warps share each scheduler, so the tensor-memory load latency is hidden across warps
 #pragma unroll 1
-      for (int c = 0; c < (p.dbg_skip == 1 ? 0 : ncol); c += 32) {
+      for (int c = 0; c < ncol; c += 32) {
         tc_ld32_issue(t_addr + uint32_t(c), rbuf0);
         tc_ld_wait(rbuf0);
         chunk(rbuf0, c);
@@ -511,7 +546,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tempty[slot]);
-      const bool last_of_segment = (u + 1 == u1) || int((u + 1) / p.NT) != mt;
+      const bool last_of_segment = (u + 1 == u1) || uc.ends_row();
       if (THRESH && last_of_segment) p.ccnt[cslot] = ncand;
       if (!THRESH && last_of_segment) {
         u64* dst = p.cand + ((size_t(blockIdx.x) * p.segmax + seg_local) * LISTS + e) * KP;
@@ -991,7 +1026,6 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   gp.nstage = tm.nstage;
   gp.scratch_bytes = 0;
   gp.norm_ring = main_ring;
-  gp.dbg_skip = getenv("FV_DBG_SKIP") ? atoi(getenv("FV_DBG_SKIP")) : 0;
   gp.bnorm = tc->norm2.as<float>();
   gp.cand = nullptr;
   gp.tau_lists = gs.cand;
