@@ -5,23 +5,27 @@
 //
 // computed as a 16-bit-input, fp32-accumulate GEMM on the 5th-generation tensor cores:
 // tcgen05.mma issued by one thread, operands staged in shared memory by TMA with the 128-byte
-// swizzle, accumulators in tensor memory.  The epilogue reads the accumulators back with
-// tcgen05.ld (one query row per thread), adds the row norms and keeps, per query and per work
-// segment, the KP smallest (score, id) pairs in registers.  A second kernel recomputes the
-// reference's exact fp32 distance chain (src/kernels.rs:200-231) for those candidates, picks the
-// k best by (distance, id) and CERTIFIES the result: a query passes only if every row that was
-// not a candidate is provably farther than its k-th result.  Queries that do not pass are
-// re-run by the full-precision scan, so the tensor cores never decide a result on their own.
+// swizzle, accumulators in tensor memory.  The accumulator IS the score: the query operand is
+// stored pre-multiplied by -2 (or -1), and for L2 one extra k step of 16 adds ||b||^2, split
+// into three 16-bit pieces, inside the MMA.  The epilogue reads the accumulators back with
+// tcgen05.ld (one query row per thread) and only compares.
 //
-// Work split: a unit is (query tile, 256 base rows).  Units are laid out query-tile major and cut
-// into equal contiguous runs, one per CTA (persistent, one CTA per SM); a run inside one query
-// tile is a segment and owns one candidate list per query.
+// Two passes.  A sample pass over 1 base row in 32 keeps, per query, its best few scores in
+// registers; the fifth best is that query's bound.  The main pass appends every row scoring below
+// the bound to a candidate list.  A third kernel recomputes the reference's exact fp32 distance
+// chain (src/kernels.rs:200-231) for those candidates, picks the k best by (distance, id) and
+// CERTIFIES the result: a query passes only if every row that was not a candidate is provably
+// farther than its k-th result.  Queries that do not pass are re-run by the full-precision scan,
+// so the tensor cores never decide a result on their own.
+//
+// Work split: a unit is (query tile, 256 base rows); see make_tiling for how units become chunks
+// and chunks are dealt to the persistent CTAs (one per SM) so that base tiles are shared in L2.
 //
 // Two tilings share the code:
-//   MH = 2: 256 queries per tile, kept in shared memory for the whole segment (K <= 128);
+//   MH = 2: 256 queries per tile, kept in shared memory for a whole chunk (K <= 128);
 //           the two 128-row halves use the two accumulator slots, so each B tile is read once
 //           from L2 for 256 queries.
-//   MH = 1: 128 queries per tile (K <= 384); the two accumulator slots alternate between tiles.
+//   MH = 1: 128 queries per tile (K <= 384); the two accumulator slots alternate between units.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -36,11 +40,13 @@
 namespace fv {
 
 static constexpr int KP = 16;          // candidate slots per query and segment in the candidate buffer
-static constexpr int NORM_RING = 4;    // row-norm tiles (1 KB each) kept in shared memory
 static constexpr int TILE_N = 256;     // base rows per unit
 static constexpr int KBLK = 64;        // k elements per shared-memory block (128 bytes)
 static constexpr int A_BLOCK_BYTES = 128 * 128;   // 128 rows x 128 B
 static constexpr int B_STAGE_BYTES = TILE_N * 128;
+static constexpr int EXT_K = 16;                  // k elements of the norm step: one MMA
+static constexpr int A_EXT_BYTES = 128 * EXT_K * 2;     // query side of the norm step
+static constexpr int B_EXT_BYTES = TILE_N * EXT_K * 2;  // base side: one 8 KB tile per unit
 static constexpr int NEPI = 16;        // epilogue warps: four per tensor-memory lane quadrant
 static constexpr int LISTS = NEPI * 32; // per-thread lists of one segment
 static constexpr int SCRATCH_BYTES = NEPI * 16 * 32 * 4;  // list mode only; per epilogue warp: 16 columns x 32 rows of scores
@@ -153,6 +159,37 @@ __device__ __forceinline__ void tc_ld_wait(uint32_t* r) {
                : "memory");
 }
 
+// The same for 64 columns.
+__device__ __forceinline__ void tc_ld64_issue(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]),
+        "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]),
+        "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
+        "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]),
+        "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld64_wait(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]), "+r"(r[32]),
+                 "+r"(r[33]), "+r"(r[34]), "+r"(r[35]), "+r"(r[36]), "+r"(r[37]), "+r"(r[38]), "+r"(r[39]), "+r"(r[40]),
+                 "+r"(r[41]), "+r"(r[42]), "+r"(r[43]), "+r"(r[44]), "+r"(r[45]), "+r"(r[46]), "+r"(r[47]), "+r"(r[48]),
+                 "+r"(r[49]), "+r"(r[50]), "+r"(r[51]), "+r"(r[52]), "+r"(r[53]), "+r"(r[54]), "+r"(r[55]), "+r"(r[56]),
+                 "+r"(r[57]), "+r"(r[58]), "+r"(r[59]), "+r"(r[60]), "+r"(r[61]), "+r"(r[62]), "+r"(r[63])
+               :
+               : "memory");
+}
+
 __device__ __forceinline__ float min3(float a, float b, float c) {
   float r;
   asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -171,29 +208,25 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   return d;
 }
 
+// The same for a K = 16 operand: rows of 32 bytes with the 32-byte swizzle, groups of 8 rows 256 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw32(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= uint64_t((saddr & 0x3FFFF) >> 4);
+  d |= uint64_t(1) << 16;
+  d |= uint64_t(256 >> 4) << 32;
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(6) << 61;                 // SWIZZLE_32B
+  return d;
+}
+
 // Instruction descriptor of kind::f16: fp32 accumulate, A and B both K-major, M x N tile.
 __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16) {
   return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (uint32_t(n >> 3) << 17) |
          (uint32_t(m >> 4) << 24);
 }
 
-// Position of a CTA in its run of units, advanced without divisions (each role loop is a single thread on the
-// critical path of the tensor pipe; a 64-bit division per unit or per k block is a measurable bubble there).
-struct UnitCursor {
-  int mt, nt, NT, ring, nring;
-  __device__ UnitCursor(long long u, int NT_, int nring_) : NT(NT_), ring(0), nring(nring_) {
-    mt = int(u / NT_);
-    nt = int(u - (long long)mt * NT_);
-  }
-  __device__ __forceinline__ void next() {
-    if (++nt == NT) {
-      nt = 0;
-      ++mt;
-    }
-    if (++ring == nring) ring = 0;
-  }
-  __device__ __forceinline__ bool ends_row() const { return nt + 1 == NT; }  // the next unit is another query tile
-};
+// Ring position (stage index and phase bit), advanced without divisions: each role loop is a single thread on
+// the critical path of the tensor pipe, and a 64-bit division per k block is a measurable bubble there.
 struct StageCursor {
   int s, n;
   uint32_t phase;
@@ -212,23 +245,22 @@ struct GemmParams {
   int KB;          // 64-wide k blocks
   int NT;          // base tiles of 256 rows
   int MT;          // query tiles of 128 * MH rows
-  long long U;     // MT * NT units
-  long long upc;   // units per CTA
-  int segmax;      // candidate segments per CTA
+  int cpn;         // base tiles per chunk
+  int nchunks;     // MT * parts; chunk g = part * MT + query tile, taken by CTA g % grid as its (g / grid)-th segment
+  int segmax;      // segments per CTA
   int nstage;
   int scratch_bytes;  // SCRATCH_BYTES in list mode, 0 in threshold mode
-  int norm_ring;      // norm tiles staged in shared memory (0: the epilogue reads the norms from global memory)
-  float scale;     // -2 (L2) or -1 (inner product)
+  int has_ext;        // L2: one more k step of 16 adds the row norms inside the MMA
+  int ext_ring;       // norm-step tiles (8 KB each) kept in shared memory
+  uint32_t aext_c;    // 16-bit pattern of the constant the query side of the norm step holds
+  const uint16_t* ext;  // base side of the norm step: 32 bytes per row, padded to whole tiles
   uint32_t idesc;
-  const float* bnorm;  // padded to a multiple of 256 with +inf
-  u64* cand;           // [grid * segmax][256][KP]  (list mode: output)
+  u64* cand;           // [grid * segmax][LISTS][KP]  (list mode: output)
   int* err;            // set to 1 when a bounded wait ran out
   // threshold mode: per-query bounds from the sample pass, and the candidate buffers they fill
-  const u64* tau_lists;  // the sample pass's `cand`
-  int tNT, tsegmax;      // its tiling
-  long long tupc;
-  u64* cbuf;             // [grid * segmax][256][ccap] (score, row) keys: one private list per epilogue thread and segment
-  unsigned int* ccnt;    // [grid * segmax][256] entries appended (may exceed ccap: overflow)
+  const float* tau;      // [MT * 128 * MH]
+  u64* cbuf;             // [grid * segmax][LISTS][ccap] (score, row) keys: one private list per epilogue thread and segment
+  unsigned int* ccnt;    // [grid * segmax][LISTS] entries appended (may exceed ccap: overflow)
   int ccap;
 };
 
@@ -240,30 +272,34 @@ struct __align__(8) Barriers {
   int abort_flag;
 };
 
-// The SAMPLE_R-th smallest score of query row `r` of query tile `mt` over the lists the sample pass left
-// (+inf when the sample holds fewer rows).  With a sample of 1 row in 32 about 32 * SAMPLE_R = 160 rows of the
-// full set score below it (negative binomial), fewer than 10 with probability < 1e-4.
 // Epilogue thread -> list index: warp group `sub` (0..3) * 128 + lane quadrant * 32 + lane.  MH = 2: sub & 1 is the
 // 128-row half of the query tile, sub >> 1 the half of the 256 columns; MH = 1: sub is the column quarter.
 // The li-th list that holds candidates of query row r of its tile:
-__device__ __forceinline__ int list_of_row(int MH, int r, int li) {
+__host__ __device__ __forceinline__ int list_of_row(int MH, int r, int li) {
   return MH == 2 ? ((r >> 7) + 2 * li) * 128 + (r & 127) : li * 128 + r;
 }
 
 static constexpr int SAMPLE_R = 5;
 static constexpr int SAMPLE_EVERY = 32;
-__device__ __forceinline__ float sample_tau(const u64* __restrict__ lists, int NT, long long upc, int segmax, int MH,
-                                            int mt, int r) {
+
+// The SAMPLE_R-th smallest score of every query over the lists the sample pass left (+inf when the sample holds
+// fewer rows).  With a sample of 1 row in 32 about 32 * SAMPLE_R = 160 rows of the full set score below it
+// (negative binomial), fewer than 10 with probability < 1e-4.
+__global__ void sample_tau_kernel(const u64* __restrict__ lists, int MT, int parts, int grid, int segmax, int MH,
+                                  int nq_pad, float* __restrict__ tau) {
+  const int q = blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= nq_pad) return;
+  const int rows_per_tile = 128 * MH;
+  const int mt = q / rows_per_tile, r = q - mt * rows_per_tile;
   float best[SAMPLE_R];
 #pragma unroll
   for (int j = 0; j < SAMPLE_R; ++j) best[j] = INFINITY;
-  const long long ub = (long long)mt * NT, ue = ub + NT - 1;
-  const int c_lo = int(ub / upc), c_hi = int(ue / upc);
   const int nl = MH == 2 ? 2 : 4;
-  for (int c = c_lo; c <= c_hi; ++c) {
-    const int seg_local = mt - int((c * upc) / NT);
+  for (int part = 0; part < parts; ++part) {
+    const int g = part * MT + mt;
+    const int c = g % grid, seg = g / grid;
     for (int li = 0; li < nl; ++li) {
-      const u64* src = lists + ((size_t(c) * segmax + seg_local) * LISTS + list_of_row(MH, r, li)) * KP;
+      const u64* src = lists + ((size_t(c) * segmax + seg) * LISTS + list_of_row(MH, r, li)) * KP;
 #pragma unroll
       for (int j = 0; j < SAMPLE_R; ++j) {
         const u64 key = src[j];
@@ -280,7 +316,7 @@ __device__ __forceinline__ float sample_tau(const u64* __restrict__ lists, int N
       }
     }
   }
-  return best[SAMPLE_R - 1];
+  tau[q] = best[SAMPLE_R - 1];
 }
 
 template <int MH, int KPT, bool THRESH>
@@ -289,31 +325,34 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   unsigned char* raw = dyn_smem();
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sA = base;                                            // [MH][KB] blocks of 16 KB
-  unsigned char* sB = sA + size_t(MH) * p.KB * A_BLOCK_BYTES;          // [nstage] stages of 32 KB
-  unsigned char* scratch = sB + size_t(p.nstage) * B_STAGE_BYTES;   // 8 epilogue warps x 4 KB
-  float* snorm = reinterpret_cast<float*>(scratch + p.scratch_bytes);  // [NORM_RING][256]
-  Barriers* bars = reinterpret_cast<Barriers*>(scratch + p.scratch_bytes + p.norm_ring * TILE_N * 4);
+  unsigned char* sAext = sA + size_t(MH) * p.KB * A_BLOCK_BYTES;       // 4 KB: the constant rows of the norm step
+  unsigned char* sB = sAext + A_EXT_BYTES;                             // [nstage] stages of 32 KB
+  unsigned char* sE = sB + size_t(p.nstage) * B_STAGE_BYTES;           // [ext_ring] norm-step tiles of 8 KB
+  unsigned char* scratch = sE + size_t(p.ext_ring) * B_EXT_BYTES;      // list mode: 16 epilogue warps x 2 KB
+  Barriers* bars = reinterpret_cast<Barriers*>(scratch + p.scratch_bytes);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long u0 = blockIdx.x * p.upc;
-  const long long u1 = min(p.U, u0 + p.upc);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < p.nstage; ++s) {
-      mbar_init(&bars->full[s], 1);
-      mbar_init(&bars->empty[s], 1);
+    for (int i = 0; i < 8; ++i) {
+      mbar_init(&bars->full[i], 1);
+      mbar_init(&bars->empty[i], 1);
     }
     mbar_init(&bars->a_full, 1);
     mbar_init(&bars->a_empty, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars->tfull[s], 1);
-      mbar_init(&bars->tempty[s], MH == 2 ? NEPI / 2 : NEPI);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->tfull[i], 1);
+      mbar_init(&bars->tempty[i], MH == 2 ? NEPI / 2 : NEPI);
     }
     bars->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  // Query side of the norm step: every row is {c, c, c, 0, 0, 0, 0, 0} twice.  Both 16-byte halves of a row are
+  // equal, so the 32-byte swizzle (which only exchanges the halves of some rows) leaves the tile as written.
+  if (threadIdx.x < A_EXT_BYTES / 16)
+    reinterpret_cast<uint4*>(sAext)[threadIdx.x] = make_uint4(p.aext_c | (p.aext_c << 16), p.aext_c, 0u, 0u);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 1) {  // the MMA warp owns the tensor memory: all 512 columns (one CTA per SM)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&bars->tmem_base))
                  : "memory");
@@ -327,35 +366,34 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      int seg = 0, cur_mt = -1;
       bool ok = true;
-      UnitCursor uc(u0, p.NT, p.norm_ring);
       StageCursor st(p.nstage);
-      for (long long u = u0; u < u1 && ok; ++u, uc.next()) {
-        const int mt = uc.mt, nt = uc.nt;
-        if (mt != cur_mt) {
-          ok = mbar_wait(&bars->a_empty, (seg & 1) ^ 1, abort_flag);
-          if (!ok) break;
-          mbar_expect_tx(&bars->a_full, uint32_t(MH * p.KB * A_BLOCK_BYTES));
-          for (int mh = 0; mh < MH; ++mh)
-            for (int kb = 0; kb < p.KB; ++kb)
-              tma_load_2d(sA + size_t(mh * p.KB + kb) * A_BLOCK_BYTES, &tmA, &bars->a_full, kb * KBLK,
-                          (mt * MH + mh) * 128);
-          cur_mt = mt;
-          seg++;
-        }
-        for (int kb = 0; kb < p.KB; ++kb, st.next()) {
-          const int s = st.s;
-          ok = mbar_wait(&bars->empty[s], st.phase ^ 1, abort_flag);
-          if (!ok) break;
-          // The unit's row norms ride on the barrier of its first k block.  A ring slot is reused NORM_RING
-          // units later; by then the epilogue of that unit is long done, because this stage could only be
-          // refilled after the MMAs of the unit nstage / KB back, which waited for the epilogues before it.
-          mbar_expect_tx(&bars->full[s], uint32_t(B_STAGE_BYTES + (kb == 0 ? TILE_N * 4 : 0)));
-          if (kb == 0)
-            bulk_load_1d(snorm + uc.ring * TILE_N, p.bnorm + size_t(nt) * TILE_N, TILE_N * 4,
-                         &bars->full[s]);
-          tma_load_2d(sB + size_t(s) * B_STAGE_BYTES, &tmB, &bars->full[s], kb * KBLK, nt * TILE_N);
+      int ring = 0;
+      for (int g = blockIdx.x, seg = 0; g < p.nchunks && ok; g += gridDim.x, ++seg) {
+        const int part = g / p.MT, mt = g - part * p.MT;
+        const int nt0 = part * p.cpn, nt1 = min(p.NT, nt0 + p.cpn);
+        ok = mbar_wait(&bars->a_empty, (seg & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(&bars->a_full, uint32_t(MH * p.KB * A_BLOCK_BYTES));
+        for (int mh = 0; mh < MH; ++mh)
+          for (int kb = 0; kb < p.KB; ++kb)
+            tma_load_2d(sA + size_t(mh * p.KB + kb) * A_BLOCK_BYTES, &tmA, &bars->a_full, kb * KBLK,
+                        (mt * MH + mh) * 128);
+        for (int nt = nt0; nt < nt1 && ok; ++nt) {
+          for (int kb = 0; kb < p.KB; ++kb, st.next()) {
+            const int s = st.s;
+            ok = mbar_wait(&bars->empty[s], st.phase ^ 1, abort_flag);
+            if (!ok) break;
+            // The unit's norm-step tile rides on the barrier of its first k block.  Its ring slot is reused
+            // ext_ring units later; the stage acquired just above was last read by a unit at most
+            // ceil(nstage / KB) back, and the commit that freed it also covers every norm step issued before it.
+            const bool with_ext = kb == 0 && p.has_ext;
+            mbar_expect_tx(&bars->full[s], uint32_t(B_STAGE_BYTES + (with_ext ? B_EXT_BYTES : 0)));
+            if (with_ext)  // stored as the swizzled shared-memory image: one contiguous 8 KB copy
+              bulk_load_1d(sE + size_t(ring) * B_EXT_BYTES, p.ext + size_t(nt) * (TILE_N * EXT_K), B_EXT_BYTES, &bars->full[s]);
+            tma_load_2d(sB + size_t(s) * B_STAGE_BYTES, &tmB, &bars->full[s], kb * KBLK, nt * TILE_N);
+          }
+          if (++ring == p.ext_ring) ring = 0;
         }
       }
       // Do not leave while copies may still land in this CTA's shared memory: wait (bounded) until the
@@ -369,187 +407,202 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      int job = 0, seg = 0, cur_mt = -1;
+      int job = 0, ring = 0;
       bool ok = true;
-      UnitCursor uc(u0, p.NT, p.norm_ring);
       StageCursor st(p.nstage);
-      const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB);
-      for (long long u = u0; u < u1 && ok; ++u, uc.next()) {
-        const int mt = uc.mt;
-        if (mt != cur_mt) {
-          ok = mbar_wait(&bars->a_full, seg & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          cur_mt = mt;
-          seg++;
-        }
-        for (int mh = 0; mh < MH && ok; ++mh, ++job) {
-          const int slot = job & 1;
-          ok = mbar_wait(&bars->tempty[slot], (uint32_t(job >> 1) & 1) ^ 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t d_tmem = tmem_base + uint32_t(slot * TILE_N);
-          StageCursor sk = st;  // both halves walk the same stages of this unit
-          for (int kb = 0; kb < p.KB; ++kb, sk.next()) {
-            const int s = sk.s;
-            if (mh == 0) {
-              ok = mbar_wait(&bars->full[s], sk.phase, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-            }
-            const uint32_t a_addr = a_base + uint32_t((mh * p.KB + kb) * A_BLOCK_BYTES);
-            const uint32_t b_addr = b_base + uint32_t(s * B_STAGE_BYTES);
+      const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB), e_base = smem_u32(sE);
+      const uint64_t aext_desc = smem_desc_sw32(smem_u32(sAext));
+      for (int g = blockIdx.x, seg = 0; g < p.nchunks && ok; g += gridDim.x, ++seg) {
+        const int part = g / p.MT;
+        const int nt0 = part * p.cpn, nt1 = min(p.NT, nt0 + p.cpn);
+        ok = mbar_wait(&bars->a_full, seg & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        for (int nt = nt0; nt < nt1 && ok; ++nt) {
+          for (int mh = 0; mh < MH && ok; ++mh, ++job) {
+            const int slot = job & 1;
+            ok = mbar_wait(&bars->tempty[slot], (uint32_t(job >> 1) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + uint32_t(slot * TILE_N);
+            StageCursor sk = st;  // both halves walk the same stages of this unit
+            uint32_t acc = 0;     // the first MMA of a job overwrites the accumulator
+            for (int kb = 0; kb < p.KB; ++kb, sk.next()) {
+              const int s = sk.s;
+              if (mh == 0) {
+                ok = mbar_wait(&bars->full[s], sk.phase, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+              }
+              if (kb == 0 && p.has_ext) {  // + ||b||^2: always the first step of a job
+                tc_mma_f16(d_tmem, aext_desc, smem_desc_sw32(e_base + uint32_t(ring * B_EXT_BYTES)), p.idesc, 0u);
+                acc = 1;
+              }
+              const uint32_t a_addr = a_base + uint32_t((mh * p.KB + kb) * A_BLOCK_BYTES);
+              const uint32_t b_addr = b_base + uint32_t(s * B_STAGE_BYTES);
 #pragma unroll
-            for (int k4 = 0; k4 < KBLK / 16; ++k4)
-              tc_mma_f16(d_tmem, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), p.idesc,
-                         (kb | k4) != 0 ? 1u : 0u);
-            if (mh == MH - 1) tc_commit(&bars->empty[s]);  // the stage is free once these MMAs have read it
+              for (int k4 = 0; k4 < KBLK / 16; ++k4)
+                tc_mma_f16(d_tmem, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), p.idesc,
+                           k4 != 0 ? 1u : acc);
+              acc = 1;
+              if (mh == MH - 1) tc_commit(&bars->empty[s]);  // the stage is free once these MMAs have read it
+            }
+            if (!ok) break;
+            tc_commit(&bars->tfull[slot]);
           }
-          if (!ok) break;
-          tc_commit(&bars->tfull[slot]);
+          for (int kb = 0; kb < p.KB; ++kb) st.next();
+          if (++ring == p.ext_ring) ring = 0;
         }
-        for (int kb = 0; kb < p.KB; ++kb) st.next();
-        const bool last_of_segment = (u + 1 == u1) || uc.ends_row();
-        if (ok && last_of_segment) tc_commit(&bars->a_empty);
+        if (ok) tc_commit(&bars->a_empty);  // the query tile may be replaced once every MMA above has read it
       }
     }
   } else {
-    // ---------------------------------------------------------------- epilogue: 8 warps, one query row per thread
+    // ---------------------------------------------------------------- epilogue: 16 warps, one query row per thread
     const int ew = warp - 2;
     const int quad = warp & 3;   // tensor-memory lanes this warp may read: 32 * quad .. +31
     const int sub = ew >> 2;     // warp group 0..3
     const int grp = MH == 2 ? (sub & 1) : 0;  // MH = 2: which 128-row half (= accumulator slot)
     const int e = sub * 128 + quad * 32 + lane;  // list index inside a segment
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
-    // the KPT best (score, id) of this thread's query row in the current segment, ascending by score;
+    // list mode: the KPT best (score, id) of this thread's query row in the current segment, ascending by score;
     // rows arrive in ascending id order, so a strict score compare keeps the (score, id) order
     float sc[KPT];
     uint32_t idv[KPT];
     float thr = INFINITY;
-    size_t cslot = 0;        // threshold mode: this thread's candidate list of the current segment
+    size_t cslot = 0;        // this thread's list of the current segment
     unsigned int ncand = 0;
-    float* sv = reinterpret_cast<float*>(scratch) + size_t(ew) * 512;  // 16 columns x 32 rows of scores
-#pragma unroll
-    for (int j = 0; j < KPT; ++j) {
-      sc[j] = INFINITY;
-      idv[j] = 0xFFFFFFFFu;
-    }
+    float* sv = reinterpret_cast<float*>(scratch) + size_t(ew) * 512;  // list mode: 16 columns x 32 rows of scores
     int tile_idx = 0;
-    int cur_mt = -1, seg_local = -1;
     bool ok = true;
-    const int ncol = MH == 2 ? TILE_N / 2 : TILE_N / 4;
-    const int col0 = MH == 2 ? (sub >> 1) * (TILE_N / 2) : sub * (TILE_N / 4);
-    UnitCursor uc(u0, p.NT, p.norm_ring);
-    for (long long u = u0; u < u1 && ok; ++u, ++tile_idx, uc.next()) {
-      const int mt = uc.mt, nt = uc.nt;
-      if (mt != cur_mt) {
-        cur_mt = mt;
-        seg_local++;
+    constexpr int NCOL = MH == 2 ? TILE_N / 2 : TILE_N / 4;
+    const int col0 = MH == 2 ? (sub >> 1) * NCOL : sub * NCOL;
+    const uint32_t n_rows = uint32_t(p.n);
+    for (int g = blockIdx.x, seg = 0; g < p.nchunks && ok; g += gridDim.x, ++seg) {
+      const int part = g / p.MT, mt = g - part * p.MT;
+      const int nt0 = part * p.cpn, nt1 = min(p.NT, nt0 + p.cpn);
+      cslot = (size_t(blockIdx.x) * p.segmax + seg) * LISTS + e;
+      ncand = 0;
+      if (THRESH) {  // the bound is fixed: the sample pass's estimate for this query
+        thr = p.tau[mt * (128 * MH) + (MH == 2 ? grp * 128 : 0) + quad * 32 + lane];
+      } else {
         thr = INFINITY;
 #pragma unroll
         for (int j = 0; j < KPT; ++j) {
           sc[j] = INFINITY;
           idv[j] = 0xFFFFFFFFu;
         }
-        if (THRESH) {  // the bound is fixed for the whole segment: the sample pass's estimate
-          const int r = MH == 2 ? grp * 128 + quad * 32 + lane : (quad * 32 + lane);
-          thr = sample_tau(p.tau_lists, p.tNT, p.tupc, p.tsegmax, MH, mt, r);
-          cslot = (size_t(blockIdx.x) * p.segmax + seg_local) * LISTS + e;
-          ncand = 0;
-        }
       }
-      const int job = MH == 2 ? tile_idx * 2 + grp : tile_idx;
-      const int slot = job & 1;
-      ok = mbar_wait(&bars->tfull[slot], uint32_t(job >> 1) & 1, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t row_base = uint32_t(nt) * TILE_N + col0;
-      const uint32_t t_addr = tmem_base + lane_addr + uint32_t(slot * TILE_N + col0);
-      uint32_t rbuf0[32];
-      // One chunk = 32 columns.  Common path: add the row norms, take the minimum, compare with the bound.
-      // Rare path (entered by the whole warp when any of its 32 rows has a column below its bound): the
-      // scores are parked in this warp's shared-memory scratch so that they can be indexed, and each row
-      // inserts its passing columns, in ascending id order, into its sorted register list.
-      auto chunk = [&](uint32_t* r, int c) {
-        const float4* nrm = reinterpret_cast<const float4*>(snorm + uc.ring * TILE_N + col0 + c);
-        float v[32];
-        float g[4] = {INFINITY, INFINITY, INFINITY, INFINITY};  // minima of the four groups of 8 columns
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 nn = nrm[i];
-          v[4 * i + 0] = __fmaf_rn(__uint_as_float(r[4 * i + 0]), p.scale, nn.x);
-          v[4 * i + 1] = __fmaf_rn(__uint_as_float(r[4 * i + 1]), p.scale, nn.y);
-          v[4 * i + 2] = __fmaf_rn(__uint_as_float(r[4 * i + 2]), p.scale, nn.z);
-          v[4 * i + 3] = __fmaf_rn(__uint_as_float(r[4 * i + 3]), p.scale, nn.w);
-          g[i >> 1] = min3(min3(g[i >> 1], v[4 * i + 0], v[4 * i + 1]), v[4 * i + 2], v[4 * i + 3]);
-        }
-        const float m = min3(fminf(g[0], g[1]), g[2], g[3]);
+      for (int nt = nt0; nt < nt1 && ok; ++nt, ++tile_idx) {
+        const int job = MH == 2 ? tile_idx * 2 + grp : tile_idx;
+        const int slot = job & 1;
+        ok = mbar_wait(&bars->tfull[slot], uint32_t(job >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t row_base = uint32_t(nt) * TILE_N + col0;
+        const uint32_t t_addr = tmem_base + lane_addr + uint32_t(slot * TILE_N + col0);
         if (THRESH) {
-          // threshold mode: every column below the (fixed) bound is appended to this thread's private list
-          // (a plain store and a register counter: nothing to wait for)
-          if (__any_sync(FV_FULL, m < thr)) {
-            u64* cl = p.cbuf + cslot * size_t(p.ccap);
+          // Threshold mode.  The accumulator IS the score (the norm step and the scaled query side put
+          // ||b||^2 - 2<q,b> there), so a chunk of 64 columns costs a minimum tree and one vote.  Every column
+          // below the bound is appended to this thread's private list: a plain store and a register counter.
+          // (Issuing the next load before working on this one was tried and ran slower than this plain loop.)
+          auto chunk = [&](const uint32_t* r, int c) {
+            float g8[8];
 #pragma unroll
-            for (int gi = 0; gi < 4; ++gi) {
-              if (__any_sync(FV_FULL, g[gi] < thr)) {
+            for (int gi = 0; gi < 8; ++gi) {
+              const uint32_t* q = r + gi * 8;
+              const float t0 = min3(__uint_as_float(q[0]), __uint_as_float(q[1]), __uint_as_float(q[2]));
+              const float t1 = min3(__uint_as_float(q[3]), __uint_as_float(q[4]), __uint_as_float(q[5]));
+              g8[gi] = fminf(min3(t0, t1, __uint_as_float(q[6])), __uint_as_float(q[7]));
+            }
+            const float m = fminf(min3(g8[0], g8[1], g8[2]), min3(min3(g8[3], g8[4], g8[5]), g8[6], g8[7]));
+            if (__any_sync(FV_FULL, m < thr)) {
+              u64* cl = p.cbuf + cslot * size_t(p.ccap);
 #pragma unroll
-                for (int i = gi * 8; i < gi * 8 + 8; ++i) {
-                  if (v[i] < thr) {
-                    if (ncand < unsigned(p.ccap)) cl[ncand] = make_key(v[i], row_base + uint32_t(c + i));
-                    ncand++;
+              for (int gi = 0; gi < 8; ++gi) {
+                if (__any_sync(FV_FULL, g8[gi] < thr)) {
+#pragma unroll
+                  for (int i = gi * 8; i < gi * 8 + 8; ++i) {
+                    const float v = __uint_as_float(r[i]);
+                    const uint32_t row = row_base + uint32_t(c + i);
+                    if (v < thr && row < n_rows) {
+                      if (ncand < unsigned(p.ccap)) cl[ncand] = make_key(v, row);
+                      ncand++;
+                    }
                   }
                 }
               }
             }
-          }
-        } else if (__any_sync(FV_FULL, m < thr)) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {  // two halves of 16 columns, in id order; the scratch holds one half
-            unsigned mask = 0;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              sv[i * 32 + lane] = v[h * 16 + i];
-              mask |= (v[h * 16 + i] < thr) ? (1u << i) : 0u;
-            }
-            while (__any_sync(FV_FULL, mask != 0)) {
-              if (mask) {
-                const int i = __ffs(mask) - 1;
-                mask &= mask - 1;
-                const float val = sv[i * 32 + lane];
-                if (val < thr) {
-                  float cs = val;
-                  uint32_t ci = row_base + uint32_t(c + h * 16 + i);
-#pragma unroll
-                  for (int j = 0; j < KPT; ++j) {
-                    const bool lt = cs < sc[j];
-                    const float ts = sc[j];
-                    const uint32_t ti = idv[j];
-                    sc[j] = lt ? cs : ts;
-                    idv[j] = lt ? ci : ti;
-                    cs = lt ? ts : cs;
-                    ci = lt ? ti : ci;
-                  }
-                  thr = sc[KPT - 1];
-                }
-              }
-            }
-          }
-        }
-      };
-      // four epilogue warps share each scheduler, so the tensor-memory load latency is hidden across warps
+          };
+          uint32_t rbuf[64];
 #pragma unroll 1
-      for (int c = 0; c < ncol; c += 32) {
-        tc_ld32_issue(t_addr + uint32_t(c), rbuf0);
-        tc_ld_wait(rbuf0);
-        chunk(rbuf0, c);
+          for (int c = 0; c < NCOL; c += 64) {
+            tc_ld64_issue(t_addr + uint32_t(c), rbuf);
+            tc_ld64_wait(rbuf);
+            if (c + 64 == NCOL) {  // the last load has landed: the MMA may overwrite this accumulator slot
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&bars->tempty[slot]);
+            }
+            chunk(rbuf, c);
+          }
+        } else {
+          // List mode.  Common path: the minimum of a chunk against the bound.  Rare path (entered by the whole
+          // warp when any of its 32 rows has a column below its bound): the scores are parked in this warp's
+          // shared-memory scratch so that they can be indexed, and each row inserts its passing columns, in
+          // ascending id order, into its sorted register list.
+          uint32_t rbuf[32];
+#pragma unroll 1
+          for (int c = 0; c < NCOL; c += 32) {
+            tc_ld32_issue(t_addr + uint32_t(c), rbuf);
+            tc_ld_wait(rbuf);
+            float m = INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) m = min3(m, __uint_as_float(rbuf[i]), __uint_as_float(rbuf[i + 1]));
+            if (__any_sync(FV_FULL, m < thr)) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {  // two halves of 16 columns, in id order; the scratch holds one half
+                unsigned mask = 0;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  const float v = __uint_as_float(rbuf[h * 16 + i]);
+                  sv[i * 32 + lane] = v;
+                  mask |= (v < thr && row_base + uint32_t(c + h * 16 + i) < n_rows) ? (1u << i) : 0u;
+                }
+                while (__any_sync(FV_FULL, mask != 0)) {
+                  if (mask) {
+                    const int i = __ffs(mask) - 1;
+                    mask &= mask - 1;
+                    const float val = sv[i * 32 + lane];
+                    if (val < thr) {
+                      float cs = val;
+                      uint32_t ci = row_base + uint32_t(c + h * 16 + i);
+#pragma unroll
+                      for (int j = 0; j < KPT; ++j) {
+                        const bool lt = cs < sc[j];
+                        const float ts = sc[j];
+                        const uint32_t ti = idv[j];
+                        sc[j] = lt ? cs : ts;
+                        idv[j] = lt ? ci : ti;
+                        cs = lt ? ts : cs;
+                        ci = lt ? ti : ci;
+                      }
+                      thr = sc[KPT - 1];
+                    }
+                  }
+                }
+              }
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->tempty[slot]);
+        }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->tempty[slot]);
-      const bool last_of_segment = (u + 1 == u1) || uc.ends_row();
-      if (THRESH && last_of_segment) p.ccnt[cslot] = ncand;
-      if (!THRESH && last_of_segment) {
-        u64* dst = p.cand + ((size_t(blockIdx.x) * p.segmax + seg_local) * LISTS + e) * KP;
+      if (!ok) break;
+      if (THRESH) {
+        p.ccnt[cslot] = ncand;
+      } else {
+        u64* dst = p.cand + cslot * KP;
 #pragma unroll
         for (int j = 0; j < KPT; j += 2) {
           const u64 k0 = idv[j] == 0xFFFFFFFFu ? FV_EMPTY_KEY : make_key(sc[j], idv[j]);
@@ -591,7 +644,7 @@ __device__ __forceinline__ void atomic_max_f(float* a, float v) {
 // one warp per row
 template <bool BF16>
 __global__ void convert_rows_kernel(const float* __restrict__ src, size_t n, int pd, int Kp, uint16_t* __restrict__ dst,
-                                    float* __restrict__ norm2, int is_l2, RangeStats* __restrict__ st) {
+                                    float* __restrict__ norm2, int is_l2, float mul, RangeStats* __restrict__ st) {
   const int lane = threadIdx.x & 31;
   const size_t row = blockIdx.x * size_t(blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n) return;
@@ -607,8 +660,8 @@ __global__ void convert_rows_kernel(const float* __restrict__ src, size_t n, int
       if (!(fabsf(x) <= 3.0e38f)) bad_fin = 1;
     }
     uint16_t h;
-    if (BF16) h = __bfloat16_as_ushort(__float2bfloat16_rn(x));
-    else h = __half_as_ushort(__float2half_rn(x));
+    if (BF16) h = __bfloat16_as_ushort(__float2bfloat16_rn(x * mul));
+    else h = __half_as_ushort(__float2half_rn(x * mul));
     dst[row * size_t(Kp) + c] = h;
   }
   for (int o = 16; o > 0; o >>= 1) {
@@ -628,6 +681,45 @@ __global__ void convert_rows_kernel(const float* __restrict__ src, size_t n, int
   }
 }
 
+// Base side of the norm step: ||b||^2 / 2^e as three 16-bit pieces (p0 + p1 + p2, each the rounding of what the
+// ones before left), then 13 zeros.  The query side holds 2^e three times, so the MMA adds the norm back exactly
+// to 24 bits (fp16: 3 x 11 bits, bf16: 3 x 8).  Rows with a non-finite norm (the padding is +inf) get +inf.
+// The array is kept as the shared-memory image of the 32-byte swizzle (the two 16-byte halves of a row trade
+// places in rows 4..7 of every 8), so that a tile is one contiguous bulk copy instead of 256 narrow TMA rows.
+template <bool BF16>
+__global__ void split_norms_kernel(const float* __restrict__ norm2, size_t first, size_t count, float inv_scale,
+                                   uint16_t* __restrict__ ext) {
+  const size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
+  if (i >= count) return;
+  const size_t row = first + i;
+  const float t = norm2[row] * inv_scale;
+  uint16_t pc[3] = {0, 0, 0};
+  if (!(fabsf(t) < INFINITY)) {
+    pc[0] = BF16 ? 0x7F80 : 0x7C00;
+  } else {
+    float r = t;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      float back;
+      if (BF16) {
+        const __nv_bfloat16 h = __float2bfloat16_rn(r);
+        pc[j] = __bfloat16_as_ushort(h);
+        back = __bfloat162float(h);
+      } else {
+        const __half h = __float2half_rn(r);
+        pc[j] = __half_as_ushort(h);
+        back = __half2float(h);
+      }
+      if (!(fabsf(back) < INFINITY)) break;  // beyond the 16-bit range: the row scores +inf and is never a candidate
+      r = __fsub_rn(r, back);
+    }
+  }
+  uint4* dst = reinterpret_cast<uint4*>(ext + row * EXT_K);
+  const int sw = int(row >> 2) & 1;
+  dst[sw] = make_uint4(uint32_t(pc[0]) | (uint32_t(pc[1]) << 16), uint32_t(pc[2]), 0u, 0u);
+  dst[sw ^ 1] = make_uint4(0u, 0u, 0u, 0u);
+}
+
 __global__ void fill_f32_kernel(float* p, size_t n, float v) {
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) p[i] = v;
 }
@@ -643,13 +735,10 @@ __global__ void init_stats_kernel(RangeStats* st) {
 // ------------------------------------------------------------------------------------------------
 // Exact re-rank and certification: one warp per query.
 struct RerankParams {
-  const u64* tau_lists;   // sample pass lists (for the bound every candidate was tested against)
-  int tNT, tsegmax;
-  long long tupc;
-  const u64* cbuf;        // candidates of the main pass: [grid * segmax][256][ccap]
+  const float* tau;       // the bound every candidate was tested against
+  const u64* cbuf;        // candidates of the main pass: [grid * segmax][LISTS][ccap]
   const unsigned int* ccnt;
-  int ccap, NT, segmax;   // main-pass tiling
-  long long upc;
+  int ccap, MT, parts, grid, segmax;  // main-pass tiling
   const float* rows;      // n x pd fp32
   const float* queries;   // nq x pd fp32
   const float* qnorm2;    // nq (0 for inner product)
@@ -677,7 +766,7 @@ __global__ void rerank_kernel(RerankParams p) {
   const float lo = fminf(p.bst->min_v, p.qst->min_v), hi = fmaxf(p.bst->max_v, p.qst->max_v);
   const float mabs = fmaxf(fabsf(lo), fabsf(hi)), range = hi - lo;
   const bool exact_regime = !p.bst->not_integer && !p.qst->not_integer && !p.bst->not_finite && !p.qst->not_finite &&
-                            mabs <= (p.bf16 ? 256.f : 2048.f) && float(p.Kp) * mabs * mabs <= 8388608.f &&
+                            mabs <= (p.bf16 ? 256.f : 2048.f) && 3.f * float(p.Kp) * mabs * mabs <= 16777216.f &&
                             float(p.Kp) * range * range < 16777216.f;
   const float qn2 = p.qnorm2[q];
   // error bound of a score against the reference distance (minus ||q||^2 for L2) outside that regime
@@ -693,49 +782,76 @@ __global__ void rerank_kernel(RerankParams p) {
     const float kf = float(p.Kp);
     const float e_dot = (2.f * u16 * (1.f + u16) + kf * 4.7683716e-7f + kf * 1.1920929e-7f) * qnorm * bn +
                         5.9604645e-8f * sqrtf(kf) * (qnorm + bn);
-    eps = p.is_l2 ? 2.f * e_dot + kf * 2.3841858e-7f * (qnorm * qnorm + bn * bn) * 2.f : e_dot;
+    // L2: the norm is added inside the MMA (its split loses < 2^-24 of the largest norm, the accumulation
+    // about 2^-21 per step of a partial sum that now includes it), then the reference chain's own rounding
+    const float e_norm = (kf + 16.f) * 4.7683716e-7f * bn * bn + 1.1920929e-7f * bn * bn;
+    eps = p.is_l2 ? 2.f * e_dot + e_norm + kf * 2.3841858e-7f * (qnorm * qnorm + bn * bn) * 2.f : e_dot;
     eps = exact_regime ? 0.f : eps * 1.01f + 1e-30f;
   }
 
   const int rows_per_tile = 128 * p.MH;
   const int mt = int(q / rows_per_tile), r = int(q % rows_per_tile);
   // every row whose score is below tau is in the buffer; every other row scores >= tau
-  const float tau = sample_tau(p.tau_lists, p.tNT, p.tupc, p.tsegmax, p.MH, mt, r);
+  const float tau = p.tau[q];
   bool overflow = false;
   bool mismatch = false;  // exact regime only: a score that is not the exact distance
   u64 bound = FV_EMPTY_KEY;
-  const long long ub = (long long)mt * p.NT, ue = ub + p.NT - 1;
-  const int c_lo = int(ub / p.upc), c_hi = int(ue / p.upc);
   const int lists_per_seg = p.MH == 2 ? 2 : 4;
-  for (int c = c_lo; c <= c_hi; ++c) {
-    const int seg_local = mt - int((c * p.upc) / p.NT);
-    for (int li = 0; li < lists_per_seg; ++li) {
-      const size_t slot = (size_t(c) * p.segmax + seg_local) * LISTS + list_of_row(p.MH, r, li);
-      const unsigned int cnt = p.ccnt[slot];
-      if (cnt > unsigned(p.ccap)) overflow = true;
-      const int nc = int(min(cnt, unsigned(p.ccap)));
-      const u64* src = p.cbuf + slot * size_t(p.ccap);
-      for (int i0 = 0; i0 < nc; i0 += 32) {
-        const int i = i0 + lane;
-        u64 key = FV_EMPTY_KEY;
-        if (i < nc) {
-          const u64 ck = src[i];
-          const uint32_t id = key_id(ck);
-          if (id < uint32_t(p.n)) {
-            const float d = p.is_l2 ? exact_distance<true>(sq, p.rows + size_t(id) * p.pd, p.pd)
-                                    : exact_distance<false>(sq, p.rows + size_t(id) * p.pd, p.pd);
-            if (exact_regime && d != key_distance(ck) + qn2) mismatch = true;
-            if (d < INFINITY) key = make_key(d, id + p.id_base);
-          } else {
-            mismatch = true;  // a padded row can only get here through a non-finite score
-          }
-        }
-        bound = warp_list_offer(list, p.k, key, bound);
+  // The candidates of this query sit in parts * lists_per_seg short lists.  32 lists at a time: each lane looks up
+  // one list's count, a prefix sum lines the entries up, and the warp walks them 32 per step (a lane finds the
+  // list of its entry by bisection over the prefix sums), so every step computes 32 exact distances.
+  const int nlist = p.parts * lists_per_seg;
+  for (int l0 = 0; l0 < nlist; l0 += 32) {
+    const int l = l0 + lane;
+    unsigned int cnt = 0;
+    unsigned long long slot = 0;
+    if (l < nlist) {
+      const int part = l / lists_per_seg, li = l - part * lists_per_seg;
+      const int g = part * p.MT + mt;
+      const int c = g % p.grid, seg_local = g / p.grid;
+      slot = (size_t(c) * p.segmax + seg_local) * LISTS + list_of_row(p.MH, r, li);
+      cnt = p.ccnt[slot];
+      if (cnt > unsigned(p.ccap)) {
+        overflow = true;
+        cnt = unsigned(p.ccap);
       }
+    }
+    unsigned int pre = cnt;  // inclusive prefix sum
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned int v = __shfl_up_sync(FV_FULL, pre, o);
+      if (lane >= o) pre += v;
+    }
+    const unsigned int total = __shfl_sync(FV_FULL, pre, 31);
+    for (unsigned int t0 = 0; t0 < total; t0 += 32) {
+      const unsigned int x = t0 + lane;
+      int j = 0;  // lists whose entries all come before entry x
+#pragma unroll
+      for (int step = 16; step > 0; step >>= 1) {
+        const unsigned int pv = __shfl_sync(FV_FULL, pre, j + step - 1);
+        if (pv <= x) j += step;
+      }
+      const unsigned int pj = __shfl_sync(FV_FULL, pre, j), cj = __shfl_sync(FV_FULL, cnt, j);
+      const unsigned long long sj = __shfl_sync(FV_FULL, slot, j);
+      u64 key = FV_EMPTY_KEY;
+      if (x < total) {
+        const u64 ck = p.cbuf[sj * size_t(p.ccap) + (x - (pj - cj))];
+        const uint32_t id = key_id(ck);
+        if (id < uint32_t(p.n)) {
+          const float d = p.is_l2 ? exact_distance<true>(sq, p.rows + size_t(id) * p.pd, p.pd)
+                                  : exact_distance<false>(sq, p.rows + size_t(id) * p.pd, p.pd);
+          if (exact_regime && d != key_distance(ck) + qn2) mismatch = true;
+          if (d < INFINITY) key = make_key(d, id + p.id_base);
+        } else {
+          mismatch = true;  // a padded row can only get here through a non-finite score
+        }
+      }
+      bound = warp_list_offer(list, p.k, key, bound);
     }
   }
   __syncwarp();
   mismatch = __any_sync(FV_FULL, mismatch);
+  overflow = __any_sync(FV_FULL, overflow);
   const u64 kth = list[p.k - 1];
   bool certified;
   if (overflow || mismatch) {
@@ -816,6 +932,9 @@ struct TcSide {
   DevBuf stats;            // RangeStats (base), RangeStats (queries), retry counter, error word
   size_t ns = 0;           // rows of the strided sample (1 in SAMPLE_EVERY)
   DevBuf samp, samp_norm2; // the sample's operand rows and norms (+inf padded)
+  DevBuf ext, samp_ext;    // norm pieces of the base rows and of the sample (padded like the norms), 32 B per row
+  int ext_e = 0;           // the pieces hold ||b||^2 / 2^ext_e
+  bool ext_valid = false;
   RangeStats h_stats{};
 };
 
@@ -824,14 +943,25 @@ void tc_free(TcSide* tc) { delete tc; }
 static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 static int convert(fv_ctx* ctx, bool bf16, const float* d_src, size_t n, int pd, int Kp, uint16_t* dst, float* norm2,
-                   bool is_l2, RangeStats* st) {
+                   bool is_l2, float mul, RangeStats* st) {
   if (n == 0) return FV_OK;
   const int wpb = 8;
   const unsigned blocks = unsigned((n + wpb - 1) / wpb);
   if (bf16)
-    convert_rows_kernel<true><<<blocks, wpb * 32, 0, ctx->stream>>>(d_src, n, pd, Kp, dst, norm2, is_l2 ? 1 : 0, st);
+    convert_rows_kernel<true><<<blocks, wpb * 32, 0, ctx->stream>>>(d_src, n, pd, Kp, dst, norm2, is_l2 ? 1 : 0, mul, st);
   else
-    convert_rows_kernel<false><<<blocks, wpb * 32, 0, ctx->stream>>>(d_src, n, pd, Kp, dst, norm2, is_l2 ? 1 : 0, st);
+    convert_rows_kernel<false><<<blocks, wpb * 32, 0, ctx->stream>>>(d_src, n, pd, Kp, dst, norm2, is_l2 ? 1 : 0, mul, st);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  return FV_OK;
+}
+
+static int split_norms(fv_ctx* ctx, bool bf16, const float* norm2, size_t first, size_t count, int e, uint16_t* ext) {
+  if (count == 0) return FV_OK;
+  const float inv = std::ldexp(1.f, -e);
+  const unsigned blocks = unsigned((count + 255) / 256);
+  if (bf16) split_norms_kernel<true><<<blocks, 256, 0, ctx->stream>>>(norm2, first, count, inv, ext);
+  else split_norms_kernel<false><<<blocks, 256, 0, ctx->stream>>>(norm2, first, count, inv, ext);
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
   return FV_OK;
@@ -863,20 +993,24 @@ int tc_append(fv_ctx* ctx, TcSide** ptc, int metric, const float* d_rows_new, si
   FV_CUDA(cudaGetLastError());
   uint16_t* dst = tc->half.as<uint16_t>() + n_old * size_t(Kp);
   float* nrm = tc->norm2.as<float>() + n_old;
-  FV_TRY(convert(ctx, tc->bf16, d_rows_new, n_new, pd, Kp, dst, nrm, metric == FV_L2, tmp_stats.as<RangeStats>()));
+  FV_TRY(convert(ctx, tc->bf16, d_rows_new, n_new, pd, Kp, dst, nrm, metric == FV_L2, 1.f, tmp_stats.as<RangeStats>()));
   RangeStats hs;
   FV_CUDA(cudaMemcpyAsync(&hs, tmp_stats.p, sizeof(hs), cudaMemcpyDeviceToHost, ctx->stream));
   FV_CUDA(cudaStreamSynchronize(ctx->stream));
   const float mabs = std::max(std::fabs(hs.min_v), std::fabs(hs.max_v));
-  const bool need_bf16 = !(mabs <= 32768.f);
+  // fp16 also needs the largest squared norm within reach of the norm step: 2^15 (query side) x 2^15 (pieces)
+  const float max_n2 = std::max(hs.max_norm2, tc->n ? tc->h_stats.max_norm2 : 0.f);
+  const bool need_bf16 = !(mabs <= 32768.f) || !(max_n2 <= 1073741824.f);
+  bool resplit = false;
   if (need_bf16 && !tc->bf16) {
+    resplit = true;
     // values beyond the fp16 range: the whole operand copy becomes bf16.  The caller passes the new rows
     // only, so the old ones are re-read from the fp32 matrix that precedes them in the same allocation.
     tc->bf16 = true;
     const float* all_rows = d_rows_new - n_old * size_t(pd);
     init_stats_kernel<<<1, 1, 0, ctx->stream>>>(tc->stats.as<RangeStats>());
     FV_TRY(convert(ctx, true, all_rows, total, pd, Kp, tc->half.as<uint16_t>(), tc->norm2.as<float>(), metric == FV_L2,
-                   tc->stats.as<RangeStats>()));
+                   1.f, tc->stats.as<RangeStats>()));
     FV_CUDA(cudaMemcpyAsync(&tc->h_stats, tc->stats.p, sizeof(RangeStats), cudaMemcpyDeviceToHost, ctx->stream));
     FV_CUDA(cudaStreamSynchronize(ctx->stream));
   } else {
@@ -897,6 +1031,25 @@ int tc_append(fv_ctx* ctx, TcSide** ptc, int metric, const float* d_rows_new, si
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
   tc->n = total;
+  if (metric == FV_L2) {
+    // norm pieces: ||b||^2 / 2^e with the largest quotient in (128, 256] when e was chosen, re-split when it outgrows 2^15
+    FV_TRY(tc->ext.grow(npad * size_t(EXT_K) * 2, n_old * size_t(EXT_K) * 2, ctx->stream));
+    int e = tc->ext_e;
+    const float mx = tc->h_stats.max_norm2;
+    if (tc->bf16) {
+      e = 0;
+      if (!tc->ext_valid || tc->ext_e != 0) resplit = true;
+    } else if (!tc->ext_valid || !(std::ldexp(mx, -e) <= 32768.f)) {
+      int ex = 0;
+      if (mx > 0.f && mx < INFINITY) std::frexp(mx, &ex);  // mx in [2^(ex-1), 2^ex)
+      e = std::min(15, std::max(-14, ex - 8));
+      resplit = true;
+    }
+    tc->ext_e = e;
+    tc->ext_valid = true;
+    const size_t first = resplit ? 0 : n_old;
+    FV_TRY(split_norms(ctx, tc->bf16, tc->norm2.as<float>(), first, npad - first, e, tc->ext.as<uint16_t>()));
+  }
   // the strided sample the threshold of the main pass is estimated from
   tc->ns = std::max<size_t>(SAMPLE_R, total / SAMPLE_EVERY);
   const size_t nspad = (tc->ns + TILE_N - 1) / TILE_N * TILE_N + TILE_N;
@@ -908,6 +1061,10 @@ int tc_append(fv_ctx* ctx, TcSide** ptc, int metric, const float* d_rows_new, si
   fill_f32_kernel<<<8, 256, 0, ctx->stream>>>(tc->samp_norm2.as<float>() + tc->ns, nspad - tc->ns, INFINITY);
   ctx->stats.launches += 2;
   FV_CUDA(cudaGetLastError());
+  if (metric == FV_L2) {
+    FV_TRY(tc->samp_ext.reserve(nspad * size_t(EXT_K) * 2));
+    FV_TRY(split_norms(ctx, tc->bf16, tc->samp_norm2.as<float>(), 0, nspad, tc->ext_e, tc->samp_ext.as<uint16_t>()));
+  }
   return FV_OK;
 }
 
@@ -917,29 +1074,50 @@ bool tc_usable(const TcSide* tc, size_t n, size_t nq, int k) {
 }
 
 // One launch of the GEMM kernel over `rows` operand rows.
+//
+// Work split.  A unit is (query tile, 256 base rows).  Each query tile's row of units is cut into `parts` chunks of
+// `cpn` units; chunk g = part * MT + query tile goes to CTA g % grid as that CTA's (g / grid)-th segment.  The CTAs
+// that run side by side therefore hold DIFFERENT query tiles but walk the SAME base tiles at about the same time:
+// a base tile is fetched from HBM once and served to the other query tiles from L2 (with a contiguous split of the
+// units the 16-bit copy of the base was streamed from HBM once per query tile).  `parts` is the value that minimises
+// waves x (chunk length + a fixed cost per chunk).
 struct Tiling {
-  int KB, MH, MT, NT, grid, segmax, nstage;
-  long long U, upc;
+  int KB, MH, MT, NT, grid, segmax, nstage, cpn, parts, nchunks, ext_ring;
   size_t smem;
 };
 
-static int make_tiling(fv_ctx* ctx, int Kp, size_t nq, size_t rows, int scratch_bytes, int norm_ring, Tiling* t) {
+static int make_tiling(fv_ctx* ctx, int Kp, size_t nq, size_t rows, int scratch_bytes, Tiling* t) {
   t->KB = Kp / KBLK;
   t->MH = t->KB <= 2 ? 2 : 1;
   const int rows_per_tile = 128 * t->MH;
   t->MT = int((nq + rows_per_tile - 1) / rows_per_tile);
   t->NT = int((rows + TILE_N - 1) / TILE_N);
-  t->U = (long long)t->MT * t->NT;
-  t->grid = int(std::min<long long>(ctx->sm_count, t->U));
-  t->upc = (t->U + t->grid - 1) / t->grid;
-  t->segmax = int((t->upc + t->NT - 1) / t->NT) + 1;
-  const size_t a_bytes = size_t(t->MH) * t->KB * A_BLOCK_BYTES;
-  const size_t fixed = 512 + a_bytes + scratch_bytes + norm_ring * TILE_N * 4;
-  if (ctx->smem_optin < fixed + 2 * B_STAGE_BYTES)
-    return fail(FV_ERR_UNSUPPORTED, "not enough shared memory for the tensor-core tiling");
-  t->nstage = std::min(int((ctx->smem_optin - fixed) / B_STAGE_BYTES), 6);
-  t->smem = a_bytes + size_t(t->nstage) * B_STAGE_BYTES + scratch_bytes + norm_ring * TILE_N * 4 + sizeof(Barriers) + 64;
-  return FV_OK;
+  t->grid = int(std::min<long long>(ctx->sm_count, (long long)t->MT * t->NT));
+  long long best = -1;
+  for (int P = 1; P <= t->NT && P <= 4096; ++P) {
+    const int cpn = (t->NT + P - 1) / P;
+    const int parts = (t->NT + cpn - 1) / cpn;
+    const long long chunks = (long long)t->MT * parts;
+    const long long waves = (chunks + t->grid - 1) / t->grid;
+    const long long cost = waves * (cpn + 3);
+    if (best < 0 || cost < best) {
+      best = cost;
+      t->cpn = cpn;
+      t->parts = parts;
+    }
+  }
+  const long long chunks = (long long)t->MT * t->parts;
+  if (chunks > 0x7FFFFFFF) return fail(FV_ERR_UNSUPPORTED, "too many work chunks for the tensor-core tiling");
+  t->nchunks = int(chunks);
+  t->segmax = int((chunks + t->grid - 1) / t->grid);
+  const size_t a_bytes = size_t(t->MH) * t->KB * A_BLOCK_BYTES + A_EXT_BYTES;
+  const size_t tail = size_t(scratch_bytes) + sizeof(Barriers) + 64;
+  for (t->nstage = 6; t->nstage >= 2; --t->nstage) {
+    t->ext_ring = (t->nstage + t->KB - 1) / t->KB + 1;
+    t->smem = 1024 + a_bytes + size_t(t->nstage) * B_STAGE_BYTES + size_t(t->ext_ring) * B_EXT_BYTES + tail;
+    if (t->smem <= ctx->smem_optin) return FV_OK;
+  }
+  return fail(FV_ERR_UNSUPPORTED, "not enough shared memory for the tensor-core tiling");
 }
 
 template <int KPT, bool THRESH>
@@ -954,31 +1132,50 @@ static int launch_gemm(fv_ctx* ctx, const Tiling& t, const CUtensorMap& tmA, con
   return FV_OK;
 }
 
-static constexpr int CAND_CAP = 256;  // candidate slots per epilogue thread and segment in the main pass
+static void fill_params(GemmParams* g, const Tiling& t, size_t rows, size_t nq, int scratch_bytes) {
+  g->n = int(rows);
+  g->nq = int(nq);
+  g->KB = t.KB;
+  g->NT = t.NT;
+  g->MT = t.MT;
+  g->cpn = t.cpn;
+  g->nchunks = t.nchunks;
+  g->segmax = t.segmax;
+  g->nstage = t.nstage;
+  g->scratch_bytes = scratch_bytes;
+  g->ext_ring = t.ext_ring;
+}
 
 // Stages (fv_stats.stage_ms): 0 query conversion, 1 sample pass, 2 main pass, 3 re-rank + certificate, 4 fallback.
-// scratch slots: 2 scan partials (fallback), 3 A operand, 5 query norms + candidate counters, 6 sample lists,
+// scratch slots: 2 scan partials (fallback), 3 A operand, 5 query norms + bounds + candidate counters, 6 sample lists,
 // 7 retry ids, 8 fallback keys, 9 candidate buffers
 int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n, int pd, const float* d_queries,
               size_t nq, int k, uint32_t id_base, u64* d_out_keys, bool mark_stages) {
   const int Kp = tc->Kp;
+  const bool is_l2 = metric == FV_L2;
   Tiling ts{}, tm{};
-  const int main_ring = NORM_RING;
-  FV_TRY(make_tiling(ctx, Kp, nq, tc->ns, SCRATCH_BYTES, NORM_RING, &ts));
-  FV_TRY(make_tiling(ctx, Kp, nq, n, 0, main_ring, &tm));
+  FV_TRY(make_tiling(ctx, Kp, nq, tc->ns, SCRATCH_BYTES, &ts));
+  FV_TRY(make_tiling(ctx, Kp, nq, n, 0, &tm));
   const int rows_per_tile = 128 * tm.MH;
 
-  // queries -> 16-bit operand rows (padded to whole tiles with zeros), norms, statistics
+  // queries -> 16-bit operand rows scaled by -2 (L2) or -1 (inner product), padded to whole tiles with zeros;
+  // norms; statistics
   const size_t nq_pad = size_t(tm.MT) * rows_per_tile;
   FV_TRY(ctx->scratch[3].reserve(nq_pad * size_t(Kp) * 2));
   const size_t nlists = size_t(tm.grid) * tm.segmax * LISTS;
-  FV_TRY(ctx->scratch[5].reserve(nq_pad * sizeof(float) + nlists * sizeof(unsigned int)));
+  // Candidate slots per epilogue thread and segment: 256 unless the buffers would pass 2 GB (they are written
+  // sparsely: about 160 entries per query in all).  A base stored cluster by cluster puts most of a query's
+  // candidates into one or two chunks, so the slots must hold more than the average.
+  int ccap = 256;
+  while (ccap > 16 && nlists * size_t(ccap) * sizeof(u64) > (size_t(2) << 30)) ccap >>= 1;
+  FV_TRY(ctx->scratch[5].reserve(2 * nq_pad * sizeof(float) + nlists * sizeof(unsigned int)));
   FV_TRY(ctx->scratch[6].reserve(size_t(ts.grid) * ts.segmax * LISTS * KP * sizeof(u64)));
   FV_TRY(ctx->scratch[7].reserve(nq * sizeof(uint32_t)));
-  FV_TRY(ctx->scratch[9].reserve(nlists * size_t(CAND_CAP) * sizeof(u64)));
+  FV_TRY(ctx->scratch[9].reserve(nlists * size_t(ccap) * sizeof(u64)));
   uint16_t* dA = ctx->scratch[3].as<uint16_t>();
   float* qn2 = ctx->scratch[5].as<float>();
-  unsigned int* ccnt = reinterpret_cast<unsigned int*>(qn2 + nq_pad);
+  float* tau = qn2 + nq_pad;
+  unsigned int* ccnt = reinterpret_cast<unsigned int*>(tau + nq_pad);
   RangeStats* bst = tc->stats.as<RangeStats>();
   RangeStats* qst = bst + 1;
   unsigned int* retry_count = reinterpret_cast<unsigned int*>(qst + 1);
@@ -991,64 +1188,46 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   init_stats_kernel<<<1, 1, 0, ctx->stream>>>(qst);
   FV_CUDA(cudaMemsetAsync(retry_count, 0, 8, ctx->stream));
   if (nq_pad > nq) FV_CUDA(cudaMemsetAsync(dA + nq * size_t(Kp), 0, (nq_pad - nq) * size_t(Kp) * 2, ctx->stream));
-  FV_TRY(convert(ctx, tc->bf16, d_queries, nq, pd, Kp, dA, qn2, metric == FV_L2, qst));
+  FV_TRY(convert(ctx, tc->bf16, d_queries, nq, pd, Kp, dA, qn2, is_l2, is_l2 ? -2.f : -1.f, qst));
   if (mark_stages) stage_mark(ctx);
 
   // sample pass: per query the SAMPLE_R best scores over 1 row in SAMPLE_EVERY
   GemmParams gs{};
-  gs.n = int(tc->ns);
-  gs.nq = int(nq);
-  gs.KB = ts.KB;
-  gs.NT = ts.NT;
-  gs.MT = ts.MT;
-  gs.U = ts.U;
-  gs.upc = ts.upc;
-  gs.segmax = ts.segmax;
-  gs.nstage = ts.nstage;
-  gs.scratch_bytes = SCRATCH_BYTES;
-  gs.norm_ring = NORM_RING;
-  gs.scale = metric == FV_L2 ? -2.f : -1.f;
+  fill_params(&gs, ts, tc->ns, nq, SCRATCH_BYTES);
+  gs.has_ext = is_l2 ? 1 : 0;
+  gs.aext_c = tc->bf16 ? 0x3F80u : uint32_t((tc->ext_e + 15) << 10);  // 1.0 (bf16) or 2^ext_e (fp16)
   gs.idesc = make_idesc(128, TILE_N, tc->bf16);
-  gs.bnorm = tc->samp_norm2.as<float>();
   gs.cand = ctx->scratch[6].as<u64>();
   gs.err = err;
+  gs.ext = tc->samp_ext.as<uint16_t>();
   FV_TRY((launch_gemm<SAMPLE_R + 1, false>(ctx, ts, tmA, tmS, gs)));
+  sample_tau_kernel<<<unsigned((nq_pad + 255) / 256), 256, 0, ctx->stream>>>(gs.cand, ts.MT, ts.parts, ts.grid, ts.segmax,
+                                                                             ts.MH, int(nq_pad), tau);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
   if (mark_stages) stage_mark(ctx);
 
   // main pass: every row scoring below the query's sampled bound becomes a candidate
   GemmParams gp = gs;
-  gp.n = int(n);
-  gp.NT = tm.NT;
-  gp.MT = tm.MT;
-  gp.U = tm.U;
-  gp.upc = tm.upc;
-  gp.segmax = tm.segmax;
-  gp.nstage = tm.nstage;
-  gp.scratch_bytes = 0;
-  gp.norm_ring = main_ring;
-  gp.bnorm = tc->norm2.as<float>();
+  fill_params(&gp, tm, n, nq, 0);
   gp.cand = nullptr;
-  gp.tau_lists = gs.cand;
-  gp.tNT = ts.NT;
-  gp.tsegmax = ts.segmax;
-  gp.tupc = ts.upc;
+  gp.tau = tau;
   gp.cbuf = ctx->scratch[9].as<u64>();
   gp.ccnt = ccnt;
-  gp.ccap = CAND_CAP;
+  gp.ccap = ccap;
+  gp.ext = tc->ext.as<uint16_t>();
   FV_TRY((launch_gemm<2, true>(ctx, tm, tmA, tmB, gp)));
   if (mark_stages) stage_mark(ctx);
 
   RerankParams rp{};
-  rp.tau_lists = gp.tau_lists;
-  rp.tNT = gp.tNT;
-  rp.tsegmax = gp.tsegmax;
-  rp.tupc = gp.tupc;
+  rp.tau = tau;
   rp.cbuf = gp.cbuf;
   rp.ccnt = gp.ccnt;
   rp.ccap = gp.ccap;
-  rp.NT = tm.NT;
+  rp.MT = tm.MT;
+  rp.parts = tm.parts;
+  rp.grid = tm.grid;
   rp.segmax = tm.segmax;
-  rp.upc = tm.upc;
   rp.rows = d_rows;
   rp.queries = d_queries;
   rp.qnorm2 = qn2;
