@@ -174,7 +174,8 @@ int exact_scan(fv_ctx* ctx, int metric, const float* d_rows, size_t n, int pd, c
   while (W > 1 && nq <= size_t(QT) * (W / 2)) W >>= 1;  // do not launch warps without queries
   // split the rows when there are too few query groups to fill the GPU
   size_t S = 1;
-  const size_t target = size_t(ctx->sm_count) * 4;
+  // aim at about 32 resident warps per SM: each lane streams its own row, so the loads need that many in flight
+  const size_t target = size_t(ctx->sm_count) * std::max(4, 32 / W);
   if (qgroups < target) S = (target + qgroups - 1) / qgroups;
   const size_t max_split = std::max<size_t>(1, n / 1024);
   S = std::min(S, max_split);

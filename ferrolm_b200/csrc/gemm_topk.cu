@@ -765,8 +765,12 @@ __global__ void rerank_kernel(RerankParams p) {
   // distance is an integer below 2^24 in both the tensor-core score and the reference's fp32 chain
   const float lo = fminf(p.bst->min_v, p.qst->min_v), hi = fmaxf(p.bst->max_v, p.qst->max_v);
   const float mabs = fmaxf(fabsf(lo), fabsf(hi)), range = hi - lo;
+  // the accumulator starts at ||b||^2 <= Kp mabs^2 and then takes the terms -2 q_i b_i: it stays within
+  // [-2 Kp mabs^2, Kp mabs^2 + 2 Kp |lo hi|], the upper end only when the values take both signs
+  const float negprod = (lo < 0.f && hi > 0.f) ? -lo * hi : 0.f;
   const bool exact_regime = !p.bst->not_integer && !p.qst->not_integer && !p.bst->not_finite && !p.qst->not_finite &&
-                            mabs <= (p.bf16 ? 256.f : 2048.f) && 3.f * float(p.Kp) * mabs * mabs <= 16777216.f &&
+                            mabs <= (p.bf16 ? 256.f : 2048.f) && float(p.Kp) * mabs * mabs <= 8388608.f &&
+                            float(p.Kp) * (mabs * mabs + 2.f * negprod) <= 16777216.f &&
                             float(p.Kp) * range * range < 16777216.f;
   const float qn2 = p.qnorm2[q];
   // error bound of a score against the reference distance (minus ||q||^2 for L2) outside that regime
