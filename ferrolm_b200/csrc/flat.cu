@@ -149,7 +149,7 @@ static int launch_scan(fv_ctx* ctx, bool is_l2, dim3 grid, int threads, size_t s
   auto kl2 = exact_scan_kernel<QT, true>;
   auto kip = exact_scan_kernel<QT, false>;
   auto k = is_l2 ? kl2 : kip;
-  if (smem > 48 * 1024) FV_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  if (smem > 40 * 1024) FV_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
   k<<<grid, threads, smem, ctx->stream>>>(rows, n, pd, q, q_stride, qids, nq, L, prefilter ? 1 : 0, id_base, rps, parts);
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
@@ -201,7 +201,7 @@ int exact_scan(fv_ctx* ctx, int metric, const float* d_rows, size_t n, int pd, c
     int wpb = 4;
     while (wpb > 1 && size_t(wpb) * L * 8 > 96 * 1024) wpb >>= 1;
     const size_t msmem = size_t(wpb) * L * 8;
-    if (msmem > 48 * 1024)
+    if (msmem > 40 * 1024)
       FV_CUDA(cudaFuncSetAttribute(merge_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(msmem)));
     merge_keys_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, msmem, ctx->stream>>>(parts, int(S), L, nq, L,
                                                                                          d_out_keys);
@@ -396,7 +396,7 @@ int fv_merge_topk_dev(fv_ctx* ctx, const fv_neighbor* d_parts, const uint32_t* d
   int wpb = 4;
   while (wpb > 1 && size_t(wpb) * k_out * 8 > 96 * 1024) wpb >>= 1;
   const size_t smem = size_t(wpb) * k_out * 8;
-  if (smem > 48 * 1024)
+  if (smem > 40 * 1024)
     FV_CUDA(cudaFuncSetAttribute(fv::merge_parts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
   fv::merge_parts_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, smem, ctx->stream>>>(
       d_parts, d_part_counts, int(nparts), nq, int(k_in), int(k_out), keys);

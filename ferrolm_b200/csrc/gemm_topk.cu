@@ -279,21 +279,42 @@ __host__ __device__ __forceinline__ int list_of_row(int MH, int r, int li) {
   return MH == 2 ? ((r >> 7) + 2 * li) * 128 + (r & 127) : li * 128 + r;
 }
 
-static constexpr int SAMPLE_R = 5;
-static constexpr int SAMPLE_EVERY = 32;
+// Sampling.  The sample pass scores 1 base row in E; a query's bound is its R-th best sampled score, so about R * E
+// rows of the full set score below it (negative binomial) and the k nearest are among them unless R or more of the
+// k - 1 nearest rows happen to be sampled: probability P(Binomial(k - 1, 1/E) >= R), kept below 2e-5 by the choice
+// of R (5..7).  E follows the base size (about sqrt(n / 1000)): the sample pass costs ~ n / E, the re-rank ~ R * E.
+static constexpr int SAMPLE_R_MIN = 5, SAMPLE_R_MAX = 7;
 
-// The SAMPLE_R-th smallest score of every query over the lists the sample pass left (+inf when the sample holds
-// fewer rows).  With a sample of 1 row in 32 about 32 * SAMPLE_R = 160 rows of the full set score below it
-// (negative binomial), fewer than 10 with probability < 1e-4.
+static int pick_sample_every(size_t n) {
+  int e = 8;
+  while (e < 128 && double(e) * double(e) * 2000.0 < double(n)) e <<= 1;  // 1M -> 32, 125k -> 8, 6M -> 64
+  return e;
+}
+
+static int pick_sample_r(int k, int every) {
+  const double p = 1.0 / every;
+  for (int r = SAMPLE_R_MIN; r < SAMPLE_R_MAX; ++r) {
+    // P(Binomial(k - 1, p) >= r) by summing the lower tail
+    double tail = 1.0, term = std::pow(1.0 - p, k - 1);
+    for (int i = 0; i < r; ++i) {
+      tail -= term;
+      term *= double(k - 1 - i) / double(i + 1) * p / (1.0 - p);
+    }
+    if (tail < 2e-5) return r;
+  }
+  return SAMPLE_R_MAX;
+}
+
+// The R-th smallest score of every query over the lists the sample pass left (+inf when the sample holds fewer rows).
 __global__ void sample_tau_kernel(const u64* __restrict__ lists, int MT, int parts, int grid, int segmax, int MH,
-                                  int nq_pad, float* __restrict__ tau) {
+                                  int nq_pad, int R, float* __restrict__ tau) {
   const int q = blockIdx.x * blockDim.x + threadIdx.x;
   if (q >= nq_pad) return;
   const int rows_per_tile = 128 * MH;
   const int mt = q / rows_per_tile, r = q - mt * rows_per_tile;
-  float best[SAMPLE_R];
+  float best[SAMPLE_R_MAX];
 #pragma unroll
-  for (int j = 0; j < SAMPLE_R; ++j) best[j] = INFINITY;
+  for (int j = 0; j < SAMPLE_R_MAX; ++j) best[j] = INFINITY;
   const int nl = MH == 2 ? 2 : 4;
   for (int part = 0; part < parts; ++part) {
     const int g = part * MT + mt;
@@ -301,12 +322,12 @@ __global__ void sample_tau_kernel(const u64* __restrict__ lists, int MT, int par
     for (int li = 0; li < nl; ++li) {
       const u64* src = lists + ((size_t(c) * segmax + seg) * LISTS + list_of_row(MH, r, li)) * KP;
 #pragma unroll
-      for (int j = 0; j < SAMPLE_R; ++j) {
-        const u64 key = src[j];
+      for (int j = 0; j < SAMPLE_R_MAX; ++j) {
+        const u64 key = j < R ? src[j] : FV_EMPTY_KEY;  // a list holds R + 1 entries; the slots behind are stale
         if (key != FV_EMPTY_KEY) {
           float sc = key_distance(key);
 #pragma unroll
-          for (int t = 0; t < SAMPLE_R; ++t) {
+          for (int t = 0; t < SAMPLE_R_MAX; ++t) {
             const bool lt = sc < best[t];
             const float tmp = best[t];
             best[t] = lt ? sc : tmp;
@@ -316,7 +337,11 @@ __global__ void sample_tau_kernel(const u64* __restrict__ lists, int MT, int par
       }
     }
   }
-  tau[q] = best[SAMPLE_R - 1];
+  float out = INFINITY;
+#pragma unroll
+  for (int t = 0; t < SAMPLE_R_MAX; ++t)
+    if (t == R - 1) out = best[t];
+  tau[q] = out;
 }
 
 template <int MH, int KPT, bool THRESH>
@@ -604,11 +629,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       } else {
         u64* dst = p.cand + cslot * KP;
 #pragma unroll
-        for (int j = 0; j < KPT; j += 2) {
+        for (int j = 0; j + 1 < KPT; j += 2) {
           const u64 k0 = idv[j] == 0xFFFFFFFFu ? FV_EMPTY_KEY : make_key(sc[j], idv[j]);
           const u64 k1 = idv[j + 1] == 0xFFFFFFFFu ? FV_EMPTY_KEY : make_key(sc[j + 1], idv[j + 1]);
           *reinterpret_cast<ulonglong2*>(dst + j) = make_ulonglong2(k0, k1);
         }
+        if (KPT & 1) dst[KPT - 1] = idv[KPT - 1] == 0xFFFFFFFFu ? FV_EMPTY_KEY : make_key(sc[KPT - 1], idv[KPT - 1]);
       }
     }
   }
@@ -934,7 +960,8 @@ struct TcSide {
   DevBuf half;             // n_cap x Kp 16-bit
   DevBuf norm2;            // padded to 256, +inf beyond n
   DevBuf stats;            // RangeStats (base), RangeStats (queries), retry counter, error word
-  size_t ns = 0;           // rows of the strided sample (1 in SAMPLE_EVERY)
+  size_t ns = 0;           // rows of the strided sample
+  int every = 32;          // 1 row in `every` is sampled
   DevBuf samp, samp_norm2; // the sample's operand rows and norms (+inf padded)
   DevBuf ext, samp_ext;    // norm pieces of the base rows and of the sample (padded like the norms), 32 B per row
   int ext_e = 0;           // the pieces hold ||b||^2 / 2^ext_e
@@ -1055,7 +1082,8 @@ int tc_append(fv_ctx* ctx, TcSide** ptc, int metric, const float* d_rows_new, si
     FV_TRY(split_norms(ctx, tc->bf16, tc->norm2.as<float>(), first, npad - first, e, tc->ext.as<uint16_t>()));
   }
   // the strided sample the threshold of the main pass is estimated from
-  tc->ns = std::max<size_t>(SAMPLE_R, total / SAMPLE_EVERY);
+  tc->every = pick_sample_every(total);
+  tc->ns = std::max<size_t>(SAMPLE_R_MAX, total / size_t(tc->every));
   const size_t nspad = (tc->ns + TILE_N - 1) / TILE_N * TILE_N + TILE_N;
   FV_TRY(tc->samp.reserve(tc->ns * size_t(Kp) * 2 + 1024));
   FV_TRY(tc->samp_norm2.reserve(nspad * sizeof(float)));
@@ -1195,7 +1223,8 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   FV_TRY(convert(ctx, tc->bf16, d_queries, nq, pd, Kp, dA, qn2, is_l2, is_l2 ? -2.f : -1.f, qst));
   if (mark_stages) stage_mark(ctx);
 
-  // sample pass: per query the SAMPLE_R best scores over 1 row in SAMPLE_EVERY
+  // sample pass: per query the R (+1) best scores over the sampled rows
+  const int R = pick_sample_r(k, tc->every);
   GemmParams gs{};
   fill_params(&gs, ts, tc->ns, nq, SCRATCH_BYTES);
   gs.has_ext = is_l2 ? 1 : 0;
@@ -1204,9 +1233,11 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   gs.cand = ctx->scratch[6].as<u64>();
   gs.err = err;
   gs.ext = tc->samp_ext.as<uint16_t>();
-  FV_TRY((launch_gemm<SAMPLE_R + 1, false>(ctx, ts, tmA, tmS, gs)));
+  if (R == 5) FV_TRY((launch_gemm<6, false>(ctx, ts, tmA, tmS, gs)));
+  else if (R == 6) FV_TRY((launch_gemm<7, false>(ctx, ts, tmA, tmS, gs)));
+  else FV_TRY((launch_gemm<8, false>(ctx, ts, tmA, tmS, gs)));
   sample_tau_kernel<<<unsigned((nq_pad + 255) / 256), 256, 0, ctx->stream>>>(gs.cand, ts.MT, ts.parts, ts.grid, ts.segmax,
-                                                                             ts.MH, int(nq_pad), tau);
+                                                                             ts.MH, int(nq_pad), R, tau);
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
   if (mark_stages) stage_mark(ctx);

@@ -537,7 +537,7 @@ static int hnsw_search_dev(fv_hnsw* h, const float* d_queries, size_t nq, size_t
     }
     auto kern = h->metric == FV_L2 ? hnsw_search_kernel<true> : hnsw_search_kernel<false>;
     const size_t smem = per_warp * W;
-    if (smem > 48 * 1024) FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    if (smem > 40 * 1024) FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     kern<<<unsigned(blocks), W * 32, smem, ctx->stream>>>(g, q, d_qids, active, int(k), int(ef), log2slots, tables, keys,
                                                          d_over, d_work);
     ctx->stats.launches++;

@@ -228,6 +228,7 @@ struct ScanArgs {
   const float* centroids;
   const float* codebooks;
   const float* pre;  // may be null
+  const float* qtab; // nq x m x 256: per query, -dot(q_j, w) (inner product) or -2 dot(q_j, w) (L2 with tables)
   const uint32_t* list_off;
   const uint8_t* codes;
   const uint32_t* ids;
@@ -237,8 +238,7 @@ struct ScanArgs {
   int shard_rank, shard_world;  // this shard scans the probed lists l with l % world == rank
   int metric, pd, m, dsub, nprobe, keep, k;
   int refine;        // 1: re-rank the kept candidates exactly
-  int buffered;      // 1: per-warp unsorted buffers of 256 keys, compacted by sorting (16 < keep <= 128)
-  int lstride;       // keys of shared memory per warp: keep, or 256 when buffered
+  int cap;           // keys of the block's candidate buffer (a power of two, >= keep + 2 * threads)
   int candidates;    // 1: write the kept candidates with both distances instead of the final k
   uint32_t id_base;
   u64* out_keys;             // nq x k        (candidates == 0)
@@ -248,99 +248,134 @@ struct ScanArgs {
   unsigned long long* rows_scanned;
 };
 
-// Sorts the 256 keys at `buf` (shared memory, owned by the calling warp) ascending: a bitonic network with 8
-// keys per lane (element r * 32 + lane in register r), strides of 32 and more inside the lane, smaller ones by
-// shuffle.  Kept out of line so that the network exists once in the kernel.
-__device__ __noinline__ void warp_sort256(u64* buf, int cap) {  // cap <= 256 keys live at buf; the rest count as empty
-  const int lane = lane_id();
-  u64 v[8];
-#pragma unroll
-  for (int r = 0; r < 8; ++r) v[r] = (r * 32 + lane) < cap ? buf[r * 32 + lane] : FV_EMPTY_KEY;
-#pragma unroll
-  for (int k = 2; k <= 256; k <<= 1) {
-#pragma unroll
+// Sorts the first `n` keys (a power of two) of `buf` (shared memory) ascending: a bitonic network run by the whole
+// block, one barrier per stage.  Called by every thread of the block.
+__device__ __forceinline__ void block_sort(u64* buf, int n) {
+  for (int k = 2; k <= n; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
-      if (j >= 32) {
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          const int pr = r ^ (j >> 5);
-          if (pr > r) {
-            const bool asc = ((r * 32 + lane) & k) == 0;
-            const u64 x = v[r], y = v[pr];
-            const bool sw = asc ? (x > y) : (x < y);
-            v[r] = sw ? y : x;
-            v[pr] = sw ? x : y;
-          }
-        }
-      } else {
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          const bool asc = ((r * 32 + lane) & k) == 0;
-          const u64 o = __shfl_xor_sync(FV_FULL, v[r], j);
-          const bool keep_min = ((lane & j) == 0) == asc;
-          const u64 lo = v[r] < o ? v[r] : o, hi = v[r] < o ? o : v[r];
-          v[r] = keep_min ? lo : hi;
+      for (int t = threadIdx.x; t < (n >> 1); t += blockDim.x) {
+        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));  // the lower index of pair t
+        const u64 x = buf[i], y = buf[i | j];
+        const bool asc = (i & k) == 0;
+        if ((x > y) == asc) {
+          buf[i] = y;
+          buf[i | j] = x;
         }
       }
+      __syncthreads();
     }
   }
-  __syncwarp();
-#pragma unroll
-  for (int r = 0; r < 8; ++r)
-    if ((r * 32 + lane) < cap) buf[r * 32 + lane] = v[r];
-  __syncwarp();
 }
 
-template <bool M16>
-__global__ void __launch_bounds__(256) ivfpq_scan_kernel(ScanArgs a) {
+// The query's part of the lookup tables for a whole batch (ivfpq.rs:236-238 inner product, :241-251 L2 with
+// precomputed tables): entry (j, e) = -dot(q_j, w_je) or -2 dot(q_j, w_je), the products summed in index order from
+// -0.0 as the reference's iterator sum does.  One block per (16 queries, sub-quantizer), one thread per entry: the
+// codebook is read once per 16 queries instead of once per query.
+__global__ void __launch_bounds__(256) query_tables_kernel(const float* __restrict__ queries, size_t nq, int pd,
+                                                           const float* __restrict__ codebooks, int m, int dsub,
+                                                           int is_ip, float* __restrict__ out) {
+  unsigned char* smem_raw = dyn_smem();
+  float* sqs = reinterpret_cast<float*>(smem_raw);  // [16][dsub]
+  const int j = blockIdx.y, e = threadIdx.x;
+  const size_t q0 = size_t(blockIdx.x) * 16;
+  for (int i = threadIdx.x; i < 16 * dsub; i += blockDim.x) {
+    const size_t qi = q0 + i / dsub;
+    sqs[i] = qi < nq ? queries[qi * size_t(pd) + j * dsub + (i % dsub)] : 0.f;
+  }
+  __syncthreads();
+  const float* wv = codebooks + (size_t(j) * KSUB + e) * dsub;
+  const size_t tab = size_t(m) * KSUB;
+  for (int qi = 0; qi < 16 && q0 + qi < nq; ++qi) {
+    float s = -0.0f;
+    for (int t = 0; t < dsub; ++t) s = __fadd_rn(s, __fmul_rn(sqs[qi * dsub + t], __ldg(wv + t)));
+    out[(q0 + qi) * tab + size_t(j) * KSUB + e] = is_ip ? -s : __fmul_rn(-2.0f, s);
+  }
+}
+
+// Entry (code byte J) of sub-quantizer J's table.  `w` is the 32-bit word of the code that holds byte J, `lut_s` the
+// shared-memory address of the tables (a multiple of 1024): the byte, times 4, is moved into bits 2..9 by one shift,
+// masked and OR-ed onto the address by one logic op, and the table's offset J * 1024 rides in the load.
+template <int J>
+__device__ __forceinline__ float lut_entry(uint32_t w, uint32_t lut_s) {
+  const uint32_t sh = (J & 3) == 0 ? (w << 2) : (w >> ((J & 3) * 8 - 2));
+  const uint32_t addr = (sh & 0x3FCu) | lut_s;
+  float t;
+  asm volatile("ld.shared.f32 %0, [%1 + %2];" : "=f"(t) : "r"(addr), "n"(J * 1024));
+  return t;
+}
+
+template <bool M16, int R>
+__global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
   unsigned char* smem_raw = dyn_smem();
   const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int tab = a.m * int(KSUB);
-  float* sq = reinterpret_cast<float*>(smem_raw);  // pd
-  float* srq = sq + a.pd;                          // pd
-  float* lut = srq + a.pd;                         // tab
-  float* qlut = lut + tab;                         // tab (L2 with tables only)
+  // the lookup table first: its shared-memory address is a multiple of 1024, so a lookup address is formed by OR
+  float* lut = reinterpret_cast<float*>(smem_raw);  // tab
   const bool use_pre = a.metric == FV_L2 && a.pre != nullptr;
-  u64* lists = reinterpret_cast<u64*>(qlut + (use_pre ? tab : 0));  // W x keep, then keep keys for the re-rank
-  u64* mylist = lists + size_t(w) * a.lstride;
-  u64* rerank = lists + size_t(W) * a.lstride;
+  float* qlut = lut + tab;                          // tab (L2 with tables only)
+  float* sq = qlut + (use_pre ? tab : 0);           // pd
+  float* srq = sq + a.pd;                           // pd
+  // Candidates: ONE unsorted buffer for the block.  A row whose key is below the bound is appended (a shared-memory
+  // counter hands out the slots); when the buffer could overflow, the block sorts it, keeps the best `keep` and
+  // takes the keep-th key as the new bound.  One list per block sees every row, so its bound is the tightest the
+  // scan order allows (lists per warp each converged on the best of their own eighth and let 5-8x more rows in).
+  u64* lists = reinterpret_cast<u64*>(srq + a.pd);  // cap keys, then keep keys for the re-rank, then k
+  const uint32_t lut_s = uint32_t(__cvta_generic_to_shared(lut));
+  u64* rerank = lists + a.cap;
   const size_t q = blockIdx.x;
 
   for (int c = tid; c < a.pd; c += blockDim.x) sq[c] = a.queries[q * size_t(a.pd) + c];
-  warp_list_init(mylist, a.lstride);
-  int bcnt = 0;  // buffered mode: keys in this warp's buffer
   __syncthreads();
-  if (a.metric == FV_INNER_PRODUCT) {  // ivfpq.rs:236-238, :307
-    for (int i = tid; i < tab; i += blockDim.x) {
-      const int j = i >> 8;
-      const float* wv = a.codebooks + size_t(i) * a.dsub;
-      float s = -0.0f;
-      for (int t = 0; t < a.dsub; ++t) s = __fadd_rn(s, __fmul_rn(sq[j * a.dsub + t], __ldg(wv + t)));
-      lut[i] = -s;
-    }
-  } else if (use_pre) {  // ivfpq.rs:241-251
-    for (int i = tid; i < tab; i += blockDim.x) {
-      const int j = i >> 8;
-      const float* wv = a.codebooks + size_t(i) * a.dsub;
-      float s = -0.0f;
-      for (int t = 0; t < a.dsub; ++t) s = __fadd_rn(s, __fmul_rn(sq[j * a.dsub + t], __ldg(wv + t)));
-      qlut[i] = __fmul_rn(-2.0f, s);
-    }
+  // the query's own table (ivfpq.rs:236-238, :241-251, :307) was computed for the whole batch by query_tables_kernel
+  if (a.metric == FV_INNER_PRODUCT || use_pre) {
+    float* dst = a.metric == FV_INNER_PRODUCT ? lut : qlut;
+    const float4* src = reinterpret_cast<const float4*>(a.qtab + q * size_t(tab));
+    for (int i = tid; i < tab / 4; i += blockDim.x) reinterpret_cast<float4*>(dst)[i] = __ldg(src + i);
   }
   __syncthreads();
 
-  // The tightest last-kept key of any warp bounds the global keep-th best from above, so every warp may
-  // filter with it: a row that cannot enter that warp's list cannot be among the best `keep` overall.
-  __shared__ unsigned long long shared_bound;
-  if (tid == 0) shared_bound = FV_EMPTY_KEY;
+  __shared__ int shared_count;  // keys in the buffer
+  if (tid == 0) shared_count = 0;
   __syncthreads();
+  // `cnt0` is every thread's copy of the count, read only at points where no append can be in flight (so all
+  // threads hold the same value and take the same branches); `bound` is the keep-th best key at the last compaction.
+  int cnt0 = 0;
   u64 bound = FV_EMPTY_KEY;
+  // Sorts the buffer, keeps the best `keep`, refreshes the bound.  Every thread calls it with the same count, at a
+  // point where no append is in flight; on return appends may resume at once.
+  auto compact = [&](int cnt) {
+    int n = 32;
+    while (n < cnt) n <<= 1;
+    for (int e = cnt + tid; e < n; e += blockDim.x) lists[e] = FV_EMPTY_KEY;
+    __syncthreads();
+    block_sort(lists, n);
+    const int kept = min(cnt, a.keep);
+    if (kept == a.keep) bound = lists[a.keep - 1];  // appends go behind it: it stays put
+    if (tid == 0) shared_count = kept;
+    __syncthreads();
+    return kept;
+  };
+  const int chunk_rows = int(blockDim.x);  // rows the block scans per warp-row step: the most one step can append
+  // Compacting early and often keeps the bound tight (the sort is over the next power of two above the count, so a
+  // small buffer sorts fast); the capacity only has to absorb the one piece that may follow a skipped compaction.
+  const int compact_at = min(a.cap - chunk_rows, 2 * a.keep + 64);
   unsigned long long scanned = 0;
-  for (int p = 0; p < a.nprobe; ++p) {
+  // the next probed cell this block scans (a list-sharded index skips the other shards' lists), or -1
+  auto next_probe = [&](int p) {
+    for (++p; p < a.nprobe; ++p) {
+      const u64 c = a.cells[q * size_t(a.nprobe) + p];
+      if (c == FV_EMPTY_KEY) return -1;
+      if (a.shard_world > 1 && int(key_id(c) % uint32_t(a.shard_world)) != a.shard_rank) continue;
+      return p;
+    }
+    return -1;
+  };
+  int p = next_probe(-1);
+  while (p >= 0) {
     const u64 cell = a.cells[q * size_t(a.nprobe) + p];
-    if (cell == FV_EMPTY_KEY) break;
     const uint32_t l = key_id(cell);
-    if (a.shard_world > 1 && int(l % uint32_t(a.shard_world)) != a.shard_rank) continue;  // another shard's list
+    const int pnext = next_probe(p);
+    cnt0 = shared_count;  // no append between the barrier that ended the last scan and the one below
     float base;
     if (a.metric == FV_L2 && use_pre) {  // ivfpq.rs:256-262
       const float* pre = a.pre + size_t(l) * tab;
@@ -368,84 +403,90 @@ __global__ void __launch_bounds__(256) ivfpq_scan_kernel(ScanArgs a) {
     const size_t off = a.list_off[l];
     const int len = int(a.list_off[l + 1] - off);
     if (tid == 0) scanned += len;
-    for (int r0 = w * 32; r0 < len; r0 += W * 32) {
-      const int r = r0 + lane;
-      u64 key = FV_EMPTY_KEY;
-      if (r < len) {
-        float d = base;  // ivfpq.rs:273-276: base first, then the m table entries in order
-        if (M16) {
-          const uint4 cw = __ldg(reinterpret_cast<const uint4*>(a.codes + (off + r) * 16));
-          const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
-#pragma unroll
-          for (int j = 0; j < 16; ++j) d = __fadd_rn(d, lut[j * 256 + ((cws[j >> 2] >> ((j & 3) * 8)) & 0xFF)]);
-        } else {
-          const uint8_t* code = a.codes + (off + r) * size_t(a.m);
-          for (int j = 0; j < a.m; ++j) d = __fadd_rn(d, lut[j * 256 + code[j]]);
-        }
-        if (d < INFINITY) key = make_key(d, a.ids[off + r]);
+    // The list is scanned in pieces that cannot overflow the buffer even if every row is appended; between pieces
+    // (and only then) the count is read, and the buffer compacted when less than one step of room is left.
+    for (int done = 0; done < len;) {
+      if (done > 0) {
+        __syncthreads();  // appends of the previous piece are complete
+        cnt0 = shared_count;
+        __syncthreads();
       }
-      const u64 sb = *reinterpret_cast<volatile unsigned long long*>(&shared_bound);
-      const u64 eff = sb < bound ? sb : bound;
-      const unsigned hit = __ballot_sync(FV_FULL, key < eff);
-      if (a.buffered) {
-        // append the passing keys; when the buffer is nearly full, sort it and keep the best `keep`
-        if (hit) {
-          if (key < eff) mylist[bcnt + __popc(hit & ((1u << lane) - 1u))] = key;
-          bcnt += __popc(hit);
-          __syncwarp();
-          if (bcnt > a.lstride - 32) {
-            for (int e = bcnt + lane; e < a.lstride; e += 32) mylist[e] = FV_EMPTY_KEY;
-            __syncwarp();
-            warp_sort256(mylist, a.lstride);
-            bcnt = min(bcnt, a.keep);
-            if (bcnt == a.keep) {
-              bound = mylist[a.keep - 1];
-              if (lane == 0) atomicMin(&shared_bound, bound);
+      if (cnt0 >= compact_at) cnt0 = compact(cnt0);
+      const u64 eff = bound;
+      const uint32_t eff_hi = uint32_t(eff >> 32);
+      const int piece = ((a.cap - cnt0) / chunk_rows) * chunk_rows;
+      const int end = min(len, done + piece);
+      // R rows per lane and step: their 16-step add chains are independent and interleave
+      for (int r0 = done + w * (32 * R); r0 < end; r0 += W * 32 * R) {
+        float d[R];
+        bool pass[R];
+        uint32_t cws[R][4];
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int r = r0 + i * 32 + lane;
+          d[i] = base;  // ivfpq.rs:273-276: base first, then the m table entries in order
+          pass[i] = false;
+          if (M16) {
+            uint4 cw = make_uint4(0u, 0u, 0u, 0u);
+            if (r < end) cw = __ldg(reinterpret_cast<const uint4*>(a.codes + (off + r) * 16));
+            cws[i][0] = cw.x;
+            cws[i][1] = cw.y;
+            cws[i][2] = cw.z;
+            cws[i][3] = cw.w;
+          }
+        }
+        if (M16) {
+          // byte j of the code, times 4, OR the table's shared address: one shift and one logic op per lookup
+#define FV_ADC_STEP(J)                                                              \
+  _Pragma("unroll") for (int i = 0; i < R; ++i) d[i] = __fadd_rn(d[i], lut_entry<J>(cws[i][(J) >> 2], lut_s));
+          FV_ADC_STEP(0) FV_ADC_STEP(1) FV_ADC_STEP(2) FV_ADC_STEP(3) FV_ADC_STEP(4) FV_ADC_STEP(5)
+          FV_ADC_STEP(6) FV_ADC_STEP(7) FV_ADC_STEP(8) FV_ADC_STEP(9) FV_ADC_STEP(10) FV_ADC_STEP(11)
+          FV_ADC_STEP(12) FV_ADC_STEP(13) FV_ADC_STEP(14) FV_ADC_STEP(15)
+#undef FV_ADC_STEP
+        } else {
+#pragma unroll
+          for (int i = 0; i < R; ++i) {
+            const int r = r0 + i * 32 + lane;
+            if (r < end) {
+              const uint8_t* code = a.codes + (off + r) * size_t(a.m);
+              for (int j = 0; j < a.m; ++j) d[i] = __fadd_rn(d[i], lut[j * 256 + code[j]]);
             }
           }
         }
-      } else if (hit) {
-        const u64 nb = warp_list_offer(mylist, a.keep, key < eff ? key : FV_EMPTY_KEY, bound);
-        if (nb < bound) {
-          bound = nb;
-          if (lane == 0) atomicMin(&shared_bound, bound);
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int r = r0 + i * 32 + lane;
+          // the distance alone decides for almost every row; the id is fetched only when it can matter
+          pass[i] = r < end && d[i] < INFINITY && order_bits(d[i]) <= eff_hi;
+        }
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          if (__any_sync(FV_FULL, pass[i])) {
+            const int r = r0 + i * 32 + lane;
+            u64 key = FV_EMPTY_KEY;
+            if (pass[i]) key = make_key(d[i], __ldg(a.ids + off + r));
+            const bool in = key < eff;
+            const unsigned hit = __ballot_sync(FV_FULL, in);
+            if (hit) {
+              int slot = 0;
+              if (lane == 0) slot = atomicAdd(&shared_count, __popc(hit));
+              slot = __shfl_sync(FV_FULL, slot, 0);
+              if (in) lists[slot + __popc(hit & ((1u << lane) - 1u))] = key;
+            }
+          }
         }
       }
+      done = end;
     }
     __syncthreads();
+    p = pnext;
   }
   if (tid == 0 && a.rows_scanned) atomicAdd(a.rows_scanned, scanned);
 
-  // fold the other warps' lists into warp 0's
-  if (a.buffered) {
-    for (int e = bcnt + lane; e < a.lstride; e += 32) mylist[e] = FV_EMPTY_KEY;
-    __syncwarp();
-    warp_sort256(mylist, a.lstride);  // every warp ends with its best `keep` sorted at the front
-  }
+  cnt0 = compact(shared_count);  // the best `keep` by (compressed distance, id), ascending, at the front of the buffer
+  for (int e = cnt0 + tid; e < a.keep; e += blockDim.x) lists[e] = FV_EMPTY_KEY;
   __syncthreads();
-  if (w == 0 && a.buffered) {
-    // merge by sorting two lists together; the buffer holds keep + 96 >= keep + 32 keys, so a list of `keep`
-    // goes in in pieces of at most lstride - keep keys
-    for (int ow = 1; ow < W; ++ow) {
-      const u64* other = lists + size_t(ow) * a.lstride;
-      const int room = a.lstride - a.keep;
-      for (int o0 = 0; o0 < a.keep; o0 += room) {
-        for (int e = lane; e < room; e += 32) mylist[a.keep + e] = (o0 + e) < a.keep ? other[o0 + e] : FV_EMPTY_KEY;
-        __syncwarp();
-        warp_sort256(mylist, a.lstride);
-      }
-    }
-  } else if (w == 0) {
-    for (int ow = 1; ow < W; ++ow) {
-      const u64* other = lists + size_t(ow) * a.lstride;
-      for (int e0 = 0; e0 < a.keep; e0 += 32) {
-        const int e = e0 + lane;
-        bound = warp_list_offer(mylist, a.keep, e < a.keep ? other[e] : FV_EMPTY_KEY, bound);
-      }
-    }
-  }
-  __syncthreads();
-  const u64* cand = lists;  // warp 0's list: the best `keep` by (compressed distance, id)
+  const u64* cand = lists;
   if (!a.refine && !a.candidates) {
     for (int e = tid; e < a.k; e += blockDim.x) a.out_keys[q * size_t(a.k) + e] = e < a.keep ? cand[e] : FV_EMPTY_KEY;
     return;
@@ -821,7 +862,7 @@ static int ivfpq_add_impl(fv_ivfpq* ix, const float* vectors, size_t n_total, bo
 int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n) { return ivfpq_add_impl(ix, vectors, n, false); }
 int fv_ivfpq_add_dev(fv_ivfpq* ix, const float* d_vectors, size_t n) { return ivfpq_add_impl(ix, d_vectors, n, true); }
 
-// scratch slots: 0 padded queries, 1 final keys, 2 scan partials, 4 cells
+// scratch slots: 0 padded queries, 1 final keys, 2 scan partials, 4 cells, 5 per-query tables (after the coarse search is done with it)
 static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,
                              bool candidates, fv_neighbor* d_out, uint32_t* d_counts, fv_neighbor* d_adc, float* d_exact) {
   fv_ctx* ctx = ix->ctx;
@@ -856,8 +897,22 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   FV_TRY(ctx->scratch[1].reserve(nq * kout * sizeof(u64)));
   unsigned long long* d_rows = reinterpret_cast<unsigned long long*>(ctx->d_flags + 16);
   FV_CUDA(cudaMemsetAsync(d_rows, 0, sizeof(unsigned long long), ctx->stream));
+  const bool use_pre = ix->metric == FV_L2 && ix->has_pre;
+  const size_t tab = ix->m * fv::KSUB;
+  const float* qtab = nullptr;
+  if (ix->metric == FV_INNER_PRODUCT || use_pre) {
+    FV_TRY(ctx->scratch[5].reserve(nq * tab * sizeof(float)));
+    qtab = ctx->scratch[5].as<float>();
+    dim3 grid(unsigned((nq + 15) / 16), unsigned(ix->m));
+    fv::query_tables_kernel<<<grid, fv::KSUB, 16 * ix->dsub * sizeof(float), ctx->stream>>>(
+        q, nq, pd, ix->codebooks.as<float>(), int(ix->m), int(ix->dsub), ix->metric == FV_INNER_PRODUCT ? 1 : 0,
+        ctx->scratch[5].as<float>());
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
+  }
   fv::ScanArgs a{};
   a.queries = q;
+  a.qtab = qtab;
   a.cells = cells;
   a.centroids = ix->centroids.as<float>();
   a.codebooks = ix->codebooks.as<float>();
@@ -877,8 +932,8 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   a.nprobe = np;
   a.keep = int(keep);
   a.k = int(k);
-  a.buffered = keep > 16 && keep <= 128 ? 1 : 0;
-  a.lstride = a.buffered ? int(std::min<size_t>(256, (keep + 96 + 31) / 32 * 32)) : int(keep);
+  a.cap = 2048;
+  while (size_t(a.cap) < keep + 1024) a.cap <<= 1;
   a.refine = rerank && !candidates ? 1 : 0;
   a.candidates = candidates ? 1 : 0;
   a.id_base = ix->id_base;
@@ -887,14 +942,12 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   a.out_exact = d_exact;
   a.out_counts = d_counts;
   a.rows_scanned = d_rows;
-  const char* wenv = getenv("FV_IVF_WARPS");  // tuning knob
-  const int W = wenv ? atoi(wenv) : (keep <= 128 ? 8 : 4);
-  const bool use_pre = ix->metric == FV_L2 && ix->has_pre;
-  const size_t tab = ix->m * fv::KSUB;
-  const size_t smem = (2 * size_t(pd) + tab * (use_pre ? 2 : 1)) * sizeof(float) + (size_t(W) * size_t(a.lstride) + keep + k) * sizeof(u64);
-  if (smem > ctx->smem_optin) return fv::fail(FV_ERR_UNSUPPORTED, "m, k * refine too large for shared memory");
-  auto kern = ix->m == 16 ? fv::ivfpq_scan_kernel<true> : fv::ivfpq_scan_kernel<false>;
-  if (smem > 48 * 1024) FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  const int W = 8;
+  const size_t smem = (2 * size_t(pd) + tab * (use_pre ? 2 : 1)) * sizeof(float) + (size_t(a.cap) + keep + k) * sizeof(u64);
+  if (smem + 256 > ctx->smem_optin) return fv::fail(FV_ERR_UNSUPPORTED, "m, k * refine too large for shared memory");
+  auto kern = ix->m == 16 ? fv::ivfpq_scan_kernel<true, 1> : fv::ivfpq_scan_kernel<false, 1>;
+  if (ix->m == 16 && getenv("FV_V") && atoi(getenv("FV_V")) == 2) kern = fv::ivfpq_scan_kernel<true, 2>;
+  if (smem > 40 * 1024) FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
   kern<<<unsigned(nq), W * 32, smem, ctx->stream>>>(a);
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
@@ -1168,7 +1221,7 @@ int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float
   FV_TRY(ctx->scratch[1].reserve(nq * k * sizeof(u64)));
   u64* keys = ctx->scratch[1].as<u64>();
   const size_t smem = (keep + k) * sizeof(u64);
-  if (smem > 48 * 1024)
+  if (smem > 40 * 1024)
     FV_CUDA(cudaFuncSetAttribute(fv::merge_refine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
   fv::merge_refine_kernel<<<unsigned(nq), 32, smem, ctx->stream>>>(d_adc_parts, d_exact_parts, d_part_counts, int(nparts),
                                                                   nq, int(keep), int(k), keys);

@@ -282,6 +282,26 @@ def test_ivfpq_short_and_empty_lists(fv, oracle, ctx):
     assert (gc <= 10).all() and gc.min() < 10 or True
 
 
+def test_ivfpq_first_launch_just_under_48k_of_shared_memory():
+    # dim 128, m 16, k 10, refine 10 needs 49,008 bytes of dynamic shared memory: below the 48 KiB opt-in threshold
+    # on its own, above it with the kernel's static shared variable.  In a fresh process no earlier, larger launch
+    # has raised the kernel's limit, so this is the launch that must raise it.
+    import subprocess
+    import sys
+
+    code = (
+        "import numpy as np, ferrolm_b200 as fv\n"
+        "ctx = fv.Context(0)\n"
+        "x = fv.datagen(0, 1, 6000, 128, 16)\n"
+        "ix = fv.IvfPq.train(ctx, 0, 128, x[:3000], fv.IvfPqParams(16, 16, 3, True, 1)); ix.add(x)\n"
+        "out, cnt = ix.search_batch(x[:50], 10, 4, 10)\n"
+        "assert (cnt == 10).all() and (out['id'][:, 0] == np.arange(50)).all()\n"
+        "print('ok')\n"
+    )
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
 def test_ivfpq_sharded_rerank_merge(fv, oracle, ctx):
     import torch
 
