@@ -75,6 +75,25 @@ __device__ __forceinline__ unsigned char* dyn_smem() {
   return fv_dyn_smem;
 }
 
+// Sorts the first `n` keys (a power of two) of `buf` (shared memory) ascending: a bitonic network run by the whole
+// block, one barrier per stage.  Called by every thread of the block.
+__device__ __forceinline__ void block_sort(u64* buf, int n) {
+  for (int k = 2; k <= n; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int t = threadIdx.x; t < (n >> 1); t += blockDim.x) {
+        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));  // the lower index of pair t
+        const u64 x = buf[i], y = buf[i | j];
+        const bool asc = (i & k) == 0;
+        if ((x > y) == asc) {
+          buf[i] = y;
+          buf[i | j] = x;
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // A sorted list of L keys (ascending) owned by ONE warp, in shared or global memory.
 // All 32 lanes call every function with the same arguments.

@@ -16,7 +16,8 @@ template <int QT, bool IS_L2>
 __global__ void __launch_bounds__(128)
     exact_scan_kernel(const float* __restrict__ rows, size_t n, int pd, const float* __restrict__ queries,
                       size_t q_stride, const uint32_t* __restrict__ qids, size_t nq, int L, int prefilter_inf,
-                      uint32_t id_base, size_t rows_per_split, u64* __restrict__ parts) {
+                      uint32_t id_base, size_t rows_per_split, u64* __restrict__ parts, u64* __restrict__ dense,
+                      size_t dense_stride) {
   unsigned char* smem_raw = dyn_smem();
   const int W = blockDim.x >> 5;
   const int w = threadIdx.x >> 5;
@@ -71,16 +72,32 @@ __global__ void __launch_bounds__(128)
         if (!IS_L2) d = -d;
         u64 key = make_key(d, id_base + uint32_t(row));
         if (!valid || (prefilter_inf && !(d < INFINITY))) key = FV_EMPTY_KEY;
-        bound[qi] = warp_list_offer(mylists + qi * L, L, key, bound[qi]);
+        if (dense) {  // every key is kept: the selection happens in block_select_kernel
+          if (valid) dense[(q0 + qi) * dense_stride + row] = key;
+        } else {
+          bound[qi] = warp_list_offer(mylists + qi * L, L, key, bound[qi]);
+        }
       }
     }
   }
   __syncwarp();
+  if (dense) return;
   const int P = gridDim.y;
   for (int qi = 0; qi < nqw; ++qi) {
     u64* dst = parts + ((q0 + qi) * size_t(P) + blockIdx.y) * size_t(L);
     for (int e = lane; e < L; e += 32) dst[e] = mylists[qi * L + e];
   }
+}
+
+// One block per query: the L smallest of n keys (n <= npow2, a power of two), by sorting them in shared memory.
+__global__ void __launch_bounds__(256) block_select_kernel(const u64* __restrict__ dense, size_t stride, int n, int npow2,
+                                                           int L, u64* __restrict__ out) {
+  u64* buf = reinterpret_cast<u64*>(dyn_smem());
+  const size_t q = blockIdx.x;
+  for (int i = threadIdx.x; i < npow2; i += blockDim.x) buf[i] = i < n ? dense[q * stride + i] : FV_EMPTY_KEY;
+  __syncthreads();
+  block_sort(buf, npow2);
+  for (int e = threadIdx.x; e < L; e += blockDim.x) out[q * size_t(L) + e] = e < npow2 ? buf[e] : FV_EMPTY_KEY;
 }
 
 // One warp per query: the L smallest of P sorted partial lists.
@@ -145,12 +162,13 @@ int keys_to_neighbors(fv_ctx* ctx, const u64* d_keys, size_t nq, int L, int k, f
 template <int QT>
 static int launch_scan(fv_ctx* ctx, bool is_l2, dim3 grid, int threads, size_t smem, const float* rows, size_t n, int pd,
                        const float* q, size_t q_stride, const uint32_t* qids, size_t nq, int L, bool prefilter,
-                       uint32_t id_base, size_t rps, u64* parts) {
+                       uint32_t id_base, size_t rps, u64* parts, u64* dense = nullptr, size_t dense_stride = 0) {
   auto kl2 = exact_scan_kernel<QT, true>;
   auto kip = exact_scan_kernel<QT, false>;
   auto k = is_l2 ? kl2 : kip;
   if (smem > 40 * 1024) FV_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-  k<<<grid, threads, smem, ctx->stream>>>(rows, n, pd, q, q_stride, qids, nq, L, prefilter ? 1 : 0, id_base, rps, parts);
+  k<<<grid, threads, smem, ctx->stream>>>(rows, n, pd, q, q_stride, qids, nq, L, prefilter ? 1 : 0, id_base, rps, parts,
+                                          dense, dense_stride);
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
   return FV_OK;
@@ -170,6 +188,31 @@ int exact_scan(fv_ctx* ctx, int metric, const float* d_rows, size_t n, int pd, c
   if (need(QT, W) > budget) QT = 2;
   if (need(QT, W) > budget)
     return fail(FV_ERR_UNSUPPORTED, "dimension and k too large for the shared-memory budget of the scan");
+  // Long lists over few rows (the coarse quantizer: 64 of 1024 cells): keeping a sorted list per query costs more
+  // than the distances.  Write every key instead and let one block per query sort them.
+  if (L >= 32 && n <= 4096 && nq >= 64 && !d_query_ids) {
+    int npow2 = 32;
+    while (size_t(npow2) < n) npow2 <<= 1;
+    FV_TRY(ctx->scratch[scratch_slot].reserve(nq * n * sizeof(u64)));
+    u64* dense = ctx->scratch[scratch_slot].as<u64>();
+    const int w4 = 4;
+    const size_t groups = (nq + size_t(QT) * w4 - 1) / (size_t(QT) * w4);
+    size_t S = std::max<size_t>(1, std::min<size_t>(n / 128, (size_t(ctx->sm_count) * 8 + groups - 1) / groups));
+    size_t rps = ((n + S - 1) / S + 31) / 32 * 32;
+    S = (n + rps - 1) / rps;
+    const dim3 grid(static_cast<unsigned>(groups), static_cast<unsigned>(S));
+    const size_t smem = size_t(w4) * QT * (size_t(pd) * 4 + 8);
+    if (QT == 8)
+      FV_TRY(launch_scan<8>(ctx, metric == FV_L2, grid, w4 * 32, smem, d_rows, n, pd, d_queries, q_stride, nullptr, nq, 1,
+                            prefilter_inf, id_base, rps, nullptr, dense, n));
+    else
+      FV_TRY(launch_scan<2>(ctx, metric == FV_L2, grid, w4 * 32, smem, d_rows, n, pd, d_queries, q_stride, nullptr, nq, 1,
+                            prefilter_inf, id_base, rps, nullptr, dense, n));
+    block_select_kernel<<<unsigned(nq), 256, size_t(npow2) * 8, ctx->stream>>>(dense, n, int(n), npow2, L, d_out_keys);
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
+    return FV_OK;
+  }
   const size_t qgroups = (nq + size_t(QT) * W - 1) / (size_t(QT) * W);
   while (W > 1 && nq <= size_t(QT) * (W / 2)) W >>= 1;  // do not launch warps without queries
   // split the rows when there are too few query groups to fill the GPU

@@ -248,25 +248,6 @@ struct ScanArgs {
   unsigned long long* rows_scanned;
 };
 
-// Sorts the first `n` keys (a power of two) of `buf` (shared memory) ascending: a bitonic network run by the whole
-// block, one barrier per stage.  Called by every thread of the block.
-__device__ __forceinline__ void block_sort(u64* buf, int n) {
-  for (int k = 2; k <= n; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int t = threadIdx.x; t < (n >> 1); t += blockDim.x) {
-        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));  // the lower index of pair t
-        const u64 x = buf[i], y = buf[i | j];
-        const bool asc = (i & k) == 0;
-        if ((x > y) == asc) {
-          buf[i] = y;
-          buf[i | j] = x;
-        }
-      }
-      __syncthreads();
-    }
-  }
-}
-
 // The query's part of the lookup tables for a whole batch (ivfpq.rs:236-238 inner product, :241-251 L2 with
 // precomputed tables): entry (j, e) = -dot(q_j, w_je) or -2 dot(q_j, w_je), the products summed in index order from
 // -0.0 as the reference's iterator sum does.  One block per (16 queries, sub-quantizer), one thread per entry: the
