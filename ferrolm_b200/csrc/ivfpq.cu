@@ -290,41 +290,41 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
   unsigned char* smem_raw = dyn_smem();
   const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int tab = a.m * int(KSUB);
-  // the lookup table first: its shared-memory address is a multiple of 1024, so a lookup address is formed by OR
-  float* lut = reinterpret_cast<float*>(smem_raw);  // tab
   const bool use_pre = a.metric == FV_L2 && a.pre != nullptr;
-  float* qlut = lut + tab;                          // tab (L2 with tables only)
-  float* sq = qlut + (use_pre ? tab : 0);           // pd
-  float* srq = sq + a.pd;                           // pd
+  // The lookup tables first: their shared-memory addresses are multiples of 1024, so a lookup address is formed by
+  // OR.  With precomputed tables there are two: NP producer warps build the next cell's table (pre[l] + the query's
+  // own table, both read from L2) while the other warps scan the current cell with the other one, so the L2 round
+  // trips of the build are off the scan's critical path and one barrier per cell is enough.
+  float* lut0 = reinterpret_cast<float*>(smem_raw);   // tab
+  float* lut1 = lut0 + tab;                           // tab (L2 with tables only)
+  float* sq = lut1 + (use_pre ? tab : 0);             // pd
+  float* srq = sq + a.pd;                             // pd
   // Candidates: ONE unsorted buffer for the block.  A row whose key is below the bound is appended (a shared-memory
-  // counter hands out the slots); when the buffer could overflow, the block sorts it, keeps the best `keep` and
-  // takes the keep-th key as the new bound.  One list per block sees every row, so its bound is the tightest the
-  // scan order allows (lists per warp each converged on the best of their own eighth and let 5-8x more rows in).
+  // counter hands out the slots); when the count passes `compact_at`, the block sorts the buffer, keeps the best
+  // `keep` and takes the keep-th key as the new bound.  One list per block sees every row, so its bound is the
+  // tightest the scan order allows (lists per warp each converged on the best of their own eighth and let 5-8x
+  // more rows in).
   u64* lists = reinterpret_cast<u64*>(srq + a.pd);  // cap keys, then keep keys for the re-rank, then k
-  const uint32_t lut_s = uint32_t(__cvta_generic_to_shared(lut));
   u64* rerank = lists + a.cap;
   const size_t q = blockIdx.x;
+  const int NP = use_pre ? 2 : 0;       // producer warps
+  const int WC = W - NP, cw = w - NP;   // consumer warps; this warp's index among them (negative: a producer)
+  const float* qtab = a.qtab ? a.qtab + q * size_t(tab) : nullptr;
 
   for (int c = tid; c < a.pd; c += blockDim.x) sq[c] = a.queries[q * size_t(a.pd) + c];
-  __syncthreads();
-  // the query's own table (ivfpq.rs:236-238, :241-251, :307) was computed for the whole batch by query_tables_kernel
-  if (a.metric == FV_INNER_PRODUCT || use_pre) {
-    float* dst = a.metric == FV_INNER_PRODUCT ? lut : qlut;
-    const float4* src = reinterpret_cast<const float4*>(a.qtab + q * size_t(tab));
-    for (int i = tid; i < tab / 4; i += blockDim.x) reinterpret_cast<float4*>(dst)[i] = __ldg(src + i);
-  }
-  __syncthreads();
-
   __shared__ int shared_count;  // keys in the buffer
   if (tid == 0) shared_count = 0;
+  // inner product: the query's own table IS the lookup table (ivfpq.rs:236-238, :307)
+  if (a.metric == FV_INNER_PRODUCT)
+    for (int i = tid; i < tab / 4; i += blockDim.x)
+      reinterpret_cast<float4*>(lut0)[i] = __ldg(reinterpret_cast<const float4*>(qtab) + i);
   __syncthreads();
-  // `cnt0` is every thread's copy of the count, read only at points where no append can be in flight (so all
-  // threads hold the same value and take the same branches); `bound` is the keep-th best key at the last compaction.
-  int cnt0 = 0;
-  u64 bound = FV_EMPTY_KEY;
-  // Sorts the buffer, keeps the best `keep`, refreshes the bound.  Every thread calls it with the same count, at a
-  // point where no append is in flight; on return appends may resume at once.
-  auto compact = [&](int cnt) {
+
+  u64 bound = FV_EMPTY_KEY;  // the keep-th best key at the last compaction
+  // Sorts the buffer, keeps the best `keep`, refreshes the bound.  Every thread calls it at a point where no append
+  // is in flight (right after a barrier every appending warp has passed); on return appends may resume at once.
+  auto compact = [&]() {
+    const int cnt = shared_count;
     int n = 32;
     while (n < cnt) n <<= 1;
     for (int e = cnt + tid; e < n; e += blockDim.x) lists[e] = FV_EMPTY_KEY;
@@ -336,10 +336,21 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
     __syncthreads();
     return kept;
   };
-  const int chunk_rows = int(blockDim.x);  // rows the block scans per warp-row step: the most one step can append
+  const int chunk_rows = WC * 32;  // rows the consumers scan per step: the most one step can append
   // Compacting early and often keeps the bound tight (the sort is over the next power of two above the count, so a
-  // small buffer sorts fast); the capacity only has to absorb the one piece that may follow a skipped compaction.
+  // small buffer sorts fast).  `seen` is the highest count this warp's own appends have produced; the barrier that
+  // ends a piece ORs "seen >= compact_at" over the block, so all threads agree on compacting without reading the
+  // counter while others may already be appending again.  `cnt_ub` bounds the count from above for sizing a piece.
   const int compact_at = min(a.cap - chunk_rows, 2 * a.keep + 64);
+  int seen = 0, cnt_ub = 0;
+  auto piece_barrier = [&]() {
+    if (__syncthreads_or(seen >= compact_at)) {
+      cnt_ub = compact();
+      seen = 0;
+    } else {
+      cnt_ub = compact_at - 1;
+    }
+  };
   unsigned long long scanned = 0;
   // the next probed cell this block scans (a list-sharded index skips the other shards' lists), or -1
   auto next_probe = [&](int p) {
@@ -351,17 +362,34 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
     }
     return -1;
   };
+  // table of cell l with precomputed tables (ivfpq.rs:256-262), by `nthr` threads of which this is number `t`
+  auto build_pre = [&](float* dst, uint32_t l, int t, int nthr) {
+    const float4* pre = reinterpret_cast<const float4*>(a.pre + size_t(l) * tab);
+    const float4* qt = reinterpret_cast<const float4*>(qtab);
+#pragma unroll 4
+    for (int i = t; i < tab / 4; i += nthr) {
+      const float4 x = __ldg(pre + i), y = __ldg(qt + i);
+      reinterpret_cast<float4*>(dst)[i] =
+          make_float4(__fadd_rn(x.x, y.x), __fadd_rn(x.y, y.y), __fadd_rn(x.z, y.z), __fadd_rn(x.w, y.w));
+    }
+  };
+
   int p = next_probe(-1);
+  int cur = 0;  // which table the scan reads
+  if (use_pre && p >= 0) {
+    build_pre(lut0, key_id(a.cells[q * size_t(a.nprobe) + p]), tid, int(blockDim.x));
+    __syncthreads();
+  }
   while (p >= 0) {
     const u64 cell = a.cells[q * size_t(a.nprobe) + p];
     const uint32_t l = key_id(cell);
     const int pnext = next_probe(p);
-    cnt0 = shared_count;  // no append between the barrier that ended the last scan and the one below
+    float* lut = cur ? lut1 : lut0;
     float base;
-    if (a.metric == FV_L2 && use_pre) {  // ivfpq.rs:256-262
-      const float* pre = a.pre + size_t(l) * tab;
-      for (int i = tid; i < tab; i += blockDim.x) lut[i] = __fadd_rn(__ldg(pre + i), qlut[i]);
+    if (use_pre) {
       base = key_distance(cell);
+      if (cw < 0 && pnext >= 0)  // producers: the next cell's table, into the other buffer
+        build_pre(cur ? lut0 : lut1, key_id(a.cells[q * size_t(a.nprobe) + pnext]), tid, NP * 32);
     } else if (a.metric == FV_L2) {  // ivfpq.rs:263-269
       const float* cen = a.centroids + size_t(l) * a.pd;
       for (int c = tid; c < a.pd; c += blockDim.x) srq[c] = __fsub_rn(sq[c], cen[c]);
@@ -377,95 +405,95 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
         lut[i] = s;
       }
       base = 0.0f;
+      __syncthreads();
     } else {
       base = key_distance(cell);  // -dot(q, centroid), the same chain as ivfpq.rs:270
     }
-    __syncthreads();
+    const uint32_t lut_s = uint32_t(__cvta_generic_to_shared(lut));
     const size_t off = a.list_off[l];
     const int len = int(a.list_off[l + 1] - off);
     if (tid == 0) scanned += len;
-    // The list is scanned in pieces that cannot overflow the buffer even if every row is appended; between pieces
-    // (and only then) the count is read, and the buffer compacted when less than one step of room is left.
-    for (int done = 0; done < len;) {
-      if (done > 0) {
-        __syncthreads();  // appends of the previous piece are complete
-        cnt0 = shared_count;
-        __syncthreads();
-      }
-      if (cnt0 >= compact_at) cnt0 = compact(cnt0);
+    // The list is scanned in pieces that cannot overflow the buffer even if every row is appended; every piece ends
+    // with the barrier that decides about compaction (the last one also hands the tables over).
+    for (int done = 0; done < len || done == 0;) {
       const u64 eff = bound;
       const uint32_t eff_hi = uint32_t(eff >> 32);
-      const int piece = ((a.cap - cnt0) / chunk_rows) * chunk_rows;
+      const int piece = ((a.cap - cnt_ub) / chunk_rows) * chunk_rows;
       const int end = min(len, done + piece);
-      // R rows per lane and step: their 16-step add chains are independent and interleave
-      for (int r0 = done + w * (32 * R); r0 < end; r0 += W * 32 * R) {
-        float d[R];
-        bool pass[R];
-        uint32_t cws[R][4];
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-          const int r = r0 + i * 32 + lane;
-          d[i] = base;  // ivfpq.rs:273-276: base first, then the m table entries in order
-          pass[i] = false;
-          if (M16) {
-            uint4 cw = make_uint4(0u, 0u, 0u, 0u);
-            if (r < end) cw = __ldg(reinterpret_cast<const uint4*>(a.codes + (off + r) * 16));
-            cws[i][0] = cw.x;
-            cws[i][1] = cw.y;
-            cws[i][2] = cw.z;
-            cws[i][3] = cw.w;
-          }
-        }
-        if (M16) {
-          // byte j of the code, times 4, OR the table's shared address: one shift and one logic op per lookup
-#define FV_ADC_STEP(J)                                                              \
-  _Pragma("unroll") for (int i = 0; i < R; ++i) d[i] = __fadd_rn(d[i], lut_entry<J>(cws[i][(J) >> 2], lut_s));
-          FV_ADC_STEP(0) FV_ADC_STEP(1) FV_ADC_STEP(2) FV_ADC_STEP(3) FV_ADC_STEP(4) FV_ADC_STEP(5)
-          FV_ADC_STEP(6) FV_ADC_STEP(7) FV_ADC_STEP(8) FV_ADC_STEP(9) FV_ADC_STEP(10) FV_ADC_STEP(11)
-          FV_ADC_STEP(12) FV_ADC_STEP(13) FV_ADC_STEP(14) FV_ADC_STEP(15)
-#undef FV_ADC_STEP
-        } else {
+      if (cw >= 0) {
+        // R rows per lane and step: their 16-step add chains are independent and interleave
+        for (int r0 = done + cw * (32 * R); r0 < end; r0 += WC * 32 * R) {
+          float d[R];
+          bool pass[R];
+          uint32_t cws[R][4];
 #pragma unroll
           for (int i = 0; i < R; ++i) {
             const int r = r0 + i * 32 + lane;
-            if (r < end) {
-              const uint8_t* code = a.codes + (off + r) * size_t(a.m);
-              for (int j = 0; j < a.m; ++j) d[i] = __fadd_rn(d[i], lut[j * 256 + code[j]]);
+            d[i] = base;  // ivfpq.rs:273-276: base first, then the m table entries in order
+            pass[i] = false;
+            if (M16) {
+              uint4 cwv = make_uint4(0u, 0u, 0u, 0u);
+              if (r < end) cwv = __ldg(reinterpret_cast<const uint4*>(a.codes + (off + r) * 16));
+              cws[i][0] = cwv.x;
+              cws[i][1] = cwv.y;
+              cws[i][2] = cwv.z;
+              cws[i][3] = cwv.w;
             }
           }
-        }
+          if (M16) {
+            // byte j of the code, times 4, OR the table's shared address: one shift and one logic op per lookup
+#define FV_ADC_STEP(J)                                                              \
+  _Pragma("unroll") for (int i = 0; i < R; ++i) d[i] = __fadd_rn(d[i], lut_entry<J>(cws[i][(J) >> 2], lut_s));
+            FV_ADC_STEP(0) FV_ADC_STEP(1) FV_ADC_STEP(2) FV_ADC_STEP(3) FV_ADC_STEP(4) FV_ADC_STEP(5)
+            FV_ADC_STEP(6) FV_ADC_STEP(7) FV_ADC_STEP(8) FV_ADC_STEP(9) FV_ADC_STEP(10) FV_ADC_STEP(11)
+            FV_ADC_STEP(12) FV_ADC_STEP(13) FV_ADC_STEP(14) FV_ADC_STEP(15)
+#undef FV_ADC_STEP
+          } else {
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-          const int r = r0 + i * 32 + lane;
-          // the distance alone decides for almost every row; the id is fetched only when it can matter
-          pass[i] = r < end && d[i] < INFINITY && order_bits(d[i]) <= eff_hi;
-        }
+            for (int i = 0; i < R; ++i) {
+              const int r = r0 + i * 32 + lane;
+              if (r < end) {
+                const uint8_t* code = a.codes + (off + r) * size_t(a.m);
+                for (int j = 0; j < a.m; ++j) d[i] = __fadd_rn(d[i], lut[j * 256 + code[j]]);
+              }
+            }
+          }
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-          if (__any_sync(FV_FULL, pass[i])) {
+          for (int i = 0; i < R; ++i) {
             const int r = r0 + i * 32 + lane;
-            u64 key = FV_EMPTY_KEY;
-            if (pass[i]) key = make_key(d[i], __ldg(a.ids + off + r));
-            const bool in = key < eff;
-            const unsigned hit = __ballot_sync(FV_FULL, in);
-            if (hit) {
-              int slot = 0;
-              if (lane == 0) slot = atomicAdd(&shared_count, __popc(hit));
-              slot = __shfl_sync(FV_FULL, slot, 0);
-              if (in) lists[slot + __popc(hit & ((1u << lane) - 1u))] = key;
+            // the distance alone decides for almost every row; the id is fetched only when it can matter
+            pass[i] = r < end && d[i] < INFINITY && order_bits(d[i]) <= eff_hi;
+          }
+#pragma unroll
+          for (int i = 0; i < R; ++i) {
+            if (__any_sync(FV_FULL, pass[i])) {
+              const int r = r0 + i * 32 + lane;
+              u64 key = FV_EMPTY_KEY;
+              if (pass[i]) key = make_key(d[i], __ldg(a.ids + off + r));
+              const bool in = key < eff;
+              const unsigned hit = __ballot_sync(FV_FULL, in);
+              if (hit) {
+                int slot = 0;
+                if (lane == 0) slot = atomicAdd(&shared_count, __popc(hit));
+                slot = __shfl_sync(FV_FULL, slot, 0);
+                if (in) lists[slot + __popc(hit & ((1u << lane) - 1u))] = key;
+                seen = max(seen, slot + __popc(hit));
+              }
             }
           }
         }
       }
       done = end;
+      piece_barrier();
+      if (len == 0) break;
     }
-    __syncthreads();
     p = pnext;
+    cur = use_pre ? cur ^ 1 : 0;
   }
   if (tid == 0 && a.rows_scanned) atomicAdd(a.rows_scanned, scanned);
 
-  cnt0 = compact(shared_count);  // the best `keep` by (compressed distance, id), ascending, at the front of the buffer
-  for (int e = cnt0 + tid; e < a.keep; e += blockDim.x) lists[e] = FV_EMPTY_KEY;
+  cnt_ub = compact();  // the best `keep` by (compressed distance, id), ascending, at the front of the buffer
+  for (int e = cnt_ub + tid; e < a.keep; e += blockDim.x) lists[e] = FV_EMPTY_KEY;
   __syncthreads();
   const u64* cand = lists;
   if (!a.refine && !a.candidates) {
@@ -926,8 +954,7 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   const int W = 8;
   const size_t smem = (2 * size_t(pd) + tab * (use_pre ? 2 : 1)) * sizeof(float) + (size_t(a.cap) + keep + k) * sizeof(u64);
   if (smem + 256 > ctx->smem_optin) return fv::fail(FV_ERR_UNSUPPORTED, "m, k * refine too large for shared memory");
-  auto kern = ix->m == 16 ? fv::ivfpq_scan_kernel<true, 1> : fv::ivfpq_scan_kernel<false, 1>;
-  if (ix->m == 16 && getenv("FV_V") && atoi(getenv("FV_V")) == 2) kern = fv::ivfpq_scan_kernel<true, 2>;
+  auto kern = ix->m == 16 ? fv::ivfpq_scan_kernel<true, 2> : fv::ivfpq_scan_kernel<false, 1>;
   if (smem > 40 * 1024) FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
   kern<<<unsigned(nq), W * 32, smem, ctx->stream>>>(a);
   ctx->stats.launches++;
