@@ -385,7 +385,7 @@ def run_ours(args):
         with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
             tr = json.load(f)[args.workload]
         if args.workload == "flat":
-            line["roofline"]["traffic"] = tr["bytes_per_query_tile"] * ((NQ + 255) // 256) * (hi - lo) / 1_000_000
+            line["roofline"]["traffic"] = tr["bytes_per_launch"] * (hi - lo) / 1_000_000
         else:
             line["roofline"]["traffic"] = tr["bytes_per_query"] * NQ
         line["roofline"]["traffic_note"] = "ncu dram bytes of a smaller capture, scaled: " + tr["scaling"]
