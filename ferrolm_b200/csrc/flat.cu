@@ -100,6 +100,71 @@ __global__ void __launch_bounds__(256) block_select_kernel(const u64* __restrict
   for (int e = threadIdx.x; e < L; e += blockDim.x) out[q * size_t(L) + e] = e < npow2 ? buf[e] : FV_EMPTY_KEY;
 }
 
+// One warp per query: the L smallest of n <= 32 * NPL keys without sorting them all.  A lane keeps the distance words
+// of rows lane, lane + 32, ... in registers; 32 bisection steps on that word find the L-th smallest distance T;
+// the rows below T and the first ties at T (rows are in id order) are gathered and only those L keys are sorted.
+template <int NPL>
+__global__ void __launch_bounds__(128) warp_select_kernel(const u64* __restrict__ dense, size_t stride, int n, int L,
+                                                          int Lpow2, size_t nq, u64* __restrict__ out) {
+  u64* buf = reinterpret_cast<u64*>(dyn_smem()) + size_t(threadIdx.x >> 5) * Lpow2;
+  const int lane = threadIdx.x & 31;
+  const size_t q = blockIdx.x * size_t(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (q >= nq) return;
+  const u64* src = dense + q * stride;
+  uint32_t h[NPL];
+#pragma unroll
+  for (int j = 0; j < NPL; ++j) {
+    const int r = j * 32 + lane;
+    h[j] = r < n ? uint32_t(src[r] >> 32) : 0xFFFFFFFFu;
+  }
+  uint32_t lo = 0, hi = 0xFFFFFFFFu;
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    int c = 0;
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) c += h[j] <= mid ? 1 : 0;
+    c = __reduce_add_sync(FV_FULL, c);
+    if (c >= L) hi = mid;
+    else lo = mid + 1;
+  }
+  const uint32_t T = lo;
+  int below = 0;
+#pragma unroll
+  for (int j = 0; j < NPL; ++j) below += h[j] < T ? 1 : 0;
+  below = __reduce_add_sync(FV_FULL, below);
+  const int ties_wanted = L - below;  // >= 1 by the choice of T (or rows ran out: then T is the filler value)
+  for (int e = lane; e < Lpow2; e += 32) buf[e] = FV_EMPTY_KEY;
+  __syncwarp();
+  int pos = 0, ties = 0;  // the same in every lane
+#pragma unroll
+  for (int j = 0; j < NPL; ++j) {
+    const int r = j * 32 + lane;
+    const unsigned tmask = __ballot_sync(FV_FULL, h[j] == T);
+    const int my_tie = ties + __popc(tmask & ((1u << lane) - 1u));
+    const bool take = h[j] < T || (h[j] == T && my_tie < ties_wanted);
+    const unsigned smask = __ballot_sync(FV_FULL, take);
+    if (take && r < n) buf[pos + __popc(smask & ((1u << lane) - 1u))] = src[r];
+    pos += __popc(smask);
+    ties += __popc(tmask);
+  }
+  __syncwarp();
+  // sort the L gathered keys (bitonic over Lpow2, one warp)
+  for (int k = 2; k <= Lpow2; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int t = lane; t < (Lpow2 >> 1); t += 32) {
+        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+        const u64 x = buf[i], y = buf[i | j];
+        if ((x > y) == ((i & k) == 0)) {
+          buf[i] = y;
+          buf[i | j] = x;
+        }
+      }
+      __syncwarp();
+    }
+  }
+  for (int e = lane; e < L; e += 32) out[q * size_t(L) + e] = buf[e];
+}
+
 // One warp per query: the L smallest of P sorted partial lists.
 __global__ void merge_keys_kernel(const u64* __restrict__ parts, int P, int Lin, size_t nq, int Lout,
                                   u64* __restrict__ out) {
@@ -208,7 +273,17 @@ int exact_scan(fv_ctx* ctx, int metric, const float* d_rows, size_t n, int pd, c
     else
       FV_TRY(launch_scan<2>(ctx, metric == FV_L2, grid, w4 * 32, smem, d_rows, n, pd, d_queries, q_stride, nullptr, nq, 1,
                             prefilter_inf, id_base, rps, nullptr, dense, n));
-    block_select_kernel<<<unsigned(nq), 256, size_t(npow2) * 8, ctx->stream>>>(dense, n, int(n), npow2, L, d_out_keys);
+    if (n <= 2048 && L <= 256) {
+      int lp = 32;
+      while (lp < L) lp <<= 1;
+      const unsigned blocks = unsigned((nq + 3) / 4);
+      if (n <= 1024)
+        warp_select_kernel<32><<<blocks, 128, size_t(4) * lp * 8, ctx->stream>>>(dense, n, int(n), L, lp, nq, d_out_keys);
+      else
+        warp_select_kernel<64><<<blocks, 128, size_t(4) * lp * 8, ctx->stream>>>(dense, n, int(n), L, lp, nq, d_out_keys);
+    } else {
+      block_select_kernel<<<unsigned(nq), 256, size_t(npow2) * 8, ctx->stream>>>(dense, n, int(n), npow2, L, d_out_keys);
+    }
     ctx->stats.launches++;
     FV_CUDA(cudaGetLastError());
     return FV_OK;

@@ -252,6 +252,7 @@ struct ScanArgs {
 // precomputed tables): entry (j, e) = -dot(q_j, w_je) or -2 dot(q_j, w_je), the products summed in index order from
 // -0.0 as the reference's iterator sum does.  One block per (16 queries, sub-quantizer), one thread per entry: the
 // codebook is read once per 16 queries instead of once per query.
+template <int DSUB>  // 0: any sub-vector length; otherwise the codebook entry is held in registers
 __global__ void __launch_bounds__(256) query_tables_kernel(const float* __restrict__ queries, size_t nq, int pd,
                                                            const float* __restrict__ codebooks, int m, int dsub,
                                                            int is_ip, float* __restrict__ out) {
@@ -266,9 +267,19 @@ __global__ void __launch_bounds__(256) query_tables_kernel(const float* __restri
   __syncthreads();
   const float* wv = codebooks + (size_t(j) * KSUB + e) * dsub;
   const size_t tab = size_t(m) * KSUB;
+  float wr[DSUB > 0 ? DSUB : 1];
+  if (DSUB > 0) {
+#pragma unroll
+    for (int t = 0; t < DSUB; ++t) wr[t] = __ldg(wv + t);
+  }
   for (int qi = 0; qi < 16 && q0 + qi < nq; ++qi) {
     float s = -0.0f;
-    for (int t = 0; t < dsub; ++t) s = __fadd_rn(s, __fmul_rn(sqs[qi * dsub + t], __ldg(wv + t)));
+    if (DSUB > 0) {
+#pragma unroll
+      for (int t = 0; t < DSUB; ++t) s = __fadd_rn(s, __fmul_rn(sqs[qi * DSUB + t], wr[t]));
+    } else {
+      for (int t = 0; t < dsub; ++t) s = __fadd_rn(s, __fmul_rn(sqs[qi * dsub + t], __ldg(wv + t)));
+    }
     out[(q0 + qi) * tab + size_t(j) * KSUB + e] = is_ip ? -s : __fmul_rn(-2.0f, s);
   }
 }
@@ -913,7 +924,8 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
     FV_TRY(ctx->scratch[5].reserve(nq * tab * sizeof(float)));
     qtab = ctx->scratch[5].as<float>();
     dim3 grid(unsigned((nq + 15) / 16), unsigned(ix->m));
-    fv::query_tables_kernel<<<grid, fv::KSUB, 16 * ix->dsub * sizeof(float), ctx->stream>>>(
+    auto qk = ix->dsub == 8 ? fv::query_tables_kernel<8> : (ix->dsub == 4 ? fv::query_tables_kernel<4> : fv::query_tables_kernel<0>);
+    qk<<<grid, fv::KSUB, 16 * ix->dsub * sizeof(float), ctx->stream>>>(
         q, nq, pd, ix->codebooks.as<float>(), int(ix->m), int(ix->dsub), ix->metric == FV_INNER_PRODUCT ? 1 : 0,
         ctx->scratch[5].as<float>());
     ctx->stats.launches++;
