@@ -420,8 +420,27 @@ def run_ours(args):
             want, wc = oix.search_batch(queries[:nsub], K, HNSW["ef"], threads)
             sample = f"first {nsub} of {NQ} queries, same graph (loaded from the FLHNSW01 bytes)"
         dt = time.perf_counter() - t0
-        line["cpu_baseline"] = {"value": nsub / dt, "unit": "queries/s", "cores": threads, "kind": "port",
-                                "sample": sample, "seconds": dt}
+        # the timed sample: about 10 s of CPU work (whole passes over the query batch, or a longer prefix of it for
+        # exact search); the pass above doubles as the parity check and as a rate estimate
+        est = nsub / dt
+        if args.workload == "flat":
+            nt = int(min(NQ, max(nsub, est * 10.0)))
+            t0 = time.perf_counter()
+            oix.search_batch(queries[:nt], K, threads)
+            cpu_dt, cpu_n = time.perf_counter() - t0, nt
+            sample = f"first {nt} of {NQ} queries"
+        else:
+            passes = int(max(1, min(64, round(est * 10.0 / NQ))))
+            t0 = time.perf_counter()
+            for _ in range(passes):
+                if args.workload == "ivfpq":
+                    oix.search_batch(queries, K, IVF["nprobe"], refine, threads)
+                else:
+                    oix.search_batch(queries, K, HNSW["ef"], threads)
+            cpu_dt, cpu_n = time.perf_counter() - t0, passes * NQ
+            sample = f"{passes} passes over all {NQ} queries; " + sample.split(", ", 1)[1]
+        line["cpu_baseline"] = {"value": cpu_n / cpu_dt, "unit": "queries/s", "cores": threads, "kind": "port",
+                                "sample": sample, "seconds": cpu_dt}
         same_ids = int((found[:nsub]["id"] == want["id"]).all(axis=1).sum())
         line["parity_sample"] = {"queries": nsub, "identical_id_rows": same_ids,
                                  "bit_equal_distances": bool((found[:nsub]["distance"].view(np.uint32) ==
