@@ -1228,6 +1228,66 @@ __global__ void merge_refine_kernel(const fv_neighbor* __restrict__ adc, const f
   __syncwarp();
   for (int e = lane; e < k; e += 32) out[q * size_t(k) + e] = fin[e];
 }
+
+// The same for at most 32 * NPL candidates per query, without sorted insertion: a lane keeps its share of the
+// (compressed distance, id) keys in registers, 64 bisection steps find the keep-th smallest key (ids are unique, so
+// keys are), and only the survivors' exact keys are offered to the k-long result list.  One warp per query.
+extern "C++" {
+template <int NPL>
+__global__ void __launch_bounds__(128) merge_refine_select_kernel(const fv_neighbor* __restrict__ adc,
+                                                                  const float* __restrict__ exact,
+                                                                  const uint32_t* __restrict__ part_counts, int nparts,
+                                                                  size_t nq, int keep, int k, u64* __restrict__ out) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const size_t q = blockIdx.x * size_t(blockDim.x >> 5) + w;
+  if (q >= nq) return;
+  u64* fin = reinterpret_cast<u64*>(dyn_smem()) + size_t(w) * k;
+  const int total = nparts * keep;
+  u64 key[NPL];
+  int nvalid = 0;
+#pragma unroll
+  for (int j = 0; j < NPL; ++j) {
+    const int e = j * 32 + lane;
+    key[j] = FV_EMPTY_KEY;
+    if (e < total) {
+      const int p = e / keep, i = e - p * keep;
+      const int cnt = part_counts ? int(min(part_counts[size_t(p) * nq + q], uint32_t(keep))) : keep;
+      const fv_neighbor nb = adc[(size_t(p) * nq + q) * size_t(keep) + i];
+      if (i < cnt && nb.id != 0xFFFFFFFFu) {
+        key[j] = make_key(nb.distance, nb.id);
+        nvalid++;
+      }
+    }
+  }
+  nvalid = __reduce_add_sync(FV_FULL, nvalid);
+  const int want = min(keep, nvalid);
+  u64 lo = 0, hi = FV_EMPTY_KEY - 1;  // the smallest T with at least `want` keys <= T
+  while (lo < hi) {
+    const u64 mid = lo + ((hi - lo) >> 1);
+    int c = 0;
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) c += key[j] <= mid ? 1 : 0;
+    c = __reduce_add_sync(FV_FULL, c);
+    if (c >= want) hi = mid;
+    else lo = mid + 1;
+  }
+  const u64 cut = want > 0 ? lo : 0;
+  warp_list_init(fin, k);
+  u64 b2 = FV_EMPTY_KEY;
+#pragma unroll
+  for (int j = 0; j < NPL; ++j) {
+    const int e = j * 32 + lane;
+    u64 ek = FV_EMPTY_KEY;
+    if (want > 0 && key[j] <= cut) {
+      const int p = e / keep, i = e - p * keep;
+      ek = make_key(exact[(size_t(p) * nq + q) * size_t(keep) + i], key_id(key[j]));
+    }
+    if (__any_sync(FV_FULL, ek != FV_EMPTY_KEY)) b2 = warp_list_offer(fin, k, ek, b2);
+  }
+  __syncwarp();
+  for (int e = lane; e < k; e += 32) out[q * size_t(k) + e] = fin[e];
+}
+}  // extern "C++"
 }  // namespace fv
 
 int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float* d_exact_parts,
@@ -1243,8 +1303,19 @@ int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float
   const size_t smem = (keep + k) * sizeof(u64);
   if (smem > 40 * 1024)
     FV_CUDA(cudaFuncSetAttribute(fv::merge_refine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-  fv::merge_refine_kernel<<<unsigned(nq), 32, smem, ctx->stream>>>(d_adc_parts, d_exact_parts, d_part_counts, int(nparts),
-                                                                  nq, int(keep), int(k), keys);
+  if (nparts * keep <= 1024 && k <= 256) {
+    const unsigned blocks = unsigned((nq + 3) / 4);
+    const size_t sm = 4 * k * sizeof(u64);
+    if (nparts * keep <= 256)
+      fv::merge_refine_select_kernel<8><<<blocks, 128, sm, ctx->stream>>>(d_adc_parts, d_exact_parts, d_part_counts,
+                                                                         int(nparts), nq, int(keep), int(k), keys);
+    else
+      fv::merge_refine_select_kernel<32><<<blocks, 128, sm, ctx->stream>>>(d_adc_parts, d_exact_parts, d_part_counts,
+                                                                          int(nparts), nq, int(keep), int(k), keys);
+  } else {
+    fv::merge_refine_kernel<<<unsigned(nq), 32, smem, ctx->stream>>>(d_adc_parts, d_exact_parts, d_part_counts,
+                                                                    int(nparts), nq, int(keep), int(k), keys);
+  }
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
   FV_TRY(fv::keys_to_neighbors(ctx, keys, nq, int(k), int(k), d_out, d_counts));
