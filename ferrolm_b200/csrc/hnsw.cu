@@ -146,7 +146,9 @@ __global__ void __launch_bounds__(256)
       cursor = pos + 1;
       const uint32_t c = uint32_t(ck >> 1) & 0x7FFFFFFFu;
       const uint32_t* row = g.links0 + size_t(c) * (g.m0 + 1);
-      const int cnt = int(row[0]);
+      // the first 32 links are requested together with the count: one round trip, not two
+      const uint32_t x_first = lane < g.m0 ? __ldg(row + 1 + lane) : 0u;
+      const int cnt = int(__ldg(row));
       n_exp += 1;
       for (int c0 = 0; c0 < cnt; c0 += 32) {
         const int i = c0 + lane;
@@ -154,7 +156,7 @@ __global__ void __launch_bounds__(256)
         bool fresh = false;
         uint32_t x = 0;
         if (i < cnt) {
-          x = row[1 + i];
+          x = c0 == 0 ? x_first : row[1 + i];
           fresh = visit(table, log2slots, x);
         }
         const int nfresh = __popc(__ballot_sync(FV_FULL, fresh));
