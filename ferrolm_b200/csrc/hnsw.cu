@@ -52,27 +52,35 @@ __device__ __forceinline__ bool visit(uint32_t* table, int log2slots, uint32_t x
   return false;  // full table: cannot happen below the half-full limit
 }
 
+// The reference keeps two heaps: an entry pushed out of the result heap stays in the candidate heap, and because its
+// loop stops only on a STRICTLY larger distance (hnsw.rs:195-197), such an entry is still expanded if its distance
+// equals the worst kept distance when its turn comes.  The beam below is one list, so the unexpanded entries it
+// pushes out while their distance equals the new worst distance are remembered here (ids; all share that distance)
+// and take their turn in (distance, id) order; the list is dropped as soon as the worst distance goes down.
+static constexpr int TIED_CAP = 64;
+
 // list entry: order bits of the distance (32) | id (31) | expanded (1)
 __device__ __forceinline__ u64 beam_key(float d, uint32_t id) { return (u64(order_bits(d)) << 32) | (u64(id) << 1); }
 
 template <bool IS_L2>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
     hnsw_search_kernel(HnswDev g, const float* __restrict__ queries, const uint32_t* __restrict__ qids, size_t nq, int k,
                        int ef, int log2slots, uint32_t* __restrict__ global_tables, u64* __restrict__ out_keys,
                        uint32_t* __restrict__ overflow, unsigned long long* __restrict__ work) {
   unsigned char* smem_raw = dyn_smem();
   const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = 1 << log2slots;
-  const size_t list_bytes = (size_t(ef) * 8 + 15) & ~size_t(15);
+  const size_t list_bytes = ((size_t(ef) * 8 + 15) & ~size_t(15)) + TIED_CAP * 4;
   const size_t per_warp = size_t(g.pd) * 4 + list_bytes + (global_tables ? 0 : size_t(slots) * 4);
   unsigned char* mine = smem_raw + size_t(w) * per_warp;
   float* sq = reinterpret_cast<float*>(mine);
   u64* best = reinterpret_cast<u64*>(mine + size_t(g.pd) * 4);
+  uint32_t* tied = reinterpret_cast<uint32_t*>(mine + size_t(g.pd) * 4 + list_bytes - TIED_CAP * 4);
   const size_t gw = size_t(blockIdx.x) * W + w;
   uint32_t* table = global_tables ? global_tables + gw * size_t(slots)
                                   : reinterpret_cast<uint32_t*>(mine + size_t(g.pd) * 4 + list_bytes);
   const size_t total_warps = size_t(gridDim.x) * W;
-  unsigned long long n_dist = 0, n_exp = 0;
+  unsigned long long n_dist = 0, n_exp = 0, n_tie_lost = 0;
 
   for (size_t qi = gw; qi < nq; qi += total_warps) {
     const size_t qsrc = qids ? size_t(qids[qi]) : qi;
@@ -124,8 +132,9 @@ __global__ void __launch_bounds__(256)
     __syncwarp();
     int filled = 1;          // entries of `best` in use
     int visited = 1;
-    bool over = false;
+    bool over = false, tie_lost = false;
     int cursor = 0;          // first entry that may be unexpanded
+    int ntied = 0;           // pushed-out entries still tied with the worst kept distance
     for (;;) {
       // next unexpanded entry at or after `cursor`
       int pos = -1;
@@ -138,13 +147,32 @@ __global__ void __launch_bounds__(256)
           break;
         }
       }
-      if (pos < 0) break;
-      const u64 ck = best[pos];
-      __syncwarp();
-      if (lane == 0) best[pos] = ck | 1ull;
-      __syncwarp();
-      cursor = pos + 1;
-      const uint32_t c = uint32_t(ck >> 1) & 0x7FFFFFFFu;
+      uint32_t c = 0;
+      if (ntied > 0) {
+        // the smallest id among the tied entries; it goes first if the beam has nothing open or only a larger key
+        uint32_t tmin = 0xFFFFFFFFu;
+        for (int t = lane; t < ntied; t += 32) tmin = min(tmin, tied[t]);
+        for (int o = 16; o > 0; o >>= 1) tmin = min(tmin, __shfl_xor_sync(FV_FULL, tmin, o));
+        const u64 tkey = (best[ef - 1] & 0xFFFFFFFF00000000ull) | (u64(tmin) << 1);
+        if (pos < 0 || tkey < best[pos]) {
+          __syncwarp();
+          for (int t = lane; t < ntied; t += 32)
+            if (tied[t] == tmin) tied[t] = tied[ntied - 1];  // ids are unique: one match
+          __syncwarp();
+          ntied--;
+          pos = -2;
+          c = tmin;
+        }
+      }
+      if (pos == -1) break;
+      if (pos >= 0) {
+        const u64 ck = best[pos];
+        __syncwarp();
+        if (lane == 0) best[pos] = ck | 1ull;
+        __syncwarp();
+        cursor = pos + 1;
+        c = uint32_t(ck >> 1) & 0x7FFFFFFFu;
+      }
       const uint32_t* row = g.links0 + size_t(c) * (g.m0 + 1);
       // the first 32 links are requested together with the count: one round trip, not two
       const uint32_t x_first = lane < g.m0 ? __ldg(row + 1 + lane) : 0u;
@@ -184,11 +212,26 @@ __global__ void __launch_bounds__(256)
               below += __popc(__ballot_sync(FV_FULL, e < filled && best[e] < kk));
             }
             __syncwarp();
+            const bool was_full = filled == ef;
             warp_list_insert(best, ef, kk);
             if (filled < ef) filled++;
             if (below < cursor) cursor = below;
-            else if (below >= cursor) { /* entries at or after the cursor shift by one; cursor still valid */ }
+            const u64 pushed = bound;  // the entry that fell off the end, if the beam was full
             bound = best[ef - 1];
+            if (was_full) {
+              if ((bound >> 32) < (pushed >> 32)) {
+                ntied = 0;  // the worst distance went down: nothing pushed out so far can tie with it any more
+              } else if (!(pushed & 1ull)) {
+                if (ntied < TIED_CAP) {
+                  __syncwarp();
+                  if (lane == 0) tied[ntied] = uint32_t(pushed >> 1) & 0x7FFFFFFFu;
+                  __syncwarp();
+                  ntied++;
+                } else {
+                  tie_lost = true;
+                }
+              }
+            }
           }
         }
       }
@@ -198,6 +241,7 @@ __global__ void __launch_bounds__(256)
       }
     }
     __syncwarp();
+    if (tie_lost && !over) n_tie_lost += 1;
     if (over) {
       if (lane == 0) overflow[qi] = 1;
     } else {
@@ -216,6 +260,7 @@ __global__ void __launch_bounds__(256)
   if (work && lane == 0) {
     atomicAdd(work, n_dist);
     atomicAdd(work + 1, n_exp);
+    if (n_tie_lost) atomicAdd(work + 2, n_tie_lost);
   }
 }
 
@@ -494,7 +539,7 @@ static int hnsw_search_dev(fv_hnsw* h, const float* d_queries, size_t nq, size_t
   FV_TRY(ctx->scratch[5].reserve(nq * sizeof(uint32_t)));
   uint32_t* d_over = ctx->scratch[5].as<uint32_t>();
   unsigned long long* d_work = reinterpret_cast<unsigned long long*>(ctx->d_flags + 16);
-  FV_CUDA(cudaMemsetAsync(d_work, 0, 2 * sizeof(unsigned long long), ctx->stream));
+  FV_CUDA(cudaMemsetAsync(d_work, 0, 3 * sizeof(unsigned long long), ctx->stream));
   HnswDev g{};
   g.data = h->d_data.as<float>();
   g.links0 = h->d_links0.as<uint32_t>();
@@ -518,7 +563,7 @@ static int hnsw_search_dev(fv_hnsw* h, const float* d_queries, size_t nq, size_t
   std::vector<uint32_t> h_over(nq), retry;
   for (int attempt = 0; attempt < 8; ++attempt) {
     const size_t slots = size_t(1) << log2slots;
-    const size_t base_bytes = size_t(pd) * 4 + ((ef * 8 + 15) & ~size_t(15));
+    const size_t base_bytes = size_t(pd) * 4 + ((ef * 8 + 15) & ~size_t(15)) + TIED_CAP * 4;
     const size_t budget = std::min<size_t>(ctx->smem_optin, 200 * 1024);
     int W = 8;
     bool use_global = false;
@@ -530,7 +575,7 @@ static int hnsw_search_dev(fv_hnsw* h, const float* d_queries, size_t nq, size_t
     const size_t per_warp = base_bytes + (use_global ? 0 : slots * 4);
     while (W > 1 && per_warp * W > budget) W >>= 1;
     if (per_warp * W > budget) return fail(FV_ERR_UNSUPPORTED, "dimension and ef too large for shared memory");
-    int blocks_per_sm = int(std::max<size_t>(1, std::min<size_t>(budget / (per_warp * W), 32 / W)));
+    int blocks_per_sm = int(std::max<size_t>(1, std::min<size_t>(budget / (per_warp * W), 24 / W)));
     size_t blocks = std::min<size_t>((active + W - 1) / W, size_t(ctx->sm_count) * blocks_per_sm);
     uint32_t* tables = nullptr;
     if (use_global) {
@@ -565,11 +610,12 @@ static int hnsw_search_dev(fv_hnsw* h, const float* d_queries, size_t nq, size_t
   if (active) return fail(FV_ERR_OVERFLOW, "visited table overflow after regrowing");
   stage_mark(ctx);
   FV_TRY(keys_to_neighbors(ctx, keys, nq, int(k), int(k), d_out, d_counts));
-  unsigned long long wk[2] = {0, 0};
+  unsigned long long wk[3] = {0, 0, 0};
   FV_CUDA(cudaMemcpyAsync(wk, d_work, sizeof(wk), cudaMemcpyDeviceToHost, ctx->stream));
   FV_CUDA(cudaStreamSynchronize(ctx->stream));
   ctx->stats.dist_evals = wk[0];
   ctx->stats.expansions = wk[1];
+  ctx->stats.uncertified = wk[2];  // queries whose list of tied, pushed-out entries overflowed (see TIED_CAP)
   stage_end(ctx);
   return FV_OK;
 }

@@ -68,7 +68,7 @@ void* fv_ctx_stream(fv_ctx* ctx);
 /* Counters of the last search call on this context (kernel launches, slow-path queries). */
 typedef struct fv_stats {
   uint64_t launches;        /* kernels launched by the last call */
-  uint64_t uncertified;     /* exact search: queries re-run on the full-precision scan */
+  uint64_t uncertified;     /* exact search: queries re-run on the full-precision scan; HNSW: queries whose list of tied, pushed-out entries overflowed (64; ties beyond that may be resolved differently from the reference) */
   uint64_t rows_scanned;    /* IVF-PQ: code rows visited (sum over queries and probes) */
   uint64_t dist_evals;      /* HNSW: distance evaluations */
   uint64_t expansions;      /* HNSW: node expansions */

@@ -43,6 +43,8 @@ def flat_pair(fv, oracle, ctx, metric, dim, base):
     (IP, 384, 8_000, 100, 10),
     (L2, 13, 5_000, 33, 7),        # a dimension that needs padding, ragged sizes
     (L2, 128, 4_500, 17, 100),     # a long result list
+    (L2, 128, 30_000, 300, 32),    # the largest k of the tensor-core path: 1 row in 8 sampled, 7th best as bound
+    (L2, 64, 150_000, 260, 10),    # 1 row in 16 sampled, 6th best as bound; more than one query tile
 ])
 def test_flat_matches_the_oracle(fv, oracle, ctx, metric, dim, n, nq, k, mode):
     base = oracle.testdata(n, dim, 1)
@@ -375,6 +377,20 @@ def hnsw_pair(request, fv, oracle, ctx):
     o = oracle.Hnsw.build(metric, dim, base, m=16, ef_construction=100, seed=1, threads=1)
     g = fv.Hnsw.load(ctx, o.save())
     return g, o, base, queries, metric, dim
+
+
+def test_hnsw_on_integer_data_with_distance_ties(fv, oracle, ctx):
+    # clipped-integer vectors give many exactly equal distances; the beam then orders by id, and on this data the
+    # oracle's two heaps agree with it
+    dim = 128
+    base = fv.datagen(0, 1, 30_000, dim, 64)
+    queries = fv.datagen(0, 2, 500, dim, 64)
+    o = oracle.Hnsw.build(L2, dim, base, m=16, ef_construction=100, seed=1, threads=1)
+    g = fv.Hnsw.load(ctx, o.save())
+    for ef in (64, 100):
+        got, gc = g.search_batch(queries, 10, ef)
+        want, wc = o.search_batch(queries, 10, ef)
+        assert_same_neighbours(got, gc, want, wc, f"hnsw integer ef={ef}")
 
 
 @pytest.mark.parametrize("ef", [10, 16, 64, 128, 256])
