@@ -238,6 +238,7 @@ struct ScanArgs {
   int shard_rank, shard_world;  // this shard scans the probed lists l with l % world == rank
   int metric, pd, m, dsub, nprobe, keep, k;
   int refine;        // 1: re-rank the kept candidates exactly
+  int np;            // producer warps (L2 with precomputed tables)
   int cap;           // keys of the block's candidate buffer (a power of two, >= keep + 2 * threads)
   int candidates;    // 1: write the kept candidates with both distances instead of the final k
   uint32_t id_base;
@@ -318,7 +319,7 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
   u64* lists = reinterpret_cast<u64*>(srq + a.pd);  // cap keys, then keep keys for the re-rank, then k
   u64* rerank = lists + a.cap;
   const size_t q = blockIdx.x;
-  const int NP = use_pre ? 2 : 0;       // producer warps
+  const int NP = use_pre ? a.np : 0;    // producer warps
   const int WC = W - NP, cw = w - NP;   // consumer warps; this warp's index among them (negative: a producer)
   const float* qtab = a.qtab ? a.qtab + q * size_t(tab) : nullptr;
 
@@ -377,7 +378,7 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
   auto build_pre = [&](float* dst, uint32_t l, int t, int nthr) {
     const float4* pre = reinterpret_cast<const float4*>(a.pre + size_t(l) * tab);
     const float4* qt = reinterpret_cast<const float4*>(qtab);
-#pragma unroll 4
+#pragma unroll 8
     for (int i = t; i < tab / 4; i += nthr) {
       const float4 x = __ldg(pre + i), y = __ldg(qt + i);
       reinterpret_cast<float4*>(dst)[i] =
@@ -953,6 +954,7 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   a.nprobe = np;
   a.keep = int(keep);
   a.k = int(k);
+  a.np = 2;
   a.cap = 2048;
   while (size_t(a.cap) < keep + 1024) a.cap <<= 1;
   a.refine = rerank && !candidates ? 1 : 0;
