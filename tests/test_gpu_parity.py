@@ -78,6 +78,39 @@ def test_flat_on_integer_data_with_ties(fv, oracle, ctx, mode):
     assert got.tobytes() == want.tobytes()
 
 
+@pytest.mark.parametrize("case", ["beyond fp16", "norms beyond 2^30", "norm scale grows between adds", "tiny"])
+def test_flat_tensor_core_path_over_value_ranges(fv, oracle, ctx, case):
+    # The tensor-core front end stores a 16-bit copy (fp16, or bf16 when the values or the squared norms leave the
+    # fp16 range) and adds the norms as scaled 16-bit pieces; whatever the range, the certified result is exact.
+    dim, n, nq, k = 64, 9_000, 96, 10
+    base = oracle.testdata(n, dim, 21)
+    queries = oracle.testdata(nq, dim, 22)
+    batches = [base]
+    if case == "beyond fp16":
+        base, queries = base * 1.0e5, queries * 1.0e5
+        batches = [base]
+    elif case == "norms beyond 2^30":
+        base, queries = base * 2.5e3, queries * 2.5e3  # values stay below 32768, squared norms reach 6e9
+        batches = [base]
+    elif case == "norm scale grows between adds":
+        base = base.copy()
+        base[n // 2:] *= 900.0  # the second batch's norms are ~1e6 times the first's: the pieces are re-split
+        batches = [base[: n // 2], base[n // 2:]]
+    else:
+        base, queries = base * 1.0e-4, queries * 1.0e-4
+        batches = [base]
+    g = fv.FlatIndex(ctx, L2, dim)
+    o = oracle.FlatIndex(L2, dim)
+    for b in batches:
+        g.add(np.ascontiguousarray(b))
+        o.add(np.ascontiguousarray(b))
+    g.set_mode(1)
+    got, gc = g.search_batch(np.ascontiguousarray(queries), k)
+    want, wc = o.search_batch(np.ascontiguousarray(queries), k)
+    eq, total = assert_same_neighbours(got, gc, want, wc, f"flat, {case}")
+    assert eq == total
+
+
 def test_flat_edge_cases(fv, oracle, ctx):
     dim = 16
     base = oracle.testdata(37, dim, 3)
