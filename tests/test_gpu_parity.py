@@ -227,6 +227,17 @@ def test_ivfpq_search_matches_the_oracle(fv, oracle, ivfpq_pair, nprobe, refine)
     assert g.ctx.stats()["rows_scanned"] == rows
 
 
+@pytest.mark.parametrize("k,nprobe,refine", [(50, 32, 40), (300, 64, 0), (7, 64, 300)])
+def test_ivfpq_long_candidate_lists(fv, oracle, ivfpq_pair, k, nprobe, refine):
+    # k * refine up to 2,100 kept candidates: the block's candidate buffer is compacted many times per query, and
+    # lists longer than one piece of the scan are cut at the buffer's capacity
+    g, o, base, queries = ivfpq_pair
+    got, gc = g.search_batch(queries[:60], k, nprobe, refine)
+    want, wc = o.search_batch(queries[:60], k, nprobe, refine)
+    eq, total = assert_same_neighbours(got, gc, want, wc, f"ivfpq k={k} nprobe={nprobe} refine={refine}")
+    assert eq == total
+
+
 def test_ivfpq_recall_grows_with_probes_and_reranking(fv, oracle, ivfpq_pair):
     # the reference's own assertion (tests/vector.rs:86-92), on the GPU results
     g, _, base, queries = ivfpq_pair
