@@ -354,7 +354,7 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
   // ends a piece ORs "seen >= compact_at" over the block, so all threads agree on compacting without reading the
   // counter while others may already be appending again.  `cnt_ub` bounds the count from above for sizing a piece.
   const int compact_at = min(a.cap - chunk_rows, 2 * a.keep + 64);
-  int seen = 0, cnt_ub = 0;
+  int seen = 0, cnt_ub = 0, rows_seen = 0;
   auto piece_barrier = [&]() {
     if (__syncthreads_or(seen >= compact_at)) {
       cnt_ub = compact();
@@ -430,7 +430,9 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
     for (int done = 0; done < len || done == 0;) {
       const u64 eff = bound;
       const uint32_t eff_hi = uint32_t(eff >> 32);
-      const int piece = ((a.cap - cnt_ub) / chunk_rows) * chunk_rows;
+      // The first pieces of a query are short (two steps, then as many rows as were scanned so far): until a bound
+      // exists every row is appended, so it pays to sort a few hundred keys early and scan the rest against a bound.
+      const int piece = min(((a.cap - cnt_ub) / chunk_rows) * chunk_rows, max(2 * chunk_rows, rows_seen));
       const int end = min(len, done + piece);
       if (cw >= 0) {
         // R rows per lane and step: their 16-step add chains are independent and interleave
@@ -495,6 +497,7 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
           }
         }
       }
+      rows_seen += end - done;
       done = end;
       piece_barrier();
       if (len == 0) break;
