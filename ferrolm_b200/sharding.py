@@ -7,7 +7,7 @@ from __future__ import annotations
 
 
 def row_range(rank: int, world: int, n: int) -> tuple[int, int]:
-    """Contiguous rows [lo, hi) of rank `rank`: local row + lo is the global id (SURVEY 8e layout)."""
+    """Contiguous rows [lo, hi) of rank `rank`: local row + lo is the global id."""
     per = (n + world - 1) // world
     lo = min(n, rank * per)
     return lo, min(n, lo + per)
