@@ -48,8 +48,9 @@ class ShardedSearch:
             return ix.search_batch(queries, k, nprobe, refine)
         if refine > 0:
             # a shard may not cut to k on its own: the global cut by compressed distance comes first
-            adc, exact, counts = ix.search_candidates(queries, k * refine, nprobe)
+            # (unused candidate slots carry the id 0xFFFFFFFF, so the per-shard counts need not travel)
+            adc, exact, _ = ix.search_candidates(queries, k * refine, nprobe)
             return self.ctx.merge_refine(all_gather_stacked(adc, self.world), all_gather_stacked(exact, self.world),
-                                         all_gather_stacked(counts, self.world), k)
+                                         None, k)
         out, counts = ix.search_batch(queries, k, nprobe, 0)
         return self.ctx.merge_topk(all_gather_stacked(out, self.world), all_gather_stacked(counts, self.world), k)

@@ -403,6 +403,9 @@ def test_ivfpq_sharded_by_list(fv, oracle, ctx, refine):
     assert total == n and scanned == rows
     if refine:
         merged, mc = ctx.merge_refine(*(torch.stack([p[i] for p in parts]) for i in range(3)), k)
+        # the counts are optional: unused candidate slots are marked by their id
+        m2, c2 = ctx.merge_refine(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]), None, k)
+        assert torch.equal(m2, merged) and torch.equal(c2, mc)
     else:
         merged, mc = ctx.merge_topk(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]), k)
     eq, tot = assert_same_neighbours(fv.neighbors_from_tensor(merged), mc.cpu().numpy(), want, wc, "list shards")
