@@ -92,6 +92,10 @@ SIGNATURES = {
     "fv_ivfpq_set_id_base": (_i, [_vp, _u32]),
     "fv_ivfpq_set_shard": (_i, [_vp, _i, _i]),
     "fv_ivfpq_search_candidates_dev": (_i, [_vp, _vp, _sz, _sz, _sz, _vp, _vp, _vp]),
+    "fv_ivfpq_nlist": (_sz, [_vp]),
+    "fv_ivfpq_coarse_dev": (_i, [_vp, _vp, _sz, _sz, _vp]),
+    "fv_ivfpq_search_batch_cells_dev": (_i, [_vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp, _vp]),
+    "fv_ivfpq_search_candidates_cells_dev": (_i, [_vp, _vp, _sz, _sz, _sz, _vp, _vp, _vp, _vp]),
     "fv_ivfpq_save_size": (_sz, [_vp]),
     "fv_ivfpq_save": (_i, [_vp, _vp, _sz, C.POINTER(_sz)]),
     "fv_ivfpq_load": (_i, [_vp, _vp, _sz, _pp]),

@@ -887,8 +887,11 @@ int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n) { return ivfpq_ad
 int fv_ivfpq_add_dev(fv_ivfpq* ix, const float* d_vectors, size_t n) { return ivfpq_add_impl(ix, d_vectors, n, true); }
 
 // scratch slots: 0 padded queries, 1 final keys, 2 scan partials, 4 cells, 5 per-query tables (after the coarse search is done with it)
+// `cells_in`: the probed cells of every query if the caller already has them (nq x min(nprobe, nlist) keys from
+// fv_ivfpq_coarse_dev), else null.  `cells_only`: stop after the coarse search and leave the keys there.
 static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,
-                             bool candidates, fv_neighbor* d_out, uint32_t* d_counts, fv_neighbor* d_adc, float* d_exact) {
+                             bool candidates, fv_neighbor* d_out, uint32_t* d_counts, fv_neighbor* d_adc, float* d_exact,
+                             const uint64_t* cells_in = nullptr, uint64_t* cells_only = nullptr) {
   fv_ctx* ctx = ix->ctx;
   if (k == 0) return fv::fail(FV_ERR_ARG, "k must be at least 1");
   if (nprobe == 0) return fv::fail(FV_ERR_ARG, "nprobe must be at least 1");
@@ -909,15 +912,27 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
     q = ctx->scratch[0].as<float>();
   }
   const int np = int(std::min(nprobe, ix->nlist));
-  FV_TRY(ctx->scratch[4].reserve(nq * size_t(np) * sizeof(u64)));
-  u64* cells = ctx->scratch[4].as<u64>();
-  // ivfpq.rs:211-220: every cell is pushed, no pre-filter
-  if (nq >= 256 && fv::tc_usable(ix->ctc, ix->nlist, nq, np))
-    FV_TRY(fv::tc_search(ctx, ix->ctc, ix->metric, ix->centroids.as<float>(), ix->nlist, pd, q, nq, np, 0, cells, false));
-  else
-    FV_TRY(fv::exact_scan(ctx, ix->metric, ix->centroids.as<float>(), ix->nlist, pd, q, size_t(pd), nullptr, nq, np,
-                          false, 0, cells, 2));
+  const u64* cells = reinterpret_cast<const u64*>(cells_in);
+  if (!cells_in) {
+    u64* dst = reinterpret_cast<u64*>(cells_only);
+    if (!dst) {
+      FV_TRY(ctx->scratch[4].reserve(nq * size_t(np) * sizeof(u64)));
+      dst = ctx->scratch[4].as<u64>();
+    }
+    // ivfpq.rs:211-220: every cell is pushed, no pre-filter
+    if (nq >= 256 && fv::tc_usable(ix->ctc, ix->nlist, nq, np))
+      FV_TRY(fv::tc_search(ctx, ix->ctc, ix->metric, ix->centroids.as<float>(), ix->nlist, pd, q, nq, np, 0, dst, false));
+    else
+      FV_TRY(fv::exact_scan(ctx, ix->metric, ix->centroids.as<float>(), ix->nlist, pd, q, size_t(pd), nullptr, nq, np,
+                            false, 0, dst, 2));
+    cells = dst;
+  }
   fv::stage_mark(ctx);
+  if (cells_only) {
+    FV_CUDA(cudaStreamSynchronize(ctx->stream));
+    fv::stage_end(ctx);
+    return FV_OK;
+  }
   FV_TRY(ctx->scratch[1].reserve(nq * kout * sizeof(u64)));
   unsigned long long* d_rows = reinterpret_cast<unsigned long long*>(ctx->d_flags + 16);
   FV_CUDA(cudaMemsetAsync(d_rows, 0, sizeof(unsigned long long), ctx->stream));
@@ -992,6 +1007,31 @@ int fv_ivfpq_search_batch_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, s
   if (!ix || (nq && (!d_queries || !d_out))) return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_batch: null argument");
   fv::DeviceGuard g(ix->ctx->device);
   return ivfpq_search_impl(ix, d_queries, nq, k, nprobe, refine, false, d_out, d_counts, nullptr, nullptr);
+}
+
+size_t fv_ivfpq_nlist(const fv_ivfpq* ix) { return ix ? ix->nlist : 0; }
+
+int fv_ivfpq_coarse_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t nprobe, uint64_t* d_cells) {
+  if (!ix || (nq && (!d_queries || !d_cells))) return fv::fail(FV_ERR_ARG, "fv_ivfpq_coarse: null argument");
+  fv::DeviceGuard g(ix->ctx->device);
+  return ivfpq_search_impl(ix, d_queries, nq, 1, nprobe, 0, false, nullptr, nullptr, nullptr, nullptr, nullptr, d_cells);
+}
+
+int fv_ivfpq_search_batch_cells_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe,
+                                    size_t refine, const uint64_t* d_cells, fv_neighbor* d_out, uint32_t* d_counts) {
+  if (!ix || (nq && (!d_queries || !d_out || !d_cells)))
+    return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_batch_cells: null argument");
+  fv::DeviceGuard g(ix->ctx->device);
+  return ivfpq_search_impl(ix, d_queries, nq, k, nprobe, refine, false, d_out, d_counts, nullptr, nullptr, d_cells);
+}
+
+int fv_ivfpq_search_candidates_cells_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t keep, size_t nprobe,
+                                         const uint64_t* d_cells, fv_neighbor* d_adc, float* d_exact,
+                                         uint32_t* d_counts) {
+  if (!ix || (nq && (!d_queries || !d_adc || !d_exact || !d_counts || !d_cells)))
+    return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_candidates_cells: null argument");
+  fv::DeviceGuard g(ix->ctx->device);
+  return ivfpq_search_impl(ix, d_queries, nq, keep, nprobe, 1, true, nullptr, d_counts, d_adc, d_exact, d_cells);
 }
 
 int fv_ivfpq_search_candidates_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t keep, size_t nprobe,

@@ -46,11 +46,33 @@ class ShardedSearch:
             return self.ctx.merge_topk(all_gather_stacked(out, self.world), all_gather_stacked(counts, self.world), k)
         if self.world == 1:
             return ix.search_batch(queries, k, nprobe, refine)
+        cells = self._coarse_by_query_slices(queries, nprobe)
         if refine > 0:
             # a shard may not cut to k on its own: the global cut by compressed distance comes first
             # (unused candidate slots carry the id 0xFFFFFFFF, so the per-shard counts need not travel)
-            adc, exact, _ = ix.search_candidates(queries, k * refine, nprobe)
+            adc, exact, _ = ix.search_candidates(queries, k * refine, nprobe, cells)
             return self.ctx.merge_refine(all_gather_stacked(adc, self.world), all_gather_stacked(exact, self.world),
                                          None, k)
-        out, counts = ix.search_batch(queries, k, nprobe, 0)
+        out, counts = ix.search_batch(queries, k, nprobe, 0, cells)
         return self.ctx.merge_topk(all_gather_stacked(out, self.world), all_gather_stacked(counts, self.world), k)
+
+    def _coarse_by_query_slices(self, queries, nprobe: int):
+        """Every list shard needs the probed cells of ALL queries; instead of each shard repeating the whole coarse
+        search, rank r computes the cells of query slice r and the slices are all-gathered.  None (= let the search
+        do its own coarse step) for host arrays and for batches too small to be worth an exchange."""
+        import torch
+
+        if not (hasattr(queries, "is_cuda") and queries.is_cuda):
+            return None
+        q = queries.contiguous().view(-1, self.index.dim)
+        nq = q.shape[0]
+        if nq < 256 * self.world:
+            return None
+        rank = torch.distributed.get_rank()
+        per = (nq + self.world - 1) // self.world
+        lo, hi = row_range(rank, self.world, nq)
+        mine = self.index.coarse(q[lo:hi], nprobe)
+        if hi - lo < per:  # the last slice may be short: pad so that all ranks send the same amount
+            pad = torch.full((per - (hi - lo), mine.shape[1]), -1, dtype=mine.dtype, device=mine.device)
+            mine = torch.cat([mine, pad])
+        return all_gather_stacked(mine, self.world).view(self.world * per, -1)[:nq].contiguous()

@@ -304,11 +304,36 @@ class IvfPq:
         out, counts = self.search_batch(_host_f32(query).reshape(1, self.dim), k, nprobe, refine)
         return out[0, : counts[0]]
 
-    def search_batch(self, queries, k: int, nprobe: int, refine: int):
+    def search_batch(self, queries, k: int, nprobe: int, refine: int, cells=None):
+        """`cells`: the keys `coarse` returned for these queries (CUDA tensors only), to skip the coarse step."""
+        if cells is not None:
+            import torch
+
+            q = queries.contiguous().view(-1, self.dim)
+            nq = q.shape[0]
+            assert cells.is_cuda and cells.dtype == torch.int64 and cells.is_contiguous() and cells.shape[0] == nq
+            out = torch.empty((nq, k, 2), dtype=torch.int32, device=q.device)
+            counts = torch.empty((nq,), dtype=torch.int32, device=q.device)
+            torch.cuda.current_stream(q.device).synchronize()
+            check(lib().fv_ivfpq_search_batch_cells_dev(self._h, q.data_ptr(), nq, k, nprobe, refine, cells.data_ptr(),
+                                                        out.data_ptr(), counts.data_ptr()))
+            return out, counts
         return _search(lib().fv_ivfpq_search_batch, self._h, queries, self.dim, k, (nprobe, refine),
                        lib().fv_ivfpq_search_batch_dev)
 
-    def search_candidates(self, queries, keep: int, nprobe: int):
+    def coarse(self, queries, nprobe: int):
+        """The probed cells of every query (CUDA tensor in, (nq, min(nprobe, nlist)) int64 keys out): the coarse step
+        of a search on its own, so that list shards can split it by queries and exchange the keys."""
+        import torch
+
+        q = queries.contiguous().view(-1, self.dim)
+        nq = q.shape[0]
+        cells = torch.empty((nq, min(nprobe, lib().fv_ivfpq_nlist(self._h))), dtype=torch.int64, device=q.device)
+        torch.cuda.current_stream(q.device).synchronize()
+        check(lib().fv_ivfpq_coarse_dev(self._h, q.data_ptr(), nq, nprobe, cells.data_ptr()))
+        return cells
+
+    def search_candidates(self, queries, keep: int, nprobe: int, cells=None):
         """Per-shard half of a re-ranked search: best `keep` by compressed distance plus exact distances."""
         import torch
 
@@ -318,8 +343,13 @@ class IvfPq:
         exact = torch.empty((nq, keep), dtype=torch.float32, device=q.device)
         counts = torch.empty((nq,), dtype=torch.int32, device=q.device)
         torch.cuda.current_stream(q.device).synchronize()
-        check(lib().fv_ivfpq_search_candidates_dev(self._h, q.data_ptr(), nq, keep, nprobe, adc.data_ptr(),
-                                                   exact.data_ptr(), counts.data_ptr()))
+        if cells is not None:
+            assert cells.is_cuda and cells.dtype == torch.int64 and cells.is_contiguous() and cells.shape[0] == nq
+            check(lib().fv_ivfpq_search_candidates_cells_dev(self._h, q.data_ptr(), nq, keep, nprobe, cells.data_ptr(),
+                                                             adc.data_ptr(), exact.data_ptr(), counts.data_ptr()))
+        else:
+            check(lib().fv_ivfpq_search_candidates_dev(self._h, q.data_ptr(), nq, keep, nprobe, adc.data_ptr(),
+                                                       exact.data_ptr(), counts.data_ptr()))
         return adc, exact, counts
 
     def save(self) -> bytes:

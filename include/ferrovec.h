@@ -120,6 +120,7 @@ int fv_ivfpq_add(fv_ivfpq* ix, const float* vectors, size_t n);                 
 int fv_ivfpq_add_dev(fv_ivfpq* ix, const float* d_vectors, size_t n);
 size_t fv_ivfpq_len(const fv_ivfpq* ix);                                              /* len   :128 */
 size_t fv_ivfpq_bytes_per_vector(const fv_ivfpq* ix);                                 /* bytes_per_vector :137 */
+size_t fv_ivfpq_nlist(const fv_ivfpq* ix);                                            /* field nlist :33 */
 int fv_ivfpq_search(fv_ivfpq* ix, const float* query, size_t k, size_t nprobe, size_t refine,
                     fv_neighbor* out, uint32_t* count);                               /* search :225 */
 int fv_ivfpq_search_batch(fv_ivfpq* ix, const float* queries, size_t nq, size_t k, size_t nprobe, size_t refine,
@@ -137,6 +138,17 @@ int fv_ivfpq_set_id_base(fv_ivfpq* ix, uint32_t id_base);
 int fv_ivfpq_set_shard(fv_ivfpq* ix, int rank, int world);
 int fv_ivfpq_search_candidates_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t keep, size_t nprobe,
                                    fv_neighbor* d_adc, float* d_exact, uint32_t* d_counts);
+/* The coarse step on its own (the cell list of search, ivfpq.rs:211-220): for every query the min(nprobe, nlist)
+ * nearest cells as keys (order-preserving bits of the f32 distance in the high word, cell number in the low word),
+ * ascending, nq x min(nprobe, nlist) keys.  The `_cells` searches take such keys instead of computing them.  With
+ * list shards every shard would otherwise repeat the same coarse step for the whole batch: each shard computes
+ * the keys of a slice of the queries, the slices are all-gathered, every shard searches with the full set. */
+int fv_ivfpq_coarse_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t nprobe, uint64_t* d_cells);
+int fv_ivfpq_search_batch_cells_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe,
+                                    size_t refine, const uint64_t* d_cells, fv_neighbor* d_out, uint32_t* d_counts);
+int fv_ivfpq_search_candidates_cells_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t keep, size_t nprobe,
+                                         const uint64_t* d_cells, fv_neighbor* d_adc, float* d_exact,
+                                         uint32_t* d_counts);
 size_t fv_ivfpq_save_size(const fv_ivfpq* ix);
 int fv_ivfpq_save(const fv_ivfpq* ix, uint8_t* buf, size_t cap, size_t* written);      /* save :332 ("FLIVFPQ1") */
 int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out);      /* load :354 */

@@ -238,6 +238,27 @@ def test_ivfpq_long_candidate_lists(fv, oracle, ivfpq_pair, k, nprobe, refine):
     assert eq == total
 
 
+@pytest.mark.parametrize("nprobe,refine", [(8, 0), (40, 5)])
+def test_ivfpq_coarse_step_on_its_own(fv, oracle, ivfpq_pair, nprobe, refine):
+    # the probed cells computed apart (in two query slices, as list shards do) give the same search
+    import torch
+
+    g, o, base, queries = ivfpq_pair
+    dq = torch.from_numpy(queries).cuda()
+    cells = torch.cat([g.coarse(dq[:77], nprobe), g.coarse(dq[77:], nprobe)])
+    assert cells.shape == (len(queries), nprobe) and torch.equal(cells, g.coarse(dq, nprobe))
+    assert bool((cells[:, 1:] > cells[:, :-1]).all())  # ascending (distance, cell) keys
+    got, gc = g.search_batch(dq, 10, nprobe, refine, cells)
+    want, wc = g.search_batch(dq, 10, nprobe, refine)
+    assert torch.equal(got, want) and torch.equal(gc, wc)
+    if refine:
+        a1, e1, c1 = g.search_candidates(dq, 10 * refine, nprobe, cells)
+        a2, e2, c2 = g.search_candidates(dq, 10 * refine, nprobe)
+        assert torch.equal(a1, a2) and torch.equal(e1.view(torch.int32), e2.view(torch.int32)) and torch.equal(c1, c2)
+    ow, owc = o.search_batch(queries, 10, nprobe, refine)
+    assert_same_neighbours(fv.neighbors_from_tensor(got), gc.cpu().numpy(), ow, owc, "given cells")
+
+
 def test_ivfpq_recall_grows_with_probes_and_reranking(fv, oracle, ivfpq_pair):
     # the reference's own assertion (tests/vector.rs:86-92), on the GPU results
     g, _, base, queries = ivfpq_pair
