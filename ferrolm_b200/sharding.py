@@ -60,19 +60,25 @@ class ShardedSearch:
         """Every list shard needs the probed cells of ALL queries; instead of each shard repeating the whole coarse
         search, rank r computes the cells of query slice r and the slices are all-gathered.  None (= let the search
         do its own coarse step) for host arrays and for batches too small to be worth an exchange."""
-        import torch
-
         if not (hasattr(queries, "is_cuda") and queries.is_cuda):
             return None
         q = queries.contiguous().view(-1, self.index.dim)
-        nq = q.shape[0]
-        if nq < 256 * self.world:
+        if q.shape[0] < 256 * self.world:
             return None
-        rank = torch.distributed.get_rank()
-        per = (nq + self.world - 1) // self.world
-        lo, hi = row_range(rank, self.world, nq)
-        mine = self.index.coarse(q[lo:hi], nprobe)
-        if hi - lo < per:  # the last slice may be short: pad so that all ranks send the same amount
-            pad = torch.full((per - (hi - lo), mine.shape[1]), -1, dtype=mine.dtype, device=mine.device)
-            mine = torch.cat([mine, pad])
-        return all_gather_stacked(mine, self.world).view(self.world * per, -1)[:nq].contiguous()
+        return per_query_slices(lambda part: self.index.coarse(part, nprobe), q, self.world)
+
+
+def per_query_slices(compute, queries, world: int):
+    """`compute(queries[lo:hi])` on this rank's contiguous slice of the query rows, all-gathered: returns what
+    `compute(queries)` would, with every rank doing 1/world of the work.  `compute` maps (n, d) -> (n, w) rows."""
+    import torch
+    import torch.distributed as dist
+
+    nq = queries.shape[0]
+    per = (nq + world - 1) // world
+    lo, hi = row_range(dist.get_rank(), world, nq)
+    mine = compute(queries[lo:hi])
+    if hi - lo < per:  # the last slices may be short: pad so that all ranks send the same amount
+        pad = torch.zeros((per - (hi - lo), mine.shape[1]), dtype=mine.dtype, device=mine.device)
+        mine = torch.cat([mine, pad])
+    return all_gather_stacked(mine, world).view(world * per, -1)[:nq].contiguous()

@@ -73,6 +73,20 @@ def _worker(rank, world, port, tmp):
         cand.sort()
         kept = sorted((c[2], c[1]) for c in cand[: k * refine])[:k]
         assert [c[1] for c in kept] == [int(x) for x in want[q]["id"][: int(wc[q])]], (rank, q)
+    # ---- work split by query slices (the coarse step of list shards): same rows as the unsplit computation,
+    # also when the query count does not divide by the world size
+    from ferrolm_b200.sharding import per_query_slices
+
+    calls = []
+
+    def keys(part):
+        calls.append(part.shape[0])
+        return (part[:, :5] * 1000.0).to(torch.int64)
+
+    tq = torch.from_numpy(queries)
+    got = per_query_slices(keys, tq, world)
+    assert torch.equal(got, (tq[:, :5] * 1000.0).to(torch.int64))
+    assert calls == [row_range(rank, world, nq)[1] - row_range(rank, world, nq)[0]] and sum(calls) < nq
     dist.barrier()
     dist.destroy_process_group()
     open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
