@@ -146,7 +146,7 @@ int fv_ctx_device(const fv_ctx* ctx) { return ctx ? ctx->device : -1; }
 
 int fv_ctx_sync(fv_ctx* ctx) {
   if (!ctx) return fv::fail(FV_ERR_ARG, "null context");
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   FV_CUDA(cudaStreamSynchronize(ctx->stream));
   return FV_OK;
 }
@@ -155,12 +155,14 @@ void* fv_ctx_stream(fv_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 
 int fv_ctx_stats(const fv_ctx* ctx, fv_stats* out) {
   if (!ctx || !out) return fv::fail(FV_ERR_ARG, "null argument");
+  std::lock_guard<std::recursive_mutex> lk(const_cast<fv_ctx*>(ctx)->mu);
   *out = ctx->stats;
   return FV_OK;
 }
 
 int fv_ctx_set_timing(fv_ctx* ctx, int on) {
   if (!ctx) return fv::fail(FV_ERR_ARG, "null context");
+  std::lock_guard<std::recursive_mutex> lk(ctx->mu);
   ctx->timing = on != 0;
   return FV_OK;
 }
@@ -361,7 +363,7 @@ extern "C" int fv_datagen_dev(fv_ctx* ctx, uint64_t seed, size_t first_row, size
     XorShift c(seed * 1000003ull + 17);
     for (auto& v : centres) v = float(c.uniform() * 255.0);
   }
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   DevBuf d_cen;
   FV_TRY(d_cen.reserve(centres.size() * sizeof(float)));
   FV_CUDA(cudaMemcpyAsync(d_cen.p, centres.data(), centres.size() * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));

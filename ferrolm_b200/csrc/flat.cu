@@ -362,20 +362,23 @@ int fv_flat_new(fv_ctx* ctx, int metric, uint32_t dim, fv_flat** out) {
 
 void fv_flat_free(fv_flat* ix) {
   if (!ix) return;
-  fv::DeviceGuard g(ix->ctx->device);
-  cudaStreamSynchronize(ix->ctx->stream);
-  fv::tc_free(ix->tc);
   fv_ctx* ctx = ix->ctx;
-  delete ix;
-  fv::ctx_release(ctx);
+  {
+    fv::CtxGuard g(ctx);
+    cudaStreamSynchronize(ctx->stream);
+    fv::tc_free(ix->tc);
+    delete ix;
+  }
+  fv::ctx_release(ctx);  // may destroy the context: its lock is no longer held
 }
 
 static int flat_add_impl(fv_flat* ix, const float* v, size_t n, bool dev) {
   if (!ix || (!v && n)) return fv::fail(FV_ERR_ARG, "fv_flat_add: null argument");
   if (n == 0) return FV_OK;
-  if (ix->n + n > 0xFFFFFFF0ull) return fv::fail(FV_ERR_UNSUPPORTED, "more than 2^32 rows");
+  if (uint64_t(ix->id_base) + ix->n + n > 0xFFFFFFF0ull)
+    return fv::fail(FV_ERR_UNSUPPORTED, "row ids (id base + rows) would pass 2^32 - 16");
   fv_ctx* ctx = ix->ctx;
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   const size_t row = size_t(ix->pd) * sizeof(float);
   FV_TRY(ix->data.grow((ix->n + n) * row, ix->n * row, ctx->stream));
   float* dst = ix->data.as<float>() + ix->n * size_t(ix->pd);
@@ -393,7 +396,7 @@ size_t fv_flat_len(const fv_flat* ix) { return ix ? ix->n : 0; }
 
 int fv_flat_vector(const fv_flat* ix, uint32_t id, float* out_padded) {
   if (!ix || !out_padded || id >= ix->n) return fv::fail(FV_ERR_ARG, "fv_flat_vector: bad argument");
-  fv::DeviceGuard g(ix->ctx->device);
+  fv::CtxGuard g(ix->ctx);
   FV_CUDA(cudaMemcpy(out_padded, ix->data.as<float>() + size_t(id) * ix->pd, size_t(ix->pd) * sizeof(float),
                      cudaMemcpyDeviceToHost));
   return FV_OK;
@@ -401,6 +404,7 @@ int fv_flat_vector(const fv_flat* ix, uint32_t id, float* out_padded) {
 
 int fv_flat_set_id_base(fv_flat* ix, uint32_t id_base) {
   if (!ix) return fv::fail(FV_ERR_ARG, "null index");
+  if (ix->n) return fv::fail(FV_ERR_ARG, "id base must be set before the first add");
   ix->id_base = id_base;
   return FV_OK;
 }
@@ -419,7 +423,7 @@ int fv_flat_search_batch_dev(fv_flat* ix, const float* d_queries, size_t nq, siz
   if (k > 4096) return fv::fail(FV_ERR_UNSUPPORTED, "k above 4096 is not supported");
   if (nq == 0) return FV_OK;
   fv_ctx* ctx = ix->ctx;
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   ctx->stats = fv_stats{};
   fv::stage_begin(ctx);
   const int pd = int(ix->pd);
@@ -436,7 +440,7 @@ int fv_flat_search_batch_dev(fv_flat* ix, const float* d_queries, size_t nq, siz
   if (want_tc) {
     if (!fv::tc_usable(ix->tc, ix->n, nq, L))
       return fv::fail(FV_ERR_UNSUPPORTED, "tensor-core search needs k <= 32, at least 4096 rows and a padded dimension of at most 384");
-    FV_TRY(fv::tc_search(ctx, ix->tc, ix->metric, ix->data.as<float>(), ix->n, pd, q, nq, L, ix->id_base, keys, true));
+    FV_TRY(fv::tc_search(ctx, ix->tc, ix->metric, ix->data.as<float>(), ix->n, pd, q, nq, L, ix->id_base, keys, true, true));
   } else {
     FV_TRY(fv::exact_scan(ctx, ix->metric, ix->data.as<float>(), ix->n, pd, q, size_t(pd), nullptr, nq, L, true,
                           ix->id_base, keys, 2));
@@ -453,7 +457,7 @@ int fv_flat_search_batch(fv_flat* ix, const float* queries, size_t nq, size_t k,
   if (!ix || (nq && (!queries || !out))) return fv::fail(FV_ERR_ARG, "fv_flat_search_batch: null argument");
   if (nq == 0) return FV_OK;
   fv_ctx* ctx = ix->ctx;
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   const size_t qbytes = nq * size_t(ix->dim) * sizeof(float);
   const size_t obytes = nq * k * sizeof(fv_neighbor);
   FV_TRY(ctx->scratch[10].reserve(qbytes));
@@ -508,7 +512,7 @@ int fv_merge_topk_dev(fv_ctx* ctx, const fv_neighbor* d_parts, const uint32_t* d
     return fv::fail(FV_ERR_ARG, "fv_merge_topk_dev: bad argument");
   if (k_out > 4096) return fv::fail(FV_ERR_UNSUPPORTED, "k above 4096 is not supported");
   if (nq == 0) return FV_OK;
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   FV_TRY(ctx->scratch[1].reserve(nq * k_out * sizeof(u64)));
   u64* keys = ctx->scratch[1].as<u64>();
   int wpb = 4;

@@ -803,11 +803,27 @@ __global__ void rerank_kernel(RerankParams p) {
   const float u16 = p.bf16 ? 0.00390625f : 0.00048828125f;
   const float qn = sqrtf(p.is_l2 ? qn2 : 0.f), bn = sqrtf(p.bst->max_norm2);
   float eps;
+  // The query operand of the GEMM is this row times -2 (L2) or -1 in the 16-bit type.  A component that leaves that
+  // type's range (fp16: 65504) turns every score of the query into +-inf or NaN, so no row is a candidate and the
+  // reasoning below ("a row that is not a candidate scores above the bound") says nothing: such a query is never
+  // certified here and goes to the full-precision scan, which returns the reference's k finite neighbours.
+  bool q_in_range;
   {
     // inner-product case needs the query norm too; it is recomputed here from the staged query
-    float s = 0.f;
-    for (int c = lane; c < p.pd; c += 32) s = __fmaf_rn(sq[c], sq[c], s);
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FV_FULL, s, o);
+    float s = 0.f, qmax = 0.f;
+    bool fin = true;
+    for (int c = lane; c < p.pd; c += 32) {
+      s = __fmaf_rn(sq[c], sq[c], s);
+      qmax = fmaxf(qmax, fabsf(sq[c]));
+      fin = fin && fabsf(sq[c]) <= 3.0e38f;  // false for inf and NaN
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      s += __shfl_xor_sync(FV_FULL, s, o);
+      qmax = fmaxf(qmax, __shfl_xor_sync(FV_FULL, qmax, o));
+    }
+    fin = __all_sync(FV_FULL, fin);
+    const float scale = p.is_l2 ? 2.f : 1.f;
+    q_in_range = fin && (p.bf16 ? qmax <= 1.0e38f : qmax * scale <= 65504.f);
     const float qnorm = p.is_l2 ? qn : sqrtf(s);
     const float kf = float(p.Kp);
     const float e_dot = (2.f * u16 * (1.f + u16) + kf * 4.7683716e-7f + kf * 1.1920929e-7f) * qnorm * bn +
@@ -884,7 +900,7 @@ __global__ void rerank_kernel(RerankParams p) {
   overflow = __any_sync(FV_FULL, overflow);
   const u64 kth = list[p.k - 1];
   bool certified;
-  if (overflow || mismatch) {
+  if (overflow || mismatch || !q_in_range || !(tau == tau)) {
     certified = false;
   } else if (tau == INFINITY) {
     certified = true;  // every row with a finite score was a candidate
@@ -1182,7 +1198,7 @@ static void fill_params(GemmParams* g, const Tiling& t, size_t rows, size_t nq, 
 // scratch slots: 2 scan partials (fallback), 3 A operand, 5 query norms + bounds + candidate counters, 6 sample lists,
 // 7 retry ids, 8 fallback keys, 9 candidate buffers
 int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n, int pd, const float* d_queries,
-              size_t nq, int k, uint32_t id_base, u64* d_out_keys, bool mark_stages) {
+              size_t nq, int k, uint32_t id_base, u64* d_out_keys, bool mark_stages, bool prefilter_inf) {
   const int Kp = tc->Kp;
   const bool is_l2 = metric == FV_L2;
   Tiling ts{}, tm{};
@@ -1297,7 +1313,7 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
     const size_t nsub = h_words[0];
     FV_TRY(ctx->scratch[8].reserve(nsub * size_t(k) * sizeof(u64)));
     u64* sub = ctx->scratch[8].as<u64>();
-    FV_TRY(exact_scan(ctx, metric, d_rows, n, pd, d_queries, size_t(pd), rp.retry_ids, nsub, k, true, id_base, sub, 2));
+    FV_TRY(exact_scan(ctx, metric, d_rows, n, pd, d_queries, size_t(pd), rp.retry_ids, nsub, k, prefilter_inf, id_base, sub, 2));
     scatter_keys_kernel<<<ctx->sm_count, 256, 0, ctx->stream>>>(sub, rp.retry_ids, nsub, k, d_out_keys);
     ctx->stats.launches++;
     FV_CUDA(cudaGetLastError());

@@ -676,7 +676,7 @@ int fv_hnsw_build(fv_ctx* ctx, int metric, uint32_t dim, const float* vectors, s
     work();
     for (auto& t : th) t.join();
   }
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   FV_TRY(fv::upload_graph(h.get()));
   *out = h.release();
   return FV_OK;
@@ -684,9 +684,14 @@ int fv_hnsw_build(fv_ctx* ctx, int metric, uint32_t dim, const float* vectors, s
 
 void fv_hnsw_free(fv_hnsw* ix) {
   if (!ix) return;
-  fv::DeviceGuard g(ix->ctx->device);
-  cudaStreamSynchronize(ix->ctx->stream);
-  delete ix;
+  fv_ctx* ctx = ix->ctx;
+  {
+    fv::CtxGuard g(ctx);
+    cudaStreamSynchronize(ctx->stream);
+    ix->ctx = nullptr;  // the destructor must not drop the reference while the lock is held
+    delete ix;
+  }
+  fv::ctx_release(ctx);  // may destroy the context
 }
 
 size_t fv_hnsw_len(const fv_hnsw* ix) { return ix ? ix->n() : 0; }
@@ -723,7 +728,7 @@ double fv_hnsw_mean_degree(const fv_hnsw* ix) {  // hnsw.rs:388-393
 int fv_hnsw_search_batch_dev(fv_hnsw* ix, const float* d_queries, size_t nq, size_t k, size_t ef, fv_neighbor* d_out,
                              uint32_t* d_counts) {
   if (!ix || (nq && (!d_queries || !d_out))) return fv::fail(FV_ERR_ARG, "fv_hnsw_search_batch: null argument");
-  fv::DeviceGuard g(ix->ctx->device);
+  fv::CtxGuard g(ix->ctx);
   return fv::hnsw_search_dev(ix, d_queries, nq, k, ef, d_out, d_counts);
 }
 
@@ -732,7 +737,7 @@ int fv_hnsw_search_batch(fv_hnsw* ix, const float* queries, size_t nq, size_t k,
   if (!ix || (nq && (!queries || !out))) return fv::fail(FV_ERR_ARG, "fv_hnsw_search_batch: null argument");
   if (nq == 0) return FV_OK;
   fv_ctx* ctx = ix->ctx;
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   const size_t qbytes = nq * size_t(ix->dim) * sizeof(float), obytes = nq * k * sizeof(fv_neighbor);
   FV_TRY(ctx->scratch[10].reserve(qbytes));
   FV_TRY(ctx->scratch[11].reserve(obytes + nq * sizeof(uint32_t)));
@@ -877,7 +882,7 @@ int fv_hnsw_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_hnsw** out) {
         if (u[1 + t] >= n || h->levels[u[1 + t]] < l + 1) return fv::fail(FV_ERR_FILE, "link out of range");
     }
   }
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   FV_TRY(fv::upload_graph(h.get()));
   *out = h.release();
   return FV_OK;

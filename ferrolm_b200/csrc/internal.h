@@ -5,6 +5,7 @@
 
 #include <cstring>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -74,6 +75,11 @@ struct DevBuf {
 enum { FV_NSCRATCH = 12, FV_NSTAGE = 8 };
 
 struct fv_ctx {
+  // Every entry point that uses the stream, the scratch arena, the events or the counters holds this lock for the
+  // whole call (fv::CtxGuard): the reference's search methods take &self and its index types are Sync
+  // (hnsw.rs:42-77, flat.rs:56-66), so several host threads may search indexes of one context at once; here
+  // their calls run one after the other.  Recursive because the host-pointer entry points call their _dev twins.
+  std::recursive_mutex mu;
   int device = 0;
   cudaStream_t stream = nullptr;
   int sm_count = 0;
@@ -103,6 +109,14 @@ struct DeviceGuard {
   }
 };
 
+// Held by an entry point for its whole duration: the context's lock, then its device made current.
+struct CtxGuard {
+  std::unique_lock<std::recursive_mutex> lk;
+  DeviceGuard dg;
+  bool ok;
+  explicit CtxGuard(fv_ctx* ctx) : lk(ctx->mu), dg(ctx->device), ok(dg.ok) {}
+};
+
 // Indexes keep their context alive: destruction is deferred until the last one is freed.
 void ctx_retain(fv_ctx* ctx);
 void ctx_release(fv_ctx* ctx);
@@ -129,8 +143,9 @@ int keys_to_neighbors(fv_ctx* ctx, const u64* d_keys, size_t nq, int L, int k, f
 struct TcSide;
 void tc_free(TcSide* tc);
 int tc_append(fv_ctx* ctx, TcSide** tc, int metric, const float* d_rows_new, size_t n_old, size_t n_new, int pd);
+// `prefilter_inf`: what the full-precision scan that re-runs uncertified queries is told (see exact_scan).
 int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n, int pd, const float* d_queries,
-              size_t nq, int k, uint32_t id_base, u64* d_out_keys, bool mark_stages);
+              size_t nq, int k, uint32_t id_base, u64* d_out_keys, bool mark_stages, bool prefilter_inf);
 bool tc_usable(const TcSide* tc, size_t n, size_t nq, int k);
 
 // pads rows of `dim` floats to `pd` on the device (host or device source)

@@ -657,7 +657,7 @@ int fv_kmeans_assign(fv_ctx* ctx, const float* data, size_t n, const float* cent
                      uint32_t* out) {
   if (!ctx || !data || !centroids || !out || k == 0 || dim == 0 || dim % 8 != 0)
     return fv::fail(FV_ERR_ARG, "fv_kmeans_assign: bad argument (dim must be a multiple of 8)");
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   DevBuf d_data, d_cen, d_out;
   FV_TRY(d_data.reserve(n * dim * sizeof(float)));
   FV_TRY(d_cen.reserve(k * dim * sizeof(float)));
@@ -673,7 +673,7 @@ int fv_kmeans_assign(fv_ctx* ctx, const float* data, size_t n, const float* cent
 int fv_kmeans_train(fv_ctx* ctx, const float* data, size_t n, size_t dim, size_t k, size_t iters, uint64_t seed,
                     float* centroids_out) {
   if (!ctx || !data || !centroids_out || k == 0 || dim == 0) return fv::fail(FV_ERR_ARG, "fv_kmeans_train: bad argument");
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   DevBuf d_data;
   FV_TRY(d_data.reserve(n * dim * sizeof(float)));
   FV_CUDA(cudaMemcpyAsync(d_data.p, data, n * dim * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
@@ -693,7 +693,7 @@ int fv_ivfpq_train(fv_ctx* ctx, int metric, uint32_t dim, const float* sample, s
   if (p->nlist == 0 || n < p->nlist)
     return fv::fail(FV_ERR_ARG, "need at least " + std::to_string(p->nlist) + " training vectors, got " + std::to_string(n));
   if (p->m * fv::KSUB * 8 + 2 * pd * 4 > 190 * 1024) return fv::fail(FV_ERR_UNSUPPORTED, "m above 92 is not supported");
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   ctx->stats = fv_stats{};
   auto ix = std::unique_ptr<fv_ivfpq>(new fv_ivfpq());
   ix->ctx = ctx;
@@ -752,9 +752,14 @@ int fv_ivfpq_train(fv_ctx* ctx, int metric, uint32_t dim, const float* sample, s
 
 void fv_ivfpq_free(fv_ivfpq* ix) {
   if (!ix) return;
-  fv::DeviceGuard g(ix->ctx->device);
-  cudaStreamSynchronize(ix->ctx->stream);
-  delete ix;
+  fv_ctx* ctx = ix->ctx;
+  {
+    fv::CtxGuard g(ctx);
+    cudaStreamSynchronize(ctx->stream);
+    ix->ctx = nullptr;  // the destructor must not drop the reference while the lock is held
+    delete ix;
+  }
+  fv::ctx_release(ctx);  // may destroy the context
 }
 
 size_t fv_ivfpq_len(const fv_ivfpq* ix) { return ix ? ix->count : 0; }
@@ -779,12 +784,14 @@ int fv_ivfpq_set_shard(fv_ivfpq* ix, int rank, int world) {
 static int ivfpq_add_impl(fv_ivfpq* ix, const float* vectors, size_t n_total, bool src_is_device) {
   if (!ix || (!vectors && n_total)) return fv::fail(FV_ERR_ARG, "fv_ivfpq_add: null argument");
   fv_ctx* ctx = ix->ctx;
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   const size_t pd = ix->pd, m = ix->m;
   const size_t CH = size_t(1) << 22;
   for (size_t b0 = 0; b0 < n_total; b0 += CH) {
     size_t n = std::min(CH, n_total - b0);
-    if (ix->seen + n > 0xFFFFFFF0ull) return fv::fail(FV_ERR_UNSUPPORTED, "more than 2^32 rows");
+    // ids are id_base + running count; 0xFFFFFFFF marks an unused result slot and must stay out of reach
+    if (uint64_t(ix->id_base) + ix->seen + n > 0xFFFFFFF0ull)
+      return fv::fail(FV_ERR_UNSUPPORTED, "row ids (id base + rows) would pass 2^32 - 16");
     const float* src = vectors + b0 * size_t(ix->dim);
     DevBuf d_x_tmp, d_assign, d_codes, d_dest, d_sel, d_xs, d_assign_s, d_ids_s;
     FV_TRY(d_x_tmp.reserve(n * pd * sizeof(float)));
@@ -921,7 +928,7 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
     }
     // ivfpq.rs:211-220: every cell is pushed, no pre-filter
     if (nq >= 256 && fv::tc_usable(ix->ctc, ix->nlist, nq, np))
-      FV_TRY(fv::tc_search(ctx, ix->ctc, ix->metric, ix->centroids.as<float>(), ix->nlist, pd, q, nq, np, 0, dst, false));
+      FV_TRY(fv::tc_search(ctx, ix->ctc, ix->metric, ix->centroids.as<float>(), ix->nlist, pd, q, nq, np, 0, dst, false, false));
     else
       FV_TRY(fv::exact_scan(ctx, ix->metric, ix->centroids.as<float>(), ix->nlist, pd, q, size_t(pd), nullptr, nq, np,
                             false, 0, dst, 2));
@@ -1005,7 +1012,7 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
 int fv_ivfpq_search_batch_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,
                               fv_neighbor* d_out, uint32_t* d_counts) {
   if (!ix || (nq && (!d_queries || !d_out))) return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_batch: null argument");
-  fv::DeviceGuard g(ix->ctx->device);
+  fv::CtxGuard g(ix->ctx);
   return ivfpq_search_impl(ix, d_queries, nq, k, nprobe, refine, false, d_out, d_counts, nullptr, nullptr);
 }
 
@@ -1013,7 +1020,7 @@ size_t fv_ivfpq_nlist(const fv_ivfpq* ix) { return ix ? ix->nlist : 0; }
 
 int fv_ivfpq_coarse_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t nprobe, uint64_t* d_cells) {
   if (!ix || (nq && (!d_queries || !d_cells))) return fv::fail(FV_ERR_ARG, "fv_ivfpq_coarse: null argument");
-  fv::DeviceGuard g(ix->ctx->device);
+  fv::CtxGuard g(ix->ctx);
   return ivfpq_search_impl(ix, d_queries, nq, 1, nprobe, 0, false, nullptr, nullptr, nullptr, nullptr, nullptr, d_cells);
 }
 
@@ -1021,7 +1028,7 @@ int fv_ivfpq_search_batch_cells_dev(fv_ivfpq* ix, const float* d_queries, size_t
                                     size_t refine, const uint64_t* d_cells, fv_neighbor* d_out, uint32_t* d_counts) {
   if (!ix || (nq && (!d_queries || !d_out || !d_cells)))
     return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_batch_cells: null argument");
-  fv::DeviceGuard g(ix->ctx->device);
+  fv::CtxGuard g(ix->ctx);
   return ivfpq_search_impl(ix, d_queries, nq, k, nprobe, refine, false, d_out, d_counts, nullptr, nullptr, d_cells);
 }
 
@@ -1030,7 +1037,7 @@ int fv_ivfpq_search_candidates_cells_dev(fv_ivfpq* ix, const float* d_queries, s
                                          uint32_t* d_counts) {
   if (!ix || (nq && (!d_queries || !d_adc || !d_exact || !d_counts || !d_cells)))
     return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_candidates_cells: null argument");
-  fv::DeviceGuard g(ix->ctx->device);
+  fv::CtxGuard g(ix->ctx);
   return ivfpq_search_impl(ix, d_queries, nq, keep, nprobe, 1, true, nullptr, d_counts, d_adc, d_exact, d_cells);
 }
 
@@ -1038,7 +1045,7 @@ int fv_ivfpq_search_candidates_dev(fv_ivfpq* ix, const float* d_queries, size_t 
                                    fv_neighbor* d_adc, float* d_exact, uint32_t* d_counts) {
   if (!ix || (nq && (!d_queries || !d_adc || !d_exact || !d_counts)))
     return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_candidates: null argument");
-  fv::DeviceGuard g(ix->ctx->device);
+  fv::CtxGuard g(ix->ctx);
   return ivfpq_search_impl(ix, d_queries, nq, keep, nprobe, 1, true, nullptr, d_counts, d_adc, d_exact);
 }
 
@@ -1047,7 +1054,7 @@ int fv_ivfpq_search_batch(fv_ivfpq* ix, const float* queries, size_t nq, size_t 
   if (!ix || (nq && (!queries || !out))) return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_batch: null argument");
   if (nq == 0) return FV_OK;
   fv_ctx* ctx = ix->ctx;
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   const size_t qbytes = nq * size_t(ix->dim) * sizeof(float), obytes = nq * k * sizeof(fv_neighbor);
   FV_TRY(ctx->scratch[10].reserve(qbytes));
   FV_TRY(ctx->scratch[11].reserve(obytes + nq * sizeof(uint32_t)));
@@ -1082,9 +1089,11 @@ size_t fv_ivfpq_save_size(const fv_ivfpq* ix) {
 int fv_ivfpq_save(const fv_ivfpq* ix, uint8_t* buf, size_t cap, size_t* written) {
   if (!ix || !buf) return fv::fail(FV_ERR_ARG, "fv_ivfpq_save: null argument");
   if (ix->shard_world > 1) return fv::fail(FV_ERR_UNSUPPORTED, "a list-sharded index holds part of the rows and cannot be saved as one file");
+  // The file has no field for an id base, and a loaded index finds the kept vector of id i in row i.
+  if (ix->id_base != 0) return fv::fail(FV_ERR_UNSUPPORTED, "a row shard (id base != 0) cannot be saved: the file format has no id base");
   const size_t need = fv_ivfpq_save_size(ix);
   if (cap < need) return fv::fail(FV_ERR_ARG, "fv_ivfpq_save: buffer too small");
-  fv::DeviceGuard g(ix->ctx->device);
+  fv::CtxGuard g(ix->ctx);
   std::vector<uint32_t> ids(ix->count);
   std::vector<uint8_t> codes(ix->count * ix->m);
   if (ix->count) {
@@ -1209,7 +1218,12 @@ int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out)
   if (ids.size() != ix->count || (has && nv != ix->count * size_t(ix->pd)))
     return fv::fail(FV_ERR_FILE, "index file sizes do not match");
   ix->keep = has;
-  fv::DeviceGuard g(ctx->device);
+  // With kept vectors the search re-ranks candidate `id` from row `id` of them (ivfpq.rs:289 indexes the same way and
+  // panics on a bad id): a damaged file must not send the kernel out of bounds.
+  if (has)
+    for (uint32_t id : ids)
+      if (id >= ix->count) return fv::fail(FV_ERR_FILE, "index file holds a row id beyond its row count");
+  fv::CtxGuard g(ctx);
   FV_TRY(fv::upload_quantizers(ix.get()));
   FV_TRY(fv::upload_offsets(ix.get()));
   FV_TRY(ix->ids.reserve(ix->count * 4 + 16));
@@ -1342,7 +1356,7 @@ int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float
     return fv::fail(FV_ERR_ARG, "fv_merge_refine_dev: bad argument");
   if (keep > 4096 || k > 4096) return fv::fail(FV_ERR_UNSUPPORTED, "k * refine above 4096 is not supported");
   if (nq == 0) return FV_OK;
-  fv::DeviceGuard g(ctx->device);
+  fv::CtxGuard g(ctx);
   FV_TRY(ctx->scratch[1].reserve(nq * k * sizeof(u64)));
   u64* keys = ctx->scratch[1].as<u64>();
   const size_t smem = (keep + k) * sizeof(u64);

@@ -1,9 +1,9 @@
 // fv_merge_topk_static_dev: the shard merge for callers that must not allocate.
 //
 // Some hosts of this library run where device allocation is off the table: a latency-critical
-// serving loop that has handed all free HBM to its own arena, a plugin running inside another
-// runtime's stream callback or graph-replay section, or code that runs after the process has
-// fixed its memory budget.  For them every other entry point is unusable, because each one may
+// serving loop that has handed all free HBM to its own arena, a component of a framework whose
+// allocator owns the device and forbids cudaMalloc beside it, or code that runs after the process
+// has fixed its memory budget.  For them every other entry point is unusable, because each one may
 // grow the context's scratch arena with cudaMalloc.  This file gives them one call that never
 // does: the intermediate keys of the merge live in a fixed array that is part of the library
 // image itself.
@@ -15,8 +15,16 @@
 //     in it has to start at zero (each call overwrites the part it reads), but two calls that overlap
 //     on the GPU -- different streams, or different threads -- race on it.  Serialise them.
 //
+// The call is synchronous: it launches two kernels on the caller's stream and waits for that stream,
+// so it is refused (FV_ERR_UNSUPPORTED) on a stream that is being captured, and it may not be made
+// from a host-function callback (no CUDA call may).
+//
 // The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
-// device current).  Make that first call before any stream capture begins.
+// device current).  With the CUDA runtime's lazy module loading that first call is also when the
+// array and this file's kernels are placed on the device, so make it once at start-up: before any
+// stream capture begins, and while the device still has a few MiB that the process has not claimed.
+#include <climits>
+
 #include "internal.h"
 
 #define FV_STATIC_MERGE_MAX_KEYS (1u << 18)
@@ -97,6 +105,8 @@ extern "C" int fv_merge_topk_static_dev(int device, void* stream, const fv_neigh
   if (!d_parts || !d_out || nparts == 0 || k_in == 0 || k_out == 0)
     return fv::fail(FV_ERR_ARG, "fv_merge_topk_static_dev: bad argument");
   if (nq == 0) return FV_OK;
+  if (nparts > size_t(INT_MAX) || k_in > size_t(INT_MAX))
+    return fv::fail(FV_ERR_UNSUPPORTED, "fv_merge_topk_static_dev: nparts and k_in must fit a 32-bit int");
   if (k_out > 1024) return fv::fail(FV_ERR_UNSUPPORTED, "fv_merge_topk_static_dev: k_out above 1024 is not supported");
   if (nq > FV_STATIC_MERGE_MAX_KEYS / k_out)
     return fv::fail(FV_ERR_UNSUPPORTED,
@@ -107,6 +117,13 @@ extern "C" int fv_merge_topk_static_dev(int device, void* stream, const fv_neigh
   u64* keys = nullptr;
   FV_TRY(fv::static_scratch(device, &keys));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &cap) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fv::fail(FV_ERR_CUDA, "fv_merge_topk_static_dev: cudaStreamIsCapturing failed");
+  }
+  if (cap != cudaStreamCaptureStatusNone)
+    return fv::fail(FV_ERR_UNSUPPORTED, "fv_merge_topk_static_dev waits for its stream and cannot run on a capturing stream");
   // 4 warps per block; k_out <= 1024 keeps the lists within the default 48 KB of shared memory
   int wpb = 4;
   while (wpb > 1 && size_t(wpb) * k_out * 8 > 48 * 1024) wpb >>= 1;

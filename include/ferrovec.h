@@ -201,14 +201,17 @@ int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float
                         fv_neighbor* d_out, uint32_t* d_counts);
 
 /* The same merge as fv_merge_topk_dev for callers that must not allocate device memory (a serving loop that
- * has given all free HBM to its own arena, a plugin running inside another runtime's callback or replayed
- * section, a process past its memory-budget checkpoint).  It has no counterpart in the reference and takes no
- * context: the intermediate keys live in a fixed 2 MiB array inside the library image, so the call performs no
+ * has given all free HBM to its own arena, a component of a framework whose allocator owns the device, a
+ * process past its memory-budget checkpoint).  It has no counterpart in the reference and takes no context:
+ * the intermediate keys live in a fixed 2 MiB array inside the library image, so the call performs no
  * cudaMalloc/cudaFree.  Limits: nq * k_out <= 262144 and k_out <= 1024, otherwise FV_ERR_UNSUPPORTED.  All
  * calls on one GPU share that array and it keeps the last call's contents (nothing in it needs clearing), so
- * calls that overlap on the GPU race: serialise them.  The first call on each device resolves the array's
- * address; make it before any stream capture starts.  Runs on `stream` (a cudaStream_t, NULL = default
- * stream) of `device` and returns when the result is complete. */
+ * calls that overlap on the GPU race: serialise them.  The call is synchronous: it runs on `stream` (a
+ * cudaStream_t, NULL = default stream) of `device`, waits for it and returns when the result is complete; a
+ * capturing stream is refused (FV_ERR_UNSUPPORTED) and it may not be called from a host callback.  The first
+ * call on each device resolves the array's address and, with lazy module loading, places the array and the
+ * kernels on the device: make it at start-up, before any stream capture and before the process has claimed
+ * the last few MiB of that device. */
 int fv_merge_topk_static_dev(int device, void* stream, const fv_neighbor* d_parts, const uint32_t* d_part_counts,
                              size_t nparts, size_t nq, size_t k_in, size_t k_out, fv_neighbor* d_out,
                              uint32_t* d_counts);

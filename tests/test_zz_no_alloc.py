@@ -34,7 +34,14 @@ def test_static_merge_equals_the_allocating_merge_twice_in_a_row():
         out = torch.full((nq, k_out, 2), -7, dtype=torch.int32, device="cuda")
         got_counts = torch.full((nq,), -7, dtype=torch.int32, device="cuda")
         torch.cuda.synchronize()
+        if call == 1:
+            # the second call finds everything in place: free device memory must not move across it
+            # (the first call may load the library's kernels and the array onto the device)
+            free_before, _ = torch.cuda.mem_get_info()
         fv.merge_topk_static(parts, counts, k_out, out, got_counts)
+        if call == 1:
+            free_after, _ = torch.cuda.mem_get_info()
+            assert free_after == free_before, "the allocation-free merge changed the free device memory"
         assert torch.equal(out, want), f"call {call}: neighbours differ"
         assert torch.equal(got_counts, want_counts), f"call {call}: counts differ"
         # against an independent statement of the merge on the host
