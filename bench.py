@@ -239,7 +239,8 @@ def run_ours(args):
         ix = fv.IvfPq.train(ctx, fv.Metric.L2, DIM, learn, fv.IvfPqParams(IVF["nlist"], IVF["m"], IVF["iters"], True, 1))
         ix.set_shard(rank, world)
         ix.add(base)
-        refine, nprobe = IVF["refine"], IVF["nprobe"]
+        ix.set_scan_mode(args.scan_mode)
+        refine, nprobe = IVF["refine"] if args.refine is None else args.refine, args.nprobe or IVF["nprobe"]
         searcher = ShardedSearch(ctx, ix, "ivfpq", world)
     elif args.workload == "flat":
         lo, hi = row_range(rank, world, N_BASE)  # contiguous row shards
@@ -263,7 +264,7 @@ def run_ours(args):
     h_out = torch.empty((NQ, K, 2), dtype=torch.int32).pin_memory()
     launches = [0]
     stage_sum = np.zeros(8)
-    rows_scanned = [0]
+    rows_scanned = [0, 0]
     work = [0, 0]
 
     def step(q):
@@ -276,7 +277,7 @@ def run_ours(args):
         st = ctx.stats()  # the merge kernels add to the launch count and leave the search's stage times in place
         launches[0] += st["launches"]
         stage_sum[:] += np.array(st["stage_ms"])
-        rows_scanned[0] = st["rows_scanned"]
+        rows_scanned[0], rows_scanned[1] = st["rows_scanned"], st["rows_list_scan"]
         work[0], work[1] = st["dist_evals"], st["expansions"]
         return r[0], r[1]
 
@@ -346,14 +347,18 @@ def run_ours(args):
         "e2e": {"value": NQ / (e2e_ms * 1e-3), "unit": "queries/s", "h2d_bytes_per_step": int(hq.numel() * 4),
                 "d2h_bytes_per_step": int(h_out.numel() * 4), "ms_per_step": e2e_ms},
         "gpu_launches": int(steady_launches), "clocks": clocks, "build_s": build_s,
-        "stage_ms": [round(float(x), 4) for x in stages[:5]],
+        "stage_ms": [round(float(x), 4) for x in stages[:6]],
     }
     # ---- roofline of the dominant kernel (per launch = per step; durations from CUDA events on the library's stream)
     if args.workload == "ivfpq":
-        kms = float(stages[1])
-        alg = rows_scanned[0] * IVF["m"]  # bytes of codes the scan has to read, this rank's shard
+        # stages of an IVF-PQ search: 0 coarse cells, 1 query tables + sample pass, 2 pair bucketing, 3 the scan,
+        # 4 merge + re-rank, 5 keys -> neighbours.  The dominant kernel is the scan of stage 3: the list-major
+        # kernel over the rows it visited (rows_list_scan), or the per-query kernel over all rows.
+        kms = float(stages[3])
+        list_major = rows_scanned[1] > 0
+        alg = (rows_scanned[1] if list_major else rows_scanned[0]) * IVF["m"]  # code bytes that launch has to read
         ach = alg / (kms * 1e-3) / 1e9
-        line["roofline"] = {"kernel": "ivfpq_scan_kernel", "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"],
+        line["roofline"] = {"kernel": "ivfpq_list_scan_kernel" if list_major else "ivfpq_scan_kernel", "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"],
                             "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
                             "algorithmic_bytes_per_launch": int(alg), "kernel_ms": kms}
     elif args.workload == "flat":
@@ -403,7 +408,7 @@ def run_ours(args):
             oix = oracle.IvfPq.load(ix.save())  # the same trained index, byte for byte
             load_s = time.perf_counter() - t0
             t0 = time.perf_counter()
-            want, wc = oix.search_batch(queries[:nsub], K, IVF["nprobe"], refine, threads)
+            want, wc = oix.search_batch(queries[:nsub], K, nprobe, refine, threads)
             sample = f"first {nsub} of {NQ} queries, same index (loaded from the GPU-built FLIVFPQ1 bytes)"
         elif args.workload == "flat":
             nsub = 64
@@ -434,7 +439,7 @@ def run_ours(args):
             t0 = time.perf_counter()
             for _ in range(passes):
                 if args.workload == "ivfpq":
-                    oix.search_batch(queries, K, IVF["nprobe"], refine, threads)
+                    oix.search_batch(queries, K, nprobe, refine, threads)
                 else:
                     oix.search_batch(queries, K, HNSW["ef"], threads)
             cpu_dt, cpu_n = time.perf_counter() - t0, passes * NQ
@@ -486,6 +491,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--nq", type=int, default=NQ, help="queries per step (smaller = a profiling-sized case)")
     ap.add_argument("--n", type=int, default=None, help="base rows (smaller = a profiling-sized case)")
+    ap.add_argument("--scan-mode", type=int, default=0, help="IVF-PQ scan: 0 automatic, 1 per-query kernel, 2 list-major")
+    ap.add_argument("--nprobe", type=int, default=0, help="IVF-PQ: probed lists (default: the benchmark's 64)")
+    ap.add_argument("--refine", type=int, default=None, help="IVF-PQ: re-rank factor (default: the benchmark's 10)")
     ap.add_argument("--big", action="store_true", help="BASELINE configs[4]: 50M rows, 4096 clusters, sharded")
     args = ap.parse_args()
     global CLUSTERS

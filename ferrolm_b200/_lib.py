@@ -41,6 +41,7 @@ class fv_stats(C.Structure):
         ("expansions", C.c_uint64),
         ("regrown", C.c_uint64),
         ("stage_ms", C.c_float * 8),
+        ("rows_list_scan", C.c_uint64),
     ]
 
 
@@ -93,6 +94,8 @@ SIGNATURES = {
     "fv_ivfpq_set_shard": (_i, [_vp, _i, _i]),
     "fv_ivfpq_search_candidates_dev": (_i, [_vp, _vp, _sz, _sz, _sz, _vp, _vp, _vp]),
     "fv_ivfpq_nlist": (_sz, [_vp]),
+    "fv_ivfpq_set_scan_mode": (_i, [_vp, _i]),
+    "fv_ivfpq_set_candidate_slots": (_i, [_vp, _sz]),
     "fv_ivfpq_coarse_dev": (_i, [_vp, _vp, _sz, _sz, _vp]),
     "fv_ivfpq_search_batch_cells_dev": (_i, [_vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp, _vp]),
     "fv_ivfpq_search_candidates_cells_dev": (_i, [_vp, _vp, _sz, _sz, _sz, _vp, _vp, _vp, _vp]),

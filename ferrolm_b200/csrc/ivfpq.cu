@@ -13,7 +13,7 @@
 #include <cstdlib>
 #include <numeric>
 
-#include "internal.h"
+#include "ivfpq_scan.h"
 
 namespace fv {
 
@@ -220,353 +220,6 @@ __global__ void gather_owned_kernel(const float* __restrict__ x, const uint32_t*
   }
 }
 
-// ------------------------------------------------------------------------------------------------
-// search: one block per query (ivfpq.rs:225-297)
-struct ScanArgs {
-  const float* queries;  // nq x pd
-  const u64* cells;      // nq x nprobe keys (distance, list), ascending
-  const float* centroids;
-  const float* codebooks;
-  const float* pre;  // may be null
-  const float* qtab; // nq x m x 256: per query, -dot(q_j, w) (inner product) or -2 dot(q_j, w) (L2 with tables)
-  const uint32_t* list_off;
-  const uint8_t* codes;
-  const uint32_t* ids;
-  const float* vectors;  // may be null
-  const uint32_t* owned_ids;  // list-sharded index: ascending ids of the kept vectors (row s of `vectors`); else null
-  uint32_t owned_n;
-  int shard_rank, shard_world;  // this shard scans the probed lists l with l % world == rank
-  int metric, pd, m, dsub, nprobe, keep, k;
-  int refine;        // 1: re-rank the kept candidates exactly
-  int np;            // producer warps (L2 with precomputed tables)
-  int cap;           // keys of the block's candidate buffer (a power of two, >= keep + 2 * threads)
-  int candidates;    // 1: write the kept candidates with both distances instead of the final k
-  uint32_t id_base;
-  u64* out_keys;             // nq x k        (candidates == 0)
-  fv_neighbor* out_adc;      // nq x keep     (candidates == 1)
-  float* out_exact;          // nq x keep
-  uint32_t* out_counts;      // nq
-  unsigned long long* rows_scanned;
-};
-
-// The query's part of the lookup tables for a whole batch (ivfpq.rs:236-238 inner product, :241-251 L2 with
-// precomputed tables): entry (j, e) = -dot(q_j, w_je) or -2 dot(q_j, w_je), the products summed in index order from
-// -0.0 as the reference's iterator sum does.  One block per (16 queries, sub-quantizer), one thread per entry: the
-// codebook is read once per 16 queries instead of once per query.
-template <int DSUB>  // 0: any sub-vector length; otherwise the codebook entry is held in registers
-__global__ void __launch_bounds__(256) query_tables_kernel(const float* __restrict__ queries, size_t nq, int pd,
-                                                           const float* __restrict__ codebooks, int m, int dsub,
-                                                           int is_ip, float* __restrict__ out) {
-  unsigned char* smem_raw = dyn_smem();
-  float* sqs = reinterpret_cast<float*>(smem_raw);  // [16][dsub]
-  const int j = blockIdx.y, e = threadIdx.x;
-  const size_t q0 = size_t(blockIdx.x) * 16;
-  for (int i = threadIdx.x; i < 16 * dsub; i += blockDim.x) {
-    const size_t qi = q0 + i / dsub;
-    sqs[i] = qi < nq ? queries[qi * size_t(pd) + j * dsub + (i % dsub)] : 0.f;
-  }
-  __syncthreads();
-  const float* wv = codebooks + (size_t(j) * KSUB + e) * dsub;
-  const size_t tab = size_t(m) * KSUB;
-  float wr[DSUB > 0 ? DSUB : 1];
-  if (DSUB > 0) {
-#pragma unroll
-    for (int t = 0; t < DSUB; ++t) wr[t] = __ldg(wv + t);
-  }
-  for (int qi = 0; qi < 16 && q0 + qi < nq; ++qi) {
-    float s = -0.0f;
-    if (DSUB > 0) {
-#pragma unroll
-      for (int t = 0; t < DSUB; ++t) s = __fadd_rn(s, __fmul_rn(sqs[qi * DSUB + t], wr[t]));
-    } else {
-      for (int t = 0; t < dsub; ++t) s = __fadd_rn(s, __fmul_rn(sqs[qi * dsub + t], __ldg(wv + t)));
-    }
-    out[(q0 + qi) * tab + size_t(j) * KSUB + e] = is_ip ? -s : __fmul_rn(-2.0f, s);
-  }
-}
-
-// Entry (code byte J) of sub-quantizer J's table.  `w` is the 32-bit word of the code that holds byte J, `lut_s` the
-// shared-memory address of the tables (a multiple of 1024): the byte, times 4, is moved into bits 2..9 by one shift,
-// masked and OR-ed onto the address by one logic op, and the table's offset J * 1024 rides in the load.
-template <int J>
-__device__ __forceinline__ float lut_entry(uint32_t w, uint32_t lut_s) {
-  const uint32_t sh = (J & 3) == 0 ? (w << 2) : (w >> ((J & 3) * 8 - 2));
-  const uint32_t addr = (sh & 0x3FCu) | lut_s;
-  float t;
-  asm volatile("ld.shared.f32 %0, [%1 + %2];" : "=f"(t) : "r"(addr), "n"(J * 1024));
-  return t;
-}
-
-template <bool M16, int R>
-__global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
-  unsigned char* smem_raw = dyn_smem();
-  const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-  const int tab = a.m * int(KSUB);
-  const bool use_pre = a.metric == FV_L2 && a.pre != nullptr;
-  // The lookup tables first: their shared-memory addresses are multiples of 1024, so a lookup address is formed by
-  // OR.  With precomputed tables there are two: NP producer warps build the next cell's table (pre[l] + the query's
-  // own table, both read from L2) while the other warps scan the current cell with the other one, so the L2 round
-  // trips of the build are off the scan's critical path and one barrier per cell is enough.
-  float* lut0 = reinterpret_cast<float*>(smem_raw);   // tab
-  float* lut1 = lut0 + tab;                           // tab (L2 with tables only)
-  float* sq = lut1 + (use_pre ? tab : 0);             // pd
-  float* srq = sq + a.pd;                             // pd
-  // Candidates: ONE unsorted buffer for the block.  A row whose key is below the bound is appended (a shared-memory
-  // counter hands out the slots); when the count passes `compact_at`, the block sorts the buffer, keeps the best
-  // `keep` and takes the keep-th key as the new bound.  One list per block sees every row, so its bound is the
-  // tightest the scan order allows (lists per warp each converged on the best of their own eighth and let 5-8x
-  // more rows in).
-  u64* lists = reinterpret_cast<u64*>(srq + a.pd);  // cap keys, then keep keys for the re-rank, then k
-  u64* rerank = lists + a.cap;
-  const size_t q = blockIdx.x;
-  const int NP = use_pre ? a.np : 0;    // producer warps
-  const int WC = W - NP, cw = w - NP;   // consumer warps; this warp's index among them (negative: a producer)
-  const float* qtab = a.qtab ? a.qtab + q * size_t(tab) : nullptr;
-
-  for (int c = tid; c < a.pd; c += blockDim.x) sq[c] = a.queries[q * size_t(a.pd) + c];
-  __shared__ int shared_count;  // keys in the buffer
-  if (tid == 0) shared_count = 0;
-  // inner product: the query's own table IS the lookup table (ivfpq.rs:236-238, :307)
-  if (a.metric == FV_INNER_PRODUCT)
-    for (int i = tid; i < tab / 4; i += blockDim.x)
-      reinterpret_cast<float4*>(lut0)[i] = __ldg(reinterpret_cast<const float4*>(qtab) + i);
-  __syncthreads();
-
-  u64 bound = FV_EMPTY_KEY;  // the keep-th best key at the last compaction
-  // Sorts the buffer, keeps the best `keep`, refreshes the bound.  Every thread calls it at a point where no append
-  // is in flight (right after a barrier every appending warp has passed); on return appends may resume at once.
-  auto compact = [&]() {
-    const int cnt = shared_count;
-    int n = 32;
-    while (n < cnt) n <<= 1;
-    for (int e = cnt + tid; e < n; e += blockDim.x) lists[e] = FV_EMPTY_KEY;
-    __syncthreads();
-    block_sort(lists, n);
-    const int kept = min(cnt, a.keep);
-    if (kept == a.keep) bound = lists[a.keep - 1];  // appends go behind it: it stays put
-    if (tid == 0) shared_count = kept;
-    __syncthreads();
-    return kept;
-  };
-  const int chunk_rows = WC * 32;  // rows the consumers scan per step: the most one step can append
-  // Compacting early and often keeps the bound tight (the sort is over the next power of two above the count, so a
-  // small buffer sorts fast).  `seen` is the highest count this warp's own appends have produced; the barrier that
-  // ends a piece ORs "seen >= compact_at" over the block, so all threads agree on compacting without reading the
-  // counter while others may already be appending again.  `cnt_ub` bounds the count from above for sizing a piece.
-  const int compact_at = min(a.cap - chunk_rows, 2 * a.keep + 64);
-  int seen = 0, cnt_ub = 0, rows_seen = 0;
-  auto piece_barrier = [&]() {
-    if (__syncthreads_or(seen >= compact_at)) {
-      cnt_ub = compact();
-      seen = 0;
-    } else {
-      cnt_ub = compact_at - 1;
-    }
-  };
-  unsigned long long scanned = 0;
-  // the next probed cell this block scans (a list-sharded index skips the other shards' lists), or -1
-  auto next_probe = [&](int p) {
-    for (++p; p < a.nprobe; ++p) {
-      const u64 c = a.cells[q * size_t(a.nprobe) + p];
-      if (c == FV_EMPTY_KEY) return -1;
-      if (a.shard_world > 1 && int(key_id(c) % uint32_t(a.shard_world)) != a.shard_rank) continue;
-      return p;
-    }
-    return -1;
-  };
-  // table of cell l with precomputed tables (ivfpq.rs:256-262), by `nthr` threads of which this is number `t`
-  auto build_pre = [&](float* dst, uint32_t l, int t, int nthr) {
-    const float4* pre = reinterpret_cast<const float4*>(a.pre + size_t(l) * tab);
-    const float4* qt = reinterpret_cast<const float4*>(qtab);
-#pragma unroll 8
-    for (int i = t; i < tab / 4; i += nthr) {
-      const float4 x = __ldg(pre + i), y = __ldg(qt + i);
-      reinterpret_cast<float4*>(dst)[i] =
-          make_float4(__fadd_rn(x.x, y.x), __fadd_rn(x.y, y.y), __fadd_rn(x.z, y.z), __fadd_rn(x.w, y.w));
-    }
-  };
-
-  int p = next_probe(-1);
-  int cur = 0;  // which table the scan reads
-  if (use_pre && p >= 0) {
-    build_pre(lut0, key_id(a.cells[q * size_t(a.nprobe) + p]), tid, int(blockDim.x));
-    __syncthreads();
-  }
-  while (p >= 0) {
-    const u64 cell = a.cells[q * size_t(a.nprobe) + p];
-    const uint32_t l = key_id(cell);
-    const int pnext = next_probe(p);
-    float* lut = cur ? lut1 : lut0;
-    float base;
-    if (use_pre) {
-      base = key_distance(cell);
-      if (cw < 0 && pnext >= 0)  // producers: the next cell's table, into the other buffer
-        build_pre(cur ? lut0 : lut1, key_id(a.cells[q * size_t(a.nprobe) + pnext]), tid, NP * 32);
-    } else if (a.metric == FV_L2) {  // ivfpq.rs:263-269
-      const float* cen = a.centroids + size_t(l) * a.pd;
-      for (int c = tid; c < a.pd; c += blockDim.x) srq[c] = __fsub_rn(sq[c], cen[c]);
-      __syncthreads();
-      for (int i = tid; i < tab; i += blockDim.x) {
-        const int j = i >> 8;
-        const float* wv = a.codebooks + size_t(i) * a.dsub;
-        float s = -0.0f;
-        for (int t = 0; t < a.dsub; ++t) {
-          const float d = __fsub_rn(srq[j * a.dsub + t], __ldg(wv + t));
-          s = __fadd_rn(s, __fmul_rn(d, d));
-        }
-        lut[i] = s;
-      }
-      base = 0.0f;
-      __syncthreads();
-    } else {
-      base = key_distance(cell);  // -dot(q, centroid), the same chain as ivfpq.rs:270
-    }
-    const uint32_t lut_s = uint32_t(__cvta_generic_to_shared(lut));
-    const size_t off = a.list_off[l];
-    const int len = int(a.list_off[l + 1] - off);
-    if (tid == 0) scanned += len;
-    // The list is scanned in pieces that cannot overflow the buffer even if every row is appended; every piece ends
-    // with the barrier that decides about compaction (the last one also hands the tables over).
-    for (int done = 0; done < len || done == 0;) {
-      const u64 eff = bound;
-      const uint32_t eff_hi = uint32_t(eff >> 32);
-      // The first pieces of a query are short (two steps, then as many rows as were scanned so far): until a bound
-      // exists every row is appended, so it pays to sort a few hundred keys early and scan the rest against a bound.
-      const int piece = min(((a.cap - cnt_ub) / chunk_rows) * chunk_rows, max(2 * chunk_rows, rows_seen));
-      const int end = min(len, done + piece);
-      if (cw >= 0) {
-        // R rows per lane and step: their 16-step add chains are independent and interleave
-        for (int r0 = done + cw * (32 * R); r0 < end; r0 += WC * 32 * R) {
-          float d[R];
-          bool pass[R];
-          uint32_t cws[R][4];
-#pragma unroll
-          for (int i = 0; i < R; ++i) {
-            const int r = r0 + i * 32 + lane;
-            d[i] = base;  // ivfpq.rs:273-276: base first, then the m table entries in order
-            pass[i] = false;
-            if (M16) {
-              uint4 cwv = make_uint4(0u, 0u, 0u, 0u);
-              if (r < end) cwv = __ldg(reinterpret_cast<const uint4*>(a.codes + (off + r) * 16));
-              cws[i][0] = cwv.x;
-              cws[i][1] = cwv.y;
-              cws[i][2] = cwv.z;
-              cws[i][3] = cwv.w;
-            }
-          }
-          if (M16) {
-            // byte j of the code, times 4, OR the table's shared address: one shift and one logic op per lookup
-#define FV_ADC_STEP(J)                                                              \
-  _Pragma("unroll") for (int i = 0; i < R; ++i) d[i] = __fadd_rn(d[i], lut_entry<J>(cws[i][(J) >> 2], lut_s));
-            FV_ADC_STEP(0) FV_ADC_STEP(1) FV_ADC_STEP(2) FV_ADC_STEP(3) FV_ADC_STEP(4) FV_ADC_STEP(5)
-            FV_ADC_STEP(6) FV_ADC_STEP(7) FV_ADC_STEP(8) FV_ADC_STEP(9) FV_ADC_STEP(10) FV_ADC_STEP(11)
-            FV_ADC_STEP(12) FV_ADC_STEP(13) FV_ADC_STEP(14) FV_ADC_STEP(15)
-#undef FV_ADC_STEP
-          } else {
-#pragma unroll
-            for (int i = 0; i < R; ++i) {
-              const int r = r0 + i * 32 + lane;
-              if (r < end) {
-                const uint8_t* code = a.codes + (off + r) * size_t(a.m);
-                for (int j = 0; j < a.m; ++j) d[i] = __fadd_rn(d[i], lut[j * 256 + code[j]]);
-              }
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < R; ++i) {
-            const int r = r0 + i * 32 + lane;
-            // the distance alone decides for almost every row; the id is fetched only when it can matter
-            pass[i] = r < end && d[i] < INFINITY && order_bits(d[i]) <= eff_hi;
-          }
-#pragma unroll
-          for (int i = 0; i < R; ++i) {
-            if (__any_sync(FV_FULL, pass[i])) {
-              const int r = r0 + i * 32 + lane;
-              u64 key = FV_EMPTY_KEY;
-              if (pass[i]) key = make_key(d[i], __ldg(a.ids + off + r));
-              const bool in = key < eff;
-              const unsigned hit = __ballot_sync(FV_FULL, in);
-              if (hit) {
-                int slot = 0;
-                if (lane == 0) slot = atomicAdd(&shared_count, __popc(hit));
-                slot = __shfl_sync(FV_FULL, slot, 0);
-                if (in) lists[slot + __popc(hit & ((1u << lane) - 1u))] = key;
-                seen = max(seen, slot + __popc(hit));
-              }
-            }
-          }
-        }
-      }
-      rows_seen += end - done;
-      done = end;
-      piece_barrier();
-      if (len == 0) break;
-    }
-    p = pnext;
-    cur = use_pre ? cur ^ 1 : 0;
-  }
-  if (tid == 0 && a.rows_scanned) atomicAdd(a.rows_scanned, scanned);
-
-  cnt_ub = compact();  // the best `keep` by (compressed distance, id), ascending, at the front of the buffer
-  for (int e = cnt_ub + tid; e < a.keep; e += blockDim.x) lists[e] = FV_EMPTY_KEY;
-  __syncthreads();
-  const u64* cand = lists;
-  if (!a.refine && !a.candidates) {
-    for (int e = tid; e < a.k; e += blockDim.x) a.out_keys[q * size_t(a.k) + e] = e < a.keep ? cand[e] : FV_EMPTY_KEY;
-    return;
-  }
-  // exact distances of the kept candidates (ivfpq.rs:285-296)
-  for (int e = tid; e < a.keep; e += blockDim.x) {
-    const u64 c = cand[e];
-    u64 rk = FV_EMPTY_KEY;
-    float ex = INFINITY;
-    if (c != FV_EMPTY_KEY) {
-      const uint32_t id = key_id(c);
-      size_t slot = size_t(id - a.id_base);
-      if (a.owned_ids) {  // position of the id among the ids this shard keeps (ascending)
-        uint32_t lo = 0, hi = a.owned_n;
-        while (lo < hi) {
-          const uint32_t mid = (lo + hi) >> 1;
-          if (a.owned_ids[mid] < id) lo = mid + 1;
-          else hi = mid;
-        }
-        slot = lo;
-      }
-      ex = exact_distance(a.metric, sq, a.vectors + slot * a.pd, a.pd);
-      rk = make_key(ex, id);
-    }
-    rerank[e] = rk;
-    if (a.candidates) {
-      fv_neighbor nb;
-      nb.id = c == FV_EMPTY_KEY ? 0xFFFFFFFFu : key_id(c);
-      nb.distance = c == FV_EMPTY_KEY ? INFINITY : key_distance(c);
-      a.out_adc[q * size_t(a.keep) + e] = nb;
-      a.out_exact[q * size_t(a.keep) + e] = ex;
-    }
-  }
-  if (a.candidates) {
-    if (w == 0) {
-      int cnt = 0;
-      for (int e0 = 0; e0 < a.keep; e0 += 32)
-        cnt += __popc(__ballot_sync(FV_FULL, (e0 + lane) < a.keep && cand[e0 + lane] != FV_EMPTY_KEY));
-      if (lane == 0) a.out_counts[q] = uint32_t(cnt);
-    }
-    return;
-  }
-  __syncthreads();
-  if (w == 1 || W == 1) {  // a second list of k entries, in the space of warp 1's (now unused) list or after
-    u64* fin = rerank + a.keep;
-    warp_list_init(fin, a.k);
-    u64 b2 = FV_EMPTY_KEY;
-    for (int e0 = 0; e0 < a.keep; e0 += 32) {
-      const int e = e0 + lane;
-      b2 = warp_list_offer(fin, a.k, e < a.keep ? rerank[e] : FV_EMPTY_KEY, b2);
-    }
-    __syncwarp();
-    for (int e = lane; e < a.k; e += 32) a.out_keys[q * size_t(a.k) + e] = fin[e];
-  }
-}
-
 }  // namespace fv
 
 // ------------------------------------------------------------------------------------------------
@@ -575,7 +228,7 @@ struct fv_ivfpq {
   ~fv_ivfpq() {
     fv::tc_free(ctc);
     centroids.release(); codebooks.release(); pre.release(); list_off.release(); owned_ids.release();
-    codes.release(); ids.release(); vectors.release();
+    codes.release(); ids.release(); vectors.release(); codes_t.release(); off16.release();
     if (ctx) fv::ctx_release(ctx);
   }
   int metric = 0;
@@ -592,6 +245,10 @@ struct fv_ivfpq {
   std::vector<uint32_t> h_off;  // nlist + 1
   DevBuf centroids, codebooks, pre, list_off, codes, ids, vectors;
   bool has_pre = false;
+  DevBuf codes_t, off16;  // m = 16: the sub-quantizer-major copy of the codes the list-major scan reads
+  bool has_codes_t = false;
+  int scan_mode = 0;      // 0 pick by size, 1 one block per query, 2 list-major whenever possible
+  int cand_slots = 0;     // list-major scan: candidate slots per query (0 = default)
 };
 
 namespace fv {
@@ -628,6 +285,16 @@ static int upload_offsets(fv_ivfpq* ix) {
   FV_TRY(ix->list_off.reserve((ix->nlist + 1) * sizeof(uint32_t)));
   FV_CUDA(cudaMemcpyAsync(ix->list_off.p, ix->h_off.data(), (ix->nlist + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice,
                           ix->ctx->stream));
+  return FV_OK;
+}
+
+// after the lists changed: the second copy of the codes (m = 16 only)
+static int refresh_transposed(fv_ivfpq* ix) {
+  ix->has_codes_t = false;
+  if (ix->m != 16) return FV_OK;
+  FV_TRY(build_transposed_codes(ix->ctx, ix->h_off.data(), ix->nlist, ix->list_off.as<uint32_t>(), ix->codes.as<uint8_t>(),
+                                &ix->codes_t, &ix->off16));
+  ix->has_codes_t = true;
   return FV_OK;
 }
 
@@ -745,6 +412,8 @@ int fv_ivfpq_train(fv_ctx* ctx, int metric, uint32_t dim, const float* sample, s
   ix->h_off.assign(ix->nlist + 1, 0);
   FV_TRY(fv::upload_quantizers(ix.get()));
   FV_TRY(fv::upload_offsets(ix.get()));
+  FV_TRY(ix->codes.reserve(16));
+  FV_TRY(fv::refresh_transposed(ix.get()));
   FV_CUDA(cudaStreamSynchronize(ctx->stream));
   *out = ix.release();
   return FV_OK;
@@ -887,6 +556,7 @@ static int ivfpq_add_impl(fv_ivfpq* ix, const float* vectors, size_t n_total, bo
     ix->count += n;
     ix->seen += n_chunk;
   }
+  FV_TRY(fv::refresh_transposed(ix));
   return FV_OK;
 }
 
@@ -941,70 +611,35 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
     return FV_OK;
   }
   FV_TRY(ctx->scratch[1].reserve(nq * kout * sizeof(u64)));
-  unsigned long long* d_rows = reinterpret_cast<unsigned long long*>(ctx->d_flags + 16);
-  FV_CUDA(cudaMemsetAsync(d_rows, 0, sizeof(unsigned long long), ctx->stream));
-  const bool use_pre = ix->metric == FV_L2 && ix->has_pre;
-  const size_t tab = ix->m * fv::KSUB;
-  const float* qtab = nullptr;
-  if (ix->metric == FV_INNER_PRODUCT || use_pre) {
-    FV_TRY(ctx->scratch[5].reserve(nq * tab * sizeof(float)));
-    qtab = ctx->scratch[5].as<float>();
-    dim3 grid(unsigned((nq + 15) / 16), unsigned(ix->m));
-    auto qk = ix->dsub == 8 ? fv::query_tables_kernel<8> : (ix->dsub == 4 ? fv::query_tables_kernel<4> : fv::query_tables_kernel<0>);
-    qk<<<grid, fv::KSUB, 16 * ix->dsub * sizeof(float), ctx->stream>>>(
-        q, nq, pd, ix->codebooks.as<float>(), int(ix->m), int(ix->dsub), ix->metric == FV_INNER_PRODUCT ? 1 : 0,
-        ctx->scratch[5].as<float>());
-    ctx->stats.launches++;
-    FV_CUDA(cudaGetLastError());
-  }
-  fv::ScanArgs a{};
-  a.queries = q;
-  a.qtab = qtab;
-  a.cells = cells;
-  a.centroids = ix->centroids.as<float>();
-  a.codebooks = ix->codebooks.as<float>();
-  a.pre = ix->has_pre ? ix->pre.as<float>() : nullptr;
-  a.list_off = ix->list_off.as<uint32_t>();
-  a.codes = ix->codes.as<uint8_t>();
-  a.ids = ix->ids.as<uint32_t>();
-  a.vectors = ix->keep ? ix->vectors.as<float>() : nullptr;
-  a.owned_ids = ix->shard_world > 1 ? ix->owned_ids.as<uint32_t>() : nullptr;
-  a.owned_n = uint32_t(ix->count);
-  a.shard_rank = ix->shard_rank;
-  a.shard_world = ix->shard_world;
-  a.metric = ix->metric;
-  a.pd = pd;
-  a.m = int(ix->m);
-  a.dsub = int(ix->dsub);
-  a.nprobe = np;
-  a.keep = int(keep);
-  a.k = int(k);
-  a.np = 2;
-  a.cap = 2048;
-  while (size_t(a.cap) < keep + 1024) a.cap <<= 1;
-  a.refine = rerank && !candidates ? 1 : 0;
-  a.candidates = candidates ? 1 : 0;
-  a.id_base = ix->id_base;
-  a.out_keys = ctx->scratch[1].as<u64>();
-  a.out_adc = d_adc;
-  a.out_exact = d_exact;
-  a.out_counts = d_counts;
-  a.rows_scanned = d_rows;
-  const int W = 8;
-  const size_t smem = (2 * size_t(pd) + tab * (use_pre ? 2 : 1)) * sizeof(float) + (size_t(a.cap) + keep + k) * sizeof(u64);
-  if (smem + 256 > ctx->smem_optin) return fv::fail(FV_ERR_UNSUPPORTED, "m, k * refine too large for shared memory");
-  auto kern = ix->m == 16 ? fv::ivfpq_scan_kernel<true, 2> : fv::ivfpq_scan_kernel<false, 1>;
-  if (smem > 40 * 1024) FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-  kern<<<unsigned(nq), W * 32, smem, ctx->stream>>>(a);
-  ctx->stats.launches++;
-  FV_CUDA(cudaGetLastError());
+  fv::ScanIndex si{};
+  si.centroids = ix->centroids.as<float>();
+  si.codebooks = ix->codebooks.as<float>();
+  si.pre = ix->has_pre ? ix->pre.as<float>() : nullptr;
+  si.list_off = ix->list_off.as<uint32_t>();
+  si.codes = ix->codes.as<uint8_t>();
+  si.ids = ix->ids.as<uint32_t>();
+  si.vectors = ix->keep ? ix->vectors.as<float>() : nullptr;
+  si.owned_ids = ix->shard_world > 1 ? ix->owned_ids.as<uint32_t>() : nullptr;
+  si.owned_n = uint32_t(ix->count);
+  si.shard_rank = ix->shard_rank;
+  si.shard_world = ix->shard_world;
+  si.metric = ix->metric;
+  si.pd = pd;
+  si.m = int(ix->m);
+  si.dsub = int(ix->dsub);
+  si.nlist = ix->nlist;
+  si.id_base = ix->id_base;
+  si.codes_t = ix->has_codes_t ? ix->codes_t.as<uint8_t>() : nullptr;
+  si.off16 = ix->has_codes_t ? ix->off16.as<uint32_t>() : nullptr;
+  fv::ScanOut so{};
+  so.keys = ctx->scratch[1].as<u64>();
+  so.adc = d_adc;
+  so.exact = d_exact;
+  so.counts = d_counts;
+  FV_TRY(fv::ivfpq_scan(ctx, si, q, nq, cells, np, int(keep), int(k), rerank, candidates, ix->scan_mode, ix->cand_slots, so));
+  if (!candidates) FV_TRY(fv::keys_to_neighbors(ctx, so.keys, nq, int(k), int(k), d_out, d_counts));
   fv::stage_mark(ctx);
-  if (!candidates) FV_TRY(fv::keys_to_neighbors(ctx, a.out_keys, nq, int(k), int(k), d_out, d_counts));
-  fv::stage_mark(ctx);
-  unsigned long long rows = 0;
-  FV_CUDA(cudaMemcpyAsync(&rows, d_rows, sizeof(rows), cudaMemcpyDeviceToHost, ctx->stream));
   FV_CUDA(cudaStreamSynchronize(ctx->stream));
-  ctx->stats.rows_scanned = rows;
   fv::stage_end(ctx);
   return FV_OK;
 }
@@ -1017,6 +652,18 @@ int fv_ivfpq_search_batch_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, s
 }
 
 size_t fv_ivfpq_nlist(const fv_ivfpq* ix) { return ix ? ix->nlist : 0; }
+
+int fv_ivfpq_set_candidate_slots(fv_ivfpq* ix, size_t slots) {
+  if (!ix || slots > 4096) return fv::fail(FV_ERR_ARG, "fv_ivfpq_set_candidate_slots: at most 4096 slots");
+  ix->cand_slots = int(slots);
+  return FV_OK;
+}
+
+int fv_ivfpq_set_scan_mode(fv_ivfpq* ix, int mode) {
+  if (!ix || mode < 0 || mode > 2) return fv::fail(FV_ERR_ARG, "fv_ivfpq_set_scan_mode: mode must be 0, 1 or 2");
+  ix->scan_mode = mode;
+  return FV_OK;
+}
 
 int fv_ivfpq_coarse_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t nprobe, uint64_t* d_cells) {
   if (!ix || (nq && (!d_queries || !d_cells))) return fv::fail(FV_ERR_ARG, "fv_ivfpq_coarse: null argument");
@@ -1237,6 +884,7 @@ int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out)
     FV_CUDA(cudaMemcpyAsync(ix->vectors.p, pv, nv * 4, cudaMemcpyHostToDevice, ctx->stream));
   }
   FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  FV_TRY(fv::refresh_transposed(ix.get()));
   // A loaded index reports the ids stored in the file; rows of the kept vectors are indexed by id.
   ix->id_base = 0;
   *out = ix.release();

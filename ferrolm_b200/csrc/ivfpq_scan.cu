@@ -1,0 +1,946 @@
+// IvfPq::search (ivfpq.rs:225-297) on the GPU: lookup tables, ADC scan, top-k and the optional exact re-rank.
+//
+// Two scans produce the same result.
+//
+//  * ivfpq_scan_kernel: one block per query.  Per probed cell the block builds the cell's table in shared memory and
+//    its lanes walk the list's rows (codes differ per lane: the sixteen lookups of a row land in random banks).
+//    It serves every index (any m, with or without precomputed tables), small batches, the SAMPLE pass and the
+//    fallback of the list-major scan.
+//
+//  * ivfpq_list_scan_kernel: list-major, for m = 16 with the query's table separable from the cell's
+//    (lut = pre[l] + qtab[q], ivfpq.rs:256-262, or lut = qtab[q] for inner product, :236-238).  The (query, probe)
+//    pairs of a batch are bucketed by list.  A task is (list, up to 1024 of its rows, up to 4 groups of 32 queries
+//    that probe it).  The 32 queries of a group sit one per LANE and a warp walks rows: every lane of a lookup
+//    reads the same table entry (sub-quantizer j, code c) of its own query, and the group's tables are stored
+//    entry-major -- word c * 36 + lane of the slice of sub-quantizer j -- so the 32 reads of a lookup fall into 32
+//    different banks: one shared-memory wavefront per 32 lookups instead of the ~2.7 of random codes.  Shared
+//    memory holds two such slices (one sub-quantizer each, 36 KB); the scan runs in 16 phases, one per
+//    sub-quantizer in the reference's order, and the partial sums of a lane's rows (64 per thread) wait in registers
+//    between phases, so every distance is base + lut[0] + ... + lut[15] added in that order: bit-identical to
+//    ivfpq.rs:272-276.  While a phase runs, the threads also build the next slice (coalesced reads of the queries'
+//    tables and of pre[l], one add, conflict-free 16-byte stores).  The code bytes come from a second,
+//    sub-quantizer-major copy of the lists, so one 16-byte broadcast read serves 16 rows of a phase.
+//    Candidates: a SAMPLE pass (the per-query kernel over each query's nearest probed list(s)) gives every query
+//    its best `keep` so far and thereby a bound; the list-major pass appends every row below the bound to the
+//    query's buffer in global memory; a finishing kernel merges buffer and sample, keeps the best `keep`
+//    and re-ranks.  A query whose buffer overflows is re-run by the per-query kernel.
+#include <algorithm>
+
+#include "ivfpq_scan.h"
+
+namespace fv {
+
+static const size_t KSUB = 256;
+
+// ------------------------------------------------------------------------------------------------
+struct ScanArgs {
+  const float* queries;  // nq x pd
+  const u64* cells;      // nq x nprobe keys (distance, list), ascending
+  const float* centroids;
+  const float* codebooks;
+  const float* pre;  // may be null
+  const float* qtab; // nq x m x 256: per query, -dot(q_j, w) (inner product) or -2 dot(q_j, w) (L2 with tables)
+  const uint32_t* list_off;
+  const uint8_t* codes;
+  const uint32_t* ids;
+  const float* vectors;  // may be null
+  const uint32_t* owned_ids;  // list-sharded index: ascending ids of the kept vectors (row s of `vectors`); else null
+  uint32_t owned_n;
+  int shard_rank, shard_world;  // this shard scans the probed lists l with l % world == rank
+  int metric, pd, m, dsub, nprobe, keep, k;
+  int refine;        // 1: re-rank the kept candidates exactly
+  int np;            // producer warps (L2 with precomputed tables)
+  int cap;           // keys of the block's candidate buffer (a power of two, >= keep + 2 * threads)
+  int candidates;    // 1: write the kept candidates with both distances instead of the final k
+  uint32_t id_base;
+  u64* out_keys;             // nq x k        (candidates == 0)
+  fv_neighbor* out_adc;      // nq x keep     (candidates == 1)
+  float* out_exact;          // nq x keep
+  uint32_t* out_counts;      // nq
+  unsigned long long* rows_scanned;
+  const uint32_t* qids;      // block b works on query qids[b] (null: query b)
+  // sample pass: stop after the probe that brings the rows seen to `sample_rows` (0: scan every probe), write the
+  // best `keep` keys to out_keys (k == keep) and the index of the first probe NOT scanned to sample_end[q]
+  int sample_rows;
+  uint32_t* sample_end;
+};
+
+// The query's part of the lookup tables for a whole batch (ivfpq.rs:236-238 inner product, :241-251 L2 with
+// precomputed tables): entry (j, e) = -dot(q_j, w_je) or -2 dot(q_j, w_je), the products summed in index order from
+// -0.0 as the reference's iterator sum does.  One block per (16 queries, sub-quantizer), one thread per entry: the
+// codebook is read once per 16 queries instead of once per query.
+template <int DSUB>  // 0: any sub-vector length; otherwise the codebook entry is held in registers
+__global__ void __launch_bounds__(256) query_tables_kernel(const float* __restrict__ queries, size_t nq, int pd,
+                                                           const float* __restrict__ codebooks, int m, int dsub,
+                                                           int is_ip, float* __restrict__ out) {
+  unsigned char* smem_raw = dyn_smem();
+  float* sqs = reinterpret_cast<float*>(smem_raw);  // [16][dsub]
+  const int j = blockIdx.y, e = threadIdx.x;
+  const size_t q0 = size_t(blockIdx.x) * 16;
+  for (int i = threadIdx.x; i < 16 * dsub; i += blockDim.x) {
+    const size_t qi = q0 + i / dsub;
+    sqs[i] = qi < nq ? queries[qi * size_t(pd) + j * dsub + (i % dsub)] : 0.f;
+  }
+  __syncthreads();
+  const float* wv = codebooks + (size_t(j) * KSUB + e) * dsub;
+  const size_t tab = size_t(m) * KSUB;
+  float wr[DSUB > 0 ? DSUB : 1];
+  if (DSUB > 0) {
+#pragma unroll
+    for (int t = 0; t < DSUB; ++t) wr[t] = __ldg(wv + t);
+  }
+  for (int qi = 0; qi < 16 && q0 + qi < nq; ++qi) {
+    float s = -0.0f;
+    if (DSUB > 0) {
+#pragma unroll
+      for (int t = 0; t < DSUB; ++t) s = __fadd_rn(s, __fmul_rn(sqs[qi * DSUB + t], wr[t]));
+    } else {
+      for (int t = 0; t < dsub; ++t) s = __fadd_rn(s, __fmul_rn(sqs[qi * dsub + t], __ldg(wv + t)));
+    }
+    out[(q0 + qi) * tab + size_t(j) * KSUB + e] = is_ip ? -s : __fmul_rn(-2.0f, s);
+  }
+}
+
+// Entry (code byte J) of sub-quantizer J's table.  `w` is the 32-bit word of the code that holds byte J, `lut_s` the
+// shared-memory address of the tables (a multiple of 1024): the byte, times 4, is moved into bits 2..9 by one shift,
+// masked and OR-ed onto the address by one logic op, and the table's offset J * 1024 rides in the load.
+template <int J>
+__device__ __forceinline__ float lut_entry(uint32_t w, uint32_t lut_s) {
+  const uint32_t sh = (J & 3) == 0 ? (w << 2) : (w >> ((J & 3) * 8 - 2));
+  const uint32_t addr = (sh & 0x3FCu) | lut_s;
+  float t;
+  asm volatile("ld.shared.f32 %0, [%1 + %2];" : "=f"(t) : "r"(addr), "n"(J * 1024));
+  return t;
+}
+
+// What follows the scan of a query, for both kernels: `cand` holds the query's best a.keep keys by (compressed
+// distance, id), ascending, padded with FV_EMPTY_KEY; `rerank` has room for a.keep + a.k keys; `sq` is the padded
+// query.  Writes the final k keys, or (candidates mode) the kept candidates with both distances and their count
+// (ivfpq.rs:285-296).  Called by every thread of the block.
+__device__ __forceinline__ void scan_tail(const ScanArgs& a, size_t q, const u64* cand, u64* rerank, const float* sq) {
+  const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  if (!a.refine && !a.candidates) {
+    for (int e = tid; e < a.k; e += blockDim.x) a.out_keys[q * size_t(a.k) + e] = e < a.keep ? cand[e] : FV_EMPTY_KEY;
+    return;
+  }
+  // exact distances of the kept candidates
+  for (int e = tid; e < a.keep; e += blockDim.x) {
+    const u64 c = cand[e];
+    u64 rk = FV_EMPTY_KEY;
+    float ex = INFINITY;
+    if (c != FV_EMPTY_KEY) {
+      const uint32_t id = key_id(c);
+      size_t slot = size_t(id - a.id_base);
+      if (a.owned_ids) {  // position of the id among the ids this shard keeps (ascending)
+        uint32_t lo = 0, hi = a.owned_n;
+        while (lo < hi) {
+          const uint32_t mid = (lo + hi) >> 1;
+          if (a.owned_ids[mid] < id) lo = mid + 1;
+          else hi = mid;
+        }
+        slot = lo;
+      }
+      ex = exact_distance(a.metric, sq, a.vectors + slot * a.pd, a.pd);
+      rk = make_key(ex, id);
+    }
+    rerank[e] = rk;
+    if (a.candidates) {
+      fv_neighbor nb;
+      nb.id = c == FV_EMPTY_KEY ? 0xFFFFFFFFu : key_id(c);
+      nb.distance = c == FV_EMPTY_KEY ? INFINITY : key_distance(c);
+      a.out_adc[q * size_t(a.keep) + e] = nb;
+      a.out_exact[q * size_t(a.keep) + e] = ex;
+    }
+  }
+  if (a.candidates) {
+    if (w == 0) {
+      int cnt = 0;
+      for (int e0 = 0; e0 < a.keep; e0 += 32)
+        cnt += __popc(__ballot_sync(FV_FULL, (e0 + lane) < a.keep && cand[e0 + lane] != FV_EMPTY_KEY));
+      if (lane == 0) a.out_counts[q] = uint32_t(cnt);
+    }
+    return;
+  }
+  __syncthreads();
+  if (w == 1 || W == 1) {  // a second list of k entries behind the re-ranked keys
+    u64* fin = rerank + a.keep;
+    warp_list_init(fin, a.k);
+    u64 b2 = FV_EMPTY_KEY;
+    for (int e0 = 0; e0 < a.keep; e0 += 32) {
+      const int e = e0 + lane;
+      b2 = warp_list_offer(fin, a.k, e < a.keep ? rerank[e] : FV_EMPTY_KEY, b2);
+    }
+    __syncwarp();
+    for (int e = lane; e < a.k; e += 32) a.out_keys[q * size_t(a.k) + e] = fin[e];
+  }
+}
+
+template <bool M16, int R>
+__global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
+  unsigned char* smem_raw = dyn_smem();
+  const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  const int tab = a.m * int(KSUB);
+  const bool use_pre = a.metric == FV_L2 && a.pre != nullptr;
+  // The lookup tables first: their shared-memory addresses are multiples of 1024, so a lookup address is formed by
+  // OR.  With precomputed tables there are two: NP producer warps build the next cell's table (pre[l] + the query's
+  // own table, both read from L2) while the other warps scan the current cell with the other one, so the L2 round
+  // trips of the build are off the scan's critical path and one barrier per cell is enough.
+  float* lut0 = reinterpret_cast<float*>(smem_raw);   // tab
+  float* lut1 = lut0 + tab;                           // tab (L2 with tables only)
+  float* sq = lut1 + (use_pre ? tab : 0);             // pd
+  float* srq = sq + a.pd;                             // pd
+  // Candidates: ONE unsorted buffer for the block.  A row whose key is below the bound is appended (a shared-memory
+  // counter hands out the slots); when the count passes `compact_at`, the block sorts the buffer, keeps the best
+  // `keep` and takes the keep-th key as the new bound.  One list per block sees every row, so its bound is the
+  // tightest the scan order allows (lists per warp each converged on the best of their own eighth and let 5-8x
+  // more rows in).
+  u64* lists = reinterpret_cast<u64*>(srq + a.pd);  // cap keys, then keep keys for the re-rank, then k
+  u64* rerank = lists + a.cap;
+  const size_t q = a.qids ? size_t(a.qids[blockIdx.x]) : size_t(blockIdx.x);
+  const int NP = use_pre ? a.np : 0;    // producer warps
+  const int WC = W - NP, cw = w - NP;   // consumer warps; this warp's index among them (negative: a producer)
+  const float* qtab = a.qtab ? a.qtab + q * size_t(tab) : nullptr;
+
+  for (int c = tid; c < a.pd; c += blockDim.x) sq[c] = a.queries[q * size_t(a.pd) + c];
+  __shared__ int shared_count;  // keys in the buffer
+  if (tid == 0) shared_count = 0;
+  // inner product: the query's own table IS the lookup table (ivfpq.rs:236-238, :307)
+  if (a.metric == FV_INNER_PRODUCT)
+    for (int i = tid; i < tab / 4; i += blockDim.x)
+      reinterpret_cast<float4*>(lut0)[i] = __ldg(reinterpret_cast<const float4*>(qtab) + i);
+  __syncthreads();
+
+  u64 bound = FV_EMPTY_KEY;  // the keep-th best key at the last compaction
+  // Sorts the buffer, keeps the best `keep`, refreshes the bound.  Every thread calls it at a point where no append
+  // is in flight (right after a barrier every appending warp has passed); on return appends may resume at once.
+  auto compact = [&]() {
+    const int cnt = shared_count;
+    int n = 32;
+    while (n < cnt) n <<= 1;
+    for (int e = cnt + tid; e < n; e += blockDim.x) lists[e] = FV_EMPTY_KEY;
+    __syncthreads();
+    block_sort(lists, n);
+    const int kept = min(cnt, a.keep);
+    if (kept == a.keep) bound = lists[a.keep - 1];  // appends go behind it: it stays put
+    if (tid == 0) shared_count = kept;
+    __syncthreads();
+    return kept;
+  };
+  const int chunk_rows = WC * 32;  // rows the consumers scan per step: the most one step can append
+  // Compacting early and often keeps the bound tight (the sort is over the next power of two above the count, so a
+  // small buffer sorts fast).  `seen` is the highest count this warp's own appends have produced; the barrier that
+  // ends a piece ORs "seen >= compact_at" over the block, so all threads agree on compacting without reading the
+  // counter while others may already be appending again.  `cnt_ub` bounds the count from above for sizing a piece.
+  const int compact_at = min(a.cap - chunk_rows, 2 * a.keep + 64);
+  int seen = 0, cnt_ub = 0, rows_seen = 0;
+  auto piece_barrier = [&]() {
+    if (__syncthreads_or(seen >= compact_at)) {
+      cnt_ub = compact();
+      seen = 0;
+    } else {
+      cnt_ub = compact_at - 1;
+    }
+  };
+  unsigned long long scanned = 0;
+  // the next probed cell this block scans (a list-sharded index skips the other shards' lists), or -1
+  auto next_probe = [&](int p) {
+    for (++p; p < a.nprobe; ++p) {
+      const u64 c = a.cells[q * size_t(a.nprobe) + p];
+      if (c == FV_EMPTY_KEY) return -1;
+      if (a.shard_world > 1 && int(key_id(c) % uint32_t(a.shard_world)) != a.shard_rank) continue;
+      return p;
+    }
+    return -1;
+  };
+  // table of cell l with precomputed tables (ivfpq.rs:256-262), by `nthr` threads of which this is number `t`
+  auto build_pre = [&](float* dst, uint32_t l, int t, int nthr) {
+    const float4* pre = reinterpret_cast<const float4*>(a.pre + size_t(l) * tab);
+    const float4* qt = reinterpret_cast<const float4*>(qtab);
+#pragma unroll 8
+    for (int i = t; i < tab / 4; i += nthr) {
+      const float4 x = __ldg(pre + i), y = __ldg(qt + i);
+      reinterpret_cast<float4*>(dst)[i] =
+          make_float4(__fadd_rn(x.x, y.x), __fadd_rn(x.y, y.y), __fadd_rn(x.z, y.z), __fadd_rn(x.w, y.w));
+    }
+  };
+
+  int p = next_probe(-1);
+  int cur = 0;  // which table the scan reads
+  int first_unscanned = a.nprobe;
+  if (use_pre && p >= 0) {
+    build_pre(lut0, key_id(a.cells[q * size_t(a.nprobe) + p]), tid, int(blockDim.x));
+    __syncthreads();
+  }
+  while (p >= 0) {
+    const u64 cell = a.cells[q * size_t(a.nprobe) + p];
+    const uint32_t l = key_id(cell);
+    const size_t off = a.list_off[l];
+    const int len = int(a.list_off[l + 1] - off);
+    int pnext = next_probe(p);
+    if (a.sample_rows && rows_seen + len >= a.sample_rows) {  // the sample pass ends with this cell
+      first_unscanned = pnext >= 0 ? pnext : a.nprobe;
+      pnext = -1;
+    }
+    float* lut = cur ? lut1 : lut0;
+    float base;
+    if (use_pre) {
+      base = key_distance(cell);
+      if (cw < 0 && pnext >= 0)  // producers: the next cell's table, into the other buffer
+        build_pre(cur ? lut0 : lut1, key_id(a.cells[q * size_t(a.nprobe) + pnext]), tid, NP * 32);
+    } else if (a.metric == FV_L2) {  // ivfpq.rs:263-269
+      const float* cen = a.centroids + size_t(l) * a.pd;
+      for (int c = tid; c < a.pd; c += blockDim.x) srq[c] = __fsub_rn(sq[c], cen[c]);
+      __syncthreads();
+      for (int i = tid; i < tab; i += blockDim.x) {
+        const int j = i >> 8;
+        const float* wv = a.codebooks + size_t(i) * a.dsub;
+        float s = -0.0f;
+        for (int t = 0; t < a.dsub; ++t) {
+          const float d = __fsub_rn(srq[j * a.dsub + t], __ldg(wv + t));
+          s = __fadd_rn(s, __fmul_rn(d, d));
+        }
+        lut[i] = s;
+      }
+      base = 0.0f;
+      __syncthreads();
+    } else {
+      base = key_distance(cell);  // -dot(q, centroid), the same chain as ivfpq.rs:270
+    }
+    const uint32_t lut_s = uint32_t(__cvta_generic_to_shared(lut));
+    if (tid == 0) scanned += len;
+    // The list is scanned in pieces that cannot overflow the buffer even if every row is appended; every piece ends
+    // with the barrier that decides about compaction (the last one also hands the tables over).
+    for (int done = 0; done < len || done == 0;) {
+      const u64 eff = bound;
+      const uint32_t eff_hi = uint32_t(eff >> 32);
+      // The first pieces of a query are short (two steps, then as many rows as were scanned so far): until a bound
+      // exists every row is appended, so it pays to sort a few hundred keys early and scan the rest against a bound.
+      const int piece = min(((a.cap - cnt_ub) / chunk_rows) * chunk_rows, max(2 * chunk_rows, rows_seen));
+      const int end = min(len, done + piece);
+      if (cw >= 0) {
+        // R rows per lane and step: their 16-step add chains are independent and interleave
+        for (int r0 = done + cw * (32 * R); r0 < end; r0 += WC * 32 * R) {
+          float d[R];
+          bool pass[R];
+          uint32_t cws[R][4];
+#pragma unroll
+          for (int i = 0; i < R; ++i) {
+            const int r = r0 + i * 32 + lane;
+            d[i] = base;  // ivfpq.rs:273-276: base first, then the m table entries in order
+            pass[i] = false;
+            if (M16) {
+              uint4 cwv = make_uint4(0u, 0u, 0u, 0u);
+              if (r < end) cwv = __ldg(reinterpret_cast<const uint4*>(a.codes + (off + r) * 16));
+              cws[i][0] = cwv.x;
+              cws[i][1] = cwv.y;
+              cws[i][2] = cwv.z;
+              cws[i][3] = cwv.w;
+            }
+          }
+          if (M16) {
+            // byte j of the code, times 4, OR the table's shared address: one shift and one logic op per lookup
+#define FV_ADC_STEP(J)                                                              \
+  _Pragma("unroll") for (int i = 0; i < R; ++i) d[i] = __fadd_rn(d[i], lut_entry<J>(cws[i][(J) >> 2], lut_s));
+            FV_ADC_STEP(0) FV_ADC_STEP(1) FV_ADC_STEP(2) FV_ADC_STEP(3) FV_ADC_STEP(4) FV_ADC_STEP(5)
+            FV_ADC_STEP(6) FV_ADC_STEP(7) FV_ADC_STEP(8) FV_ADC_STEP(9) FV_ADC_STEP(10) FV_ADC_STEP(11)
+            FV_ADC_STEP(12) FV_ADC_STEP(13) FV_ADC_STEP(14) FV_ADC_STEP(15)
+#undef FV_ADC_STEP
+          } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+              const int r = r0 + i * 32 + lane;
+              if (r < end) {
+                const uint8_t* code = a.codes + (off + r) * size_t(a.m);
+                for (int j = 0; j < a.m; ++j) d[i] = __fadd_rn(d[i], lut[j * 256 + code[j]]);
+              }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < R; ++i) {
+            const int r = r0 + i * 32 + lane;
+            // the distance alone decides for almost every row; the id is fetched only when it can matter
+            pass[i] = r < end && d[i] < INFINITY && order_bits(d[i]) <= eff_hi;
+          }
+#pragma unroll
+          for (int i = 0; i < R; ++i) {
+            if (__any_sync(FV_FULL, pass[i])) {
+              const int r = r0 + i * 32 + lane;
+              u64 key = FV_EMPTY_KEY;
+              if (pass[i]) key = make_key(d[i], __ldg(a.ids + off + r));
+              const bool in = key < eff;
+              const unsigned hit = __ballot_sync(FV_FULL, in);
+              if (hit) {
+                int slot = 0;
+                if (lane == 0) slot = atomicAdd(&shared_count, __popc(hit));
+                slot = __shfl_sync(FV_FULL, slot, 0);
+                if (in) lists[slot + __popc(hit & ((1u << lane) - 1u))] = key;
+                seen = max(seen, slot + __popc(hit));
+              }
+            }
+          }
+        }
+      }
+      rows_seen += end - done;
+      done = end;
+      piece_barrier();
+      if (len == 0) break;
+    }
+    p = pnext;
+    cur = use_pre ? cur ^ 1 : 0;
+  }
+  if (tid == 0 && a.rows_scanned) atomicAdd(a.rows_scanned, scanned);
+  if (tid == 0 && a.sample_end) a.sample_end[q] = uint32_t(first_unscanned);
+
+  cnt_ub = compact();  // the best `keep` by (compressed distance, id), ascending, at the front of the buffer
+  for (int e = cnt_ub + tid; e < a.keep; e += blockDim.x) lists[e] = FV_EMPTY_KEY;
+  __syncthreads();
+  scan_tail(a, q, lists, rerank, sq);
+}
+
+// ================================================================================================
+// The list-major scan.
+
+static constexpr int LS_THREADS = 512;                     // 16 warps, one block per SM
+static constexpr int LS_WARPS = LS_THREADS / 32;
+static constexpr int LS_NG = 4;                            // row groups (16 rows each) per warp: 64 partial sums per thread
+static constexpr int LS_CH = LS_WARPS * LS_NG * 16;        // rows of a list one task covers: 1024
+static constexpr int LS_STRIDE = 36;                       // words per table entry: 32 query slots + 4 so that 16-byte stores of
+                                                           // eight consecutive entries cover all banks
+static constexpr int LS_SLICE = 256 * LS_STRIDE;           // words of one sub-quantizer's slice
+static constexpr int LS_GB = 4;                            // query groups per task
+static constexpr size_t LS_SMEM = size_t(2) * LS_SLICE * 4 + size_t(16) * LS_CH;
+
+// How a list of `len` rows probed by `npairs` queries of the batch becomes tasks: equal row chunks of at most LS_CH
+// rows (multiples of 16) times blocks of LS_GB query groups.
+__host__ __device__ __forceinline__ uint32_t ls_chunks(uint32_t len) { return (len + LS_CH - 1) / LS_CH; }
+__host__ __device__ __forceinline__ uint32_t ls_chunk_rows(uint32_t len) {
+  const uint32_t n = ls_chunks(len);
+  return n ? ((len + n - 1) / n + 15) / 16 * 16 : 0;
+}
+__host__ __device__ __forceinline__ uint32_t ls_group_blocks(uint32_t npairs) {
+  return ((npairs + 31) / 32 + LS_GB - 1) / LS_GB;
+}
+__host__ __device__ __forceinline__ uint32_t ls_tasks(uint32_t len, uint32_t npairs) {
+  return (len && npairs) ? ls_chunks(len) * ls_group_blocks(npairs) : 0u;
+}
+
+// counters (u32 words): 0 next task, 1 number of tasks, 2 queries whose buffer overflowed, 3 number of pairs
+enum { LS_C_NEXT = 0, LS_C_TASKS = 1, LS_C_OVER = 2, LS_C_PAIRS = 3, LS_NCOUNTERS = 8 };
+
+struct PairArgs {
+  const u64* cells;
+  const uint32_t* sample_end;
+  size_t nq;
+  int nprobe, shard_rank, shard_world;
+  uint32_t* pair_cnt;   // nlist (zeroed): pairs per list
+  uint32_t* cursor;     // nlist (zeroed)
+  const uint32_t* pair_off;
+  uint2* pairs;         // (query, bits of the cell distance)
+};
+
+// One thread per query: the probes the sample pass left, counted per list (FILL = false) or filed under their
+// list (FILL = true).  The order of a list's pairs is whatever the atomics give; results do not depend on it.
+template <bool FILL>
+__global__ void pair_kernel(PairArgs a) {
+  const size_t q = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
+  if (q >= a.nq) return;
+  for (int p = int(a.sample_end[q]); p < a.nprobe; ++p) {
+    const u64 c = a.cells[q * size_t(a.nprobe) + p];
+    if (c == FV_EMPTY_KEY) break;
+    const uint32_t l = key_id(c);
+    if (a.shard_world > 1 && int(l % uint32_t(a.shard_world)) != a.shard_rank) continue;
+    if (FILL) {
+      const uint32_t slot = atomicAdd(a.cursor + l, 1u);
+      a.pairs[a.pair_off[l] + slot] = make_uint2(uint32_t(q), uint32_t(c >> 32));
+    } else {
+      atomicAdd(a.pair_cnt + l, 1u);
+    }
+  }
+}
+
+// One block: exclusive prefix sums over the lists of the pair counts and of the task counts.
+__global__ void __launch_bounds__(1024) pair_offsets_kernel(const uint32_t* __restrict__ pair_cnt,
+                                                            const uint32_t* __restrict__ list_off, size_t nlist,
+                                                            uint32_t* __restrict__ pair_off, uint32_t* __restrict__ task_off,
+                                                            uint32_t* __restrict__ counters) {
+  __shared__ uint32_t sp[1024], st[1024];
+  const int tid = threadIdx.x;
+  const size_t per = (nlist + 1023) / 1024;
+  const size_t l0 = min(nlist, size_t(tid) * per), l1 = min(nlist, l0 + per);
+  uint32_t np = 0, nt = 0;
+  for (size_t l = l0; l < l1; ++l) {
+    np += pair_cnt[l];
+    nt += ls_tasks(list_off[l + 1] - list_off[l], pair_cnt[l]);
+  }
+  sp[tid] = np;
+  st[tid] = nt;
+  __syncthreads();
+  for (int o = 1; o < 1024; o <<= 1) {  // inclusive scan
+    const uint32_t a = tid >= o ? sp[tid - o] : 0u, b = tid >= o ? st[tid - o] : 0u;
+    __syncthreads();
+    sp[tid] += a;
+    st[tid] += b;
+    __syncthreads();
+  }
+  uint32_t bp = sp[tid] - np, bt = st[tid] - nt;  // exclusive
+  for (size_t l = l0; l < l1; ++l) {
+    pair_off[l] = bp;
+    task_off[l] = bt;
+    bp += pair_cnt[l];
+    bt += ls_tasks(list_off[l + 1] - list_off[l], pair_cnt[l]);
+  }
+  if (tid == 1023) {
+    pair_off[nlist] = sp[1023];
+    task_off[nlist] = st[1023];
+    counters[LS_C_TASKS] = st[1023];
+    counters[LS_C_PAIRS] = sp[1023];
+  }
+}
+
+struct ListScanArgs {
+  const float* qtab;           // nq x 16 x 256
+  const float* pre;            // nlist x 16 x 256 (HAS_PRE)
+  const uint32_t* list_off;
+  const uint32_t* off16;
+  const uint8_t* codes_t;
+  const uint32_t* ids;
+  const uint32_t* pair_off;
+  const uint32_t* task_off;
+  const uint2* pairs;
+  uint32_t nlist;
+  const u64* sample_keys;      // nq x keep: the sample pass's best keys, ascending
+  int keep;
+  u64* cand;                   // nq x cap
+  uint32_t* cand_cnt;          // nq (zeroed); may pass cap: the query overflowed
+  int cap;
+  uint32_t* counters;
+  unsigned long long* rows_scanned;
+};
+
+template <bool HAS_PRE>
+__global__ void __launch_bounds__(LS_THREADS, 1) ivfpq_list_scan_kernel(ListScanArgs a) {
+  float* slice = reinterpret_cast<float*>(dyn_smem());                       // [2][LS_SLICE]
+  uint8_t* codes_s = reinterpret_cast<uint8_t*>(slice + 2 * LS_SLICE);       // [16][LS_CH]
+  __shared__ __align__(16) uint32_t s_q[2][32];   // the queries of the current and of the next group, by slot
+  __shared__ uint32_t s_task[8];
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int fc = tid & 255, fh = tid >> 8;        // table building: this thread's entry and its half of the slots
+  const uint32_t ntasks = a.counters[LS_C_TASKS];
+  unsigned long long scanned = 0;
+
+  for (;;) {
+    if (tid == 0) {
+      const uint32_t t = atomicAdd(a.counters + LS_C_NEXT, 1u);
+      s_task[0] = t;
+      if (t < ntasks) {
+        uint32_t lo = 0, hi = a.nlist;  // the list l with task_off[l] <= t < task_off[l + 1]
+        while (hi - lo > 1) {
+          const uint32_t mid = (lo + hi) >> 1;
+          if (a.task_off[mid] <= t) lo = mid;
+          else hi = mid;
+        }
+        const uint32_t l = lo, local = t - a.task_off[l];
+        const uint32_t npair = a.pair_off[l + 1] - a.pair_off[l];
+        const uint32_t len = a.list_off[l + 1] - a.list_off[l];
+        const uint32_t ngb = ls_group_blocks(npair);
+        s_task[1] = l;
+        s_task[2] = (local / ngb) * ls_chunk_rows(len);   // first row of the chunk
+        s_task[3] = (local % ngb) * LS_GB;                // first query group
+      }
+    }
+    __syncthreads();
+    if (s_task[0] >= ntasks) break;
+    const uint32_t l = s_task[1], r0 = s_task[2], g0 = s_task[3];
+    const uint32_t pbase = a.pair_off[l], npair = a.pair_off[l + 1] - pbase;
+    const uint32_t loff = a.list_off[l], len = a.list_off[l + 1] - loff;
+    const int nrows = r0 < len ? int(min(len - r0, ls_chunk_rows(len))) : 0;  // (rounding can leave a last chunk empty)
+    const int rows_pad = (nrows + 15) & ~15;
+    const int ngroups = int(min(uint32_t(LS_GB), (npair + 31) / 32 - g0));
+    {  // this chunk's code bytes, sub-quantizer w by warp w
+      const uint32_t len16 = a.off16[l + 1] - a.off16[l];
+      const uint4* src = reinterpret_cast<const uint4*>(a.codes_t + size_t(a.off16[l]) * 16 + size_t(w) * len16 + r0);
+      uint4* dst = reinterpret_cast<uint4*>(codes_s + w * LS_CH);
+      for (int v = lane; v < rows_pad / 16; v += 32) dst[v] = __ldg(src + v);
+    }
+    // the pair of slot `lane` of group g: (query, base distance, slot in use)
+    uint32_t q_cur, q_nxt = 0;
+    float base_cur, base_nxt = 0.f;
+    bool valid_cur, valid_nxt = false;
+    auto load_pair = [&](uint32_t g, uint32_t& qo, float& bo, bool& vo) {
+      const uint32_t i = g * 32 + lane;
+      vo = i < npair;
+      const uint2 pr = a.pairs[pbase + (vo ? i : g * 32)];  // an unused slot repeats the group's first query
+      qo = pr.x;
+      bo = __uint_as_float(pr.y);
+    };
+    load_pair(g0, q_cur, base_cur, valid_cur);
+    if (w == 0) s_q[0][lane] = q_cur;
+    __syncthreads();
+
+    // Builds quarter `pc` of the slice of sub-quantizer fj for the group whose queries are in s_q[par]:
+    // entry fc of four queries (slots fh * 16 + pc * 4 ..), read from their tables, plus pre[l]'s entry.
+    auto fill_load = [&](int par, int fj, int pc, float (&v)[4]) {
+      const uint4 qs = *reinterpret_cast<const uint4*>(&s_q[par][fh * 16 + pc * 4]);
+      const float* src = a.qtab + fj * 256 + fc;
+      v[0] = __ldg(src + size_t(qs.x) * 4096);
+      v[1] = __ldg(src + size_t(qs.y) * 4096);
+      v[2] = __ldg(src + size_t(qs.z) * 4096);
+      v[3] = __ldg(src + size_t(qs.w) * 4096);
+    };
+    auto fill_store = [&](int buf, int pc, float prev, const float (&v)[4]) {
+      float4 o;
+      if (HAS_PRE) o = make_float4(__fadd_rn(prev, v[0]), __fadd_rn(prev, v[1]), __fadd_rn(prev, v[2]), __fadd_rn(prev, v[3]));
+      else o = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(slice + buf * LS_SLICE + fc * LS_STRIDE + fh * 16 + pc * 4) = o;
+    };
+    const float* pre_l = HAS_PRE ? a.pre + size_t(l) * 4096 + fc : nullptr;
+    {  // the first slice of the first group: nothing to overlap it with
+      const float prev = HAS_PRE ? __ldg(pre_l) : 0.f;
+      float v[4][4];
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) fill_load(0, 0, pc, v[pc]);
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) fill_store(0, pc, prev, v[pc]);
+    }
+    __syncthreads();
+
+    for (int gi = 0; gi < ngroups; ++gi) {
+      float acc[LS_NG][16];
+#pragma unroll
+      for (int g = 0; g < LS_NG; ++g)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[g][i] = base_cur;  // ivfpq.rs:273: the distance starts at the cell's base
+      const bool more = gi + 1 < ngroups;
+      if (more) {
+        load_pair(g0 + gi + 1, q_nxt, base_nxt, valid_nxt);
+        if (w == 0) s_q[(gi + 1) & 1][lane] = q_nxt;  // read from phase 15 on: many barriers away
+      }
+#pragma unroll 1
+      for (int j = 0; j < 16; ++j) {
+        // this phase adds sub-quantizer j from buffer j & 1 and builds the next slice into the other one:
+        // sub-quantizer j + 1 of this group, or sub-quantizer 0 of the next group
+        const int fj = (j + 1) & 15;
+        const int par = j < 15 ? (gi & 1) : ((gi + 1) & 1);
+        const bool do_fill = j < 15 || more;
+        const float* tb = slice + (j & 1) * LS_SLICE + lane;
+        const float prev = (HAS_PRE && do_fill) ? __ldg(pre_l + fj * 256) : 0.f;
+#pragma unroll
+        for (int g = 0; g < LS_NG; ++g) {
+          float v[4];
+          if (do_fill) fill_load(par, fj, g, v);
+          const int G = g * LS_WARPS + w;
+          if (G * 16 < rows_pad) {
+            const uint4 cw = *reinterpret_cast<const uint4*>(codes_s + j * LS_CH + G * 16);
+            const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const uint32_t c = (cws[i >> 2] >> ((i & 3) * 8)) & 0xFFu;
+              acc[g][i] = __fadd_rn(acc[g][i], tb[c * LS_STRIDE]);
+            }
+          }
+          if (do_fill) fill_store((j + 1) & 1, g, prev, v);
+        }
+        __syncthreads();
+      }
+      // rows below the query's bound become candidates
+      {
+        const u64 tau = a.sample_keys[size_t(q_cur) * a.keep + (a.keep - 1)];
+        const float tau_d = tau == FV_EMPTY_KEY ? INFINITY : key_distance(tau);
+        const uint32_t nvalid = min(32u, npair - (g0 + gi) * 32);
+        if (tid == 0) scanned += (unsigned long long)nrows * nvalid;
+        if (valid_cur) {
+#pragma unroll
+          for (int g = 0; g < LS_NG; ++g) {
+            const int G = g * LS_WARPS + w;
+            if (G * 16 < nrows) {
+              float mn = acc[g][0];
+#pragma unroll
+              for (int i = 1; i < 16; ++i) mn = fminf(mn, acc[g][i]);
+              if (mn <= tau_d) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  const int row = G * 16 + i;
+                  const float d = acc[g][i];
+                  if (d <= tau_d && d < INFINITY && row < nrows) {
+                    const u64 key = make_key(d, __ldg(a.ids + loff + r0 + row));
+                    if (key < tau) {
+                      const uint32_t slot = atomicAdd(a.cand_cnt + q_cur, 1u);
+                      if (slot < uint32_t(a.cap)) a.cand[size_t(q_cur) * a.cap + slot] = key;
+                    }
+                  }
+                }
+              }
+            }
+          }
+        }
+      }
+      q_cur = q_nxt;
+      base_cur = base_nxt;
+      valid_cur = valid_nxt;
+    }
+  }
+  if (tid == 0 && a.rows_scanned && scanned) atomicAdd(a.rows_scanned, scanned);
+}
+
+struct FinishArgs {
+  const u64* sample_keys;
+  const u64* cand;
+  const uint32_t* cand_cnt;
+  int cap;
+  uint32_t* counters;
+  uint32_t* over_ids;
+};
+
+// One block per query: the best `keep` of (sample pass's keys + appended candidates), then the common tail.
+__global__ void __launch_bounds__(256) ivfpq_finish_kernel(ScanArgs a, FinishArgs f, int n2max) {
+  u64* lists = reinterpret_cast<u64*>(dyn_smem());  // n2max keys
+  u64* rerank = lists + n2max;                      // keep + k
+  float* sq = reinterpret_cast<float*>(rerank + a.keep + a.k);
+  const size_t q = blockIdx.x;
+  const int tid = threadIdx.x;
+  const uint32_t cnt = f.cand_cnt[q];
+  if (cnt > uint32_t(f.cap)) {  // the per-query kernel re-runs this query
+    if (tid == 0) f.over_ids[atomicAdd(f.counters + LS_C_OVER, 1u)] = uint32_t(q);
+    return;
+  }
+  const int total = a.keep + int(cnt);
+  int n = 32;
+  while (n < total) n <<= 1;
+  for (int e = tid; e < n; e += blockDim.x) {
+    u64 key = FV_EMPTY_KEY;
+    if (e < a.keep) key = f.sample_keys[q * size_t(a.keep) + e];
+    else if (e < total) key = f.cand[q * size_t(f.cap) + (e - a.keep)];
+    lists[e] = key;
+  }
+  for (int c = tid; c < a.pd; c += blockDim.x) sq[c] = a.queries[q * size_t(a.pd) + c];
+  __syncthreads();
+  block_sort(lists, n);
+  __syncthreads();
+  scan_tail(a, q, lists, rerank, sq);
+}
+
+// codes (rows x 16, by list) -> sub-quantizer-major copy, lists padded to 16 rows with zero bytes
+__global__ void transpose_codes_kernel(const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ off16,
+                                       const uint8_t* __restrict__ codes, uint8_t* __restrict__ out) {
+  const size_t l = blockIdx.x;
+  const uint32_t off = list_off[l], len = list_off[l + 1] - off;
+  const uint32_t len16 = off16[l + 1] - off16[l];
+  uint8_t* dst = out + size_t(off16[l]) * 16;
+  for (uint32_t r = threadIdx.x; r < len16; r += blockDim.x) {
+    uint4 cw = make_uint4(0u, 0u, 0u, 0u);
+    if (r < len) cw = *reinterpret_cast<const uint4*>(codes + (size_t(off) + r) * 16);
+    const uint32_t wds[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) dst[size_t(j) * len16 + r] = uint8_t((wds[j >> 2] >> ((j & 3) * 8)) & 0xFFu);
+  }
+}
+
+int build_transposed_codes(fv_ctx* ctx, const uint32_t* h_off, size_t nlist, const uint32_t* d_list_off,
+                           const uint8_t* d_codes, DevBuf* codes_t, DevBuf* off16) {
+  std::vector<uint32_t> o16(nlist + 1, 0);
+  for (size_t l = 0; l < nlist; ++l) {
+    const uint64_t next = uint64_t(o16[l]) + ((h_off[l + 1] - h_off[l] + 15u) & ~15u);
+    if (next > 0xFFFFFFF0ull) return fail(FV_ERR_UNSUPPORTED, "more than 2^32 padded rows");
+    o16[l + 1] = uint32_t(next);
+  }
+  FV_TRY(off16->reserve((nlist + 1) * sizeof(uint32_t)));
+  FV_TRY(codes_t->reserve(size_t(o16[nlist]) * 16 + 16));
+  FV_CUDA(cudaMemcpyAsync(off16->p, o16.data(), (nlist + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+  if (o16[nlist]) {
+    transpose_codes_kernel<<<unsigned(nlist), 256, 0, ctx->stream>>>(d_list_off, off16->as<uint32_t>(), d_codes,
+                                                                    codes_t->as<uint8_t>());
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
+  }
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));  // o16 leaves scope
+  return FV_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+static int launch_block_scan(fv_ctx* ctx, const ScanArgs& a, size_t nblocks, bool use_pre) {
+  const size_t tab = size_t(a.m) * KSUB;
+  const size_t smem = (2 * size_t(a.pd) + tab * (use_pre ? 2 : 1)) * sizeof(float) +
+                      (size_t(a.cap) + size_t(a.keep) + size_t(a.k)) * sizeof(u64);
+  if (smem + 256 > ctx->smem_optin) return fail(FV_ERR_UNSUPPORTED, "m, k * refine too large for shared memory");
+  auto kern = a.m == 16 ? ivfpq_scan_kernel<true, 2> : ivfpq_scan_kernel<false, 1>;
+  if (smem > 40 * 1024) FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  kern<<<unsigned(nblocks), 256, smem, ctx->stream>>>(a);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  return FV_OK;
+}
+
+// Stages (fv_stats.stage_ms) of an IVF-PQ search: 0 coarse cells (marked by the caller), 1 query tables and, on the
+// list-major path, the sample pass, 2 bucketing the (query, probe) pairs by list, 3 the scan, 4 merging, re-ranking
+// and any re-run of overflowed queries, 5 keys -> neighbours (marked by the caller).  The per-query kernel alone:
+// everything in stage 3, stages 2 and 4 empty.
+int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, const u64* cells, int nprobe, int keep,
+               int k, bool refine, bool candidates, int mode, int cand_slots, const ScanOut& out) {
+  const bool use_pre = ix.metric == FV_L2 && ix.pre != nullptr;
+  const bool separable = use_pre || ix.metric == FV_INNER_PRODUCT;
+  const size_t tab = size_t(ix.m) * KSUB;
+  unsigned long long* d_rows = reinterpret_cast<unsigned long long*>(ctx->d_flags + 16);  // [0] per-query kernel, [1] list-major
+  FV_CUDA(cudaMemsetAsync(d_rows, 0, 2 * sizeof(unsigned long long), ctx->stream));
+  const float* qtab = nullptr;
+  if (separable) {
+    FV_TRY(ctx->scratch[5].reserve(nq * tab * sizeof(float)));
+    qtab = ctx->scratch[5].as<float>();
+    dim3 grid(unsigned((nq + 15) / 16), unsigned(ix.m));
+    auto qk = ix.dsub == 8 ? query_tables_kernel<8> : (ix.dsub == 4 ? query_tables_kernel<4> : query_tables_kernel<0>);
+    qk<<<grid, KSUB, 16 * ix.dsub * sizeof(float), ctx->stream>>>(q, nq, ix.pd, ix.codebooks, ix.m, ix.dsub,
+                                                                   ix.metric == FV_INNER_PRODUCT ? 1 : 0,
+                                                                   ctx->scratch[5].as<float>());
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
+  }
+  ScanArgs a{};
+  a.queries = q;
+  a.qtab = qtab;
+  a.cells = cells;
+  a.centroids = ix.centroids;
+  a.codebooks = ix.codebooks;
+  a.pre = ix.pre;
+  a.list_off = ix.list_off;
+  a.codes = ix.codes;
+  a.ids = ix.ids;
+  a.vectors = ix.vectors;
+  a.owned_ids = ix.owned_ids;
+  a.owned_n = ix.owned_n;
+  a.shard_rank = ix.shard_rank;
+  a.shard_world = ix.shard_world;
+  a.metric = ix.metric;
+  a.pd = ix.pd;
+  a.m = ix.m;
+  a.dsub = ix.dsub;
+  a.nprobe = nprobe;
+  a.keep = keep;
+  a.k = k;
+  a.np = 2;
+  a.cap = 2048;
+  while (a.cap < keep + 1024) a.cap <<= 1;
+  a.refine = refine && !candidates ? 1 : 0;
+  a.candidates = candidates ? 1 : 0;
+  a.id_base = ix.id_base;
+  a.out_keys = out.keys;
+  a.out_adc = out.adc;
+  a.out_exact = out.exact;
+  a.out_counts = out.counts;
+  a.rows_scanned = d_rows;
+
+  // The list-major scan needs enough queries per list to fill its 32-lane groups: on average at least 24 pairs per
+  // owned list after the sample pass has taken each query's first probe.
+  const size_t owned_lists = std::max<size_t>(1, ix.nlist / size_t(std::max(1, ix.shard_world)));
+  bool list_major = ix.m == 16 && ix.codes_t && separable && nprobe >= 2 && keep <= 1024 && mode != 1;
+  if (list_major && mode == 0) list_major = nq * size_t(nprobe - 1) >= 24 * owned_lists && nq >= 64;
+  if (!list_major) {
+    stage_mark(ctx);  // 1
+    stage_mark(ctx);  // 2 (empty)
+    FV_TRY(launch_block_scan(ctx, a, nq, use_pre));
+    stage_mark(ctx);  // 3
+    stage_mark(ctx);  // 4 (empty)
+  } else {
+    // candidate slots per query: 1024, fewer when the buffers of a large batch would pass 256 MB
+    int cap = 1024;
+    while (cap > 256 && nq * size_t(cap) * sizeof(u64) > (size_t(256) << 20)) cap >>= 1;
+    if (cand_slots > 0) cap = std::min(cand_slots, 4096);
+    const size_t nl = ix.nlist;
+    // small arrays in one allocation; the first `nzero` words start at zero
+    const size_t o_cnt = 0, o_cur = nl, o_cc = 2 * nl, o_ctr = (2 * nl + nq + 1) & ~size_t(1);
+    const size_t nzero = o_ctr + LS_NCOUNTERS;
+    const size_t o_poff = nzero, o_toff = o_poff + nl + 1, o_send = o_toff + nl + 1, o_over = o_send + nq;
+    FV_TRY(ctx->scratch[8].reserve((o_over + nq) * sizeof(uint32_t)));
+    uint32_t* sm = ctx->scratch[8].as<uint32_t>();
+    FV_CUDA(cudaMemsetAsync(sm, 0, nzero * sizeof(uint32_t), ctx->stream));
+    FV_TRY(ctx->scratch[6].reserve(nq * size_t(keep) * sizeof(u64)));
+    FV_TRY(ctx->scratch[7].reserve(nq * size_t(nprobe) * sizeof(uint2) + 16));
+    FV_TRY(ctx->scratch[9].reserve(nq * size_t(cap) * sizeof(u64)));
+    u64* sample_keys = ctx->scratch[6].as<u64>();
+    // sample pass: each query's nearest probed list(s) until `keep` rows (at least 256) were seen
+    ScanArgs s = a;
+    s.k = keep;
+    s.refine = 0;
+    s.candidates = 0;
+    s.out_keys = sample_keys;
+    s.sample_rows = std::max(keep, 256);
+    s.sample_end = sm + o_send;
+    FV_TRY(launch_block_scan(ctx, s, nq, use_pre));
+    stage_mark(ctx);  // 1
+    PairArgs pa{};
+    pa.cells = cells;
+    pa.sample_end = sm + o_send;
+    pa.nq = nq;
+    pa.nprobe = nprobe;
+    pa.shard_rank = ix.shard_rank;
+    pa.shard_world = ix.shard_world;
+    pa.pair_cnt = sm + o_cnt;
+    pa.cursor = sm + o_cur;
+    pa.pair_off = sm + o_poff;
+    pa.pairs = ctx->scratch[7].as<uint2>();
+    const unsigned qblocks = unsigned((nq + 255) / 256);
+    pair_kernel<false><<<qblocks, 256, 0, ctx->stream>>>(pa);
+    pair_offsets_kernel<<<1, 1024, 0, ctx->stream>>>(sm + o_cnt, ix.list_off, nl, sm + o_poff, sm + o_toff, sm + o_ctr);
+    pair_kernel<true><<<qblocks, 256, 0, ctx->stream>>>(pa);
+    ctx->stats.launches += 3;
+    FV_CUDA(cudaGetLastError());
+    stage_mark(ctx);  // 2
+    ListScanArgs la{};
+    la.qtab = qtab;
+    la.pre = ix.pre;
+    la.list_off = ix.list_off;
+    la.off16 = ix.off16;
+    la.codes_t = ix.codes_t;
+    la.ids = ix.ids;
+    la.pair_off = sm + o_poff;
+    la.task_off = sm + o_toff;
+    la.pairs = pa.pairs;
+    la.nlist = uint32_t(nl);
+    la.sample_keys = sample_keys;
+    la.keep = keep;
+    la.cand = ctx->scratch[9].as<u64>();
+    la.cand_cnt = sm + o_cc;
+    la.cap = cap;
+    la.counters = sm + o_ctr;
+    la.rows_scanned = d_rows + 1;
+    auto lk = use_pre ? ivfpq_list_scan_kernel<true> : ivfpq_list_scan_kernel<false>;
+    FV_CUDA(cudaFuncSetAttribute(lk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(LS_SMEM)));
+    lk<<<ctx->sm_count, LS_THREADS, LS_SMEM, ctx->stream>>>(la);
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
+    stage_mark(ctx);  // 3
+    FinishArgs fa{};
+    fa.sample_keys = sample_keys;
+    fa.cand = la.cand;
+    fa.cand_cnt = la.cand_cnt;
+    fa.cap = cap;
+    fa.counters = sm + o_ctr;
+    fa.over_ids = sm + o_over;
+    int n2max = 32;
+    while (n2max < keep + cap) n2max <<= 1;
+    const size_t fsmem = (size_t(n2max) + size_t(keep) + size_t(k)) * sizeof(u64) + size_t(ix.pd) * sizeof(float);
+    if (fsmem + 256 > ctx->smem_optin) return fail(FV_ERR_UNSUPPORTED, "k * refine too large for shared memory");
+    if (fsmem > 40 * 1024)
+      FV_CUDA(cudaFuncSetAttribute(ivfpq_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(fsmem)));
+    ivfpq_finish_kernel<<<unsigned(nq), 256, fsmem, ctx->stream>>>(a, fa, n2max);
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
+    uint32_t n_over = 0;
+    FV_CUDA(cudaMemcpyAsync(&n_over, sm + o_ctr + LS_C_OVER, sizeof(n_over), cudaMemcpyDeviceToHost, ctx->stream));
+    FV_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (n_over) {  // buffers that ran over: those queries once more, by the per-query kernel (their rows are counted already)
+      ScanArgs r = a;
+      r.qids = sm + o_over;
+      r.rows_scanned = nullptr;
+      FV_TRY(launch_block_scan(ctx, r, n_over, use_pre));
+    }
+    ctx->stats.uncertified = n_over;
+    stage_mark(ctx);  // 4
+  }
+  unsigned long long rows[2] = {0, 0};
+  FV_CUDA(cudaMemcpyAsync(rows, d_rows, sizeof(rows), cudaMemcpyDeviceToHost, ctx->stream));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  ctx->stats.rows_scanned = rows[0] + rows[1];
+  ctx->stats.rows_list_scan = rows[1];
+  return FV_OK;
+}
+
+}  // namespace fv

@@ -107,7 +107,7 @@ class Context:
         check(lib().fv_ctx_stats(self._h, C.byref(s)))
         return {"launches": s.launches, "uncertified": s.uncertified, "rows_scanned": s.rows_scanned,
                 "dist_evals": s.dist_evals, "expansions": s.expansions, "regrown": s.regrown,
-                "stage_ms": list(s.stage_ms)}
+                "stage_ms": list(s.stage_ms), "rows_list_scan": s.rows_list_scan}
 
     def stream_handle(self) -> int:
         return lib().fv_ctx_stream(self._h) or 0
@@ -293,6 +293,14 @@ class IvfPq:
     def set_shard(self, rank: int, world: int):
         """Keep and scan only the inverted lists l with l % world == rank (give every shard the same rows)."""
         check(lib().fv_ivfpq_set_shard(self._h, rank, world))
+
+    def set_scan_mode(self, mode: int):
+        """0 chosen by size, 1 one block per query, 2 the list-major scan whenever the index allows it."""
+        check(lib().fv_ivfpq_set_scan_mode(self._h, mode))
+
+    def set_candidate_slots(self, slots: int):
+        """Candidate slots per query of the list-major scan (0 = default); overflowing queries are re-run."""
+        check(lib().fv_ivfpq_set_candidate_slots(self._h, slots))
 
     def __len__(self) -> int:
         return lib().fv_ivfpq_len(self._h)

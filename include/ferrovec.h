@@ -68,12 +68,13 @@ void* fv_ctx_stream(fv_ctx* ctx);
 /* Counters of the last search call on this context (kernel launches, slow-path queries). */
 typedef struct fv_stats {
   uint64_t launches;        /* kernels launched by the last call */
-  uint64_t uncertified;     /* exact search: queries re-run on the full-precision scan; HNSW: queries whose list of tied, pushed-out entries overflowed (64; ties beyond that may be resolved differently from the reference) */
+  uint64_t uncertified;     /* exact search: queries re-run on the full-precision scan; IVF-PQ: queries whose candidate buffer ran over in the list-major scan and were re-run by the per-query kernel; HNSW: queries whose list of tied, pushed-out entries overflowed (64; ties beyond that may be resolved differently from the reference) */
   uint64_t rows_scanned;    /* IVF-PQ: code rows visited (sum over queries and probes) */
   uint64_t dist_evals;      /* HNSW: distance evaluations */
   uint64_t expansions;      /* HNSW: node expansions */
   uint64_t regrown;         /* HNSW: queries re-run with a larger visited table */
   float stage_ms[8];        /* per-stage device time of the last call when timing is on */
+  uint64_t rows_list_scan;  /* IVF-PQ: the part of rows_scanned that the list-major kernel visited (0: per-query kernel only) */
 } fv_stats;
 int fv_ctx_stats(const fv_ctx* ctx, fv_stats* out);
 /* 1 = record per-stage device times (CUDA events) for fv_ctx_stats; 0 = off (default). */
@@ -149,6 +150,14 @@ int fv_ivfpq_search_batch_cells_dev(fv_ivfpq* ix, const float* d_queries, size_t
 int fv_ivfpq_search_candidates_cells_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t keep, size_t nprobe,
                                          const uint64_t* d_cells, fv_neighbor* d_adc, float* d_exact,
                                          uint32_t* d_counts);
+/* Which scan a search uses: 0 = chosen by batch and index size (default), 1 = one block per query, 2 = the
+ * list-major scan whenever the index allows it (m = 16, L2 with precomputed tables or inner product).  All give the
+ * same neighbours; 1 and 2 exist for validation and measurement. */
+int fv_ivfpq_set_scan_mode(fv_ivfpq* ix, int mode);
+/* List-major scan: global-memory candidate slots per query (8 bytes each; 0 = default, 1024 or fewer for very large
+ * batches; at most 4096).  A query that finds more rows below its bound than it has slots is re-run by the
+ * per-query kernel (counted in fv_stats.uncertified), so a small value trades memory for re-runs, never results. */
+int fv_ivfpq_set_candidate_slots(fv_ivfpq* ix, size_t slots);
 size_t fv_ivfpq_save_size(const fv_ivfpq* ix);
 int fv_ivfpq_save(const fv_ivfpq* ix, uint8_t* buf, size_t cap, size_t* written);      /* save :332 ("FLIVFPQ1") */
 int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out);      /* load :354 */

@@ -111,6 +111,68 @@ def test_flat_tensor_core_path_over_value_ranges(fv, oracle, ctx, case):
     assert eq == total
 
 
+@pytest.mark.parametrize("case", ["queries x300", "one huge component", "an infinite component"])
+def test_flat_queries_that_leave_the_operand_range(fv, oracle, ctx, case):
+    # The base picks the 16-bit type (fp16 here: values in [0, 255]); a query whose doubled components pass 65504
+    # cannot be scored by the tensor cores at all.  It must never be certified on an empty candidate list: the
+    # reference returns k finite neighbours whatever the query's scale (flat.rs:40-53).
+    dim, n, nq, k = 64, 9_000, 96, 10
+    base = fv.datagen(0, 1, n, dim, 16)
+    queries = fv.datagen(0, 2, nq, dim, 16)
+    if case == "queries x300":
+        queries = queries * np.float32(300.0)
+    elif case == "one huge component":
+        queries[5, 3] = np.float32(1.0e30)
+        queries[40, 0] = np.float32(-7.0e4)
+    else:
+        queries[7, 1] = np.float32(np.inf)  # every distance is +inf: no row may enter (flat.rs:45)
+    g, o = flat_pair(fv, oracle, ctx, L2, dim, base)
+    g.set_mode(1)
+    got, gc = g.search_batch(queries, k)
+    want, wc = o.search_batch(queries, k)
+    eq, total = assert_same_neighbours(got, gc, want, wc, f"flat, {case}")
+    assert eq == total
+    assert ctx.stats()["uncertified"] >= (nq if case == "queries x300" else 1)
+
+
+def test_concurrent_searches_on_one_context(fv, oracle, ctx):
+    # The reference's search methods take &self and its index types are Sync: host threads may search indexes of one
+    # pool at the same time.  Here they share one context (stream, scratch arena); the results must be the serial ones.
+    import threading
+
+    dim, n, nq, k = 64, 12_000, 120, 10
+    base = oracle.testdata(n, dim, 31)
+    queries = oracle.testdata(nq, dim, 32)
+    flat = fv.FlatIndex(ctx, L2, dim)
+    flat.add(base)
+    ivf = fv.IvfPq.train(ctx, L2, dim, base[:6000], fv.IvfPqParams(32, 16, 4, True, 1))
+    ivf.add(base)
+    ivf.set_scan_mode(2)
+    oh = oracle.Hnsw.build(L2, dim, base, m=8, ef_construction=40, seed=1, threads=1)
+    hn = fv.Hnsw.load(ctx, oh.save())
+    calls = [lambda: flat.search_batch(queries, k), lambda: ivf.search_batch(queries, k, 16, 4),
+             lambda: hn.search_batch(queries, k, 48), lambda: flat.search_batch(queries[:7], 3)]
+    serial = [c() for c in calls]
+    errors = []
+
+    def worker(t):
+        try:
+            for rep in range(6):
+                i = (t + rep) % len(calls)
+                out, cnt = calls[i]()
+                if out.tobytes() != serial[i][0].tobytes() or (cnt != serial[i][1]).any():
+                    errors.append(f"thread {t} call {i} rep {rep}: result differs from the serial one")
+        except Exception as e:  # noqa: BLE001
+            errors.append(f"thread {t}: {e!r}")
+
+    threads = [threading.Thread(target=worker, args=(t,)) for t in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors[:3]
+
+
 def test_flat_edge_cases(fv, oracle, ctx):
     dim = 16
     base = oracle.testdata(37, dim, 3)
@@ -308,6 +370,124 @@ def test_ivfpq_variants(fv, oracle, ctx, metric, dim, m, nlist, keep):
         want, wc = o.search_batch(queries, 10, nprobe, refine)
         eq, total = assert_same_neighbours(got, gc, want, wc, f"variant {metric} {dim}")
         assert eq == total
+
+
+@pytest.fixture(scope="module")
+def ivfpq16_pair(fv, oracle, ctx):
+    # m = 16 on SIFT-like integers; 24 lists over 40,000 rows: most lists are longer than the 1024 rows one task of
+    # the list-major scan covers, so lists are cut into row chunks, and 700 queries fill several 32-query groups per list
+    dim = 128
+    base = fv.datagen(0, 1, 40_000, dim, 32)
+    queries = fv.datagen(0, 2, 700, dim, 32)
+    g = fv.IvfPq.train(ctx, L2, dim, base[:12_000], fv.IvfPqParams(24, 16, 6, True, 1))
+    g.add(base[:25_000])
+    g.add(base[25_000:])
+    o = oracle.IvfPq.load(g.save())
+    return g, o, base, queries
+
+
+@pytest.mark.parametrize("nprobe,refine,k", [(2, 0, 10), (8, 0, 10), (24, 0, 10), (8, 10, 10), (24, 10, 10), (16, 30, 20),
+                                             (24, 0, 200)])
+def test_ivfpq_list_major_scan_matches_the_oracle(fv, oracle, ivfpq16_pair, nprobe, refine, k):
+    g, o, base, queries = ivfpq16_pair
+    want, wc, rows = o.search_batch(queries, k, nprobe, refine, want_rows=True)
+    outs = {}
+    for mode in (2, 1):
+        g.set_scan_mode(mode)
+        got, gc = g.search_batch(queries, k, nprobe, refine)
+        eq, total = assert_same_neighbours(got, gc, want, wc, f"ivfpq m=16 mode {mode} nprobe={nprobe} refine={refine}")
+        assert eq == total
+        assert g.ctx.stats()["rows_scanned"] == rows
+        outs[mode] = got
+    g.set_scan_mode(0)
+    assert outs[1].tobytes() == outs[2].tobytes()
+
+
+def test_ivfpq_list_major_scan_reruns_queries_whose_buffer_overflows(fv, oracle, ivfpq16_pair):
+    g, o, base, queries = ivfpq16_pair
+    want, wc = o.search_batch(queries, 10, 16, 10)
+    g.set_scan_mode(2)
+    g.set_candidate_slots(8)  # far fewer slots than rows below the bound: most queries overflow and are re-run
+    try:
+        got, gc = g.search_batch(queries, 10, 16, 10)
+        over = g.ctx.stats()["uncertified"]
+    finally:
+        g.set_candidate_slots(0)
+        g.set_scan_mode(0)
+    eq, total = assert_same_neighbours(got, gc, want, wc, "ivfpq list-major, 8 candidate slots")
+    assert eq == total and over > 0
+
+
+def test_ivfpq_list_major_scan_inner_product_and_ragged_lists(fv, oracle, ctx):
+    # inner product (the query's table is the lookup table, ivfpq.rs:236-238), dsub = 4, many short and empty lists,
+    # row counts that are not multiples of 16, fewer than 32 queries on some lists
+    dim = 64
+    base = oracle.normalize(oracle.testdata(9_001, dim, 41))
+    queries = oracle.normalize(oracle.testdata(333, dim, 42))
+    g = fv.IvfPq.train(ctx, IP, dim, base[:3000], fv.IvfPqParams(150, 16, 4, True, 1))
+    g.add(base)
+    o = oracle.IvfPq.load(g.save())
+    g.set_scan_mode(2)
+    for nprobe, refine in [(20, 0), (150, 5), (3, 2)]:
+        got, gc = g.search_batch(queries, 10, nprobe, refine)
+        want, wc, rows = o.search_batch(queries, 10, nprobe, refine, want_rows=True)
+        eq, total = assert_same_neighbours(got, gc, want, wc, f"ivfpq IP list-major nprobe={nprobe}")
+        assert eq == total and g.ctx.stats()["rows_scanned"] == rows
+
+
+@pytest.mark.parametrize("refine", [0, 5])
+def test_ivfpq_list_major_scan_on_list_shards(fv, oracle, ctx, ivfpq16_pair, refine):
+    import torch
+
+    _, o, base, queries = ivfpq16_pair
+    k, nprobe, world = 10, 12, 3
+    want, wc, rows = o.search_batch(queries, k, nprobe, refine, want_rows=True)
+    empty = fv.IvfPq.train(ctx, L2, 128, base[:12_000], fv.IvfPqParams(24, 16, 6, True, 1)).save()
+    dq = torch.from_numpy(queries).cuda()
+    parts, scanned = [], 0
+    for r in range(world):
+        g = fv.IvfPq.load(ctx, empty)
+        g.set_shard(r, world)
+        g.add(base)
+        g.set_scan_mode(2)
+        parts.append(g.search_candidates(dq, k * refine, nprobe) if refine else g.search_batch(dq, k, nprobe, 0))
+        scanned += ctx.stats()["rows_scanned"]
+    assert scanned == rows
+    if refine:
+        merged, mc = ctx.merge_refine(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]), None, k)
+    else:
+        merged, mc = ctx.merge_topk(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]), k)
+    eq, tot = assert_same_neighbours(fv.neighbors_from_tensor(merged), mc.cpu().numpy(), want, wc, "list shards, list-major")
+    assert eq == tot
+
+
+def test_ivfpq_load_rejects_ids_beyond_the_row_count(fv, oracle, ctx, ivfpq_pair):
+    # with kept vectors candidate `id` is re-ranked from row `id`: a damaged id must stop the load, not the kernel
+    _, o, _, _ = ivfpq_pair
+    blob = bytearray(o.save())
+    dim, nlist, m = 32, 64, 8
+    ids_at = 8 + 5 * 4 + (8 + nlist * dim * 4) + (8 + m * 256 * (dim // m) * 4) + 8  # first id of list 0
+    assert int(np.frombuffer(bytes(blob[ids_at - 8:ids_at]), dtype="<u8")[0]) > 0
+    blob[ids_at:ids_at + 4] = np.array([20_000], dtype="<u4").tobytes()
+    with pytest.raises(fv.FerrovecError, match="beyond its row count"):
+        fv.IvfPq.load(ctx, bytes(blob))
+
+
+def test_a_row_shard_cannot_be_saved_and_id_bases_come_first(fv, oracle, ctx, ivfpq_pair):
+    _, o, base, _ = ivfpq_pair
+    g = fv.IvfPq.load(ctx, oracle.IvfPq.train(L2, 32, base[:10_000], 64, 8, 2, True, 1).save())
+    g.set_id_base(1000)
+    g.add(base[:500])
+    with pytest.raises(fv.FerrovecError, match="id base"):
+        g.save()
+    f = fv.FlatIndex(ctx, L2, 32)
+    f.add(base[:10])
+    with pytest.raises(fv.FerrovecError, match="before the first add"):
+        f.set_id_base(5)
+    f2 = fv.FlatIndex(ctx, L2, 32)
+    f2.set_id_base(0xFFFFFF00)
+    with pytest.raises(fv.FerrovecError, match=r"2\^32"):
+        f2.add(base[:1000])
 
 
 def test_ivfpq_without_precomputed_tables(fv, oracle, ctx):
