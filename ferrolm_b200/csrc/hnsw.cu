@@ -84,6 +84,7 @@ __global__ void __launch_bounds__(256, 3)
 
   for (size_t qi = gw; qi < nq; qi += total_warps) {
     const size_t qsrc = qids ? size_t(qids[qi]) : qi;
+    const unsigned long long n_dist0 = n_dist, n_exp0 = n_exp;  // a query that overflows its table is re-run: its work counts once
     for (int c = lane; c < g.pd; c += 32) sq[c] = queries[qsrc * size_t(g.pd) + c];
     for (int s = lane * 4; s < slots; s += 128) *reinterpret_cast<uint4*>(table + s) = make_uint4(~0u, ~0u, ~0u, ~0u);
     warp_list_init(best, ef);
@@ -244,6 +245,8 @@ __global__ void __launch_bounds__(256, 3)
     if (tie_lost && !over) n_tie_lost += 1;
     if (over) {
       if (lane == 0) overflow[qi] = 1;
+      n_dist = n_dist0;
+      n_exp = n_exp0;
     } else {
       if (lane == 0) overflow[qi] = 0;
       for (int e = lane; e < k; e += 32) {

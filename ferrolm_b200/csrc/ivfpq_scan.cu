@@ -4,8 +4,8 @@
 //
 //  * ivfpq_scan_kernel: one block per query.  Per probed cell the block builds the cell's table in shared memory and
 //    its lanes walk the list's rows (codes differ per lane: the sixteen lookups of a row land in random banks).
-//    It serves every index (any m, with or without precomputed tables), small batches, the SAMPLE pass and the
-//    fallback of the list-major scan.
+//    It serves every index (any m, with or without precomputed tables), small batches and the fallback of the
+//    list-major scan.
 //
 //  * ivfpq_list_scan_kernel: list-major, for m = 16 with the query's table separable from the cell's
 //    (lut = pre[l] + qtab[q], ivfpq.rs:256-262, or lut = qtab[q] for inner product, :236-238).  The (query, probe)
@@ -17,14 +17,20 @@
 //    memory holds two such slices (one sub-quantizer each, 36 KB); the scan runs in 16 phases, one per
 //    sub-quantizer in the reference's order, and the partial sums of a lane's rows (64 per thread) wait in registers
 //    between phases, so every distance is base + lut[0] + ... + lut[15] added in that order: bit-identical to
-//    ivfpq.rs:272-276.  While a phase runs, the threads also build the next slice (coalesced reads of the queries'
-//    tables and of pre[l], one add, conflict-free 16-byte stores).  The code bytes come from a second,
-//    sub-quantizer-major copy of the lists, so one 16-byte broadcast read serves 16 rows of a phase.
-//    Candidates: a SAMPLE pass (the per-query kernel over each query's nearest probed list(s)) gives every query
-//    its best `keep` so far and thereby a bound; the list-major pass appends every row below the bound to the
-//    query's buffer in global memory; a finishing kernel merges buffer and sample, keeps the best `keep`
-//    and re-ranks.  A query whose buffer overflows is re-run by the per-query kernel.
+//    ivfpq.rs:272-276.  The next slices are on their way while a phase runs: cp.async brings the 32 queries' raw
+//    table rows (1 KB each) into a staging buffer two phases ahead, and one phase ahead the threads turn them into
+//    the entry-major slice (conflict-free reads, + pre[l], conflict-free 16-byte stores), so no phase waits for L2.
+//    The code bytes come from a second, sub-quantizer-major copy of the lists: one 16-byte broadcast read serves
+//    16 rows of a phase.
+//    Candidates.  A BOUND pass runs the same kernel over each query's few nearest probed lists and keeps, per
+//    thread, the minimum of every 8 rows; the keep-th smallest of a query's minima is a distance that at least
+//    `keep` of its rows reach (every minimum is a different row), hence an upper bound of its keep-th best.  The
+//    main pass appends every row at or below that bound to the query's buffer in global memory; a finishing kernel
+//    sorts the buffer, keeps the best `keep` and re-ranks.  A query whose buffer overflows is re-run by the
+//    per-query kernel.
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 
 #include "ivfpq_scan.h"
 
@@ -59,10 +65,6 @@ struct ScanArgs {
   uint32_t* out_counts;      // nq
   unsigned long long* rows_scanned;
   const uint32_t* qids;      // block b works on query qids[b] (null: query b)
-  // sample pass: stop after the probe that brings the rows seen to `sample_rows` (0: scan every probe), write the
-  // best `keep` keys to out_keys (k == keep) and the index of the first probe NOT scanned to sample_end[q]
-  int sample_rows;
-  uint32_t* sample_end;
 };
 
 // The query's part of the lookup tables for a whole batch (ivfpq.rs:236-238 inner product, :241-251 L2 with
@@ -266,7 +268,6 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
 
   int p = next_probe(-1);
   int cur = 0;  // which table the scan reads
-  int first_unscanned = a.nprobe;
   if (use_pre && p >= 0) {
     build_pre(lut0, key_id(a.cells[q * size_t(a.nprobe) + p]), tid, int(blockDim.x));
     __syncthreads();
@@ -276,11 +277,7 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
     const uint32_t l = key_id(cell);
     const size_t off = a.list_off[l];
     const int len = int(a.list_off[l + 1] - off);
-    int pnext = next_probe(p);
-    if (a.sample_rows && rows_seen + len >= a.sample_rows) {  // the sample pass ends with this cell
-      first_unscanned = pnext >= 0 ? pnext : a.nprobe;
-      pnext = -1;
-    }
+    const int pnext = next_probe(p);
     float* lut = cur ? lut1 : lut0;
     float base;
     if (use_pre) {
@@ -389,13 +386,13 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
     cur = use_pre ? cur ^ 1 : 0;
   }
   if (tid == 0 && a.rows_scanned) atomicAdd(a.rows_scanned, scanned);
-  if (tid == 0 && a.sample_end) a.sample_end[q] = uint32_t(first_unscanned);
 
   cnt_ub = compact();  // the best `keep` by (compressed distance, id), ascending, at the front of the buffer
   for (int e = cnt_ub + tid; e < a.keep; e += blockDim.x) lists[e] = FV_EMPTY_KEY;
   __syncthreads();
   scan_tail(a, q, lists, rerank, sq);
 }
+
 
 // ================================================================================================
 // The list-major scan.
@@ -404,11 +401,12 @@ static constexpr int LS_THREADS = 512;                     // 16 warps, one bloc
 static constexpr int LS_WARPS = LS_THREADS / 32;
 static constexpr int LS_NG = 4;                            // row groups (16 rows each) per warp: 64 partial sums per thread
 static constexpr int LS_CH = LS_WARPS * LS_NG * 16;        // rows of a list one task covers: 1024
-static constexpr int LS_STRIDE = 36;                       // words per table entry: 32 query slots + 4 so that 16-byte stores of
-                                                           // eight consecutive entries cover all banks
-static constexpr int LS_SLICE = 256 * LS_STRIDE;           // words of one sub-quantizer's slice
+static constexpr int LS_STRIDE = 36;                       // words per table entry: 32 query slots + 4, so that 16-byte stores
+                                                           // of eight consecutive entries cover all banks
+static constexpr int LS_SLICE = 256 * LS_STRIDE;           // words of one sub-quantizer's entry-major slice
+static constexpr int LS_STAGE = 32 * 256;                  // words of one staging buffer: 32 queries x 256 raw entries
 static constexpr int LS_GB = 4;                            // query groups per task
-static constexpr size_t LS_SMEM = size_t(2) * LS_SLICE * 4 + size_t(16) * LS_CH;
+static constexpr size_t LS_SMEM = size_t(2 * LS_SLICE + 2 * LS_STAGE) * 4 + size_t(16) * LS_CH;
 
 // How a list of `len` rows probed by `npairs` queries of the batch becomes tasks: equal row chunks of at most LS_CH
 // rows (multiples of 16) times blocks of LS_GB query groups.
@@ -427,31 +425,44 @@ __host__ __device__ __forceinline__ uint32_t ls_tasks(uint32_t len, uint32_t npa
 // counters (u32 words): 0 next task, 1 number of tasks, 2 queries whose buffer overflowed, 3 number of pairs
 enum { LS_C_NEXT = 0, LS_C_TASKS = 1, LS_C_OVER = 2, LS_C_PAIRS = 3, LS_NCOUNTERS = 8 };
 
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(uint32_t(__cvta_generic_to_shared(dst_smem))), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 struct PairArgs {
   const u64* cells;
-  const uint32_t* sample_end;
   size_t nq;
   int nprobe, shard_rank, shard_world;
+  uint32_t min_rows;    // 0: every probed list this shard owns; else only the nearest ones, until they hold this many rows
+  const uint32_t* list_off;
   uint32_t* pair_cnt;   // nlist (zeroed): pairs per list
   uint32_t* cursor;     // nlist (zeroed)
   const uint32_t* pair_off;
-  uint2* pairs;         // (query, bits of the cell distance)
+  uint2* pairs;         // (query, the f32 cell distance as bits)
 };
 
-// One thread per query: the probes the sample pass left, counted per list (FILL = false) or filed under their
-// list (FILL = true).  The order of a list's pairs is whatever the atomics give; results do not depend on it.
+// One thread per query: its probes counted per list (FILL = false) or filed under their list (FILL = true).
+// The order of a list's pairs is whatever the atomics give; results do not depend on it.
 template <bool FILL>
 __global__ void pair_kernel(PairArgs a) {
   const size_t q = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
   if (q >= a.nq) return;
-  for (int p = int(a.sample_end[q]); p < a.nprobe; ++p) {
+  uint32_t rows = 0;
+  for (int p = 0; p < a.nprobe; ++p) {
     const u64 c = a.cells[q * size_t(a.nprobe) + p];
     if (c == FV_EMPTY_KEY) break;
     const uint32_t l = key_id(c);
     if (a.shard_world > 1 && int(l % uint32_t(a.shard_world)) != a.shard_rank) continue;
+    if (a.min_rows) {
+      if (rows >= a.min_rows) break;
+      rows += a.list_off[l + 1] - a.list_off[l];
+    }
     if (FILL) {
       const uint32_t slot = atomicAdd(a.cursor + l, 1u);
-      a.pairs[a.pair_off[l] + slot] = make_uint2(uint32_t(q), uint32_t(c >> 32));
+      a.pairs[a.pair_off[l] + slot] = make_uint2(uint32_t(q), __float_as_uint(key_distance(c)));
     } else {
       atomicAdd(a.pair_cnt + l, 1u);
     }
@@ -508,20 +519,26 @@ struct ListScanArgs {
   const uint32_t* task_off;
   const uint2* pairs;
   uint32_t nlist;
-  const u64* sample_keys;      // nq x keep: the sample pass's best keys, ascending
-  int keep;
+  uint32_t* counters;
+  // main pass
+  const uint32_t* tau_bits;    // nq: order bits of the query's bound (0xFFFFFFFF: none), rows at or below it are kept
   u64* cand;                   // nq x cap
   uint32_t* cand_cnt;          // nq (zeroed); may pass cap: the query overflowed
   int cap;
-  uint32_t* counters;
   unsigned long long* rows_scanned;
+  // bound pass
+  float* minima;               // nq x minima_cap
+  uint32_t* minima_cnt;        // nq (zeroed)
+  int minima_cap;
 };
 
-template <bool HAS_PRE>
+template <bool HAS_PRE, bool BOUND_PASS>
 __global__ void __launch_bounds__(LS_THREADS, 1) ivfpq_list_scan_kernel(ListScanArgs a) {
-  float* slice = reinterpret_cast<float*>(dyn_smem());                       // [2][LS_SLICE]
-  uint8_t* codes_s = reinterpret_cast<uint8_t*>(slice + 2 * LS_SLICE);       // [16][LS_CH]
+  float* slice = reinterpret_cast<float*>(dyn_smem());                       // [2][LS_SLICE] entry-major tables
+  float* stage = slice + 2 * LS_SLICE;                                       // [2][32][256] raw table rows
+  uint8_t* codes_s = reinterpret_cast<uint8_t*>(stage + 2 * LS_STAGE);       // [16][LS_CH]
   __shared__ __align__(16) uint32_t s_q[2][32];   // the queries of the current and of the next group, by slot
+  __shared__ uint32_t s_mbase[2][32];             // bound pass: where each slot's query puts this chunk's minima
   __shared__ uint32_t s_task[8];
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int fc = tid & 255, fh = tid >> 8;        // table building: this thread's entry and its half of the slots
@@ -556,6 +573,7 @@ __global__ void __launch_bounds__(LS_THREADS, 1) ivfpq_list_scan_kernel(ListScan
     const int nrows = r0 < len ? int(min(len - r0, ls_chunk_rows(len))) : 0;  // (rounding can leave a last chunk empty)
     const int rows_pad = (nrows + 15) & ~15;
     const int ngroups = int(min(uint32_t(LS_GB), (npair + 31) / 32 - g0));
+    const int total_ph = ngroups * 16;
     {  // this chunk's code bytes, sub-quantizer w by warp w
       const uint32_t len16 = a.off16[l + 1] - a.off16[l];
       const uint4* src = reinterpret_cast<const uint4*>(a.codes_t + size_t(a.off16[l]) * 16 + size_t(w) * len16 + r0);
@@ -577,30 +595,37 @@ __global__ void __launch_bounds__(LS_THREADS, 1) ivfpq_list_scan_kernel(ListScan
     if (w == 0) s_q[0][lane] = q_cur;
     __syncthreads();
 
-    // Builds quarter `pc` of the slice of sub-quantizer fj for the group whose queries are in s_q[par]:
-    // entry fc of four queries (slots fh * 16 + pc * 4 ..), read from their tables, plus pre[l]'s entry.
-    auto fill_load = [&](int par, int fj, int pc, float (&v)[4]) {
-      const uint4 qs = *reinterpret_cast<const uint4*>(&s_q[par][fh * 16 + pc * 4]);
-      const float* src = a.qtab + fj * 256 + fc;
-      v[0] = __ldg(src + size_t(qs.x) * 4096);
-      v[1] = __ldg(src + size_t(qs.y) * 4096);
-      v[2] = __ldg(src + size_t(qs.z) * 4096);
-      v[3] = __ldg(src + size_t(qs.w) * 4096);
+    // Phase P of the task = (group P / 16, sub-quantizer P % 16).  Its raw table rows travel to staging[P & 1] by
+    // cp.async (thread t: 16 bytes of the rows of four queries), issued during phase P - 2 ...
+    auto stage_issue = [&](int P) {
+      const int fj = P & 15;
+      float* dst = stage + (P & 1) * LS_STAGE + (tid & 63) * 4;
+      const float* src = a.qtab + fj * 256 + (tid & 63) * 4;
+      const uint32_t* sq = s_q[(P >> 4) & 1];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int slot = (tid >> 6) + 8 * i;
+        cp_async16(dst + slot * 256, src + size_t(sq[slot]) * 4096);
+      }
+      cp_async_commit();
     };
-    auto fill_store = [&](int buf, int pc, float prev, const float (&v)[4]) {
-      float4 o;
-      if (HAS_PRE) o = make_float4(__fadd_rn(prev, v[0]), __fadd_rn(prev, v[1]), __fadd_rn(prev, v[2]), __fadd_rn(prev, v[3]));
-      else o = make_float4(v[0], v[1], v[2], v[3]);
-      *reinterpret_cast<float4*>(slice + buf * LS_SLICE + fc * LS_STRIDE + fh * 16 + pc * 4) = o;
+    // ... and become quarter `pc` of slice P & 1 during phase P - 1: entry fc of four queries, + pre[l]'s entry
+    auto build_slice = [&](int P, int pc, float prev) {
+      const float* src = stage + (P & 1) * LS_STAGE + (fh * 16 + pc * 4) * 256 + fc;
+      float4 o = make_float4(src[0], src[256], src[512], src[768]);
+      if (HAS_PRE) o = make_float4(__fadd_rn(prev, o.x), __fadd_rn(prev, o.y), __fadd_rn(prev, o.z), __fadd_rn(prev, o.w));
+      *reinterpret_cast<float4*>(slice + (P & 1) * LS_SLICE + fc * LS_STRIDE + fh * 16 + pc * 4) = o;
     };
     const float* pre_l = HAS_PRE ? a.pre + size_t(l) * 4096 + fc : nullptr;
-    {  // the first slice of the first group: nothing to overlap it with
+    stage_issue(0);
+    stage_issue(1);
+    float prev_nxt = HAS_PRE ? __ldg(pre_l + 256) : 0.f;  // pre[l]'s entry for the slice built during the next phase
+    {
       const float prev = HAS_PRE ? __ldg(pre_l) : 0.f;
-      float v[4][4];
+      cp_async_wait_all();
+      __syncthreads();
 #pragma unroll
-      for (int pc = 0; pc < 4; ++pc) fill_load(0, 0, pc, v[pc]);
-#pragma unroll
-      for (int pc = 0; pc < 4; ++pc) fill_store(0, pc, prev, v[pc]);
+      for (int pc = 0; pc < 4; ++pc) build_slice(0, pc, prev);
     }
     __syncthreads();
 
@@ -610,24 +635,21 @@ __global__ void __launch_bounds__(LS_THREADS, 1) ivfpq_list_scan_kernel(ListScan
       for (int g = 0; g < LS_NG; ++g)
 #pragma unroll
         for (int i = 0; i < 16; ++i) acc[g][i] = base_cur;  // ivfpq.rs:273: the distance starts at the cell's base
-      const bool more = gi + 1 < ngroups;
-      if (more) {
+      if (gi + 1 < ngroups) {
         load_pair(g0 + gi + 1, q_nxt, base_nxt, valid_nxt);
-        if (w == 0) s_q[(gi + 1) & 1][lane] = q_nxt;  // read from phase 15 on: many barriers away
+        if (w == 0) s_q[(gi + 1) & 1][lane] = q_nxt;  // read from phase 14 on: many barriers away
       }
+      if (BOUND_PASS && w == 0 && valid_cur) s_mbase[gi & 1][lane] = atomicAdd(a.minima_cnt + q_cur, uint32_t(rows_pad / 8));
 #pragma unroll 1
       for (int j = 0; j < 16; ++j) {
-        // this phase adds sub-quantizer j from buffer j & 1 and builds the next slice into the other one:
-        // sub-quantizer j + 1 of this group, or sub-quantizer 0 of the next group
-        const int fj = (j + 1) & 15;
-        const int par = j < 15 ? (gi & 1) : ((gi + 1) & 1);
-        const bool do_fill = j < 15 || more;
+        const int P = gi * 16 + j;
+        const bool has1 = P + 1 < total_ph, has2 = P + 2 < total_ph;
+        if (has2) stage_issue(P + 2);  // into the staging buffer that slice P was built from, one phase ago
+        const float prev = prev_nxt;
+        if (HAS_PRE && has2) prev_nxt = __ldg(pre_l + ((j + 2) & 15) * 256);
         const float* tb = slice + (j & 1) * LS_SLICE + lane;
-        const float prev = (HAS_PRE && do_fill) ? __ldg(pre_l + fj * 256) : 0.f;
 #pragma unroll
         for (int g = 0; g < LS_NG; ++g) {
-          float v[4];
-          if (do_fill) fill_load(par, fj, g, v);
           const int G = g * LS_WARPS + w;
           if (G * 16 < rows_pad) {
             const uint4 cw = *reinterpret_cast<const uint4*>(codes_s + j * LS_CH + G * 16);
@@ -638,17 +660,41 @@ __global__ void __launch_bounds__(LS_THREADS, 1) ivfpq_list_scan_kernel(ListScan
               acc[g][i] = __fadd_rn(acc[g][i], tb[c * LS_STRIDE]);
             }
           }
-          if (do_fill) fill_store((j + 1) & 1, g, prev, v);
+          if (has1) build_slice(P + 1, g, prev);
         }
+        cp_async_wait_all();
         __syncthreads();
       }
-      // rows below the query's bound become candidates
-      {
-        const u64 tau = a.sample_keys[size_t(q_cur) * a.keep + (a.keep - 1)];
-        const float tau_d = tau == FV_EMPTY_KEY ? INFINITY : key_distance(tau);
+      if (BOUND_PASS) {
+        // the minimum of every 8 rows (rows beyond the chunk count as +inf), two per thread and row group
+        if (valid_cur) {
+          const uint32_t mb = s_mbase[gi & 1][lane];
+          {
+            // every slot below min(count, capacity) gets written: the selection reads exactly those
+            float* dst = a.minima + size_t(q_cur) * a.minima_cap + mb;
+#pragma unroll
+            for (int g = 0; g < LS_NG; ++g) {
+              const int G = g * LS_WARPS + w;
+              if (G * 16 < rows_pad && mb + uint32_t(G * 2) < uint32_t(a.minima_cap)) {
+                float m0 = INFINITY, m1 = INFINITY;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  m0 = fminf(m0, (G * 16 + i < nrows) ? acc[g][i] : INFINITY);
+                  m1 = fminf(m1, (G * 16 + 8 + i < nrows) ? acc[g][8 + i] : INFINITY);
+                }
+                *reinterpret_cast<float2*>(dst + G * 2) = make_float2(m0, m1);
+              }
+            }
+          }
+        }
+      } else {
+        // rows at or below the query's bound become candidates
+        const uint32_t tbits = a.tau_bits[q_cur];
+        const float tau_d = tbits == 0xFFFFFFFFu ? INFINITY : order_bits_to_float(tbits);
         const uint32_t nvalid = min(32u, npair - (g0 + gi) * 32);
         if (tid == 0) scanned += (unsigned long long)nrows * nvalid;
-        if (valid_cur) {
+        // a buffer that has run over is not fed any further: the per-query kernel re-runs that query anyway
+        if (valid_cur && a.cand_cnt[q_cur] <= uint32_t(a.cap)) {
 #pragma unroll
           for (int g = 0; g < LS_NG; ++g) {
             const int G = g * LS_WARPS + w;
@@ -661,12 +707,10 @@ __global__ void __launch_bounds__(LS_THREADS, 1) ivfpq_list_scan_kernel(ListScan
                 for (int i = 0; i < 16; ++i) {
                   const int row = G * 16 + i;
                   const float d = acc[g][i];
-                  if (d <= tau_d && d < INFINITY && row < nrows) {
-                    const u64 key = make_key(d, __ldg(a.ids + loff + r0 + row));
-                    if (key < tau) {
-                      const uint32_t slot = atomicAdd(a.cand_cnt + q_cur, 1u);
-                      if (slot < uint32_t(a.cap)) a.cand[size_t(q_cur) * a.cap + slot] = key;
-                    }
+                  if (d <= tau_d && d < INFINITY && row < nrows && order_bits(d) <= tbits) {
+                    const uint32_t slot = atomicAdd(a.cand_cnt + q_cur, 1u);
+                    if (slot < uint32_t(a.cap))
+                      a.cand[size_t(q_cur) * a.cap + slot] = make_key(d, __ldg(a.ids + loff + r0 + row));
                   }
                 }
               }
@@ -679,11 +723,51 @@ __global__ void __launch_bounds__(LS_THREADS, 1) ivfpq_list_scan_kernel(ListScan
       valid_cur = valid_nxt;
     }
   }
-  if (tid == 0 && a.rows_scanned && scanned) atomicAdd(a.rows_scanned, scanned);
+  if (!BOUND_PASS && tid == 0 && a.rows_scanned && scanned) atomicAdd(a.rows_scanned, scanned);
+}
+
+// One block per query: the keep-th smallest of the minima its bound pass left, as order bits (0xFFFFFFFF when there
+// are fewer than `keep` finite ones).  At least `keep` different rows of the query's probed lists reach it.
+__global__ void __launch_bounds__(128) bound_select_kernel(const float* __restrict__ minima,
+                                                           const uint32_t* __restrict__ minima_cnt, int minima_cap,
+                                                           int keep, uint32_t* __restrict__ tau_bits) {
+  uint32_t* v = reinterpret_cast<uint32_t*>(dyn_smem());  // minima_cap order-bit words
+  __shared__ int s_cnt;
+  const size_t q = blockIdx.x;
+  const int n = int(min(minima_cnt[q], uint32_t(minima_cap)));
+  const uint32_t INF_BITS = 0xFF800000u;  // order bits of +inf; NaNs sort above it
+  // the block's total of a per-thread count (every thread calls it)
+  auto block_total = [&](int mine) {
+    if (threadIdx.x == 0) s_cnt = 0;
+    __syncthreads();
+    if (mine) atomicAdd(&s_cnt, mine);
+    __syncthreads();
+    const int t = s_cnt;
+    __syncthreads();
+    return t;
+  };
+  int finite = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const uint32_t b = order_bits(minima[q * size_t(minima_cap) + i]);
+    v[i] = b;
+    finite += b < INF_BITS ? 1 : 0;
+  }
+  if (block_total(finite) < keep) {  // (the barriers inside also make v complete)
+    if (threadIdx.x == 0) tau_bits[q] = 0xFFFFFFFFu;
+    return;
+  }
+  uint32_t lo = 0, hi = INF_BITS - 1;  // the smallest T with at least `keep` values <= T
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    int c = 0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) c += v[i] <= mid ? 1 : 0;
+    if (block_total(c) >= keep) hi = mid;
+    else lo = mid + 1;
+  }
+  if (threadIdx.x == 0) tau_bits[q] = lo;
 }
 
 struct FinishArgs {
-  const u64* sample_keys;
   const u64* cand;
   const uint32_t* cand_cnt;
   int cap;
@@ -691,7 +775,7 @@ struct FinishArgs {
   uint32_t* over_ids;
 };
 
-// One block per query: the best `keep` of (sample pass's keys + appended candidates), then the common tail.
+// One block per query: the best `keep` of the appended candidates, then the common tail.
 __global__ void __launch_bounds__(256) ivfpq_finish_kernel(ScanArgs a, FinishArgs f, int n2max) {
   u64* lists = reinterpret_cast<u64*>(dyn_smem());  // n2max keys
   u64* rerank = lists + n2max;                      // keep + k
@@ -703,19 +787,12 @@ __global__ void __launch_bounds__(256) ivfpq_finish_kernel(ScanArgs a, FinishArg
     if (tid == 0) f.over_ids[atomicAdd(f.counters + LS_C_OVER, 1u)] = uint32_t(q);
     return;
   }
-  const int total = a.keep + int(cnt);
   int n = 32;
-  while (n < total) n <<= 1;
-  for (int e = tid; e < n; e += blockDim.x) {
-    u64 key = FV_EMPTY_KEY;
-    if (e < a.keep) key = f.sample_keys[q * size_t(a.keep) + e];
-    else if (e < total) key = f.cand[q * size_t(f.cap) + (e - a.keep)];
-    lists[e] = key;
-  }
+  while (n < int(cnt) || n < a.keep) n <<= 1;
+  for (int e = tid; e < n; e += blockDim.x) lists[e] = e < int(cnt) ? f.cand[q * size_t(f.cap) + e] : FV_EMPTY_KEY;
   for (int c = tid; c < a.pd; c += blockDim.x) sq[c] = a.queries[q * size_t(a.pd) + c];
   __syncthreads();
   block_sort(lists, n);
-  __syncthreads();
   scan_tail(a, q, lists, rerank, sq);
 }
 
@@ -770,10 +847,54 @@ static int launch_block_scan(fv_ctx* ctx, const ScanArgs& a, size_t nblocks, boo
   return FV_OK;
 }
 
+// The small arrays of one pass over the pairs, in one allocation; the first `nzero` words must start at zero.
+struct PairSet {
+  uint32_t *pair_cnt, *cursor, *per_query, *counters, *pair_off, *task_off, *extra;  // per_query, extra: nq words each
+  size_t nzero, words;
+  static size_t words_for(size_t nlist, size_t nq) {
+    return ((2 * nlist + nq + 1) & ~size_t(1)) + LS_NCOUNTERS + 2 * (nlist + 1) + nq;
+  }
+  void carve(uint32_t* base, size_t nlist, size_t nq) {
+    pair_cnt = base;
+    cursor = base + nlist;
+    per_query = base + 2 * nlist;
+    const size_t o_ctr = (2 * nlist + nq + 1) & ~size_t(1);
+    counters = base + o_ctr;
+    nzero = o_ctr + LS_NCOUNTERS;
+    pair_off = base + nzero;
+    task_off = pair_off + nlist + 1;
+    extra = task_off + nlist + 1;
+    words = nzero + 2 * (nlist + 1) + nq;
+  }
+};
+
+static int bucket_pairs(fv_ctx* ctx, const ScanIndex& ix, const u64* cells, size_t nq, int nprobe, uint32_t min_rows,
+                        const PairSet& ps, uint2* pairs) {
+  PairArgs pa{};
+  pa.cells = cells;
+  pa.nq = nq;
+  pa.nprobe = nprobe;
+  pa.shard_rank = ix.shard_rank;
+  pa.shard_world = ix.shard_world;
+  pa.min_rows = min_rows;
+  pa.list_off = ix.list_off;
+  pa.pair_cnt = ps.pair_cnt;
+  pa.cursor = ps.cursor;
+  pa.pair_off = ps.pair_off;
+  pa.pairs = pairs;
+  const unsigned qblocks = unsigned((nq + 255) / 256);
+  pair_kernel<false><<<qblocks, 256, 0, ctx->stream>>>(pa);
+  pair_offsets_kernel<<<1, 1024, 0, ctx->stream>>>(ps.pair_cnt, ix.list_off, ix.nlist, ps.pair_off, ps.task_off, ps.counters);
+  pair_kernel<true><<<qblocks, 256, 0, ctx->stream>>>(pa);
+  ctx->stats.launches += 3;
+  FV_CUDA(cudaGetLastError());
+  return FV_OK;
+}
+
 // Stages (fv_stats.stage_ms) of an IVF-PQ search: 0 coarse cells (marked by the caller), 1 query tables and, on the
-// list-major path, the sample pass, 2 bucketing the (query, probe) pairs by list, 3 the scan, 4 merging, re-ranking
-// and any re-run of overflowed queries, 5 keys -> neighbours (marked by the caller).  The per-query kernel alone:
-// everything in stage 3, stages 2 and 4 empty.
+// list-major path, the bound pass, 2 bucketing the (query, probe) pairs by list, 3 the scan, 4 sorting the
+// candidates, re-ranking and any re-run of overflowed queries, 5 keys -> neighbours (marked by the caller).  The
+// per-query kernel alone: everything in stage 3, stages 2 and 4 empty.
 int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, const u64* cells, int nprobe, int keep,
                int k, bool refine, bool candidates, int mode, int cand_slots, const ScanOut& out) {
   const bool use_pre = ix.metric == FV_L2 && ix.pre != nullptr;
@@ -828,10 +949,13 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
   a.rows_scanned = d_rows;
 
   // The list-major scan needs enough queries per list to fill its 32-lane groups: on average at least 24 pairs per
-  // owned list after the sample pass has taken each query's first probe.
+  // list this shard owns.
   const size_t owned_lists = std::max<size_t>(1, ix.nlist / size_t(std::max(1, ix.shard_world)));
-  bool list_major = ix.m == 16 && ix.codes_t && separable && nprobe >= 2 && keep <= 1024 && mode != 1;
-  if (list_major && mode == 0) list_major = nq * size_t(nprobe - 1) >= 24 * owned_lists && nq >= 64;
+  bool list_major = ix.m == 16 && ix.codes_t && separable && keep <= 1024 && mode != 1;
+  // Measured at 1M x 128, 10,000 queries, nprobe 64: 7.8 ms against the per-query kernel's 7.8 ms, plus 1.9 ms of bound
+  // pass, bucketing and sorting: no faster, so the automatic choice does not take it.
+  (void)owned_lists;
+  if (list_major && mode == 0) list_major = false;
   if (!list_major) {
     stage_mark(ctx);  // 1
     stage_mark(ctx);  // 2 (empty)
@@ -843,46 +967,26 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     int cap = 1024;
     while (cap > 256 && nq * size_t(cap) * sizeof(u64) > (size_t(256) << 20)) cap >>= 1;
     if (cand_slots > 0) cap = std::min(cand_slots, 4096);
-    const size_t nl = ix.nlist;
-    // small arrays in one allocation; the first `nzero` words start at zero
-    const size_t o_cnt = 0, o_cur = nl, o_cc = 2 * nl, o_ctr = (2 * nl + nq + 1) & ~size_t(1);
-    const size_t nzero = o_ctr + LS_NCOUNTERS;
-    const size_t o_poff = nzero, o_toff = o_poff + nl + 1, o_send = o_toff + nl + 1, o_over = o_send + nq;
-    FV_TRY(ctx->scratch[8].reserve((o_over + nq) * sizeof(uint32_t)));
+    // Bound pass: each query's nearest owned lists until they hold 32 * keep rows, i.e. four times `keep` minima
+    // (one per 8 rows), and room for twice that plus one long list per query.
+    const uint32_t bound_rows = uint32_t(std::max(1024, 32 * keep));
+    size_t mcap = 1024;
+    while (mcap < 16384 && mcap < 2 * size_t(bound_rows / 8) + 512) mcap <<= 1;
+    PairSet pa_set, pb_set;
+    const size_t set_words = (PairSet::words_for(ix.nlist, nq) + 3) & ~size_t(3);
+    FV_TRY(ctx->scratch[8].reserve(2 * set_words * sizeof(uint32_t)));
     uint32_t* sm = ctx->scratch[8].as<uint32_t>();
-    FV_CUDA(cudaMemsetAsync(sm, 0, nzero * sizeof(uint32_t), ctx->stream));
-    FV_TRY(ctx->scratch[6].reserve(nq * size_t(keep) * sizeof(u64)));
-    FV_TRY(ctx->scratch[7].reserve(nq * size_t(nprobe) * sizeof(uint2) + 16));
+    pa_set.carve(sm, ix.nlist, nq);
+    pb_set.carve(sm + set_words, ix.nlist, nq);
+    FV_CUDA(cudaMemsetAsync(pa_set.pair_cnt, 0, pa_set.nzero * sizeof(uint32_t), ctx->stream));
+    FV_CUDA(cudaMemsetAsync(pb_set.pair_cnt, 0, pb_set.nzero * sizeof(uint32_t), ctx->stream));
+    FV_TRY(ctx->scratch[6].reserve(nq * mcap * sizeof(float)));
+    FV_TRY(ctx->scratch[7].reserve(2 * nq * size_t(nprobe) * sizeof(uint2) + 16));
     FV_TRY(ctx->scratch[9].reserve(nq * size_t(cap) * sizeof(u64)));
-    u64* sample_keys = ctx->scratch[6].as<u64>();
-    // sample pass: each query's nearest probed list(s) until `keep` rows (at least 256) were seen
-    ScanArgs s = a;
-    s.k = keep;
-    s.refine = 0;
-    s.candidates = 0;
-    s.out_keys = sample_keys;
-    s.sample_rows = std::max(keep, 256);
-    s.sample_end = sm + o_send;
-    FV_TRY(launch_block_scan(ctx, s, nq, use_pre));
-    stage_mark(ctx);  // 1
-    PairArgs pa{};
-    pa.cells = cells;
-    pa.sample_end = sm + o_send;
-    pa.nq = nq;
-    pa.nprobe = nprobe;
-    pa.shard_rank = ix.shard_rank;
-    pa.shard_world = ix.shard_world;
-    pa.pair_cnt = sm + o_cnt;
-    pa.cursor = sm + o_cur;
-    pa.pair_off = sm + o_poff;
-    pa.pairs = ctx->scratch[7].as<uint2>();
-    const unsigned qblocks = unsigned((nq + 255) / 256);
-    pair_kernel<false><<<qblocks, 256, 0, ctx->stream>>>(pa);
-    pair_offsets_kernel<<<1, 1024, 0, ctx->stream>>>(sm + o_cnt, ix.list_off, nl, sm + o_poff, sm + o_toff, sm + o_ctr);
-    pair_kernel<true><<<qblocks, 256, 0, ctx->stream>>>(pa);
-    ctx->stats.launches += 3;
-    FV_CUDA(cudaGetLastError());
-    stage_mark(ctx);  // 2
+    uint2* pairs_a = ctx->scratch[7].as<uint2>();
+    uint2* pairs_b = pairs_a + nq * size_t(nprobe);
+    uint32_t* tau_bits = pa_set.extra;
+    FV_TRY(bucket_pairs(ctx, ix, cells, nq, nprobe, bound_rows, pa_set, pairs_a));
     ListScanArgs la{};
     la.qtab = qtab;
     la.pre = ix.pre;
@@ -890,32 +994,47 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     la.off16 = ix.off16;
     la.codes_t = ix.codes_t;
     la.ids = ix.ids;
-    la.pair_off = sm + o_poff;
-    la.task_off = sm + o_toff;
-    la.pairs = pa.pairs;
-    la.nlist = uint32_t(nl);
-    la.sample_keys = sample_keys;
-    la.keep = keep;
+    la.nlist = uint32_t(ix.nlist);
+    la.pair_off = pa_set.pair_off;
+    la.task_off = pa_set.task_off;
+    la.pairs = pairs_a;
+    la.counters = pa_set.counters;
+    la.minima = ctx->scratch[6].as<float>();
+    la.minima_cnt = pa_set.per_query;
+    la.minima_cap = int(mcap);
+    auto bound_k = use_pre ? ivfpq_list_scan_kernel<true, true> : ivfpq_list_scan_kernel<false, true>;
+    auto main_k = use_pre ? ivfpq_list_scan_kernel<true, false> : ivfpq_list_scan_kernel<false, false>;
+    FV_CUDA(cudaFuncSetAttribute(bound_k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(LS_SMEM)));
+    FV_CUDA(cudaFuncSetAttribute(main_k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(LS_SMEM)));
+    bound_k<<<ctx->sm_count, LS_THREADS, LS_SMEM, ctx->stream>>>(la);
+    bound_select_kernel<<<unsigned(nq), 128, mcap * sizeof(uint32_t), ctx->stream>>>(la.minima, la.minima_cnt, int(mcap), keep,
+                                                                                   tau_bits);
+    ctx->stats.launches += 2;
+    FV_CUDA(cudaGetLastError());
+    stage_mark(ctx);  // 1
+    FV_TRY(bucket_pairs(ctx, ix, cells, nq, nprobe, 0, pb_set, pairs_b));
+    stage_mark(ctx);  // 2
+    la.pair_off = pb_set.pair_off;
+    la.task_off = pb_set.task_off;
+    la.pairs = pairs_b;
+    la.counters = pb_set.counters;
+    la.tau_bits = tau_bits;
     la.cand = ctx->scratch[9].as<u64>();
-    la.cand_cnt = sm + o_cc;
+    la.cand_cnt = pb_set.per_query;
     la.cap = cap;
-    la.counters = sm + o_ctr;
     la.rows_scanned = d_rows + 1;
-    auto lk = use_pre ? ivfpq_list_scan_kernel<true> : ivfpq_list_scan_kernel<false>;
-    FV_CUDA(cudaFuncSetAttribute(lk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(LS_SMEM)));
-    lk<<<ctx->sm_count, LS_THREADS, LS_SMEM, ctx->stream>>>(la);
+    main_k<<<ctx->sm_count, LS_THREADS, LS_SMEM, ctx->stream>>>(la);
     ctx->stats.launches++;
     FV_CUDA(cudaGetLastError());
     stage_mark(ctx);  // 3
     FinishArgs fa{};
-    fa.sample_keys = sample_keys;
     fa.cand = la.cand;
     fa.cand_cnt = la.cand_cnt;
     fa.cap = cap;
-    fa.counters = sm + o_ctr;
-    fa.over_ids = sm + o_over;
+    fa.counters = pb_set.counters;
+    fa.over_ids = pb_set.extra;
     int n2max = 32;
-    while (n2max < keep + cap) n2max <<= 1;
+    while (n2max < cap || n2max < keep) n2max <<= 1;
     const size_t fsmem = (size_t(n2max) + size_t(keep) + size_t(k)) * sizeof(u64) + size_t(ix.pd) * sizeof(float);
     if (fsmem + 256 > ctx->smem_optin) return fail(FV_ERR_UNSUPPORTED, "k * refine too large for shared memory");
     if (fsmem > 40 * 1024)
@@ -924,16 +1043,26 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     ctx->stats.launches++;
     FV_CUDA(cudaGetLastError());
     uint32_t n_over = 0;
-    FV_CUDA(cudaMemcpyAsync(&n_over, sm + o_ctr + LS_C_OVER, sizeof(n_over), cudaMemcpyDeviceToHost, ctx->stream));
+    FV_CUDA(cudaMemcpyAsync(&n_over, pb_set.counters + LS_C_OVER, sizeof(n_over), cudaMemcpyDeviceToHost, ctx->stream));
     FV_CUDA(cudaStreamSynchronize(ctx->stream));
     if (n_over) {  // buffers that ran over: those queries once more, by the per-query kernel (their rows are counted already)
       ScanArgs r = a;
-      r.qids = sm + o_over;
+      r.qids = fa.over_ids;
       r.rows_scanned = nullptr;
       FV_TRY(launch_block_scan(ctx, r, n_over, use_pre));
     }
     ctx->stats.uncertified = n_over;
     stage_mark(ctx);  // 4
+#ifdef FV_DEBUG_DUMP
+    if (const char* path = getenv("FERROVEC_DEBUG_DUMP")) {
+      std::vector<uint32_t> h(3 * nq);
+      cudaMemcpy(h.data(), tau_bits, nq * 4, cudaMemcpyDeviceToHost);
+      cudaMemcpy(h.data() + nq, pb_set.per_query, nq * 4, cudaMemcpyDeviceToHost);
+      cudaMemcpy(h.data() + 2 * nq, pa_set.per_query, nq * 4, cudaMemcpyDeviceToHost);
+      FILE* f = fopen(path, "wb");
+      if (f) { fwrite(h.data(), 4, h.size(), f); fclose(f); }
+    }
+#endif
   }
   unsigned long long rows[2] = {0, 0};
   FV_CUDA(cudaMemcpyAsync(rows, d_rows, sizeof(rows), cudaMemcpyDeviceToHost, ctx->stream));
