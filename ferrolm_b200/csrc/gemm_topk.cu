@@ -262,6 +262,12 @@ struct GemmParams {
   u64* cbuf;             // [grid * segmax][LISTS][ccap] (score, row) keys: one private list per epilogue thread and segment
   unsigned int* ccnt;    // [grid * segmax][LISTS] entries appended (may exceed ccap: overflow)
   int ccap;
+  // task mode (TASKS): the work is a table of (A tile, run of B units) pairs instead of the tiling above
+  const uint4* tasks;          // x: first operand row of the 256-row A tile, y: first B row, z: B units of 256 rows, w: valid B rows
+  const uint32_t* ntasks;      // device word: number of tasks
+  u64* pool;                   // [grid][pool_cap] survivors: (A row << 32) | B row relative to y
+  unsigned int* pool_cnt;      // [grid] entries each CTA produced (may exceed pool_cap: overflow)
+  unsigned int pool_cap;
 };
 
 struct __align__(8) Barriers {
@@ -270,6 +276,7 @@ struct __align__(8) Barriers {
   uint64_t tfull[2], tempty[2];
   uint32_t tmem_base;
   int abort_flag;
+  unsigned int pool_pos;  // task mode: survivors this CTA has appended
 };
 
 // Epilogue thread -> list index: warp group `sub` (0..3) * 128 + lane quadrant * 32 + lane.  MH = 2: sub & 1 is the
@@ -344,7 +351,7 @@ __global__ void sample_tau_kernel(const u64* __restrict__ lists, int MT, int par
   tau[q] = out;
 }
 
-template <int MH, int KPT, bool THRESH>
+template <int MH, int KPT, bool THRESH, bool TASKS = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
     gemm_topk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   unsigned char* raw = dyn_smem();
@@ -371,6 +378,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       mbar_init(&bars->tempty[i], MH == 2 ? NEPI / 2 : NEPI);
     }
     bars->abort_flag = 0;
+    bars->pool_pos = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // Query side of the norm step: every row is {c, c, c, 0, 0, 0, 0, 0} twice.  Both 16-byte halves of a row are
@@ -387,6 +395,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  // Work items: chunk g of the tiling, or task g of the table; CTA b takes g = b, b + grid, ...
+  const int nwork = TASKS ? int(*p.ntasks) : p.nchunks;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -394,16 +404,26 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       bool ok = true;
       StageCursor st(p.nstage);
       int ring = 0;
-      for (int g = blockIdx.x, seg = 0; g < p.nchunks && ok; g += gridDim.x, ++seg) {
-        const int part = g / p.MT, mt = g - part * p.MT;
-        const int nt0 = part * p.cpn, nt1 = min(p.NT, nt0 + p.cpn);
+      for (int g = blockIdx.x, seg = 0; g < nwork && ok; g += gridDim.x, ++seg) {
+        int nt0, nt1, a_row0, b_row0 = 0;
+        if (TASKS) {
+          const uint4 t = p.tasks[g];
+          a_row0 = int(t.x);
+          b_row0 = int(t.y);
+          nt0 = 0;
+          nt1 = int(t.z);
+        } else {
+          const int part = g / p.MT, mt = g - part * p.MT;
+          nt0 = part * p.cpn;
+          nt1 = min(p.NT, nt0 + p.cpn);
+          a_row0 = mt * MH * 128;
+        }
         ok = mbar_wait(&bars->a_empty, (seg & 1) ^ 1, abort_flag);
         if (!ok) break;
         mbar_expect_tx(&bars->a_full, uint32_t(MH * p.KB * A_BLOCK_BYTES));
         for (int mh = 0; mh < MH; ++mh)
           for (int kb = 0; kb < p.KB; ++kb)
-            tma_load_2d(sA + size_t(mh * p.KB + kb) * A_BLOCK_BYTES, &tmA, &bars->a_full, kb * KBLK,
-                        (mt * MH + mh) * 128);
+            tma_load_2d(sA + size_t(mh * p.KB + kb) * A_BLOCK_BYTES, &tmA, &bars->a_full, kb * KBLK, a_row0 + mh * 128);
         for (int nt = nt0; nt < nt1 && ok; ++nt) {
           for (int kb = 0; kb < p.KB; ++kb, st.next()) {
             const int s = st.s;
@@ -414,9 +434,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             // ceil(nstage / KB) back, and the commit that freed it also covers every norm step issued before it.
             const bool with_ext = kb == 0 && p.has_ext;
             mbar_expect_tx(&bars->full[s], uint32_t(B_STAGE_BYTES + (with_ext ? B_EXT_BYTES : 0)));
+            // first B row of the unit (task mode: a multiple of 8, which keeps the norm tile's swizzle image in step)
+            const size_t brow = size_t(b_row0) + size_t(nt) * TILE_N;
             if (with_ext)  // stored as the swizzled shared-memory image: one contiguous 8 KB copy
-              bulk_load_1d(sE + size_t(ring) * B_EXT_BYTES, p.ext + size_t(nt) * (TILE_N * EXT_K), B_EXT_BYTES, &bars->full[s]);
-            tma_load_2d(sB + size_t(s) * B_STAGE_BYTES, &tmB, &bars->full[s], kb * KBLK, nt * TILE_N);
+              bulk_load_1d(sE + size_t(ring) * B_EXT_BYTES, p.ext + brow * EXT_K, B_EXT_BYTES, &bars->full[s]);
+            tma_load_2d(sB + size_t(s) * B_STAGE_BYTES, &tmB, &bars->full[s], kb * KBLK, int(brow));
           }
           if (++ring == p.ext_ring) ring = 0;
         }
@@ -437,9 +459,16 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       StageCursor st(p.nstage);
       const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB), e_base = smem_u32(sE);
       const uint64_t aext_desc = smem_desc_sw32(smem_u32(sAext));
-      for (int g = blockIdx.x, seg = 0; g < p.nchunks && ok; g += gridDim.x, ++seg) {
-        const int part = g / p.MT;
-        const int nt0 = part * p.cpn, nt1 = min(p.NT, nt0 + p.cpn);
+      for (int g = blockIdx.x, seg = 0; g < nwork && ok; g += gridDim.x, ++seg) {
+        int nt0, nt1;
+        if (TASKS) {
+          nt0 = 0;
+          nt1 = int(p.tasks[g].z);
+        } else {
+          const int part = g / p.MT;
+          nt0 = part * p.cpn;
+          nt1 = min(p.NT, nt0 + p.cpn);
+        }
         ok = mbar_wait(&bars->a_full, seg & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
@@ -501,14 +530,26 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     bool ok = true;
     constexpr int NCOL = MH == 2 ? TILE_N / 2 : TILE_N / 4;
     const int col0 = MH == 2 ? (sub >> 1) * NCOL : sub * NCOL;
-    const uint32_t n_rows = uint32_t(p.n);
-    for (int g = blockIdx.x, seg = 0; g < p.nchunks && ok; g += gridDim.x, ++seg) {
-      const int part = g / p.MT, mt = g - part * p.MT;
-      const int nt0 = part * p.cpn, nt1 = min(p.NT, nt0 + p.cpn);
+    uint32_t n_rows = uint32_t(p.n);
+    uint32_t a_row = 0;  // task mode: this thread's operand row
+    for (int g = blockIdx.x, seg = 0; g < nwork && ok; g += gridDim.x, ++seg) {
+      int nt0, nt1, mt = 0;
+      if (TASKS) {
+        const uint4 t = p.tasks[g];
+        nt0 = 0;
+        nt1 = int(t.z);
+        n_rows = t.w;  // rows of this task's B run; the rest of its last unit belongs to someone else
+        a_row = t.x + uint32_t((MH == 2 ? grp * 128 : 0) + quad * 32 + lane);
+      } else {
+        const int part = g / p.MT;
+        mt = g - part * p.MT;
+        nt0 = part * p.cpn;
+        nt1 = min(p.NT, nt0 + p.cpn);
+      }
       cslot = (size_t(blockIdx.x) * p.segmax + seg) * LISTS + e;
       ncand = 0;
       if (THRESH) {  // the bound is fixed: the sample pass's estimate for this query
-        thr = p.tau[mt * (128 * MH) + (MH == 2 ? grp * 128 : 0) + quad * 32 + lane];
+        thr = TASKS ? p.tau[a_row] : p.tau[mt * (128 * MH) + (MH == 2 ? grp * 128 : 0) + quad * 32 + lane];
       } else {
         thr = INFINITY;
 #pragma unroll
@@ -558,6 +599,44 @@ __global__ void __launch_bounds__(NTHREADS, 1)
               }
             }
           };
+          // Task mode.  Survivors are dense where a query meets its own neighbourhood (one row in ten of a near list),
+          // so the append must not cost a shared-memory atomic per hit: every thread collects its hits of the chunk
+          // as two bit masks, the warp reserves room for all of them with ONE atomic on the CTA's counter, and each
+          // thread stores its own.
+          auto chunk_tasks = [&](const uint32_t* r, int c) {
+            float m = __uint_as_float(r[0]);
+#pragma unroll
+            for (int i = 1; i < 64; ++i) m = fminf(m, __uint_as_float(r[i]));
+            if (!__any_sync(FV_FULL, m < thr)) return;
+            uint32_t mk[2] = {0u, 0u};
+#pragma unroll
+            for (int i = 0; i < 64; ++i)
+              if (__uint_as_float(r[i]) < thr && row_base + uint32_t(c + i) < n_rows) mk[i >> 5] |= 1u << (i & 31);
+            const int mine = __popc(mk[0]) + __popc(mk[1]);
+            int incl = mine;  // inclusive prefix sum over the warp
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+              const int t = __shfl_up_sync(FV_FULL, incl, o);
+              if (lane >= o) incl += t;
+            }
+            const int total = __shfl_sync(FV_FULL, incl, 31);
+            if (total == 0) return;
+            unsigned int base = 0;
+            if (lane == 31) base = atomicAdd(&bars->pool_pos, unsigned(total));
+            base = __shfl_sync(FV_FULL, base, 31);
+            unsigned int pos = base + unsigned(incl - mine);
+            u64* dst = p.pool + size_t(blockIdx.x) * p.pool_cap;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t mm = mk[h];
+              while (mm) {
+                const int i = __ffs(mm) - 1;
+                mm &= mm - 1;
+                if (pos < p.pool_cap) dst[pos] = (u64(a_row) << 32) | u64(row_base + uint32_t(c + h * 32 + i));
+                ++pos;
+              }
+            }
+          };
           uint32_t rbuf[64];
 #pragma unroll 1
           for (int c = 0; c < NCOL; c += 64) {
@@ -568,7 +647,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
               __syncwarp();
               if (lane == 0) mbar_arrive(&bars->tempty[slot]);
             }
-            chunk(rbuf, c);
+            if (TASKS) chunk_tasks(rbuf, c);
+            else chunk(rbuf, c);
           }
         } else {
           // List mode.  Common path: the minimum of a chunk against the bound.  Rare path (entered by the whole
@@ -625,7 +705,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       }
       if (!ok) break;
       if (THRESH) {
-        p.ccnt[cslot] = ncand;
+        if (!TASKS) p.ccnt[cslot] = ncand;
       } else {
         u64* dst = p.cand + cslot * KP;
 #pragma unroll
@@ -643,6 +723,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 1);
+  if (TASKS && threadIdx.x == 0) p.pool_cnt[blockIdx.x] = bars->pool_pos;
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
@@ -1192,6 +1273,66 @@ static void fill_params(GemmParams* g, const Tiling& t, size_t rows, size_t nq, 
   g->nstage = t.nstage;
   g->scratch_bytes = scratch_bytes;
   g->ext_ring = t.ext_ring;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Task mode for other callers (the IVF-PQ scan): operand rows they prepared, scored against runs of this side's rows.
+void tc_info(const TcSide* tc, TcInfo* out) {
+  out->Kp = tc->Kp;
+  out->bf16 = tc->bf16;
+  out->n = tc->n;
+  out->max_norm2 = tc->h_stats.max_norm2;
+  out->min_v = tc->h_stats.min_v;
+  out->max_v = tc->h_stats.max_v;
+  out->not_finite = tc->h_stats.not_finite != 0;
+}
+
+int* tc_error_word(TcSide* tc) {
+  RangeStats* qst = tc->stats.as<RangeStats>() + 1;
+  return reinterpret_cast<int*>(reinterpret_cast<unsigned int*>(qst + 1) + 1);
+}
+
+int tc_prepare_queries(fv_ctx* ctx, TcSide* tc, int metric, const float* d_queries, size_t nq, int pd, uint16_t* d_out,
+                       float* d_qn2) {
+  RangeStats* qst = tc->stats.as<RangeStats>() + 1;
+  init_stats_kernel<<<1, 1, 0, ctx->stream>>>(qst);
+  FV_CUDA(cudaGetLastError());
+  const bool is_l2 = metric == FV_L2;
+  return convert(ctx, tc->bf16, d_queries, nq, pd, tc->Kp, d_out, d_qn2, is_l2, is_l2 ? -2.f : -1.f, qst);
+}
+
+int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_t a_rows, const float* d_thr,
+                 const uint4* d_tasks, const uint32_t* d_ntasks, u64* d_pool, unsigned int* d_pool_cnt,
+                 unsigned int pool_cap, int* grid_out) {
+  const int Kp = tc->Kp;
+  if (Kp > 2 * KBLK) return fail(FV_ERR_UNSUPPORTED, "task mode of the tensor-core kernel covers padded dimensions up to 128");
+  Tiling t{};
+  FV_TRY(make_tiling(ctx, Kp, 256, size_t(TILE_N) * 1024, 0, &t));  // stages, shared memory; the tiling itself is unused
+  GemmParams gp{};
+  fill_params(&gp, t, tc->n, a_rows, 0);
+  gp.nchunks = 0;
+  gp.has_ext = metric == FV_L2 ? 1 : 0;
+  gp.aext_c = tc->bf16 ? 0x3F80u : uint32_t((tc->ext_e + 15) << 10);
+  gp.idesc = make_idesc(128, TILE_N, tc->bf16);
+  gp.err = tc_error_word(tc);
+  gp.ext = tc->ext.as<uint16_t>();
+  gp.tau = d_thr;
+  gp.tasks = d_tasks;
+  gp.ntasks = d_ntasks;
+  gp.pool = d_pool;
+  gp.pool_cnt = d_pool_cnt;
+  gp.pool_cap = pool_cap;
+  CUtensorMap tmA, tmB;
+  FV_TRY(make_tmap(&tmA, tc->bf16, const_cast<uint16_t*>(d_A), a_rows, Kp, 128));
+  FV_TRY(make_tmap(&tmB, tc->bf16, tc->half.p, tc->n, Kp, TILE_N));
+  FV_CUDA(cudaMemsetAsync(gp.err, 0, sizeof(int), ctx->stream));
+  void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams) = gemm_topk_kernel<2, 2, true, true>;
+  FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(t.smem)));
+  kern<<<ctx->sm_count, NTHREADS, t.smem, ctx->stream>>>(tmA, tmB, gp);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  *grid_out = ctx->sm_count;
+  return FV_OK;
 }
 
 // Stages (fv_stats.stage_ms): 0 query conversion, 1 sample pass, 2 main pass, 3 re-rank + certificate, 4 fallback.

@@ -72,7 +72,7 @@ struct DevBuf {
   }
 };
 
-enum { FV_NSCRATCH = 12, FV_NSTAGE = 8 };
+enum { FV_NSCRATCH = 16, FV_NSTAGE = 8 };
 
 struct fv_ctx {
   // Every entry point that uses the stream, the scratch arena, the events or the counters holds this lock for the
@@ -147,6 +147,30 @@ int tc_append(fv_ctx* ctx, TcSide** tc, int metric, const float* d_rows_new, siz
 int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n, int pd, const float* d_queries,
               size_t nq, int k, uint32_t id_base, u64* d_out_keys, bool mark_stages, bool prefilter_inf);
 bool tc_usable(const TcSide* tc, size_t n, size_t nq, int k);
+
+// ---- the same kernel in task mode, for callers that bring their own operand rows and work table (the IVF-PQ scan).
+struct TcInfo {
+  int Kp;            // operand row length (padded dimension rounded up to 64)
+  bool bf16;         // operand type (else fp16)
+  size_t n;          // rows of the side
+  float max_norm2, min_v, max_v;
+  bool not_finite;
+};
+void tc_info(const TcSide* tc, TcInfo* out);
+// Device word that a bounded wait inside the kernel sets when it runs out (zeroed by tc_list_pass).
+int* tc_error_word(TcSide* tc);
+// nq x pd f32 rows -> nq x Kp operand rows in the side's 16-bit type, scaled by -2 (L2) or -1; squared norms (0 for
+// inner product) to d_qn2.
+int tc_prepare_queries(fv_ctx* ctx, TcSide* tc, int metric, const float* d_queries, size_t nq, int pd, uint16_t* d_out,
+                       float* d_qn2);
+// Scores the 256 operand rows of every task against its run of side rows: d_tasks[t] = {first operand row, first side
+// row (a multiple of 8), units of 256 side rows, valid side rows}.  Every (operand row, side row) whose score
+// ||b||^2 - 2<a, b> (L2; -<a, b> for inner product, operand rows being pre-scaled) is below d_thr[operand row] goes to
+// the survivor pool as (operand row << 32 | side row relative to the task's first): CTA c of *grid_out fills
+// d_pool[c * pool_cap ..] and writes its count (which may exceed pool_cap: overflow) to d_pool_cnt[c].  Asynchronous.
+int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_t a_rows, const float* d_thr,
+                 const uint4* d_tasks, const uint32_t* d_ntasks, u64* d_pool, unsigned int* d_pool_cnt,
+                 unsigned int pool_cap, int* grid_out);
 
 // pads rows of `dim` floats to `pd` on the device (host or device source)
 int upload_padded(fv_ctx* ctx, const float* src, bool src_is_device, size_t n, size_t dim, size_t pd, float* d_dst);

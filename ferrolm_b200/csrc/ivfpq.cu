@@ -227,6 +227,8 @@ struct fv_ivfpq {
   fv_ctx* ctx = nullptr;
   ~fv_ivfpq() {
     fv::tc_free(ctc);
+    fv::tc_free(recon);
+    roff8.release();
     centroids.release(); codebooks.release(); pre.release(); list_off.release(); owned_ids.release();
     codes.release(); ids.release(); vectors.release(); codes_t.release(); off16.release();
     if (ctx) fv::ctx_release(ctx);
@@ -247,7 +249,11 @@ struct fv_ivfpq {
   bool has_pre = false;
   DevBuf codes_t, off16;  // m = 16: the sub-quantizer-major copy of the codes the list-major scan reads
   bool has_codes_t = false;
-  int scan_mode = 0;      // 0 pick by size, 1 one block per query, 2 list-major whenever possible
+  fv::TcSide* recon = nullptr;  // 16-bit reconstruction of every row for the tensor-core pass, built on first use
+  DevBuf roff8;
+  bool recon_valid = false;     // false after an add: rebuilt by the next search that wants it
+  float cen_norm2_max = 0.f, code_norm2_max = 0.f;
+  int scan_mode = 0;      // 0 pick by size, 1 one block per query, 2 list-major table scan, 3 list-major tensor-core pass
   int cand_slots = 0;     // list-major scan: candidate slots per query (0 = default)
 };
 
@@ -273,6 +279,26 @@ static int upload_quantizers(fv_ivfpq* ix) {
     FV_CUDA(cudaGetLastError());
     ix->has_pre = true;
   }
+  // bounds the tensor-core pass's error margin needs: the largest centroid, the largest sum of codewords
+  ix->cen_norm2_max = 0.f;
+  for (size_t l = 0; l < ix->nlist; ++l) {
+    double s = 0.0;
+    for (size_t d = 0; d < ix->pd; ++d) s += double(ix->h_centroids[l * ix->pd + d]) * ix->h_centroids[l * ix->pd + d];
+    ix->cen_norm2_max = std::max(ix->cen_norm2_max, float(s * 1.000001));
+  }
+  ix->code_norm2_max = 0.f;
+  for (size_t j = 0; j < ix->m; ++j) {
+    double best = 0.0;
+    for (size_t c = 0; c < KSUB; ++c) {
+      double s = 0.0;
+      for (size_t t = 0; t < ix->dsub; ++t) {
+        const double w = ix->h_codebooks[(j * KSUB + c) * ix->dsub + t];
+        s += w * w;
+      }
+      best = std::max(best, s);
+    }
+    ix->code_norm2_max += float(best * 1.000001);
+  }
   // coarse search as a small GEMM when there are enough cells (ivfpq.rs:211-220 at batch scale)
   tc_free(ix->ctc);
   ix->ctc = nullptr;
@@ -291,6 +317,7 @@ static int upload_offsets(fv_ivfpq* ix) {
 // after the lists changed: the second copy of the codes (m = 16 only)
 static int refresh_transposed(fv_ivfpq* ix) {
   ix->has_codes_t = false;
+  ix->recon_valid = false;
   if (ix->m != 16) return FV_OK;
   FV_TRY(build_transposed_codes(ix->ctx, ix->h_off.data(), ix->nlist, ix->list_off.as<uint32_t>(), ix->codes.as<uint8_t>(),
                                 &ix->codes_t, &ix->off16));
@@ -631,6 +658,19 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   si.id_base = ix->id_base;
   si.codes_t = ix->has_codes_t ? ix->codes_t.as<uint8_t>() : nullptr;
   si.off16 = ix->has_codes_t ? ix->off16.as<uint32_t>() : nullptr;
+  // the reconstruction the tensor-core pass needs: built by the first search that may take that path
+  const bool separable = ix->metric == FV_INNER_PRODUCT || ix->has_pre;
+  if (ix->has_codes_t && separable && ix->pd <= 128 && ix->count > 0 && keep <= 1024 && !ix->recon_valid &&
+      fv::ivfpq_wants_tensor(ix->scan_mode, nq, size_t(np), ix->nlist, ix->shard_world)) {
+    FV_TRY(fv::build_reconstruction(ctx, ix->metric, pd, int(ix->m), int(ix->dsub), ix->h_off.data(), ix->nlist,
+                                    ix->list_off.as<uint32_t>(), ix->codes.as<uint8_t>(), ix->centroids.as<float>(),
+                                    ix->codebooks.as<float>(), &ix->recon, &ix->roff8));
+    ix->recon_valid = true;
+  }
+  si.recon = ix->recon_valid ? ix->recon : nullptr;
+  si.roff8 = ix->recon_valid && ix->recon ? ix->roff8.as<uint32_t>() : nullptr;
+  si.cen_norm2_max = ix->cen_norm2_max;
+  si.code_norm2_max = ix->code_norm2_max;
   fv::ScanOut so{};
   so.keys = ctx->scratch[1].as<u64>();
   so.adc = d_adc;
@@ -660,7 +700,7 @@ int fv_ivfpq_set_candidate_slots(fv_ivfpq* ix, size_t slots) {
 }
 
 int fv_ivfpq_set_scan_mode(fv_ivfpq* ix, int mode) {
-  if (!ix || mode < 0 || mode > 2) return fv::fail(FV_ERR_ARG, "fv_ivfpq_set_scan_mode: mode must be 0, 1 or 2");
+  if (!ix || mode < 0 || mode > 3) return fv::fail(FV_ERR_ARG, "fv_ivfpq_set_scan_mode: mode must be 0, 1, 2 or 3");
   ix->scan_mode = mode;
   return FV_OK;
 }

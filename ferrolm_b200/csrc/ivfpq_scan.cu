@@ -29,8 +29,12 @@
 //    sorts the buffer, keeps the best `keep` and re-ranks.  A query whose buffer overflows is re-run by the
 //    per-query kernel.
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "ivfpq_scan.h"
 
@@ -726,45 +730,37 @@ __global__ void __launch_bounds__(LS_THREADS, 1) ivfpq_list_scan_kernel(ListScan
   if (!BOUND_PASS && tid == 0 && a.rows_scanned && scanned) atomicAdd(a.rows_scanned, scanned);
 }
 
-// One block per query: the keep-th smallest of the minima its bound pass left, as order bits (0xFFFFFFFF when there
+// One warp per query: the keep-th smallest of the minima its bound pass left, as order bits (0xFFFFFFFF when there
 // are fewer than `keep` finite ones).  At least `keep` different rows of the query's probed lists reach it.
 __global__ void __launch_bounds__(128) bound_select_kernel(const float* __restrict__ minima,
                                                            const uint32_t* __restrict__ minima_cnt, int minima_cap,
-                                                           int keep, uint32_t* __restrict__ tau_bits) {
-  uint32_t* v = reinterpret_cast<uint32_t*>(dyn_smem());  // minima_cap order-bit words
-  __shared__ int s_cnt;
-  const size_t q = blockIdx.x;
+                                                           int keep, size_t nq, uint32_t* __restrict__ tau_bits) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const size_t q = blockIdx.x * size_t(blockDim.x >> 5) + w;
+  if (q >= nq) return;
+  uint32_t* v = reinterpret_cast<uint32_t*>(dyn_smem()) + size_t(w) * minima_cap;  // order-bit words
   const int n = int(min(minima_cnt[q], uint32_t(minima_cap)));
   const uint32_t INF_BITS = 0xFF800000u;  // order bits of +inf; NaNs sort above it
-  // the block's total of a per-thread count (every thread calls it)
-  auto block_total = [&](int mine) {
-    if (threadIdx.x == 0) s_cnt = 0;
-    __syncthreads();
-    if (mine) atomicAdd(&s_cnt, mine);
-    __syncthreads();
-    const int t = s_cnt;
-    __syncthreads();
-    return t;
-  };
   int finite = 0;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+  for (int i = lane; i < n; i += 32) {
     const uint32_t b = order_bits(minima[q * size_t(minima_cap) + i]);
     v[i] = b;
     finite += b < INF_BITS ? 1 : 0;
   }
-  if (block_total(finite) < keep) {  // (the barriers inside also make v complete)
-    if (threadIdx.x == 0) tau_bits[q] = 0xFFFFFFFFu;
+  __syncwarp();
+  if (__reduce_add_sync(FV_FULL, finite) < keep) {
+    if (lane == 0) tau_bits[q] = 0xFFFFFFFFu;
     return;
   }
   uint32_t lo = 0, hi = INF_BITS - 1;  // the smallest T with at least `keep` values <= T
   while (lo < hi) {
     const uint32_t mid = lo + ((hi - lo) >> 1);
     int c = 0;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) c += v[i] <= mid ? 1 : 0;
-    if (block_total(c) >= keep) hi = mid;
+    for (int i = lane; i < n; i += 32) c += v[i] <= mid ? 1 : 0;
+    if (__reduce_add_sync(FV_FULL, c) >= keep) hi = mid;
     else lo = mid + 1;
   }
-  if (threadIdx.x == 0) tau_bits[q] = lo;
+  if (lane == 0) tau_bits[q] = lo;
 }
 
 struct FinishArgs {
@@ -833,6 +829,298 @@ int build_transposed_codes(fv_ctx* ctx, const uint32_t* h_off, size_t nlist, con
   return FV_OK;
 }
 
+// ================================================================================================
+// The tensor-core pass.  The compressed distance of a row is, up to rounding, the true distance between the query and
+// the vector its code stands for: base + sum_j lut[j][code_j] = ||(q - centroid) - codewords||^2 (ivfpq.rs:108-126,
+// :256-262), or -<q, centroid> - <q, codewords> for inner product.  So the list-major work -- every query that
+// probes a list against every row of the list -- is a GEMM between the queries' residuals q - centroid (one operand
+// row per (query, probe) pair; plain q for inner product) and a 16-bit copy of the rows' codewords: the tcgen05
+// kernel of exact search in task mode scores 256 pairs x 256 rows per unit and hands back every (pair, row) whose
+// score is below the query's bound plus a rigorous error margin.  Working on residuals keeps both operands small
+// (a few hundred instead of a few thousand in norm), and with them the 16-bit rounding the margin has to cover.  Only those survivors get the reference's table arithmetic
+// (rescore_kernel: base first, then the m table entries in order, each lut entry rounded on its own), and only a
+// survivor whose exact compressed distance is at or below the bound becomes a candidate.  The tensor cores decide
+// nothing on their own: a row they drop is provably above the bound.
+
+// the residual each stored row's code stands for (its m codewords side by side), f32, list by list; lists start at
+// multiples of 8 rows, the filler rows are zero
+__global__ void reconstruct_kernel(const uint32_t* __restrict__ list_off, const uint32_t* __restrict__ roff8,
+                                   const uint8_t* __restrict__ codes, const float* __restrict__ centroids,
+                                   const float* __restrict__ codebooks, int pd, int m, int dsub, float* __restrict__ out) {
+  const size_t l = blockIdx.x;
+  const uint32_t off = list_off[l], len = list_off[l + 1] - off;
+  const uint32_t r0 = roff8[l], len8 = roff8[l + 1] - r0;
+  const size_t total = size_t(len8) * pd;
+  for (size_t i = threadIdx.x; i < total; i += blockDim.x) {
+    const uint32_t r = uint32_t(i / pd);
+    const int d = int(i - size_t(r) * pd);
+    float v = 0.f;
+    if (r < len) {
+      const int j = d / dsub, t = d - j * dsub;
+      const uint32_t c = codes[(size_t(off) + r) * m + j];
+      v = codebooks[(size_t(j) * KSUB + c) * dsub + t];
+    }
+    out[(size_t(r0) + r) * pd + d] = v;
+  }
+}
+
+int build_reconstruction(fv_ctx* ctx, int metric, int pd, int m, int dsub, const uint32_t* h_off, size_t nlist,
+                         const uint32_t* d_list_off, const uint8_t* d_codes, const float* d_centroids,
+                         const float* d_codebooks, TcSide** recon, DevBuf* roff8) {
+  tc_free(*recon);
+  *recon = nullptr;
+  std::vector<uint32_t> o8(nlist + 1, 0);
+  for (size_t l = 0; l < nlist; ++l) {
+    const uint64_t next = uint64_t(o8[l]) + ((h_off[l + 1] - h_off[l] + 7u) & ~7u);
+    if (next > 0x7FFFFF00ull) return FV_OK;  // beyond the kernel's row range: no tensor-core pass for this index
+    o8[l + 1] = uint32_t(next);
+  }
+  const size_t rows = o8[nlist];
+  if (rows == 0 || pd > 128) return FV_OK;
+  // behind the offsets: the list numbers, longest list first (the order the tasks are dealt in)
+  o8.resize(2 * nlist + 1);
+  for (size_t l = 0; l < nlist; ++l) o8[nlist + 1 + l] = uint32_t(l);
+  std::stable_sort(o8.begin() + nlist + 1, o8.end(),
+                   [&](uint32_t x, uint32_t y) { return h_off[x + 1] - h_off[x] > h_off[y + 1] - h_off[y]; });
+  FV_TRY(roff8->reserve(o8.size() * sizeof(uint32_t)));
+  FV_CUDA(cudaMemcpyAsync(roff8->p, o8.data(), o8.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+  DevBuf tmp;
+  FV_TRY(tmp.reserve(rows * size_t(pd) * sizeof(float)));
+  reconstruct_kernel<<<unsigned(nlist), 256, 0, ctx->stream>>>(d_list_off, roff8->as<uint32_t>(), d_codes, d_centroids,
+                                                              d_codebooks, pd, m, dsub, tmp.as<float>());
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  FV_TRY(tc_append(ctx, recon, metric, tmp.as<float>(), 0, rows, pd));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));  // tmp and o8 leave scope
+  return FV_OK;
+}
+
+// One block: the tasks of the tensor-core pass.  A list with n pairs and len rows gives ceil(n / 256) tasks, each
+// 256 gathered operand rows against all of the list's rows; a_off[l] is the list's first gathered row.
+// Lists are walked in `order` (longest first), so the tasks come out sorted by decreasing length and dealing them
+// round-robin to the persistent CTAs balances the load.
+__global__ void __launch_bounds__(1024) tc_tasks_kernel(const uint32_t* __restrict__ pair_off,
+                                                        const uint32_t* __restrict__ list_off,
+                                                        const uint32_t* __restrict__ roff8,
+                                                        const uint32_t* __restrict__ order, size_t nlist,
+                                                        uint4* __restrict__ tasks, uint32_t* __restrict__ a_off,
+                                                        uint32_t* __restrict__ ntasks, unsigned long long* __restrict__ rows) {
+  __shared__ uint32_t st[1024];
+  const int tid = threadIdx.x;
+  const size_t per = (nlist + 1023) / 1024;
+  const size_t l0 = min(nlist, size_t(tid) * per), l1 = min(nlist, l0 + per);
+  auto tasks_of = [&](size_t l) {
+    const uint32_t n = pair_off[l + 1] - pair_off[l], len = list_off[l + 1] - list_off[l];
+    return (n && len) ? (n + 255u) / 256u : 0u;
+  };
+  uint32_t nt = 0;
+  unsigned long long nr = 0;
+  for (size_t o = l0; o < l1; ++o) {
+    const size_t l = order[o];
+    nt += tasks_of(l);
+    nr += (unsigned long long)(pair_off[l + 1] - pair_off[l]) * (list_off[l + 1] - list_off[l]);
+  }
+  st[tid] = nt;
+  __syncthreads();
+  for (int o = 1; o < 1024; o <<= 1) {
+    const uint32_t b = tid >= o ? st[tid - o] : 0u;
+    __syncthreads();
+    st[tid] += b;
+    __syncthreads();
+  }
+  uint32_t bt = st[tid] - nt;
+  for (size_t o = l0; o < l1; ++o) {
+    const size_t l = order[o];
+    const uint32_t k = tasks_of(l), len = list_off[l + 1] - list_off[l];
+    a_off[l] = bt * 256u;
+    for (uint32_t t = 0; t < k; ++t) tasks[bt + t] = make_uint4((bt + t) * 256u, roff8[l], (len + 255u) / 256u, len);
+    bt += k;
+  }
+  if (tid == 1023) *ntasks = st[1023];
+  if (nr && rows) atomicAdd(rows, nr);
+}
+
+struct GatherArgs {
+  const uint32_t* pair_off;
+  const uint32_t* list_off;
+  const uint32_t* a_off;
+  const uint2* pairs;
+  const float* queries;       // nq x pd f32
+  const float* centroids;     // nlist x pd
+  const uint32_t* tau_bits;   // nq
+  uint32_t* cand_cnt;         // nq
+  int cap, pd, Kp, is_l2, bf16;
+  float kf, bn, cw2, c1;      // Kp; largest codeword-row norm; max ||centroid||^2 + max ||codewords||^2; rounding count of the chain
+  uint16_t* qg;               // gathered operand rows
+  float* thr;                 // per gathered row
+  uint32_t* g_q;
+  uint32_t* g_l;
+  float* g_base;
+};
+
+__device__ __forceinline__ uint16_t to_operand(float x, int bf16) {
+  return bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(x)) : __half_as_ushort(__float2half_rn(x));
+}
+
+// One warp per gathered row (blockIdx.x = list, blockIdx.y strides its rows): writes the pair's operand row,
+// -2 (q - centroid) for L2 or -q for inner product in the side's 16-bit type, and turns the query's bound into the
+// score threshold of that row.  With a = q - centroid (L2) the kernel's score is ||w||^2 - 2 <a, w> for the row's
+// codewords w, and |score + ||a||^2 - compressed distance| <= eps, where eps adds up
+//   - the 16-bit score against the f32 arithmetic on (a, w): input rounding 2 u |a||w|, fp32 accumulation, the norm
+//     step (the margin exact search uses, on the residuals' norms);
+//   - the rounding of the reference's own chain (base, precomputed and query tables, the m + 1 additions): c1
+//     roundings of at most 2^-24 * 3 (|q|^2 + |c|^2 + |w|^2) each;
+//   - the rounding of a itself and of ||a||^2.
+// Every row with compressed distance <= bound therefore scores below bound - ||a||^2 + eps.  For inner product the
+// score is -<q, w> and the threshold bound - base + eps with base = -<q, centroid> as the reference computed it.
+// Queries the tensor cores cannot score (no bound, non-finite or beyond the 16-bit range) are marked for the
+// per-query kernel instead.
+__global__ void __launch_bounds__(256) tc_gather_kernel(GatherArgs a) {
+  const size_t l = blockIdx.x;
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t p0 = a.pair_off[l], n = a.pair_off[l + 1] - p0;
+  if (n == 0 || a.list_off[l + 1] == a.list_off[l]) return;
+  const uint32_t rows = (n + 255u) / 256u * 256u;
+  const uint32_t a0 = a.a_off[l];
+  const float* cen = a.centroids + l * size_t(a.pd);
+  const float mul = a.is_l2 ? -2.f : -1.f;
+  for (uint32_t r = blockIdx.y * 8 + w; r < rows; r += gridDim.y * 8) {
+    const uint32_t arow = a0 + r;
+    if (r >= n) {
+      if (lane == 0) a.thr[arow] = -INFINITY;  // filler row: never below its threshold
+      continue;
+    }
+    const uint2 pr = a.pairs[p0 + r];
+    const uint32_t q = pr.x;
+    const float* qv = a.queries + size_t(q) * a.pd;
+    uint16_t* dst = a.qg + size_t(arow) * a.Kp;
+    float mx = 0.f, a2 = 0.f, q2 = 0.f;
+    bool fin = true;
+    for (int c0 = 0; c0 < a.Kp; c0 += 128) {  // four elements per lane and step
+      const int c = c0 + lane * 4;
+      float x[4] = {0.f, 0.f, 0.f, 0.f};
+      if (c < a.pd) {  // pd is a multiple of 8
+        const float4 qq = *reinterpret_cast<const float4*>(qv + c);
+        x[0] = qq.x;
+        x[1] = qq.y;
+        x[2] = qq.z;
+        x[3] = qq.w;
+        q2 = __fmaf_rn(qq.x, qq.x, __fmaf_rn(qq.y, qq.y, __fmaf_rn(qq.z, qq.z, __fmaf_rn(qq.w, qq.w, q2))));
+        if (a.is_l2) {
+          const float4 cc = *reinterpret_cast<const float4*>(cen + c);
+          x[0] = __fsub_rn(x[0], cc.x);
+          x[1] = __fsub_rn(x[1], cc.y);
+          x[2] = __fsub_rn(x[2], cc.z);
+          x[3] = __fsub_rn(x[3], cc.w);
+        }
+      }
+      uint16_t h[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        mx = fmaxf(mx, fabsf(x[i]));
+        a2 = __fmaf_rn(x[i], x[i], a2);
+        fin = fin && fabsf(x[i]) <= 3.0e38f;
+        h[i] = to_operand(x[i] * mul, a.bf16);
+      }
+      if (c < a.Kp)
+        *reinterpret_cast<uint2*>(dst + c) =
+            make_uint2(uint32_t(h[0]) | (uint32_t(h[1]) << 16), uint32_t(h[2]) | (uint32_t(h[3]) << 16));
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(FV_FULL, mx, o));
+      a2 += __shfl_xor_sync(FV_FULL, a2, o);
+      q2 += __shfl_xor_sync(FV_FULL, q2, o);
+    }
+    fin = __all_sync(FV_FULL, fin);
+    if (lane == 0) {
+      const uint32_t tb = a.tau_bits[q];
+      const bool in_range = fin && (a.bf16 ? mx <= 1.0e38f : mx * (a.is_l2 ? 2.f : 1.f) <= 65504.f);
+      const float base = __uint_as_float(pr.y);
+      float thr = -INFINITY;
+      if (tb != 0xFFFFFFFFu && in_range) {
+        const float tau = order_bits_to_float(tb);
+        const float u16 = a.bf16 ? 0.00390625f : 0.00048828125f;
+        const float an = sqrtf(a2), bn = a.bn, kf = a.kf;
+        const float e_dot = (2.f * u16 * (1.f + u16) + kf * 4.7683716e-7f + kf * 1.1920929e-7f) * an * bn +
+                            5.9604645e-8f * sqrtf(kf) * (an + bn);
+        const float e_norm = (kf + 16.f) * 4.7683716e-7f * bn * bn + 1.1920929e-7f * bn * bn;
+        const float e_score = a.is_l2 ? 2.f * e_dot + e_norm + kf * 4.7683716e-7f * (a2 + bn * bn) : e_dot;
+        const float e_chain = a.c1 * 5.9604645e-8f * 3.f * (q2 + a.cw2);
+        const float e_self = 2.4e-7f * (an + bn) * an + 2.0e-6f * a2;
+        const float eps = 1.05f * (e_score + e_chain + e_self) + 1e-30f;
+        thr = a.is_l2 ? (tau - a2) + eps : (tau - base) + eps;
+        if (!(thr == thr) || thr == INFINITY) thr = -INFINITY;  // a margin that is not a number: leave it to the other kernel
+      }
+      if (thr == -INFINITY) a.cand_cnt[q] = uint32_t(a.cap) + 1u;  // re-run by the per-query kernel
+      a.thr[arow] = thr;
+      a.g_q[arow] = q;
+      a.g_l[arow] = uint32_t(l);
+      a.g_base[arow] = base;
+    }
+  }
+}
+
+struct RescoreArgs {
+  const u64* pool;
+  const unsigned int* pool_cnt;
+  unsigned int pool_cap;
+  const uint32_t* g_q;
+  const uint32_t* g_l;
+  const float* g_base;
+  const uint32_t* list_off;
+  const uint8_t* codes;
+  const uint32_t* ids;
+  const float* qtab;
+  const float* pre;  // or null (inner product)
+  int m;
+  const uint32_t* tau_bits;
+  u64* cand;
+  uint32_t* cand_cnt;
+  int cap;
+};
+
+// One thread per survivor: the reference's compressed distance (ivfpq.rs:256-262, :272-276), bit for bit; kept if
+// at or below the query's bound.
+__global__ void __launch_bounds__(128) rescore_kernel(RescoreArgs a) {
+  const size_t c = blockIdx.x;
+  const unsigned int n = min(a.pool_cnt[c], a.pool_cap);
+  const size_t tab = size_t(a.m) * KSUB;
+  for (unsigned int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
+    const u64 e = a.pool[c * size_t(a.pool_cap) + i];
+    const uint32_t arow = uint32_t(e >> 32), row = uint32_t(e);
+    const uint32_t q = a.g_q[arow], l = a.g_l[arow];
+    const size_t r = size_t(a.list_off[l]) + row;
+    const uint8_t* code = a.codes + r * a.m;
+    const float* qt = a.qtab + size_t(q) * tab;
+    const float* pt = a.pre ? a.pre + size_t(l) * tab : nullptr;
+    float d = a.g_base[arow];
+    if (a.m == 16) {  // all 32 table reads in flight before the chain of additions starts
+      const uint4 cw = *reinterpret_cast<const uint4*>(code);
+      const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
+      float t[16], pv[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int cj = int((cws[j >> 2] >> ((j & 3) * 8)) & 0xFFu);
+        t[j] = __ldg(qt + j * 256 + cj);
+        pv[j] = pt ? __ldg(pt + j * 256 + cj) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) d = __fadd_rn(d, pt ? __fadd_rn(pv[j], t[j]) : t[j]);
+    } else {
+      for (int j = 0; j < a.m; ++j) {
+        const int cj = code[j];
+        float t = __ldg(qt + j * 256 + cj);
+        if (pt) t = __fadd_rn(__ldg(pt + j * 256 + cj), t);
+        d = __fadd_rn(d, t);
+      }
+    }
+    if (d < INFINITY && order_bits(d) <= a.tau_bits[q]) {
+      const uint32_t slot = atomicAdd(a.cand_cnt + q, 1u);
+      if (slot < uint32_t(a.cap)) a.cand[size_t(q) * a.cap + slot] = make_key(d, __ldg(a.ids + r));
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 static int launch_block_scan(fv_ctx* ctx, const ScanArgs& a, size_t nblocks, bool use_pre) {
   const size_t tab = size_t(a.m) * KSUB;
@@ -891,10 +1179,18 @@ static int bucket_pairs(fv_ctx* ctx, const ScanIndex& ix, const u64* cells, size
   return FV_OK;
 }
 
-// Stages (fv_stats.stage_ms) of an IVF-PQ search: 0 coarse cells (marked by the caller), 1 query tables and, on the
-// list-major path, the bound pass, 2 bucketing the (query, probe) pairs by list, 3 the scan, 4 sorting the
-// candidates, re-ranking and any re-run of overflowed queries, 5 keys -> neighbours (marked by the caller).  The
-// per-query kernel alone: everything in stage 3, stages 2 and 4 empty.
+bool ivfpq_wants_tensor(int mode, size_t nq, size_t nprobe, size_t nlist, int shard_world) {
+  if (mode == 3) return nq >= 1;
+  if (mode != 0) return false;
+  const size_t owned_lists = std::max<size_t>(1, nlist / size_t(std::max(1, shard_world)));
+  return nq >= 256 && nq * nprobe >= 96 * owned_lists;
+}
+
+// Stages (fv_stats.stage_ms) of an IVF-PQ search: 0 coarse cells (marked by the caller); 1 query tables and, on the
+// list-major paths, the bound pass; 2 bucketing the (query, probe) pairs by list (tensor-core pass: plus the task
+// table and the gathered operand rows); 3 the scan (the per-query kernel, the list-major table kernel, or the
+// tensor-core kernel); 4 re-scoring survivors (tensor-core pass); 5 sorting the candidates, re-ranking and any re-run
+// of queries by the per-query kernel; 6 keys -> neighbours (marked by the caller).
 int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, const u64* cells, int nprobe, int keep,
                int k, bool refine, bool candidates, int mode, int cand_slots, const ScanOut& out) {
   const bool use_pre = ix.metric == FV_L2 && ix.pre != nullptr;
@@ -948,23 +1244,27 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
   a.out_counts = out.counts;
   a.rows_scanned = d_rows;
 
-  // The list-major scan needs enough queries per list to fill its 32-lane groups: on average at least 24 pairs per
-  // list this shard owns.
-  const size_t owned_lists = std::max<size_t>(1, ix.nlist / size_t(std::max(1, ix.shard_world)));
-  bool list_major = ix.m == 16 && ix.codes_t && separable && keep <= 1024 && mode != 1;
-  // Measured at 1M x 128, 10,000 queries, nprobe 64: 7.8 ms against the per-query kernel's 7.8 ms, plus 1.9 ms of bound
-  // pass, bucketing and sorting: no faster, so the automatic choice does not take it.
-  (void)owned_lists;
-  if (list_major && mode == 0) list_major = false;
-  if (!list_major) {
+  // Which scan.  Both list-major paths need m = 16 (the bound pass reads the sub-quantizer-major codes), a table that
+  // separates into a list part and a query part, and at most 1024 kept candidates.  The tensor-core pass also needs
+  // the reconstructed rows and enough pairs per list to fill its 256-query tiles: on average at least 96 per list
+  // this shard owns.  The table scan is never chosen automatically (measured no faster than the per-query kernel).
+  enum { BLOCK, LIST_TABLE, LIST_TENSOR } path = BLOCK;
+  const bool list_ok = ix.m == 16 && ix.codes_t && separable && keep <= 1024;
+  const bool tensor_ok = list_ok && ix.recon != nullptr;
+  if (mode == 2 && list_ok) path = LIST_TABLE;
+  if (tensor_ok && ivfpq_wants_tensor(mode, nq, size_t(nprobe), ix.nlist, ix.shard_world)) path = LIST_TENSOR;
+  if (path == BLOCK) {
     stage_mark(ctx);  // 1
     stage_mark(ctx);  // 2 (empty)
     FV_TRY(launch_block_scan(ctx, a, nq, use_pre));
     stage_mark(ctx);  // 3
     stage_mark(ctx);  // 4 (empty)
+    stage_mark(ctx);  // 5 (empty)
   } else {
-    // candidate slots per query: 1024, fewer when the buffers of a large batch would pass 256 MB
-    int cap = 1024;
+    // candidate slots per query: 2048 (at the benchmark's size one query in twenty finds more than 1024 rows at or
+    // below its bound, and any re-run costs the latency of a whole pass of the per-query kernel), fewer when the
+    // buffers of a large batch would pass 256 MB
+    int cap = 2048;
     while (cap > 256 && nq * size_t(cap) * sizeof(u64) > (size_t(256) << 20)) cap >>= 1;
     if (cand_slots > 0) cap = std::min(cand_slots, 4096);
     // Bound pass: each query's nearest owned lists until they hold 32 * keep rows, i.e. four times `keep` minima
@@ -1005,31 +1305,120 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     auto bound_k = use_pre ? ivfpq_list_scan_kernel<true, true> : ivfpq_list_scan_kernel<false, true>;
     auto main_k = use_pre ? ivfpq_list_scan_kernel<true, false> : ivfpq_list_scan_kernel<false, false>;
     FV_CUDA(cudaFuncSetAttribute(bound_k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(LS_SMEM)));
-    FV_CUDA(cudaFuncSetAttribute(main_k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(LS_SMEM)));
     bound_k<<<ctx->sm_count, LS_THREADS, LS_SMEM, ctx->stream>>>(la);
-    bound_select_kernel<<<unsigned(nq), 128, mcap * sizeof(uint32_t), ctx->stream>>>(la.minima, la.minima_cnt, int(mcap), keep,
-                                                                                   tau_bits);
+    {
+      const int wpb = mcap <= 2048 ? 4 : 1;  // warps (queries) per block, by the shared memory their minima take
+      const size_t ssmem = size_t(wpb) * mcap * sizeof(uint32_t);
+      if (ssmem > 40 * 1024)
+        FV_CUDA(cudaFuncSetAttribute(bound_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ssmem)));
+      bound_select_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, ssmem, ctx->stream>>>(la.minima, la.minima_cnt, int(mcap),
+                                                                                             keep, nq, tau_bits);
+    }
     ctx->stats.launches += 2;
     FV_CUDA(cudaGetLastError());
     stage_mark(ctx);  // 1
     FV_TRY(bucket_pairs(ctx, ix, cells, nq, nprobe, 0, pb_set, pairs_b));
-    stage_mark(ctx);  // 2
-    la.pair_off = pb_set.pair_off;
-    la.task_off = pb_set.task_off;
-    la.pairs = pairs_b;
-    la.counters = pb_set.counters;
-    la.tau_bits = tau_bits;
-    la.cand = ctx->scratch[9].as<u64>();
-    la.cand_cnt = pb_set.per_query;
-    la.cap = cap;
-    la.rows_scanned = d_rows + 1;
-    main_k<<<ctx->sm_count, LS_THREADS, LS_SMEM, ctx->stream>>>(la);
-    ctx->stats.launches++;
-    FV_CUDA(cudaGetLastError());
-    stage_mark(ctx);  // 3
+    u64* cand = ctx->scratch[9].as<u64>();
+    uint32_t* cand_cnt = pb_set.per_query;
+    unsigned int* pool_cnt = nullptr;
+    int tc_grid = 0;
+    unsigned int pool_cap = 0;
+    if (path == LIST_TABLE) {
+      stage_mark(ctx);  // 2
+      la.pair_off = pb_set.pair_off;
+      la.task_off = pb_set.task_off;
+      la.pairs = pairs_b;
+      la.counters = pb_set.counters;
+      la.tau_bits = tau_bits;
+      la.cand = cand;
+      la.cand_cnt = cand_cnt;
+      la.cap = cap;
+      la.rows_scanned = d_rows + 1;
+      FV_CUDA(cudaFuncSetAttribute(main_k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(LS_SMEM)));
+      main_k<<<ctx->sm_count, LS_THREADS, LS_SMEM, ctx->stream>>>(la);
+      ctx->stats.launches++;
+      FV_CUDA(cudaGetLastError());
+      stage_mark(ctx);  // 3
+    } else {
+      TcInfo ti{};
+      tc_info(ix.recon, &ti);
+      const size_t Kp = size_t(ti.Kp);
+      // gathered operand rows: every pair once, every list's rows rounded up to whole 256-row tiles
+      const size_t a_rows = nq * size_t(nprobe) + 256 * std::min<size_t>(ix.nlist, nq * size_t(nprobe)) + 256;
+      const size_t max_tasks = a_rows / 256;
+      FV_TRY(ctx->scratch[12].reserve(a_rows * Kp * sizeof(uint16_t)));
+      FV_TRY(ctx->scratch[13].reserve(a_rows * 4 * sizeof(uint32_t) + 64));
+      FV_TRY(ctx->scratch[14].reserve(max_tasks * sizeof(uint4) + (ix.nlist + 8 + size_t(ctx->sm_count)) * sizeof(uint32_t)));
+      pool_cap = unsigned(std::max<size_t>(32768, nq * 2048 / size_t(ctx->sm_count)));
+      FV_TRY(ctx->scratch[15].reserve(size_t(ctx->sm_count) * pool_cap * sizeof(u64)));
+      uint16_t* qg = ctx->scratch[12].as<uint16_t>();
+      float* thr = ctx->scratch[13].as<float>();
+      uint32_t* g_q = reinterpret_cast<uint32_t*>(thr + a_rows);
+      uint32_t* g_l = g_q + a_rows;
+      float* g_base = reinterpret_cast<float*>(g_l + a_rows);
+      uint4* tasks = ctx->scratch[14].as<uint4>();
+      uint32_t* a_off = reinterpret_cast<uint32_t*>(tasks + max_tasks);
+      uint32_t* ntasks = a_off + ix.nlist;
+      pool_cnt = ntasks + 8;
+      tc_tasks_kernel<<<1, 1024, 0, ctx->stream>>>(pb_set.pair_off, ix.list_off, ix.roff8, ix.roff8 + ix.nlist + 1, ix.nlist,
+                                                   tasks, a_off, ntasks, d_rows + 1);
+      ctx->stats.launches++;
+      FV_CUDA(cudaGetLastError());
+      GatherArgs ga{};
+      ga.pair_off = pb_set.pair_off;
+      ga.list_off = ix.list_off;
+      ga.a_off = a_off;
+      ga.pairs = pairs_b;
+      ga.queries = q;
+      ga.centroids = ix.centroids;
+      ga.tau_bits = tau_bits;
+      ga.cand_cnt = cand_cnt;
+      ga.cap = cap;
+      ga.pd = ix.pd;
+      ga.Kp = ti.Kp;
+      ga.is_l2 = ix.metric == FV_L2 ? 1 : 0;
+      ga.bf16 = ti.bf16 ? 1 : 0;
+      ga.kf = float(ti.Kp);
+      ga.bn = std::sqrt(ti.max_norm2);
+      ga.cw2 = ix.cen_norm2_max + ix.code_norm2_max;
+      ga.c1 = 4.f * float(ix.pd / 8 + ix.m + 3 * ix.dsub + 24);
+      ga.qg = qg;
+      ga.thr = thr;
+      ga.g_q = g_q;
+      ga.g_l = g_l;
+      ga.g_base = g_base;
+      tc_gather_kernel<<<dim3(unsigned(ix.nlist), 4), 256, 0, ctx->stream>>>(ga);
+      ctx->stats.launches++;
+      FV_CUDA(cudaGetLastError());
+      stage_mark(ctx);  // 2
+      FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, thr, tasks, ntasks, ctx->scratch[15].as<u64>(), pool_cnt,
+                          pool_cap, &tc_grid));
+      stage_mark(ctx);  // 3
+      RescoreArgs ra{};
+      ra.pool = ctx->scratch[15].as<u64>();
+      ra.pool_cnt = pool_cnt;
+      ra.pool_cap = pool_cap;
+      ra.g_q = g_q;
+      ra.g_l = g_l;
+      ra.g_base = g_base;
+      ra.list_off = ix.list_off;
+      ra.codes = ix.codes;
+      ra.ids = ix.ids;
+      ra.qtab = qtab;
+      ra.pre = use_pre ? ix.pre : nullptr;
+      ra.m = ix.m;
+      ra.tau_bits = tau_bits;
+      ra.cand = cand;
+      ra.cand_cnt = cand_cnt;
+      ra.cap = cap;
+      rescore_kernel<<<dim3(unsigned(tc_grid), 32), 128, 0, ctx->stream>>>(ra);
+      ctx->stats.launches++;
+      FV_CUDA(cudaGetLastError());
+    }
+    stage_mark(ctx);  // 4
     FinishArgs fa{};
-    fa.cand = la.cand;
-    fa.cand_cnt = la.cand_cnt;
+    fa.cand = cand;
+    fa.cand_cnt = cand_cnt;
     fa.cap = cap;
     fa.counters = pb_set.counters;
     fa.over_ids = pb_set.extra;
@@ -1043,26 +1432,32 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     ctx->stats.launches++;
     FV_CUDA(cudaGetLastError());
     uint32_t n_over = 0;
+    std::vector<unsigned int> h_pool(size_t(tc_grid) + 1, 0u);
     FV_CUDA(cudaMemcpyAsync(&n_over, pb_set.counters + LS_C_OVER, sizeof(n_over), cudaMemcpyDeviceToHost, ctx->stream));
+    if (tc_grid) {
+      FV_CUDA(cudaMemcpyAsync(h_pool.data(), pool_cnt, size_t(tc_grid) * sizeof(unsigned int), cudaMemcpyDeviceToHost, ctx->stream));
+      FV_CUDA(cudaMemcpyAsync(&h_pool[tc_grid], tc_error_word(ix.recon), sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    }
     FV_CUDA(cudaStreamSynchronize(ctx->stream));
-    if (n_over) {  // buffers that ran over: those queries once more, by the per-query kernel (their rows are counted already)
+    if (tc_grid && h_pool[tc_grid]) return fail(FV_ERR_TIMEOUT, "a bounded wait inside the tensor-core kernel ran out");
+    bool pool_over = false;
+    for (int c = 0; c < tc_grid; ++c) {
+      pool_over = pool_over || h_pool[c] > pool_cap;
+      ctx->stats.dist_evals += h_pool[c];  // survivors of the tensor-core pass: pairs re-scored exactly
+    }
+    if (pool_over) {  // survivors were dropped: the whole batch once more, by the per-query kernel
+      ScanArgs r = a;
+      r.rows_scanned = nullptr;
+      FV_TRY(launch_block_scan(ctx, r, nq, use_pre));
+      n_over = uint32_t(nq);
+    } else if (n_over) {  // buffers that ran over, queries the tensor cores could not score: those queries once more
       ScanArgs r = a;
       r.qids = fa.over_ids;
       r.rows_scanned = nullptr;
       FV_TRY(launch_block_scan(ctx, r, n_over, use_pre));
     }
     ctx->stats.uncertified = n_over;
-    stage_mark(ctx);  // 4
-#ifdef FV_DEBUG_DUMP
-    if (const char* path = getenv("FERROVEC_DEBUG_DUMP")) {
-      std::vector<uint32_t> h(3 * nq);
-      cudaMemcpy(h.data(), tau_bits, nq * 4, cudaMemcpyDeviceToHost);
-      cudaMemcpy(h.data() + nq, pb_set.per_query, nq * 4, cudaMemcpyDeviceToHost);
-      cudaMemcpy(h.data() + 2 * nq, pa_set.per_query, nq * 4, cudaMemcpyDeviceToHost);
-      FILE* f = fopen(path, "wb");
-      if (f) { fwrite(h.data(), 4, h.size(), f); fclose(f); }
-    }
-#endif
+    stage_mark(ctx);  // 5
   }
   unsigned long long rows[2] = {0, 0};
   FV_CUDA(cudaMemcpyAsync(rows, d_rows, sizeof(rows), cudaMemcpyDeviceToHost, ctx->stream));

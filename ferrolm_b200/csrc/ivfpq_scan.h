@@ -25,6 +25,12 @@ struct ScanIndex {
   // with len16 = off16[l+1] - off16[l] (the list length rounded up to 16) byte (j, r) sits at j * len16 + r.
   const uint8_t* codes_t;     // or null
   const uint32_t* off16;      // nlist + 1
+  // Tensor-core pass: every stored row once more as the vector its code stands for (centroid + codewords), 16-bit,
+  // list by list with every list starting at a multiple of 8 rows (roff8[l]); null when not built.
+  TcSide* recon;
+  const uint32_t* roff8;      // nlist + 1 row offsets, then the nlist list numbers in order of decreasing length
+  float cen_norm2_max;        // largest squared centroid norm
+  float code_norm2_max;       // sum over sub-quantizers of their largest squared codeword norm
 };
 
 struct ScanOut {
@@ -34,12 +40,23 @@ struct ScanOut {
   uint32_t* counts;      // nq                                 (candidates == true)
 };
 
-// mode: 0 = pick by size, 1 = one block per query only, 2 = the list-major scan whenever the index allows it.
+// mode: 0 = pick by size, 1 = one block per query only, 2 = the list-major table scan whenever the index allows it,
+// 3 = the list-major tensor-core pass whenever the index allows it.
 // `cells`: nq x nprobe keys (distance, list), ascending.  `keep` = candidates kept by compressed distance;
 // `refine`: re-rank them exactly and cut to k.  Marks the context's stages and fills stats.rows_scanned.
-// `cand_slots`: candidate slots per query of the list-major scan (0 = default).  Scratch slots used: 5, 6, 7, 8, 9.
+// `cand_slots`: candidate slots per query of the list-major scans (0 = default).
+// Scratch slots used: 5, 6, 7, 8, 9, 12, 13, 14, 15.
 int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* d_queries, size_t nq, const u64* d_cells, int nprobe,
                int keep, int k, bool refine, bool candidates, int mode, int cand_slots, const ScanOut& out);
+
+// Whether a search of this size would take the tensor-core pass if the index has what it needs (so that the index
+// builds the reconstruction only when it will be used).
+bool ivfpq_wants_tensor(int mode, size_t nq, size_t nprobe, size_t nlist, int shard_world);
+
+// Builds the 16-bit reconstruction of every stored row for the tensor-core pass (padded dimension up to 128).
+int build_reconstruction(fv_ctx* ctx, int metric, int pd, int m, int dsub, const uint32_t* h_off, size_t nlist,
+                         const uint32_t* d_list_off, const uint8_t* d_codes, const float* d_centroids,
+                         const float* d_codebooks, TcSide** recon, DevBuf* roff8);
 
 // Builds codes_t / off16 from the row-major lists (m = 16).  h_off: nlist + 1 host offsets.
 int build_transposed_codes(fv_ctx* ctx, const uint32_t* h_off, size_t nlist, const uint32_t* d_list_off,

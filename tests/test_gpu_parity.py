@@ -392,7 +392,7 @@ def test_ivfpq_list_major_scan_matches_the_oracle(fv, oracle, ivfpq16_pair, npro
     g, o, base, queries = ivfpq16_pair
     want, wc, rows = o.search_batch(queries, k, nprobe, refine, want_rows=True)
     outs = {}
-    for mode in (2, 1):
+    for mode in (3, 2, 1):
         g.set_scan_mode(mode)
         got, gc = g.search_batch(queries, k, nprobe, refine)
         eq, total = assert_same_neighbours(got, gc, want, wc, f"ivfpq m=16 mode {mode} nprobe={nprobe} refine={refine}")
@@ -400,13 +400,14 @@ def test_ivfpq_list_major_scan_matches_the_oracle(fv, oracle, ivfpq16_pair, npro
         assert g.ctx.stats()["rows_scanned"] == rows
         outs[mode] = got
     g.set_scan_mode(0)
-    assert outs[1].tobytes() == outs[2].tobytes()
+    assert outs[1].tobytes() == outs[2].tobytes() == outs[3].tobytes()
 
 
-def test_ivfpq_list_major_scan_reruns_queries_whose_buffer_overflows(fv, oracle, ivfpq16_pair):
+@pytest.mark.parametrize("mode", [2, 3])
+def test_ivfpq_list_major_scan_reruns_queries_whose_buffer_overflows(fv, oracle, ivfpq16_pair, mode):
     g, o, base, queries = ivfpq16_pair
     want, wc = o.search_batch(queries, 10, 16, 10)
-    g.set_scan_mode(2)
+    g.set_scan_mode(mode)
     g.set_candidate_slots(8)  # far fewer slots than rows below the bound: most queries overflow and are re-run
     try:
         got, gc = g.search_batch(queries, 10, 16, 10)
@@ -427,16 +428,18 @@ def test_ivfpq_list_major_scan_inner_product_and_ragged_lists(fv, oracle, ctx):
     g = fv.IvfPq.train(ctx, IP, dim, base[:3000], fv.IvfPqParams(150, 16, 4, True, 1))
     g.add(base)
     o = oracle.IvfPq.load(g.save())
-    g.set_scan_mode(2)
     for nprobe, refine in [(20, 0), (150, 5), (3, 2)]:
-        got, gc = g.search_batch(queries, 10, nprobe, refine)
         want, wc, rows = o.search_batch(queries, 10, nprobe, refine, want_rows=True)
-        eq, total = assert_same_neighbours(got, gc, want, wc, f"ivfpq IP list-major nprobe={nprobe}")
-        assert eq == total and g.ctx.stats()["rows_scanned"] == rows
+        for mode in (2, 3):
+            g.set_scan_mode(mode)
+            got, gc = g.search_batch(queries, 10, nprobe, refine)
+            eq, total = assert_same_neighbours(got, gc, want, wc, f"ivfpq IP list-major mode {mode} nprobe={nprobe}")
+            assert eq == total and g.ctx.stats()["rows_scanned"] == rows
 
 
+@pytest.mark.parametrize("mode", [2, 3])
 @pytest.mark.parametrize("refine", [0, 5])
-def test_ivfpq_list_major_scan_on_list_shards(fv, oracle, ctx, ivfpq16_pair, refine):
+def test_ivfpq_list_major_scan_on_list_shards(fv, oracle, ctx, ivfpq16_pair, refine, mode):
     import torch
 
     _, o, base, queries = ivfpq16_pair
@@ -449,7 +452,7 @@ def test_ivfpq_list_major_scan_on_list_shards(fv, oracle, ctx, ivfpq16_pair, ref
         g = fv.IvfPq.load(ctx, empty)
         g.set_shard(r, world)
         g.add(base)
-        g.set_scan_mode(2)
+        g.set_scan_mode(mode)
         parts.append(g.search_candidates(dq, k * refine, nprobe) if refine else g.search_batch(dq, k, nprobe, 0))
         scanned += ctx.stats()["rows_scanned"]
     assert scanned == rows
