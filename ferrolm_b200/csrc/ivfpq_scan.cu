@@ -427,7 +427,8 @@ __host__ __device__ __forceinline__ uint32_t ls_tasks(uint32_t len, uint32_t npa
 }
 
 // counters (u32 words): 0 next task, 1 number of tasks, 2 queries whose buffer overflowed, 3 number of pairs
-enum { LS_C_NEXT = 0, LS_C_TASKS = 1, LS_C_OVER = 2, LS_C_PAIRS = 3, LS_NCOUNTERS = 8 };
+// 4 queries left to the per-query kernel
+enum { LS_C_NEXT = 0, LS_C_TASKS = 1, LS_C_OVER = 2, LS_C_PAIRS = 3, LS_C_RERUN = 4, LS_NCOUNTERS = 8 };
 
 __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(uint32_t(__cvta_generic_to_shared(dst_smem))), "l"(src)
@@ -765,10 +766,22 @@ __global__ void __launch_bounds__(128) bound_select_kernel(const float* __restri
 
 struct FinishArgs {
   const u64* cand;
-  const uint32_t* cand_cnt;
+  uint32_t* cand_cnt;
   int cap;
   uint32_t* counters;
+  const uint32_t* qids;    // second round: the queries to finish (null: all, block b = query b)
+  // A query whose buffer ran over (count > cap):
+  //   tighten == 1: its stored `cap` candidates still give a valid, tighter bound -- the keep-th smallest of them,
+  //                 since that many rows reach it -- which goes to tau_bits[q]; the count is reset, redo[q] is set and
+  //                 q is appended to over_ids, so that the survivors of exactly these queries are re-scored against
+  //                 the new bound and finished in a second round;
+  //   tighten == 0: q is appended to rerun_ids, the queries the per-query kernel takes over.
+  // A count of 0xFFFFFFFF marks a query the scan could not handle at all: always to rerun_ids.
+  int tighten;
+  uint32_t* tau_bits;
+  uint32_t* redo;
   uint32_t* over_ids;
+  uint32_t* rerun_ids;
 };
 
 // One block per query: the best `keep` of the appended candidates, then the common tail.
@@ -776,19 +789,29 @@ __global__ void __launch_bounds__(256) ivfpq_finish_kernel(ScanArgs a, FinishArg
   u64* lists = reinterpret_cast<u64*>(dyn_smem());  // n2max keys
   u64* rerank = lists + n2max;                      // keep + k
   float* sq = reinterpret_cast<float*>(rerank + a.keep + a.k);
-  const size_t q = blockIdx.x;
+  const size_t q = f.qids ? size_t(f.qids[blockIdx.x]) : size_t(blockIdx.x);
   const int tid = threadIdx.x;
   const uint32_t cnt = f.cand_cnt[q];
-  if (cnt > uint32_t(f.cap)) {  // the per-query kernel re-runs this query
-    if (tid == 0) f.over_ids[atomicAdd(f.counters + LS_C_OVER, 1u)] = uint32_t(q);
+  if (cnt == 0xFFFFFFFFu || (cnt > uint32_t(f.cap) && !f.tighten)) {
+    if (tid == 0) f.rerun_ids[atomicAdd(f.counters + LS_C_RERUN, 1u)] = uint32_t(q);
     return;
   }
+  const int have = int(min(cnt, uint32_t(f.cap)));
   int n = 32;
-  while (n < int(cnt) || n < a.keep) n <<= 1;
-  for (int e = tid; e < n; e += blockDim.x) lists[e] = e < int(cnt) ? f.cand[q * size_t(f.cap) + e] : FV_EMPTY_KEY;
+  while (n < have || n < a.keep) n <<= 1;
+  for (int e = tid; e < n; e += blockDim.x) lists[e] = e < have ? f.cand[q * size_t(f.cap) + e] : FV_EMPTY_KEY;
   for (int c = tid; c < a.pd; c += blockDim.x) sq[c] = a.queries[q * size_t(a.pd) + c];
   __syncthreads();
   block_sort(lists, n);
+  if (cnt > uint32_t(f.cap)) {  // ran over: a tighter bound from what was stored, and a second round
+    if (tid == 0) {
+      f.tau_bits[q] = uint32_t(lists[a.keep - 1] >> 32);  // cap >= keep entries are stored
+      f.cand_cnt[q] = 0;
+      f.redo[q] = 1;
+      f.over_ids[atomicAdd(f.counters + LS_C_OVER, 1u)] = uint32_t(q);
+    }
+    return;
+  }
   scan_tail(a, q, lists, rerank, sq);
 }
 
@@ -1051,7 +1074,7 @@ __global__ void __launch_bounds__(256) tc_gather_kernel(GatherArgs a) {
         thr = a.is_l2 ? (tau - a2) + eps : (tau - base) + eps;
         if (!(thr == thr) || thr == INFINITY) thr = -INFINITY;  // a margin that is not a number: leave it to the other kernel
       }
-      if (thr == -INFINITY) a.cand_cnt[q] = uint32_t(a.cap) + 1u;  // re-run by the per-query kernel
+      if (thr == -INFINITY) a.cand_cnt[q] = 0xFFFFFFFFu;  // left to the per-query kernel (none of its rows survives)
       a.thr[arow] = thr;
       a.g_q[arow] = q;
       a.g_l[arow] = uint32_t(l);
@@ -1077,6 +1100,7 @@ struct RescoreArgs {
   u64* cand;
   uint32_t* cand_cnt;
   int cap;
+  const uint32_t* only;  // second round: only survivors of queries with only[q] != 0 (null: all)
 };
 
 // One thread per survivor: the reference's compressed distance (ivfpq.rs:256-262, :272-276), bit for bit; kept if
@@ -1089,6 +1113,7 @@ __global__ void __launch_bounds__(128) rescore_kernel(RescoreArgs a) {
     const u64 e = a.pool[c * size_t(a.pool_cap) + i];
     const uint32_t arow = uint32_t(e >> 32), row = uint32_t(e);
     const uint32_t q = a.g_q[arow], l = a.g_l[arow];
+    if (a.only && !a.only[q]) continue;
     const size_t r = size_t(a.list_off[l]) + row;
     const uint8_t* code = a.codes + r * a.m;
     const float* qt = a.qtab + size_t(q) * tab;
@@ -1137,10 +1162,10 @@ static int launch_block_scan(fv_ctx* ctx, const ScanArgs& a, size_t nblocks, boo
 
 // The small arrays of one pass over the pairs, in one allocation; the first `nzero` words must start at zero.
 struct PairSet {
-  uint32_t *pair_cnt, *cursor, *per_query, *counters, *pair_off, *task_off, *extra;  // per_query, extra: nq words each
+  uint32_t *pair_cnt, *cursor, *per_query, *counters, *pair_off, *task_off, *extra, *extra2;  // per_query, extra, extra2: nq words each
   size_t nzero, words;
   static size_t words_for(size_t nlist, size_t nq) {
-    return ((2 * nlist + nq + 1) & ~size_t(1)) + LS_NCOUNTERS + 2 * (nlist + 1) + nq;
+    return ((2 * nlist + nq + 1) & ~size_t(1)) + LS_NCOUNTERS + 2 * (nlist + 1) + 2 * nq;
   }
   void carve(uint32_t* base, size_t nlist, size_t nq) {
     pair_cnt = base;
@@ -1152,7 +1177,8 @@ struct PairSet {
     pair_off = base + nzero;
     task_off = pair_off + nlist + 1;
     extra = task_off + nlist + 1;
-    words = nzero + 2 * (nlist + 1) + nq;
+    extra2 = extra + nq;
+    words = nzero + 2 * (nlist + 1) + 2 * nq;
   }
 };
 
@@ -1320,6 +1346,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     FV_TRY(bucket_pairs(ctx, ix, cells, nq, nprobe, 0, pb_set, pairs_b));
     u64* cand = ctx->scratch[9].as<u64>();
     uint32_t* cand_cnt = pb_set.per_query;
+    RescoreArgs ra{};
     unsigned int* pool_cnt = nullptr;
     int tc_grid = 0;
     unsigned int pool_cap = 0;
@@ -1394,7 +1421,6 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, thr, tasks, ntasks, ctx->scratch[15].as<u64>(), pool_cnt,
                           pool_cap, &tc_grid));
       stage_mark(ctx);  // 3
-      RescoreArgs ra{};
       ra.pool = ctx->scratch[15].as<u64>();
       ra.pool_cnt = pool_cnt;
       ra.pool_cap = pool_cap;
@@ -1416,12 +1442,19 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       FV_CUDA(cudaGetLastError());
     }
     stage_mark(ctx);  // 4
+    // the bound pass is done with its per-query counters: they become the marks of queries that get a second round
+    uint32_t* redo = pa_set.per_query;
+    FV_CUDA(cudaMemsetAsync(redo, 0, nq * sizeof(uint32_t), ctx->stream));
     FinishArgs fa{};
     fa.cand = cand;
     fa.cand_cnt = cand_cnt;
     fa.cap = cap;
     fa.counters = pb_set.counters;
+    fa.tighten = path == LIST_TENSOR ? 1 : 0;  // the table scan keeps no survivor list to re-score
+    fa.tau_bits = tau_bits;
+    fa.redo = redo;
     fa.over_ids = pb_set.extra;
+    fa.rerun_ids = pb_set.extra2;
     int n2max = 32;
     while (n2max < cap || n2max < keep) n2max <<= 1;
     const size_t fsmem = (size_t(n2max) + size_t(keep) + size_t(k)) * sizeof(u64) + size_t(ix.pd) * sizeof(float);
@@ -1431,9 +1464,9 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     ivfpq_finish_kernel<<<unsigned(nq), 256, fsmem, ctx->stream>>>(a, fa, n2max);
     ctx->stats.launches++;
     FV_CUDA(cudaGetLastError());
-    uint32_t n_over = 0;
+    uint32_t h_ctr[LS_NCOUNTERS] = {};
     std::vector<unsigned int> h_pool(size_t(tc_grid) + 1, 0u);
-    FV_CUDA(cudaMemcpyAsync(&n_over, pb_set.counters + LS_C_OVER, sizeof(n_over), cudaMemcpyDeviceToHost, ctx->stream));
+    FV_CUDA(cudaMemcpyAsync(h_ctr, pb_set.counters, sizeof(h_ctr), cudaMemcpyDeviceToHost, ctx->stream));
     if (tc_grid) {
       FV_CUDA(cudaMemcpyAsync(h_pool.data(), pool_cnt, size_t(tc_grid) * sizeof(unsigned int), cudaMemcpyDeviceToHost, ctx->stream));
       FV_CUDA(cudaMemcpyAsync(&h_pool[tc_grid], tc_error_word(ix.recon), sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
@@ -1445,17 +1478,33 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       pool_over = pool_over || h_pool[c] > pool_cap;
       ctx->stats.dist_evals += h_pool[c];  // survivors of the tensor-core pass: pairs re-scored exactly
     }
+    uint32_t n_over = h_ctr[LS_C_OVER], n_rerun = h_ctr[LS_C_RERUN];
     if (pool_over) {  // survivors were dropped: the whole batch once more, by the per-query kernel
       ScanArgs r = a;
       r.rows_scanned = nullptr;
       FV_TRY(launch_block_scan(ctx, r, nq, use_pre));
-      n_over = uint32_t(nq);
-    } else if (n_over) {  // buffers that ran over, queries the tensor cores could not score: those queries once more
-      ScanArgs r = a;
-      r.qids = fa.over_ids;
-      r.rows_scanned = nullptr;
-      FV_TRY(launch_block_scan(ctx, r, n_over, use_pre));
+      n_rerun = uint32_t(nq);
+    } else {
+      if (n_over) {  // second round: the marked queries' survivors against their tightened bounds
+        ra.only = redo;
+        rescore_kernel<<<dim3(unsigned(tc_grid), 32), 128, 0, ctx->stream>>>(ra);
+        fa.qids = fa.over_ids;
+        fa.tighten = 0;
+        ivfpq_finish_kernel<<<n_over, 256, fsmem, ctx->stream>>>(a, fa, n2max);
+        ctx->stats.launches += 2;
+        FV_CUDA(cudaGetLastError());
+        FV_CUDA(cudaMemcpyAsync(&n_rerun, pb_set.counters + LS_C_RERUN, sizeof(n_rerun), cudaMemcpyDeviceToHost, ctx->stream));
+        FV_CUDA(cudaStreamSynchronize(ctx->stream));
+      }
+      if (n_rerun) {  // whatever is left: those queries once more, by the per-query kernel (their rows are counted already)
+        ScanArgs r = a;
+        r.qids = fa.rerun_ids;
+        r.rows_scanned = nullptr;
+        FV_TRY(launch_block_scan(ctx, r, n_rerun, use_pre));
+      }
     }
+    ctx->stats.regrown = n_over;
+    n_over = n_rerun;
     ctx->stats.uncertified = n_over;
     stage_mark(ctx);  // 5
   }
