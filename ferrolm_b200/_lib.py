@@ -116,6 +116,12 @@ SIGNATURES = {
     "fv_padded": (_sz, [_sz]),
     "fv_normalize": (_i, [_vp, _sz, _sz]),
     "fv_recall": (C.c_double, [_vp, _vp, _vp, _sz, _sz, _sz]),
+    "fv_comm_unique_id": (_i, [_vp]),
+    "fv_ctx_comm_init": (_i, [_vp, _vp, _i, _i]),
+    "fv_ctx_comm_rank": (_i, [_vp]),
+    "fv_ctx_comm_size": (_i, [_vp]),
+    "fv_flat_search_sharded_dev": (_i, [_vp, _vp, _sz, _sz, _vp, _vp]),
+    "fv_ivfpq_search_sharded_dev": (_i, [_vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp]),
     "fv_merge_topk_dev": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp]),
     "fv_merge_refine_dev": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp]),
     "fv_merge_topk_static_dev": (_i, [_i, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp]),
@@ -151,7 +157,7 @@ class FerrovecError(RuntimeError):
         self.status = status
 
 
-FV_OK, FV_ERR_ARG, FV_ERR_FILE, FV_ERR_CUDA, FV_ERR_TIMEOUT, FV_ERR_OVERFLOW, FV_ERR_UNSUPPORTED, FV_ERR_NOMEM = range(8)
+FV_OK, FV_ERR_ARG, FV_ERR_FILE, FV_ERR_CUDA, FV_ERR_TIMEOUT, FV_ERR_OVERFLOW, FV_ERR_UNSUPPORTED, FV_ERR_NOMEM, FV_ERR_COMM = range(9)
 
 
 def check(status: int):

@@ -29,7 +29,13 @@ void ctx_release(fv_ctx* ctx) {
   if (--ctx->refs == 0 && ctx->closing) ctx_destroy_now(ctx);
 }
 
+void stage_mark_outer(fv_ctx* ctx) {
+  if (!ctx->timing || ctx->ev_used == 0 || ctx->ev_used > FV_NSTAGE) return;
+  cudaEventRecord(ctx->ev[ctx->ev_used], ctx->stream);
+  ctx->ev_used++;
+}
 void stage_begin(fv_ctx* ctx) {
+  if (ctx->stage_outer) return;
   ctx->ev_used = 0;
   for (int i = 0; i < FV_NSTAGE; i++) ctx->stats.stage_ms[i] = 0.f;
   if (!ctx->timing) return;
@@ -37,12 +43,13 @@ void stage_begin(fv_ctx* ctx) {
   ctx->ev_used = 1;
 }
 void stage_mark(fv_ctx* ctx) {
-  if (!ctx->timing || ctx->ev_used == 0 || ctx->ev_used > FV_NSTAGE) return;
+  if (ctx->stage_outer || !ctx->timing || ctx->ev_used == 0 || ctx->ev_used > FV_NSTAGE) return;
   cudaEventRecord(ctx->ev[ctx->ev_used], ctx->stream);
   ctx->ev_used++;
 }
 void stage_end(fv_ctx* ctx) {
-  if (!ctx->timing) return;
+  if (ctx->stage_outer || !ctx->timing) return;
+  for (int i = 0; i < FV_NSTAGE; i++) ctx->stats.stage_ms[i] = 0.f;
   for (int i = 1; i < ctx->ev_used; i++) {
     float ms = 0.f;
     if (cudaEventElapsedTime(&ms, ctx->ev[i - 1], ctx->ev[i]) == cudaSuccess) ctx->stats.stage_ms[i - 1] = ms;
@@ -82,6 +89,7 @@ int upload_padded(fv_ctx* ctx, const float* src, bool src_is_device, size_t n, s
 static void ctx_destroy_now(fv_ctx* ctx) {
   fv::DeviceGuard g(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  fv::comm_destroy(ctx);
   for (auto& b : ctx->scratch) b.release();
   for (auto& ev : ctx->ev)
     if (ev) cudaEventDestroy(ev);

@@ -506,6 +506,26 @@ __global__ void merge_parts_kernel(const fv_neighbor* __restrict__ parts, const 
 }
 }  // namespace fv
 
+extern "C++" {
+namespace fv {
+int merge_topk_impl(fv_ctx* ctx, const fv_neighbor* d_parts, const uint32_t* d_part_counts, size_t nparts, size_t nq,
+                    size_t k_in, size_t k_out, fv_neighbor* d_out, uint32_t* d_counts) {
+  FV_TRY(ctx->scratch[1].reserve(nq * k_out * sizeof(u64)));
+  u64* keys = ctx->scratch[1].as<u64>();
+  int wpb = 4;
+  while (wpb > 1 && size_t(wpb) * k_out * 8 > 96 * 1024) wpb >>= 1;
+  const size_t smem = size_t(wpb) * k_out * 8;
+  if (smem > 40 * 1024)
+    FV_CUDA(cudaFuncSetAttribute(merge_parts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  merge_parts_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, smem, ctx->stream>>>(d_parts, d_part_counts, int(nparts), nq,
+                                                                                     int(k_in), int(k_out), keys);
+  ctx->stats.launches++;
+  FV_CUDA(cudaGetLastError());
+  return keys_to_neighbors(ctx, keys, nq, int(k_out), int(k_out), d_out, d_counts);
+}
+}  // namespace fv
+}  // extern "C++"
+
 int fv_merge_topk_dev(fv_ctx* ctx, const fv_neighbor* d_parts, const uint32_t* d_part_counts, size_t nparts, size_t nq,
                       size_t k_in, size_t k_out, fv_neighbor* d_out, uint32_t* d_counts) {
   if (!ctx || !d_parts || !d_out || nparts == 0 || k_in == 0 || k_out == 0)
@@ -513,18 +533,35 @@ int fv_merge_topk_dev(fv_ctx* ctx, const fv_neighbor* d_parts, const uint32_t* d
   if (k_out > 4096) return fv::fail(FV_ERR_UNSUPPORTED, "k above 4096 is not supported");
   if (nq == 0) return FV_OK;
   fv::CtxGuard g(ctx);
-  FV_TRY(ctx->scratch[1].reserve(nq * k_out * sizeof(u64)));
-  u64* keys = ctx->scratch[1].as<u64>();
-  int wpb = 4;
-  while (wpb > 1 && size_t(wpb) * k_out * 8 > 96 * 1024) wpb >>= 1;
-  const size_t smem = size_t(wpb) * k_out * 8;
-  if (smem > 40 * 1024)
-    FV_CUDA(cudaFuncSetAttribute(fv::merge_parts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-  fv::merge_parts_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, smem, ctx->stream>>>(
-      d_parts, d_part_counts, int(nparts), nq, int(k_in), int(k_out), keys);
-  ctx->stats.launches++;
-  FV_CUDA(cudaGetLastError());
-  FV_TRY(fv::keys_to_neighbors(ctx, keys, nq, int(k_out), int(k_out), d_out, d_counts));
+  FV_TRY(fv::merge_topk_impl(ctx, d_parts, d_part_counts, nparts, nq, k_in, k_out, d_out, d_counts));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  return FV_OK;
+}
+
+// Search over row shards, one per rank of the context's communicator: the local search (ids carry the shard's id
+// base), one exchange of the per-shard result lists, the merge.  Every rank ends up with the full result.
+// Stages (fv_stats.stage_ms): 0 the local search, 1 the exchange, 2 the merge.
+int fv_flat_search_sharded_dev(fv_flat* ix, const float* d_queries, size_t nq, size_t k, fv_neighbor* d_out,
+                               uint32_t* d_counts) {
+  if (!ix || (nq && (!d_queries || !d_out))) return fv::fail(FV_ERR_ARG, "fv_flat_search_sharded: null argument");
+  fv_ctx* ctx = ix->ctx;
+  fv::CtxGuard g(ctx);
+  const int world = ctx->comm_size;
+  if (world <= 1) return fv_flat_search_batch_dev(ix, d_queries, nq, k, d_out, d_counts);
+  if (nq == 0) return FV_OK;
+  if (k == 0 || k > 4096) return fv::fail(FV_ERR_ARG, "k must be in 1..4096");
+  fv::StageScope scope(ctx);
+  const size_t blk = nq * k * sizeof(fv_neighbor);
+  FV_TRY(ctx->scratch[10].reserve(blk));
+  FV_TRY(ctx->scratch[11].reserve(nq * sizeof(uint32_t)));
+  fv_neighbor* mine = ctx->scratch[10].as<fv_neighbor>();
+  FV_TRY(fv_flat_search_batch_dev(ix, d_queries, nq, k, mine, ctx->scratch[11].as<uint32_t>()));
+  fv::stage_mark_outer(ctx);  // 0
+  FV_TRY(ctx->scratch[15].reserve(size_t(world) * blk));
+  FV_TRY(fv::comm_all_gather(ctx, mine, ctx->scratch[15].p, blk));  // unused slots carry the id 0xFFFFFFFF: no counts needed
+  fv::stage_mark_outer(ctx);  // 1
+  FV_TRY(fv::merge_topk_impl(ctx, ctx->scratch[15].as<fv_neighbor>(), nullptr, size_t(world), nq, k, k, d_out, d_counts));
+  fv::stage_mark_outer(ctx);  // 2
   FV_CUDA(cudaStreamSynchronize(ctx->stream));
   return FV_OK;
 }

@@ -90,6 +90,10 @@ struct fv_ctx {
   cudaEvent_t ev[FV_NSTAGE + 1] = {};
   int ev_used = 0;
   int* d_flags = nullptr;  // small device word array for error / overflow flags
+  bool stage_outer = false;  // an enclosing call owns the stage table: nested searches leave it alone
+  // the group this context belongs to (fv_ctx_comm_init): one rank per GPU, NCCL over NVLink for the one exchange step
+  void* comm = nullptr;      // ncclComm_t
+  int comm_rank = 0, comm_size = 1;
   int refs = 0;            // indexes alive on this context
   bool closing = false;    // fv_ctx_destroy was called while indexes were alive
 };
@@ -125,6 +129,30 @@ void ctx_release(fv_ctx* ctx);
 void stage_begin(fv_ctx* ctx);
 void stage_mark(fv_ctx* ctx);  // closes the current stage
 void stage_end(fv_ctx* ctx);   // after the stream is synchronised: fills stats.stage_ms
+
+// A call that runs several searches under one stage table (the sharded searches): begins the table, keeps the nested
+// calls from restarting or marking it, and closes it when the call returns (the stream is synchronised by then).
+struct StageScope {
+  fv_ctx* ctx;
+  explicit StageScope(fv_ctx* c) : ctx(c) {
+    stage_begin(c);
+    c->stage_outer = true;
+  }
+  ~StageScope() {
+    ctx->stage_outer = false;
+    stage_end(ctx);
+  }
+};
+void stage_mark_outer(fv_ctx* ctx);  // the enclosing call's own marks
+
+// ---- exchange between the ranks of the context's group (comm.cu): every rank contributes `bytes` and receives
+// all contributions, rank-major, on the context's stream.
+int comm_all_gather(fv_ctx* ctx, const void* d_send, void* d_recv, size_t bytes);
+void comm_destroy(fv_ctx* ctx);
+
+// merge of per-shard result lists (flat.cu): nparts blocks of nq * k_in neighbours -> the k_out best per query
+int merge_topk_impl(fv_ctx* ctx, const fv_neighbor* d_parts, const uint32_t* d_part_counts, size_t nparts, size_t nq,
+                    size_t k_in, size_t k_out, fv_neighbor* d_out, uint32_t* d_counts);
 
 // ---- the full-precision scan (flat.cu): for every query the L best rows by (distance, id).
 // d_out_keys: nq * L keys, ascending, FV_EMPTY_KEY padded.  `prefilter_inf`: a distance must be

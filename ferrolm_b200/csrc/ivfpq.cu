@@ -933,9 +933,10 @@ int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out)
 
 // Cross-shard re-ranking: global best `keep` by compressed distance, then the k best of those by exact distance.
 namespace fv {
+// Part p's candidates of query q start at adc[p * adc_stride + q * keep] and exact[p * exact_stride + q * keep].
 __global__ void merge_refine_kernel(const fv_neighbor* __restrict__ adc, const float* __restrict__ exact,
                                     const uint32_t* __restrict__ part_counts, int nparts, size_t nq, int keep, int k,
-                                    u64* __restrict__ out) {
+                                    size_t adc_stride, size_t exact_stride, u64* __restrict__ out) {
   unsigned char* smem_raw = dyn_smem();
   const int lane = threadIdx.x & 31;
   const size_t q = blockIdx.x;
@@ -948,7 +949,7 @@ __global__ void merge_refine_kernel(const fv_neighbor* __restrict__ adc, const f
   u64 bound = FV_EMPTY_KEY;
   for (int p = 0; p < nparts; ++p) {
     const int cnt = part_counts ? int(min(part_counts[size_t(p) * nq + q], uint32_t(keep))) : keep;
-    const fv_neighbor* src = adc + (size_t(p) * nq + q) * size_t(keep);
+    const fv_neighbor* src = adc + size_t(p) * adc_stride + q * size_t(keep);
     for (int i0 = 0; i0 < cnt; i0 += 32) {
       const int i = i0 + lane;
       u64 key = FV_EMPTY_KEY;
@@ -961,13 +962,13 @@ __global__ void merge_refine_kernel(const fv_neighbor* __restrict__ adc, const f
   u64 b2 = FV_EMPTY_KEY;
   for (int p = 0; p < nparts; ++p) {
     const int cnt = part_counts ? int(min(part_counts[size_t(p) * nq + q], uint32_t(keep))) : keep;
-    const size_t base = (size_t(p) * nq + q) * size_t(keep);
+    const size_t base = size_t(p) * adc_stride + q * size_t(keep), ebase = size_t(p) * exact_stride + q * size_t(keep);
     for (int i0 = 0; i0 < cnt; i0 += 32) {
       const int i = i0 + lane;
       u64 key = FV_EMPTY_KEY;
       if (i < cnt && adc[base + i].id != 0xFFFFFFFFu) {
         const u64 ak = make_key(adc[base + i].distance, adc[base + i].id);
-        if (ak <= cut) key = make_key(exact[base + i], adc[base + i].id);
+        if (ak <= cut) key = make_key(exact[ebase + i], adc[base + i].id);
       }
       b2 = warp_list_offer(fin, k, key, b2);
     }
@@ -984,7 +985,8 @@ template <int NPL>
 __global__ void __launch_bounds__(128) merge_refine_select_kernel(const fv_neighbor* __restrict__ adc,
                                                                   const float* __restrict__ exact,
                                                                   const uint32_t* __restrict__ part_counts, int nparts,
-                                                                  size_t nq, int keep, int k, u64* __restrict__ out) {
+                                                                  size_t nq, int keep, int k, size_t adc_stride,
+                                                                  size_t exact_stride, u64* __restrict__ out) {
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const size_t q = blockIdx.x * size_t(blockDim.x >> 5) + w;
   if (q >= nq) return;
@@ -999,7 +1001,7 @@ __global__ void __launch_bounds__(128) merge_refine_select_kernel(const fv_neigh
     if (e < total) {
       const int p = e / keep, i = e - p * keep;
       const int cnt = part_counts ? int(min(part_counts[size_t(p) * nq + q], uint32_t(keep))) : keep;
-      const fv_neighbor nb = adc[(size_t(p) * nq + q) * size_t(keep) + i];
+      const fv_neighbor nb = adc[size_t(p) * adc_stride + q * size_t(keep) + i];
       if (i < cnt && nb.id != 0xFFFFFFFFu) {
         key[j] = make_key(nb.distance, nb.id);
         nvalid++;
@@ -1027,7 +1029,7 @@ __global__ void __launch_bounds__(128) merge_refine_select_kernel(const fv_neigh
     u64 ek = FV_EMPTY_KEY;
     if (want > 0 && key[j] <= cut) {
       const int p = e / keep, i = e - p * keep;
-      ek = make_key(exact[(size_t(p) * nq + q) * size_t(keep) + i], key_id(key[j]));
+      ek = make_key(exact[size_t(p) * exact_stride + q * size_t(keep) + i], key_id(key[j]));
     }
     if (__any_sync(FV_FULL, ek != FV_EMPTY_KEY)) b2 = warp_list_offer(fin, k, ek, b2);
   }
@@ -1037,14 +1039,10 @@ __global__ void __launch_bounds__(128) merge_refine_select_kernel(const fv_neigh
 }  // extern "C++"
 }  // namespace fv
 
-int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float* d_exact_parts,
-                        const uint32_t* d_part_counts, size_t nparts, size_t nq, size_t keep, size_t k,
-                        fv_neighbor* d_out, uint32_t* d_counts) {
-  if (!ctx || !d_adc_parts || !d_exact_parts || !d_out || nparts == 0 || keep == 0 || k == 0)
-    return fv::fail(FV_ERR_ARG, "fv_merge_refine_dev: bad argument");
-  if (keep > 4096 || k > 4096) return fv::fail(FV_ERR_UNSUPPORTED, "k * refine above 4096 is not supported");
-  if (nq == 0) return FV_OK;
-  fv::CtxGuard g(ctx);
+// merge of the per-shard candidates (see merge_refine_kernel for the strides); keys to scratch slot 1, then neighbours
+static int merge_refine_impl(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float* d_exact_parts,
+                             const uint32_t* d_part_counts, size_t nparts, size_t nq, size_t keep, size_t k,
+                             size_t adc_stride, size_t exact_stride, fv_neighbor* d_out, uint32_t* d_counts) {
   FV_TRY(ctx->scratch[1].reserve(nq * k * sizeof(u64)));
   u64* keys = ctx->scratch[1].as<u64>();
   const size_t smem = (keep + k) * sizeof(u64);
@@ -1055,17 +1053,112 @@ int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float
     const size_t sm = 4 * k * sizeof(u64);
     if (nparts * keep <= 256)
       fv::merge_refine_select_kernel<8><<<blocks, 128, sm, ctx->stream>>>(d_adc_parts, d_exact_parts, d_part_counts,
-                                                                         int(nparts), nq, int(keep), int(k), keys);
+                                                                         int(nparts), nq, int(keep), int(k), adc_stride,
+                                                                         exact_stride, keys);
     else
       fv::merge_refine_select_kernel<32><<<blocks, 128, sm, ctx->stream>>>(d_adc_parts, d_exact_parts, d_part_counts,
-                                                                          int(nparts), nq, int(keep), int(k), keys);
+                                                                          int(nparts), nq, int(keep), int(k), adc_stride,
+                                                                          exact_stride, keys);
   } else {
     fv::merge_refine_kernel<<<unsigned(nq), 32, smem, ctx->stream>>>(d_adc_parts, d_exact_parts, d_part_counts,
-                                                                    int(nparts), nq, int(keep), int(k), keys);
+                                                                    int(nparts), nq, int(keep), int(k), adc_stride,
+                                                                    exact_stride, keys);
   }
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
   FV_TRY(fv::keys_to_neighbors(ctx, keys, nq, int(k), int(k), d_out, d_counts));
+  return FV_OK;
+}
+
+int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float* d_exact_parts,
+                        const uint32_t* d_part_counts, size_t nparts, size_t nq, size_t keep, size_t k,
+                        fv_neighbor* d_out, uint32_t* d_counts) {
+  if (!ctx || !d_adc_parts || !d_exact_parts || !d_out || nparts == 0 || keep == 0 || k == 0)
+    return fv::fail(FV_ERR_ARG, "fv_merge_refine_dev: bad argument");
+  if (keep > 4096 || k > 4096) return fv::fail(FV_ERR_UNSUPPORTED, "k * refine above 4096 is not supported");
+  if (nq == 0) return FV_OK;
+  fv::CtxGuard g(ctx);
+  FV_TRY(merge_refine_impl(ctx, d_adc_parts, d_exact_parts, d_part_counts, nparts, nq, keep, k, nq * keep, nq * keep, d_out,
+                           d_counts));
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  return FV_OK;
+}
+
+// ---- search over list shards, one per rank of the context's communicator: coarse cells by query slices (exchanged),
+// the local scan, one exchange of the per-shard candidates, the merge.  Every rank ends up with the full result.
+// Stages (fv_stats.stage_ms): 0 coarse cells of this rank's query slice, 1 their exchange, 2 the local search up to
+// its candidates (bound pass, bucketing, scan, re-score, sort, re-rank), 3 the candidate exchange, 4 the merge.
+int fv_ivfpq_search_sharded_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,
+                                fv_neighbor* d_out, uint32_t* d_counts) {
+  if (!ix || (nq && (!d_queries || !d_out))) return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_sharded: null argument");
+  fv_ctx* ctx = ix->ctx;
+  fv::CtxGuard g(ctx);
+  const int world = ctx->comm_size, rank = ctx->comm_rank;
+  if (world <= 1) return ivfpq_search_impl(ix, d_queries, nq, k, nprobe, refine, false, d_out, d_counts, nullptr, nullptr);
+  if (ix->shard_world != world || ix->shard_rank != rank)
+    return fv::fail(FV_ERR_ARG, "the index's shard (fv_ivfpq_set_shard) does not match the context's communicator");
+  if (nq == 0) return FV_OK;
+  if (k == 0 || nprobe == 0) return fv::fail(FV_ERR_ARG, "k and nprobe must be at least 1");
+  const size_t np = std::min(nprobe, ix->nlist);
+  fv::StageScope scope(ctx);  // one stage table for the whole call: the inner searches do not restart it
+  // every shard needs the probed cells of all queries: rank r computes those of query slice r
+  const size_t per = (nq + size_t(world) - 1) / size_t(world);
+  const size_t lo = std::min(nq, size_t(rank) * per), hi = std::min(nq, lo + per);
+  const uint64_t* cells = nullptr;
+  if (nq >= 256 * size_t(world)) {
+    FV_TRY(ctx->scratch[13].reserve(per * np * sizeof(u64)));
+    u64* mine = ctx->scratch[13].as<u64>();
+    if (hi > lo)
+      FV_TRY(ivfpq_search_impl(ix, d_queries + lo * size_t(ix->dim), hi - lo, 1, nprobe, 0, false, nullptr, nullptr, nullptr,
+                               nullptr, nullptr, reinterpret_cast<uint64_t*>(mine)));
+    if (hi - lo < per) FV_CUDA(cudaMemsetAsync(mine + (hi - lo) * np, 0xFF, (per - (hi - lo)) * np * sizeof(u64), ctx->stream));
+    fv::stage_mark_outer(ctx);  // 0
+    FV_TRY(ctx->scratch[14].reserve(size_t(world) * per * np * sizeof(u64)));
+    u64* all = ctx->scratch[14].as<u64>();
+    FV_TRY(fv::comm_all_gather(ctx, mine, all, per * np * sizeof(u64)));
+    // the gathered keys are needed until the local search has bucketed them; it uses slot 14 itself only on the
+    // tensor-core path, after the pairs are built -- so they move to a slot of their own
+    FV_TRY(ctx->scratch[4].reserve(nq * np * sizeof(u64)));
+    FV_CUDA(cudaMemcpyAsync(ctx->scratch[4].p, all, nq * np * sizeof(u64), cudaMemcpyDeviceToDevice, ctx->stream));
+    cells = ctx->scratch[4].as<uint64_t>();
+    fv::stage_mark_outer(ctx);  // 1
+  } else {
+    fv::stage_mark_outer(ctx);  // 0 (the local search does its own coarse step)
+    fv::stage_mark_outer(ctx);  // 1
+  }
+  const bool rerank = refine > 0 && ix->keep;
+  if (rerank) {
+    // a shard may not cut to k on its own: the global cut by compressed distance comes first (ivfpq.rs:285-296).
+    // One record block per rank: its candidates (id, compressed distance), then their exact distances.
+    const size_t keep = k * refine;
+    const size_t blk = (nq * keep * 12 + 15) & ~size_t(15);
+    FV_TRY(ctx->scratch[10].reserve(blk));
+    unsigned char* send = ctx->scratch[10].as<unsigned char>();
+    fv_neighbor* adc = reinterpret_cast<fv_neighbor*>(send);
+    float* exact = reinterpret_cast<float*>(send + nq * keep * sizeof(fv_neighbor));
+    FV_TRY(ctx->scratch[11].reserve(nq * sizeof(uint32_t)));
+    FV_TRY(ivfpq_search_impl(ix, d_queries, nq, keep, nprobe, 1, true, nullptr, ctx->scratch[11].as<uint32_t>(), adc, exact, cells));
+    fv::stage_mark_outer(ctx);  // 2
+    FV_TRY(ctx->scratch[15].reserve(size_t(world) * blk));
+    unsigned char* recv = ctx->scratch[15].as<unsigned char>();
+    FV_TRY(fv::comm_all_gather(ctx, send, recv, blk));
+    fv::stage_mark_outer(ctx);  // 3
+    FV_TRY(merge_refine_impl(ctx, reinterpret_cast<const fv_neighbor*>(recv),
+                             reinterpret_cast<const float*>(recv + nq * keep * sizeof(fv_neighbor)), nullptr, size_t(world), nq,
+                             keep, k, blk / sizeof(fv_neighbor), blk / sizeof(float), d_out, d_counts));
+  } else {
+    const size_t blk = nq * k * sizeof(fv_neighbor);
+    FV_TRY(ctx->scratch[10].reserve(blk));
+    FV_TRY(ctx->scratch[11].reserve(nq * sizeof(uint32_t)));
+    fv_neighbor* mine = ctx->scratch[10].as<fv_neighbor>();
+    FV_TRY(ivfpq_search_impl(ix, d_queries, nq, k, nprobe, 0, false, mine, ctx->scratch[11].as<uint32_t>(), nullptr, nullptr, cells));
+    fv::stage_mark_outer(ctx);  // 2
+    FV_TRY(ctx->scratch[15].reserve(size_t(world) * blk));
+    FV_TRY(fv::comm_all_gather(ctx, mine, ctx->scratch[15].p, blk));
+    fv::stage_mark_outer(ctx);  // 3
+    FV_TRY(fv::merge_topk_impl(ctx, ctx->scratch[15].as<fv_neighbor>(), nullptr, size_t(world), nq, k, k, d_out, d_counts));
+  }
+  fv::stage_mark_outer(ctx);  // 4
   FV_CUDA(cudaStreamSynchronize(ctx->stream));
   return FV_OK;
 }

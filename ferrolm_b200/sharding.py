@@ -1,7 +1,8 @@
-"""Host-side plumbing of the multi-GPU layout: one process per GPU, `torch.distributed` for the one
-exchange step.  The base is split over the ranks (contiguous row ranges for exact search, inverted lists
-for IVF-PQ), every rank searches its part for the whole query batch, the per-rank candidate lists are
-all-gathered and merged by a kernel of the library.  Nothing here computes distances.
+"""Host-side plumbing of the multi-GPU layout: one process per GPU.  The base is split over the ranks (contiguous
+row ranges for exact search, inverted lists for IVF-PQ), every rank searches its part for the whole query batch,
+the per-rank candidate lists are all-gathered and merged.  On GPUs all of that happens inside the library
+(fv_*_search_sharded_dev: NCCL on the context's stream, then a merge kernel); this module forms the group and keeps
+the small helpers that state the exchange protocol on CPU tensors for the gloo test.  Nothing here computes distances.
 """
 from __future__ import annotations
 
@@ -27,11 +28,31 @@ def all_gather_stacked(t, world: int):
     return out
 
 
+def init_group(ctx, rank: int, world: int):
+    """Puts `ctx` into the library's group of `world` ranks.  The 128-byte group id is made by rank 0 and travels by
+    a `torch.distributed` broadcast (any host channel would do: the library only needs the bytes on every rank)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from .vector import comm_unique_id
+
+    if world == 1:
+        return
+    dev = torch.device("cuda", ctx.device) if torch.cuda.is_available() and dist.get_backend() == "nccl" else torch.device("cpu")
+    t = torch.zeros(128, dtype=torch.uint8, device=dev)
+    if rank == 0:
+        t.copy_(torch.from_numpy(np.frombuffer(comm_unique_id(), dtype=np.uint8).copy()))
+    dist.broadcast(t, 0)
+    ctx.comm_init(bytes(t.cpu().numpy()), world, rank)
+
+
 class ShardedSearch:
-    """search_batch over an index that is split across the ranks of the default process group.
+    """search_batch over an index that is split across the ranks of the context's group (`init_group`).
 
     kind "flat":  `index` is a FlatIndex over this rank's row range (set_id_base(lo) before add).
     kind "ivfpq": `index` is an IvfPq with set_shard(rank, world) that was given all rows.
+    The exchange and the merge happen inside the library (NCCL on the context's stream): one collective call.
     """
 
     def __init__(self, ctx, index, kind: str, world: int):
@@ -40,32 +61,10 @@ class ShardedSearch:
     def search_batch(self, queries, k: int, nprobe: int = 0, refine: int = 0):
         ix = self.index
         if self.kind == "flat":
-            out, counts = ix.search_batch(queries, k)
-            if self.world == 1:
-                return out, counts
-            return self.ctx.merge_topk(all_gather_stacked(out, self.world), all_gather_stacked(counts, self.world), k)
+            return ix.search_sharded(queries, k) if self.world > 1 else ix.search_batch(queries, k)
         if self.world == 1:
             return ix.search_batch(queries, k, nprobe, refine)
-        cells = self._coarse_by_query_slices(queries, nprobe)
-        if refine > 0:
-            # a shard may not cut to k on its own: the global cut by compressed distance comes first
-            # (unused candidate slots carry the id 0xFFFFFFFF, so the per-shard counts need not travel)
-            adc, exact, _ = ix.search_candidates(queries, k * refine, nprobe, cells)
-            return self.ctx.merge_refine(all_gather_stacked(adc, self.world), all_gather_stacked(exact, self.world),
-                                         None, k)
-        out, counts = ix.search_batch(queries, k, nprobe, 0, cells)
-        return self.ctx.merge_topk(all_gather_stacked(out, self.world), all_gather_stacked(counts, self.world), k)
-
-    def _coarse_by_query_slices(self, queries, nprobe: int):
-        """Every list shard needs the probed cells of ALL queries; instead of each shard repeating the whole coarse
-        search, rank r computes the cells of query slice r and the slices are all-gathered.  None (= let the search
-        do its own coarse step) for host arrays and for batches too small to be worth an exchange."""
-        if not (hasattr(queries, "is_cuda") and queries.is_cuda):
-            return None
-        q = queries.contiguous().view(-1, self.index.dim)
-        if q.shape[0] < 256 * self.world:
-            return None
-        return per_query_slices(lambda part: self.index.coarse(part, nprobe), q, self.world)
+        return ix.search_sharded(queries, k, nprobe, refine)
 
 
 def per_query_slices(compute, queries, world: int):

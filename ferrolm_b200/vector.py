@@ -68,6 +68,13 @@ def datagen_dev(ctx, seed: int, n: int, dim: int, clusters: int, first_row: int 
     return out
 
 
+def comm_unique_id() -> bytes:
+    """The 128-byte id of a new group of contexts; rank 0 makes it, every rank passes it to Context.comm_init."""
+    buf = (C.c_uint8 * 128)()
+    check(lib().fv_comm_unique_id(buf))
+    return bytes(buf)
+
+
 def _is_cuda_tensor(x) -> bool:
     return hasattr(x, "is_cuda") and bool(x.is_cuda)
 
@@ -111,6 +118,19 @@ class Context:
 
     def stream_handle(self) -> int:
         return lib().fv_ctx_stream(self._h) or 0
+
+    def comm_init(self, group_id: bytes, nranks: int, rank: int):
+        """Joins the group `group_id` (collective: returns when every rank has called it)."""
+        buf = (C.c_uint8 * 128).from_buffer_copy(group_id)
+        check(lib().fv_ctx_comm_init(self._h, buf, nranks, rank))
+
+    @property
+    def comm_rank(self) -> int:
+        return lib().fv_ctx_comm_rank(self._h)
+
+    @property
+    def comm_size(self) -> int:
+        return lib().fv_ctx_comm_size(self._h)
 
     # ---- merging per-shard results (device tensors)
     def merge_topk(self, parts, part_counts, k_out: int):
@@ -238,6 +258,10 @@ class FlatIndex:
     def search_batch(self, queries, k: int):
         return _search(lib().fv_flat_search_batch, self._h, queries, self.dim, k, (), lib().fv_flat_search_batch_dev)
 
+    def search_sharded(self, queries, k: int):
+        """Collective search over the row shards of the context's group (CUDA tensor, the same on every rank)."""
+        return _search(None, self._h, queries, self.dim, k, (), lib().fv_flat_search_sharded_dev)
+
 
 @dataclass
 class IvfPqParams:
@@ -328,6 +352,10 @@ class IvfPq:
             return out, counts
         return _search(lib().fv_ivfpq_search_batch, self._h, queries, self.dim, k, (nprobe, refine),
                        lib().fv_ivfpq_search_batch_dev)
+
+    def search_sharded(self, queries, k: int, nprobe: int, refine: int):
+        """Collective search over the list shards of the context's group (CUDA tensor, the same on every rank)."""
+        return _search(None, self._h, queries, self.dim, k, (nprobe, refine), lib().fv_ivfpq_search_sharded_dev)
 
     def coarse(self, queries, nprobe: int):
         """The probed cells of every query (CUDA tensor in, (nq, min(nprobe, nlist)) int64 keys out): the coarse step
@@ -465,4 +493,4 @@ def kmeans_assign(ctx: Context, data, centroids) -> np.ndarray:
 
 __all__ = ["Metric", "Context", "FlatIndex", "IvfPq", "IvfPqParams", "Hnsw", "HnswParams", "NEIGHBOR", "padded",
            "normalize", "recall", "datagen", "datagen_dev", "kmeans_train", "kmeans_assign", "neighbors_from_tensor",
-           "merge_topk_static", "FerrovecError"]
+           "merge_topk_static", "comm_unique_id", "FerrovecError"]

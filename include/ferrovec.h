@@ -48,7 +48,8 @@ typedef enum fv_status {
   FV_ERR_TIMEOUT = 4,     /* a bounded device-side wait ran out */
   FV_ERR_OVERFLOW = 5,    /* a device-side work list ran out of room even after regrowing */
   FV_ERR_UNSUPPORTED = 6, /* size beyond a documented limit of this library */
-  FV_ERR_NOMEM = 7
+  FV_ERR_NOMEM = 7,
+  FV_ERR_COMM = 8         /* NCCL is missing or a collective failed */
 } fv_status;
 
 const char* fv_last_error(void);
@@ -70,9 +71,9 @@ typedef struct fv_stats {
   uint64_t launches;        /* kernels launched by the last call */
   uint64_t uncertified;     /* exact search: queries re-run on the full-precision scan; IVF-PQ: queries whose candidate buffer ran over in the list-major scan and were re-run by the per-query kernel; HNSW: queries whose list of tied, pushed-out entries overflowed (64; ties beyond that may be resolved differently from the reference) */
   uint64_t rows_scanned;    /* IVF-PQ: code rows visited (sum over queries and probes) */
-  uint64_t dist_evals;      /* HNSW: distance evaluations */
+  uint64_t dist_evals;      /* HNSW: distance evaluations; IVF-PQ tensor-core pass: (query, row) pairs that survived the tensor-core scores and were re-scored with the exact table arithmetic */
   uint64_t expansions;      /* HNSW: node expansions */
-  uint64_t regrown;         /* HNSW: queries re-run with a larger visited table */
+  uint64_t regrown;         /* HNSW: queries re-run with a larger visited table; IVF-PQ list-major scans: queries whose candidate buffer ran over and that got a second round with a tightened bound */
   float stage_ms[8];        /* per-stage device time of the last call when timing is on */
   uint64_t rows_list_scan;  /* IVF-PQ: the part of rows_scanned that the list-major kernel visited (0: per-query kernel only) */
 } fv_stats;
@@ -199,6 +200,25 @@ double fv_recall(const fv_neighbor* found, const uint32_t* counts, const uint32_
 int fv_read_fvecs(const char* path, size_t limit, float** out, size_t* n, size_t* dim);      /* read_fvecs :30 */
 int fv_read_ivecs(const char* path, size_t limit, uint32_t** out, size_t* n, size_t* dim);   /* read_ivecs :36 */
 void fv_free(void* p);
+
+/* ---- searching a sharded index with one rank per GPU (no counterpart in the single-process reference).
+ * The base set is split over the ranks -- contiguous row ranges for exact search (fv_flat_set_id_base), inverted
+ * lists for IVF-PQ (fv_ivfpq_set_shard) -- and every rank holds a context that belongs to the same group.  Rank 0
+ * makes the 128-byte group id with fv_comm_unique_id and hands it to the other ranks by whatever channel the host
+ * has (a file, a socket, MPI, its own RPC); then every rank calls fv_ctx_comm_init (collective).  NCCL
+ * (libnccl.so.2) is bound at run time, so hosts that never shard do not need it.
+ * The *_sharded_dev searches are collective too: every rank calls them with the SAME queries (device pointers);
+ * each searches its shard, the per-shard candidates are all-gathered over NVLink on the context's stream and merged
+ * by a kernel of this library, and every rank gets the complete result.  HNSW is searched by replicas (one graph;
+ * per-shard graphs would change the results): split the query batch over the ranks instead. */
+int fv_comm_unique_id(uint8_t* id128);
+int fv_ctx_comm_init(fv_ctx* ctx, const uint8_t* id128, int nranks, int rank);
+int fv_ctx_comm_rank(const fv_ctx* ctx);
+int fv_ctx_comm_size(const fv_ctx* ctx);
+int fv_flat_search_sharded_dev(fv_flat* ix, const float* d_queries, size_t nq, size_t k, fv_neighbor* d_out,
+                               uint32_t* d_counts);
+int fv_ivfpq_search_sharded_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,
+                                fv_neighbor* d_out, uint32_t* d_counts);
 
 /* ---- merging per-shard results (no counterpart in the single-process reference; the row-sharded layout
  * needs it).  `d_parts` holds nparts blocks of nq*k_in neighbours, `d_part_counts` nparts*nq counts (may be

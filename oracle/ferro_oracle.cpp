@@ -1073,6 +1073,40 @@ void orc_testdata(size_t n, size_t dim, uint64_t seed, float* out) {
   }
 }
 
+// The benchmark's stand-in for SIFT1M and for encoder embeddings: a seeded mixture of `clusters` Gaussians whose row i
+// depends on (seed, i) only.  kind 0: centres uniform in [0, 255]^dim, sigma 30, rounded and clipped to [0, 255];
+// kind 1: centres normal * 3, sigma 1, rows scaled to unit length.  The product library generates the same rows
+// (its fv_datagen); this copy lets the CPU arm of the benchmark run without loading that library.
+void orc_datagen(int kind, uint64_t seed, size_t first_row, size_t n, size_t dim, size_t clusters, int threads, float* out) {
+  std::vector<float> centres(clusters * dim);
+  {
+    Rng c(seed * 1000003ull + 17);
+    for (auto& v : centres) v = kind == 0 ? float(c.uniform() * 255.0) : float(c.normal()) * 3.0f;
+  }
+  pool_run(threads, n, [&](size_t i) {
+    const size_t row = first_row + i;
+    Rng r(seed ^ ((row + 1) * 0xD1B54A32D192ED03ull));
+    r.next_u64();
+    const size_t c = size_t(r.next_u64() % clusters);
+    float* o = out + i * dim;
+    if (kind == 0) {
+      for (size_t d = 0; d < dim; d++) {
+        float v = centres[c * dim + d] + float(r.normal()) * 30.0f;
+        v = std::nearbyint(v);
+        o[d] = v < 0.f ? 0.f : (v > 255.f ? 255.f : v);
+      }
+    } else {
+      double ss = 0.0;
+      for (size_t d = 0; d < dim; d++) {
+        o[d] = centres[c * dim + d] + float(r.normal());
+        ss += double(o[d]) * double(o[d]);
+      }
+      const float inv = ss > 0 ? float(1.0 / std::sqrt(ss)) : 0.f;
+      for (size_t d = 0; d < dim; d++) o[d] *= inv;
+    }
+  });
+}
+
 // ---- primitives
 float orc_l2sq(const float* a, const float* b, size_t n) { return l2sq(a, b, n); }
 float orc_dot(const float* a, const float* b, size_t n) { return dot(a, b, n); }

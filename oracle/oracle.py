@@ -49,6 +49,7 @@ def lib():
             "orc_rng_uniform": (C.c_double, [vp]),
             "orc_rng_normal": (C.c_double, [vp]),
             "orc_testdata": (None, [sz, sz, u64, f32p]),
+            "orc_datagen": (None, [i, u64, sz, sz, sz, sz, i, f32p]),
             "orc_l2sq": (C.c_float, [f32p, f32p, sz]),
             "orc_dot": (C.c_float, [f32p, f32p, sz]),
             "orc_l2sq_scalar": (C.c_float, [f32p, f32p, sz]),
@@ -132,6 +133,14 @@ def testdata(n: int, dim: int, seed: int) -> np.ndarray:
     """The generator of tests/vector.rs:11-24."""
     out = np.empty((n, dim), dtype=np.float32)
     lib().orc_testdata(n, dim, seed, _p(out))
+    return out
+
+
+def datagen(kind: int, seed: int, n: int, dim: int, clusters: int, first_row: int = 0, threads: int | None = None) -> np.ndarray:
+    """The benchmark's seeded Gaussian-mixture rows (kind 0: SIFT-like integers, kind 1: unit-length embeddings):
+    the same bytes the product library's fv_datagen gives."""
+    out = np.empty((n, dim), dtype=np.float32)
+    lib().orc_datagen(kind, seed, first_row, n, dim, clusters, threads or cores(), _p(out))
     return out
 
 

@@ -58,6 +58,14 @@ def test_datagen_is_seeded_and_row_addressable(fv):
     assert np.allclose(np.linalg.norm(e, axis=1), 1.0, atol=1e-5)
 
 
+def test_the_oracle_generates_the_same_benchmark_rows(fv, oracle):
+    # the CPU arm of the benchmark generates its data without loading the product library: same bytes
+    for kind, dim, clusters in [(0, 128, 256), (1, 384, 1000), (0, 24, 7)]:
+        a = fv.datagen(kind, 5, 3000, dim, clusters, first_row=123)
+        b = oracle.datagen(kind, 5, 3000, dim, clusters, first_row=123)
+        assert a.tobytes() == b.tobytes()
+
+
 def test_no_gpu_means_a_loud_failure(fv):
     import torch
 
