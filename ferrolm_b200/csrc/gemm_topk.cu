@@ -268,6 +268,12 @@ struct GemmParams {
   u64* pool;                   // [grid][pool_cap] survivors: (A row << 32) | B row relative to y
   unsigned int* pool_cnt;      // [grid] entries each CTA produced (may exceed pool_cap: overflow)
   unsigned int pool_cap;
+  // task mode, minima variant (minima != null): instead of survivors, the smallest score of every 8 B rows, for the
+  // first task_rows[t] operand rows of task t: minima[task_moff[t] + (row in tile * units + unit) * 32 + column / 8];
+  // B rows beyond the task's valid ones count as +inf.  Tasks with task_moff[t] == 0xFFFFFFFF write nothing.
+  float* minima;
+  const uint32_t* task_moff;
+  const uint32_t* task_rows;
 };
 
 struct __align__(8) Barriers {
@@ -532,6 +538,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     const int col0 = MH == 2 ? (sub >> 1) * NCOL : sub * NCOL;
     uint32_t n_rows = uint32_t(p.n);
     uint32_t a_row = 0;  // task mode: this thread's operand row
+    float* mdst = nullptr;  // task mode, minima variant: where this thread's minima of the current task go
     for (int g = blockIdx.x, seg = 0; g < nwork && ok; g += gridDim.x, ++seg) {
       int nt0, nt1, mt = 0;
       if (TASKS) {
@@ -540,6 +547,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         nt1 = int(t.z);
         n_rows = t.w;  // rows of this task's B run; the rest of its last unit belongs to someone else
         a_row = t.x + uint32_t((MH == 2 ? grp * 128 : 0) + quad * 32 + lane);
+        if (p.minima) {
+          const uint32_t moff = p.task_moff[g];
+          const uint32_t rt = a_row - t.x;
+          mdst = (moff != 0xFFFFFFFFu && rt < p.task_rows[g]) ? p.minima + size_t(moff) + size_t(rt) * t.z * 32 : nullptr;
+        }
       } else {
         const int part = g / p.MT;
         mt = g - part * p.MT;
@@ -549,7 +561,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       cslot = (size_t(blockIdx.x) * p.segmax + seg) * LISTS + e;
       ncand = 0;
       if (THRESH) {  // the bound is fixed: the sample pass's estimate for this query
-        thr = TASKS ? p.tau[a_row] : p.tau[mt * (128 * MH) + (MH == 2 ? grp * 128 : 0) + quad * 32 + lane];
+        thr = TASKS ? (p.minima ? 0.f : p.tau[a_row]) : p.tau[mt * (128 * MH) + (MH == 2 ? grp * 128 : 0) + quad * 32 + lane];
       } else {
         thr = INFINITY;
 #pragma unroll
@@ -647,8 +659,32 @@ __global__ void __launch_bounds__(NTHREADS, 1)
               __syncwarp();
               if (lane == 0) mbar_arrive(&bars->tempty[slot]);
             }
-            if (TASKS) chunk_tasks(rbuf, c);
-            else chunk(rbuf, c);
+            if (TASKS) {
+              if (p.minima) {
+                // minima variant: the smallest score of every 8 columns of this chunk, rows beyond the task's as +inf
+                if (mdst) {
+                  float g8[8];
+                  const bool tail = row_base + uint32_t(c + 63) >= n_rows;
+#pragma unroll
+                  for (int gi = 0; gi < 8; ++gi) {
+                    float m = INFINITY;
+#pragma unroll
+                    for (int i = gi * 8; i < gi * 8 + 8; ++i) {
+                      const float v = __uint_as_float(rbuf[i]);
+                      m = fminf(m, (!tail || row_base + uint32_t(c + i) < n_rows) ? v : INFINITY);
+                    }
+                    g8[gi] = m;
+                  }
+                  float4* d4 = reinterpret_cast<float4*>(mdst + size_t(nt) * 32 + (col0 + c) / 8);
+                  d4[0] = make_float4(g8[0], g8[1], g8[2], g8[3]);
+                  d4[1] = make_float4(g8[4], g8[5], g8[6], g8[7]);
+                }
+              } else {
+                chunk_tasks(rbuf, c);
+              }
+            } else {
+              chunk(rbuf, c);
+            }
           }
         } else {
           // List mode.  Common path: the minimum of a chunk against the bound.  Rare path (entered by the whole
@@ -1303,7 +1339,8 @@ int tc_prepare_queries(fv_ctx* ctx, TcSide* tc, int metric, const float* d_queri
 
 int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_t a_rows, const float* d_thr,
                  const uint4* d_tasks, const uint32_t* d_ntasks, u64* d_pool, unsigned int* d_pool_cnt,
-                 unsigned int pool_cap, int* grid_out) {
+                 unsigned int pool_cap, int* grid_out, float* d_minima, const uint32_t* d_task_moff,
+                 const uint32_t* d_task_rows) {
   const int Kp = tc->Kp;
   if (Kp > 2 * KBLK) return fail(FV_ERR_UNSUPPORTED, "task mode of the tensor-core kernel covers padded dimensions up to 128");
   Tiling t{};
@@ -1322,6 +1359,9 @@ int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_
   gp.pool = d_pool;
   gp.pool_cnt = d_pool_cnt;
   gp.pool_cap = pool_cap;
+  gp.minima = d_minima;
+  gp.task_moff = d_task_moff;
+  gp.task_rows = d_task_rows;
   CUtensorMap tmA, tmB;
   FV_TRY(make_tmap(&tmA, tc->bf16, const_cast<uint16_t*>(d_A), a_rows, Kp, 128));
   FV_TRY(make_tmap(&tmB, tc->bf16, tc->half.p, tc->n, Kp, TILE_N));

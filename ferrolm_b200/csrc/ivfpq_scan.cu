@@ -764,6 +764,56 @@ __global__ void __launch_bounds__(128) bound_select_kernel(const float* __restri
   if (lane == 0) tau_bits[q] = lo;
 }
 
+// Bound from the tensor-core scores.  The minima variant of the kernel left, per (query, near list) pair, the smallest
+// score of every 8 rows; score + add[row] is an upper bound of the compressed distance of the row that attains it.
+// One warp per query collects those bounds over its pairs; their keep-th smallest is a distance that at least `keep`
+// different rows of the query's probed lists do not exceed.
+__global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __restrict__ minima, const uint4* __restrict__ tasks,
+                                                              const uint32_t* __restrict__ task_moff,
+                                                              const uint32_t* __restrict__ task_rows,
+                                                              const float* __restrict__ add, const uint32_t* __restrict__ q_rows,
+                                                              const uint32_t* __restrict__ q_cnt, int q_slots, int vcap,
+                                                              int keep, size_t nq, uint32_t* __restrict__ tau_bits) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const size_t q = blockIdx.x * size_t(blockDim.x >> 5) + w;
+  if (q >= nq) return;
+  uint32_t* v = reinterpret_cast<uint32_t*>(dyn_smem()) + size_t(w) * vcap;  // order-bit words
+  const uint32_t INF_BITS = 0xFF800000u;
+  const int np = int(min(q_cnt[q], uint32_t(q_slots)));
+  int n = 0, finite = 0;
+  for (int s = 0; s < np; ++s) {
+    const uint32_t arow = q_rows[q * size_t(q_slots) + s];
+    const uint32_t t = arow >> 8, rt = arow & 255u;
+    const uint32_t moff = task_moff[t];
+    if (moff == 0xFFFFFFFFu || rt >= task_rows[t]) continue;
+    const int cnt = int(tasks[t].z) * 32;
+    const float* src = minima + size_t(moff) + size_t(rt) * cnt;
+    const float ad = add[arow];
+    const int room = min(cnt, vcap - n);
+    for (int i = lane; i < room; i += 32) {
+      const uint32_t b = order_bits(__fadd_ru(src[i], ad));  // rounded up: still an upper bound
+      v[n + i] = b;
+      finite += b < INF_BITS ? 1 : 0;
+    }
+    n += room;
+    if (n >= vcap) break;
+  }
+  __syncwarp();
+  if (__reduce_add_sync(FV_FULL, finite) < keep) {
+    if (lane == 0) tau_bits[q] = 0xFFFFFFFFu;
+    return;
+  }
+  uint32_t lo = 0, hi = INF_BITS - 1;
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    int c = 0;
+    for (int i = lane; i < n; i += 32) c += v[i] <= mid ? 1 : 0;
+    if (__reduce_add_sync(FV_FULL, c) >= keep) hi = mid;
+    else lo = mid + 1;
+  }
+  if (lane == 0) tau_bits[q] = lo;
+}
+
 struct FinishArgs {
   const u64* cand;
   uint32_t* cand_cnt;
@@ -927,8 +977,11 @@ __global__ void __launch_bounds__(1024) tc_tasks_kernel(const uint32_t* __restri
                                                         const uint32_t* __restrict__ roff8,
                                                         const uint32_t* __restrict__ order, size_t nlist,
                                                         uint4* __restrict__ tasks, uint32_t* __restrict__ a_off,
-                                                        uint32_t* __restrict__ ntasks, unsigned long long* __restrict__ rows) {
+                                                        uint32_t* __restrict__ ntasks, unsigned long long* __restrict__ rows,
+                                                        uint32_t* __restrict__ task_moff, uint32_t* __restrict__ task_rows,
+                                                        uint32_t minima_cap) {
   __shared__ uint32_t st[1024];
+  __shared__ unsigned long long sm8[1024];  // minima variant: floats of minima the tasks before a thread's need
   const int tid = threadIdx.x;
   const size_t per = (nlist + 1023) / 1024;
   const size_t l0 = min(nlist, size_t(tid) * per), l1 = min(nlist, l0 + per);
@@ -937,26 +990,42 @@ __global__ void __launch_bounds__(1024) tc_tasks_kernel(const uint32_t* __restri
     return (n && len) ? (n + 255u) / 256u : 0u;
   };
   uint32_t nt = 0;
-  unsigned long long nr = 0;
+  unsigned long long nr = 0, nm = 0;
   for (size_t o = l0; o < l1; ++o) {
     const size_t l = order[o];
+    const uint32_t n = pair_off[l + 1] - pair_off[l], len = list_off[l + 1] - list_off[l];
     nt += tasks_of(l);
-    nr += (unsigned long long)(pair_off[l + 1] - pair_off[l]) * (list_off[l + 1] - list_off[l]);
+    nr += (unsigned long long)n * len;
+    if (len) nm += (unsigned long long)n * ((len + 255u) / 256u) * 32u;  // 32 minima per pair and unit
   }
   st[tid] = nt;
+  sm8[tid] = nm;
   __syncthreads();
   for (int o = 1; o < 1024; o <<= 1) {
     const uint32_t b = tid >= o ? st[tid - o] : 0u;
+    const unsigned long long b8 = tid >= o ? sm8[tid - o] : 0ull;
     __syncthreads();
     st[tid] += b;
+    sm8[tid] += b8;
     __syncthreads();
   }
   uint32_t bt = st[tid] - nt;
+  unsigned long long bm = sm8[tid] - nm;
   for (size_t o = l0; o < l1; ++o) {
     const size_t l = order[o];
-    const uint32_t k = tasks_of(l), len = list_off[l + 1] - list_off[l];
+    const uint32_t k = tasks_of(l), len = list_off[l + 1] - list_off[l], n = pair_off[l + 1] - pair_off[l];
+    const uint32_t units = (len + 255u) / 256u;
     a_off[l] = bt * 256u;
-    for (uint32_t t = 0; t < k; ++t) tasks[bt + t] = make_uint4((bt + t) * 256u, roff8[l], (len + 255u) / 256u, len);
+    for (uint32_t t = 0; t < k; ++t) {
+      tasks[bt + t] = make_uint4((bt + t) * 256u, roff8[l], units, len);
+      if (task_moff) {
+        const uint32_t valid = min(256u, n - t * 256u);
+        const unsigned long long need = (unsigned long long)valid * units * 32u;
+        task_rows[bt + t] = valid;
+        task_moff[bt + t] = bm + need <= minima_cap ? uint32_t(bm) : 0xFFFFFFFFu;  // beyond the buffer: this task leaves no minima
+        bm += need;
+      }
+    }
     bt += k;
   }
   if (tid == 1023) *ntasks = st[1023];
@@ -979,6 +1048,11 @@ struct GatherArgs {
   uint32_t* g_q;
   uint32_t* g_l;
   float* g_base;
+  // bound variant (q_rows != null): thr[row] receives what turns a score into an UPPER bound of the compressed
+  // distance (||a||^2 + eps, or base + eps), and the row is filed under its query: q_rows[q * q_slots + i]
+  uint32_t* q_rows;
+  uint32_t* q_cnt;
+  int q_slots;
 };
 
 __device__ __forceinline__ uint16_t to_operand(float x, int bf16) {
@@ -1056,12 +1130,13 @@ __global__ void __launch_bounds__(256) tc_gather_kernel(GatherArgs a) {
     }
     fin = __all_sync(FV_FULL, fin);
     if (lane == 0) {
-      const uint32_t tb = a.tau_bits[q];
+      const bool bound_pass = a.q_rows != nullptr;
+      const uint32_t tb = bound_pass ? 0u : a.tau_bits[q];
       const bool in_range = fin && (a.bf16 ? mx <= 1.0e38f : mx * (a.is_l2 ? 2.f : 1.f) <= 65504.f);
       const float base = __uint_as_float(pr.y);
       float thr = -INFINITY;
       if (tb != 0xFFFFFFFFu && in_range) {
-        const float tau = order_bits_to_float(tb);
+        const float tau = bound_pass ? 0.f : order_bits_to_float(tb);
         const float u16 = a.bf16 ? 0.00390625f : 0.00048828125f;
         const float an = sqrtf(a2), bn = a.bn, kf = a.kf;
         const float e_dot = (2.f * u16 * (1.f + u16) + kf * 4.7683716e-7f + kf * 1.1920929e-7f) * an * bn +
@@ -1071,10 +1146,22 @@ __global__ void __launch_bounds__(256) tc_gather_kernel(GatherArgs a) {
         const float e_chain = a.c1 * 5.9604645e-8f * 3.f * (q2 + a.cw2);
         const float e_self = 2.4e-7f * (an + bn) * an + 2.0e-6f * a2;
         const float eps = 1.05f * (e_score + e_chain + e_self) + 1e-30f;
-        thr = a.is_l2 ? (tau - a2) + eps : (tau - base) + eps;
-        if (!(thr == thr) || thr == INFINITY) thr = -INFINITY;  // a margin that is not a number: leave it to the other kernel
+        if (bound_pass) {
+          thr = a.is_l2 ? a2 + eps : base + eps;  // score + this >= the row's compressed distance
+          if (!(thr == thr)) thr = INFINITY;
+        } else {
+          thr = a.is_l2 ? (tau - a2) + eps : (tau - base) + eps;
+          if (!(thr == thr) || thr == INFINITY) thr = -INFINITY;  // a margin that is not a number: leave it to the other kernel
+        }
+      } else if (bound_pass) {
+        thr = INFINITY;  // no usable scores for this query: its minima say nothing
       }
-      if (thr == -INFINITY) a.cand_cnt[q] = 0xFFFFFFFFu;  // left to the per-query kernel (none of its rows survives)
+      if (bound_pass) {
+        const uint32_t slot = atomicAdd(a.q_cnt + q, 1u);
+        if (slot < uint32_t(a.q_slots)) a.q_rows[size_t(q) * a.q_slots + slot] = arow;
+      } else if (thr == -INFINITY) {
+        a.cand_cnt[q] = 0xFFFFFFFFu;  // left to the per-query kernel (none of its rows survives)
+      }
       a.thr[arow] = thr;
       a.g_q[arow] = q;
       a.g_l[arow] = uint32_t(l);
@@ -1306,7 +1393,6 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     pb_set.carve(sm + set_words, ix.nlist, nq);
     FV_CUDA(cudaMemsetAsync(pa_set.pair_cnt, 0, pa_set.nzero * sizeof(uint32_t), ctx->stream));
     FV_CUDA(cudaMemsetAsync(pb_set.pair_cnt, 0, pb_set.nzero * sizeof(uint32_t), ctx->stream));
-    FV_TRY(ctx->scratch[6].reserve(nq * mcap * sizeof(float)));
     FV_TRY(ctx->scratch[7].reserve(2 * nq * size_t(nprobe) * sizeof(uint2) + 16));
     FV_TRY(ctx->scratch[9].reserve(nq * size_t(cap) * sizeof(u64)));
     uint2* pairs_a = ctx->scratch[7].as<uint2>();
@@ -1321,35 +1407,121 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     la.codes_t = ix.codes_t;
     la.ids = ix.ids;
     la.nlist = uint32_t(ix.nlist);
-    la.pair_off = pa_set.pair_off;
-    la.task_off = pa_set.task_off;
-    la.pairs = pairs_a;
-    la.counters = pa_set.counters;
-    la.minima = ctx->scratch[6].as<float>();
-    la.minima_cnt = pa_set.per_query;
-    la.minima_cap = int(mcap);
-    auto bound_k = use_pre ? ivfpq_list_scan_kernel<true, true> : ivfpq_list_scan_kernel<false, true>;
     auto main_k = use_pre ? ivfpq_list_scan_kernel<true, false> : ivfpq_list_scan_kernel<false, false>;
-    FV_CUDA(cudaFuncSetAttribute(bound_k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(LS_SMEM)));
-    bound_k<<<ctx->sm_count, LS_THREADS, LS_SMEM, ctx->stream>>>(la);
-    {
-      const int wpb = mcap <= 2048 ? 4 : 1;  // warps (queries) per block, by the shared memory their minima take
-      const size_t ssmem = size_t(wpb) * mcap * sizeof(uint32_t);
-      if (ssmem > 40 * 1024)
-        FV_CUDA(cudaFuncSetAttribute(bound_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ssmem)));
-      bound_select_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, ssmem, ctx->stream>>>(la.minima, la.minima_cnt, int(mcap),
-                                                                                             keep, nq, tau_bits);
+    // buffers of the tensor-core pass (both its bound pass and its main pass use them, one after the other)
+    TcInfo ti{};
+    size_t a_rows = 0, max_tasks = 0;
+    uint16_t* qg = nullptr;
+    float* thr = nullptr;
+    uint32_t *g_q = nullptr, *g_l = nullptr, *a_off = nullptr, *ntasks = nullptr, *task_moff = nullptr, *task_rows = nullptr;
+    float* g_base = nullptr;
+    uint4* tasks = nullptr;
+    unsigned int* pool_cnt = nullptr;
+    unsigned int pool_cap = 0;
+    GatherArgs ga{};
+    if (path == LIST_TENSOR) {
+      tc_info(ix.recon, &ti);
+      const size_t Kp = size_t(ti.Kp);
+      // gathered operand rows: every pair once, every list's rows rounded up to whole 256-row tiles
+      a_rows = nq * size_t(nprobe) + 256 * std::min<size_t>(ix.nlist, nq * size_t(nprobe)) + 256;
+      max_tasks = a_rows / 256;
+      const int q_slots = std::min(nprobe, 64);
+      FV_TRY(ctx->scratch[12].reserve(a_rows * Kp * sizeof(uint16_t)));
+      FV_TRY(ctx->scratch[13].reserve((a_rows * 4 + nq * size_t(q_slots + 1)) * sizeof(uint32_t) + 64));
+      FV_TRY(ctx->scratch[14].reserve(max_tasks * (sizeof(uint4) + 2 * sizeof(uint32_t)) +
+                                      (ix.nlist + 8 + size_t(ctx->sm_count)) * sizeof(uint32_t)));
+      pool_cap = unsigned(std::max<size_t>(32768, nq * 2048 / size_t(ctx->sm_count)));
+      FV_TRY(ctx->scratch[15].reserve(size_t(ctx->sm_count) * pool_cap * sizeof(u64)));
+      qg = ctx->scratch[12].as<uint16_t>();
+      thr = ctx->scratch[13].as<float>();
+      g_q = reinterpret_cast<uint32_t*>(thr + a_rows);
+      g_l = g_q + a_rows;
+      g_base = reinterpret_cast<float*>(g_l + a_rows);
+      uint32_t* q_rows = reinterpret_cast<uint32_t*>(g_base + a_rows);
+      uint32_t* q_cnt = q_rows + nq * size_t(q_slots);
+      tasks = ctx->scratch[14].as<uint4>();
+      task_moff = reinterpret_cast<uint32_t*>(tasks + max_tasks);
+      task_rows = task_moff + max_tasks;
+      a_off = task_rows + max_tasks;
+      ntasks = a_off + ix.nlist;
+      pool_cnt = ntasks + 8;
+      ga.list_off = ix.list_off;
+      ga.a_off = a_off;
+      ga.queries = q;
+      ga.centroids = ix.centroids;
+      ga.tau_bits = tau_bits;
+      ga.cand_cnt = pb_set.per_query;
+      ga.cap = cap;
+      ga.pd = ix.pd;
+      ga.Kp = ti.Kp;
+      ga.is_l2 = ix.metric == FV_L2 ? 1 : 0;
+      ga.bf16 = ti.bf16 ? 1 : 0;
+      ga.kf = float(ti.Kp);
+      ga.bn = std::sqrt(ti.max_norm2);
+      ga.cw2 = ix.cen_norm2_max + ix.code_norm2_max;
+      ga.c1 = 4.f * float(ix.pd / 8 + ix.m + 3 * ix.dsub + 24);
+      ga.qg = qg;
+      ga.thr = thr;
+      ga.g_q = g_q;
+      ga.g_l = g_l;
+      ga.g_base = g_base;
+      // ---- the bound pass on the tensor cores: the near pairs' rows scored, the minimum of every 8 kept
+      size_t mfloats = std::max<size_t>(size_t(1) << 20, nq * 4096);
+      mfloats = std::min<size_t>(mfloats, size_t(1) << 30);
+      FV_TRY(ctx->scratch[6].reserve(mfloats * sizeof(float)));
+      FV_CUDA(cudaMemsetAsync(q_cnt, 0, nq * sizeof(uint32_t), ctx->stream));
+      tc_tasks_kernel<<<1, 1024, 0, ctx->stream>>>(pa_set.pair_off, ix.list_off, ix.roff8, ix.roff8 + ix.nlist + 1, ix.nlist, tasks,
+                                                   a_off, ntasks, nullptr, task_moff, task_rows, uint32_t(mfloats));
+      GatherArgs gb = ga;
+      gb.pair_off = pa_set.pair_off;
+      gb.pairs = pairs_a;
+      gb.q_rows = q_rows;
+      gb.q_cnt = q_cnt;
+      gb.q_slots = q_slots;
+      tc_gather_kernel<<<dim3(unsigned(ix.nlist), 4), 256, 0, ctx->stream>>>(gb);
+      ctx->stats.launches += 2;
+      FV_CUDA(cudaGetLastError());
+      int g0 = 0;
+      FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, nullptr, tasks, ntasks, nullptr, pool_cnt, 0, &g0,
+                          ctx->scratch[6].as<float>(), task_moff, task_rows));
+      const int vcap = 4096;
+      const size_t ssmem = size_t(4) * vcap * sizeof(uint32_t);
+      FV_CUDA(cudaFuncSetAttribute(tc_bound_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ssmem)));
+      tc_bound_select_kernel<<<unsigned((nq + 3) / 4), 128, ssmem, ctx->stream>>>(ctx->scratch[6].as<float>(), tasks, task_moff,
+                                                                                 task_rows, thr, q_rows, q_cnt, q_slots, vcap, keep,
+                                                                                 nq, tau_bits);
+      ctx->stats.launches++;
+      FV_CUDA(cudaGetLastError());
+    } else {
+      la.pair_off = pa_set.pair_off;
+      la.task_off = pa_set.task_off;
+      la.pairs = pairs_a;
+      la.counters = pa_set.counters;
+      la.minima = ctx->scratch[6].as<float>();
+      la.minima_cnt = pa_set.per_query;
+      la.minima_cap = int(mcap);
+      FV_TRY(ctx->scratch[6].reserve(nq * mcap * sizeof(float)));
+      la.minima = ctx->scratch[6].as<float>();
+      auto bound_k = use_pre ? ivfpq_list_scan_kernel<true, true> : ivfpq_list_scan_kernel<false, true>;
+      FV_CUDA(cudaFuncSetAttribute(bound_k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(LS_SMEM)));
+      bound_k<<<ctx->sm_count, LS_THREADS, LS_SMEM, ctx->stream>>>(la);
+      {
+        const int wpb = mcap <= 2048 ? 4 : 1;  // warps (queries) per block, by the shared memory their minima take
+        const size_t ssmem = size_t(wpb) * mcap * sizeof(uint32_t);
+        if (ssmem > 40 * 1024)
+          FV_CUDA(cudaFuncSetAttribute(bound_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ssmem)));
+        bound_select_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, ssmem, ctx->stream>>>(la.minima, la.minima_cnt, int(mcap),
+                                                                                               keep, nq, tau_bits);
+      }
+      ctx->stats.launches += 2;
+      FV_CUDA(cudaGetLastError());
     }
-    ctx->stats.launches += 2;
-    FV_CUDA(cudaGetLastError());
     stage_mark(ctx);  // 1
     FV_TRY(bucket_pairs(ctx, ix, cells, nq, nprobe, 0, pb_set, pairs_b));
     u64* cand = ctx->scratch[9].as<u64>();
     uint32_t* cand_cnt = pb_set.per_query;
     RescoreArgs ra{};
-    unsigned int* pool_cnt = nullptr;
     int tc_grid = 0;
-    unsigned int pool_cap = 0;
     if (path == LIST_TABLE) {
       stage_mark(ctx);  // 2
       la.pair_off = pb_set.pair_off;
@@ -1367,55 +1539,12 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       FV_CUDA(cudaGetLastError());
       stage_mark(ctx);  // 3
     } else {
-      TcInfo ti{};
-      tc_info(ix.recon, &ti);
-      const size_t Kp = size_t(ti.Kp);
-      // gathered operand rows: every pair once, every list's rows rounded up to whole 256-row tiles
-      const size_t a_rows = nq * size_t(nprobe) + 256 * std::min<size_t>(ix.nlist, nq * size_t(nprobe)) + 256;
-      const size_t max_tasks = a_rows / 256;
-      FV_TRY(ctx->scratch[12].reserve(a_rows * Kp * sizeof(uint16_t)));
-      FV_TRY(ctx->scratch[13].reserve(a_rows * 4 * sizeof(uint32_t) + 64));
-      FV_TRY(ctx->scratch[14].reserve(max_tasks * sizeof(uint4) + (ix.nlist + 8 + size_t(ctx->sm_count)) * sizeof(uint32_t)));
-      pool_cap = unsigned(std::max<size_t>(32768, nq * 2048 / size_t(ctx->sm_count)));
-      FV_TRY(ctx->scratch[15].reserve(size_t(ctx->sm_count) * pool_cap * sizeof(u64)));
-      uint16_t* qg = ctx->scratch[12].as<uint16_t>();
-      float* thr = ctx->scratch[13].as<float>();
-      uint32_t* g_q = reinterpret_cast<uint32_t*>(thr + a_rows);
-      uint32_t* g_l = g_q + a_rows;
-      float* g_base = reinterpret_cast<float*>(g_l + a_rows);
-      uint4* tasks = ctx->scratch[14].as<uint4>();
-      uint32_t* a_off = reinterpret_cast<uint32_t*>(tasks + max_tasks);
-      uint32_t* ntasks = a_off + ix.nlist;
-      pool_cnt = ntasks + 8;
-      tc_tasks_kernel<<<1, 1024, 0, ctx->stream>>>(pb_set.pair_off, ix.list_off, ix.roff8, ix.roff8 + ix.nlist + 1, ix.nlist,
-                                                   tasks, a_off, ntasks, d_rows + 1);
-      ctx->stats.launches++;
-      FV_CUDA(cudaGetLastError());
-      GatherArgs ga{};
+      tc_tasks_kernel<<<1, 1024, 0, ctx->stream>>>(pb_set.pair_off, ix.list_off, ix.roff8, ix.roff8 + ix.nlist + 1, ix.nlist, tasks,
+                                                   a_off, ntasks, d_rows + 1, nullptr, nullptr, 0u);
       ga.pair_off = pb_set.pair_off;
-      ga.list_off = ix.list_off;
-      ga.a_off = a_off;
       ga.pairs = pairs_b;
-      ga.queries = q;
-      ga.centroids = ix.centroids;
-      ga.tau_bits = tau_bits;
-      ga.cand_cnt = cand_cnt;
-      ga.cap = cap;
-      ga.pd = ix.pd;
-      ga.Kp = ti.Kp;
-      ga.is_l2 = ix.metric == FV_L2 ? 1 : 0;
-      ga.bf16 = ti.bf16 ? 1 : 0;
-      ga.kf = float(ti.Kp);
-      ga.bn = std::sqrt(ti.max_norm2);
-      ga.cw2 = ix.cen_norm2_max + ix.code_norm2_max;
-      ga.c1 = 4.f * float(ix.pd / 8 + ix.m + 3 * ix.dsub + 24);
-      ga.qg = qg;
-      ga.thr = thr;
-      ga.g_q = g_q;
-      ga.g_l = g_l;
-      ga.g_base = g_base;
       tc_gather_kernel<<<dim3(unsigned(ix.nlist), 4), 256, 0, ctx->stream>>>(ga);
-      ctx->stats.launches++;
+      ctx->stats.launches += 2;
       FV_CUDA(cudaGetLastError());
       stage_mark(ctx);  // 2
       FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, thr, tasks, ntasks, ctx->scratch[15].as<u64>(), pool_cnt,
