@@ -268,6 +268,10 @@ struct GemmParams {
   u64* pool;                   // [grid][pool_cap] survivors: (A row << 32) | B row relative to y
   unsigned int* pool_cnt;      // [grid] entries each CTA produced (may exceed pool_cap: overflow)
   unsigned int pool_cap;
+  // A survivor that finds its CTA's pool full is dropped, and the owner of its operand row (row_owner[A row], a
+  // query number) is marked in owner_dropped so that the caller can hand that query to another kernel.
+  const uint32_t* row_owner;
+  uint32_t* owner_dropped;
   // task mode, minima variant (minima != null): instead of survivors, the smallest score of every 8 B rows, for the
   // first task_rows[t] operand rows of task t: minima[task_moff[t] + (row in tile * units + unit) * 32 + column / 8];
   // B rows beyond the task's valid ones count as +inf.  Tasks with task_moff[t] == 0xFFFFFFFF write nothing.
@@ -648,6 +652,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 ++pos;
               }
             }
+            if (mine && pos > p.pool_cap) p.owner_dropped[p.row_owner[a_row]] = 1u;  // some of this row's did not fit
           };
           uint32_t rbuf[64];
 #pragma unroll 1
@@ -1339,8 +1344,8 @@ int tc_prepare_queries(fv_ctx* ctx, TcSide* tc, int metric, const float* d_queri
 
 int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_t a_rows, const float* d_thr,
                  const uint4* d_tasks, const uint32_t* d_ntasks, u64* d_pool, unsigned int* d_pool_cnt,
-                 unsigned int pool_cap, int* grid_out, float* d_minima, const uint32_t* d_task_moff,
-                 const uint32_t* d_task_rows) {
+                 unsigned int pool_cap, const uint32_t* d_row_owner, uint32_t* d_dropped, int* grid_out, float* d_minima,
+                 const uint32_t* d_task_moff, const uint32_t* d_task_rows) {
   const int Kp = tc->Kp;
   if (Kp > 2 * KBLK) return fail(FV_ERR_UNSUPPORTED, "task mode of the tensor-core kernel covers padded dimensions up to 128");
   Tiling t{};
@@ -1359,6 +1364,8 @@ int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_
   gp.pool = d_pool;
   gp.pool_cnt = d_pool_cnt;
   gp.pool_cap = pool_cap;
+  gp.row_owner = d_row_owner;
+  gp.owner_dropped = d_dropped;
   gp.minima = d_minima;
   gp.task_moff = d_task_moff;
   gp.task_rows = d_task_rows;

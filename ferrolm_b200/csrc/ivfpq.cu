@@ -255,6 +255,7 @@ struct fv_ivfpq {
   float cen_norm2_max = 0.f, code_norm2_max = 0.f;
   int scan_mode = 0;      // 0 pick by size, 1 one block per query, 2 list-major table scan, 3 list-major tensor-core pass
   int cand_slots = 0;     // list-major scan: candidate slots per query (0 = default)
+  size_t survivor_slots = 0;  // tensor-core pass: survivor pool entries per CTA (0 = default)
 };
 
 namespace fv {
@@ -671,6 +672,7 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   si.roff8 = ix->recon_valid && ix->recon ? ix->roff8.as<uint32_t>() : nullptr;
   si.cen_norm2_max = ix->cen_norm2_max;
   si.code_norm2_max = ix->code_norm2_max;
+  si.survivor_slots = ix->survivor_slots;
   fv::ScanOut so{};
   so.keys = ctx->scratch[1].as<u64>();
   so.adc = d_adc;
@@ -696,6 +698,12 @@ size_t fv_ivfpq_nlist(const fv_ivfpq* ix) { return ix ? ix->nlist : 0; }
 int fv_ivfpq_set_candidate_slots(fv_ivfpq* ix, size_t slots) {
   if (!ix || slots > 4096) return fv::fail(FV_ERR_ARG, "fv_ivfpq_set_candidate_slots: at most 4096 slots");
   ix->cand_slots = int(slots);
+  return FV_OK;
+}
+
+int fv_ivfpq_set_survivor_slots(fv_ivfpq* ix, size_t slots) {
+  if (!ix || slots > (size_t(1) << 21)) return fv::fail(FV_ERR_ARG, "fv_ivfpq_set_survivor_slots: at most 2^21 slots");
+  ix->survivor_slots = slots;
   return FV_OK;
 }
 

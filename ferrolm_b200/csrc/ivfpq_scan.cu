@@ -781,22 +781,37 @@ __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __res
   const uint32_t INF_BITS = 0xFF800000u;
   const int np = int(min(q_cnt[q], uint32_t(q_slots)));
   int n = 0, finite = 0;
-  for (int s = 0; s < np; ++s) {
-    const uint32_t arow = q_rows[q * size_t(q_slots) + s];
-    const uint32_t t = arow >> 8, rt = arow & 255u;
-    const uint32_t moff = task_moff[t];
-    if (moff == 0xFFFFFFFFu || rt >= task_rows[t]) continue;
-    const int cnt = int(tasks[t].z) * 32;
-    const float* src = minima + size_t(moff) + size_t(rt) * cnt;
-    const float ad = add[arow];
-    const int room = min(cnt, vcap - n);
-    for (int i = lane; i < room; i += 32) {
-      const uint32_t b = order_bits(__fadd_ru(src[i], ad));  // rounded up: still an upper bound
-      v[n + i] = b;
-      finite += b < INF_BITS ? 1 : 0;
+  for (int s0 = 0; s0 < np && n < vcap; s0 += 32) {
+    // lane i looks up pair s0 + i (one round of dependent loads for 32 pairs instead of one per pair) ...
+    uint32_t my_off = 0xFFFFFFFFu;
+    int my_cnt = 0;
+    float my_add = 0.f;
+    if (s0 + lane < np) {
+      const uint32_t arow = q_rows[q * size_t(q_slots) + s0 + lane];
+      const uint32_t t = arow >> 8, rt = arow & 255u;
+      const uint32_t moff = task_moff[t];
+      if (moff != 0xFFFFFFFFu && rt < task_rows[t]) {
+        my_cnt = int(tasks[t].z) * 32;
+        my_off = moff + rt * uint32_t(my_cnt);
+        my_add = add[arow];
+      }
     }
-    n += room;
-    if (n >= vcap) break;
+    // ... and the warp copies their minima one pair after the other
+    const int np32 = min(32, np - s0);
+    for (int j = 0; j < np32 && n < vcap; ++j) {
+      const uint32_t off = __shfl_sync(FV_FULL, my_off, j);
+      const int cnt = __shfl_sync(FV_FULL, my_cnt, j);
+      const float ad = __shfl_sync(FV_FULL, my_add, j);
+      if (off == 0xFFFFFFFFu) continue;
+      const float* src = minima + size_t(off);
+      const int room = min(cnt, vcap - n);
+      for (int i = lane; i < room; i += 32) {
+        const uint32_t b = order_bits(__fadd_ru(src[i], ad));  // rounded up: still an upper bound
+        v[n + i] = b;
+        finite += b < INF_BITS ? 1 : 0;
+      }
+      n += room;
+    }
   }
   __syncwarp();
   if (__reduce_add_sync(FV_FULL, finite) < keep) {
@@ -832,6 +847,7 @@ struct FinishArgs {
   uint32_t* redo;
   uint32_t* over_ids;
   uint32_t* rerun_ids;
+  const uint32_t* dropped;  // or null; dropped[q] != 0: the scan lost survivors of q (a full pool): to rerun_ids
 };
 
 // One block per query: the best `keep` of the appended candidates, then the common tail.
@@ -842,7 +858,7 @@ __global__ void __launch_bounds__(256) ivfpq_finish_kernel(ScanArgs a, FinishArg
   const size_t q = f.qids ? size_t(f.qids[blockIdx.x]) : size_t(blockIdx.x);
   const int tid = threadIdx.x;
   const uint32_t cnt = f.cand_cnt[q];
-  if (cnt == 0xFFFFFFFFu || (cnt > uint32_t(f.cap) && !f.tighten)) {
+  if (cnt == 0xFFFFFFFFu || (cnt > uint32_t(f.cap) && !f.tighten) || (f.dropped && f.dropped[q])) {
     if (tid == 0) f.rerun_ids[atomicAdd(f.counters + LS_C_RERUN, 1u)] = uint32_t(q);
     return;
   }
@@ -1174,6 +1190,7 @@ struct RescoreArgs {
   const u64* pool;
   const unsigned int* pool_cnt;
   unsigned int pool_cap;
+  int npools;
   const uint32_t* g_q;
   const uint32_t* g_l;
   const float* g_base;
@@ -1192,12 +1209,31 @@ struct RescoreArgs {
 
 // One thread per survivor: the reference's compressed distance (ivfpq.rs:256-262, :272-276), bit for bit; kept if
 // at or below the query's bound.
+// The pools are very unequal (a CTA that drew the lists of a dense region holds several times the average), so the
+// blocks split the concatenation of all pools evenly instead of a pool each.
 __global__ void __launch_bounds__(128) rescore_kernel(RescoreArgs a) {
-  const size_t c = blockIdx.x;
-  const unsigned int n = min(a.pool_cnt[c], a.pool_cap);
+  uint32_t* start = reinterpret_cast<uint32_t*>(dyn_smem());  // npools + 1: first global index of every pool
+  if (threadIdx.x == 0) {
+    uint32_t s = 0;
+    for (int c = 0; c < a.npools; ++c) {
+      start[c] = s;
+      s += min(a.pool_cnt[c], a.pool_cap);
+    }
+    start[a.npools] = s;
+  }
+  __syncthreads();
+  const uint32_t total = start[a.npools];
+  const uint32_t per = ((total + gridDim.x - 1) / gridDim.x + 127u) & ~127u;
+  const uint32_t i0 = min(total, blockIdx.x * per), i1 = min(total, i0 + per);
   const size_t tab = size_t(a.m) * KSUB;
-  for (unsigned int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
-    const u64 e = a.pool[c * size_t(a.pool_cap) + i];
+  for (uint32_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+    int lo = 0, hi = a.npools - 1;  // the pool holding global index i: the last one starting at or before it
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (start[mid] <= i) lo = mid;
+      else hi = mid - 1;
+    }
+    const u64 e = a.pool[size_t(lo) * a.pool_cap + (i - start[lo])];
     const uint32_t arow = uint32_t(e >> 32), row = uint32_t(e);
     const uint32_t q = a.g_q[arow], l = a.g_l[arow];
     if (a.only && !a.only[q]) continue;
@@ -1418,6 +1454,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     uint4* tasks = nullptr;
     unsigned int* pool_cnt = nullptr;
     unsigned int pool_cap = 0;
+    uint32_t* dropped = nullptr;  // per query: the main pass lost survivors of it (a full pool)
     GatherArgs ga{};
     if (path == LIST_TENSOR) {
       tc_info(ix.recon, &ti);
@@ -1427,10 +1464,12 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       max_tasks = a_rows / 256;
       const int q_slots = std::min(nprobe, 64);
       FV_TRY(ctx->scratch[12].reserve(a_rows * Kp * sizeof(uint16_t)));
-      FV_TRY(ctx->scratch[13].reserve((a_rows * 4 + nq * size_t(q_slots + 1)) * sizeof(uint32_t) + 64));
+      FV_TRY(ctx->scratch[13].reserve((a_rows * 4 + nq * size_t(q_slots + 2)) * sizeof(uint32_t) + 64));
       FV_TRY(ctx->scratch[14].reserve(max_tasks * (sizeof(uint4) + 2 * sizeof(uint32_t)) +
                                       (ix.nlist + 8 + size_t(ctx->sm_count)) * sizeof(uint32_t)));
-      pool_cap = unsigned(std::max<size_t>(32768, nq * 2048 / size_t(ctx->sm_count)));
+      // per CTA; the fullest pool measured holds four to six times the average
+      pool_cap = unsigned(std::min<size_t>(size_t(1) << 21, std::max<size_t>(65536, nq * 4096 / size_t(ctx->sm_count))));
+      if (ix.survivor_slots) pool_cap = unsigned(ix.survivor_slots);
       FV_TRY(ctx->scratch[15].reserve(size_t(ctx->sm_count) * pool_cap * sizeof(u64)));
       qg = ctx->scratch[12].as<uint16_t>();
       thr = ctx->scratch[13].as<float>();
@@ -1439,6 +1478,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       g_base = reinterpret_cast<float*>(g_l + a_rows);
       uint32_t* q_rows = reinterpret_cast<uint32_t*>(g_base + a_rows);
       uint32_t* q_cnt = q_rows + nq * size_t(q_slots);
+      dropped = q_cnt + nq;
       tasks = ctx->scratch[14].as<uint4>();
       task_moff = reinterpret_cast<uint32_t*>(tasks + max_tasks);
       task_rows = task_moff + max_tasks;
@@ -1482,14 +1522,16 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       ctx->stats.launches += 2;
       FV_CUDA(cudaGetLastError());
       int g0 = 0;
-      FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, nullptr, tasks, ntasks, nullptr, pool_cnt, 0, &g0,
+      FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, nullptr, tasks, ntasks, nullptr, pool_cnt, 0, nullptr, nullptr, &g0,
                           ctx->scratch[6].as<float>(), task_moff, task_rows));
-      const int vcap = 4096;
-      const size_t ssmem = size_t(4) * vcap * sizeof(uint32_t);
+      // bounds looked at per query: room for twice the 8-row minima of the rows the bound pass aims at
+      int vcap = 2048;
+      while (vcap < 16384 && size_t(vcap) < 2 * size_t(bound_rows / 8) + 512) vcap <<= 1;
+      const int wpb = vcap <= 4096 ? 4 : 1;  // warps (queries) per block, by the shared memory their bounds take
+      const size_t ssmem = size_t(wpb) * vcap * sizeof(uint32_t);
       FV_CUDA(cudaFuncSetAttribute(tc_bound_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ssmem)));
-      tc_bound_select_kernel<<<unsigned((nq + 3) / 4), 128, ssmem, ctx->stream>>>(ctx->scratch[6].as<float>(), tasks, task_moff,
-                                                                                 task_rows, thr, q_rows, q_cnt, q_slots, vcap, keep,
-                                                                                 nq, tau_bits);
+      tc_bound_select_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, ssmem, ctx->stream>>>(
+          ctx->scratch[6].as<float>(), tasks, task_moff, task_rows, thr, q_rows, q_cnt, q_slots, vcap, keep, nq, tau_bits);
       ctx->stats.launches++;
       FV_CUDA(cudaGetLastError());
     } else {
@@ -1547,12 +1589,14 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       ctx->stats.launches += 2;
       FV_CUDA(cudaGetLastError());
       stage_mark(ctx);  // 2
+      FV_CUDA(cudaMemsetAsync(dropped, 0, nq * sizeof(uint32_t), ctx->stream));
       FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, thr, tasks, ntasks, ctx->scratch[15].as<u64>(), pool_cnt,
-                          pool_cap, &tc_grid));
+                          pool_cap, g_q, dropped, &tc_grid));
       stage_mark(ctx);  // 3
       ra.pool = ctx->scratch[15].as<u64>();
       ra.pool_cnt = pool_cnt;
       ra.pool_cap = pool_cap;
+      ra.npools = tc_grid;
       ra.g_q = g_q;
       ra.g_l = g_l;
       ra.g_base = g_base;
@@ -1566,7 +1610,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       ra.cand = cand;
       ra.cand_cnt = cand_cnt;
       ra.cap = cap;
-      rescore_kernel<<<dim3(unsigned(tc_grid), 32), 128, 0, ctx->stream>>>(ra);
+      rescore_kernel<<<unsigned(tc_grid) * 16, 128, size_t(tc_grid + 1) * sizeof(uint32_t), ctx->stream>>>(ra);
       ctx->stats.launches++;
       FV_CUDA(cudaGetLastError());
     }
@@ -1584,6 +1628,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     fa.redo = redo;
     fa.over_ids = pb_set.extra;
     fa.rerun_ids = pb_set.extra2;
+    fa.dropped = dropped;
     int n2max = 32;
     while (n2max < cap || n2max < keep) n2max <<= 1;
     const size_t fsmem = (size_t(n2max) + size_t(keep) + size_t(k)) * sizeof(u64) + size_t(ix.pd) * sizeof(float);
@@ -1602,21 +1647,14 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     }
     FV_CUDA(cudaStreamSynchronize(ctx->stream));
     if (tc_grid && h_pool[tc_grid]) return fail(FV_ERR_TIMEOUT, "a bounded wait inside the tensor-core kernel ran out");
-    bool pool_over = false;
-    for (int c = 0; c < tc_grid; ++c) {
-      pool_over = pool_over || h_pool[c] > pool_cap;
-      ctx->stats.dist_evals += h_pool[c];  // survivors of the tensor-core pass: pairs re-scored exactly
-    }
+    // survivors of the tensor-core pass: pairs re-scored exactly (a pool that ran over dropped the rest, and the
+    // finishing kernel has put the queries they belonged to on the re-run list)
+    for (int c = 0; c < tc_grid; ++c) ctx->stats.dist_evals += std::min(h_pool[c], pool_cap);
     uint32_t n_over = h_ctr[LS_C_OVER], n_rerun = h_ctr[LS_C_RERUN];
-    if (pool_over) {  // survivors were dropped: the whole batch once more, by the per-query kernel
-      ScanArgs r = a;
-      r.rows_scanned = nullptr;
-      FV_TRY(launch_block_scan(ctx, r, nq, use_pre));
-      n_rerun = uint32_t(nq);
-    } else {
+    {
       if (n_over) {  // second round: the marked queries' survivors against their tightened bounds
         ra.only = redo;
-        rescore_kernel<<<dim3(unsigned(tc_grid), 32), 128, 0, ctx->stream>>>(ra);
+        rescore_kernel<<<unsigned(tc_grid) * 16, 128, size_t(tc_grid + 1) * sizeof(uint32_t), ctx->stream>>>(ra);
         fa.qids = fa.over_ids;
         fa.tighten = 0;
         ivfpq_finish_kernel<<<n_over, 256, fsmem, ctx->stream>>>(a, fa, n2max);

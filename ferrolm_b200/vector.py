@@ -326,6 +326,10 @@ class IvfPq:
         """Candidate slots per query of the list-major scan (0 = default); overflowing queries are re-run."""
         check(lib().fv_ivfpq_set_candidate_slots(self._h, slots))
 
+    def set_survivor_slots(self, slots: int):
+        """Survivor pool entries per CTA of the tensor-core pass (0 = default); queries that lose survivors are re-run."""
+        check(lib().fv_ivfpq_set_survivor_slots(self._h, slots))
+
     def __len__(self) -> int:
         return lib().fv_ivfpq_len(self._h)
 

@@ -161,6 +161,10 @@ int fv_ivfpq_set_scan_mode(fv_ivfpq* ix, int mode);
  * batches; at most 4096).  A query that finds more rows below its bound than it has slots is re-run by the
  * per-query kernel (counted in fv_stats.uncertified), so a small value trades memory for re-runs, never results. */
 int fv_ivfpq_set_candidate_slots(fv_ivfpq* ix, size_t slots);
+/* Tensor-core pass: entries (8 bytes each) of the pool every CTA appends its survivors to (0 = default, sized from
+ * the batch; at most 2^21).  Survivors that find the pool full are dropped and the queries they belong to re-run by
+ * the per-query kernel (fv_stats.uncertified): again memory against re-runs, never results. */
+int fv_ivfpq_set_survivor_slots(fv_ivfpq* ix, size_t slots);
 size_t fv_ivfpq_save_size(const fv_ivfpq* ix);
 int fv_ivfpq_save(const fv_ivfpq* ix, uint8_t* buf, size_t cap, size_t* written);      /* save :332 ("FLIVFPQ1") */
 int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out);      /* load :354 */

@@ -419,6 +419,27 @@ def test_ivfpq_list_major_scan_reruns_queries_whose_buffer_overflows(fv, oracle,
     assert eq == total and over > 0
 
 
+@pytest.mark.parametrize("slots", [64, 20000])
+def test_ivfpq_tensor_pass_reruns_queries_whose_survivors_were_dropped(fv, oracle, ivfpq16_pair, slots):
+    # a survivor pool far smaller than the survivors of the batch: the tensor-core pass drops what does not fit, marks
+    # the queries concerned, and exactly those go to the per-query kernel -- the neighbours stay the reference's
+    g, o, base, queries = ivfpq16_pair
+    want, wc = o.search_batch(queries, 10, 16, 10)
+    g.set_scan_mode(3)
+    g.set_survivor_slots(slots)
+    try:
+        got, gc = g.search_batch(queries, 10, 16, 10)
+        st = g.ctx.stats()
+    finally:
+        g.set_survivor_slots(0)
+        g.set_scan_mode(0)
+    eq, total = assert_same_neighbours(got, gc, want, wc, f"ivfpq tensor pass, {slots} survivor slots per CTA")
+    assert eq == total
+    assert st["uncertified"] <= len(queries)
+    if slots == 64:
+        assert st["uncertified"] > 0
+
+
 def test_ivfpq_list_major_scan_inner_product_and_ragged_lists(fv, oracle, ctx):
     # inner product (the query's table is the lookup table, ivfpq.rs:236-238), dsub = 4, many short and empty lists,
     # row counts that are not multiples of 16, fewer than 32 queries on some lists
