@@ -405,8 +405,15 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
-  // Work items: chunk g of the tiling, or task g of the table; CTA b takes g = b, b + grid, ...
+  // Work items: chunk g of the tiling, CTA b taking g = b, b + grid, ...; or task g of the table.  The caller sorts
+  // tasks by decreasing length, so they are dealt back and forth (b, 2 grid - 1 - b, 2 grid + b, ...): the CTA that
+  // drew the longest task of one round draws the shortest of the next, which evens out what plain dealing leaves
+  // unequal by about one longest task.
   const int nwork = TASKS ? int(*p.ntasks) : p.nchunks;
+  auto work_of = [&](int seg) {
+    const int G = int(gridDim.x), b = int(blockIdx.x);
+    return seg * G + ((TASKS && (seg & 1)) ? G - 1 - b : b);
+  };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -414,7 +421,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       bool ok = true;
       StageCursor st(p.nstage);
       int ring = 0;
-      for (int g = blockIdx.x, seg = 0; g < nwork && ok; g += gridDim.x, ++seg) {
+      for (int seg = 0, g = work_of(0); g < nwork && ok; g = work_of(++seg)) {
         int nt0, nt1, a_row0, b_row0 = 0;
         if (TASKS) {
           const uint4 t = p.tasks[g];
@@ -469,7 +476,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       StageCursor st(p.nstage);
       const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB), e_base = smem_u32(sE);
       const uint64_t aext_desc = smem_desc_sw32(smem_u32(sAext));
-      for (int g = blockIdx.x, seg = 0; g < nwork && ok; g += gridDim.x, ++seg) {
+      for (int seg = 0, g = work_of(0); g < nwork && ok; g = work_of(++seg)) {
         int nt0, nt1;
         if (TASKS) {
           nt0 = 0;
@@ -543,7 +550,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     uint32_t n_rows = uint32_t(p.n);
     uint32_t a_row = 0;  // task mode: this thread's operand row
     float* mdst = nullptr;  // task mode, minima variant: where this thread's minima of the current task go
-    for (int g = blockIdx.x, seg = 0; g < nwork && ok; g += gridDim.x, ++seg) {
+    for (int seg = 0, g = work_of(0); g < nwork && ok; g = work_of(++seg)) {
       int nt0, nt1, mt = 0;
       if (TASKS) {
         const uint4 t = p.tasks[g];
