@@ -265,6 +265,7 @@ struct GemmParams {
   // task mode (TASKS): the work is a table of (A tile, run of B units) pairs instead of the tiling above
   const uint4* tasks;          // x: first operand row of the 256-row A tile, y: first B row, z: B units of 256 rows, w: valid B rows
   const uint32_t* ntasks;      // device word: number of tasks
+  unsigned int* next_task;     // device word, zero at launch: the next task nobody has taken yet
   u64* pool;                   // [grid][pool_cap] survivors: (A row << 32) | B row relative to y
   unsigned int* pool_cnt;      // [grid] entries each CTA produced (may exceed pool_cap: overflow)
   unsigned int pool_cap;
@@ -287,6 +288,10 @@ struct __align__(8) Barriers {
   uint32_t tmem_base;
   int abort_flag;
   unsigned int pool_pos;  // task mode: survivors this CTA has appended
+  // task mode: the tasks this CTA has drawn, handed from the producer to the MMA and epilogue warps.  Entry
+  // i & 7 holds the i-th draw (a value >= the task count ends the work); tq_full[i & 7] completes once per draw.
+  uint64_t tq_full[8];
+  unsigned int tq[8];
 };
 
 // Epilogue thread -> list index: warp group `sub` (0..3) * 128 + lane quadrant * 32 + lane.  MH = 2: sub & 1 is the
@@ -383,6 +388,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     }
     mbar_init(&bars->a_full, 1);
     mbar_init(&bars->a_empty, 1);
+    for (int i = 0; i < 8; ++i) mbar_init(&bars->tq_full[i], 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->tfull[i], 1);
       mbar_init(&bars->tempty[i], MH == 2 ? NEPI / 2 : NEPI);
@@ -405,14 +411,25 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
-  // Work items: chunk g of the tiling, CTA b taking g = b, b + grid, ...; or task g of the table.  The caller sorts
-  // tasks by decreasing length, so they are dealt back and forth (b, 2 grid - 1 - b, 2 grid + b, ...): the CTA that
-  // drew the longest task of one round draws the shortest of the next, which evens out what plain dealing leaves
-  // unequal by about one longest task.
+  // Work items.  Plain and threshold mode: chunk g of the tiling, CTA b taking g = b, b + grid, ...
+  // Task mode: tasks cost very different amounts (their length, and how many survivors the epilogue has to append),
+  // so they are not dealt in advance: the producer draws the next task from a device-wide counter whenever the
+  // operand tile is free again, and passes the number on to the MMA and epilogue warps through a small ring in shared
+  // memory.  The ring has 8 entries; the producer is at most 3 draws ahead of the slowest reader, because it draws
+  // task i + 1 only after every MMA of task i - 1 has completed, by when the epilogue is at work on task i - 2 at
+  // the latest (two accumulator slots).  The caller sorts the tasks by decreasing length: longest first.
   const int nwork = TASKS ? int(*p.ntasks) : p.nchunks;
-  auto work_of = [&](int seg) {
-    const int G = int(gridDim.x), b = int(blockIdx.x);
-    return seg * G + ((TASKS && (seg & 1)) ? G - 1 - b : b);
+  auto work_of = [&](int seg) -> int {  // consumer side
+    if (!TASKS) return int(blockIdx.x) + seg * int(gridDim.x);
+    if (!mbar_wait(&bars->tq_full[seg & 7], uint32_t(seg >> 3) & 1, abort_flag)) return 0x7FFFFFFF;
+    return int(*reinterpret_cast<volatile unsigned int*>(&bars->tq[seg & 7]));
+  };
+  auto draw = [&](int seg) -> int {  // producer side
+    if (!TASKS) return int(blockIdx.x) + seg * int(gridDim.x);
+    const unsigned int g = min(atomicAdd(p.next_task, 1u), 0x7FFFFFFEu);
+    bars->tq[seg & 7] = g;
+    mbar_arrive(&bars->tq_full[seg & 7]);  // release: the entry is visible to whoever sees this phase complete
+    return int(g);
   };
 
   if (warp == 0) {
@@ -421,7 +438,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       bool ok = true;
       StageCursor st(p.nstage);
       int ring = 0;
-      for (int seg = 0, g = work_of(0); g < nwork && ok; g = work_of(++seg)) {
+      for (int seg = 0, g = draw(0); g < nwork && ok; g = draw(++seg)) {
         int nt0, nt1, a_row0, b_row0 = 0;
         if (TASKS) {
           const uint4 t = p.tasks[g];
@@ -1350,7 +1367,7 @@ int tc_prepare_queries(fv_ctx* ctx, TcSide* tc, int metric, const float* d_queri
 }
 
 int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_t a_rows, const float* d_thr,
-                 const uint4* d_tasks, const uint32_t* d_ntasks, u64* d_pool, unsigned int* d_pool_cnt,
+                 const uint4* d_tasks, const uint32_t* d_ntasks, unsigned int* d_next_task, u64* d_pool, unsigned int* d_pool_cnt,
                  unsigned int pool_cap, const uint32_t* d_row_owner, uint32_t* d_dropped, int* grid_out, float* d_minima,
                  const uint32_t* d_task_moff, const uint32_t* d_task_rows) {
   const int Kp = tc->Kp;
@@ -1368,6 +1385,7 @@ int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_
   gp.tau = d_thr;
   gp.tasks = d_tasks;
   gp.ntasks = d_ntasks;
+  gp.next_task = d_next_task;
   gp.pool = d_pool;
   gp.pool_cnt = d_pool_cnt;
   gp.pool_cap = pool_cap;
@@ -1380,6 +1398,7 @@ int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_
   FV_TRY(make_tmap(&tmA, tc->bf16, const_cast<uint16_t*>(d_A), a_rows, Kp, 128));
   FV_TRY(make_tmap(&tmB, tc->bf16, tc->half.p, tc->n, Kp, TILE_N));
   FV_CUDA(cudaMemsetAsync(gp.err, 0, sizeof(int), ctx->stream));
+  FV_CUDA(cudaMemsetAsync(d_next_task, 0, sizeof(unsigned int), ctx->stream));
   void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams) = gemm_topk_kernel<2, 2, true, true>;
   FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(t.smem)));
   kern<<<ctx->sm_count, NTHREADS, t.smem, ctx->stream>>>(tmA, tmB, gp);

@@ -1522,7 +1522,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       ctx->stats.launches += 2;
       FV_CUDA(cudaGetLastError());
       int g0 = 0;
-      FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, nullptr, tasks, ntasks, nullptr, pool_cnt, 0, nullptr, nullptr, &g0,
+      FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, nullptr, tasks, ntasks, ntasks + 1, nullptr, pool_cnt, 0, nullptr, nullptr, &g0,
                           ctx->scratch[6].as<float>(), task_moff, task_rows));
       // bounds looked at per query: room for twice the 8-row minima of the rows the bound pass aims at
       int vcap = 2048;
@@ -1590,7 +1590,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       FV_CUDA(cudaGetLastError());
       stage_mark(ctx);  // 2
       FV_CUDA(cudaMemsetAsync(dropped, 0, nq * sizeof(uint32_t), ctx->stream));
-      FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, thr, tasks, ntasks, ctx->scratch[15].as<u64>(), pool_cnt,
+      FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, thr, tasks, ntasks, ntasks + 1, ctx->scratch[15].as<u64>(), pool_cnt,
                           pool_cap, g_q, dropped, &tc_grid));
       stage_mark(ctx);  // 3
       ra.pool = ctx->scratch[15].as<u64>();
