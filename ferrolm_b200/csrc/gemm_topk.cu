@@ -263,7 +263,10 @@ struct GemmParams {
   unsigned int* ccnt;    // [grid * segmax][LISTS] entries appended (may exceed ccap: overflow)
   int ccap;
   // task mode (TASKS): the work is a table of (A tile, run of B units) pairs instead of the tiling above
-  const uint4* tasks;          // x: first operand row of the 256-row A tile, y: first B row, z: B units of 256 rows, w: valid B rows
+  // x: first operand row of the 256-row A tile; y: first B row of the task; z: its B units of 256 rows (low 16 bits)
+  // and the number of the first one within the run of B rows the task is a segment of (high 16 bits: survivors and
+  // the valid-row test count rows from the start of that run); w: valid B rows of the run
+  const uint4* tasks;
   const uint32_t* ntasks;      // device word: number of tasks
   unsigned int* next_task;     // device word, zero at launch: the next task nobody has taken yet
   u64* pool;                   // [grid][pool_cap] survivors: (A row << 32) | B row relative to y
@@ -445,7 +448,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           a_row0 = int(t.x);
           b_row0 = int(t.y);
           nt0 = 0;
-          nt1 = int(t.z);
+          nt1 = int(t.z & 0xFFFFu);
         } else {
           const int part = g / p.MT, mt = g - part * p.MT;
           nt0 = part * p.cpn;
@@ -497,7 +500,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         int nt0, nt1;
         if (TASKS) {
           nt0 = 0;
-          nt1 = int(p.tasks[g].z);
+          nt1 = int(p.tasks[g].z & 0xFFFFu);
         } else {
           const int part = g / p.MT;
           nt0 = part * p.cpn;
@@ -566,19 +569,21 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     const int col0 = MH == 2 ? (sub >> 1) * NCOL : sub * NCOL;
     uint32_t n_rows = uint32_t(p.n);
     uint32_t a_row = 0;  // task mode: this thread's operand row
+    uint32_t unit0 = 0;  // task mode: number of the task's first unit within its B run
     float* mdst = nullptr;  // task mode, minima variant: where this thread's minima of the current task go
     for (int seg = 0, g = work_of(0); g < nwork && ok; g = work_of(++seg)) {
       int nt0, nt1, mt = 0;
       if (TASKS) {
         const uint4 t = p.tasks[g];
         nt0 = 0;
-        nt1 = int(t.z);
+        nt1 = int(t.z & 0xFFFFu);
+        unit0 = t.z >> 16;
         n_rows = t.w;  // rows of this task's B run; the rest of its last unit belongs to someone else
         a_row = t.x + uint32_t((MH == 2 ? grp * 128 : 0) + quad * 32 + lane);
         if (p.minima) {
           const uint32_t moff = p.task_moff[g];
           const uint32_t rt = a_row - t.x;
-          mdst = (moff != 0xFFFFFFFFu && rt < p.task_rows[g]) ? p.minima + size_t(moff) + size_t(rt) * t.z * 32 : nullptr;
+          mdst = (moff != 0xFFFFFFFFu && rt < p.task_rows[g]) ? p.minima + size_t(moff) + size_t(rt) * (t.z & 0xFFFFu) * 32 : nullptr;
         }
       } else {
         const int part = g / p.MT;
@@ -604,7 +609,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         ok = mbar_wait(&bars->tfull[slot], uint32_t(job >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t row_base = uint32_t(nt) * TILE_N + col0;
+        const uint32_t row_base = (unit0 + uint32_t(nt)) * TILE_N + col0;
         const uint32_t t_addr = tmem_base + lane_addr + uint32_t(slot * TILE_N + col0);
         if (THRESH) {
           // Threshold mode.  The accumulator IS the score (the norm step and the scaled query side put

@@ -672,6 +672,8 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   si.roff8 = ix->recon_valid && ix->recon ? ix->roff8.as<uint32_t>() : nullptr;
   si.cen_norm2_max = ix->cen_norm2_max;
   si.code_norm2_max = ix->code_norm2_max;
+  si.max_list_rows = 0;
+  for (size_t l = 0; l < ix->nlist; ++l) si.max_list_rows = std::max(si.max_list_rows, ix->h_off[l + 1] - ix->h_off[l]);
   si.survivor_slots = ix->survivor_slots;
   fv::ScanOut so{};
   so.keys = ctx->scratch[1].as<u64>();

@@ -769,6 +769,7 @@ __global__ void __launch_bounds__(128) bound_select_kernel(const float* __restri
 // One warp per query collects those bounds over its pairs; their keep-th smallest is a distance that at least `keep`
 // different rows of the query's probed lists do not exceed.
 __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __restrict__ minima, const uint4* __restrict__ tasks,
+                                                              const uint32_t* __restrict__ tile_task0,
                                                               const uint32_t* __restrict__ task_moff,
                                                               const uint32_t* __restrict__ task_rows,
                                                               const float* __restrict__ add, const uint32_t* __restrict__ q_rows,
@@ -783,34 +784,34 @@ __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __res
   int n = 0, finite = 0;
   for (int s0 = 0; s0 < np && n < vcap; s0 += 32) {
     // lane i looks up pair s0 + i (one round of dependent loads for 32 pairs instead of one per pair) ...
-    uint32_t my_off = 0xFFFFFFFFu;
-    int my_cnt = 0;
+    uint32_t my_t0 = 0, my_t1 = 0, my_rt = 0;
     float my_add = 0.f;
     if (s0 + lane < np) {
       const uint32_t arow = q_rows[q * size_t(q_slots) + s0 + lane];
-      const uint32_t t = arow >> 8, rt = arow & 255u;
-      const uint32_t moff = task_moff[t];
-      if (moff != 0xFFFFFFFFu && rt < task_rows[t]) {
-        my_cnt = int(tasks[t].z) * 32;
-        my_off = moff + rt * uint32_t(my_cnt);
-        my_add = add[arow];
-      }
+      my_rt = arow & 255u;
+      my_t0 = tile_task0[arow >> 8];
+      my_t1 = tile_task0[(arow >> 8) + 1];
+      my_add = add[arow];
     }
-    // ... and the warp copies their minima one pair after the other
+    // ... and the warp copies their minima, one pair and one of its tile's tasks (list segments) after the other
     const int np32 = min(32, np - s0);
     for (int j = 0; j < np32 && n < vcap; ++j) {
-      const uint32_t off = __shfl_sync(FV_FULL, my_off, j);
-      const int cnt = __shfl_sync(FV_FULL, my_cnt, j);
+      const uint32_t t0 = __shfl_sync(FV_FULL, my_t0, j), t1 = __shfl_sync(FV_FULL, my_t1, j);
+      const uint32_t rt = __shfl_sync(FV_FULL, my_rt, j);
       const float ad = __shfl_sync(FV_FULL, my_add, j);
-      if (off == 0xFFFFFFFFu) continue;
-      const float* src = minima + size_t(off);
-      const int room = min(cnt, vcap - n);
-      for (int i = lane; i < room; i += 32) {
-        const uint32_t b = order_bits(__fadd_ru(src[i], ad));  // rounded up: still an upper bound
-        v[n + i] = b;
-        finite += b < INF_BITS ? 1 : 0;
+      for (uint32_t t = t0; t < t1 && n < vcap; ++t) {
+        const uint32_t moff = task_moff[t];
+        if (moff == 0xFFFFFFFFu || rt >= task_rows[t]) continue;
+        const int cnt = int(tasks[t].z & 0xFFFFu) * 32;
+        const float* src = minima + size_t(moff) + size_t(rt) * cnt;
+        const int room = min(cnt, vcap - n);
+        for (int i = lane; i < room; i += 32) {
+          const uint32_t b = order_bits(__fadd_ru(src[i], ad));  // rounded up: still an upper bound
+          v[n + i] = b;
+          finite += b < INF_BITS ? 1 : 0;
+        }
+        n += room;
       }
-      n += room;
     }
   }
   __syncwarp();
@@ -984,67 +985,84 @@ int build_reconstruction(fv_ctx* ctx, int metric, int pd, int m, int dsub, const
   return FV_OK;
 }
 
-// One block: the tasks of the tensor-core pass.  A list with n pairs and len rows gives ceil(n / 256) tasks, each
-// 256 gathered operand rows against all of the list's rows; a_off[l] is the list's first gathered row.
-// Lists are walked in `order` (longest first), so the tasks come out sorted by decreasing length and dealing them
-// round-robin to the persistent CTAs balances the load.
+// One block: the tasks of the tensor-core pass.  The n pairs of a list with len rows fill ceil(n / 256) operand tiles
+// of 256 gathered rows (a_off[l] is the list's first gathered row), and every tile meets the list's rows in segments
+// of at most TC_SEG_UNITS units of 256 rows: one task per (tile, segment), so that no task is longer than a segment
+// and a few very long lists cannot hold up the CTAs that drew them.  A tile's tasks are consecutive;
+// tile_task0[tile] is the first (and tile_task0[tiles] the task count).  Lists are walked in `order` (longest
+// first), so the long tasks are drawn first.
+// A task is {first operand row, first side row of the segment, units in the segment | first unit << 16, list length}.
+static constexpr uint32_t TC_SEG_UNITS = 8;
+
 __global__ void __launch_bounds__(1024) tc_tasks_kernel(const uint32_t* __restrict__ pair_off,
                                                         const uint32_t* __restrict__ list_off,
                                                         const uint32_t* __restrict__ roff8,
                                                         const uint32_t* __restrict__ order, size_t nlist,
                                                         uint4* __restrict__ tasks, uint32_t* __restrict__ a_off,
+                                                        uint32_t* __restrict__ tile_task0, uint32_t max_tasks,
                                                         uint32_t* __restrict__ ntasks, unsigned long long* __restrict__ rows,
                                                         uint32_t* __restrict__ task_moff, uint32_t* __restrict__ task_rows,
                                                         uint32_t minima_cap) {
-  __shared__ uint32_t st[1024];
+  __shared__ uint32_t st[1024], sl[1024];
   __shared__ unsigned long long sm8[1024];  // minima variant: floats of minima the tasks before a thread's need
   const int tid = threadIdx.x;
   const size_t per = (nlist + 1023) / 1024;
   const size_t l0 = min(nlist, size_t(tid) * per), l1 = min(nlist, l0 + per);
-  auto tasks_of = [&](size_t l) {
-    const uint32_t n = pair_off[l + 1] - pair_off[l], len = list_off[l + 1] - list_off[l];
-    return (n && len) ? (n + 255u) / 256u : 0u;
-  };
-  uint32_t nt = 0;
+  uint32_t nt = 0, ntl = 0;  // tasks, tiles
   unsigned long long nr = 0, nm = 0;
   for (size_t o = l0; o < l1; ++o) {
     const size_t l = order[o];
     const uint32_t n = pair_off[l + 1] - pair_off[l], len = list_off[l + 1] - list_off[l];
-    nt += tasks_of(l);
+    if (!n || !len) continue;
+    const uint32_t tiles = (n + 255u) / 256u, units = (len + 255u) / 256u;
+    ntl += tiles;
+    nt += tiles * ((units + TC_SEG_UNITS - 1) / TC_SEG_UNITS);
     nr += (unsigned long long)n * len;
-    if (len) nm += (unsigned long long)n * ((len + 255u) / 256u) * 32u;  // 32 minima per pair and unit
+    nm += (unsigned long long)n * units * 32u;  // 32 minima per pair and unit
   }
   st[tid] = nt;
+  sl[tid] = ntl;
   sm8[tid] = nm;
   __syncthreads();
   for (int o = 1; o < 1024; o <<= 1) {
-    const uint32_t b = tid >= o ? st[tid - o] : 0u;
+    const uint32_t b = tid >= o ? st[tid - o] : 0u, bl = tid >= o ? sl[tid - o] : 0u;
     const unsigned long long b8 = tid >= o ? sm8[tid - o] : 0ull;
     __syncthreads();
     st[tid] += b;
+    sl[tid] += bl;
     sm8[tid] += b8;
     __syncthreads();
   }
-  uint32_t bt = st[tid] - nt;
+  uint32_t bt = st[tid] - nt, bl = sl[tid] - ntl;
   unsigned long long bm = sm8[tid] - nm;
   for (size_t o = l0; o < l1; ++o) {
     const size_t l = order[o];
-    const uint32_t k = tasks_of(l), len = list_off[l + 1] - list_off[l], n = pair_off[l + 1] - pair_off[l];
-    const uint32_t units = (len + 255u) / 256u;
-    a_off[l] = bt * 256u;
-    for (uint32_t t = 0; t < k; ++t) {
-      tasks[bt + t] = make_uint4((bt + t) * 256u, roff8[l], units, len);
-      if (task_moff) {
-        const uint32_t valid = min(256u, n - t * 256u);
-        const unsigned long long need = (unsigned long long)valid * units * 32u;
-        task_rows[bt + t] = valid;
-        task_moff[bt + t] = bm + need <= minima_cap ? uint32_t(bm) : 0xFFFFFFFFu;  // beyond the buffer: this task leaves no minima
-        bm += need;
+    const uint32_t len = list_off[l + 1] - list_off[l], n = pair_off[l + 1] - pair_off[l];
+    a_off[l] = bl * 256u;
+    if (!n || !len) continue;
+    const uint32_t tiles = (n + 255u) / 256u, units = (len + 255u) / 256u;
+    const uint32_t nseg = (units + TC_SEG_UNITS - 1) / TC_SEG_UNITS;
+    for (uint32_t t = 0; t < tiles; ++t) {
+      tile_task0[bl + t] = bt;
+      const uint32_t valid = min(256u, n - t * 256u);
+      for (uint32_t sg = 0; sg < nseg; ++sg, ++bt) {
+        if (bt >= max_tasks) continue;  // cannot happen with the caller's sizing; never write past the table
+        const uint32_t u0 = sg * TC_SEG_UNITS, un = min(TC_SEG_UNITS, units - u0);
+        tasks[bt] = make_uint4((bl + t) * 256u, roff8[l] + u0 * 256u, un | (u0 << 16), len);
+        if (task_moff) {
+          const unsigned long long need = (unsigned long long)valid * un * 32u;
+          task_rows[bt] = valid;
+          task_moff[bt] = bm + need <= minima_cap ? uint32_t(bm) : 0xFFFFFFFFu;  // beyond the buffer: this task leaves no minima
+          bm += need;
+        }
       }
     }
-    bt += k;
+    bl += tiles;
   }
-  if (tid == 1023) *ntasks = st[1023];
+  if (tid == 1023) {
+    *ntasks = min(st[1023], max_tasks);
+    tile_task0[sl[1023]] = min(st[1023], max_tasks);
+  }
   if (nr && rows) atomicAdd(rows, nr);
 }
 
@@ -1450,6 +1468,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     uint16_t* qg = nullptr;
     float* thr = nullptr;
     uint32_t *g_q = nullptr, *g_l = nullptr, *a_off = nullptr, *ntasks = nullptr, *task_moff = nullptr, *task_rows = nullptr;
+    uint32_t* tile_task0 = nullptr;
     float* g_base = nullptr;
     uint4* tasks = nullptr;
     unsigned int* pool_cnt = nullptr;
@@ -1461,12 +1480,15 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       const size_t Kp = size_t(ti.Kp);
       // gathered operand rows: every pair once, every list's rows rounded up to whole 256-row tiles
       a_rows = nq * size_t(nprobe) + 256 * std::min<size_t>(ix.nlist, nq * size_t(nprobe)) + 256;
-      max_tasks = a_rows / 256;
+      const size_t max_tiles = a_rows / 256;
+      const size_t max_units = (size_t(ix.max_list_rows) + 255) / 256;
+      max_tasks = max_tiles * std::max<size_t>(1, (max_units + TC_SEG_UNITS - 1) / TC_SEG_UNITS);
+      if (max_tasks > 0x7FFFFFF0u) return fail(FV_ERR_UNSUPPORTED, "too many tasks for one tensor-core pass");
       const int q_slots = std::min(nprobe, 64);
       FV_TRY(ctx->scratch[12].reserve(a_rows * Kp * sizeof(uint16_t)));
       FV_TRY(ctx->scratch[13].reserve((a_rows * 4 + nq * size_t(q_slots + 2)) * sizeof(uint32_t) + 64));
       FV_TRY(ctx->scratch[14].reserve(max_tasks * (sizeof(uint4) + 2 * sizeof(uint32_t)) +
-                                      (ix.nlist + 8 + size_t(ctx->sm_count)) * sizeof(uint32_t)));
+                                      (ix.nlist + 8 + size_t(ctx->sm_count) + max_tiles + 2) * sizeof(uint32_t)));
       // per CTA; the fullest pool measured holds four to six times the average
       pool_cap = unsigned(std::min<size_t>(size_t(1) << 21, std::max<size_t>(65536, nq * 4096 / size_t(ctx->sm_count))));
       if (ix.survivor_slots) pool_cap = unsigned(ix.survivor_slots);
@@ -1485,6 +1507,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       a_off = task_rows + max_tasks;
       ntasks = a_off + ix.nlist;
       pool_cnt = ntasks + 8;
+      tile_task0 = pool_cnt + ctx->sm_count;
       ga.list_off = ix.list_off;
       ga.a_off = a_off;
       ga.queries = q;
@@ -1511,7 +1534,8 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       FV_TRY(ctx->scratch[6].reserve(mfloats * sizeof(float)));
       FV_CUDA(cudaMemsetAsync(q_cnt, 0, nq * sizeof(uint32_t), ctx->stream));
       tc_tasks_kernel<<<1, 1024, 0, ctx->stream>>>(pa_set.pair_off, ix.list_off, ix.roff8, ix.roff8 + ix.nlist + 1, ix.nlist, tasks,
-                                                   a_off, ntasks, nullptr, task_moff, task_rows, uint32_t(mfloats));
+                                                   a_off, tile_task0, uint32_t(max_tasks), ntasks, nullptr, task_moff, task_rows,
+                                                   uint32_t(mfloats));
       GatherArgs gb = ga;
       gb.pair_off = pa_set.pair_off;
       gb.pairs = pairs_a;
@@ -1531,7 +1555,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       const size_t ssmem = size_t(wpb) * vcap * sizeof(uint32_t);
       FV_CUDA(cudaFuncSetAttribute(tc_bound_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ssmem)));
       tc_bound_select_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, ssmem, ctx->stream>>>(
-          ctx->scratch[6].as<float>(), tasks, task_moff, task_rows, thr, q_rows, q_cnt, q_slots, vcap, keep, nq, tau_bits);
+          ctx->scratch[6].as<float>(), tasks, tile_task0, task_moff, task_rows, thr, q_rows, q_cnt, q_slots, vcap, keep, nq, tau_bits);
       ctx->stats.launches++;
       FV_CUDA(cudaGetLastError());
     } else {
@@ -1582,7 +1606,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       stage_mark(ctx);  // 3
     } else {
       tc_tasks_kernel<<<1, 1024, 0, ctx->stream>>>(pb_set.pair_off, ix.list_off, ix.roff8, ix.roff8 + ix.nlist + 1, ix.nlist, tasks,
-                                                   a_off, ntasks, d_rows + 1, nullptr, nullptr, 0u);
+                                                   a_off, tile_task0, uint32_t(max_tasks), ntasks, d_rows + 1, nullptr, nullptr, 0u);
       ga.pair_off = pb_set.pair_off;
       ga.pairs = pairs_b;
       tc_gather_kernel<<<dim3(unsigned(ix.nlist), 4), 256, 0, ctx->stream>>>(ga);

@@ -31,6 +31,7 @@ struct ScanIndex {
   const uint32_t* roff8;      // nlist + 1 row offsets, then the nlist list numbers in order of decreasing length
   float cen_norm2_max;        // largest squared centroid norm
   float code_norm2_max;       // sum over sub-quantizers of their largest squared codeword norm
+  uint32_t max_list_rows;     // length of the longest list
   size_t survivor_slots;      // survivor pool entries per CTA of the tensor-core pass (0 = sized from the batch)
 };
 
