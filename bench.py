@@ -49,6 +49,8 @@ IVF_STAGES = ["coarse cells", "query tables + bound pass", "pair bucketing + ope
               "sort + re-rank", "keys -> neighbours"]
 IVF_SHARDED_STAGES = ["coarse cells of the rank's query slice", "cell exchange (NCCL all-gather)",
                       "local search up to the shard's candidates", "candidate exchange (NCCL all-gather)", "merge"]
+IVF_GRID_STAGES = ["(no coarse step outside the local search)", "(no cell exchange)", "local search of the rank's query slice", "candidate exchange between the list shards (NCCL all-gather)",
+                   "merge + result exchange (NCCL all-gather) + unpacking"]
 FLAT_STAGES = ["query conversion", "sample pass", "main pass (tensor cores)", "exact re-rank + certificate",
                "full-precision re-run of uncertified queries", "keys -> neighbours"]
 FLAT_SHARDED_STAGES = ["local search", "result exchange (NCCL all-gather)", "merge"]
@@ -111,10 +113,18 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def workload_config(workload: str, n_gpus: int, nprobe: int, refine: int) -> dict:
+def workload_config(workload: str, n_gpus: int, nprobe: int, refine: int, list_shards: int = 0) -> dict:
+    if n_gpus == 1:
+        sharding = "single GPU"
+    elif workload == "ivfpq" and list_shards and list_shards < n_gpus:
+        sharding = (f"grid of {list_shards} list shard(s) x {n_gpus // list_shards} query slices over {n_gpus} GPUs: a rank searches its "
+                    "slice of the batch on its lists; candidates are all-gathered between list shards and merged, finished "
+                    "slices all-gathered (NCCL) so that every rank holds the whole result")
+    else:
+        sharding = (f"{'inverted lists' if workload == 'ivfpq' else 'row ranges'} over {n_gpus} GPUs, per-shard candidates "
+                    "all-gathered (NCCL) and merged")
     cfg = {"n": N_BASE, "d": DIM, "nq": NQ, "k": K, "distribution": f"clipped-integer Gaussian mixture, {CLUSTERS} clusters",
-           "sharding": (f"{'inverted lists' if workload == 'ivfpq' else 'row ranges'} over {n_gpus} GPUs, per-shard candidates "
-                        "all-gathered (NCCL) and merged") if n_gpus > 1 else "single GPU",
+           "sharding": sharding,
            "l2_note": "inputs exceed L2: 1M x 128 f32 rows (512 MB), 256 MB of 16-bit codeword rows and 164 MB of query "
                       "tables are re-read each step"}
     if workload == "ivfpq":
@@ -359,6 +369,7 @@ def run_ours(args):
     t_build = time.perf_counter()
     refine, nprobe = 0, 0
     base, empty_blob = None, None
+    list_shards = world  # IVF-PQ: list shards of the grid (the rest of the group are query slices)
     if args.big:
         # BASELINE configs[4]: 50M x 128, 4096 clusters; rows are generated on the GPU in chunks and never
         # exist on the host.  exact search: row ranges; IVF-PQ: nlist=16384, nprobe=32, sharded by list.
@@ -399,7 +410,12 @@ def run_ours(args):
         ix = fv.IvfPq.train(ctx, fv.Metric.L2, DIM, learn, fv.IvfPqParams(IVF["nlist"], IVF["m"], IVF["iters"], True, 1))
         if world > 1 and rank == 0:
             empty_blob = ix.save()  # the trained quantizers, for the unsharded copy the result is checked against
-        ix.set_shard(rank, world)
+        # the group is a grid: list_shards list shards x (world / list_shards) query slices, rank = slice * L + shard
+        list_shards = args.list_shards or 1
+        if world % list_shards:
+            raise SystemExit("--list-shards must divide the number of GPUs")
+        if list_shards > 1:
+            ix.set_shard(rank % list_shards, list_shards)
         ix.add(base)
         ix.set_scan_mode(args.scan_mode)
         refine, nprobe = IVF["refine"] if args.refine is None else args.refine, args.nprobe or IVF["nprobe"]
@@ -490,8 +506,11 @@ def run_ours(args):
     local_st = None
     if world > 1:
         with torch.cuda.stream(stream):
-            if args.workload == "ivfpq":
-                ix.search_batch(dq, K, nprobe, 0)
+            if args.workload == "ivfpq":  # the rank's slice of the batch on its lists
+                slices = world // list_shards
+                per = (NQ + slices - 1) // slices
+                s0 = (rank // list_shards) * per
+                ix.search_batch(dq[s0:min(NQ, s0 + per)].contiguous(), K, nprobe, refine if list_shards == 1 else 0)
             else:
                 ix.search_batch(dq, K)
         local_st = ctx.stats()
@@ -513,7 +532,7 @@ def run_ours(args):
         args.no_cpu = True  # the rows never exist on the host; runs at different N are compared by the checksum below
     pk = peaks()
     if args.workload == "ivfpq":
-        names = IVF_SHARDED_STAGES if world > 1 else IVF_STAGES
+        names = IVF_STAGES if world == 1 else IVF_SHARDED_STAGES if list_shards == world else IVF_GRID_STAGES
     elif args.workload == "flat":
         names = FLAT_SHARDED_STAGES if world > 1 else FLAT_STAGES
     else:
@@ -523,7 +542,7 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "data": "synthetic",
         "dtype": "f32" if args.workload == "hnsw" else "f16 operands, f32 accumulate, f32 exact re-score",
-        "config": workload_config(args.workload, world, nprobe, refine),
+        "config": workload_config(args.workload, world, nprobe, refine, list_shards),
         "e2e": {"value": NQ / (e2e_ms * 1e-3), "unit": "queries/s", "h2d_bytes_per_step": int(hq.numel() * 4),
                 "d2h_bytes_per_step": int(h_out.numel() * 4), "ms_per_step": e2e_ms},
         "gpu_launches": int(steady_launches), "clocks": clocks, "build_s": build_s,
@@ -600,7 +619,11 @@ def run_ours(args):
         threads = oracle.cores()
         nsub = min(NQ, 2000)
         if args.workload == "ivfpq":
-            if world > 1:  # the shards cannot be saved as one file: the same index once more, unsharded, on this rank
+            if world > 1 and list_shards == 1:  # every rank holds the whole index: the plain search is the check
+                blob = ix.save()
+                ref_out, ref_cnt = ix.search_batch(dq, K, nprobe, refine)
+                line["sharded_equals_unsharded"] = bool(torch.equal(ref_out, out) and torch.equal(ref_cnt, counts))
+            elif world > 1:  # the shards cannot be saved as one file: the same index once more, unsharded, on this rank
                 full = fv.IvfPq.load(ctx, empty_blob)
                 full.add(base)
                 blob = full.save()
@@ -690,6 +713,8 @@ def main():
                     help="IVF-PQ scan: 0 automatic, 1 per-query kernel, 2 list-major table scan, 3 list-major tensor-core pass")
     ap.add_argument("--nprobe", type=int, default=0, help="IVF-PQ: probed lists (default: the benchmark's 64)")
     ap.add_argument("--refine", type=int, default=None, help="IVF-PQ: re-rank factor (default: the benchmark's 10)")
+    ap.add_argument("--list-shards", type=int, default=0,
+                    help="IVF-PQ at N > 1: list shards L of the L x (N / L) grid (default 1: query slices only; N: list shards only)")
     ap.add_argument("--big", action="store_true", help="BASELINE configs[4]: 50M rows, 4096 clusters, sharded")
     args = ap.parse_args()
     global CLUSTERS

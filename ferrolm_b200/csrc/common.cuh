@@ -18,11 +18,19 @@ namespace fv {
 void set_error(const std::string& msg);
 int fail(int status, const std::string& msg);
 
+inline const char* base_name(const char* path) {  // the file's name without its directories, for error messages
+  const char* b = path;
+  for (const char* c = path; *c; ++c)
+    if (*c == '/') b = c + 1;
+  return b;
+}
+
 #define FV_CUDA(expr)                                                                          \
   do {                                                                                         \
     cudaError_t _e = (expr);                                                                   \
     if (_e != cudaSuccess)                                                                     \
-      return fv::fail(FV_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e));        \
+      return fv::fail(FV_ERR_CUDA, std::string(#expr) + " (" + fv::base_name(__FILE__) + ":" +  \
+                                       std::to_string(__LINE__) + "): " + cudaGetErrorString(_e)); \
   } while (0)
 
 #define FV_TRY(expr)            \

@@ -480,7 +480,7 @@ int fv_flat_search(fv_flat* ix, const float* query, size_t k, fv_neighbor* out, 
 // Merging per-shard results: the k_out best of nparts * k_in candidates per query.
 namespace fv {
 __global__ void merge_parts_kernel(const fv_neighbor* __restrict__ parts, const uint32_t* __restrict__ part_counts,
-                                   int nparts, size_t nq, int k_in, int k_out, u64* __restrict__ out) {
+                                   int nparts, size_t nq, int k_in, int k_out, size_t part_stride, u64* __restrict__ out) {
   unsigned char* smem_raw = dyn_smem();
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t q = size_t(blockIdx.x) * (blockDim.x >> 5) + w;
@@ -490,7 +490,7 @@ __global__ void merge_parts_kernel(const fv_neighbor* __restrict__ parts, const 
   u64 bound = FV_EMPTY_KEY;
   for (int p = 0; p < nparts; ++p) {
     const int cnt = part_counts ? int(min(part_counts[size_t(p) * nq + q], uint32_t(k_in))) : k_in;
-    const fv_neighbor* src = parts + (size_t(p) * nq + q) * size_t(k_in);
+    const fv_neighbor* src = parts + size_t(p) * part_stride + q * size_t(k_in);
     for (int i0 = 0; i0 < cnt; i0 += 32) {
       const int i = i0 + lane;
       u64 key = FV_EMPTY_KEY;
@@ -509,7 +509,8 @@ __global__ void merge_parts_kernel(const fv_neighbor* __restrict__ parts, const 
 extern "C++" {
 namespace fv {
 int merge_topk_impl(fv_ctx* ctx, const fv_neighbor* d_parts, const uint32_t* d_part_counts, size_t nparts, size_t nq,
-                    size_t k_in, size_t k_out, fv_neighbor* d_out, uint32_t* d_counts) {
+                    size_t k_in, size_t k_out, fv_neighbor* d_out, uint32_t* d_counts, size_t part_stride) {
+  if (part_stride == 0) part_stride = nq * k_in;
   FV_TRY(ctx->scratch[1].reserve(nq * k_out * sizeof(u64)));
   u64* keys = ctx->scratch[1].as<u64>();
   int wpb = 4;
@@ -518,7 +519,7 @@ int merge_topk_impl(fv_ctx* ctx, const fv_neighbor* d_parts, const uint32_t* d_p
   if (smem > 40 * 1024)
     FV_CUDA(cudaFuncSetAttribute(merge_parts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
   merge_parts_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, smem, ctx->stream>>>(d_parts, d_part_counts, int(nparts), nq,
-                                                                                     int(k_in), int(k_out), keys);
+                                                                                     int(k_in), int(k_out), part_stride, keys);
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
   return keys_to_neighbors(ctx, keys, nq, int(k_out), int(k_out), d_out, d_counts);

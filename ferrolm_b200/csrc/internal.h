@@ -72,7 +72,7 @@ struct DevBuf {
   }
 };
 
-enum { FV_NSCRATCH = 16, FV_NSTAGE = 8 };
+enum { FV_NSCRATCH = 18, FV_NSTAGE = 8 };
 
 struct fv_ctx {
   // Every entry point that uses the stream, the scratch arena, the events or the counters holds this lock for the
@@ -150,9 +150,10 @@ void stage_mark_outer(fv_ctx* ctx);  // the enclosing call's own marks
 int comm_all_gather(fv_ctx* ctx, const void* d_send, void* d_recv, size_t bytes);
 void comm_destroy(fv_ctx* ctx);
 
-// merge of per-shard result lists (flat.cu): nparts blocks of nq * k_in neighbours -> the k_out best per query
+// merge of per-shard result lists (flat.cu): nparts blocks of nq * k_in neighbours -> the k_out best per query.
+// part_stride: neighbours between the starts of two blocks (0: nq * k_in, the blocks are adjacent)
 int merge_topk_impl(fv_ctx* ctx, const fv_neighbor* d_parts, const uint32_t* d_part_counts, size_t nparts, size_t nq,
-                    size_t k_in, size_t k_out, fv_neighbor* d_out, uint32_t* d_counts);
+                    size_t k_in, size_t k_out, fv_neighbor* d_out, uint32_t* d_counts, size_t part_stride = 0);
 
 // ---- the full-precision scan (flat.cu): for every query the L best rows by (distance, id).
 // d_out_keys: nq * L keys, ascending, FV_EMPTY_KEY padded.  `prefilter_inf`: a distance must be

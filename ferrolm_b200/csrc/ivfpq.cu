@@ -1098,6 +1098,82 @@ int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float
 // the local scan, one exchange of the per-shard candidates, the merge.  Every rank ends up with the full result.
 // Stages (fv_stats.stage_ms): 0 coarse cells of this rank's query slice, 1 their exchange, 2 the local search up to
 // its candidates (bound pass, bucketing, scan, re-score, sort, re-rank), 3 the candidate exchange, 4 the merge.
+// Sharded search on a grid with more than one query slice.  Rank (slice s, list shard l) searches query slice s on
+// its lists; with L > 1 the L shards of a slice exchange their candidates (one all-gather over the whole group, each
+// rank reading the blocks of its slice) and merge them as the reference cuts (ivfpq.rs:285-296); the finished slices
+// are then gathered so that every rank holds the whole result.  Called with the context locked and its stage table
+// open (stages: 0 and 1 empty, 2 local search, 3 candidate exchange, 4 merge, result exchange and unpacking).
+static int search_grid(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,
+                       fv_neighbor* d_out, uint32_t* d_counts, int L) {
+  fv_ctx* ctx = ix->ctx;
+  const int world = ctx->comm_size, rank = ctx->comm_rank;
+  const int Q = world / L, slice = rank / L;
+  const size_t per = (nq + size_t(Q) - 1) / size_t(Q);
+  const size_t lo = std::min(nq, size_t(slice) * per), hi = std::min(nq, lo + per), ns = hi - lo;
+  const float* q = d_queries + lo * size_t(ix->dim);
+  fv::stage_mark_outer(ctx);  // 0
+  fv::stage_mark_outer(ctx);  // 1
+  // the finished slice: per x k neighbours, then per counts
+  const size_t rblk = (per * k * sizeof(fv_neighbor) + per * sizeof(uint32_t) + 15) & ~size_t(15);
+  FV_TRY(ctx->scratch[16].reserve(rblk));  // slots 16 and 17 belong to this function: the slice's result lives across the local search
+  unsigned char* res = ctx->scratch[16].as<unsigned char>();
+  fv_neighbor* res_nb = reinterpret_cast<fv_neighbor*>(res);
+  uint32_t* res_cnt = reinterpret_cast<uint32_t*>(res + per * k * sizeof(fv_neighbor));
+  const bool rerank = refine > 0 && ix->keep;
+  if (L == 1) {
+    if (ns) FV_TRY(ivfpq_search_impl(ix, q, ns, k, nprobe, refine, false, res_nb, res_cnt, nullptr, nullptr));
+    fv::stage_mark_outer(ctx);  // 2
+    fv::stage_mark_outer(ctx);  // 3
+  } else if (rerank) {
+    const size_t keep = k * refine;
+    const size_t blk = (per * keep * 12 + 15) & ~size_t(15);
+    FV_TRY(ctx->scratch[10].reserve(blk));
+    unsigned char* send = ctx->scratch[10].as<unsigned char>();
+    fv_neighbor* adc = reinterpret_cast<fv_neighbor*>(send);
+    float* exact = reinterpret_cast<float*>(send + per * keep * sizeof(fv_neighbor));
+    FV_TRY(ctx->scratch[11].reserve(per * sizeof(uint32_t)));
+    if (ns) FV_TRY(ivfpq_search_impl(ix, q, ns, keep, nprobe, 1, true, nullptr, ctx->scratch[11].as<uint32_t>(), adc, exact, nullptr));
+    fv::stage_mark_outer(ctx);  // 2
+    FV_TRY(ctx->scratch[15].reserve(size_t(world) * blk));
+    unsigned char* recv = ctx->scratch[15].as<unsigned char>();
+    FV_TRY(fv::comm_all_gather(ctx, send, recv, blk));
+    fv::stage_mark_outer(ctx);  // 3
+    const unsigned char* mine = recv + size_t(slice) * size_t(L) * blk;  // the L blocks of this slice are adjacent
+    if (ns)
+      FV_TRY(merge_refine_impl(ctx, reinterpret_cast<const fv_neighbor*>(mine),
+                               reinterpret_cast<const float*>(mine + per * keep * sizeof(fv_neighbor)), nullptr, size_t(L), ns, keep,
+                               k, blk / sizeof(fv_neighbor), blk / sizeof(float), res_nb, res_cnt));
+  } else {
+    const size_t blk = (per * k * sizeof(fv_neighbor) + 15) & ~size_t(15);
+    FV_TRY(ctx->scratch[10].reserve(blk));
+    FV_TRY(ctx->scratch[11].reserve(per * sizeof(uint32_t)));
+    fv_neighbor* part = ctx->scratch[10].as<fv_neighbor>();
+    if (ns) FV_TRY(ivfpq_search_impl(ix, q, ns, k, nprobe, 0, false, part, ctx->scratch[11].as<uint32_t>(), nullptr, nullptr, nullptr));
+    fv::stage_mark_outer(ctx);  // 2
+    FV_TRY(ctx->scratch[15].reserve(size_t(world) * blk));
+    FV_TRY(fv::comm_all_gather(ctx, part, ctx->scratch[15].p, blk));
+    fv::stage_mark_outer(ctx);  // 3
+    const fv_neighbor* mine = reinterpret_cast<const fv_neighbor*>(ctx->scratch[15].as<unsigned char>() + size_t(slice) * size_t(L) * blk);
+    if (ns) FV_TRY(fv::merge_topk_impl(ctx, mine, nullptr, size_t(L), ns, k, k, res_nb, res_cnt, blk / sizeof(fv_neighbor)));
+  }
+  // every rank gets every slice (the L shards of a slice hold the same one: shard 0's is taken)
+  FV_TRY(ctx->scratch[17].reserve(size_t(world) * rblk));
+  unsigned char* all = ctx->scratch[17].as<unsigned char>();
+  FV_TRY(fv::comm_all_gather(ctx, res, all, rblk));
+  for (int s = 0; s < Q; ++s) {
+    const size_t slo = std::min(nq, size_t(s) * per), shi = std::min(nq, slo + per);
+    if (shi == slo) continue;
+    const unsigned char* src = all + size_t(s) * size_t(L) * rblk;
+    FV_CUDA(cudaMemcpyAsync(d_out + slo * k, src, (shi - slo) * k * sizeof(fv_neighbor), cudaMemcpyDeviceToDevice, ctx->stream));
+    if (d_counts)
+      FV_CUDA(cudaMemcpyAsync(d_counts + slo, src + per * k * sizeof(fv_neighbor), (shi - slo) * sizeof(uint32_t),
+                              cudaMemcpyDeviceToDevice, ctx->stream));
+  }
+  fv::stage_mark_outer(ctx);  // 4
+  FV_CUDA(cudaStreamSynchronize(ctx->stream));
+  return FV_OK;
+}
+
 int fv_ivfpq_search_sharded_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,
                                 fv_neighbor* d_out, uint32_t* d_counts) {
   if (!ix || (nq && (!d_queries || !d_out))) return fv::fail(FV_ERR_ARG, "fv_ivfpq_search_sharded: null argument");
@@ -1105,12 +1181,17 @@ int fv_ivfpq_search_sharded_dev(fv_ivfpq* ix, const float* d_queries, size_t nq,
   fv::CtxGuard g(ctx);
   const int world = ctx->comm_size, rank = ctx->comm_rank;
   if (world <= 1) return ivfpq_search_impl(ix, d_queries, nq, k, nprobe, refine, false, d_out, d_counts, nullptr, nullptr);
-  if (ix->shard_world != world || ix->shard_rank != rank)
-    return fv::fail(FV_ERR_ARG, "the index's shard (fv_ivfpq_set_shard) does not match the context's communicator");
+  // The group is a grid of L list shards x Q query slices, rank = slice * L + list shard: L is the number of shards
+  // the index was built for (1: every rank holds all lists), Q = group size / L.
+  const int L = std::max(1, ix->shard_world);
+  if (world % L != 0 || ix->shard_rank != rank % L)
+    return fv::fail(FV_ERR_ARG, "the index's shard (fv_ivfpq_set_shard) does not fit the context's group: its shard count must "
+                                "divide the group size and its shard number equal rank % shard count");
   if (nq == 0) return FV_OK;
   if (k == 0 || nprobe == 0) return fv::fail(FV_ERR_ARG, "k and nprobe must be at least 1");
   const size_t np = std::min(nprobe, ix->nlist);
   fv::StageScope scope(ctx);  // one stage table for the whole call: the inner searches do not restart it
+  if (world / L > 1) return search_grid(ix, d_queries, nq, k, nprobe, refine, d_out, d_counts, L);
   // every shard needs the probed cells of all queries: rank r computes those of query slice r
   const size_t per = (nq + size_t(world) - 1) / size_t(world);
   const size_t lo = std::min(nq, size_t(rank) * per), hi = std::min(nq, lo + per);

@@ -214,7 +214,16 @@ void fv_free(void* p);
  * The *_sharded_dev searches are collective too: every rank calls them with the SAME queries (device pointers);
  * each searches its shard, the per-shard candidates are all-gathered over NVLink on the context's stream and merged
  * by a kernel of this library, and every rank gets the complete result.  HNSW is searched by replicas (one graph;
- * per-shard graphs would change the results): split the query batch over the ranks instead. */
+ * per-shard graphs would change the results): split the query batch over the ranks instead.
+ * For IVF-PQ the group is a grid of L list shards x Q query slices, rank = slice * L + shard, where L is the shard
+ * count the index was given (fv_ivfpq_set_shard; 1 when it was never called: every rank holds all lists) and
+ * Q = group size / L.  A rank searches its slice of the batch on its lists; the L shards of a slice exchange and merge
+ * their candidates (nothing to exchange when L = 1), and the finished slices are all-gathered.  L = group size is the
+ * plain list-sharded search (for indexes beyond one GPU's memory); L = 1 divides a batch over replicas of an index
+ * that fits every GPU, which costs the least per query.
+ * fv_stats.stage_ms after a sharded IVF-PQ search: L = group size: 0 coarse step of the rank's query slice, 1 cell
+ * exchange, 2 local search, 3 candidate exchange, 4 merge; Q > 1: 0 and 1 empty, 2 local search of the slice,
+ * 3 candidate exchange, 4 merge + result exchange + unpacking. */
 int fv_comm_unique_id(uint8_t* id128);
 int fv_ctx_comm_init(fv_ctx* ctx, const uint8_t* id128, int nranks, int rank);
 int fv_ctx_comm_rank(const fv_ctx* ctx);

@@ -54,6 +54,14 @@ def _worker(rank, world, port, tmp):
             got, gc = ShardedSearch(ctx, part, "ivfpq", world).search_batch(dq, k, nprobe, refine)
             want, wc = full.search_batch(dq, k, nprobe, refine)
             assert torch.equal(got, want) and torch.equal(gc, wc), f"IVF-PQ list shards, mode {mode} nprobe {nprobe} refine {refine}"
+    # query slices over replicas (no list shards: L = 1, Q = 2), odd batch sizes included
+    for mode in (0, 3):
+        full.set_scan_mode(mode)
+        for nq_s, nprobe, refine in [(nq, 16, 10), (nq - 1, 48, 0), (1, 4, 3), (3, 8, 0)]:
+            got, gc = full.search_sharded(dq[:nq_s].contiguous(), k, nprobe, refine)
+            want, wc = full.search_batch(dq[:nq_s].contiguous(), k, nprobe, refine)
+            assert torch.equal(got, want) and torch.equal(gc, wc), f"IVF-PQ query slices, mode {mode} nq {nq_s}"
+    full.set_scan_mode(0)
     # a small batch: every rank does its own coarse step, no cell exchange
     got, gc = part.search_sharded(dq[:50], k, 8, 4)
     want, wc = full.search_batch(dq[:50], k, 8, 4)
