@@ -72,6 +72,44 @@ __host__ __device__ __forceinline__ u64 make_key(float d, uint32_t id) {
 __host__ __device__ __forceinline__ float key_distance(u64 k) { return order_bits_to_float(uint32_t(k >> 32)); }
 __host__ __device__ __forceinline__ uint32_t key_id(u64 k) { return uint32_t(k & 0xFFFFFFFFull); }
 
+// Debug build (make EXTRA=-DFV_BOUNDS): the indices kernels gather through (probed cells, list offsets, row ids,
+// graph links, vector slots, gathered operand rows) are checked against their extents before the access.  A
+// violation is recorded in the translation unit's g_bounds words {count, site, index, extent} and the access is
+// skipped; at the end of a search the host turns a non-zero count into FV_ERR_OVERFLOW (bounds_report_*).
+// FV_BOUNDS_TU(name) goes once into every .cu with checked kernels.
+#if defined(FV_BOUNDS) && defined(__CUDACC__)
+static __device__ unsigned long long g_bounds[4];
+__device__ __forceinline__ bool idx_ok(unsigned long long i, unsigned long long n, int site) {
+  if (i < n) return true;
+  if (atomicAdd(&g_bounds[0], 1ull) == 0ull) {
+    g_bounds[1] = (unsigned long long)site;
+    g_bounds[2] = i;
+    g_bounds[3] = n;
+  }
+  return false;
+}
+#define FV_IDX_OK(i, n, site) fv::idx_ok((unsigned long long)(i), (unsigned long long)(n), site)
+#define FV_BOUNDS_TU(name)                                                                                        \
+  namespace fv {                                                                                                  \
+  int bounds_report_##name() {                                                                                    \
+    unsigned long long h[4] = {0, 0, 0, 0};                                                                       \
+    if (cudaMemcpyFromSymbol(h, g_bounds, sizeof(h)) != cudaSuccess) return fail(FV_ERR_CUDA, "bounds words");    \
+    if (h[0] == 0) return FV_OK;                                                                                  \
+    const unsigned long long z[4] = {0, 0, 0, 0};                                                                 \
+    cudaMemcpyToSymbol(g_bounds, z, sizeof(z));                                                                   \
+    return fail(FV_ERR_OVERFLOW, std::string("bounds check in " #name ": ") + std::to_string(h[0]) +              \
+                                     " violation(s); first at site " + std::to_string(h[1]) + ", index " +         \
+                                     std::to_string(h[2]) + ", extent " + std::to_string(h[3]));                   \
+  }                                                                                                               \
+  }
+#else
+#define FV_IDX_OK(i, n, site) true
+#define FV_BOUNDS_TU(name)                          \
+  namespace fv {                                    \
+  int bounds_report_##name() { return FV_OK; }      \
+  }
+#endif
+
 #ifdef __CUDACC__
 #define FV_FULL 0xFFFFFFFFu
 

@@ -25,6 +25,8 @@
 
 #include "internal.h"
 
+FV_BOUNDS_TU(hnsw)
+
 namespace fv {
 
 struct HnswDev {
@@ -174,6 +176,7 @@ __global__ void __launch_bounds__(256, 3)
         cursor = pos + 1;
         c = uint32_t(ck >> 1) & 0x7FFFFFFFu;
       }
+      if (!FV_IDX_OK(c, g.n, 1)) break;
       const uint32_t* row = g.links0 + size_t(c) * (g.m0 + 1);
       // the first 32 links are requested together with the count: one round trip, not two
       const uint32_t x_first = lane < g.m0 ? __ldg(row + 1 + lane) : 0u;
@@ -186,7 +189,7 @@ __global__ void __launch_bounds__(256, 3)
         uint32_t x = 0;
         if (i < cnt) {
           x = c0 == 0 ? x_first : row[1 + i];
-          fresh = visit(table, log2slots, x);
+          fresh = FV_IDX_OK(x, g.n, 2) && visit(table, log2slots, x);
         }
         const int nfresh = __popc(__ballot_sync(FV_FULL, fresh));
         visited += nfresh;
@@ -620,7 +623,7 @@ static int hnsw_search_dev(fv_hnsw* h, const float* d_queries, size_t nq, size_t
   ctx->stats.expansions = wk[1];
   ctx->stats.uncertified = wk[2];  // queries whose list of tied, pushed-out entries overflowed (see TIED_CAP)
   stage_end(ctx);
-  return FV_OK;
+  return bounds_report_hnsw();
 }
 
 }  // namespace fv

@@ -147,6 +147,11 @@ void stage_mark_outer(fv_ctx* ctx);  // the enclosing call's own marks
 
 // ---- exchange between the ranks of the context's group (comm.cu): every rank contributes `bytes` and receives
 // all contributions, rank-major, on the context's stream.
+// Debug build (FV_BOUNDS): FV_ERR_OVERFLOW if a checked gather index of that file's kernels was out of range since
+// the last call; always FV_OK in the normal build.  Call after the stream has been synchronized.
+int bounds_report_ivfpq_scan();
+int bounds_report_hnsw();
+
 int comm_all_gather(fv_ctx* ctx, const void* d_send, void* d_recv, size_t bytes);
 void comm_destroy(fv_ctx* ctx);
 

@@ -674,6 +674,7 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   si.code_norm2_max = ix->code_norm2_max;
   si.max_list_rows = 0;
   for (size_t l = 0; l < ix->nlist; ++l) si.max_list_rows = std::max(si.max_list_rows, ix->h_off[l + 1] - ix->h_off[l]);
+  si.nrows = ix->h_off[ix->nlist];
   si.survivor_slots = ix->survivor_slots;
   fv::ScanOut so{};
   so.keys = ctx->scratch[1].as<u64>();
@@ -685,7 +686,7 @@ static int ivfpq_search_impl(fv_ivfpq* ix, const float* d_queries, size_t nq, si
   fv::stage_mark(ctx);
   FV_CUDA(cudaStreamSynchronize(ctx->stream));
   fv::stage_end(ctx);
-  return FV_OK;
+  return fv::bounds_report_ivfpq_scan();
 }
 
 int fv_ivfpq_search_batch_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,

@@ -38,6 +38,16 @@
 
 #include "ivfpq_scan.h"
 
+FV_BOUNDS_TU(ivfpq_scan)
+
+extern "C" int fv_debug_bounds_build(void) {
+#ifdef FV_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 namespace fv {
 
 static const size_t KSUB = 256;
@@ -69,6 +79,7 @@ struct ScanArgs {
   uint32_t* out_counts;      // nq
   unsigned long long* rows_scanned;
   const uint32_t* qids;      // block b works on query qids[b] (null: query b)
+  uint32_t nlist, nrows, nvec;  // extents (lists, rows in all lists, kept vectors), for the checks of the debug build
 };
 
 // The query's part of the lookup tables for a whole batch (ivfpq.rs:236-238 inner product, :241-251 L2 with
@@ -146,8 +157,10 @@ __device__ __forceinline__ void scan_tail(const ScanArgs& a, size_t q, const u64
         }
         slot = lo;
       }
-      ex = exact_distance(a.metric, sq, a.vectors + slot * a.pd, a.pd);
-      rk = make_key(ex, id);
+      if (FV_IDX_OK(slot, a.nvec, 3)) {
+        ex = exact_distance(a.metric, sq, a.vectors + slot * a.pd, a.pd);
+        rk = make_key(ex, id);
+      }
     }
     rerank[e] = rk;
     if (a.candidates) {
@@ -254,6 +267,7 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
       const u64 c = a.cells[q * size_t(a.nprobe) + p];
       if (c == FV_EMPTY_KEY) return -1;
       if (a.shard_world > 1 && int(key_id(c) % uint32_t(a.shard_world)) != a.shard_rank) continue;
+      if (!FV_IDX_OK(key_id(c), a.nlist, 1)) continue;
       return p;
     }
     return -1;
@@ -367,7 +381,7 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
             if (__any_sync(FV_FULL, pass[i])) {
               const int r = r0 + i * 32 + lane;
               u64 key = FV_EMPTY_KEY;
-              if (pass[i]) key = make_key(d[i], __ldg(a.ids + off + r));
+              if (pass[i] && FV_IDX_OK(off + r, a.nrows, 2)) key = make_key(d[i], __ldg(a.ids + off + r));
               const bool in = key < eff;
               const unsigned hit = __ballot_sync(FV_FULL, in);
               if (hit) {
@@ -441,6 +455,7 @@ struct PairArgs {
   const u64* cells;
   size_t nq;
   int nprobe, shard_rank, shard_world;
+  uint32_t nlist;       // lists of the index (the debug build checks the probed cells against it)
   uint32_t min_rows;    // 0: every probed list this shard owns; else only the nearest ones, until they hold this many rows
   const uint32_t* list_off;
   uint32_t* pair_cnt;   // nlist (zeroed): pairs per list
@@ -461,6 +476,7 @@ __global__ void pair_kernel(PairArgs a) {
     if (c == FV_EMPTY_KEY) break;
     const uint32_t l = key_id(c);
     if (a.shard_world > 1 && int(l % uint32_t(a.shard_world)) != a.shard_rank) continue;
+    if (!FV_IDX_OK(l, a.nlist, 4)) continue;
     if (a.min_rows) {
       if (rows >= a.min_rows) break;
       rows += a.list_off[l + 1] - a.list_off[l];
@@ -715,7 +731,7 @@ __global__ void __launch_bounds__(LS_THREADS, 1) ivfpq_list_scan_kernel(ListScan
                   if (d <= tau_d && d < INFINITY && row < nrows && order_bits(d) <= tbits) {
                     const uint32_t slot = atomicAdd(a.cand_cnt + q_cur, 1u);
                     if (slot < uint32_t(a.cap))
-                      a.cand[size_t(q_cur) * a.cap + slot] = make_key(d, __ldg(a.ids + loff + r0 + row));
+                      a.cand[size_t(q_cur) * a.cap + slot] = make_key(d, __ldg(a.ids + loff + r0 + row));  // (row < len by construction)
                   }
                 }
               }
@@ -1223,6 +1239,8 @@ struct RescoreArgs {
   uint32_t* cand_cnt;
   int cap;
   const uint32_t* only;  // second round: only survivors of queries with only[q] != 0 (null: all)
+  size_t a_rows;         // extents (gathered operand rows, lists, rows in all lists), for the checks of the debug build
+  uint32_t nlist, nrows;
 };
 
 // One thread per survivor: the reference's compressed distance (ivfpq.rs:256-262, :272-276), bit for bit; kept if
@@ -1253,9 +1271,12 @@ __global__ void __launch_bounds__(128) rescore_kernel(RescoreArgs a) {
     }
     const u64 e = a.pool[size_t(lo) * a.pool_cap + (i - start[lo])];
     const uint32_t arow = uint32_t(e >> 32), row = uint32_t(e);
+    if (!FV_IDX_OK(arow, a.a_rows, 5)) continue;
     const uint32_t q = a.g_q[arow], l = a.g_l[arow];
+    if (!FV_IDX_OK(l, a.nlist, 6)) continue;
     if (a.only && !a.only[q]) continue;
     const size_t r = size_t(a.list_off[l]) + row;
+    if (!FV_IDX_OK(r, a.nrows, 7)) continue;
     const uint8_t* code = a.codes + r * a.m;
     const float* qt = a.qtab + size_t(q) * tab;
     const float* pt = a.pre ? a.pre + size_t(l) * tab : nullptr;
@@ -1332,6 +1353,7 @@ static int bucket_pairs(fv_ctx* ctx, const ScanIndex& ix, const u64* cells, size
   pa.shard_rank = ix.shard_rank;
   pa.shard_world = ix.shard_world;
   pa.min_rows = min_rows;
+  pa.nlist = uint32_t(ix.nlist);
   pa.list_off = ix.list_off;
   pa.pair_cnt = ps.pair_cnt;
   pa.cursor = ps.cursor;
@@ -1405,6 +1427,9 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
   a.refine = refine && !candidates ? 1 : 0;
   a.candidates = candidates ? 1 : 0;
   a.id_base = ix.id_base;
+  a.nlist = uint32_t(ix.nlist);
+  a.nrows = ix.nrows;
+  a.nvec = ix.owned_n;
   a.out_keys = out.keys;
   a.out_adc = out.adc;
   a.out_exact = out.exact;
@@ -1620,6 +1645,9 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       ra.pool = ctx->scratch[15].as<u64>();
       ra.pool_cnt = pool_cnt;
       ra.pool_cap = pool_cap;
+      ra.a_rows = a_rows;
+      ra.nlist = uint32_t(ix.nlist);
+      ra.nrows = ix.nrows;
       ra.npools = tc_grid;
       ra.g_q = g_q;
       ra.g_l = g_l;

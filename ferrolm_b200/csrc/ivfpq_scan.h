@@ -32,6 +32,7 @@ struct ScanIndex {
   float cen_norm2_max;        // largest squared centroid norm
   float code_norm2_max;       // sum over sub-quantizers of their largest squared codeword norm
   uint32_t max_list_rows;     // length of the longest list
+  uint32_t nrows;             // rows in all lists of this index (list_off[nlist])
   size_t survivor_slots;      // survivor pool entries per CTA of the tensor-core pass (0 = sized from the batch)
 };
 

@@ -165,6 +165,12 @@ int fv_ivfpq_set_candidate_slots(fv_ivfpq* ix, size_t slots);
  * the batch; at most 2^21).  Survivors that find the pool full are dropped and the queries they belong to re-run by
  * the per-query kernel (fv_stats.uncertified): again memory against re-runs, never results. */
 int fv_ivfpq_set_survivor_slots(fv_ivfpq* ix, size_t slots);
+/* 1 when the library was built with -DFV_BOUNDS (make EXTRA=-DFV_BOUNDS), the debug build in which the kernels check
+ * every index they gather through (probed cells, row ids, vector slots, graph links) against its extent, skip an
+ * access that would leave it and make the search return FV_ERR_OVERFLOW with the first offending site, index and
+ * extent in fv_last_error; 0 for the normal build, which trusts its inputs (the *_cells_dev entry points in
+ * particular take the probed cells from the caller unchecked). */
+int fv_debug_bounds_build(void);
 size_t fv_ivfpq_save_size(const fv_ivfpq* ix);
 int fv_ivfpq_save(const fv_ivfpq* ix, uint8_t* buf, size_t cap, size_t* written);      /* save :332 ("FLIVFPQ1") */
 int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out);      /* load :354 */
