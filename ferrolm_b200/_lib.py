@@ -98,6 +98,7 @@ SIGNATURES = {
     "fv_ivfpq_set_candidate_slots": (_i, [_vp, _sz]),
     "fv_ivfpq_set_survivor_slots": (_i, [_vp, _sz]),
     "fv_debug_bounds_build": (_i, []),
+    "fv_debug_tc_fault": (_i, [C.c_longlong, _i]),
     "fv_ivfpq_coarse_dev": (_i, [_vp, _vp, _sz, _sz, _vp]),
     "fv_ivfpq_search_batch_cells_dev": (_i, [_vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp, _vp]),
     "fv_ivfpq_search_candidates_cells_dev": (_i, [_vp, _vp, _sz, _sz, _sz, _vp, _vp, _vp, _vp]),

@@ -31,6 +31,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -79,10 +80,16 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// What a waiting thread needs to give up: the CTA's abort flag (shared memory) and the launch's limit in cycles.
+struct AbortCtl {
+  volatile int* flag;
+  long long limit;
+};
+
 // Bounded wait.  Returns false when the limit ran out or another thread already gave up.
 // Every failed probe reads shared memory, and the tensor cores fetch their operands through the same port:
 // sixteen warps probing back to back slow the MMAs measurably, so a waiting thread sleeps between probes.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned sleep_ns = 64) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtl& abort_flag, unsigned sleep_ns = 64) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
@@ -90,9 +97,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (sleep_ns) __nanosleep(sleep_ns);
       if (mbar_try(bar, parity)) return true;
     }
-    if (*abort_flag) return false;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-      *abort_flag = 1;
+    if (*abort_flag.flag) return false;
+    if (clock64() - t0 > abort_flag.limit) {
+      *abort_flag.flag = 1;
       return false;
     }
   }
@@ -257,6 +264,8 @@ struct GemmParams {
   uint32_t idesc;
   u64* cand;           // [grid * segmax][LISTS][KP]  (list mode: output)
   int* err;            // set to 1 when a bounded wait ran out
+  long long wait_limit;  // cycles a thread waits on one barrier before the kernel gives up (WAIT_LIMIT_CYCLES)
+  int fault_skip_unit;   // test hook, -1 = off: the producer of work item 0 leaves out the loads of this unit of it
   // threshold mode: per-query bounds from the sample pass, and the candidate buffers they fill
   const float* tau;      // [MT * 128 * MH]
   u64* cbuf;             // [grid * segmax][LISTS][ccap] (score, row) keys: one private list per epilogue thread and segment
@@ -380,7 +389,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   unsigned char* sE = sB + size_t(p.nstage) * B_STAGE_BYTES;           // [ext_ring] norm-step tiles of 8 KB
   unsigned char* scratch = sE + size_t(p.ext_ring) * B_EXT_BYTES;      // list mode: 16 epilogue warps x 2 KB
   Barriers* bars = reinterpret_cast<Barriers*>(scratch + p.scratch_bytes);
-  volatile int* abort_flag = &bars->abort_flag;
+  const AbortCtl abort_flag{&bars->abort_flag, p.wait_limit};
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -470,6 +479,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             // ext_ring units later; the stage acquired just above was last read by a unit at most
             // ceil(nstage / KB) back, and the commit that freed it also covers every norm step issued before it.
             const bool with_ext = kb == 0 && p.has_ext;
+            // (test hook: the stage is never posted, its consumer waits until the limit and the kernel gives up)
+            if (p.fault_skip_unit >= 0 && g == 0 && nt == nt0 + p.fault_skip_unit) continue;
             mbar_expect_tx(&bars->full[s], uint32_t(B_STAGE_BYTES + (with_ext ? B_EXT_BYTES : 0)));
             // first B row of the unit (task mode: a multiple of 8, which keeps the norm tile's swizzle image in step)
             const size_t brow = size_t(b_row0) + size_t(nt) * TILE_N;
@@ -792,7 +803,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 1);
+  if (threadIdx.x == 0 && *abort_flag.flag) atomicExch(p.err, 1);
   if (TASKS && threadIdx.x == 0) p.pool_cnt[blockIdx.x] = bars->pool_pos;
   if (warp == 1) {
     tc_fence_after();
@@ -1331,7 +1342,19 @@ static int launch_gemm(fv_ctx* ctx, const Tiling& t, const CUtensorMap& tmA, con
   return FV_OK;
 }
 
+// Test hook (fv_debug_tc_fault): the next launch of the kernel, once, runs with this wait limit and with one unit's
+// loads left out, so that the give-up path of the bounded waits can be exercised without any fault on the device.
+static std::atomic<long long> g_test_wait_limit{0};
+static std::atomic<int> g_test_skip_unit{-1};
+
 static void fill_params(GemmParams* g, const Tiling& t, size_t rows, size_t nq, int scratch_bytes) {
+  g->wait_limit = WAIT_LIMIT_CYCLES;
+  g->fault_skip_unit = -1;
+  const long long test_limit = g_test_wait_limit.exchange(0);
+  if (test_limit > 0) {
+    g->wait_limit = test_limit;
+    g->fault_skip_unit = g_test_skip_unit.exchange(-1);
+  }
   g->n = int(rows);
   g->nq = int(nq);
   g->KB = t.KB;
@@ -1402,7 +1425,6 @@ int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_
   CUtensorMap tmA, tmB;
   FV_TRY(make_tmap(&tmA, tc->bf16, const_cast<uint16_t*>(d_A), a_rows, Kp, 128));
   FV_TRY(make_tmap(&tmB, tc->bf16, tc->half.p, tc->n, Kp, TILE_N));
-  FV_CUDA(cudaMemsetAsync(gp.err, 0, sizeof(int), ctx->stream));
   FV_CUDA(cudaMemsetAsync(d_next_task, 0, sizeof(unsigned int), ctx->stream));
   void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams) = gemm_topk_kernel<2, 2, true, true>;
   FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(t.smem)));
@@ -1542,3 +1564,14 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
 }
 
 }  // namespace fv
+
+// Test hook: arms the next launch of the tensor-core kernel (once) with a short wait limit, in cycles, and makes the
+// producer of work item 0 leave out the loads of unit `skip_unit` of it: the consumer of that stage waits until
+// the limit, the kernel sets its error word, frees its tensor memory and returns, and the search that launched it
+// fails with FV_ERR_TIMEOUT.  Nothing on the device faults or spins without bound.  (0, -1) disarms.
+extern "C" int fv_debug_tc_fault(long long wait_limit_cycles, int skip_unit) {
+  if (wait_limit_cycles < 0 || skip_unit < -1) return fv::fail(FV_ERR_ARG, "fv_debug_tc_fault: bad argument");
+  fv::g_test_skip_unit.store(skip_unit);
+  fv::g_test_wait_limit.store(wait_limit_cycles);
+  return FV_OK;
+}

@@ -191,7 +191,8 @@ struct TcInfo {
   bool not_finite;
 };
 void tc_info(const TcSide* tc, TcInfo* out);
-// Device word that a bounded wait inside the kernel sets when it runs out (zeroed by tc_list_pass).
+// Device word that a bounded wait inside the kernel sets when it runs out.  tc_list_pass does not clear it: a caller
+// that launches several passes clears it once (cudaMemsetAsync on the context's stream) and reads it after the last.
 int* tc_error_word(TcSide* tc);
 // nq x pd f32 rows -> nq x Kp operand rows in the side's 16-bit type, scaled by -2 (L2) or -1; squared norms (0 for
 // inner product) to d_qn2.

@@ -1502,6 +1502,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     GatherArgs ga{};
     if (path == LIST_TENSOR) {
       tc_info(ix.recon, &ti);
+      FV_CUDA(cudaMemsetAsync(tc_error_word(ix.recon), 0, sizeof(int), ctx->stream));  // read after the last pass
       const size_t Kp = size_t(ti.Kp);
       // gathered operand rows: every pair once, every list's rows rounded up to whole 256-row tiles
       a_rows = nq * size_t(nprobe) + 256 * std::min<size_t>(ix.nlist, nq * size_t(nprobe)) + 256;

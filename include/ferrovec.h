@@ -171,6 +171,12 @@ int fv_ivfpq_set_survivor_slots(fv_ivfpq* ix, size_t slots);
  * extent in fv_last_error; 0 for the normal build, which trusts its inputs (the *_cells_dev entry points in
  * particular take the probed cells from the caller unchecked). */
 int fv_debug_bounds_build(void);
+/* Test hook for the give-up path of the bounded waits in the tensor-core kernel: arms the NEXT launch of that kernel,
+ * once, with a wait limit of wait_limit_cycles and makes one CTA's producer leave out the loads of unit skip_unit of
+ * its first work item.  The consumer of that stage waits until the limit, the kernel sets its error word, frees its
+ * tensor memory and returns, and the search that launched it fails with FV_ERR_TIMEOUT; the context stays usable.
+ * Nothing on the device faults or spins without bound.  (0, -1) disarms.  Not for production callers. */
+int fv_debug_tc_fault(long long wait_limit_cycles, int skip_unit);
 size_t fv_ivfpq_save_size(const fv_ivfpq* ix);
 int fv_ivfpq_save(const fv_ivfpq* ix, uint8_t* buf, size_t cap, size_t* written);      /* save :332 ("FLIVFPQ1") */
 int fv_ivfpq_load(fv_ctx* ctx, const uint8_t* bytes, size_t len, fv_ivfpq** out);      /* load :354 */
