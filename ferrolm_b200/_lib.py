@@ -94,6 +94,10 @@ SIGNATURES = {
     "fv_ivfpq_set_shard": (_i, [_vp, _i, _i]),
     "fv_ivfpq_search_candidates_dev": (_i, [_vp, _vp, _sz, _sz, _sz, _vp, _vp, _vp]),
     "fv_ivfpq_nlist": (_sz, [_vp]),
+    "fv_ivfpq_dim": (_u32, [_vp]),
+    "fv_ivfpq_metric": (_i, [_vp]),
+    "fv_hnsw_dim": (_u32, [_vp]),
+    "fv_hnsw_metric": (_i, [_vp]),
     "fv_ivfpq_set_scan_mode": (_i, [_vp, _i]),
     "fv_ivfpq_set_candidate_slots": (_i, [_vp, _sz]),
     "fv_ivfpq_set_survivor_slots": (_i, [_vp, _sz]),

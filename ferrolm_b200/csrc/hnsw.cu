@@ -701,6 +701,8 @@ void fv_hnsw_free(fv_hnsw* ix) {
 }
 
 size_t fv_hnsw_len(const fv_hnsw* ix) { return ix ? ix->n() : 0; }
+uint32_t fv_hnsw_dim(const fv_hnsw* ix) { return ix ? ix->dim : 0; }
+int fv_hnsw_metric(const fv_hnsw* ix) { return ix ? ix->metric : -1; }
 
 size_t fv_hnsw_reachable(const fv_hnsw* ix) {  // hnsw.rs:367-385
   if (!ix || ix->n() == 0) return 0;

@@ -697,6 +697,8 @@ int fv_ivfpq_search_batch_dev(fv_ivfpq* ix, const float* d_queries, size_t nq, s
 }
 
 size_t fv_ivfpq_nlist(const fv_ivfpq* ix) { return ix ? ix->nlist : 0; }
+uint32_t fv_ivfpq_dim(const fv_ivfpq* ix) { return ix ? uint32_t(ix->dim) : 0; }
+int fv_ivfpq_metric(const fv_ivfpq* ix) { return ix ? ix->metric : -1; }
 
 int fv_ivfpq_set_candidate_slots(fv_ivfpq* ix, size_t slots) {
   if (!ix || slots > 4096) return fv::fail(FV_ERR_ARG, "fv_ivfpq_set_candidate_slots: at most 4096 slots");

@@ -404,8 +404,7 @@ class IvfPq:
         buf = np.frombuffer(data, dtype=np.uint8)
         h = C.c_void_p()
         check(lib().fv_ivfpq_load(ctx._h, buf.ctypes.data_as(C.c_void_p), buf.size, C.byref(h)))
-        dim = int(np.frombuffer(data[12:16], dtype="<u4")[0])
-        return IvfPq(ctx, h, dim)
+        return IvfPq(ctx, h, int(lib().fv_ivfpq_dim(h)))
 
 
 @dataclass
@@ -472,8 +471,7 @@ class Hnsw:
         buf = np.frombuffer(data, dtype=np.uint8)
         h = C.c_void_p()
         check(lib().fv_hnsw_load(ctx._h, buf.ctypes.data_as(C.c_void_p), buf.size, C.byref(h)))
-        dim = int(np.frombuffer(data[12:16], dtype="<u4")[0])
-        return Hnsw(ctx, h, dim)
+        return Hnsw(ctx, h, int(lib().fv_hnsw_dim(h)))
 
 
 def kmeans_train(ctx: Context, data, k: int, iters: int, seed: int) -> np.ndarray:

@@ -123,6 +123,8 @@ int fv_ivfpq_add_dev(fv_ivfpq* ix, const float* d_vectors, size_t n);
 size_t fv_ivfpq_len(const fv_ivfpq* ix);                                              /* len   :128 */
 size_t fv_ivfpq_bytes_per_vector(const fv_ivfpq* ix);                                 /* bytes_per_vector :137 */
 size_t fv_ivfpq_nlist(const fv_ivfpq* ix);                                            /* field nlist :33 */
+uint32_t fv_ivfpq_dim(const fv_ivfpq* ix);                                            /* field dim   :31 */
+int fv_ivfpq_metric(const fv_ivfpq* ix);                                              /* field metric :30 (fv_metric) */
 int fv_ivfpq_search(fv_ivfpq* ix, const float* query, size_t k, size_t nprobe, size_t refine,
                     fv_neighbor* out, uint32_t* count);                               /* search :225 */
 int fv_ivfpq_search_batch(fv_ivfpq* ix, const float* queries, size_t nq, size_t k, size_t nprobe, size_t refine,
@@ -193,6 +195,8 @@ int fv_hnsw_build(fv_ctx* ctx, int metric, uint32_t dim, const float* vectors, s
                   const fv_hnsw_params* p, int threads, fv_hnsw** out);                /* build :85 */
 void fv_hnsw_free(fv_hnsw* ix);
 size_t fv_hnsw_len(const fv_hnsw* ix);                                                /* len :131 */
+uint32_t fv_hnsw_dim(const fv_hnsw* ix);                                              /* field dim :44 */
+int fv_hnsw_metric(const fv_hnsw* ix);                                                /* field metric :43 (fv_metric) */
 size_t fv_hnsw_reachable(const fv_hnsw* ix);                                          /* reachable :367 */
 double fv_hnsw_mean_degree(const fv_hnsw* ix);                                        /* mean_degree :388 */
 int fv_hnsw_search(fv_hnsw* ix, const float* query, size_t k, size_t ef, fv_neighbor* out, uint32_t* count); /* :323 */
