@@ -283,7 +283,7 @@ def also_section(fv, oracle, ctx, stream, ix, base, queries, dq, pk, nprobe, ref
     ix.set_scan_mode(0)
     out["ivfpq_scans"] = scans
     # HNSW (BASELINE configs[3]) on a 200,000-node graph built by the oracle, efSearch 64
-    hn, hq = 200_000, 2_000
+    hn, hq = 200_000, NQ
     oh = oracle.Hnsw.build(oracle.L2, DIM, base[:hn], HNSW["m"], HNSW["ef_construction"], 1, threads)
     h = fv.Hnsw.load(ctx, oh.save())
     dqh = dq[:hq].contiguous()
@@ -565,17 +565,25 @@ def run_ours(args):
         tensor = rows_list > 0 and surv > 0
         alg = (rows_list if rows_list else rows) * IVF["m"]
         ach = alg / (kms * 1e-3) / 1e9
-        line["roofline"] = {"kernel": ("gemm_topk_kernel (task mode)" if tensor else
-                                       "ivfpq_list_scan_kernel" if rows_list else "ivfpq_scan_kernel"),
-                            "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
-                            "traffic": None, "peak_source": pk["source"], "algorithmic_bytes_per_launch": int(alg), "kernel_ms": kms}
         if tensor:
-            tf = 2.0 * (rows_list if rows_list else rows) * DIM / (kms * 1e-3) / 1e12
-            line["roofline"].update({
-                "tensor_tflops": tf, "tensor_frac_of_measured_peak": tf / pk["tflops"], "survivors_rescored": int(surv),
-                "how_to_read": "code bytes are not read per (query, probe) by this kernel: `achieved` is the equivalent scan "
-                               "throughput (code bytes of all pairs / kernel time) and may pass the HBM peak; tensor_tflops "
-                               "= 2 * pairs' rows * d / kernel time"})
+            # The tensor-core pass scores every (pair, row) as a 16-bit GEMM: 2 * rows * d flop of useful work per
+            # launch (padding of the 256 x 256 tiles not counted).  The code bytes of a list are not read per pair
+            # by this kernel, so its bound is the tensor pipe, not HBM; the equivalent scan rate (code bytes of all
+            # pairs / kernel time) is given beside it for comparison with the scanning kernels.
+            flops = 2.0 * rows_list * DIM
+            tf = flops / (kms * 1e-3) / 1e12
+            line["roofline"] = {"kernel": "gemm_topk_kernel (task mode)", "bound": "tensor", "achieved": tf, "peak": pk["tflops"],
+                                "unit": "TFLOP/s", "frac": tf / pk["tflops"], "traffic": None, "peak_source": pk["source"],
+                                "algorithmic_flops_per_launch": flops, "kernel_ms": kms,
+                                "frac_of_sustained_peak": tf / pk["tflops_sustained"],
+                                "survivors_rescored": int(surv), "equivalent_scan_gbs": ach,
+                                "equivalent_scan_note": "code bytes of all (query, probe) pairs / kernel time: what a kernel that "
+                                                        "reads the codes per pair would have to sustain; not DRAM traffic"}
+        else:
+            line["roofline"] = {"kernel": "ivfpq_list_scan_kernel" if rows_list else "ivfpq_scan_kernel",
+                                "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
+                                "traffic": None, "peak_source": pk["source"], "algorithmic_bytes_per_launch": int(alg),
+                                "kernel_ms": kms}
     elif args.workload == "flat":
         kms = float(src["stage_ms"][2])
         alg = 2.0 * NQ * (hi - lo) * DIM
@@ -604,10 +612,13 @@ def run_ours(args):
             raise KeyError("no capture at this size")
         with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
             tr = json.load(f)[line["roofline"]["kernel"]]
+        nq_local = NQ
+        if args.workload == "ivfpq" and world > 1:
+            nq_local = (NQ + world // list_shards - 1) // (world // list_shards)
         if "bytes_per_launch" in tr:
-            line["roofline"]["traffic"] = tr["bytes_per_launch"] * (hi - lo) / 1_000_000
+            line["roofline"]["traffic"] = tr["bytes_per_launch"] * (hi - lo) / 1_000_000 + tr.get("bytes_per_query", 0.0) * nq_local
         else:
-            line["roofline"]["traffic"] = tr["bytes_per_query"] * NQ / (world if args.workload == "ivfpq" else 1)
+            line["roofline"]["traffic"] = tr["bytes_per_query"] * nq_local / (list_shards if args.workload == "ivfpq" and world > 1 else 1)
         line["roofline"]["traffic_note"] = "ncu dram bytes of a smaller capture, scaled: " + tr["scaling"]
     except Exception:
         pass

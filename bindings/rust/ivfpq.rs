@@ -20,7 +20,7 @@ pub struct IvfPqParams {
 pub struct IvfPq {
     pub metric: Metric,
     pub dim: usize,
-    pub nlist: usize,
+    nlist: usize,
     h: *mut c_void,
 }
 

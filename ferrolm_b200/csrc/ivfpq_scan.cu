@@ -1372,7 +1372,10 @@ bool ivfpq_wants_tensor(int mode, size_t nq, size_t nprobe, size_t nlist, int sh
   if (mode == 3) return nq >= 1;
   if (mode != 0) return false;
   const size_t owned_lists = std::max<size_t>(1, nlist / size_t(std::max(1, shard_world)));
-  return nq >= 256 && nq * nprobe >= 96 * owned_lists;
+  // The tensor-core pass costs about one unit of work per (list, 256-pair tile, 256 rows) whatever the tile holds, the
+  // per-query kernel one per (pair, row): measured on 1M x 128 / 1024 lists, the pass wins from about 8 pairs per
+  // list (4 pairs per list: 0.50 against 0.46 ms; 78: 0.80 against 1.34 ms).
+  return nq >= 256 && nq * nprobe >= 24 * owned_lists;
 }
 
 // Stages (fv_stats.stage_ms) of an IVF-PQ search: 0 coarse cells (marked by the caller); 1 query tables and, on the
