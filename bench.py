@@ -577,6 +577,7 @@ def run_ours(args):
                                 "algorithmic_flops_per_launch": flops, "kernel_ms": kms,
                                 "frac_of_sustained_peak": tf / pk["tflops_sustained"],
                                 "survivors_rescored": int(surv), "equivalent_scan_gbs": ach,
+                                "equivalent_scan_frac_of_hbm_peak": ach / pk["hbm_gbs"], "algorithmic_bytes_per_launch": int(alg),
                                 "equivalent_scan_note": "code bytes of all (query, probe) pairs / kernel time: what a kernel that "
                                                         "reads the codes per pair would have to sustain; not DRAM traffic"}
         else:
