@@ -33,8 +33,6 @@
 #include <algorithm>
 #include <atomic>
 #include <cmath>
-#include <cstdio>
-#include <cstdlib>
 
 #include "internal.h"
 
@@ -1383,15 +1381,6 @@ void tc_info(const TcSide* tc, TcInfo* out) {
 int* tc_error_word(TcSide* tc) {
   RangeStats* qst = tc->stats.as<RangeStats>() + 1;
   return reinterpret_cast<int*>(reinterpret_cast<unsigned int*>(qst + 1) + 1);
-}
-
-int tc_prepare_queries(fv_ctx* ctx, TcSide* tc, int metric, const float* d_queries, size_t nq, int pd, uint16_t* d_out,
-                       float* d_qn2) {
-  RangeStats* qst = tc->stats.as<RangeStats>() + 1;
-  init_stats_kernel<<<1, 1, 0, ctx->stream>>>(qst);
-  FV_CUDA(cudaGetLastError());
-  const bool is_l2 = metric == FV_L2;
-  return convert(ctx, tc->bf16, d_queries, nq, pd, tc->Kp, d_out, d_qn2, is_l2, is_l2 ? -2.f : -1.f, qst);
 }
 
 int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_t a_rows, const float* d_thr,

@@ -194,10 +194,6 @@ void tc_info(const TcSide* tc, TcInfo* out);
 // Device word that a bounded wait inside the kernel sets when it runs out.  tc_list_pass does not clear it: a caller
 // that launches several passes clears it once (cudaMemsetAsync on the context's stream) and reads it after the last.
 int* tc_error_word(TcSide* tc);
-// nq x pd f32 rows -> nq x Kp operand rows in the side's 16-bit type, scaled by -2 (L2) or -1; squared norms (0 for
-// inner product) to d_qn2.
-int tc_prepare_queries(fv_ctx* ctx, TcSide* tc, int metric, const float* d_queries, size_t nq, int pd, uint16_t* d_out,
-                       float* d_qn2);
 // Scores the 256 operand rows of every task against its run of side rows: d_tasks[t] = {first operand row, first side
 // row (a multiple of 8), units of 256 side rows, valid side rows}.  Every (operand row, side row) whose score
 // ||b||^2 - 2<a, b> (L2; -<a, b> for inner product, operand rows being pre-scaled) is below d_thr[operand row] goes to

@@ -30,8 +30,6 @@
 //    per-query kernel.
 #include <algorithm>
 #include <cmath>
-#include <cstdio>
-#include <cstdlib>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
