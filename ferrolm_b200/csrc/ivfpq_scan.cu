@@ -1107,114 +1107,116 @@ __device__ __forceinline__ uint16_t to_operand(float x, int bf16) {
   return bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(x)) : __half_as_ushort(__float2half_rn(x));
 }
 
-// One warp per gathered row (blockIdx.x = list, blockIdx.y strides its rows): writes the pair's operand row,
-// -2 (q - centroid) for L2 or -q for inner product in the side's 16-bit type, and turns the query's bound into the
-// score threshold of that row.  With a = q - centroid (L2) the kernel's score is ||w||^2 - 2 <a, w> for the row's
-// codewords w, and |score + ||a||^2 - compressed distance| <= eps, where eps adds up
+// Eight lanes per gathered row, four rows per warp and step (blockIdx.x = list, blockIdx.y strides its rows): writes
+// the pair's operand row, -2 (q - centroid) for L2 or -q for inner product in the side's 16-bit type, and turns the
+// query's bound into the score threshold of that row.  (One warp per row spent two thirds of its instructions in
+// the single lane that works out the margin; with eight lanes per row four margins are worked out side by side.)
+// With a = q - centroid (L2) the kernel's score is ||w||^2 - 2 <a, w> for the row's codewords w, and
+// |score + ||a||^2 - compressed distance| <= eps, where eps adds up
 //   - the 16-bit score against the f32 arithmetic on (a, w): input rounding 2 u |a||w|, fp32 accumulation, the norm
 //     step (the margin exact search uses, on the residuals' norms);
 //   - the rounding of the reference's own chain (base, precomputed and query tables, the m + 1 additions): c1
 //     roundings of at most 2^-24 * 3 (|q|^2 + |c|^2 + |w|^2) each;
-//   - the rounding of a itself and of ||a||^2.
+//   - the rounding of a itself and of ||a||^2 (summed in any order: 2e-6 ||a||^2 covers it).
 // Every row with compressed distance <= bound therefore scores below bound - ||a||^2 + eps.  For inner product the
 // score is -<q, w> and the threshold bound - base + eps with base = -<q, centroid> as the reference computed it.
 // Queries the tensor cores cannot score (no bound, non-finite or beyond the 16-bit range) are marked for the
 // per-query kernel instead.
 __global__ void __launch_bounds__(256) tc_gather_kernel(GatherArgs a) {
   const size_t l = blockIdx.x;
-  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;
   const uint32_t p0 = a.pair_off[l], n = a.pair_off[l + 1] - p0;
   if (n == 0 || a.list_off[l + 1] == a.list_off[l]) return;
   const uint32_t rows = (n + 255u) / 256u * 256u;
   const uint32_t a0 = a.a_off[l];
   const float* cen = a.centroids + l * size_t(a.pd);
   const float mul = a.is_l2 ? -2.f : -1.f;
-  for (uint32_t r = blockIdx.y * 8 + w; r < rows; r += gridDim.y * 8) {
-    const uint32_t arow = a0 + r;
-    if (r >= n) {
-      if (lane == 0) a.thr[arow] = -INFINITY;  // filler row: never below its threshold
-      continue;
-    }
-    const uint2 pr = a.pairs[p0 + r];
+  const int e_per = a.Kp >> 3;  // elements of a row per lane: a multiple of 8 (Kp is a multiple of 64)
+  for (uint32_t rb = blockIdx.y * 32 + w * 4; rb < rows; rb += gridDim.y * 32) {  // rows is a multiple of 256
+    const uint32_t r = rb + grp, arow = a0 + r;
+    const bool live = r < n;
+    uint2 pr = make_uint2(0u, 0u);
+    if (live) pr = a.pairs[p0 + r];
     const uint32_t q = pr.x;
     const float* qv = a.queries + size_t(q) * a.pd;
     uint16_t* dst = a.qg + size_t(arow) * a.Kp;
     float mx = 0.f, a2 = 0.f, q2 = 0.f;
     bool fin = true;
-    for (int c0 = 0; c0 < a.Kp; c0 += 128) {  // four elements per lane and step
-      const int c = c0 + lane * 4;
-      float x[4] = {0.f, 0.f, 0.f, 0.f};
-      if (c < a.pd) {  // pd is a multiple of 8
-        const float4 qq = *reinterpret_cast<const float4*>(qv + c);
-        x[0] = qq.x;
-        x[1] = qq.y;
-        x[2] = qq.z;
-        x[3] = qq.w;
-        q2 = __fmaf_rn(qq.x, qq.x, __fmaf_rn(qq.y, qq.y, __fmaf_rn(qq.z, qq.z, __fmaf_rn(qq.w, qq.w, q2))));
-        if (a.is_l2) {
-          const float4 cc = *reinterpret_cast<const float4*>(cen + c);
-          x[0] = __fsub_rn(x[0], cc.x);
-          x[1] = __fsub_rn(x[1], cc.y);
-          x[2] = __fsub_rn(x[2], cc.z);
-          x[3] = __fsub_rn(x[3], cc.w);
-        }
-      }
-      uint16_t h[4];
+    if (live) {
+      for (int e = 0; e < e_per; e += 8) {
+        const int c = sub * e_per + e;
+        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (c < a.pd) {  // pd is a multiple of 8: the whole group of 8 is inside or outside
+          const float4 q0 = *reinterpret_cast<const float4*>(qv + c), q1 = *reinterpret_cast<const float4*>(qv + c + 4);
+          x[0] = q0.x, x[1] = q0.y, x[2] = q0.z, x[3] = q0.w, x[4] = q1.x, x[5] = q1.y, x[6] = q1.z, x[7] = q1.w;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        mx = fmaxf(mx, fabsf(x[i]));
-        a2 = __fmaf_rn(x[i], x[i], a2);
-        fin = fin && fabsf(x[i]) <= 3.0e38f;
-        h[i] = to_operand(x[i] * mul, a.bf16);
+          for (int i = 0; i < 8; ++i) q2 = __fmaf_rn(x[i], x[i], q2);
+          if (a.is_l2) {
+            const float4 c0 = *reinterpret_cast<const float4*>(cen + c), c1 = *reinterpret_cast<const float4*>(cen + c + 4);
+            x[0] = __fsub_rn(x[0], c0.x), x[1] = __fsub_rn(x[1], c0.y), x[2] = __fsub_rn(x[2], c0.z), x[3] = __fsub_rn(x[3], c0.w);
+            x[4] = __fsub_rn(x[4], c1.x), x[5] = __fsub_rn(x[5], c1.y), x[6] = __fsub_rn(x[6], c1.z), x[7] = __fsub_rn(x[7], c1.w);
+          }
+        }
+        uint32_t h[4];
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          mx = fmaxf(mx, fmaxf(fabsf(x[i]), fabsf(x[i + 1])));
+          a2 = __fmaf_rn(x[i], x[i], a2);
+          a2 = __fmaf_rn(x[i + 1], x[i + 1], a2);
+          fin = fin && fabsf(x[i]) <= 3.0e38f && fabsf(x[i + 1]) <= 3.0e38f;
+          h[i >> 1] = uint32_t(to_operand(x[i] * mul, a.bf16)) | (uint32_t(to_operand(x[i + 1] * mul, a.bf16)) << 16);
+        }
+        *reinterpret_cast<uint4*>(dst + c) = make_uint4(h[0], h[1], h[2], h[3]);
       }
-      if (c < a.Kp)
-        *reinterpret_cast<uint2*>(dst + c) =
-            make_uint2(uint32_t(h[0]) | (uint32_t(h[1]) << 16), uint32_t(h[2]) | (uint32_t(h[3]) << 16));
     }
-    for (int o = 16; o > 0; o >>= 1) {
+    for (int o = 4; o > 0; o >>= 1) {  // over the eight lanes of the row
       mx = fmaxf(mx, __shfl_xor_sync(FV_FULL, mx, o));
       a2 += __shfl_xor_sync(FV_FULL, a2, o);
       q2 += __shfl_xor_sync(FV_FULL, q2, o);
     }
-    fin = __all_sync(FV_FULL, fin);
-    if (lane == 0) {
-      const bool bound_pass = a.q_rows != nullptr;
-      const uint32_t tb = bound_pass ? 0u : a.tau_bits[q];
-      const bool in_range = fin && (a.bf16 ? mx <= 1.0e38f : mx * (a.is_l2 ? 2.f : 1.f) <= 65504.f);
-      const float base = __uint_as_float(pr.y);
-      float thr = -INFINITY;
-      if (tb != 0xFFFFFFFFu && in_range) {
-        const float tau = bound_pass ? 0.f : order_bits_to_float(tb);
-        const float u16 = a.bf16 ? 0.00390625f : 0.00048828125f;
-        const float an = sqrtf(a2), bn = a.bn, kf = a.kf;
-        const float e_dot = (2.f * u16 * (1.f + u16) + kf * 4.7683716e-7f + kf * 1.1920929e-7f) * an * bn +
-                            5.9604645e-8f * sqrtf(kf) * (an + bn);
-        const float e_norm = (kf + 16.f) * 4.7683716e-7f * bn * bn + 1.1920929e-7f * bn * bn;
-        const float e_score = a.is_l2 ? 2.f * e_dot + e_norm + kf * 4.7683716e-7f * (a2 + bn * bn) : e_dot;
-        const float e_chain = a.c1 * 5.9604645e-8f * 3.f * (q2 + a.cw2);
-        const float e_self = 2.4e-7f * (an + bn) * an + 2.0e-6f * a2;
-        const float eps = 1.05f * (e_score + e_chain + e_self) + 1e-30f;
-        if (bound_pass) {
-          thr = a.is_l2 ? a2 + eps : base + eps;  // score + this >= the row's compressed distance
-          if (!(thr == thr)) thr = INFINITY;
-        } else {
-          thr = a.is_l2 ? (tau - a2) + eps : (tau - base) + eps;
-          if (!(thr == thr) || thr == INFINITY) thr = -INFINITY;  // a margin that is not a number: leave it to the other kernel
-        }
-      } else if (bound_pass) {
-        thr = INFINITY;  // no usable scores for this query: its minima say nothing
-      }
-      if (bound_pass) {
-        const uint32_t slot = atomicAdd(a.q_cnt + q, 1u);
-        if (slot < uint32_t(a.q_slots)) a.q_rows[size_t(q) * a.q_slots + slot] = arow;
-      } else if (thr == -INFINITY) {
-        a.cand_cnt[q] = 0xFFFFFFFFu;  // left to the per-query kernel (none of its rows survives)
-      }
-      a.thr[arow] = thr;
-      a.g_q[arow] = q;
-      a.g_l[arow] = uint32_t(l);
-      a.g_base[arow] = base;
+    const unsigned finb = __ballot_sync(FV_FULL, fin);
+    fin = ((finb >> (grp * 8)) & 0xFFu) == 0xFFu;
+    if (sub != 0) continue;
+    if (!live) {
+      a.thr[arow] = -INFINITY;  // filler row: never below its threshold
+      continue;
     }
+    const bool bound_pass = a.q_rows != nullptr;
+    const uint32_t tb = bound_pass ? 0u : a.tau_bits[q];
+    const bool in_range = fin && (a.bf16 ? mx <= 1.0e38f : mx * (a.is_l2 ? 2.f : 1.f) <= 65504.f);
+    const float base = __uint_as_float(pr.y);
+    float thr = -INFINITY;
+    if (tb != 0xFFFFFFFFu && in_range) {
+      const float tau = bound_pass ? 0.f : order_bits_to_float(tb);
+      const float u16 = a.bf16 ? 0.00390625f : 0.00048828125f;
+      const float an = sqrtf(a2), bn = a.bn, kf = a.kf;
+      const float e_dot = (2.f * u16 * (1.f + u16) + kf * 4.7683716e-7f + kf * 1.1920929e-7f) * an * bn +
+                          5.9604645e-8f * sqrtf(kf) * (an + bn);
+      const float e_norm = (kf + 16.f) * 4.7683716e-7f * bn * bn + 1.1920929e-7f * bn * bn;
+      const float e_score = a.is_l2 ? 2.f * e_dot + e_norm + kf * 4.7683716e-7f * (a2 + bn * bn) : e_dot;
+      const float e_chain = a.c1 * 5.9604645e-8f * 3.f * (q2 + a.cw2);
+      const float e_self = 2.4e-7f * (an + bn) * an + 2.0e-6f * a2;
+      const float eps = 1.05f * (e_score + e_chain + e_self) + 1e-30f;
+      if (bound_pass) {
+        thr = a.is_l2 ? a2 + eps : base + eps;  // score + this >= the row's compressed distance
+        if (!(thr == thr)) thr = INFINITY;
+      } else {
+        thr = a.is_l2 ? (tau - a2) + eps : (tau - base) + eps;
+        if (!(thr == thr) || thr == INFINITY) thr = -INFINITY;  // a margin that is not a number: leave it to the other kernel
+      }
+    } else if (bound_pass) {
+      thr = INFINITY;  // no usable scores for this query: its minima say nothing
+    }
+    if (bound_pass) {
+      const uint32_t slot = atomicAdd(a.q_cnt + q, 1u);
+      if (slot < uint32_t(a.q_slots)) a.q_rows[size_t(q) * a.q_slots + slot] = arow;
+    } else if (thr == -INFINITY) {
+      a.cand_cnt[q] = 0xFFFFFFFFu;  // left to the per-query kernel (none of its rows survives)
+    }
+    a.thr[arow] = thr;
+    a.g_q[arow] = q;
+    a.g_l[arow] = uint32_t(l);
+    a.g_base[arow] = base;
   }
 }
 
