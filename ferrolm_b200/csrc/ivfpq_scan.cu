@@ -849,7 +849,8 @@ struct FinishArgs {
   uint32_t* cand_cnt;
   int cap;
   uint32_t* counters;
-  const uint32_t* qids;    // second round: the queries to finish (null: all, block b = query b)
+  const uint32_t* qids;    // second round: the queries to finish (null: all, block b = query b) ...
+  const uint32_t* nqids;   // ... and the device word that says how many there are
   // A query whose buffer ran over (count > cap):
   //   tighten == 1: its stored `cap` candidates still give a valid, tighter bound -- the keep-th smallest of them,
   //                 since that many rows reach it -- which goes to tau_bits[q]; the count is reset, redo[q] is set and
@@ -865,12 +866,11 @@ struct FinishArgs {
   const uint32_t* dropped;  // or null; dropped[q] != 0: the scan lost survivors of q (a full pool): to rerun_ids
 };
 
-// One block per query: the best `keep` of the appended candidates, then the common tail.
-__global__ void __launch_bounds__(256) ivfpq_finish_kernel(ScanArgs a, FinishArgs f, int n2max) {
-  u64* lists = reinterpret_cast<u64*>(dyn_smem());  // n2max keys
-  u64* rerank = lists + n2max;                      // keep + k
-  float* sq = reinterpret_cast<float*>(rerank + a.keep + a.k);
-  const size_t q = f.qids ? size_t(f.qids[blockIdx.x]) : size_t(blockIdx.x);
+// One block per query: the best `keep` of the appended candidates, then the common tail.  With f.qids the blocks
+// walk that list (*f.nqids entries: a count only the device knows when the kernel is launched) instead of taking
+// query blockIdx.x.
+__device__ __forceinline__ void finish_block_query(const ScanArgs& a, const FinishArgs& f, size_t q, u64* lists, u64* rerank,
+                                                   float* sq) {
   const int tid = threadIdx.x;
   const uint32_t cnt = f.cand_cnt[q];
   if (cnt == 0xFFFFFFFFu || (cnt > uint32_t(f.cap) && !f.tighten) || (f.dropped && f.dropped[q])) {
@@ -894,6 +894,21 @@ __global__ void __launch_bounds__(256) ivfpq_finish_kernel(ScanArgs a, FinishArg
     return;
   }
   scan_tail(a, q, lists, rerank, sq);
+}
+
+__global__ void __launch_bounds__(256) ivfpq_finish_kernel(ScanArgs a, FinishArgs f, int n2max) {
+  u64* lists = reinterpret_cast<u64*>(dyn_smem());  // n2max keys
+  u64* rerank = lists + n2max;                      // keep + k
+  float* sq = reinterpret_cast<float*>(rerank + a.keep + a.k);
+  if (!f.qids) {
+    finish_block_query(a, f, blockIdx.x, lists, rerank, sq);
+    return;
+  }
+  const uint32_t n = *f.nqids;
+  for (uint32_t i = blockIdx.x; i < n; i += gridDim.x) {
+    finish_block_query(a, f, f.qids[i], lists, rerank, sq);
+    __syncthreads();  // the shared buffers are reused by the next query
+  }
 }
 
 // codes (rows x 16, by list) -> sub-quantizer-major copy, lists padded to 16 rows with zero bytes
@@ -1239,6 +1254,7 @@ struct RescoreArgs {
   uint32_t* cand_cnt;
   int cap;
   const uint32_t* only;  // second round: only survivors of queries with only[q] != 0 (null: all)
+  const uint32_t* gate;  // second round: the device word that counts its queries; the kernel leaves at once if it is 0
   size_t a_rows;         // extents (gathered operand rows, lists, rows in all lists), for the checks of the debug build
   uint32_t nlist, nrows;
 };
@@ -1248,6 +1264,7 @@ struct RescoreArgs {
 // The pools are very unequal (a CTA that drew the lists of a dense region holds several times the average), so the
 // blocks split the concatenation of all pools evenly instead of a pool each.
 __global__ void __launch_bounds__(128) rescore_kernel(RescoreArgs a) {
+  if (a.gate && *a.gate == 0) return;
   uint32_t* start = reinterpret_cast<uint32_t*>(dyn_smem());  // npools + 1: first global index of every pool
   if (threadIdx.x == 0) {
     uint32_t s = 0;
@@ -1694,42 +1711,49 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     ivfpq_finish_kernel<<<unsigned(nq), 256, fsmem, ctx->stream>>>(a, fa, n2max);
     ctx->stats.launches++;
     FV_CUDA(cudaGetLastError());
+    if (path == LIST_TENSOR) {
+      // Second round, launched without asking the host: the queries whose buffer ran over (their count is a device
+      // word) get their survivors re-scored against the tightened bounds and are finished from the list the first
+      // round left.  Both kernels leave at once when there are none.
+      ra.only = redo;
+      ra.gate = pb_set.counters + LS_C_OVER;
+      rescore_kernel<<<unsigned(tc_grid) * 16, 128, size_t(tc_grid + 1) * sizeof(uint32_t), ctx->stream>>>(ra);
+      FinishArgs f2 = fa;
+      f2.qids = fa.over_ids;
+      f2.nqids = pb_set.counters + LS_C_OVER;
+      f2.tighten = 0;
+      ivfpq_finish_kernel<<<unsigned(std::min<size_t>(nq, size_t(ctx->sm_count) * 4)), 256, fsmem, ctx->stream>>>(a, f2, n2max);
+      ctx->stats.launches += 2;
+      FV_CUDA(cudaGetLastError());
+    }
+    // one read-back for the whole scan: counters, pool fill, the kernel's error word, rows scanned
     uint32_t h_ctr[LS_NCOUNTERS] = {};
     std::vector<unsigned int> h_pool(size_t(tc_grid) + 1, 0u);
+    unsigned long long rows2[2] = {0, 0};
     FV_CUDA(cudaMemcpyAsync(h_ctr, pb_set.counters, sizeof(h_ctr), cudaMemcpyDeviceToHost, ctx->stream));
     if (tc_grid) {
       FV_CUDA(cudaMemcpyAsync(h_pool.data(), pool_cnt, size_t(tc_grid) * sizeof(unsigned int), cudaMemcpyDeviceToHost, ctx->stream));
       FV_CUDA(cudaMemcpyAsync(&h_pool[tc_grid], tc_error_word(ix.recon), sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     }
+    FV_CUDA(cudaMemcpyAsync(rows2, d_rows, sizeof(rows2), cudaMemcpyDeviceToHost, ctx->stream));
     FV_CUDA(cudaStreamSynchronize(ctx->stream));
     if (tc_grid && h_pool[tc_grid]) return fail(FV_ERR_TIMEOUT, "a bounded wait inside the tensor-core kernel ran out");
     // survivors of the tensor-core pass: pairs re-scored exactly (a pool that ran over dropped the rest, and the
     // finishing kernel has put the queries they belonged to on the re-run list)
     for (int c = 0; c < tc_grid; ++c) ctx->stats.dist_evals += std::min(h_pool[c], pool_cap);
-    uint32_t n_over = h_ctr[LS_C_OVER], n_rerun = h_ctr[LS_C_RERUN];
-    {
-      if (n_over) {  // second round: the marked queries' survivors against their tightened bounds
-        ra.only = redo;
-        rescore_kernel<<<unsigned(tc_grid) * 16, 128, size_t(tc_grid + 1) * sizeof(uint32_t), ctx->stream>>>(ra);
-        fa.qids = fa.over_ids;
-        fa.tighten = 0;
-        ivfpq_finish_kernel<<<n_over, 256, fsmem, ctx->stream>>>(a, fa, n2max);
-        ctx->stats.launches += 2;
-        FV_CUDA(cudaGetLastError());
-        FV_CUDA(cudaMemcpyAsync(&n_rerun, pb_set.counters + LS_C_RERUN, sizeof(n_rerun), cudaMemcpyDeviceToHost, ctx->stream));
-        FV_CUDA(cudaStreamSynchronize(ctx->stream));
-      }
-      if (n_rerun) {  // whatever is left: those queries once more, by the per-query kernel (their rows are counted already)
-        ScanArgs r = a;
-        r.qids = fa.rerun_ids;
-        r.rows_scanned = nullptr;
-        FV_TRY(launch_block_scan(ctx, r, n_rerun, use_pre));
-      }
+    const uint32_t n_rerun = h_ctr[LS_C_RERUN];
+    if (n_rerun) {  // whatever is left: those queries once more, by the per-query kernel (their rows are counted already)
+      ScanArgs r = a;
+      r.qids = fa.rerun_ids;
+      r.rows_scanned = nullptr;
+      FV_TRY(launch_block_scan(ctx, r, n_rerun, use_pre));
     }
-    ctx->stats.regrown = n_over;
-    n_over = n_rerun;
-    ctx->stats.uncertified = n_over;
+    ctx->stats.regrown = h_ctr[LS_C_OVER];
+    ctx->stats.uncertified = n_rerun;
     stage_mark(ctx);  // 5
+    ctx->stats.rows_scanned = rows2[0] + rows2[1];
+    ctx->stats.rows_list_scan = rows2[1];
+    return FV_OK;
   }
   unsigned long long rows[2] = {0, 0};
   FV_CUDA(cudaMemcpyAsync(rows, d_rows, sizeof(rows), cudaMemcpyDeviceToHost, ctx->stream));
