@@ -249,7 +249,8 @@ static int launch_scan(fv_ctx* ctx, bool is_l2, dim3 grid, int threads, size_t s
   // the row tile goes behind the queries and lists when the shared memory of an SM still holds four such blocks
   const size_t tile_bytes = size_t(32) * (size_t(pd) + 4) * sizeof(float);
   const size_t with_tile = ((smem + 15) & ~size_t(15)) + tile_bytes;
-  const bool tiled = with_tile <= 56 * 1024;
+  // (only for full blocks: a single warp that scans a long run of rows for a few queries streams them faster itself)
+  const bool tiled = with_tile <= 56 * 1024 && threads >= 128;
   auto k = is_l2 ? (tiled ? exact_scan_kernel<QT, true, true> : exact_scan_kernel<QT, true, false>)
                  : (tiled ? exact_scan_kernel<QT, false, true> : exact_scan_kernel<QT, false, false>);
   if (tiled) smem = with_tile;
