@@ -135,14 +135,29 @@ __global__ void __launch_bounds__(128) warp_select_kernel(const u64* __restrict_
     const int r = j * 32 + lane;
     h[j] = r < n ? uint32_t(src[r] >> 32) : 0xFFFFFFFFu;
   }
-  uint32_t lo = 0, hi = 0xFFFFFFFFu;
+  // Bisection between the smallest and the largest word.  It may stop at any value with exactly L words at or below
+  // it: that value separates the same rows as the L-th smallest word itself (the selection below takes every row
+  // below T and as many rows at T as are still wanted, which is then all of them).
+  uint32_t lo = 0xFFFFFFFFu, hi = 0;
+#pragma unroll
+  for (int j = 0; j < NPL; ++j) {
+    lo = min(lo, h[j]);
+    if (j * 32 + lane < n) hi = max(hi, h[j]);
+  }
+  lo = __reduce_min_sync(FV_FULL, lo);
+  hi = __reduce_max_sync(FV_FULL, hi);
+  if (n < L) hi = 0xFFFFFFFFu;  // fewer rows than wanted: the filler value is the L-th smallest
   while (lo < hi) {
     const uint32_t mid = lo + ((hi - lo) >> 1);
     int c = 0;
 #pragma unroll
     for (int j = 0; j < NPL; ++j) c += h[j] <= mid ? 1 : 0;
     c = __reduce_add_sync(FV_FULL, c);
-    if (c >= L) hi = mid;
+    if (c == L) {
+      lo = mid;
+      break;
+    }
+    if (c > L) hi = mid;
     else lo = mid + 1;
   }
   const uint32_t T = lo;

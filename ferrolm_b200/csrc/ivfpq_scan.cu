@@ -796,6 +796,7 @@ __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __res
   const uint32_t INF_BITS = 0xFF800000u;
   const int np = int(min(q_cnt[q], uint32_t(q_slots)));
   int n = 0, finite = 0;
+  uint32_t vmin = 0xFFFFFFFFu, vmax = 0u;  // over the finite bounds
   for (int s0 = 0; s0 < np && n < vcap; s0 += 32) {
     // lane i looks up pair s0 + i (one round of dependent loads for 32 pairs instead of one per pair) ...
     uint32_t my_t0 = 0, my_t1 = 0, my_rt = 0;
@@ -822,7 +823,11 @@ __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __res
         for (int i = lane; i < room; i += 32) {
           const uint32_t b = order_bits(__fadd_ru(src[i], ad));  // rounded up: still an upper bound
           v[n + i] = b;
-          finite += b < INF_BITS ? 1 : 0;
+          if (b < INF_BITS) {
+            finite += 1;
+            vmin = min(vmin, b);
+            vmax = max(vmax, b);
+          }
         }
         n += room;
       }
@@ -833,12 +838,19 @@ __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __res
     if (lane == 0) tau_bits[q] = 0xFFFFFFFFu;
     return;
   }
-  uint32_t lo = 0, hi = INF_BITS - 1;
+  // Bisection between the smallest and the largest finite bound; any value with exactly `keep` bounds at or below it
+  // will do (it is at least the keep-th smallest and below the next one), so the search stops there.
+  uint32_t lo = __reduce_min_sync(FV_FULL, vmin), hi = __reduce_max_sync(FV_FULL, vmax);
   while (lo < hi) {
     const uint32_t mid = lo + ((hi - lo) >> 1);
     int c = 0;
     for (int i = lane; i < n; i += 32) c += v[i] <= mid ? 1 : 0;
-    if (__reduce_add_sync(FV_FULL, c) >= keep) hi = mid;
+    c = __reduce_add_sync(FV_FULL, c);
+    if (c == keep) {
+      lo = mid;
+      break;
+    }
+    if (c > keep) hi = mid;
     else lo = mid + 1;
   }
   if (lane == 0) tau_bits[q] = lo;
