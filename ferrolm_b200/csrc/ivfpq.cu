@@ -713,7 +713,7 @@ int fv_ivfpq_set_survivor_slots(fv_ivfpq* ix, size_t slots) {
 }
 
 int fv_ivfpq_set_scan_mode(fv_ivfpq* ix, int mode) {
-  if (!ix || mode < 0 || mode > 3) return fv::fail(FV_ERR_ARG, "fv_ivfpq_set_scan_mode: mode must be 0, 1, 2 or 3");
+  if (!ix || mode < 0 || mode > 4) return fv::fail(FV_ERR_ARG, "fv_ivfpq_set_scan_mode: mode must be 0, 1, 2, 3 or 4");
   ix->scan_mode = mode;
   return FV_OK;
 }

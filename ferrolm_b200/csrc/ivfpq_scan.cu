@@ -78,6 +78,11 @@ struct ScanArgs {
   unsigned long long* rows_scanned;
   const uint32_t* qids;      // block b works on query qids[b] (null: query b)
   uint32_t nlist, nrows, nvec;  // extents (lists, rows in all lists, kept vectors), for the checks of the debug build
+  // Bound mode (bound_out != null): only the nearest probed lists are scanned, until they hold row_budget rows, and
+  // instead of results the query's keep-th best compressed distance over those rows goes to bound_out[q] as its
+  // order bits (0xFFFFFFFF when they hold fewer than keep rows): an upper bound for the list-major passes.
+  uint32_t row_budget;
+  uint32_t* bound_out;
 };
 
 // The query's part of the lookup tables for a whole batch (ivfpq.rs:236-238 inner product, :241-251 L2 with
@@ -134,6 +139,10 @@ __device__ __forceinline__ float lut_entry(uint32_t w, uint32_t lut_s) {
 // (ivfpq.rs:285-296).  Called by every thread of the block.
 __device__ __forceinline__ void scan_tail(const ScanArgs& a, size_t q, const u64* cand, u64* rerank, const float* sq) {
   const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  if (a.bound_out) {
+    if (tid == 0) a.bound_out[q] = cand[a.keep - 1] == FV_EMPTY_KEY ? 0xFFFFFFFFu : uint32_t(cand[a.keep - 1] >> 32);
+    return;
+  }
   if (!a.refine && !a.candidates) {
     for (int e = tid; e < a.k; e += blockDim.x) a.out_keys[q * size_t(a.k) + e] = e < a.keep ? cand[e] : FV_EMPTY_KEY;
     return;
@@ -260,12 +269,17 @@ __global__ void __launch_bounds__(256, 4) ivfpq_scan_kernel(ScanArgs a) {
   };
   unsigned long long scanned = 0;
   // the next probed cell this block scans (a list-sharded index skips the other shards' lists), or -1
+  uint32_t budget_used = 0;  // bound mode: rows of the lists taken so far (the same in every thread)
   auto next_probe = [&](int p) {
     for (++p; p < a.nprobe; ++p) {
       const u64 c = a.cells[q * size_t(a.nprobe) + p];
       if (c == FV_EMPTY_KEY) return -1;
       if (a.shard_world > 1 && int(key_id(c) % uint32_t(a.shard_world)) != a.shard_rank) continue;
       if (!FV_IDX_OK(key_id(c), a.nlist, 1)) continue;
+      if (a.row_budget) {
+        if (budget_used >= a.row_budget) return -1;
+        budget_used += a.list_off[key_id(c) + 1] - a.list_off[key_id(c)];
+      }
       return p;
     }
     return -1;
@@ -1398,13 +1412,14 @@ static int bucket_pairs(fv_ctx* ctx, const ScanIndex& ix, const u64* cells, size
 }
 
 bool ivfpq_wants_tensor(int mode, size_t nq, size_t nprobe, size_t nlist, int shard_world) {
-  if (mode == 3) return nq >= 1;
+  (void)shard_world;  // a list shard sees 1 / world of the pairs on 1 / world of the lists: the same pairs per list
+  if (mode == 3 || mode == 4) return nq >= 1;
   if (mode != 0) return false;
-  const size_t owned_lists = std::max<size_t>(1, nlist / size_t(std::max(1, shard_world)));
   // The tensor-core pass costs about one unit of work per (list, 256-pair tile, 256 rows) whatever the tile holds, the
   // per-query kernel one per (pair, row): measured on 1M x 128 / 1024 lists, the pass wins from about 8 pairs per
-  // list (4 pairs per list: 0.50 against 0.46 ms; 78: 0.80 against 1.34 ms).
-  return nq >= 256 && nq * nprobe >= 24 * owned_lists;
+  // list (4 pairs per list: 0.50 against 0.46 ms; 78: 0.80 against 1.34 ms), and on 50M x 128 / 16384 lists with 20
+  // pairs per list it takes 8.6 ms against 18.7.
+  return nq >= 256 && nq * nprobe >= 12 * std::max<size_t>(1, nlist);
 }
 
 // Stages (fv_stats.stage_ms) of an IVF-PQ search: 0 coarse cells (marked by the caller); 1 query tables and, on the
@@ -1470,8 +1485,8 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
 
   // Which scan.  Both list-major paths need m = 16 (the bound pass reads the sub-quantizer-major codes), a table that
   // separates into a list part and a query part, and at most 1024 kept candidates.  The tensor-core pass also needs
-  // the reconstructed rows and enough pairs per list to fill its 256-query tiles: on average at least 96 per list
-  // this shard owns.  The table scan is never chosen automatically (measured no faster than the per-query kernel).
+  // the reconstructed rows and enough pairs per list (ivfpq_wants_tensor).  The table scan is never chosen
+  // automatically (measured no faster than the per-query kernel).
   enum { BLOCK, LIST_TABLE, LIST_TENSOR } path = BLOCK;
   const bool list_ok = ix.m == 16 && ix.codes_t && separable && keep <= 1024;
   const bool tensor_ok = list_ok && ix.recon != nullptr;
@@ -1509,7 +1524,33 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     uint2* pairs_a = ctx->scratch[7].as<uint2>();
     uint2* pairs_b = pairs_a + nq * size_t(nprobe);
     uint32_t* tau_bits = pa_set.extra;
-    FV_TRY(bucket_pairs(ctx, ix, cells, nq, nprobe, bound_rows, pa_set, pairs_a));
+    // How the bound is found.  The tensor-core bound pass costs about one unit of work per (touched list, 256 rows)
+    // however few of the batch's queries are near that list, plus five small kernels; scanning each query's few
+    // nearest lists with the per-query kernel costs one (query, row) evaluation each, at a poor rate (short blocks).
+    // Both are estimated from measured rates (1M x 128 / 1024 lists: 0.185 ms on the tensor cores at 1,250 queries,
+    // 0.20 and 0.31 ms by the per-query kernel at 1,250 and 2,500; 50M x 128 / 16384 lists, 10,000 queries: 2.5
+    // against 1.5 ms) and the cheaper one is taken: the tensor cores unless the lists are long and many.
+    bool mini_bound = false;
+    if (path == LIST_TENSOR) {
+      const double avg_len = double(ix.nrows) / double(std::max<size_t>(1, ix.nlist));
+      const double lists_per_query = std::max(1.0, std::ceil(double(bound_rows) / std::max(1.0, avg_len)));
+      const double pairs_a_est = double(nq) * std::min(lists_per_query, double(nprobe));
+      const size_t owned = std::max<size_t>(1, ix.nlist / size_t(std::max(1, ix.shard_world)));
+      const double t_mini = pairs_a_est * avg_len * 5e-5;                                                    // microseconds
+      const double t_tc = std::min(double(owned), pairs_a_est) * std::max(1.0, avg_len / 256.0) * 0.025 + 80.0;
+      mini_bound = t_mini < t_tc || mode == 4;
+    }
+    if (mini_bound) {
+      ScanArgs b = a;
+      b.row_budget = bound_rows;
+      b.bound_out = tau_bits;
+      b.rows_scanned = nullptr;
+      b.refine = 0;
+      b.candidates = 0;
+      FV_TRY(launch_block_scan(ctx, b, nq, use_pre));
+    } else {
+      FV_TRY(bucket_pairs(ctx, ix, cells, nq, nprobe, bound_rows, pa_set, pairs_a));
+    }
     ListScanArgs la{};
     la.qtab = qtab;
     la.pre = ix.pre;
@@ -1587,6 +1628,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       ga.g_l = g_l;
       ga.g_base = g_base;
       // ---- the bound pass on the tensor cores: the near pairs' rows scored, the minimum of every 8 kept
+      if (!mini_bound) {
       size_t mfloats = std::max<size_t>(size_t(1) << 20, nq * 4096);
       mfloats = std::min<size_t>(mfloats, size_t(1) << 30);
       FV_TRY(ctx->scratch[6].reserve(mfloats * sizeof(float)));
@@ -1616,6 +1658,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
           ctx->scratch[6].as<float>(), tasks, tile_task0, task_moff, task_rows, thr, q_rows, q_cnt, q_slots, vcap, keep, nq, tau_bits);
       ctx->stats.launches++;
       FV_CUDA(cudaGetLastError());
+      }
     } else {
       la.pair_off = pa_set.pair_off;
       la.task_off = pa_set.task_off;

@@ -44,7 +44,8 @@ struct ScanOut {
 };
 
 // mode: 0 = pick by size, 1 = one block per query only, 2 = the list-major table scan whenever the index allows it,
-// 3 = the list-major tensor-core pass whenever the index allows it.
+// 3 = the list-major tensor-core pass whenever the index allows it, 4 = the same with the bounds from the per-query
+// kernel (the form it takes by itself when the lists are long and many).
 // `cells`: nq x nprobe keys (distance, list), ascending.  `keep` = candidates kept by compressed distance;
 // `refine`: re-rank them exactly and cut to k.  Marks the context's stages and fills stats.rows_scanned.
 // `cand_slots`: candidate slots per query of the list-major scans (0 = default).

@@ -319,7 +319,8 @@ class IvfPq:
         check(lib().fv_ivfpq_set_shard(self._h, rank, world))
 
     def set_scan_mode(self, mode: int):
-        """0 chosen by size, 1 one block per query, 2 the list-major scan whenever the index allows it."""
+        """0 chosen by size, 1 one block per query, 2 the list-major table scan, 3 the list-major tensor-core pass,
+        4 that pass with its bounds from the per-query kernel (2 to 4 whenever the index allows it)."""
         check(lib().fv_ivfpq_set_scan_mode(self._h, mode))
 
     def set_candidate_slots(self, slots: int):

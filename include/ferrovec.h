@@ -154,10 +154,11 @@ int fv_ivfpq_search_candidates_cells_dev(fv_ivfpq* ix, const float* d_queries, s
                                          const uint64_t* d_cells, fv_neighbor* d_adc, float* d_exact,
                                          uint32_t* d_counts);
 /* Which scan a search uses: 0 = chosen by batch and index size (default), 1 = one block per query, 2 = the
- * list-major table scan, 3 = the list-major tensor-core pass (2 and 3 whenever the index allows it: m = 16, L2 with
- * precomputed tables or inner product, for 3 also a padded dimension up to 128; 3 keeps a 16-bit reconstruction of
- * every row, 2 * padded dimension bytes per row, built by the first search that uses it).  All give the same
- * neighbours; 1, 2 and 3 exist for validation and measurement. */
+ * list-major table scan, 3 = the list-major tensor-core pass, 4 = that pass with its bounds from the per-query kernel
+ * instead of the tensor cores (2, 3 and 4 whenever the index allows it: m = 16, L2 with precomputed tables or inner
+ * product, for 3 and 4 also a padded dimension up to 128; they keep a 16-bit reconstruction of every row,
+ * 2 * padded dimension bytes per row, built by the first search that uses it).  All give the same neighbours;
+ * 1 to 4 exist for validation and measurement. */
 int fv_ivfpq_set_scan_mode(fv_ivfpq* ix, int mode);
 /* List-major scan: global-memory candidate slots per query (8 bytes each; 0 = default, 1024 or fewer for very large
  * batches; at most 4096).  A query that finds more rows below its bound than it has slots is re-run by the

@@ -392,7 +392,7 @@ def test_ivfpq_list_major_scan_matches_the_oracle(fv, oracle, ivfpq16_pair, npro
     g, o, base, queries = ivfpq16_pair
     want, wc, rows = o.search_batch(queries, k, nprobe, refine, want_rows=True)
     outs = {}
-    for mode in (3, 2, 1):
+    for mode in (4, 3, 2, 1):
         g.set_scan_mode(mode)
         got, gc = g.search_batch(queries, k, nprobe, refine)
         eq, total = assert_same_neighbours(got, gc, want, wc, f"ivfpq m=16 mode {mode} nprobe={nprobe} refine={refine}")
@@ -400,7 +400,7 @@ def test_ivfpq_list_major_scan_matches_the_oracle(fv, oracle, ivfpq16_pair, npro
         assert g.ctx.stats()["rows_scanned"] == rows
         outs[mode] = got
     g.set_scan_mode(0)
-    assert outs[1].tobytes() == outs[2].tobytes() == outs[3].tobytes()
+    assert outs[1].tobytes() == outs[2].tobytes() == outs[3].tobytes() == outs[4].tobytes()
 
 
 @pytest.mark.parametrize("mode", [2, 3])
@@ -451,14 +451,14 @@ def test_ivfpq_list_major_scan_inner_product_and_ragged_lists(fv, oracle, ctx):
     o = oracle.IvfPq.load(g.save())
     for nprobe, refine in [(20, 0), (150, 5), (3, 2)]:
         want, wc, rows = o.search_batch(queries, 10, nprobe, refine, want_rows=True)
-        for mode in (2, 3):
+        for mode in (2, 3, 4):
             g.set_scan_mode(mode)
             got, gc = g.search_batch(queries, 10, nprobe, refine)
             eq, total = assert_same_neighbours(got, gc, want, wc, f"ivfpq IP list-major mode {mode} nprobe={nprobe}")
             assert eq == total and g.ctx.stats()["rows_scanned"] == rows
 
 
-@pytest.mark.parametrize("mode", [2, 3])
+@pytest.mark.parametrize("mode", [2, 3, 4])
 @pytest.mark.parametrize("refine", [0, 5])
 def test_ivfpq_list_major_scan_on_list_shards(fv, oracle, ctx, ivfpq16_pair, refine, mode):
     import torch
