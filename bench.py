@@ -205,7 +205,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": qps, "unit": "queries/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.workload, 1, nprobe, refine),
+        # the configuration of the arm this one is compared with at the same N (the CPU search itself has one layout)
+        "config": workload_config(args.workload, int(os.environ.get("WORLD_SIZE", "1")), nprobe, refine,
+                                  (args.list_shards or 1) if args.workload == "ivfpq" else 0),
         "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": threads, "kind": "port", "sample": sample,
                          "qps_1": qps_1, "qps_1_note": f"one thread, first {n1} queries (the reference's own protocol)",
                          "build_s": build_s},
