@@ -283,8 +283,8 @@ struct GemmParams {
   // query number) is marked in owner_dropped so that the caller can hand that query to another kernel.
   const uint32_t* row_owner;
   uint32_t* owner_dropped;
-  // task mode, minima variant (minima != null): instead of survivors, the smallest score of every 8 B rows, for the
-  // first task_rows[t] operand rows of task t: minima[task_moff[t] + (row in tile * units + unit) * 32 + column / 8];
+  // task mode, minima variant (minima != null): instead of survivors, the smallest score of every 32 B rows, for the
+  // first task_rows[t] operand rows of task t: minima[task_moff[t] + (row in tile * units + unit) * 8 + column / 32];
   // B rows beyond the task's valid ones count as +inf.  Tasks with task_moff[t] == 0xFFFFFFFF write nothing.
   float* minima;
   const uint32_t* task_moff;
@@ -592,7 +592,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         if (p.minima) {
           const uint32_t moff = p.task_moff[g];
           const uint32_t rt = a_row - t.x;
-          mdst = (moff != 0xFFFFFFFFu && rt < p.task_rows[g]) ? p.minima + size_t(moff) + size_t(rt) * (t.z & 0xFFFFu) * 32 : nullptr;
+          mdst = (moff != 0xFFFFFFFFu && rt < p.task_rows[g]) ? p.minima + size_t(moff) + size_t(rt) * (t.z & 0xFFFFu) * 8 : nullptr;
         }
       } else {
         const int part = g / p.MT;
@@ -704,23 +704,21 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             }
             if (TASKS) {
               if (p.minima) {
-                // minima variant: the smallest score of every 8 columns of this chunk, rows beyond the task's as +inf
+                // minima variant: the smallest score of every 32 columns of this chunk, rows beyond the task's as +inf
                 if (mdst) {
-                  float g8[8];
+                  float g2[2];
                   const bool tail = row_base + uint32_t(c + 63) >= n_rows;
 #pragma unroll
-                  for (int gi = 0; gi < 8; ++gi) {
+                  for (int gi = 0; gi < 2; ++gi) {
                     float m = INFINITY;
 #pragma unroll
-                    for (int i = gi * 8; i < gi * 8 + 8; ++i) {
+                    for (int i = gi * 32; i < gi * 32 + 32; ++i) {
                       const float v = __uint_as_float(rbuf[i]);
                       m = fminf(m, (!tail || row_base + uint32_t(c + i) < n_rows) ? v : INFINITY);
                     }
-                    g8[gi] = m;
+                    g2[gi] = m;
                   }
-                  float4* d4 = reinterpret_cast<float4*>(mdst + size_t(nt) * 32 + (col0 + c) / 8);
-                  d4[0] = make_float4(g8[0], g8[1], g8[2], g8[3]);
-                  d4[1] = make_float4(g8[4], g8[5], g8[6], g8[7]);
+                  *reinterpret_cast<float2*>(mdst + size_t(nt) * 8 + (col0 + c) / 32) = make_float2(g2[0], g2[1]);
                 }
               } else {
                 chunk_tasks(rbuf, c);

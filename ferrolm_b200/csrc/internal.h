@@ -202,8 +202,8 @@ int* tc_error_word(TcSide* tc);
 // that does not fit is dropped and d_dropped[d_row_owner[operand row]] set to 1.  The CTAs draw the tasks in table
 // order from the counter *d_next_task (which this call zeroes): sort the table longest first.  Asynchronous.
 // Minima variant (d_minima != null): no survivors; instead, for the first d_task_rows[t] operand rows of task t, the
-// smallest score of every 8 side rows (rows beyond the task's valid ones as +inf) goes to
-// d_minima[d_task_moff[t] + (operand row in the task * units + unit) * 32 + side row in the unit / 8]; a task with
+// smallest score of every 32 side rows (rows beyond the task's valid ones as +inf) goes to
+// d_minima[d_task_moff[t] + (operand row in the task * units + unit) * 8 + side row in the unit / 32]; a task with
 // d_task_moff[t] == 0xFFFFFFFF writes nothing.  d_thr and the pool are not used then.
 int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_t a_rows, const float* d_thr,
                  const uint4* d_tasks, const uint32_t* d_ntasks, unsigned int* d_next_task, u64* d_pool, unsigned int* d_pool_cnt,

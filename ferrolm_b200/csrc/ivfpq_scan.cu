@@ -793,7 +793,7 @@ __global__ void __launch_bounds__(128) bound_select_kernel(const float* __restri
 }
 
 // Bound from the tensor-core scores.  The minima variant of the kernel left, per (query, near list) pair, the smallest
-// score of every 8 rows; score + add[row] is an upper bound of the compressed distance of the row that attains it.
+// score of every 32 rows; score + add[row] is an upper bound of the compressed distance of the row that attains it.
 // One warp per query collects those bounds over its pairs; their keep-th smallest is a distance that at least `keep`
 // different rows of the query's probed lists do not exceed.
 __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __restrict__ minima, const uint4* __restrict__ tasks,
@@ -831,7 +831,7 @@ __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __res
       for (uint32_t t = t0; t < t1 && n < vcap; ++t) {
         const uint32_t moff = task_moff[t];
         if (moff == 0xFFFFFFFFu || rt >= task_rows[t]) continue;
-        const int cnt = int(tasks[t].z & 0xFFFFu) * 32;
+        const int cnt = int(tasks[t].z & 0xFFFFu) * 8;
         const float* src = minima + size_t(moff) + size_t(rt) * cnt;
         const int room = min(cnt, vcap - n);
         for (int i = lane; i < room; i += 32) {
@@ -1073,7 +1073,7 @@ __global__ void __launch_bounds__(1024) tc_tasks_kernel(const uint32_t* __restri
     ntl += tiles;
     nt += tiles * ((units + TC_SEG_UNITS - 1) / TC_SEG_UNITS);
     nr += (unsigned long long)n * len;
-    nm += (unsigned long long)n * units * 32u;  // 32 minima per pair and unit
+    nm += (unsigned long long)n * units * 8u;  // 8 minima per pair and unit
   }
   st[tid] = nt;
   sl[tid] = ntl;
@@ -1105,7 +1105,7 @@ __global__ void __launch_bounds__(1024) tc_tasks_kernel(const uint32_t* __restri
         const uint32_t u0 = sg * TC_SEG_UNITS, un = min(TC_SEG_UNITS, units - u0);
         tasks[bt] = make_uint4((bl + t) * 256u, roff8[l] + u0 * 256u, un | (u0 << 16), len);
         if (task_moff) {
-          const unsigned long long need = (unsigned long long)valid * un * 32u;
+          const unsigned long long need = (unsigned long long)valid * un * 8u;
           task_rows[bt] = valid;
           task_moff[bt] = bm + need <= minima_cap ? uint32_t(bm) : 0xFFFFFFFFu;  // beyond the buffer: this task leaves no minima
           bm += need;
@@ -1509,6 +1509,11 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     // Bound pass: each query's nearest owned lists until they hold 32 * keep rows, i.e. four times `keep` minima
     // (one per 8 rows), and room for twice that plus one long list per query.
     const uint32_t bound_rows = uint32_t(std::max(1024, 32 * keep));
+    // The tensor-core bound pass keeps one minimum per 32 rows and looks at three times the rows: the lists a query's
+    // best candidates come from are more than its nearest three or four, and a bound that has seen ten of them lets
+    // about half as many rows through the main pass (180 against 350 per query at keep = 100) for the same number
+    // of minima to select from.
+    const uint32_t bound_rows_tc = uint32_t(std::max(3072, 96 * keep));
     size_t mcap = 1024;
     while (mcap < 16384 && mcap < 2 * size_t(bound_rows / 8) + 512) mcap <<= 1;
     PairSet pa_set, pb_set;
@@ -1549,7 +1554,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       b.candidates = 0;
       FV_TRY(launch_block_scan(ctx, b, nq, use_pre));
     } else {
-      FV_TRY(bucket_pairs(ctx, ix, cells, nq, nprobe, bound_rows, pa_set, pairs_a));
+      FV_TRY(bucket_pairs(ctx, ix, cells, nq, nprobe, path == LIST_TENSOR ? bound_rows_tc : bound_rows, pa_set, pairs_a));
     }
     ListScanArgs la{};
     la.qtab = qtab;
@@ -1627,7 +1632,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       ga.g_q = g_q;
       ga.g_l = g_l;
       ga.g_base = g_base;
-      // ---- the bound pass on the tensor cores: the near pairs' rows scored, the minimum of every 8 kept
+      // ---- the bound pass on the tensor cores: the near pairs' rows scored, the minimum of every 32 kept
       if (!mini_bound) {
       size_t mfloats = std::max<size_t>(size_t(1) << 20, nq * 4096);
       mfloats = std::min<size_t>(mfloats, size_t(1) << 30);
@@ -1648,9 +1653,9 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       int g0 = 0;
       FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, nullptr, tasks, ntasks, ntasks + 1, nullptr, pool_cnt, 0, nullptr, nullptr, &g0,
                           ctx->scratch[6].as<float>(), task_moff, task_rows));
-      // bounds looked at per query: room for twice the 8-row minima of the rows the bound pass aims at
+      // bounds looked at per query: room for twice the 32-row minima of the rows the bound pass aims at
       int vcap = 2048;
-      while (vcap < 16384 && size_t(vcap) < 2 * size_t(bound_rows / 8) + 512) vcap <<= 1;
+      while (vcap < 16384 && size_t(vcap) < 2 * size_t(bound_rows_tc / 32) + 512) vcap <<= 1;
       const int wpb = vcap <= 4096 ? 4 : 1;  // warps (queries) per block, by the shared memory their bounds take
       const size_t ssmem = size_t(wpb) * vcap * sizeof(uint32_t);
       FV_CUDA(cudaFuncSetAttribute(tc_bound_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ssmem)));
