@@ -1292,9 +1292,9 @@ struct Tiling {
   size_t smem;
 };
 
-static int make_tiling(fv_ctx* ctx, int Kp, size_t nq, size_t rows, int scratch_bytes, Tiling* t) {
+static int make_tiling(fv_ctx* ctx, int Kp, size_t nq, size_t rows, int scratch_bytes, Tiling* t, int force_mh = 0) {
   t->KB = Kp / KBLK;
-  t->MH = t->KB <= 2 ? 2 : 1;
+  t->MH = force_mh ? force_mh : (t->KB <= 2 ? 2 : 1);
   const int rows_per_tile = 128 * t->MH;
   t->MT = int((nq + rows_per_tile - 1) / rows_per_tile);
   t->NT = int((rows + TILE_N - 1) / TILE_N);
@@ -1383,12 +1383,14 @@ int* tc_error_word(TcSide* tc) {
 
 int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_t a_rows, const float* d_thr,
                  const uint4* d_tasks, const uint32_t* d_ntasks, unsigned int* d_next_task, u64* d_pool, unsigned int* d_pool_cnt,
-                 unsigned int pool_cap, const uint32_t* d_row_owner, uint32_t* d_dropped, int* grid_out, float* d_minima,
-                 const uint32_t* d_task_moff, const uint32_t* d_task_rows) {
+                 unsigned int pool_cap, const uint32_t* d_row_owner, uint32_t* d_dropped, int* grid_out, int tile_rows,
+                 float* d_minima, const uint32_t* d_task_moff, const uint32_t* d_task_rows) {
   const int Kp = tc->Kp;
   if (Kp > 2 * KBLK) return fail(FV_ERR_UNSUPPORTED, "task mode of the tensor-core kernel covers padded dimensions up to 128");
+  if (tile_rows != 128 && tile_rows != 256) return fail(FV_ERR_ARG, "operand tiles have 128 or 256 rows");
   Tiling t{};
-  FV_TRY(make_tiling(ctx, Kp, 256, size_t(TILE_N) * 1024, 0, &t));  // stages, shared memory; the tiling itself is unused
+  // stages and shared memory for operand tiles of that height; the tiling itself is unused
+  FV_TRY(make_tiling(ctx, Kp, 256, size_t(TILE_N) * 1024, 0, &t, tile_rows == 128 ? 1 : 2));
   GemmParams gp{};
   fill_params(&gp, t, tc->n, a_rows, 0);
   gp.nchunks = 0;
@@ -1413,7 +1415,8 @@ int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_
   FV_TRY(make_tmap(&tmA, tc->bf16, const_cast<uint16_t*>(d_A), a_rows, Kp, 128));
   FV_TRY(make_tmap(&tmB, tc->bf16, tc->half.p, tc->n, Kp, TILE_N));
   FV_CUDA(cudaMemsetAsync(d_next_task, 0, sizeof(unsigned int), ctx->stream));
-  void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams) = gemm_topk_kernel<2, 2, true, true>;
+  void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams) =
+      tile_rows == 128 ? gemm_topk_kernel<1, 2, true, true> : gemm_topk_kernel<2, 2, true, true>;
   FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(t.smem)));
   kern<<<ctx->sm_count, NTHREADS, t.smem, ctx->stream>>>(tmA, tmB, gp);
   ctx->stats.launches++;

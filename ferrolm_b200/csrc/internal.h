@@ -194,7 +194,7 @@ void tc_info(const TcSide* tc, TcInfo* out);
 // Device word that a bounded wait inside the kernel sets when it runs out.  tc_list_pass does not clear it: a caller
 // that launches several passes clears it once (cudaMemsetAsync on the context's stream) and reads it after the last.
 int* tc_error_word(TcSide* tc);
-// Scores the 256 operand rows of every task against its run of side rows: d_tasks[t] = {first operand row, first side
+// Scores the tile_rows (256 or 128) operand rows of every task against its run of side rows: d_tasks[t] = {first operand row, first side
 // row (a multiple of 8), units of 256 side rows, valid side rows}.  Every (operand row, side row) whose score
 // ||b||^2 - 2<a, b> (L2; -<a, b> for inner product, operand rows being pre-scaled) is below d_thr[operand row] goes to
 // the survivor pool as (operand row << 32 | side row relative to the task's first): CTA c of *grid_out fills
@@ -207,7 +207,7 @@ int* tc_error_word(TcSide* tc);
 // d_task_moff[t] == 0xFFFFFFFF writes nothing.  d_thr and the pool are not used then.
 int tc_list_pass(fv_ctx* ctx, TcSide* tc, int metric, const uint16_t* d_A, size_t a_rows, const float* d_thr,
                  const uint4* d_tasks, const uint32_t* d_ntasks, unsigned int* d_next_task, u64* d_pool, unsigned int* d_pool_cnt,
-                 unsigned int pool_cap, const uint32_t* d_row_owner, uint32_t* d_dropped, int* grid_out,
+                 unsigned int pool_cap, const uint32_t* d_row_owner, uint32_t* d_dropped, int* grid_out, int tile_rows = 256,
                  float* d_minima = nullptr, const uint32_t* d_task_moff = nullptr, const uint32_t* d_task_rows = nullptr);
 
 // pads rows of `dim` floats to `pd` on the device (host or device source)

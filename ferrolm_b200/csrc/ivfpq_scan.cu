@@ -30,6 +30,7 @@
 //    per-query kernel.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -826,7 +827,8 @@ __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __res
                                                               const uint32_t* __restrict__ task_rows,
                                                               const float* __restrict__ add, const uint32_t* __restrict__ q_rows,
                                                               const uint32_t* __restrict__ q_cnt, int q_slots, int vcap,
-                                                              int keep, size_t nq, uint32_t* __restrict__ tau_bits) {
+                                                              int keep, size_t nq, uint32_t* __restrict__ tau_bits,
+                                                              int tile_shift) {
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const size_t q = blockIdx.x * size_t(blockDim.x >> 5) + w;
   if (q >= nq) return;
@@ -841,9 +843,9 @@ __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __res
     float my_add = 0.f;
     if (s0 + lane < np) {
       const uint32_t arow = q_rows[q * size_t(q_slots) + s0 + lane];
-      my_rt = arow & 255u;
-      my_t0 = tile_task0[arow >> 8];
-      my_t1 = tile_task0[(arow >> 8) + 1];
+      my_rt = arow & ((1u << tile_shift) - 1u);
+      my_t0 = tile_task0[arow >> tile_shift];
+      my_t1 = tile_task0[(arow >> tile_shift) + 1];
       my_add = add[arow];
     }
     // ... and the warp copies their minima, one pair and one of its tile's tasks (list segments) after the other
@@ -1064,8 +1066,9 @@ int build_reconstruction(fv_ctx* ctx, int metric, int pd, int m, int dsub, const
   return FV_OK;
 }
 
-// One block: the tasks of the tensor-core pass.  The n pairs of a list with len rows fill ceil(n / 256) operand tiles
-// of 256 gathered rows (a_off[l] is the list's first gathered row), and every tile meets the list's rows in segments
+// One block: the tasks of the tensor-core pass.  The n pairs of a list with len rows fill ceil(n / TR) operand tiles
+// of TR gathered rows (a_off[l] is the list's first gathered row; TR = 256, or 128 when the lists have few pairs each,
+// so that a half-empty tile does not cost a whole tile's multiplications), and every tile meets the list's rows in segments
 // of at most TC_SEG_UNITS units of 256 rows: one task per (tile, segment), so that no task is longer than a segment
 // and a few very long lists cannot hold up the CTAs that drew them.  A tile's tasks are consecutive;
 // tile_task0[tile] is the first (and tile_task0[tiles] the task count).  Lists are walked in `order` (longest
@@ -1081,7 +1084,7 @@ __global__ void __launch_bounds__(1024) tc_tasks_kernel(const uint32_t* __restri
                                                         uint32_t* __restrict__ tile_task0, uint32_t max_tasks,
                                                         uint32_t* __restrict__ ntasks, unsigned long long* __restrict__ rows,
                                                         uint32_t* __restrict__ task_moff, uint32_t* __restrict__ task_rows,
-                                                        uint32_t minima_cap) {
+                                                        uint32_t minima_cap, uint32_t TR) {  // TR: rows of an operand tile, 128 or 256
   __shared__ uint32_t st[1024], sl[1024];
   __shared__ unsigned long long sm8[1024];  // minima variant: floats of minima the tasks before a thread's need
   const int tid = threadIdx.x;
@@ -1093,7 +1096,7 @@ __global__ void __launch_bounds__(1024) tc_tasks_kernel(const uint32_t* __restri
     const size_t l = order[o];
     const uint32_t n = pair_off[l + 1] - pair_off[l], len = list_off[l + 1] - list_off[l];
     if (!n || !len) continue;
-    const uint32_t tiles = (n + 255u) / 256u, units = (len + 255u) / 256u;
+    const uint32_t tiles = (n + TR - 1u) / TR, units = (len + 255u) / 256u;
     ntl += tiles;
     nt += tiles * ((units + TC_SEG_UNITS - 1) / TC_SEG_UNITS);
     nr += (unsigned long long)n * len;
@@ -1117,17 +1120,17 @@ __global__ void __launch_bounds__(1024) tc_tasks_kernel(const uint32_t* __restri
   for (size_t o = l0; o < l1; ++o) {
     const size_t l = order[o];
     const uint32_t len = list_off[l + 1] - list_off[l], n = pair_off[l + 1] - pair_off[l];
-    a_off[l] = bl * 256u;
+    a_off[l] = bl * TR;
     if (!n || !len) continue;
-    const uint32_t tiles = (n + 255u) / 256u, units = (len + 255u) / 256u;
+    const uint32_t tiles = (n + TR - 1u) / TR, units = (len + 255u) / 256u;
     const uint32_t nseg = (units + TC_SEG_UNITS - 1) / TC_SEG_UNITS;
     for (uint32_t t = 0; t < tiles; ++t) {
       tile_task0[bl + t] = bt;
-      const uint32_t valid = min(256u, n - t * 256u);
+      const uint32_t valid = min(TR, n - t * TR);
       for (uint32_t sg = 0; sg < nseg; ++sg, ++bt) {
         if (bt >= max_tasks) continue;  // cannot happen with the caller's sizing; never write past the table
         const uint32_t u0 = sg * TC_SEG_UNITS, un = min(TC_SEG_UNITS, units - u0);
-        tasks[bt] = make_uint4((bl + t) * 256u, roff8[l] + u0 * 256u, un | (u0 << 16), len);
+        tasks[bt] = make_uint4((bl + t) * TR, roff8[l] + u0 * 256u, un | (u0 << 16), len);
         if (task_moff) {
           const unsigned long long need = (unsigned long long)valid * un * 8u;
           task_rows[bt] = valid;
@@ -1146,6 +1149,7 @@ __global__ void __launch_bounds__(1024) tc_tasks_kernel(const uint32_t* __restri
 }
 
 struct GatherArgs {
+  uint32_t tile_rows;          // rows of an operand tile (128 or 256): a list's rows are padded to whole tiles
   const uint32_t* pair_off;
   const uint32_t* list_off;
   const uint32_t* a_off;
@@ -1192,12 +1196,12 @@ __global__ void __launch_bounds__(256) tc_gather_kernel(GatherArgs a) {
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;
   const uint32_t p0 = a.pair_off[l], n = a.pair_off[l + 1] - p0;
   if (n == 0 || a.list_off[l + 1] == a.list_off[l]) return;
-  const uint32_t rows = (n + 255u) / 256u * 256u;
+  const uint32_t rows = (n + a.tile_rows - 1u) / a.tile_rows * a.tile_rows;
   const uint32_t a0 = a.a_off[l];
   const float* cen = a.centroids + l * size_t(a.pd);
   const float mul = a.is_l2 ? -2.f : -1.f;
   const int e_per = a.Kp >> 3;  // elements of a row per lane: a multiple of 8 (Kp is a multiple of 64)
-  for (uint32_t rb = blockIdx.y * 32 + w * 4; rb < rows; rb += gridDim.y * 32) {  // rows is a multiple of 256
+  for (uint32_t rb = blockIdx.y * 32 + w * 4; rb < rows; rb += gridDim.y * 32) {  // rows is a multiple of 128
     const uint32_t r = rb + grp, arow = a0 + r;
     const bool live = r < n;
     uint2 pr = make_uint2(0u, 0u);
@@ -1605,6 +1609,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
     float* thr = nullptr;
     uint32_t *g_q = nullptr, *g_l = nullptr, *a_off = nullptr, *ntasks = nullptr, *task_moff = nullptr, *task_rows = nullptr;
     uint32_t* tile_task0 = nullptr;
+    uint32_t tr_a = 256u, tr_b = 256u;  // operand tile rows of the bound pass and of the main pass
     float* g_base = nullptr;
     uint4* tasks = nullptr;
     unsigned int* pool_cnt = nullptr;
@@ -1617,7 +1622,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       const size_t Kp = size_t(ti.Kp);
       // gathered operand rows: every pair once, every list's rows rounded up to whole 256-row tiles
       a_rows = nq * size_t(nprobe) + 256 * std::min<size_t>(ix.nlist, nq * size_t(nprobe)) + 256;
-      const size_t max_tiles = a_rows / 256;
+      const size_t max_tiles = a_rows / 128;  // (tiles of 128 rows at the most)
       const size_t max_units = (size_t(ix.max_list_rows) + 255) / 256;
       max_tasks = max_tiles * std::max<size_t>(1, (max_units + TC_SEG_UNITS - 1) / TC_SEG_UNITS);
       if (max_tasks > 0x7FFFFFF0u) return fail(FV_ERR_UNSUPPORTED, "too many tasks for one tensor-core pass");
@@ -1665,6 +1670,15 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       ga.g_q = g_q;
       ga.g_l = g_l;
       ga.g_base = g_base;
+      // Operand tiles of 128 rows instead of 256 when a list has few pairs: the pass costs a tile's multiplications
+      // whatever the tile holds.  Estimated from the averages (pairs per list), per pass.
+      const double avg_len = double(ix.nrows) / double(std::max<size_t>(1, ix.nlist));
+      const double pairs_b_per_list = double(nq) * double(nprobe) / double(std::max<size_t>(1, ix.nlist));
+      const double lists_a = std::min(double(nprobe), std::max(1.0, std::ceil(double(bound_rows_tc) / std::max(1.0, avg_len))));
+      const double pairs_a_per_list = double(nq) * lists_a / double(std::max<size_t>(1, ix.nlist));
+      const double tr_max = 1000.0;  // 128-row tiles never issue more MMA rows than 256-row ones, only more B-tile reads
+      tr_a = pairs_a_per_list <= tr_max ? 128u : 256u;
+      tr_b = pairs_b_per_list <= tr_max ? 128u : 256u;
       // ---- the bound pass on the tensor cores: the near pairs' rows scored, the minimum of every 32 kept
       if (!mini_bound) {
       size_t mfloats = std::max<size_t>(size_t(1) << 20, nq * 4096);
@@ -1673,8 +1687,9 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       FV_CUDA(cudaMemsetAsync(q_cnt, 0, nq * sizeof(uint32_t), ctx->stream));
       tc_tasks_kernel<<<1, 1024, 0, ctx->stream>>>(pa_set.pair_off, ix.list_off, ix.roff8, ix.roff8 + ix.nlist + 1, ix.nlist, tasks,
                                                    a_off, tile_task0, uint32_t(max_tasks), ntasks, nullptr, task_moff, task_rows,
-                                                   uint32_t(mfloats));
+                                                   uint32_t(mfloats), tr_a);
       GatherArgs gb = ga;
+      gb.tile_rows = tr_a;
       gb.pair_off = pa_set.pair_off;
       gb.pairs = pairs_a;
       gb.q_rows = q_rows;
@@ -1685,7 +1700,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       FV_CUDA(cudaGetLastError());
       int g0 = 0;
       FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, nullptr, tasks, ntasks, ntasks + 1, nullptr, pool_cnt, 0, nullptr, nullptr, &g0,
-                          ctx->scratch[6].as<float>(), task_moff, task_rows));
+                          int(tr_a), ctx->scratch[6].as<float>(), task_moff, task_rows));
       // bounds looked at per query: room for twice the 32-row minima of the rows the bound pass aims at
       int vcap = 2048;
       while (vcap < 16384 && size_t(vcap) < 2 * size_t(bound_rows_tc / 32) + 512) vcap <<= 1;
@@ -1693,7 +1708,8 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       const size_t ssmem = size_t(wpb) * vcap * sizeof(uint32_t);
       FV_CUDA(cudaFuncSetAttribute(tc_bound_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ssmem)));
       tc_bound_select_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, ssmem, ctx->stream>>>(
-          ctx->scratch[6].as<float>(), tasks, tile_task0, task_moff, task_rows, thr, q_rows, q_cnt, q_slots, vcap, keep, nq, tau_bits);
+          ctx->scratch[6].as<float>(), tasks, tile_task0, task_moff, task_rows, thr, q_rows, q_cnt, q_slots, vcap, keep, nq, tau_bits,
+          tr_a == 128u ? 7 : 8);
       ctx->stats.launches++;
       FV_CUDA(cudaGetLastError());
       }
@@ -1745,7 +1761,8 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       stage_mark(ctx);  // 3
     } else {
       tc_tasks_kernel<<<1, 1024, 0, ctx->stream>>>(pb_set.pair_off, ix.list_off, ix.roff8, ix.roff8 + ix.nlist + 1, ix.nlist, tasks,
-                                                   a_off, tile_task0, uint32_t(max_tasks), ntasks, d_rows + 1, nullptr, nullptr, 0u);
+                                                   a_off, tile_task0, uint32_t(max_tasks), ntasks, d_rows + 1, nullptr, nullptr, 0u, tr_b);
+      ga.tile_rows = tr_b;
       ga.pair_off = pb_set.pair_off;
       ga.pairs = pairs_b;
       tc_gather_kernel<<<dim3(unsigned(ix.nlist), 4), 256, 0, ctx->stream>>>(ga);
@@ -1754,7 +1771,7 @@ int ivfpq_scan(fv_ctx* ctx, const ScanIndex& ix, const float* q, size_t nq, cons
       stage_mark(ctx);  // 2
       FV_CUDA(cudaMemsetAsync(dropped, 0, nq * sizeof(uint32_t), ctx->stream));
       FV_TRY(tc_list_pass(ctx, ix.recon, ix.metric, qg, a_rows, thr, tasks, ntasks, ntasks + 1, ctx->scratch[15].as<u64>(), pool_cnt,
-                          pool_cap, g_q, dropped, &tc_grid));
+                          pool_cap, g_q, dropped, &tc_grid, int(tr_b)));
       stage_mark(ctx);  // 3
       ra.pool = ctx->scratch[15].as<u64>();
       ra.pool_cnt = pool_cnt;
