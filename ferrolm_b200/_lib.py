@@ -110,6 +110,7 @@ SIGNATURES = {
     "fv_ivfpq_save": (_i, [_vp, _vp, _sz, C.POINTER(_sz)]),
     "fv_ivfpq_load": (_i, [_vp, _vp, _sz, _pp]),
     "fv_hnsw_build": (_i, [_vp, _i, _u32, _vp, _sz, C.POINTER(fv_hnsw_params), _i, _pp]),
+    "fv_hnsw_build_batched": (_i, [_vp, _i, _u32, _vp, _sz, C.POINTER(fv_hnsw_params), _sz, _sz, _pp]),
     "fv_hnsw_free": (None, [_vp]),
     "fv_hnsw_len": (_sz, [_vp]),
     "fv_hnsw_reachable": (_sz, [_vp]),

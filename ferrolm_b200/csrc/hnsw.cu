@@ -23,7 +23,7 @@
 #include <mutex>
 #include <thread>
 
-#include "internal.h"
+#include "hnsw.cuh"
 
 FV_BOUNDS_TU(hnsw)
 
@@ -38,31 +38,6 @@ struct HnswDev {
   uint32_t ep;
   size_t n;
 };
-
-__device__ __forceinline__ uint32_t hash_slot(uint32_t x, int log2slots) { return (x * 2654435761u) >> (32 - log2slots); }
-
-// true if x was not in the table (and is now)
-__device__ __forceinline__ bool visit(uint32_t* table, int log2slots, uint32_t x) {
-  const uint32_t mask = (1u << log2slots) - 1u;
-  uint32_t s = hash_slot(x, log2slots);
-  for (uint32_t probe = 0; probe <= mask; ++probe) {
-    const uint32_t old = atomicCAS(table + s, 0xFFFFFFFFu, x);
-    if (old == 0xFFFFFFFFu) return true;
-    if (old == x) return false;
-    s = (s + 1) & mask;
-  }
-  return false;  // full table: cannot happen below the half-full limit
-}
-
-// The reference keeps two heaps: an entry pushed out of the result heap stays in the candidate heap, and because its
-// loop stops only on a STRICTLY larger distance (hnsw.rs:195-197), such an entry is still expanded if its distance
-// equals the worst kept distance when its turn comes.  The beam below is one list, so the unexpanded entries it
-// pushes out while their distance equals the new worst distance are remembered here (ids; all share that distance)
-// and take their turn in (distance, id) order; the list is dropped as soon as the worst distance goes down.
-static constexpr int TIED_CAP = 64;
-
-// list entry: order bits of the distance (32) | id (31) | expanded (1)
-__device__ __forceinline__ u64 beam_key(float d, uint32_t id) { return (u64(order_bits(d)) << 32) | (u64(id) << 1); }
 
 template <bool IS_L2>
 __global__ void __launch_bounds__(256, 4)
@@ -301,27 +276,6 @@ static inline bool h_less(const HNb& a, const HNb& b) {
 
 }  // namespace fv
 
-struct fv_hnsw {
-  fv_ctx* ctx = nullptr;
-  ~fv_hnsw() {
-    d_data.release(); d_links0.release(); d_upper_off.release(); d_upper_flat.release();
-    if (ctx) fv::ctx_release(ctx);
-  }
-  int metric = 0;
-  uint32_t dim = 0, pd = 0;
-  size_t m = 0, m0 = 0;
-  uint32_t ep = 0;
-  size_t top = 0;
-  // host copies (the file's content)
-  std::vector<float> data;
-  std::vector<uint8_t> levels;
-  std::vector<uint32_t> links0;
-  std::vector<std::vector<uint32_t>> upper;  // per node: concatenated (count, ids...) per layer, fixed stride m+1
-  // device copies
-  DevBuf d_data, d_links0, d_upper_off, d_upper_flat;
-  size_t n() const { return levels.size(); }
-};
-
 namespace fv {
 
 // upper[node] holds `level` blocks of (m + 1) u32: count then ids.
@@ -342,15 +296,16 @@ static void flatten_upper(const fv_hnsw* h, std::vector<uint32_t>& off, std::vec
   off[n] = uint32_t(flat.size());
 }
 
-static int upload_graph(fv_hnsw* h) {
+int upload_graph(fv_hnsw* h, bool with_data) {
   fv_ctx* ctx = h->ctx;
   std::vector<uint32_t> off, flat;
   flatten_upper(h, off, flat);
-  FV_TRY(h->d_data.reserve(h->data.size() * 4 + 16));
+  if (with_data) FV_TRY(h->d_data.reserve(h->data.size() * 4 + 16));
   FV_TRY(h->d_links0.reserve(h->links0.size() * 4 + 16));
   FV_TRY(h->d_upper_off.reserve(off.size() * 4 + 16));
   FV_TRY(h->d_upper_flat.reserve(flat.size() * 4 + 16));
-  FV_CUDA(cudaMemcpyAsync(h->d_data.p, h->data.data(), h->data.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+  if (with_data)
+    FV_CUDA(cudaMemcpyAsync(h->d_data.p, h->data.data(), h->data.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
   FV_CUDA(cudaMemcpyAsync(h->d_links0.p, h->links0.data(), h->links0.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
   FV_CUDA(cudaMemcpyAsync(h->d_upper_off.p, off.data(), off.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
   if (!flat.empty())
@@ -628,21 +583,17 @@ static int hnsw_search_dev(fv_hnsw* h, const float* d_queries, size_t nq, size_t
   return bounds_report_hnsw();
 }
 
-}  // namespace fv
-
-extern "C" {
-
-int fv_hnsw_build(fv_ctx* ctx, int metric, uint32_t dim, const float* vectors, size_t n, const fv_hnsw_params* p,
-                  int threads, fv_hnsw** out) {
-  if (!ctx || !p || !out || (!vectors && n) || dim == 0 || (metric != FV_L2 && metric != FV_INNER_PRODUCT))
-    return fv::fail(FV_ERR_ARG, "fv_hnsw_build: bad argument");
-  if (p->m < 2 || p->m > 64) return fv::fail(FV_ERR_UNSUPPORTED, "m must be in 2..64");
+int hnsw_new(fv_ctx* ctx, int metric, uint32_t dim, const float* vectors, size_t n, const fv_hnsw_params* p,
+             std::unique_ptr<fv_hnsw>& out) {
+  if (!ctx || !p || (!vectors && n) || dim == 0 || (metric != FV_L2 && metric != FV_INNER_PRODUCT))
+    return fail(FV_ERR_ARG, "hnsw build: bad argument");
+  if (p->m < 2 || p->m > 64) return fail(FV_ERR_UNSUPPORTED, "m must be in 2..64");
   auto h = std::unique_ptr<fv_hnsw>(new fv_hnsw());
   h->ctx = ctx;
-  fv::ctx_retain(ctx);
+  ctx_retain(ctx);
   h->metric = metric;
   h->dim = dim;
-  h->pd = uint32_t(fv::padded(dim));
+  h->pd = uint32_t(padded(dim));
   h->m = p->m;
   h->m0 = 2 * p->m;
   h->data.assign(n * size_t(h->pd), 0.f);
@@ -665,6 +616,19 @@ int fv_hnsw_build(fv_ctx* ctx, int metric, uint32_t dim, const float* vectors, s
   h->links0.assign(n * (h->m0 + 1), 0);
   h->ep = 0;
   h->top = n ? h->levels[0] : 0;
+  out = std::move(h);
+  return FV_OK;
+}
+
+}  // namespace fv
+
+extern "C" {
+
+int fv_hnsw_build(fv_ctx* ctx, int metric, uint32_t dim, const float* vectors, size_t n, const fv_hnsw_params* p,
+                  int threads, fv_hnsw** out) {
+  if (!out) return fv::fail(FV_ERR_ARG, "fv_hnsw_build: bad argument");
+  std::unique_ptr<fv_hnsw> h;
+  FV_TRY(fv::hnsw_new(ctx, metric, dim, vectors, n, p, h));
   if (n > 1) {
     fv::Builder b;
     b.h = h.get();

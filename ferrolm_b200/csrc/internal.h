@@ -151,6 +151,7 @@ void stage_mark_outer(fv_ctx* ctx);  // the enclosing call's own marks
 // the last call; always FV_OK in the normal build.  Call after the stream has been synchronized.
 int bounds_report_ivfpq_scan();
 int bounds_report_hnsw();
+int bounds_report_hnsw_build();
 
 int comm_all_gather(fv_ctx* ctx, const void* d_send, void* d_recv, size_t bytes);
 void comm_destroy(fv_ctx* ctx);

@@ -443,6 +443,19 @@ class Hnsw:
                                   C.byref(h)))
         return Hnsw(ctx, h, dim)
 
+    @staticmethod
+    def build_batched(ctx: Context, metric: int, dim: int, vectors, p: HnswParams = HnswParams(), max_batch: int = 8192,
+                      divisor: int = 32) -> "Hnsw":
+        """The construction (hnsw.rs:85-129, :244-320) on the GPU, in id order in batches of at most `max_batch` nodes
+        and at most 1/`divisor` of the nodes already in.  Deterministic; `max_batch=1` gives the graph of the
+        reference's single-thread build byte for byte."""
+        v = _host_f32(vectors).reshape(-1, dim)
+        cp = fv_hnsw_params(p.m, p.ef_construction, p.seed)
+        h = C.c_void_p()
+        check(lib().fv_hnsw_build_batched(ctx._h, metric, dim, v.ctypes.data_as(C.c_void_p), v.shape[0], C.byref(cp),
+                                          max_batch, divisor, C.byref(h)))
+        return Hnsw(ctx, h, dim)
+
     def __len__(self) -> int:
         return lib().fv_hnsw_len(self._h)
 

@@ -194,6 +194,14 @@ typedef struct fv_hnsw_params { /* HnswParams, hnsw.rs:24-40; defaults m=16, ef_
 /* Graph construction runs on the host cores (`threads` of them, as the reference's pool; 1 = deterministic). */
 int fv_hnsw_build(fv_ctx* ctx, int metric, uint32_t dim, const float* vectors, size_t n,
                   const fv_hnsw_params* p, int threads, fv_hnsw** out);                /* build :85 */
+/* Graph construction on the GPU, batch-synchronous (build :85, insert :244, select :230, add_links :294).  Nodes go in
+ * in id order in batches of at most `max_batch` nodes and at most 1/`divisor` of the nodes already in; within a batch
+ * every node searches the graph as it stood when the batch began, then the reverse links are made target by target
+ * with the sources in ascending id.  The same input always gives the same graph; with max_batch = 1 it is byte for
+ * byte the graph of the reference's single-thread build.  A wider batch is what `threads` is to the reference's
+ * build: more nodes in flight that do not see one another.  Suggested: max_batch 8192, divisor 32. */
+int fv_hnsw_build_batched(fv_ctx* ctx, int metric, uint32_t dim, const float* vectors, size_t n,
+                          const fv_hnsw_params* p, size_t max_batch, size_t divisor, fv_hnsw** out);
 void fv_hnsw_free(fv_hnsw* ix);
 size_t fv_hnsw_len(const fv_hnsw* ix);                                                /* len :131 */
 uint32_t fv_hnsw_dim(const fv_hnsw* ix);                                              /* field dim :44 */

@@ -843,6 +843,42 @@ struct Hnsw {
     }
   }
 
+  // The first half of insert (hnsw.rs:244-279) for the batch-synchronous build: the descent, the per-layer
+  // search_layer and select, and the node's own lists; the reverse links (hnsw.rs:280-282) are only recorded as
+  // (target, layer, source), and the entry point is left alone.
+  struct PendingLink {
+    uint32_t target, layer, source;
+  };
+  void insert_forward(uint32_t id, size_t ef, Visited& vs, std::vector<PendingLink>& pending) {
+    std::vector<float> q(vec(id), vec(id) + pd);
+    size_t level = levels[id];
+    Neighbor cur{ep, dist(q.data(), ep)};
+    std::vector<uint32_t> nb;
+    for (size_t layer = top; layer >= level + 1; layer--) {
+      bool changed = true;
+      while (changed) {
+        changed = false;
+        neighbors(cur.id, layer, false, nb);
+        for (uint32_t x : nb) {
+          float d = dist(q.data(), x);
+          if (d < cur.distance) {
+            cur = {x, d};
+            changed = true;
+          }
+        }
+      }
+    }
+    std::vector<Neighbor> entry{cur};
+    for (size_t layer = std::min(level, top) + 1; layer-- > 0;) {
+      auto found = search_layer(q.data(), entry, ef, layer, false, vs);
+      size_t cap = layer == 0 ? m0 : m;
+      auto chosen = select(found, cap);
+      add_links(id, layer, chosen, cap);
+      for (uint32_t n : chosen) pending.push_back({n, uint32_t(layer), id});
+      entry = std::move(found);
+    }
+  }
+
   // hnsw.rs:323-351
   std::vector<Neighbor> search(const float* query, size_t k, size_t ef, Visited& vs, uint64_t* n_dist = nullptr,
                                uint64_t* n_expand = nullptr) {
@@ -921,8 +957,8 @@ struct Hnsw {
   }
 };
 
-Hnsw* hnsw_build(int threads, int metric, size_t dim, const float* vectors, size_t n, size_t m, size_t efc,
-                 uint64_t seed) {  // hnsw.rs:85-129
+// hnsw.rs:85-112: the rows padded, the levels drawn, every list empty, node 0 the entry point
+static Hnsw* hnsw_prepare(int metric, size_t dim, const float* vectors, size_t n, size_t m, uint64_t seed) {
   auto* h = new Hnsw();
   h->metric = metric;
   h->dim = dim;
@@ -945,6 +981,12 @@ Hnsw* hnsw_build(int threads, int metric, size_t dim, const float* vectors, size
   h->locks.reset(new std::mutex[std::max<size_t>(n, 1)]);
   h->ep = 0;
   h->top = n ? h->levels[0] : 0;
+  return h;
+}
+
+Hnsw* hnsw_build(int threads, int metric, size_t dim, const float* vectors, size_t n, size_t m, size_t efc,
+                 uint64_t seed) {  // hnsw.rs:85-129
+  Hnsw* h = hnsw_prepare(metric, dim, vectors, n, m, seed);
   if (n <= 1) return h;
   std::atomic<size_t> next{1};
   int nt = std::max(threads, 1);
@@ -956,6 +998,44 @@ Hnsw* hnsw_build(int threads, int metric, size_t dim, const float* vectors, size
       h->insert(uint32_t(i), efc, vs);
     }
   });
+  return h;
+}
+
+// The batch-synchronous order of the same construction, as the GPU build of the product runs it: nodes go in in id
+// order in batches of at most `max_batch` nodes and at most 1/`divisor` of the nodes already in, a node whose level
+// is above the current top layer going in alone.  Within a batch every node runs the first half of insert
+// (hnsw.rs:244-279) against the graph as it stood when the batch began; then the reverse links
+// (add_links(n, layer, [id]), hnsw.rs:280-282) are made in ascending source id, and the entry point moves
+// (hnsw.rs:285-289).  With max_batch = 1 this is hnsw_build with one thread.
+Hnsw* hnsw_build_batched(int metric, size_t dim, const float* vectors, size_t n, size_t m, size_t efc, uint64_t seed,
+                         size_t max_batch, size_t divisor) {
+  Hnsw* h = hnsw_prepare(metric, dim, vectors, n, m, seed);
+  if (n <= 1) return h;
+  Hnsw::Visited vs;
+  std::vector<Hnsw::PendingLink> pending;
+  size_t inserted = 1;
+  while (inserted < n) {
+    size_t b = std::max<size_t>(1, std::min(max_batch, inserted / std::max<size_t>(1, divisor)));
+    b = std::min(b, n - inserted);
+    if (h->levels[inserted] > h->top) {
+      b = 1;
+    } else {
+      for (size_t j = 1; j < b; j++)
+        if (h->levels[inserted + j] > h->top) {
+          b = j;
+          break;
+        }
+    }
+    pending.clear();
+    for (size_t j = 0; j < b; j++) h->insert_forward(uint32_t(inserted + j), efc, vs, pending);
+    // pending is in ascending source id already (nodes were taken in id order)
+    for (const auto& e : pending) h->add_links(e.target, e.layer, {e.source}, e.layer == 0 ? h->m0 : h->m);
+    if (h->levels[inserted] > h->top) {
+      h->ep = uint32_t(inserted);
+      h->top = h->levels[inserted];
+    }
+    inserted += b;
+  }
   return h;
 }
 
@@ -1216,6 +1296,10 @@ void* orc_ivfpq_load(const uint8_t* bytes, size_t len, char* err, size_t errcap)
 void* orc_hnsw_build(int metric, size_t dim, const float* v, size_t n, size_t m, size_t efc, uint64_t seed,
                      int threads) {
   return hnsw_build(threads, metric, dim, v, n, m, efc, seed);
+}
+void* orc_hnsw_build_batched(int metric, size_t dim, const float* v, size_t n, size_t m, size_t efc, uint64_t seed,
+                             size_t max_batch, size_t divisor) {
+  return hnsw_build_batched(metric, dim, v, n, m, efc, seed, max_batch, divisor);
 }
 void orc_hnsw_free(void* p) { delete static_cast<Hnsw*>(p); }
 size_t orc_hnsw_len(void* p) { return static_cast<Hnsw*>(p)->len(); }

@@ -77,6 +77,7 @@ def lib():
             "orc_ivfpq_save": (sz, [vp, vp, sz]),
             "orc_ivfpq_load": (vp, [vp, sz, C.c_char_p, sz]),
             "orc_hnsw_build": (vp, [i, sz, f32p, sz, sz, sz, u64, i]),
+            "orc_hnsw_build_batched": (vp, [i, sz, f32p, sz, sz, sz, u64, sz, sz]),
             "orc_hnsw_free": (None, [vp]),
             "orc_hnsw_len": (sz, [vp]),
             "orc_hnsw_reachable": (sz, [vp]),
@@ -311,6 +312,14 @@ class Hnsw:
         """`threads=1` is the only deterministic build (hnsw.rs:117-127 races by design)."""
         v = _f32(vectors).reshape(-1, dim)
         return Hnsw(lib().orc_hnsw_build(metric, dim, _p(v), v.shape[0], m, ef_construction, seed, threads), dim)
+
+    @staticmethod
+    def build_batched(metric: int, dim: int, vectors, m: int = 16, ef_construction: int = 200, seed: int = 1,
+                      max_batch: int = 8192, divisor: int = 32) -> "Hnsw":
+        """The batch-synchronous order of the construction (what the product's GPU build runs); deterministic."""
+        v = _f32(vectors).reshape(-1, dim)
+        return Hnsw(lib().orc_hnsw_build_batched(metric, dim, _p(v), v.shape[0], m, ef_construction, seed, max_batch,
+                                                 divisor), dim)
 
     def __len__(self):
         return lib().orc_hnsw_len(self._h)

@@ -1,0 +1,108 @@
+"""Hnsw construction on the GPU (fv_hnsw_build_batched) against the oracle: byte-identical graphs.
+
+The reference's own build (src/vector/hnsw.rs:85-129) is deterministic only with one thread; the batch-synchronous
+order is restated in the oracle (Hnsw.build_batched), and with batches of one node it IS the single-thread build."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+L2, IP = 0, 1
+
+
+@pytest.fixture(scope="module")
+def fv():
+    import ferrolm_b200
+
+    return ferrolm_b200
+
+
+@pytest.fixture(scope="module")
+def ctx(fv):
+    c = fv.Context(0)
+    yield c
+    c.close()
+
+
+@pytest.mark.parametrize("metric", [L2, IP])
+def test_batches_of_one_node_give_the_single_thread_graph(fv, oracle, ctx, metric):
+    dim = 24
+    base = oracle.testdata(1500, dim, 31)
+    if metric == IP:
+        base = oracle.normalize(base)
+    g = fv.Hnsw.build_batched(ctx, metric, dim, base, fv.HnswParams(8, 40, 3), max_batch=1, divisor=1)
+    o = oracle.Hnsw.build(metric, dim, base, m=8, ef_construction=40, seed=3, threads=1)
+    assert g.save() == o.save()
+    assert ctx.stats()["uncertified"] == 0
+
+
+@pytest.mark.parametrize("metric,dim,m,efc,max_batch,divisor", [
+    (L2, 40, 8, 40, 64, 8),
+    (IP, 40, 8, 40, 500, 4),
+    (L2, 13, 4, 20, 4096, 2),     # a padded dimension, short lists, half of the graph per batch
+    (L2, 96, 16, 200, 256, 32),   # the default parameters
+])
+def test_batched_build_equals_the_oracles_batched_build(fv, oracle, ctx, metric, dim, m, efc, max_batch, divisor):
+    base = oracle.testdata(4000, dim, 77)
+    if metric == IP:
+        base = oracle.normalize(base)
+    g = fv.Hnsw.build_batched(ctx, metric, dim, base, fv.HnswParams(m, efc, 9), max_batch=max_batch, divisor=divisor)
+    o = oracle.Hnsw.build_batched(metric, dim, base, m=m, ef_construction=efc, seed=9, max_batch=max_batch,
+                                  divisor=divisor)
+    assert g.save() == o.save()
+    assert g.reachable() == o.reachable() and g.mean_degree() == o.mean_degree()
+    q = oracle.testdata(64, dim, 78)
+    got, gc = g.search_batch(q, 10, 64)
+    want, wc = o.search_batch(q, 10, 64)
+    assert np.array_equal(gc, wc) and np.array_equal(got["id"], want["id"])
+    assert np.array_equal(got["distance"].view(np.uint32), want["distance"].view(np.uint32))
+
+
+def test_batched_build_on_integer_data_with_distance_ties(fv, oracle, ctx):
+    # clipped-integer rows: many exactly equal distances in the beam, in select and in the re-selection of add_links
+    dim = 32
+    base = fv.datagen(0, 5, 6000, dim, 16)
+    g = fv.Hnsw.build_batched(ctx, L2, dim, base, fv.HnswParams(8, 50, 1), max_batch=128, divisor=16)
+    o = oracle.Hnsw.build_batched(L2, dim, base, m=8, ef_construction=50, seed=1, max_batch=128, divisor=16)
+    if ctx.stats()["uncertified"] == 0:  # no tie list overflowed: the graphs are the same
+        assert g.save() == o.save()
+    assert g.reachable() >= int(0.95 * o.reachable())
+
+
+def test_batched_build_is_deterministic_and_connected(fv, oracle, ctx):
+    # tests/vector.rs:104-125 (text-embedding-like rows) on the GPU build with its suggested batch sizes
+    n, nq, dim = 5000, 200, 384
+    rng = oracle.Rng(7)
+    common = np.array([np.float32(rng.normal()) * np.float32(3.0) for _ in range(dim)], dtype=np.float32)
+
+    def sample(count):
+        v = oracle.testdata(count, dim, rng.next_u64())
+        return oracle.normalize((v / np.float32(3.0) + common).astype(np.float32))
+
+    base, queries = sample(n), sample(nq)
+    flat = oracle.FlatIndex(IP, dim)
+    flat.add(base)
+    t = flat.search_batch(queries, 10)[0]["id"]
+    h = fv.Hnsw.build_batched(ctx, IP, dim, base, fv.HnswParams())
+    assert h.reachable() >= n - 2
+    out, counts = h.search_batch(queries, 10, 256)
+    assert fv.recall(out, counts, t, 10) >= 0.999
+    again = fv.Hnsw.build_batched(ctx, IP, dim, base, fv.HnswParams())
+    assert again.save() == h.save()
+    o = oracle.Hnsw.build_batched(IP, dim, base, m=16, ef_construction=200, seed=1)
+    assert o.save() == h.save()
+
+
+def test_batched_build_edge_cases(fv, oracle, ctx):
+    dim = 8
+    one = oracle.testdata(1, dim, 1)
+    h = fv.Hnsw.build_batched(ctx, L2, dim, one, fv.HnswParams(4, 10, 1))
+    got, gc = h.search_batch(one, 3, 5)
+    assert gc[0] == 1 and got["id"][0, 0] == 0
+    empty = fv.Hnsw.build_batched(ctx, L2, dim, np.zeros((0, dim), np.float32), fv.HnswParams(4, 10, 1))
+    assert len(empty) == 0 and empty.search_batch(one, 3, 5)[1][0] == 0
+    two = oracle.testdata(2, dim, 2)
+    h = fv.Hnsw.build_batched(ctx, L2, dim, two, fv.HnswParams(4, 10, 1))
+    assert h.save() == oracle.Hnsw.build(L2, dim, two, m=4, ef_construction=10, seed=1).save()
+    with pytest.raises(fv.FerrovecError):
+        fv.Hnsw.build_batched(ctx, L2, dim, two, fv.HnswParams(4, 10, 1), max_batch=0)
