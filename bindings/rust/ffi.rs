@@ -56,6 +56,7 @@ extern "C" {
     pub fn fv_ivfpq_dim(ix: *const c_void) -> u32;
     // Hnsw (hnsw.rs)
     pub fn fv_hnsw_build(ctx: *mut c_void, metric: c_int, dim: u32, vectors: *const f32, n: usize, p: *const FvHnswParams, threads: c_int, out: *mut *mut c_void) -> c_int;
+    pub fn fv_hnsw_build_batched(ctx: *mut c_void, metric: c_int, dim: u32, vectors: *const f32, n: usize, p: *const FvHnswParams, max_batch: usize, divisor: usize, out: *mut *mut c_void) -> c_int;
     pub fn fv_hnsw_free(ix: *mut c_void);
     pub fn fv_hnsw_len(ix: *const c_void) -> usize;
     pub fn fv_hnsw_reachable(ix: *const c_void) -> usize;

@@ -1,6 +1,8 @@
-//! `src/vector/hnsw.rs` over libferrovec: the graph is built on the host by the library (the reference's
-//! algorithm, `pool.threads()` threads; one thread gives the reference's single-thread graph byte for byte) and
-//! searched on the GPU, one warp per query.  Public surface as in the reference (hnsw.rs:24-466).
+//! `src/vector/hnsw.rs` over libferrovec: the graph is built by the library, on the GPU in batches (`build`, what a
+//! pool of many threads is to the reference: nodes in flight that do not see one another, but with a result that
+//! does not depend on timing) or on the host cores (`build_on_host`: the reference's algorithm on `pool.threads()`
+//! threads; one thread gives the reference's single-thread graph byte for byte), and searched on the GPU, one warp
+//! per query.  Public surface as in the reference (hnsw.rs:24-466).
 use super::ffi;
 use super::{Metric, Neighbor};
 use crate::pool::Pool;
@@ -35,7 +37,20 @@ impl Hnsw {
         Hnsw { metric, dim: unsafe { ffi::fv_hnsw_dim(h) } as usize, h }
     }
 
+    /// hnsw.rs:85.  A pool of one thread asks for the deterministic single-thread graph and gets it (batches of one
+    /// node); any other pool gets batches of up to 8192 nodes and 1/32 of the graph.
     pub fn build(pool: &Pool, metric: Metric, dim: usize, vectors: &[f32], p: HnswParams) -> Hnsw {
+        let fp = ffi::FvHnswParams { m: p.m, ef_construction: p.ef_construction, seed: p.seed };
+        let (max_batch, divisor) = if pool.threads() == 1 { (1, 1) } else { (8192, 32) };
+        let mut h = std::ptr::null_mut();
+        ffi::check(unsafe {
+            ffi::fv_hnsw_build_batched(ffi::gpu_ctx(), metric.code() as i32, dim as u32, vectors.as_ptr(), vectors.len() / dim, &fp, max_batch, divisor, &mut h)
+        });
+        Hnsw::wrap(h)
+    }
+
+    /// The same construction on the host cores, with the reference's locks and its timing-dependent result.
+    pub fn build_on_host(pool: &Pool, metric: Metric, dim: usize, vectors: &[f32], p: HnswParams) -> Hnsw {
         let fp = ffi::FvHnswParams { m: p.m, ef_construction: p.ef_construction, seed: p.seed };
         let mut h = std::ptr::null_mut();
         ffi::check(unsafe {

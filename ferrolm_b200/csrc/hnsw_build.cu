@@ -25,6 +25,7 @@ FV_BOUNDS_TU(hnsw_build)
 namespace fv {
 
 static constexpr uint32_t NIL = 0xFFFFFFFFu;
+static constexpr int BUILD_BLOCKS_PER_SM = 3;  // of 256 threads: 24 warps per SM at up to 80 registers
 static constexpr int SRC_CAP = 128;  // sources of one chain sorted in shared memory; longer chains are walked again per source
 
 struct Edge {
@@ -204,10 +205,11 @@ __device__ __forceinline__ int select_links(const BuildDev& g, const u64* cand, 
 
 // flags: [0] visited-table overflows, [1] tie lists that overflowed, [2] edges that did not fit
 template <bool IS_L2>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, BUILD_BLOCKS_PER_SM)
     hnsw_insert_kernel(BuildDev g, uint32_t lo, uint32_t hi, uint32_t ep, int top, int ef, int log2slots,
                        uint32_t* __restrict__ tables, Edge* __restrict__ edges, uint32_t* __restrict__ edge_cnt,
-                       uint32_t edge_cap, uint32_t* __restrict__ head, unsigned long long* __restrict__ flags) {
+                       uint32_t* __restrict__ next_node, uint32_t edge_cap, uint32_t* __restrict__ head,
+                       unsigned long long* __restrict__ flags) {
   unsigned char* smem_raw = dyn_smem();
   const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t list_bytes = (size_t(ef) * 8 + 15) & ~size_t(15);
@@ -218,10 +220,16 @@ __global__ void __launch_bounds__(256, 2)
   u64* best = reinterpret_cast<u64*>(mine + size_t(g.pd) * 8);
   uint32_t* tied = reinterpret_cast<uint32_t*>(mine + size_t(g.pd) * 8 + list_bytes);
   uint32_t* sel = tied + TIED_CAP;
-  const uint32_t gw = blockIdx.x * W + w, total_warps = gridDim.x * W;
+  const uint32_t gw = blockIdx.x * W + w;
   uint32_t* table = tables + (size_t(gw) << log2slots);
 
-  for (uint32_t id = lo + gw; id < hi; id += total_warps) {
+  // nodes are drawn from a counter: a search takes anything from a few to a few hundred expansions, and which warp
+  // inserts which node changes nothing in the result
+  for (;;) {
+    uint32_t id = 0;
+    if (lane == 0) id = lo + atomicAdd(next_node, 1u);
+    id = __shfl_sync(FV_FULL, id, 0);
+    if (id >= hi) break;
     const int level = g.levels[id];
     __syncwarp();
     for (int c = lane; c < g.pd; c += 32) sq[c] = g.data[size_t(id) * g.pd + c];
@@ -302,7 +310,7 @@ __global__ void __launch_bounds__(256, 2)
 // add_links(target, layer, [source]) (hnsw.rs:294-320) for every edge of the batch.  The warp whose edge was the
 // first pushed on its chain (next == NIL) owns the chain's (target, layer).
 template <bool IS_L2>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, BUILD_BLOCKS_PER_SM)
     hnsw_link_kernel(BuildDev g, const Edge* __restrict__ edges, const uint32_t* __restrict__ edge_cnt,
                      uint32_t edge_cap, uint32_t* __restrict__ head) {
   unsigned char* smem_raw = dyn_smem();
@@ -471,6 +479,7 @@ static int build_on_device(fv_hnsw* h, size_t ef, size_t max_batch, size_t divis
   FV_TRY(d_edges.reserve((edge_cap + 1) * sizeof(Edge)));
   FV_TRY(d_words.reserve(64));
   uint32_t* d_edge_cnt = d_words.as<uint32_t>();
+  uint32_t* d_next_node = d_edge_cnt + 1;
   unsigned long long* d_flags = reinterpret_cast<unsigned long long*>(d_words.as<unsigned char>() + 16);
   cudaStream_t st = ctx->stream;
   FV_CUDA(cudaMemcpyAsync(h->d_data.p, h->data.data(), h->data.size() * 4, cudaMemcpyHostToDevice, st));
@@ -496,9 +505,9 @@ static int build_on_device(fv_hnsw* h, size_t ef, size_t max_batch, size_t divis
   const size_t link_warp = ((size_t(pd) * 8 + 2 * keys_bytes + (nc + m0 + 2 * SRC_CAP + 1) * 4) + 15) & ~size_t(15);
   const size_t budget = std::min<size_t>(ctx->smem_optin, 200 * 1024);
   int W = 8;
-  while (W > 1 && std::max(ins_warp, link_warp) * W > budget / 2) W >>= 1;
+  while (W > 1 && std::max(ins_warp, link_warp) * W > budget / BUILD_BLOCKS_PER_SM) W >>= 1;
   if (std::max(ins_warp, link_warp) * W > budget) return fail(FV_ERR_UNSUPPORTED, "dimension and ef_construction too large for shared memory");
-  const size_t resident_blocks = size_t(ctx->sm_count) * 2;
+  const size_t resident_blocks = size_t(ctx->sm_count) * BUILD_BLOCKS_PER_SM;
   const size_t ins_blocks_max = std::min<size_t>(resident_blocks, (widest + W - 1) / W);
   auto ins = h->metric == FV_L2 ? hnsw_insert_kernel<true> : hnsw_insert_kernel<false>;
   auto lnk = h->metric == FV_L2 ? hnsw_link_kernel<true> : hnsw_link_kernel<false>;
@@ -506,7 +515,7 @@ static int build_on_device(fv_hnsw* h, size_t ef, size_t max_batch, size_t divis
   if (link_warp * W > 40 * 1024) FV_CUDA(cudaFuncSetAttribute(lnk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(link_warp * W)));
 
   int log2slots = 11;
-  while ((size_t(1) << log2slots) < ef * 64 && log2slots < 24) log2slots++;
+  while ((size_t(1) << log2slots) < ef * 128 && log2slots < 24) log2slots++;
   for (int attempt = 0; attempt < 3; ++attempt, log2slots += 2) {
     FV_TRY(d_tables.reserve((ins_blocks_max * W << log2slots) * 4 + 16));
     FV_CUDA(cudaMemsetAsync(h->d_links0.p, 0, h->links0.size() * 4, st));
@@ -515,13 +524,15 @@ static int build_on_device(fv_hnsw* h, size_t ef, size_t max_batch, size_t divis
     FV_CUDA(cudaMemsetAsync(d_words.p, 0, 64, st));
     size_t inserted = 1, top = h->levels[0];
     uint32_t ep = 0;
+    stage_begin(ctx);  // stage 0: uploads and clears; stage 1: the batches
+    stage_mark(ctx);
     while (inserted < n) {
       const size_t b = next_batch(h->levels, inserted, top, max_batch, divisor);
-      FV_CUDA(cudaMemsetAsync(d_edge_cnt, 0, 4, st));
+      FV_CUDA(cudaMemsetAsync(d_edge_cnt, 0, 8, st));  // and the node counter
       const size_t ins_blocks = std::min<size_t>(ins_blocks_max, (b + W - 1) / W);
       ins<<<unsigned(ins_blocks), W * 32, ins_warp * W, st>>>(g, uint32_t(inserted), uint32_t(inserted + b), ep, int(top),
                                                                int(ef), log2slots, d_tables.as<uint32_t>(),
-                                                               d_edges.as<Edge>(), d_edge_cnt, uint32_t(edge_cap),
+                                                               d_edges.as<Edge>(), d_edge_cnt, d_next_node, uint32_t(edge_cap),
                                                                d_head.as<uint32_t>(), d_flags);
       FV_CUDA(cudaGetLastError());
       size_t e_max = 0;
@@ -537,9 +548,11 @@ static int build_on_device(fv_hnsw* h, size_t ef, size_t max_batch, size_t divis
       }
       inserted += b;
     }
+    stage_mark(ctx);
     unsigned long long flags[3] = {0, 0, 0};
     FV_CUDA(cudaMemcpyAsync(flags, d_flags, sizeof(flags), cudaMemcpyDeviceToHost, st));
     FV_CUDA(cudaStreamSynchronize(st));
+    stage_end(ctx);
     FV_TRY(bounds_report_hnsw_build());
     if (flags[2]) return fail(FV_ERR_OVERFLOW, "hnsw build: edge buffer overflow");
     if (flags[0]) {
