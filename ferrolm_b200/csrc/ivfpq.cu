@@ -1106,6 +1106,24 @@ int fv_merge_refine_dev(fv_ctx* ctx, const fv_neighbor* d_adc_parts, const float
 // rank reading the blocks of its slice) and merge them as the reference cuts (ivfpq.rs:285-296); the finished slices
 // are then gathered so that every rank holds the whole result.  Called with the context locked and its stage table
 // open (stages: 0 and 1 empty, 2 local search, 3 candidate exchange, 4 merge, result exchange and unpacking).
+// The gathered result blocks (per slice: per x k neighbours, then per counts; the blocks of a slice's L shards are
+// adjacent and equal) laid out as the caller's arrays, in one launch.
+__global__ void unpack_slices_kernel(const unsigned char* __restrict__ all, size_t rblk, int L, size_t per, size_t k,
+                                     size_t nq, fv_neighbor* __restrict__ out, uint32_t* __restrict__ counts) {
+  const size_t total = nq * k;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total + nq; i += size_t(gridDim.x) * blockDim.x) {
+    if (i < total) {
+      const size_t q = i / k, s = q / per;
+      const fv_neighbor* src = reinterpret_cast<const fv_neighbor*>(all + s * size_t(L) * rblk);
+      out[i] = src[(q - s * per) * k + (i - q * k)];
+    } else if (counts) {
+      const size_t q = i - total, s = q / per;
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(all + s * size_t(L) * rblk + per * k * sizeof(fv_neighbor));
+      counts[q] = src[q - s * per];
+    }
+  }
+}
+
 static int search_grid(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k, size_t nprobe, size_t refine,
                        fv_neighbor* d_out, uint32_t* d_counts, int L) {
   fv_ctx* ctx = ix->ctx;
@@ -1163,14 +1181,12 @@ static int search_grid(fv_ivfpq* ix, const float* d_queries, size_t nq, size_t k
   FV_TRY(ctx->scratch[17].reserve(size_t(world) * rblk));
   unsigned char* all = ctx->scratch[17].as<unsigned char>();
   FV_TRY(fv::comm_all_gather(ctx, res, all, rblk));
-  for (int s = 0; s < Q; ++s) {
-    const size_t slo = std::min(nq, size_t(s) * per), shi = std::min(nq, slo + per);
-    if (shi == slo) continue;
-    const unsigned char* src = all + size_t(s) * size_t(L) * rblk;
-    FV_CUDA(cudaMemcpyAsync(d_out + slo * k, src, (shi - slo) * k * sizeof(fv_neighbor), cudaMemcpyDeviceToDevice, ctx->stream));
-    if (d_counts)
-      FV_CUDA(cudaMemcpyAsync(d_counts + slo, src + per * k * sizeof(fv_neighbor), (shi - slo) * sizeof(uint32_t),
-                              cudaMemcpyDeviceToDevice, ctx->stream));
+  {
+    const size_t items = nq * k + nq;
+    const unsigned blocks = unsigned(std::min<size_t>((items + 255) / 256, size_t(ctx->sm_count) * 8));
+    unpack_slices_kernel<<<blocks, 256, 0, ctx->stream>>>(all, rblk, L, per, k, nq, d_out, d_counts);
+    ctx->stats.launches++;
+    FV_CUDA(cudaGetLastError());
   }
   fv::stage_mark_outer(ctx);  // 4
   FV_CUDA(cudaStreamSynchronize(ctx->stream));
