@@ -24,7 +24,9 @@ def main(argv=None):
     ap.add_argument("--learn")
     ap.add_argument("--n", type=int)
     ap.add_argument("--queries", type=int, default=10_000)
-    ap.add_argument("--threads", type=int, default=0, help="host threads for the HNSW build")
+    ap.add_argument("--threads", type=int, default=0, help="host threads for the HNSW build (with --host-build)")
+    ap.add_argument("--host-build", action="store_true",
+                    help="build the HNSW graph on the host threads as the reference does (default: on the GPU, in batches)")
     ap.add_argument("--m", type=int, default=16)
     ap.add_argument("--ef-construction", type=int, default=200)
     ap.add_argument("--ef", default="16,32,64,128,256")
@@ -88,7 +90,9 @@ def main(argv=None):
     lst = lambda s: [int(x) for x in str(s).split(",")]
     if a.index == "hnsw":
         t = time.perf_counter()
-        h = fv.Hnsw.build(ctx, fv.Metric.L2, dim, base, fv.HnswParams(a.m, a.ef_construction, 1), threads=threads)
+        hp = fv.HnswParams(a.m, a.ef_construction, 1)
+        h = (fv.Hnsw.build(ctx, fv.Metric.L2, dim, base, hp, threads=threads) if a.host_build
+             else fv.Hnsw.build_batched(ctx, fv.Metric.L2, dim, base, hp))
         build = time.perf_counter() - t
         print(f"HNSW over {len(h)} vectors built in {build:.0f} s, mean degree {h.mean_degree():.1f}")
         for ef in lst(a.ef):

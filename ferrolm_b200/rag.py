@@ -14,7 +14,7 @@ from .vector import Context, FlatIndex, Hnsw, HnswParams, Metric
 
 class Retriever:
     def __init__(self, ctx: Context, passage_vectors, passage_doc, hnsw: HnswParams | None = None, ef: int = 64,
-                 build_threads: int = 1):
+                 build_threads: int = 0):
         """passage_vectors: (n, dim) unit-length embeddings; passage_doc[i]: the document of passage i
         (non-decreasing, as rag.rs:98-104 builds it)."""
         v = np.ascontiguousarray(passage_vectors, dtype=np.float32)
@@ -22,7 +22,11 @@ class Retriever:
         self.passage_doc = np.asarray(passage_doc, dtype=np.uint32)
         self.flat = FlatIndex(ctx, Metric.InnerProduct, self.dim)      # rag.rs:111-112
         self.flat.add(v)
-        self.hnsw = Hnsw.build(ctx, Metric.InnerProduct, self.dim, v, hnsw, threads=build_threads) if hnsw else None
+        # the graph is built on the GPU (deterministic batches) unless host threads are asked for
+        self.hnsw = None
+        if hnsw:
+            self.hnsw = (Hnsw.build(ctx, Metric.InnerProduct, self.dim, v, hnsw, threads=build_threads) if build_threads
+                         else Hnsw.build_batched(ctx, Metric.InnerProduct, self.dim, v, hnsw))
         self.ef = ef
 
     def set_ef(self, ef: int):                                          # rag.rs:145-149

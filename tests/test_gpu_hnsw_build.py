@@ -69,6 +69,29 @@ def test_batched_build_on_integer_data_with_distance_ties(fv, oracle, ctx):
     assert g.reachable() >= int(0.95 * o.reachable())
 
 
+def test_batched_build_with_the_widest_lists(fv, oracle, ctx):
+    # m = 64: 128 links on layer 0, so select and the re-selection walk the kept list in four steps of 32 lanes
+    dim = 16
+    base = oracle.testdata(2500, dim, 5)
+    g = fv.Hnsw.build_batched(ctx, L2, dim, base, fv.HnswParams(64, 150, 2), max_batch=300, divisor=4)
+    o = oracle.Hnsw.build_batched(L2, dim, base, m=64, ef_construction=150, seed=2, max_batch=300, divisor=4)
+    assert g.save() == o.save()
+
+
+def test_batched_build_with_hubs_and_duplicate_rows(fv, oracle, ctx):
+    # 40 distinct rows repeated: every batch sends hundreds of new nodes to the same few targets (chains longer than
+    # the 128 sources sorted in shared memory), and all distances between copies are exactly zero
+    dim = 8
+    centres = oracle.testdata(40, dim, 11)
+    rng = np.random.default_rng(4)
+    base = np.ascontiguousarray(centres[rng.integers(0, 40, 3000)])
+    g = fv.Hnsw.build_batched(ctx, L2, dim, base, fv.HnswParams(6, 30, 1), max_batch=1500, divisor=1)
+    o = oracle.Hnsw.build_batched(L2, dim, base, m=6, ef_construction=30, seed=1, max_batch=1500, divisor=1)
+    if ctx.stats()["uncertified"] == 0:
+        assert g.save() == o.save()
+    assert len(g) == 3000
+
+
 def test_batched_build_is_deterministic_and_connected(fv, oracle, ctx):
     # tests/vector.rs:104-125 (text-embedding-like rows) on the GPU build with its suggested batch sizes
     n, nq, dim = 5000, 200, 384
