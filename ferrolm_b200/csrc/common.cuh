@@ -233,6 +233,90 @@ __device__ __forceinline__ float exact_distance(const float* __restrict__ a, con
   return IS_L2 ? s : -s;
 }
 
+// Exact distances to FOUR gathered rows at once, for rows fetched by id (a re-rank).  With one row per lane every
+// load instruction touches 32 different rows, 16 bytes of each, and a row costs one trip to memory per unrolled group
+// of loads.  Here the warp copies four rows into shared memory with asynchronous 16-byte copies (quad_issue: whole
+// rows in flight at once, no registers held, coalesced 512 bytes per instruction), and while the next four are on
+// their way works on the current ones as 4 rows x 8 chain lanes (quad_compute): lane (r, l) runs chain l of row r --
+// elements l, l + 8, ... in order, src/kernels.rs:200-231 -- and the eight lane sums are added in the reference's
+// pairwise order, so the result is bit for bit exact_distance's.  Lane i brings the id of candidate i and whether it
+// has one; a quad is candidates 4 qd .. 4 qd + 3.  A stage buffer holds 4 * quad_stride(pd) floats, 16-byte aligned.
+__host__ __device__ __forceinline__ int quad_stride(int pd) { return ((pd + 31) / 32) * 32 + 8; }  // = 8 mod 32: no bank conflicts
+
+__device__ __forceinline__ void quad_issue(const float* __restrict__ rows, int pd, uint32_t id, bool valid, int qd,
+                                           float* stage) {
+  const int lane = lane_id();
+  const int ts = quad_stride(pd), q4 = pd >> 2;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const uint32_t rid = __shfl_sync(FV_FULL, id, 4 * qd + r);
+    const bool rv = __shfl_sync(FV_FULL, int(valid), 4 * qd + r) != 0;
+    if (rv) {  // (a candidate without a row leaves its part of the stage as it is: its lanes' results are not used)
+      const float4* src = reinterpret_cast<const float4*>(rows + size_t(rid) * pd);
+      const uint32_t dst = uint32_t(__cvta_generic_to_shared(stage + r * ts));
+      for (int c = lane; c < q4; c += 32)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + uint32_t(c) * 16u), "l"(src + c) : "memory");
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+// waits until at most `pending` of this thread's copy groups are still in flight (0 or 1), then lines the warp up
+__device__ __forceinline__ void quad_wait(int pending) {
+  if (pending) asm volatile("cp.async.wait_group 1;" ::: "memory");
+  else asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncwarp();
+}
+// returns, in lanes 4 qd .. 4 qd + 3 of the quad that was staged, the distance of the lane's own candidate (every lane
+// gets the distance of row lane & 3)
+template <bool IS_L2>
+__device__ __forceinline__ float quad_compute(const float* sq, int pd, const float* stage) {
+  const int lane = lane_id();
+  const int ts = quad_stride(pd);
+  const float* b = stage + (lane >> 3) * ts + (lane & 7);
+  const float* a = sq + (lane & 7);
+  float acc = 0.f;
+#pragma unroll 4
+  for (int t = 0; t < pd; t += 8) {
+    if (IS_L2) {
+      const float d = __fsub_rn(a[t], b[t]);
+      acc = __fmaf_rn(d, d, acc);
+    } else {
+      acc = __fmaf_rn(a[t], b[t], acc);
+    }
+  }
+  // hsum8: ((l0 + l4) + (l2 + l6)) + ((l1 + l5) + (l3 + l7)); fadd commutes, so all eight lanes end with that value
+  float s = __fadd_rn(acc, __shfl_xor_sync(FV_FULL, acc, 4));
+  s = __fadd_rn(s, __shfl_xor_sync(FV_FULL, s, 2));
+  s = __fadd_rn(s, __shfl_xor_sync(FV_FULL, s, 1));
+  const float mine = __shfl_sync(FV_FULL, s, (lane & 3) * 8);
+  __syncwarp();  // the stage may be refilled
+  return IS_L2 ? mine : -mine;
+}
+// The distances of up to 32 candidates (one per lane), quads pipelined through two stage buffers.
+template <bool IS_L2>
+__device__ __forceinline__ float quad_distances(const float* sq, const float* __restrict__ rows, int pd, uint32_t id,
+                                                bool valid, float* stage2) {
+  const int lane = lane_id();
+  const int qs = 4 * quad_stride(pd);
+  unsigned quads = 0;  // bit qd: quad qd has a candidate
+  const unsigned act = __ballot_sync(FV_FULL, valid);
+  for (int qd = 0; qd < 8; ++qd)
+    if ((act >> (4 * qd)) & 0xFu) quads |= 1u << qd;
+  float d = INFINITY;
+  int buf = 0;
+  if (quads) quad_issue(rows, pd, id, valid, __ffs(quads) - 1, stage2);
+  while (quads) {
+    const int cur = __ffs(quads) - 1;
+    quads &= quads - 1;
+    if (quads) quad_issue(rows, pd, id, valid, __ffs(quads) - 1, stage2 + (buf ^ 1) * qs);
+    quad_wait(quads ? 1 : 0);
+    const float dv = quad_compute<IS_L2>(sq, pd, stage2 + buf * qs);
+    if ((lane >> 2) == cur) d = dv;
+    buf ^= 1;
+  }
+  return d;
+}
+
 __device__ __forceinline__ float exact_distance(int metric, const float* a, const float* b, int pd) {
   return metric == FV_L2 ? exact_distance<true>(a, b, pd) : exact_distance<false>(a, b, pd);
 }

@@ -942,6 +942,8 @@ __global__ void rerank_kernel(RerankParams p) {
   if (q >= size_t(p.nq)) return;
   float* sq = reinterpret_cast<float*>(smem_raw) + size_t(w) * p.pd;
   u64* list = reinterpret_cast<u64*>(smem_raw + size_t(W) * p.pd * sizeof(float)) + size_t(w) * p.k;
+  float* stage = reinterpret_cast<float*>(smem_raw + ((size_t(W) * (size_t(p.pd) * 4 + size_t(p.k) * 8) + 15) & ~size_t(15))) +
+                 size_t(w) * 8 * quad_stride(p.pd);  // two stage buffers
   for (int c = lane; c < p.pd; c += 32) sq[c] = p.queries[q * size_t(p.pd) + c];
   warp_list_init(list, p.k);
 
@@ -1037,18 +1039,21 @@ __global__ void rerank_kernel(RerankParams p) {
       }
       const unsigned int pj = __shfl_sync(FV_FULL, pre, j), cj = __shfl_sync(FV_FULL, cnt, j);
       const unsigned long long sj = __shfl_sync(FV_FULL, slot, j);
-      u64 key = FV_EMPTY_KEY;
+      u64 key = FV_EMPTY_KEY, ck = 0;
+      uint32_t id = 0;
+      bool have = false;
       if (x < total) {
-        const u64 ck = p.cbuf[sj * size_t(p.ccap) + (x - (pj - cj))];
-        const uint32_t id = key_id(ck);
-        if (id < uint32_t(p.n)) {
-          const float d = p.is_l2 ? exact_distance<true>(sq, p.rows + size_t(id) * p.pd, p.pd)
-                                  : exact_distance<false>(sq, p.rows + size_t(id) * p.pd, p.pd);
-          if (exact_regime && d != key_distance(ck) + qn2) mismatch = true;
-          if (d < INFINITY) key = make_key(d, id + p.id_base);
-        } else {
-          mismatch = true;  // a padded row can only get here through a non-finite score
-        }
+        ck = p.cbuf[sj * size_t(p.ccap) + (x - (pj - cj))];
+        id = key_id(ck);
+        have = id < uint32_t(p.n);
+        if (!have) mismatch = true;  // a padded row can only get here through a non-finite score
+      }
+      // four candidates' rows at a time (asynchronous coalesced gathers, 4 rows x 8 chain lanes)
+      const float d = p.is_l2 ? quad_distances<true>(sq, p.rows, p.pd, id, have, stage)
+                              : quad_distances<false>(sq, p.rows, p.pd, id, have, stage);
+      if (have) {
+        if (exact_regime && d != key_distance(ck) + qn2) mismatch = true;
+        if (d < INFINITY) key = make_key(d, id + p.id_base);
       }
       bound = warp_list_offer(list, p.k, key, bound);
     }
@@ -1528,8 +1533,10 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   rp.retry_ids = ctx->scratch[7].as<uint32_t>();
   rp.retry_count = retry_count;
   int wpb = 8;
-  while (wpb > 1 && size_t(wpb) * (size_t(pd) * 4 + size_t(k) * 8) > 48 * 1024) wpb >>= 1;
-  const size_t rsmem = size_t(wpb) * (size_t(pd) * 4 + size_t(k) * 8);
+  const size_t rwarp = size_t(pd) * 4 + size_t(k) * 8 + size_t(8 * quad_stride(pd)) * 4;  // query, list, two stages of four rows
+  while (wpb > 1 && size_t(wpb) * rwarp + 16 > 72 * 1024) wpb >>= 1;
+  const size_t rsmem = ((size_t(wpb) * (size_t(pd) * 4 + size_t(k) * 8) + 15) & ~size_t(15)) + size_t(wpb) * 8 * quad_stride(pd) * 4;
+  if (rsmem > 48 * 1024) FV_CUDA(cudaFuncSetAttribute(rerank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(rsmem)));
   rerank_kernel<<<unsigned((nq + wpb - 1) / wpb), wpb * 32, rsmem, ctx->stream>>>(rp);
   ctx->stats.launches++;
   FV_CUDA(cudaGetLastError());
