@@ -49,125 +49,6 @@ __device__ __forceinline__ uint32_t head_slot(const BuildDev& g, uint32_t x, int
   return layer == 0 ? x : g.n + g.up_blk[x] + uint32_t(layer - 1);
 }
 
-// search_layer (hnsw.rs:179-226) on `layer`, from the entries best[0..filled) (sorted).  The beam is one sorted list
-// of ef entries with an "expanded" bit each; see TIED_CAP for how ties with the worst kept distance are handled.
-// On return best[0..filled) is the reference's result, nearest first.
-template <bool IS_L2>
-__device__ __forceinline__ void beam_search(const BuildDev& g, int layer, const float* sq, u64* best, int ef,
-                                            uint32_t* tied, uint32_t* table, int log2slots, int& filled, bool& over,
-                                            bool& tie_lost) {
-  const int lane = lane_id();
-  const int slots = 1 << log2slots;
-  const int width = layer == 0 ? g.m0 : g.m;
-  for (int s = lane * 4; s < slots; s += 128) *reinterpret_cast<uint4*>(table + s) = make_uint4(~0u, ~0u, ~0u, ~0u);
-  __syncwarp();
-  for (int e = lane; e < filled; e += 32) {
-    const u64 b = best[e] & ~1ull;
-    best[e] = b;
-    visit(table, log2slots, beam_id(b));
-  }
-  __syncwarp();
-  int visited = filled, cursor = 0, ntied = 0;
-  over = false;
-  for (;;) {
-    int pos = -1;
-    for (int e0 = cursor & ~31; e0 < filled; e0 += 32) {
-      const int e = e0 + lane;
-      const bool open = e >= cursor && e < filled && !(best[e] & 1ull);
-      const unsigned mk = __ballot_sync(FV_FULL, open);
-      if (mk) {
-        pos = e0 + __ffs(mk) - 1;
-        break;
-      }
-    }
-    uint32_t c = 0;
-    if (ntied > 0) {
-      uint32_t tmin = NIL;
-      for (int t = lane; t < ntied; t += 32) tmin = min(tmin, tied[t]);
-      for (int o = 16; o > 0; o >>= 1) tmin = min(tmin, __shfl_xor_sync(FV_FULL, tmin, o));
-      const u64 tkey = (best[ef - 1] & 0xFFFFFFFF00000000ull) | (u64(tmin) << 1);
-      if (pos < 0 || tkey < best[pos]) {
-        __syncwarp();
-        for (int t = lane; t < ntied; t += 32)
-          if (tied[t] == tmin) tied[t] = tied[ntied - 1];
-        __syncwarp();
-        ntied--;
-        pos = -2;
-        c = tmin;
-      }
-    }
-    if (pos == -1) break;
-    if (pos >= 0) {
-      const u64 ck = best[pos];
-      __syncwarp();
-      if (lane == 0) best[pos] = ck | 1ull;
-      __syncwarp();
-      cursor = pos + 1;
-      c = beam_id(ck);
-    }
-    if (!FV_IDX_OK(c, g.n, 1)) break;
-    const uint32_t* row = link_row(g, c, layer);
-    const int cnt = min(int(row[0]), width);
-    for (int c0 = 0; c0 < cnt; c0 += 32) {
-      const int i = c0 + lane;
-      u64 key = FV_EMPTY_KEY;
-      bool fresh = false;
-      uint32_t x = 0;
-      if (i < cnt) {
-        x = row[1 + i];
-        fresh = FV_IDX_OK(x, g.n, 2) && visit(table, log2slots, x);
-      }
-      visited += __popc(__ballot_sync(FV_FULL, fresh));
-      if (fresh) {
-        const char* rowp = reinterpret_cast<const char*>(g.data + size_t(x) * g.pd);
-        for (int b = 0; b < g.pd * 4; b += 128) asm volatile("prefetch.global.L1 [%0];" ::"l"(rowp + b));
-        key = beam_key(exact_distance<IS_L2>(sq, g.data + size_t(x) * g.pd, g.pd), x);
-      }
-      // offered in stored order: admitted while the list is not full, or on a strictly smaller distance
-      u64 bound = best[ef - 1];
-      unsigned pending = __ballot_sync(FV_FULL, fresh);
-      while (pending) {
-        const int src = __ffs(pending) - 1;
-        pending &= pending - 1;
-        const u64 kk = __shfl_sync(FV_FULL, key, src);
-        if ((kk >> 32) < (bound >> 32)) {
-          int below = 0;
-          for (int e0 = 0; e0 < filled; e0 += 32) {
-            const int e = e0 + lane;
-            below += __popc(__ballot_sync(FV_FULL, e < filled && best[e] < kk));
-          }
-          __syncwarp();
-          const bool was_full = filled == ef;
-          warp_list_insert(best, ef, kk);
-          if (filled < ef) filled++;
-          if (below < cursor) cursor = below;
-          const u64 pushed = bound;
-          bound = best[ef - 1];
-          if (was_full) {
-            if ((bound >> 32) < (pushed >> 32)) {
-              ntied = 0;
-            } else if (!(pushed & 1ull)) {
-              if (ntied < TIED_CAP) {
-                __syncwarp();
-                if (lane == 0) tied[ntied] = beam_id(pushed);
-                __syncwarp();
-                ntied++;
-              } else {
-                tie_lost = true;
-              }
-            }
-          }
-        }
-      }
-    }
-    if (visited > (slots >> 1)) {
-      over = true;
-      break;
-    }
-  }
-  __syncwarp();
-}
-
 // select (hnsw.rs:230-242): from candidates sorted nearest first (keys: order bits of the distance above, id at
 // `id_shift` below), keep those farther from every kept one than from the base, up to cap.  `sc` stages the
 // candidate's row.  Returns the number kept (ids in sel[]).
@@ -271,7 +152,10 @@ __global__ void __launch_bounds__(256, BUILD_BLOCKS_PER_SM)
     bool tie_lost = false;
     for (int layer = min(level, top); layer >= 0; --layer) {
       bool over = false;
-      beam_search<IS_L2>(g, layer, sq, best, ef, tied, table, log2slots, filled, over, tie_lost);
+      unsigned long long n_dist = 0, n_exp = 0;  // (not reported by the build)
+      beam_search<IS_L2>(g.data, g.pd, g.n, [&](uint32_t c) { return (const uint32_t*)link_row(g, c, layer); },
+                         layer == 0 ? g.m0 : g.m, sq, best, ef, tied, table, log2slots, filled, over, tie_lost, n_dist,
+                         n_exp);
       if (over) {
         if (lane == 0) atomicAdd(flags, 1ull);
         break;
