@@ -312,6 +312,15 @@ def also_section(fv, oracle, ctx, stream, ix, base, queries, dq, pk, nprobe, ref
         "graph_build": {"gpu_batched_s": round(gpu_build_s, 3), "reachable": h.reachable(),
                         "cpu_oracle_s": round(cpu_build_s, 3), "cpu_threads": threads, "cpu_reachable": cpu_reachable,
                         "note": "m 16, ef_construction 200; seconds include the host-side padding and copies"}}
+    # the reference's ef sweep (src/main.rs:523-524) on the same graph
+    sweep = {}
+    for ef in (16, 32, 128, 256):
+        ms_e = time_gpu(lambda: h.search_batch(dqh, K, ef), stream, 3, warm=1)
+        o_e = h.search_batch(dqh, K, ef)
+        sweep[f"ef{ef}"] = {"queries_per_s": round(hq / (ms_e * 1e-3)), "ms_per_step": round(ms_e, 3),
+                            "recall_at_10": round(float(fv.recall(fv.neighbors_from_tensor(o_e[0]),
+                                                                  o_e[1].cpu().numpy().astype(np.uint32), ht, K)), 4)}
+    out["hnsw_ef64_200k_nodes"]["ef_sweep"] = sweep
     del h, oh, fsub
     # IVF-PQ on the reference's own test generator (tests/vector.rs:11-24: 50 centres, sigma 1), where the compressed
     # distances rank well: one operating point with a recall that says something
@@ -493,18 +502,28 @@ def run_ours(args):
     ms = ev0.elapsed_time(ev1) / args.steps
     steady_launches = launches[0]
     stages = stage_sum / args.steps
-    # ---- end to end: host queries (pinned) in, host results out, every step
-    for _ in range(2):
+    # ---- end to end: host queries (pinned) in, host results out, every step.  A rank of a query-slice grid reads
+    # only its own slice of the batch (fv_ivfpq_search_sharded_dev), so that is what it copies.
+    q_lo, q_hi = 0, NQ
+    if world > 1 and args.workload == "ivfpq" and list_shards < world:
+        slices = world // list_shards
+        per = (NQ + slices - 1) // slices
+        q_lo = min(NQ, (rank // list_shards) * per)
+        q_hi = min(NQ, q_lo + per)
+    q_dev = torch.empty_like(dq)
+
+    def upload():
         with torch.cuda.stream(stream):
-            q = hq.to(f"cuda:{local}", non_blocking=True)
+            q_dev[q_lo:q_hi].copy_(hq[q_lo:q_hi], non_blocking=True)
         stream.synchronize()
-        o, c = step(q)
+        return q_dev
+
+    for _ in range(2):
+        o, c = step(upload())
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        with torch.cuda.stream(stream):
-            q = hq.to(f"cuda:{local}", non_blocking=True)
-        stream.synchronize()
+        q = upload()
         o, c = step(q)
         with torch.cuda.stream(stream):
             h_out.copy_(o, non_blocking=True)
@@ -553,8 +572,9 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "data": "synthetic",
         "dtype": "f32" if args.workload == "hnsw" else "f16 operands, f32 accumulate, f32 exact re-score",
         "config": workload_config(args.workload, world, nprobe, refine, list_shards),
-        "e2e": {"value": NQ / (e2e_ms * 1e-3), "unit": "queries/s", "h2d_bytes_per_step": int(hq.numel() * 4),
-                "d2h_bytes_per_step": int(h_out.numel() * 4), "ms_per_step": e2e_ms},
+        "e2e": {"value": NQ / (e2e_ms * 1e-3), "unit": "queries/s", "h2d_bytes_per_step": int((q_hi - q_lo) * DIM * 4),
+                "d2h_bytes_per_step": int(h_out.numel() * 4), "ms_per_step": e2e_ms,
+                "bytes_note": "per rank: the queries the rank searches in, all results out"},
         "gpu_launches": int(steady_launches), "clocks": clocks, "build_s": build_s,
         "stage_ms": {n: round(float(x), 4) for n, x in zip(names, stages_max)},
         "stage_ms_note": "device time per stage of one step (CUDA events on the library's stream), max over ranks",
