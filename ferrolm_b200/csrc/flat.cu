@@ -286,7 +286,7 @@ int exact_scan(fv_ctx* ctx, int metric, const float* d_rows, size_t n, int pd, c
   // choose queries per warp (QT) and warps per block (W) so that queries + lists fit in shared memory
   int QT = 8, W = 4;
   auto need = [&](int qt, int w) { return size_t(w) * qt * (size_t(pd) * 4 + size_t(L) * 8); };
-  if (nq <= 8) QT = 2;
+  if (nq <= 64) QT = 2;  // few queries: spread them over warps instead of queueing eight behind one
   while (need(QT, W) > budget && W > 1) W >>= 1;
   if (need(QT, W) > budget) QT = 2;
   if (need(QT, W) > budget)
@@ -333,7 +333,9 @@ int exact_scan(fv_ctx* ctx, int metric, const float* d_rows, size_t n, int pd, c
   // aim at about 32 resident warps per SM: each lane streams its own row, so the loads need that many in flight
   const size_t target = size_t(ctx->sm_count) * std::max(4, 32 / W);
   if (qgroups < target) S = (target + qgroups - 1) / qgroups;
-  const size_t max_split = std::max<size_t>(1, n / 1024);
+  // (a handful of queries over a few thousand rows -- the re-run of the uncertified queries of a coarse step -- is
+  // all latency: 128-row splits give the SMs something to do)
+  const size_t max_split = std::max<size_t>(1, n / (nq <= 64 ? 128 : 1024));
   S = std::min(S, max_split);
   S = std::min<size_t>(S, 4096);
   size_t rps = (n + S - 1) / S;

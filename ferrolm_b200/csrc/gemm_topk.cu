@@ -314,8 +314,10 @@ __host__ __device__ __forceinline__ int list_of_row(int MH, int r, int li) {
 // Sampling.  The sample pass scores 1 base row in E; a query's bound is its R-th best sampled score, so about R * E
 // rows of the full set score below it (negative binomial) and the k nearest are among them unless R or more of the
 // k - 1 nearest rows happen to be sampled: probability P(Binomial(k - 1, 1/E) >= R), kept below 2e-5 by the choice
-// of R (5..7).  E follows the base size (about sqrt(n / 1000)): the sample pass costs ~ n / E, the re-rank ~ R * E.
-static constexpr int SAMPLE_R_MIN = 5, SAMPLE_R_MAX = 7;
+// of R (5..13: k = 10 takes 5 to 7, k = 32 up to 13 -- with R capped at 7 a quarter of the queries of a k = 32
+// search over 16384 rows failed their certificate and went to the full-precision scan).  E follows the base size
+// (about sqrt(n / 1000)): the sample pass costs ~ n / E, the re-rank ~ R * E.
+static constexpr int SAMPLE_R_MIN = 5, SAMPLE_R_MAX = 13;
 
 static int pick_sample_every(size_t n) {
   int e = 8;
@@ -1476,7 +1478,10 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   if (mark_stages) stage_mark(ctx);
 
   // sample pass: per query the R (+1) best scores over the sampled rows
-  const int R = pick_sample_r(k, tc->every);
+  // the epilogue keeps its lists in registers, so their length is a template parameter: R is rounded up to the next
+  // instantiated length - 1 (a larger R only loosens the bound)
+  int R = pick_sample_r(k, tc->every);
+  R = R <= 7 ? R : (R <= 9 ? 9 : 13);
   GemmParams gs{};
   fill_params(&gs, ts, tc->ns, nq, SCRATCH_BYTES);
   gs.has_ext = is_l2 ? 1 : 0;
@@ -1487,7 +1492,9 @@ int tc_search(fv_ctx* ctx, TcSide* tc, int metric, const float* d_rows, size_t n
   gs.ext = tc->samp_ext.as<uint16_t>();
   if (R == 5) FV_TRY((launch_gemm<6, false>(ctx, ts, tmA, tmS, gs)));
   else if (R == 6) FV_TRY((launch_gemm<7, false>(ctx, ts, tmA, tmS, gs)));
-  else FV_TRY((launch_gemm<8, false>(ctx, ts, tmA, tmS, gs)));
+  else if (R == 7) FV_TRY((launch_gemm<8, false>(ctx, ts, tmA, tmS, gs)));
+  else if (R == 9) FV_TRY((launch_gemm<10, false>(ctx, ts, tmA, tmS, gs)));
+  else FV_TRY((launch_gemm<14, false>(ctx, ts, tmA, tmS, gs)));
   sample_tau_kernel<<<unsigned((nq_pad + 255) / 256), 256, 0, ctx->stream>>>(gs.cand, ts.MT, ts.parts, ts.grid, ts.segmax,
                                                                              ts.MH, int(nq_pad), R, tau);
   ctx->stats.launches++;
