@@ -43,7 +43,7 @@ def flat_pair(fv, oracle, ctx, metric, dim, base):
     (IP, 384, 8_000, 100, 10),
     (L2, 13, 5_000, 33, 7),        # a dimension that needs padding, ragged sizes
     (L2, 128, 4_500, 17, 100),     # a long result list
-    (L2, 128, 30_000, 300, 32),    # the largest k of the tensor-core path: 1 row in 8 sampled, 7th best as bound
+    (L2, 128, 30_000, 300, 32),    # the largest k of the tensor-core path: 1 row in 8 sampled, 13th best as bound
     (L2, 64, 150_000, 260, 10),    # 1 row in 16 sampled, 6th best as bound; more than one query tile
 ])
 def test_flat_matches_the_oracle(fv, oracle, ctx, metric, dim, n, nq, k, mode):
@@ -59,6 +59,23 @@ def test_flat_matches_the_oracle(fv, oracle, ctx, metric, dim, n, nq, k, mode):
     want, wc = o.search_batch(queries, k)
     eq, total = assert_same_neighbours(got, gc, want, wc, f"flat {metric} {dim}")
     assert eq == total, f"only {eq} of {total} distances bit-equal"
+
+
+def test_flat_32_nearest_of_few_rows_certifies_nearly_every_query(fv, oracle, ctx):
+    # the coarse step of a large IVF-PQ index: 32 nearest of 16384 rows.  The bound is the 13th best of 1 sampled row in
+    # 8; with the 7th best (an earlier limit) a quarter of the queries failed their certificate and were re-run in
+    # full precision.  Results are the oracle's either way; this pins the share that takes the fast path.
+    dim, n, nq, k = 128, 16384, 2000, 32
+    rng = np.random.default_rng(9)
+    base = (oracle.testdata(n, dim, 3) + rng.standard_normal((n, dim)).astype(np.float32) * np.float32(0.25)).astype(np.float32)
+    queries = oracle.testdata(nq, dim, 4)
+    g, o = flat_pair(fv, oracle, ctx, L2, dim, base)
+    g.set_mode(1)
+    got, gc = g.search_batch(queries, k)
+    want, wc = o.search_batch(queries, k)
+    eq, total = assert_same_neighbours(got, gc, want, wc, "flat 32 of 16384")
+    assert eq == total
+    assert ctx.stats()["uncertified"] <= nq // 100
 
 
 @pytest.mark.parametrize("mode", [2, 1])
