@@ -420,6 +420,21 @@ def test_ivfpq_list_major_scan_matches_the_oracle(fv, oracle, ivfpq16_pair, npro
     assert outs[1].tobytes() == outs[2].tobytes() == outs[3].tobytes() == outs[4].tobytes()
 
 
+def test_ivfpq_tensor_pass_with_more_than_1000_pairs_per_list(fv, oracle, ivfpq16_pair):
+    # every query probes every list: 1,200 (query, probe) pairs per list, above the 1,000 from which the pass takes
+    # operand tiles of 256 pairs (two accumulator halves per tile) instead of 128
+    g, o, base, _ = ivfpq16_pair
+    queries = fv.datagen(0, 7, 1200, 128, 32)
+    want, wc = o.search_batch(queries, 10, 24, 10)
+    g.set_scan_mode(3)
+    try:
+        got, gc = g.search_batch(queries, 10, 24, 10)
+    finally:
+        g.set_scan_mode(0)
+    eq, total = assert_same_neighbours(got, gc, want, wc, "ivfpq tensor pass, 256-pair tiles")
+    assert eq == total
+
+
 @pytest.mark.parametrize("mode", [2, 3])
 def test_ivfpq_list_major_scan_reruns_queries_whose_buffer_overflows(fv, oracle, ivfpq16_pair, mode):
     g, o, base, queries = ivfpq16_pair
