@@ -67,15 +67,19 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs: ONE process for all the job's GPUs
+    (rank 0 starts it; a poller per rank, eight on one host, delays the ranks' launches by different amounts and the
+    step waits for the slowest)."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
+    def __init__(self, index):
         self.index, self.lines, self.proc, self.thread = index, [], None, None
 
     def start(self):
+        if self.index is None:  # a rank that leaves the sampling to rank 0
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -484,9 +488,18 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-resident timing (value)
-    sampler = ClockSampler(local)
+    # rank 0 samples every GPU of the job (ranks use GPUs 0..world-1 of the node)
+    sampler = ClockSampler(",".join(str(i) for i in range(world)) if rank == 0 else None)
     sampler.start()
-    for _ in range(max(args.warmup, 3)):
+    n_warm = max(args.warmup, 3)
+    if world > 1 and searcher is not None:
+        # NCCL sets its channels up over the first collectives of a group: a few small sharded searches (not steps of
+        # the workload) before the warm-up steps, so that the warm-up steps are already steady
+        with torch.cuda.stream(stream):
+            for _ in range(8):
+                searcher.search_batch(dq[:64 * world].contiguous(), K, *((nprobe, refine) if args.workload == "ivfpq" else ()))
+        barrier()
+    for _ in range(n_warm):
         step(dq)
     barrier()
     launches[0] = 0
@@ -568,7 +581,7 @@ def run_ours(args):
         names = ["beam search", "keys -> neighbours"]
     line = {
         "metric": METRIC, "value": NQ / (ms * 1e-3), "unit": "queries/s",
-        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "n_gpus": world, "steps": args.steps, "warmup": n_warm, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "data": "synthetic",
         "dtype": "f32" if args.workload == "hnsw" else "f16 operands, f32 accumulate, f32 exact re-score",
         "config": workload_config(args.workload, world, nprobe, refine, list_shards),
