@@ -116,6 +116,21 @@ def test_batched_build_is_deterministic_and_connected(fv, oracle, ctx):
     assert o.save() == h.save()
 
 
+def test_batched_build_at_the_benchmark_parameters(fv, oracle, ctx):
+    # the benchmark's data (clipped-integer Gaussian mixture, 128 dimensions), m 16, ef_construction 200, the default
+    # batches (up to 8192 nodes, 1/32 of the graph): 60,000 nodes, the largest the single-threaded oracle builds in
+    # about ten seconds
+    dim, n = 128, 60_000
+    base = fv.datagen(0, 1, n, dim, 256)
+    g = fv.Hnsw.build_batched(ctx, L2, dim, base, fv.HnswParams())
+    assert ctx.stats()["regrown"] == 0
+    o = oracle.Hnsw.build_batched(L2, dim, base, m=16, ef_construction=200, seed=1)
+    if ctx.stats()["uncertified"] == 0:  # no search lost entries of its tie list: the graphs are the same
+        assert g.save() == o.save()
+    else:
+        assert g.reachable() >= int(0.99 * o.reachable())
+
+
 def test_batched_build_edge_cases(fv, oracle, ctx):
     dim = 8
     one = oracle.testdata(1, dim, 1)
