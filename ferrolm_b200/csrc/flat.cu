@@ -52,22 +52,37 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
   for (int qi = 0; qi < QT; ++qi) bound[qi] = FV_EMPTY_KEY;
 
-  for (size_t r0 = r_begin; r0 < r_end; r0 += 32) {
+  // TILE: two buffers; the copy of the next 32 rows (asynchronous, 16 bytes per request, rows past the end filled
+  // with zeros) is in flight while the current 32 are worked on
+  const int tile_floats = 32 * tstride;
+  auto stage_rows = [&](size_t r0, float* dst) {
+    const int q4 = pd >> 2;
+    for (int i = threadIdx.x; i < 32 * q4; i += blockDim.x) {
+      const int tr = i / q4, c4 = i - tr * q4;
+      const bool in = r0 + tr < r_end;
+      const float4* src = reinterpret_cast<const float4*>(rows + (in ? r0 + tr : r_begin) * size_t(pd)) + c4;
+      const uint32_t d = uint32_t(__cvta_generic_to_shared(dst + tr * tstride + c4 * 4));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(in ? 16 : 0) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (TILE && r_begin < r_end) stage_rows(r_begin, tile);
+  int buf = 0;
+  for (size_t r0 = r_begin; r0 < r_end; r0 += 32, buf ^= 1) {
     const size_t row = r0 + lane;
     const bool valid = row < r_end;
+    const float* cur_tile = tile + buf * tile_floats;
     if (TILE) {
-      __syncthreads();  // everybody is done with the previous step's rows
-      const int q4 = pd >> 2;
-      for (int i = threadIdx.x; i < 32 * q4; i += blockDim.x) {
-        const int tr = i / q4, c4 = i - tr * q4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r0 + tr < r_end) v = __ldg(reinterpret_cast<const float4*>(rows + (r0 + tr) * size_t(pd)) + c4);
-        *reinterpret_cast<float4*>(tile + tr * tstride + c4 * 4) = v;
+      if (r0 + 32 < r_end) {
+        stage_rows(r0 + 32, tile + (buf ^ 1) * tile_floats);  // (its last readers passed the barrier below one step ago)
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
       }
-      __syncthreads();
-      if (nqw == 0) continue;
+      __syncthreads();  // this step's rows have landed, for every thread's copies
     }
-    const float4* b4 = TILE ? reinterpret_cast<const float4*>(tile + lane * tstride)
+    if (!TILE || nqw > 0) {
+    const float4* b4 = TILE ? reinterpret_cast<const float4*>(cur_tile + lane * tstride)
                             : reinterpret_cast<const float4*>(rows + (valid ? row : r_begin) * size_t(pd));
     float acc[QT][8];
 #pragma unroll
@@ -97,6 +112,8 @@ __global__ void __launch_bounds__(128)
         }
       }
     }
+    }
+    if (TILE) __syncthreads();  // everybody is done with this buffer before the step after next refills it
   }
   __syncwarp();
   if (dense || nqw == 0) return;
@@ -262,10 +279,10 @@ static int launch_scan(fv_ctx* ctx, bool is_l2, dim3 grid, int threads, size_t s
                        const float* q, size_t q_stride, const uint32_t* qids, size_t nq, int L, bool prefilter,
                        uint32_t id_base, size_t rps, u64* parts, u64* dense = nullptr, size_t dense_stride = 0) {
   // the row tile goes behind the queries and lists when the shared memory of an SM still holds four such blocks
-  const size_t tile_bytes = size_t(32) * (size_t(pd) + 4) * sizeof(float);
+  const size_t tile_bytes = 2 * size_t(32) * (size_t(pd) + 4) * sizeof(float);  // two buffers
   const size_t with_tile = ((smem + 15) & ~size_t(15)) + tile_bytes;
   // (only for full blocks: a single warp that scans a long run of rows for a few queries streams them faster itself)
-  const bool tiled = with_tile <= 56 * 1024 && threads >= 128;
+  const bool tiled = with_tile <= 72 * 1024 && threads >= 128;
   auto k = is_l2 ? (tiled ? exact_scan_kernel<QT, true, true> : exact_scan_kernel<QT, true, false>)
                  : (tiled ? exact_scan_kernel<QT, false, true> : exact_scan_kernel<QT, false, false>);
   if (tiled) smem = with_tile;
