@@ -841,12 +841,25 @@ __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __res
     // lane i looks up pair s0 + i (one round of dependent loads for 32 pairs instead of one per pair) ...
     uint32_t my_t0 = 0, my_t1 = 0, my_rt = 0;
     float my_add = 0.f;
+    // (the first two tasks of the pair's tile -- most lists are one or two segments long -- are looked up here too:
+    // minima offset, or none when the pair's row lies beyond the task's rows, and the count of minima per row)
+    uint32_t my_moff[2] = {0xFFFFFFFFu, 0xFFFFFFFFu};
+    int my_cnt[2] = {0, 0};
     if (s0 + lane < np) {
       const uint32_t arow = q_rows[q * size_t(q_slots) + s0 + lane];
       my_rt = arow & ((1u << tile_shift) - 1u);
       my_t0 = tile_task0[arow >> tile_shift];
       my_t1 = tile_task0[(arow >> tile_shift) + 1];
       my_add = add[arow];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (my_t0 + u < my_t1) {
+          const uint32_t t = my_t0 + u;
+          const uint32_t mo = task_moff[t], tr = task_rows[t];
+          my_cnt[u] = int(tasks[t].z & 0xFFFFu) * 8;
+          my_moff[u] = my_rt < tr ? mo : 0xFFFFFFFFu;
+        }
+      }
     }
     // ... and the warp copies their minima, one pair and one of its tile's tasks (list segments) after the other
     const int np32 = min(32, np - s0);
@@ -854,10 +867,20 @@ __global__ void __launch_bounds__(128) tc_bound_select_kernel(const float* __res
       const uint32_t t0 = __shfl_sync(FV_FULL, my_t0, j), t1 = __shfl_sync(FV_FULL, my_t1, j);
       const uint32_t rt = __shfl_sync(FV_FULL, my_rt, j);
       const float ad = __shfl_sync(FV_FULL, my_add, j);
+      const uint32_t mo0 = __shfl_sync(FV_FULL, my_moff[0], j), mo1 = __shfl_sync(FV_FULL, my_moff[1], j);
+      const int cn0 = __shfl_sync(FV_FULL, my_cnt[0], j), cn1 = __shfl_sync(FV_FULL, my_cnt[1], j);
       for (uint32_t t = t0; t < t1 && n < vcap; ++t) {
-        const uint32_t moff = task_moff[t];
-        if (moff == 0xFFFFFFFFu || rt >= task_rows[t]) continue;
-        const int cnt = int(tasks[t].z & 0xFFFFu) * 8;
+        uint32_t moff;
+        int cnt;
+        if (t - t0 < 2u) {
+          moff = t == t0 ? mo0 : mo1;
+          cnt = t == t0 ? cn0 : cn1;
+          if (moff == 0xFFFFFFFFu) continue;
+        } else {
+          moff = task_moff[t];
+          if (moff == 0xFFFFFFFFu || rt >= task_rows[t]) continue;
+          cnt = int(tasks[t].z & 0xFFFFu) * 8;
+        }
         const float* src = minima + size_t(moff) + size_t(rt) * cnt;
         const int room = min(cnt, vcap - n);
         for (int i = lane; i < room; i += 32) {
