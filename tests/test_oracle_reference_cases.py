@@ -158,6 +158,22 @@ def test_parallel_hnsw_build_keeps_the_graph_connected(oracle):
     assert oracle.recall(out, counts, t, 10) >= 0.999
 
 
+def test_batched_hnsw_build_with_batches_of_one_is_the_single_thread_build(oracle):
+    # the batch-synchronous order the GPU construction runs (and is compared with, byte for byte, in the GPU tests) is
+    # pinned to the reference's own order where the two must coincide: one node per batch
+    dim = 24
+    base = oracle.testdata(2500, dim, 5)
+    for metric in (oracle.L2, oracle.INNER_PRODUCT):
+        v = oracle.normalize(base) if metric == oracle.INNER_PRODUCT else base
+        seq = oracle.Hnsw.build(metric, dim, v, m=8, ef_construction=40, seed=3, threads=1)
+        one = oracle.Hnsw.build_batched(metric, dim, v, m=8, ef_construction=40, seed=3, max_batch=1, divisor=1)
+        assert one.save() == seq.save()
+        wide = oracle.Hnsw.build_batched(metric, dim, v, m=8, ef_construction=40, seed=3, max_batch=256, divisor=8)
+        again = oracle.Hnsw.build_batched(metric, dim, v, m=8, ef_construction=40, seed=3, max_batch=256, divisor=8)
+        assert wide.save() == again.save() and wide.save() != seq.save()
+        assert abs(wide.reachable() - seq.reachable()) <= 25 and abs(wide.mean_degree() - seq.mean_degree()) < 0.5
+
+
 def test_index_files_reject_damage(oracle):
     # src/vector/io.rs:82, hnsw.rs:425-452, ivfpq.rs:355-357
     base = oracle.testdata(300, 8, 1)
