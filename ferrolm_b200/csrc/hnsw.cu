@@ -43,7 +43,8 @@ template <bool IS_L2>
 __global__ void __launch_bounds__(256, 4)
     hnsw_search_kernel(HnswDev g, const float* __restrict__ queries, const uint32_t* __restrict__ qids, size_t nq, int k,
                        int ef, int log2slots, uint32_t* __restrict__ global_tables, u64* __restrict__ out_keys,
-                       uint32_t* __restrict__ overflow, unsigned long long* __restrict__ work) {
+                       uint32_t* __restrict__ overflow, unsigned long long* __restrict__ work,
+                       unsigned int* __restrict__ next_query) {
   unsigned char* smem_raw = dyn_smem();
   const int W = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = 1 << log2slots;
@@ -56,10 +57,15 @@ __global__ void __launch_bounds__(256, 4)
   const size_t gw = size_t(blockIdx.x) * W + w;
   uint32_t* table = global_tables ? global_tables + gw * size_t(slots)
                                   : reinterpret_cast<uint32_t*>(mine + size_t(g.pd) * 4 + list_bytes);
-  const size_t total_warps = size_t(gridDim.x) * W;
   unsigned long long n_dist = 0, n_exp = 0, n_tie_lost = 0;
 
-  for (size_t qi = gw; qi < nq; qi += total_warps) {
+  // Queries are drawn from a counter (zero at launch): a batch gives every resident warp two or three of them and
+  // they differ in length, so a fixed deal leaves the warps that drew three long ones running alone at the end.
+  for (;;) {
+    size_t qi = 0;
+    if (lane == 0) qi = atomicAdd(next_query, 1u);
+    qi = __shfl_sync(FV_FULL, qi, 0);
+    if (qi >= nq) break;
     const size_t qsrc = qids ? size_t(qids[qi]) : qi;
     const unsigned long long n_dist0 = n_dist, n_exp0 = n_exp;  // a query that overflows its table is re-run: its work counts once
     for (int c = lane; c < g.pd; c += 32) sq[c] = queries[qsrc * size_t(g.pd) + c];
@@ -550,8 +556,10 @@ static int hnsw_search_dev(fv_hnsw* h, const float* d_queries, size_t nq, size_t
     auto kern = h->metric == FV_L2 ? hnsw_search_kernel<true> : hnsw_search_kernel<false>;
     const size_t smem = per_warp * W;
     if (smem > 40 * 1024) FV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    unsigned int* d_next = reinterpret_cast<unsigned int*>(ctx->d_flags + 32);
+    FV_CUDA(cudaMemsetAsync(d_next, 0, sizeof(unsigned int), ctx->stream));
     kern<<<unsigned(blocks), W * 32, smem, ctx->stream>>>(g, q, d_qids, active, int(k), int(ef), log2slots, tables, keys,
-                                                         d_over, d_work);
+                                                         d_over, d_work, d_next);
     ctx->stats.launches++;
     FV_CUDA(cudaGetLastError());
     FV_CUDA(cudaMemcpyAsync(h_over.data(), d_over, active * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
